@@ -1,0 +1,691 @@
+"""The training loop: own implementation of what the reference inherits from
+``transformers.Trainer`` (trl/trainer/base_trainer.py:67 ``class _BaseTrainer(Trainer)``).
+
+Hook names are kept (``compute_loss``, ``training_step``, ``_prepare_inputs``,
+``get_train_dataloader``, ``_get_train_sampler``, ``prediction_step``, ``log``,
+``_save_checkpoint``, ``evaluate``, ``save_model``) so subclasses written for the
+reference's loop read the same.  Checkpoints use the Hugging Face layout:
+``checkpoint-<step>/{config.json, model.safetensors, trainer_state.json,
+optimizer*.pt, scheduler.pt, rng_state_<rank>.pth, training_args.json}``.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+import random
+import re
+import shutil
+import time
+from collections import defaultdict
+from typing import Any, Callable, Optional
+
+import numpy as np
+import torch
+import torch.nn as nn
+
+from ..parallel import dist as D
+from ..parallel.engine import TrainEngine
+from .optim import LRScheduler, lr_lambda_for
+from .state import (CallbackHandler, DefaultFlowCallback, PrinterCallback, TrainerCallback, TrainerControl,
+                    TrainerState)
+from .training_args import TrainingArguments
+
+PREFIX_CHECKPOINT_DIR = "checkpoint"
+
+
+def set_seed(seed: int, deterministic: bool = False):
+    random.seed(seed)
+    np.random.seed(seed % (2**32))
+    torch.manual_seed(seed)
+    if torch.cuda.is_available():
+        torch.cuda.manual_seed_all(seed)
+    if deterministic:
+        torch.use_deterministic_algorithms(True, warn_only=True)
+
+
+class TrainOutput(tuple):
+    def __new__(cls, global_step, training_loss, metrics):
+        o = super().__new__(cls, (global_step, training_loss, metrics))
+        o.global_step, o.training_loss, o.metrics = global_step, training_loss, metrics
+        return o
+
+
+class ShardedBatchSampler:
+    """Global batches of ``batch_size * world`` indices; rank r takes slice r (what
+    accelerate's BatchSamplerShard does with ``split_batches=False``)."""
+
+    def __init__(self, sampler, batch_size: int, drop_last: bool, rank: int, world: int, shard: bool = True):
+        self.sampler, self.bs, self.drop_last = sampler, batch_size, drop_last
+        self.rank, self.world = (rank, world) if shard else (0, 1)
+
+    def __iter__(self):
+        g = self.bs * self.world
+        buf = []
+        first = None
+        for i in self.sampler:
+            buf.append(i)
+            if len(buf) == g:
+                first = first or list(buf)
+                yield buf[self.rank * self.bs:(self.rank + 1) * self.bs]
+                buf = []
+        if buf and not self.drop_last:
+            # pad the tail by cycling from the start so every rank gets a (non-empty) batch
+            src = first or list(buf)
+            while len(buf) % self.world != 0 or len(buf) < self.world:
+                buf.append(src[len(buf) % len(src)])
+            per = len(buf) // self.world
+            yield buf[self.rank * per:(self.rank + 1) * per]
+
+    def __len__(self):
+        n = len(self.sampler)
+        g = self.bs * self.world
+        return n // g if self.drop_last else math.ceil(n / g)
+
+
+class SeededRandomSampler:
+    def __init__(self, n: int, seed: int):
+        self.n, self.seed, self.epoch = n, seed, 0
+
+    def set_epoch(self, e):
+        self.epoch = e
+
+    def __iter__(self):
+        g = torch.Generator()
+        g.manual_seed(self.seed + self.epoch)
+        return iter(torch.randperm(self.n, generator=g).tolist())
+
+    def __len__(self):
+        return self.n
+
+
+class DataLoaderLite:
+    """Minimal map-style / iterable loader (single process; collate on the host)."""
+
+    def __init__(self, dataset, batch_sampler=None, collate_fn=None, batch_size=None, rank=0, world=1,
+                 pin_memory=False):
+        self.dataset, self.batch_sampler, self.collate_fn = dataset, batch_sampler, collate_fn or (lambda x: x)
+        self.batch_size, self.rank, self.world, self.pin = batch_size, rank, world, pin_memory
+
+    def __iter__(self):
+        if self.batch_sampler is not None:
+            for idxs in self.batch_sampler:
+                yield self._finish(self.collate_fn([self.dataset[int(i)] for i in idxs]))
+        else:  # iterable dataset: every rank reads the stream, keeps its slice
+            buf = []
+            g = self.batch_size * self.world
+            for ex in self.dataset:
+                buf.append(ex)
+                if len(buf) == g:
+                    yield self._finish(self.collate_fn(buf[self.rank * self.batch_size:(self.rank + 1) * self.batch_size]))
+                    buf = []
+
+    def _finish(self, batch):
+        if self.pin and isinstance(batch, dict):
+            batch = {k: (v.pin_memory() if torch.is_tensor(v) else v) for k, v in batch.items()}
+        return batch
+
+    def __len__(self):
+        if self.batch_sampler is not None:
+            return len(self.batch_sampler)
+        raise TypeError("iterable dataset has no length")
+
+    def set_epoch(self, e):
+        s = getattr(self.batch_sampler, "sampler", None)
+        if hasattr(s, "set_epoch"):
+            s.set_epoch(e)
+
+
+class JsonlSink(TrainerCallback):
+    """``report_to=["jsonl"]``: one JSON object per log call under ``output_dir/logs.jsonl``."""
+
+    def on_log(self, args, state, control, logs=None, **kw):
+        if state.is_world_process_zero and logs:
+            os.makedirs(args.output_dir, exist_ok=True)
+            with open(os.path.join(args.output_dir, "logs.jsonl"), "a") as f:
+                f.write(json.dumps({"step": state.global_step, **logs}, default=float) + "\n")
+
+
+class TensorBoardSink(TrainerCallback):
+    def __init__(self):
+        self.w = None
+
+    def on_log(self, args, state, control, logs=None, **kw):
+        if not state.is_world_process_zero or not logs:
+            return
+        if self.w is None:
+            try:
+                from torch.utils.tensorboard import SummaryWriter
+
+                self.w = SummaryWriter(args.logging_dir or os.path.join(args.output_dir, "runs"))
+            except Exception:
+                self.w = False
+        if self.w:
+            for k, v in logs.items():
+                if isinstance(v, (int, float)):
+                    self.w.add_scalar(k, v, state.global_step)
+
+
+_SINKS = {"jsonl": JsonlSink, "tensorboard": TensorBoardSink}
+
+
+class Trainer:
+    _tag_names: list[str] = []
+    _name = "Trainer"
+    model_accepts_loss_kwargs = True
+
+    def __init__(self, model=None, args: TrainingArguments | None = None, data_collator=None, train_dataset=None,
+                 eval_dataset=None, processing_class=None, compute_loss_func=None, compute_metrics=None,
+                 callbacks=None, optimizers=(None, None), optimizer_cls_and_kwargs=None,
+                 preprocess_logits_for_metrics=None, model_init=None, tokenizer=None):
+        self.args = args or TrainingArguments()
+        D.init_process_group(self.args.use_cpu, self.args.ddp_timeout)
+        set_seed(self.args.seed, self.args.full_determinism)
+        self.model = model
+        self.data_collator = data_collator
+        self.train_dataset, self.eval_dataset = train_dataset, eval_dataset
+        self.processing_class = processing_class or tokenizer
+        self.compute_loss_func, self.compute_metrics = compute_loss_func, compute_metrics
+        self.preprocess_logits_for_metrics = preprocess_logits_for_metrics
+        self.state = TrainerState(is_local_process_zero=D.local_rank() == 0, is_world_process_zero=D.is_main())
+        self.control = TrainerControl()
+        self.engine: TrainEngine | None = None
+        self.lr_scheduler: LRScheduler | None = None
+        self.optimizer = None
+        self._metrics = {"train": defaultdict(list), "eval": defaultdict(list)}
+        self._train_batch_size = self.args.per_device_train_batch_size
+        self.is_in_train = False
+        self._place_model()
+        cbs = [DefaultFlowCallback()] + list(callbacks or [])
+        for r in self.args.report_to:
+            if r in _SINKS:
+                cbs.append(_SINKS[r]())
+        if not any(isinstance(c, PrinterCallback) for c in cbs) and self.args.disable_tqdm:
+            cbs.append(PrinterCallback())
+        self.callback_handler = CallbackHandler(cbs, self.model, self.processing_class, None, None)
+        self.control = self.callback_handler.call_event("on_init_end", self.args, self.state, self.control)
+
+    # ---- model placement / precision ---------------------------------------------
+    def _place_model(self):
+        if self.model is None:
+            return
+        dev = self.args.device
+        if dev.type == "cuda":
+            torch.cuda.set_device(dev)
+            dt = torch.bfloat16 if self.args.bf16 else (torch.float16 if self.args.fp16 else None)
+            self.model.to(device=dev, dtype=dt) if dt is not None else self.model.to(dev)
+        if self.args.gradient_checkpointing and hasattr(self.model, "gradient_checkpointing_enable"):
+            self.model.gradient_checkpointing_enable(self.args.gradient_checkpointing_kwargs)
+
+    @property
+    def accelerator(self):
+        """Small shim exposing the accelerate calls subclasses and callbacks use."""
+        return _AcceleratorShim(self)
+
+    @property
+    def tokenizer(self):
+        return self.processing_class
+
+    def add_callback(self, cb):
+        self.callback_handler.add_callback(cb)
+
+    def pop_callback(self, cb):
+        return self.callback_handler.pop_callback(cb)
+
+    def remove_callback(self, cb):
+        self.callback_handler.remove_callback(cb)
+
+    def is_world_process_zero(self):
+        return D.is_main()
+
+    def is_local_process_zero(self):
+        return D.local_rank() == 0
+
+    # ---- data -----------------------------------------------------------------------
+    def _get_train_sampler(self, dataset=None):
+        ds = dataset if dataset is not None else self.train_dataset
+        if getattr(self.args, "train_sampling_strategy", "random") == "sequential":
+            return range(len(ds))
+        seed = self.args.data_seed if self.args.data_seed is not None else self.args.seed
+        return SeededRandomSampler(len(ds), seed)
+
+    def _get_eval_sampler(self, dataset):
+        return range(len(dataset))
+
+    def _shard_train_batches(self) -> bool:
+        return True
+
+    def get_train_dataloader(self):
+        ds = self.train_dataset
+        if ds is None:
+            raise ValueError("Trainer: training requires a train_dataset.")
+        if not hasattr(ds, "__len__") or not hasattr(ds, "__getitem__"):
+            return DataLoaderLite(ds, None, self.data_collator, self._train_batch_size, D.rank(), D.world_size())
+        bs = ShardedBatchSampler(self._get_train_sampler(ds), self._train_batch_size, self.args.dataloader_drop_last,
+                                 D.rank(), D.world_size(), self._shard_train_batches())
+        return DataLoaderLite(ds, bs, self.data_collator,
+                              pin_memory=self.args.dataloader_pin_memory and self.args.device.type == "cuda")
+
+    def get_eval_dataloader(self, eval_dataset=None):
+        ds = eval_dataset if eval_dataset is not None else self.eval_dataset
+        if isinstance(ds, str):
+            ds = self.eval_dataset[ds]
+        bs = ShardedBatchSampler(self._get_eval_sampler(ds), self.args.per_device_eval_batch_size, False,
+                                 D.rank(), D.world_size())
+        return DataLoaderLite(ds, bs, self.data_collator)
+
+    def _prepare_input(self, v):
+        if torch.is_tensor(v):
+            return v.to(self.args.device, non_blocking=True)
+        if isinstance(v, dict):
+            return {k: self._prepare_input(x) for k, x in v.items()}
+        if isinstance(v, (list, tuple)) and v and torch.is_tensor(v[0]):
+            return type(v)(self._prepare_input(x) for x in v)
+        return v
+
+    def _prepare_inputs(self, inputs):
+        return self._prepare_input(inputs)
+
+    # ---- optimizer --------------------------------------------------------------------
+    def create_optimizer_and_scheduler(self, num_training_steps: int):
+        a = self.args
+        if self.engine is None:
+            self.engine = self._create_engine()
+        self.optimizer = self.engine
+        warm = a.get_warmup_steps(num_training_steps)
+        self.lr_scheduler = LRScheduler(a.learning_rate, lr_lambda_for(a.lr_scheduler_type, warm, num_training_steps,
+                                                                       **(a.lr_scheduler_kwargs or {})))
+        self.callback_handler.optimizer, self.callback_handler.lr_scheduler = self.engine, self.lr_scheduler
+
+    def _create_engine(self) -> TrainEngine:
+        a = self.args
+        mode = a.shard_mode
+        if mode == "full_shard" and D.world_size() > 1:
+            from ..parallel.fullshard import FullShardEngine
+
+            return FullShardEngine(self.model, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
+                                   weight_decay=a.weight_decay, offload_activations=a.activation_offloading)
+        return TrainEngine(self.model, mode=mode, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
+                           weight_decay=a.weight_decay)
+
+    def _get_learning_rate(self) -> float:
+        return self.lr_scheduler.get_last_lr()[0]
+
+    # ---- loss ---------------------------------------------------------------------------
+    def compute_loss(self, model, inputs, return_outputs=False, num_items_in_batch=None):
+        labels = inputs.get("labels") if self.compute_loss_func is not None else None
+        outputs = model(**inputs)
+        if self.compute_loss_func is not None:
+            loss = self.compute_loss_func(outputs, labels, num_items_in_batch=num_items_in_batch)
+        else:
+            loss = outputs["loss"] if isinstance(outputs, dict) else outputs.loss
+        return (loss, outputs) if return_outputs else loss
+
+    def training_step(self, model, inputs, num_items_in_batch=None):
+        model.train()
+        inputs = self._prepare_inputs(inputs)
+        loss = self.compute_loss(model, inputs, num_items_in_batch=num_items_in_batch)
+        if (not self.model_accepts_loss_kwargs or num_items_in_batch is None) and self.compute_loss_func is None:
+            loss = loss / self.current_gradient_accumulation_steps
+        self.engine.backward(loss)
+        return loss.detach()
+
+    def _count_items(self, batches) -> Optional[torch.Tensor]:
+        """Global number of supervised tokens over the accumulation window (HF ``num_items_in_batch``)."""
+        try:
+            n = sum(int((b["labels"] != -100).sum()) for b in batches)
+        except (TypeError, KeyError):
+            return None
+        t = torch.tensor(n, dtype=torch.long, device=self.args.device)
+        if self.args.average_tokens_across_devices and D.world_size() > 1:
+            D.all_reduce(t, "sum")
+        return t
+
+    # ---- main loop ------------------------------------------------------------------------
+    def train(self, resume_from_checkpoint: str | bool | None = None, **kw):
+        a = self.args
+        self.is_in_train = True
+        resume_from_checkpoint = resume_from_checkpoint if resume_from_checkpoint is not None else a.resume_from_checkpoint
+        if resume_from_checkpoint is True:
+            resume_from_checkpoint = get_last_checkpoint(a.output_dir)
+            if resume_from_checkpoint is None:
+                raise ValueError(f"No valid checkpoint found in output directory ({a.output_dir})")
+        loader = self.get_train_dataloader()
+        self.callback_handler.train_dataloader = loader
+        ga = a.gradient_accumulation_steps
+        try:
+            n_batches = len(loader)
+            steps_per_epoch = max(1, n_batches // ga + int(n_batches % ga > 0))
+        except TypeError:
+            n_batches, steps_per_epoch = None, None
+        if a.max_steps > 0:
+            max_steps = a.max_steps
+            epochs = math.ceil(max_steps / steps_per_epoch) if steps_per_epoch else 10**9
+        else:
+            if steps_per_epoch is None:
+                raise ValueError("max_steps must be set for datasets without a length")
+            max_steps = math.ceil(a.num_train_epochs * steps_per_epoch)
+            epochs = math.ceil(a.num_train_epochs)
+        st = self.state
+        st.max_steps, st.num_train_epochs = max_steps, epochs
+        st.train_batch_size = self._train_batch_size
+        for name in ("logging_steps", "eval_steps", "save_steps"):
+            v = getattr(a, name)
+            if v is not None:
+                setattr(st, name, max(1, int(v * max_steps)) if v < 1 else int(v))
+        self.create_optimizer_and_scheduler(max_steps)
+        start_epoch, skip_batches = 0, 0
+        if resume_from_checkpoint:
+            self._load_from_checkpoint(resume_from_checkpoint)
+            st = self.state
+            st.max_steps, st.num_train_epochs = max_steps, epochs
+            if steps_per_epoch and not a.ignore_data_skip:
+                start_epoch = st.global_step // steps_per_epoch
+                skip_batches = (st.global_step % steps_per_epoch) * ga
+            elif steps_per_epoch:
+                start_epoch = st.global_step // steps_per_epoch
+        self.control = self.callback_handler.call_event("on_train_begin", a, st, self.control)
+        if a.eval_on_start:
+            self.evaluate()
+        tr_loss = torch.zeros((), device=a.device)
+        self._total_loss_scalar, self._logged_step = 0.0, st.global_step
+        t_start = time.time()
+        self.engine.zero_grad()
+        grad_norm = None
+        for epoch in range(start_epoch, epochs):
+            loader.set_epoch(epoch) if hasattr(loader, "set_epoch") else None
+            self.control = self.callback_handler.call_event("on_epoch_begin", a, st, self.control)
+            it = iter(loader)
+            if epoch == start_epoch and skip_batches:
+                for _ in range(skip_batches):
+                    next(it, None)
+            step_in_epoch = skip_batches // ga if epoch == start_epoch else 0
+            exhausted = False
+            while not exhausted:
+                batches = []
+                for _ in range(ga):
+                    b = next(it, None)
+                    if b is None:
+                        exhausted = True
+                        break
+                    batches.append(b)
+                if not batches:
+                    break
+                self.current_gradient_accumulation_steps = len(batches)
+                n_items = self._count_items(batches)
+                self.control = self.callback_handler.call_event("on_step_begin", a, st, self.control)
+                for i, b in enumerate(batches):
+                    loss = self.training_step(self.model, b, n_items)
+                    if a.logging_nan_inf_filter and not bool(torch.isfinite(loss)):
+                        tr_loss += tr_loss / max(1, 1 + st.global_step - self._logged_step)
+                    else:
+                        tr_loss += loss
+                    if i < len(batches) - 1:
+                        self.control = self.callback_handler.call_event("on_substep_end", a, st, self.control)
+                self.control = self.callback_handler.call_event("on_pre_optimizer_step", a, st, self.control)
+                lr = self._get_learning_rate()
+                grad_norm = self.engine.step(lr, a.max_grad_norm)
+                self.control = self.callback_handler.call_event("on_optimizer_step", a, st, self.control)
+                self.lr_scheduler.step()
+                self.engine.zero_grad()
+                st.global_step += 1
+                step_in_epoch += 1
+                st.epoch = epoch + (step_in_epoch / steps_per_epoch if steps_per_epoch else 0)
+                self.control = self.callback_handler.call_event("on_step_end", a, st, self.control)
+                tr_loss = self._maybe_log_save_evaluate(tr_loss, grad_norm, lr, t_start)
+                if a.torch_empty_cache_steps and st.global_step % a.torch_empty_cache_steps == 0 and torch.cuda.is_available():
+                    torch.cuda.empty_cache()
+                if self.control.should_training_stop or self.control.should_epoch_stop:
+                    break
+            self.control = self.callback_handler.call_event("on_epoch_end", a, st, self.control)
+            tr_loss = self._maybe_log_save_evaluate(tr_loss, grad_norm, self._get_learning_rate(), t_start)
+            if self.control.should_training_stop:
+                break
+        self._total_loss_scalar += float(tr_loss)
+        train_loss = self._total_loss_scalar / max(1, st.global_step)
+        runtime = time.time() - t_start
+        metrics = {"train_runtime": round(runtime, 4), "train_steps_per_second": round(st.global_step / max(runtime, 1e-9), 3),
+                   "train_loss": train_loss, "epoch": st.epoch}
+        self.log(metrics)
+        self.control = self.callback_handler.call_event("on_train_end", a, st, self.control)
+        self.is_in_train = False
+        return TrainOutput(st.global_step, train_loss, metrics)
+
+    def _maybe_log_save_evaluate(self, tr_loss, grad_norm, lr, t_start):
+        st, a = self.state, self.args
+        if self.control.should_log and st.global_step > self._logged_step:
+            t = tr_loss.clone()
+            if D.world_size() > 1:
+                D.all_reduce(t, "mean")
+            scalar = float(t)
+            logs = {"loss": round(scalar / (st.global_step - self._logged_step), 4)}
+            if grad_norm is not None:
+                logs["grad_norm"] = float(grad_norm)
+            logs["learning_rate"] = lr
+            self._total_loss_scalar += scalar
+            self._logged_step = st.global_step
+            tr_loss = torch.zeros_like(tr_loss)
+            self.log(logs, t_start)
+            self.control.should_log = False
+        metrics = None
+        if self.control.should_evaluate:
+            metrics = self.evaluate()
+            self.control.should_evaluate = False
+        if self.control.should_save:
+            self._save_checkpoint(self.model, metrics=metrics)
+            self.control = self.callback_handler.call_event("on_save", a, st, self.control)
+            self.control.should_save = False
+        return tr_loss
+
+    def log(self, logs: dict, start_time: float | None = None):
+        mode = "train" if self.model is None or self.model.training else "eval"
+        own = self._metrics[mode]
+        if own:
+            avg = {k: sum(v) / len(v) for k, v in own.items() if len(v)}
+            if mode == "eval":
+                avg = {f"eval_{k}": v for k, v in avg.items()}
+            logs = {**logs, **avg}
+            own.clear()
+        if self.state.epoch is not None:
+            logs["epoch"] = round(self.state.epoch, 4) if isinstance(self.state.epoch, float) else self.state.epoch
+        self.state.log_history.append({**logs, "step": self.state.global_step})
+        self.control = self.callback_handler.call_event("on_log", self.args, self.state, self.control, logs=logs)
+
+    # ---- evaluation ---------------------------------------------------------------------------
+    def prediction_step(self, model, inputs, prediction_loss_only=True, ignore_keys=None):
+        inputs = self._prepare_inputs(inputs)
+        with torch.no_grad():
+            loss = self.compute_loss(model, inputs)
+        return loss.detach(), None, None
+
+    def evaluate(self, eval_dataset=None, ignore_keys=None, metric_key_prefix: str = "eval"):
+        if eval_dataset is None and isinstance(self.eval_dataset, dict):
+            out = {}
+            for name, ds in self.eval_dataset.items():
+                out.update(self.evaluate(ds, ignore_keys, f"{metric_key_prefix}_{name}"))
+            return out
+        loader = self.get_eval_dataloader(eval_dataset)
+        was_training = self.model.training
+        self.model.eval()
+        losses, preds, labels_all = [], [], []
+        t0 = time.time()
+        for batch in loader:
+            loss, logits, labels = self.prediction_step(self.model, batch, prediction_loss_only=self.compute_metrics is None)
+            losses.append(loss.float().reshape(1))
+            if logits is not None and self.compute_metrics is not None:
+                preds.append(logits.cpu())
+                labels_all.append(labels.cpu() if labels is not None else None)
+            self.control = self.callback_handler.call_event("on_prediction_step", self.args, self.state, self.control)
+        metrics = {}
+        if losses:
+            l = torch.cat(losses)
+            l = D.gather(l) if D.world_size() > 1 else l
+            metrics[f"{metric_key_prefix}_loss"] = float(l.mean())
+        if self.compute_metrics is not None and preds:
+            from types import SimpleNamespace
+
+            ep = SimpleNamespace(predictions=torch.cat(preds).numpy(),
+                                 label_ids=torch.cat(labels_all).numpy() if labels_all[0] is not None else None)
+            for k, v in self.compute_metrics(ep).items():
+                metrics[k if k.startswith(metric_key_prefix) else f"{metric_key_prefix}_{k}"] = v
+        metrics[f"{metric_key_prefix}_runtime"] = round(time.time() - t0, 4)
+        self.log(metrics)
+        self.control = self.callback_handler.call_event("on_evaluate", self.args, self.state, self.control, metrics=metrics)
+        if was_training:
+            self.model.train()
+        return metrics
+
+    # ---- persistence ------------------------------------------------------------------------------
+    def _full_state_dict(self):
+        if self.engine is not None and hasattr(self.engine, "gather_full_params"):
+            self.engine.gather_full_params()
+        return None
+
+    def save_model(self, output_dir: str | None = None, _internal_call: bool = False):
+        output_dir = output_dir or self.args.output_dir
+        self._full_state_dict()
+        if self.args.should_save:
+            os.makedirs(output_dir, exist_ok=True)
+            self._save(output_dir)
+        D.barrier()
+
+    def _save(self, output_dir: str):
+        m = self.model
+        if getattr(m, "peft_config", None) is not None and hasattr(m, "save_adapter"):
+            m.save_adapter(output_dir)
+        elif hasattr(m, "save_pretrained"):
+            m.save_pretrained(output_dir)
+        else:
+            torch.save(m.state_dict(), os.path.join(output_dir, "pytorch_model.bin"))
+        if self.processing_class is not None and hasattr(self.processing_class, "save_pretrained"):
+            self.processing_class.save_pretrained(output_dir)
+        with open(os.path.join(output_dir, "training_args.json"), "w") as f:
+            f.write(self.args.to_json_string())
+
+    def _save_checkpoint(self, model, trial=None, metrics=None):
+        a, st = self.args, self.state
+        folder = os.path.join(a.output_dir, f"{PREFIX_CHECKPOINT_DIR}-{st.global_step}")
+        self.save_model(folder, _internal_call=True)
+        os.makedirs(folder, exist_ok=True)
+        if not a.save_only_model:
+            sharded = self.engine.sharded
+            if sharded or a.should_save:
+                name = f"optimizer_rank{D.rank()}.pt" if sharded else "optimizer.pt"
+                torch.save(self.engine.optimizer_state_dict(), os.path.join(folder, name))
+            if a.should_save:
+                torch.save(self.lr_scheduler.state_dict(), os.path.join(folder, "scheduler.pt"))
+            rng = {"python": random.getstate(), "numpy": np.random.get_state(), "cpu": torch.get_rng_state()}
+            if torch.cuda.is_available() and a.device.type == "cuda":
+                rng["cuda"] = torch.cuda.get_rng_state()
+            torch.save(rng, os.path.join(folder, f"rng_state_{D.rank()}.pth" if D.world_size() > 1 else "rng_state.pth"))
+        if metrics and a.metric_for_best_model:
+            k = a.metric_for_best_model if a.metric_for_best_model.startswith("eval_") else f"eval_{a.metric_for_best_model}"
+            v = metrics.get(k)
+            if v is not None:
+                gib = a.greater_is_better if a.greater_is_better is not None else not k.endswith("loss")
+                if st.best_metric is None or (v > st.best_metric if gib else v < st.best_metric):
+                    st.best_metric, st.best_model_checkpoint, st.best_global_step = v, folder, st.global_step
+        if a.should_save:
+            st.stateful_callbacks = {type(c).__name__: c.state() for c in self.callback_handler.callbacks
+                                     if hasattr(c, "state") and callable(c.state)}
+            st.save_to_json(os.path.join(folder, "trainer_state.json"))
+            self._rotate_checkpoints()
+        D.barrier()
+
+    def _rotate_checkpoints(self):
+        lim = self.args.save_total_limit
+        if not lim or lim <= 0:
+            return
+        cks = sorted_checkpoints(self.args.output_dir)
+        best = self.state.best_model_checkpoint
+        for c in cks[:max(0, len(cks) - lim)]:
+            if best and os.path.abspath(c) == os.path.abspath(best):
+                continue
+            shutil.rmtree(c, ignore_errors=True)
+
+    def _load_from_checkpoint(self, folder: str):
+        from ..models.hf_io import load_hf_state_dict, load_state_dict_dir
+
+        if not os.path.isdir(folder):
+            raise ValueError(f"Can't find a valid checkpoint at {folder}")
+        m = self.model
+        if hasattr(m, "load_adapter") and os.path.exists(os.path.join(folder, "adapter_model.safetensors")):
+            m.load_adapter(folder)
+        elif getattr(m, "_is_native", False):
+            load_hf_state_dict(m, load_state_dict_dir(folder), strict=True)
+        sp = os.path.join(folder, "trainer_state.json")
+        if os.path.exists(sp):
+            old = TrainerState.load_from_json(sp)
+            old.is_world_process_zero, old.is_local_process_zero = self.state.is_world_process_zero, self.state.is_local_process_zero
+            self.state = old
+        op = os.path.join(folder, f"optimizer_rank{D.rank()}.pt" if self.engine.sharded else "optimizer.pt")
+        if os.path.exists(op):
+            self.engine.load_optimizer_state_dict(torch.load(op, map_location="cpu", weights_only=False))
+        elif getattr(m, "_is_native", False):
+            self.engine.refresh_master_from_params() if hasattr(self.engine, "refresh_master_from_params") else None
+        sc = os.path.join(folder, "scheduler.pt")
+        if os.path.exists(sc):
+            self.lr_scheduler.load_state_dict(torch.load(sc, weights_only=False))
+        for cand in (f"rng_state_{D.rank()}.pth", "rng_state.pth"):
+            rp = os.path.join(folder, cand)
+            if os.path.exists(rp):
+                rng = torch.load(rp, weights_only=False)
+                random.setstate(rng["python"])
+                np.random.set_state(rng["numpy"])
+                torch.set_rng_state(rng["cpu"])
+                if "cuda" in rng and torch.cuda.is_available():
+                    torch.cuda.set_rng_state(rng["cuda"])
+                break
+        self._on_checkpoint_loaded(folder)
+
+    def _on_checkpoint_loaded(self, folder: str):
+        pass
+
+    def create_model_card(self, *a, **k):
+        pass
+
+    def push_to_hub(self, *a, **k):
+        raise RuntimeError("push_to_hub needs network access, which this build does not assume")
+
+
+class _AcceleratorShim:
+    def __init__(self, trainer):
+        self._t = trainer
+
+    num_processes = property(lambda s: D.world_size())
+    process_index = property(lambda s: D.rank())
+    is_main_process = property(lambda s: D.is_main())
+    device = property(lambda s: s._t.args.device)
+
+    def gather(self, t):
+        return D.gather(t)
+
+    gather_for_metrics = gather
+
+    def reduce(self, t, reduction="sum"):
+        return D.all_reduce(t.clone(), reduction)
+
+    def unwrap_model(self, m, **k):
+        return m
+
+    def wait_for_everyone(self):
+        D.barrier()
+
+    def pad_across_processes(self, t, dim=0, pad_index=0):
+        return D.pad_across_processes(t, dim, pad_index)
+
+
+def sorted_checkpoints(output_dir: str) -> list[str]:
+    if not os.path.isdir(output_dir):
+        return []
+    out = []
+    for d in os.listdir(output_dir):
+        m = re.match(rf"^{PREFIX_CHECKPOINT_DIR}-(\d+)$", d)
+        if m and os.path.isdir(os.path.join(output_dir, d)):
+            out.append((int(m.group(1)), os.path.join(output_dir, d)))
+    return [p for _, p in sorted(out)]
+
+
+def get_last_checkpoint(output_dir: str) -> Optional[str]:
+    cks = sorted_checkpoints(output_dir)
+    return cks[-1] if cks else None

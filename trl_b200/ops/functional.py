@@ -1,0 +1,104 @@
+"""Op entry points used by the models, the trainers and the rollout engine.
+
+Every function has two implementations behind one signature:
+
+* CUDA tensors run the hand-written sm_100a kernels from ``trl_b200/csrc``
+  (``ops/cuda.py`` wraps them in ``torch.autograd.Function``).  If the native
+  library is missing on a machine that has a GPU the call raises; there is no
+  silent eager fallback for the kernels this module owns.
+* CPU tensors run the fp32 PyTorch oracle (``trl_b200/oracle/ops.py``), which
+  is also what the kernels are tested against.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from ..oracle import ops as _ref
+
+
+def _cuda():
+    from . import cuda as _c
+
+    return _c
+
+
+def _use_kernel(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype in (torch.bfloat16,)
+
+
+def linear(x, weight, bias=None):
+    """Plain library GEMM (cuBLAS through torch).  Fused variants live in ops.cuda."""
+    return F.linear(x, weight, bias)
+
+
+def rms_norm(x, weight, eps):
+    if _use_kernel(x):
+        return _cuda().RMSNormFn.apply(x, weight, eps)
+    return _ref.rms_norm(x, weight, eps)
+
+
+def apply_rope_qk(q, k, positions, theta):
+    """RoPE on q [T,Hq,D] and k [T,Hkv,D]; returns new tensors."""
+    if _use_kernel(q):
+        return _cuda().RopeFn.apply(q, k, positions, theta)
+    return _ref.apply_rope(q, positions, theta), _ref.apply_rope(k, positions, theta)
+
+
+def swiglu(gate_up):
+    if _use_kernel(gate_up):
+        return _cuda().SwigluFn.apply(gate_up)
+    return _ref.swiglu(gate_up)
+
+
+def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True):
+    if q.is_cuda:
+        return _cuda().attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal)
+    return _ref.attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal)
+
+
+def lm_head_logprobs(hidden, weight, labels, temperature=1.0, bias=None, softcap=None,
+                     compute_entropy=True, chunk_tokens: int = 4096):
+    """Fused lm_head GEMM + log-softmax gather (+entropy); logits never materialise."""
+    if _use_kernel(hidden) and bias is None and not softcap:
+        return _cuda().lm_head_logprobs(hidden, weight, labels, temperature, compute_entropy)
+    if hidden.shape[0] <= chunk_tokens or not torch.is_grad_enabled():
+        outs = [
+            _ref.lm_head_logprobs(h, weight, y, temperature, bias, softcap, compute_entropy)
+            for h, y in zip(hidden.split(chunk_tokens), labels.split(chunk_tokens))
+        ] or [(hidden.new_zeros(0, dtype=torch.float32), hidden.new_zeros(0, dtype=torch.float32))]
+        lp = torch.cat([o[0] for o in outs])
+        en = torch.cat([o[1] for o in outs]) if compute_entropy else None
+        return lp, en
+    # token-chunked with recompute so the [chunk, V] logits tile is the peak
+    from torch.utils.checkpoint import checkpoint
+
+    lps, ens = [], []
+    for h, y in zip(hidden.split(chunk_tokens), labels.split(chunk_tokens)):
+        lp, en = checkpoint(_ref.lm_head_logprobs, h, weight, y, temperature, bias, softcap,
+                            compute_entropy, use_reentrant=False)
+        lps.append(lp)
+        ens.append(en)
+    return torch.cat(lps), (torch.cat(ens) if compute_entropy else None)
+
+
+def lm_head_ce(hidden, weight, labels, ignore_index=-100, bias=None):
+    """Sum NLL + (correct, entropy_sum, n_valid) without a full logits tensor."""
+    if _use_kernel(hidden) and bias is None:
+        return _cuda().lm_head_ce(hidden, weight, labels, ignore_index)
+    return _ref.lm_head_ce(hidden, weight, labels, ignore_index, bias)
+
+
+def moe_mlp(hidden, router_w, gate_up_w, down_w, top_k, norm_topk_prob):
+    """Router + experts.  Returns (out, router_probs, topk_idx)."""
+    w, idx, probs = _ref.moe_router(hidden, router_w, top_k, norm_topk_prob)
+    if hidden.is_cuda:
+        out = _cuda().moe_experts(hidden, gate_up_w, down_w, w, idx)
+    else:
+        out = _ref.moe_experts(hidden, gate_up_w, down_w, w, idx)
+    return out, probs, idx
+
+
+selective_log_softmax = _ref.selective_log_softmax
+entropy_from_logits = _ref.entropy_from_logits
+load_balancing_loss = _ref.load_balancing_loss

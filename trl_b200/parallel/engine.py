@@ -1,0 +1,237 @@
+"""Flat-bucket training engine: gradient reduction + sharded AdamW.
+
+One bucket per decoder layer (plus embeddings / head).  A bucket owns
+
+* ``flat_param``  - the compute copy (bf16 on GPUs, fp32 on CPU); every
+  ``nn.Parameter`` of the bucket is a view into it,
+* ``flat_grad``   - the accumulation buffer (fp32 "main grads" by default),
+* an fp32 ``master / exp_avg / exp_avg_sq`` triple for the slice this rank owns.
+
+Modes (they replace the reference's accelerate profiles, trl/accelerate_configs/*.yaml):
+
+``ddp``        gradients all-reduced, optimizer state replicated.
+``zero1/2``    gradients reduce-scattered, optimizer state sharded, updated
+               parameters all-gathered (ZeRO-1/2; the two differ only in when
+               the full gradient buffer is released, which flat buckets make moot).
+``full_shard`` parameters live as 1/world shards between uses; see
+               :mod:`trl_b200.parallel.fullshard`, which reuses the buckets below.
+
+On GPUs the reduce-scatter, the fp32 cast/scale, the norm partials and the
+AdamW update are the ``rs_adamw`` kernels over symmetric memory
+(:mod:`trl_b200.parallel.symm`); the NCCL calls below are the measured baseline
+and the gloo/CPU path.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as td
+import torch.nn as nn
+
+from ..loop.optim import adamw_flat
+from . import dist as D
+
+_ALIGN = 256  # elements; keeps every shard 16-byte aligned for TMA / vector access
+
+
+@dataclass
+class Bucket:
+    name: str
+    names: list[str]
+    params: list[nn.Parameter]
+    offsets: list[int]
+    numel: int  # padded to world * _ALIGN
+    flat_param: torch.Tensor = None
+    flat_grad: torch.Tensor = None
+    decay_mask: torch.Tensor | None = None  # None => uniform decay
+    lo: int = 0
+    hi: int = 0
+    master: torch.Tensor = None
+    exp_avg: torch.Tensor = None
+    exp_avg_sq: torch.Tensor = None
+    no_decay_ranges: list = field(default_factory=list)
+
+    def shard(self, t: torch.Tensor) -> torch.Tensor:
+        return t[self.lo:self.hi]
+
+
+def default_bucket_of(name: str) -> str:
+    parts = name.split(".")
+    if parts[0] == "layers":
+        return f"layers.{parts[1]}"
+    return parts[0]
+
+
+class TrainEngine:
+    def __init__(self, model: nn.Module, *, mode: str = "ddp", betas=(0.9, 0.999), eps=1e-8,
+                 weight_decay: float = 0.0, grad_dtype: torch.dtype | None = None, bucket_of=default_bucket_of,
+                 use_symm_kernels: bool | None = None, group=None):
+        self.model = model
+        self.world, self.rank = D.world_size(), D.rank()
+        self.group = group
+        self.mode = "ddp" if (mode in ("auto", None) or self.world == 1 and mode != "full_shard") else mode
+        if mode == "auto" and self.world > 1:
+            self.mode = "zero2"
+        self.betas, self.eps, self.weight_decay = betas, eps, weight_decay
+        self.step_count = 0
+        self.sharded = self.mode in ("zero1", "zero2", "full_shard") and self.world > 1
+        self._build_buckets(bucket_of, grad_dtype)
+        self.use_symm = bool(use_symm_kernels) if use_symm_kernels is not None else False
+        self._hooks = []
+        self._install_grad_views()
+
+    # ---- construction ---------------------------------------------------------
+    def _build_buckets(self, bucket_of, grad_dtype):
+        groups: dict[str, list] = {}
+        seen = set()
+        for n, p in self.model.named_parameters():
+            if not p.requires_grad or id(p) in seen:
+                continue
+            seen.add(id(p))
+            groups.setdefault((bucket_of(n), p.dtype), []).append((n, p))
+        self.buckets: list[Bucket] = []
+        unit = self.world * _ALIGN
+        for (bname, dtype), items in groups.items():
+            offs, cur = [], 0
+            for _, p in items:
+                offs.append(cur)
+                cur += (p.numel() + 15) // 16 * 16
+            numel = (cur + unit - 1) // unit * unit
+            dev = items[0][1].device
+            b = Bucket(bname, [n for n, _ in items], [p for _, p in items], offs, numel)
+            b.flat_param = torch.zeros(numel, dtype=dtype, device=dev)
+            for (n, p), o in zip(items, offs):
+                b.flat_param[o:o + p.numel()].view_as(p).copy_(p.data)
+                p.data = b.flat_param[o:o + p.numel()].view_as(p)
+                if p.ndim <= 1:  # biases and norm weights: no weight decay (HF convention)
+                    b.no_decay_ranges.append((o, o + p.numel()))
+            gd = grad_dtype or torch.float32
+            b.flat_grad = torch.zeros(numel, dtype=gd, device=dev)
+            if self.sharded:
+                per = numel // self.world
+                b.lo, b.hi = self.rank * per, (self.rank + 1) * per
+            else:
+                b.lo, b.hi = 0, numel
+            n_sh = b.hi - b.lo
+            if dtype == torch.float32:
+                b.master = b.flat_param[b.lo:b.hi]  # alias: fp32 params are their own master
+            else:
+                b.master = b.flat_param[b.lo:b.hi].float()
+            b.exp_avg = torch.zeros(n_sh, dtype=torch.float32, device=dev)
+            b.exp_avg_sq = torch.zeros(n_sh, dtype=torch.float32, device=dev)
+            if self.weight_decay and b.no_decay_ranges:
+                mask = torch.ones(numel, dtype=torch.float32, device=dev)
+                for lo, hi in b.no_decay_ranges:
+                    mask[lo:hi] = 0
+                b.decay_mask = mask[b.lo:b.hi].contiguous()
+            self.buckets.append(b)
+
+    def _install_grad_views(self):
+        for b in self.buckets:
+            same = b.flat_grad.dtype == b.flat_param.dtype
+            for p, o in zip(b.params, b.offsets):
+                gview = b.flat_grad[o:o + p.numel()].view_as(p)
+                if same:
+                    p.grad = gview
+                else:
+                    p.grad = None
+
+                    def hook(param, gview=gview):
+                        gview.add_(param.grad)
+                        param.grad = None
+
+                    self._hooks.append(p.register_post_accumulate_grad_hook(hook))
+
+    # ---- step API ---------------------------------------------------------------
+    def zero_grad(self):
+        for b in self.buckets:
+            b.flat_grad.zero_()
+            if b.flat_grad.dtype == b.flat_param.dtype:
+                for p, o in zip(b.params, b.offsets):
+                    if p.grad is None or p.grad.data_ptr() != b.flat_grad[o:o + 1].data_ptr():
+                        p.grad = b.flat_grad[o:o + p.numel()].view_as(p)
+
+    def backward(self, loss: torch.Tensor):
+        loss.backward()
+
+    def _reduce(self, b: Bucket) -> torch.Tensor:
+        """Average gradients over ranks; returns this rank's (shard of the) reduced gradient."""
+        if self.world == 1:
+            return b.flat_grad
+        if self.sharded:
+            out = torch.empty(b.hi - b.lo, dtype=b.flat_grad.dtype, device=b.flat_grad.device)
+            if b.flat_grad.is_cuda:
+                td.reduce_scatter_tensor(out, b.flat_grad, op=td.ReduceOp.AVG, group=self.group)
+            else:  # gloo has no reduce_scatter: all-reduce then slice
+                td.all_reduce(b.flat_grad, group=self.group)
+                out = b.flat_grad[b.lo:b.hi] / self.world
+            return out
+        td.all_reduce(b.flat_grad, group=self.group)
+        b.flat_grad /= self.world
+        return b.flat_grad
+
+    def step(self, lr: float, max_grad_norm: float | None = None) -> torch.Tensor:
+        """Reduce, clip by global norm, AdamW, refresh the compute copy.  Returns the pre-clip norm."""
+        self.step_count += 1
+        reduced = [self._reduce(b) for b in self.buckets]
+        sq = torch.zeros((), dtype=torch.float32, device=reduced[0].device)
+        for g in reduced:
+            sq += g.float().pow(2).sum()
+        if self.sharded:
+            D.all_reduce(sq, "sum", group=self.group)
+        norm = sq.sqrt()
+        scale = 1.0
+        if max_grad_norm is not None and max_grad_norm > 0:
+            scale = torch.clamp(max_grad_norm / (norm + 1e-6), max=1.0)
+        b1, b2 = self.betas
+        for b, g in zip(self.buckets, reduced):
+            shadow = None if b.flat_param.dtype == torch.float32 else b.flat_param[b.lo:b.hi]
+            gs = scale  # python float or 0-dim tensor (stays on device: no host sync)
+            if b.decay_mask is None:  # uniform decay over the bucket (or none at all)
+                adamw_flat(b.master, g, b.exp_avg, b.exp_avg_sq, self.step_count, lr, b1, b2, self.eps,
+                           self.weight_decay, gs, shadow)
+            else:  # biases / norm weights inside the bucket are exempt from decay
+                self._masked_adamw(b, g, lr, gs, shadow)
+            if self.sharded:
+                td.all_gather_into_tensor(b.flat_param, b.flat_param[b.lo:b.hi].clone(), group=self.group)
+        return norm
+
+    def _masked_adamw(self, b: Bucket, g, lr, gs, shadow):
+        b1, b2 = self.betas
+        before = b.master.clone()
+        adamw_flat(b.master, g, b.exp_avg, b.exp_avg_sq, self.step_count, lr, b1, b2, self.eps, 0.0, gs, None)
+        b.master.sub_(before * b.decay_mask * (lr * self.weight_decay))
+        if shadow is not None:
+            shadow.copy_(b.master)
+
+    # ---- (de)serialisation of optimizer state -------------------------------------
+    def optimizer_state_dict(self) -> dict:
+        return {
+            "step": self.step_count, "mode": self.mode, "world": self.world, "rank": self.rank,
+            "buckets": {b.name + "|" + str(b.flat_param.dtype): {
+                "names": b.names, "lo": b.lo, "hi": b.hi,
+                "master": b.master.detach().cpu().clone(), "exp_avg": b.exp_avg.cpu(), "exp_avg_sq": b.exp_avg_sq.cpu()}
+                for b in self.buckets},
+        }
+
+    def load_optimizer_state_dict(self, sd: dict):
+        self.step_count = sd["step"]
+        for b in self.buckets:
+            s = sd["buckets"][b.name + "|" + str(b.flat_param.dtype)]
+            if (s["lo"], s["hi"]) != (b.lo, b.hi):
+                raise ValueError("optimizer shard layout changed (world size differs from the checkpoint)")
+            b.master.copy_(s["master"])
+            b.exp_avg.copy_(s["exp_avg"])
+            b.exp_avg_sq.copy_(s["exp_avg_sq"])
+
+    @torch.no_grad()
+    def refresh_master_from_params(self):
+        """Re-derive the fp32 master shard after weights were loaded into the compute copy."""
+        for b in self.buckets:
+            if b.master.data_ptr() != b.flat_param[b.lo:b.hi].data_ptr():
+                b.master.copy_(b.flat_param[b.lo:b.hi])
+
+    def grad_tensors(self):
+        return [b.flat_grad for b in self.buckets]

@@ -1,0 +1,374 @@
+"""Tensor / sampler / bookkeeping utilities shared by the trainers.
+
+Same names and results as trl/trainer/utils.py (line references in each
+docstring); the heavy ones (``selective_log_softmax``, ``entropy_from_logits``,
+chunked lm-head log-probs) delegate to :mod:`trl_b200.ops`.
+"""
+from __future__ import annotations
+
+import asyncio
+import contextlib
+import hashlib
+import threading
+from typing import Any, Iterable, Sequence
+
+import numpy as np
+import torch
+import torch.nn as nn
+
+from ..ops.functional import entropy_from_logits, selective_log_softmax  # noqa: F401  (re-exported)
+from ..parallel.dist import ensure_master_addr_port  # noqa: F401  (re-exported)
+
+
+def pad(tensors: list[torch.Tensor], padding_value: int = 0, padding_side: str = "right",
+        pad_to_multiple_of: int | None = None) -> torch.Tensor:
+    """Stack tensors of different leading sizes (utils.py:116-179)."""
+    shape = np.max([t.shape for t in tensors], 0).tolist()
+    if pad_to_multiple_of is not None:
+        r = shape[0] % pad_to_multiple_of
+        if r:
+            shape[0] += pad_to_multiple_of - r
+    out = torch.full((len(tensors), *shape), padding_value, dtype=tensors[0].dtype, device=tensors[0].device)
+    for i, t in enumerate(tensors):
+        n = t.shape[0]
+        if padding_side == "left":
+            sl = slice(shape[0] - n, shape[0])
+        elif padding_side == "right":
+            sl = slice(0, n)
+        else:
+            raise ValueError("padding_side must be 'left' or 'right'")
+        out[(i, sl) + tuple(slice(0, s) for s in t.shape[1:])] = t
+    return out
+
+
+def disable_dropout_in_model(model: nn.Module) -> None:
+    for m in model.modules():
+        if isinstance(m, nn.Dropout):
+            m.p = 0
+
+
+def flush_left(mask: torch.Tensor, *tensors: torch.Tensor):
+    """Shift every row left so its first non-zero mask entry sits in column 0, then drop
+    trailing all-zero columns (utils.py:414-476)."""
+    _, M = mask.shape
+    first = mask.argmax(dim=1)
+    pos = torch.arange(M, device=mask.device)[None]
+    idx = (pos + first[:, None]).clamp(max=M - 1)
+    valid_src = (pos + first[:, None]) < M
+    mask_r = mask.gather(1, idx) * valid_src
+    outs = [t.gather(1, idx) * valid_src.to(t.dtype) if t.ndim == 2 else t for t in tensors]
+    keep = mask_r.sum(0) != 0
+    last = int(keep.nonzero().max()) + 1 if keep.any() else 0
+    mask_r = mask_r[:, :last]
+    outs = [t[:, :last] for t in outs]
+    return (mask_r, *outs) if tensors else mask_r
+
+
+def flush_right(mask: torch.Tensor, *tensors: torch.Tensor):
+    m = mask.flip(1)
+    res = flush_left(m, *[t.flip(1) for t in tensors])
+    if not tensors:
+        return res.flip(1)
+    return tuple(r.flip(1) for r in res)
+
+
+class RepeatSampler:
+    """Index sampler for online RL (utils.py:695-788): permute, cut into chunks of
+    ``batch_size`` (incomplete tail dropped), emit every chunk ``repeat_count`` times and every
+    index ``mini_repeat_count`` times."""
+
+    def __init__(self, data_source, mini_repeat_count: int, batch_size: int = 1, repeat_count: int = 1,
+                 shuffle: bool = True, seed: int | None = None):
+        self.data_source, self.mini_repeat_count = data_source, mini_repeat_count
+        self.batch_size, self.repeat_count, self.shuffle, self.seed = batch_size, repeat_count, shuffle, seed
+        self.num_samples = len(data_source)
+        self.generator = torch.Generator()
+        if seed is not None:
+            self.generator.manual_seed(seed)
+
+    def __iter__(self):
+        order = (torch.randperm(self.num_samples, generator=self.generator).tolist() if self.shuffle
+                 else list(range(self.num_samples)))
+        chunks = [order[i:i + self.batch_size] for i in range(0, len(order), self.batch_size)]
+        for chunk in chunks:
+            if len(chunk) != self.batch_size:
+                continue
+            for _ in range(self.repeat_count):
+                for idx in chunk:
+                    for _ in range(self.mini_repeat_count):
+                        yield idx
+
+    def __len__(self) -> int:
+        return (self.num_samples // self.batch_size) * self.batch_size * self.mini_repeat_count * self.repeat_count
+
+
+RepeatRandomSampler = RepeatSampler
+
+
+def repeat_iterable_dataset(rows: Iterable, mini_repeat_count: int, batch_size: int, repeat_count: int):
+    """Streaming counterpart of :class:`RepeatSampler` (utils.py:791-853): a generator over rows."""
+    import copy
+
+    buf = []
+    for r in rows:
+        buf.append(r)
+        if len(buf) == batch_size:
+            for _ in range(repeat_count):
+                for x in buf:
+                    for _ in range(mini_repeat_count):
+                        yield copy.deepcopy(x)
+            buf = []
+
+
+def nanstd(t: torch.Tensor, dim=None, keepdim: bool = False) -> torch.Tensor:
+    """Bessel-corrected std ignoring NaNs; NaN where fewer than two values (utils.py:857-890)."""
+    if dim is None:
+        v = t[~torch.isnan(t)]
+        n = v.numel()
+        if n <= 1:
+            return t.new_tensor(float("nan"))
+        return ((v - v.mean()) ** 2).sum().div(n - 1).sqrt()
+    valid = ~torch.isnan(t)
+    cnt = valid.sum(dim, keepdim=True)
+    mean = torch.nansum(t, dim=dim, keepdim=True) / cnt.clamp_min(1)
+    sq = torch.where(valid, (t - mean) ** 2, torch.zeros_like(t)).sum(dim, keepdim=True)
+    out = (sq / (cnt - 1).clamp_min(1)).sqrt()
+    out = torch.where(cnt > 1, out, torch.full_like(out, float("nan")))
+    return out if keepdim else out.squeeze(dim)
+
+
+def nanmin(t: torch.Tensor) -> torch.Tensor:
+    v = t[~torch.isnan(t)]
+    return v.min() if v.numel() else t.new_tensor(float("nan"))
+
+
+def nanmax(t: torch.Tensor) -> torch.Tensor:
+    v = t[~torch.isnan(t)]
+    return v.max() if v.numel() else t.new_tensor(float("nan"))
+
+
+def split_tensor_dict(d: dict[str, Any], num_chunks: int) -> list[dict[str, Any]]:
+    """Equal dim-0 chunks; 0-dim tensors / scalars replicated, ``None`` preserved (utils.py:893-927)."""
+    first = next(v for v in d.values() if torch.is_tensor(v) and v.ndim > 0)
+    n = first.shape[0] // num_chunks
+    out = []
+    for i in range(num_chunks):
+        c = {}
+        for k, v in d.items():
+            if torch.is_tensor(v) and v.ndim > 0:
+                c[k] = v[i * n:(i + 1) * n]
+            elif isinstance(v, list) and len(v) == first.shape[0]:
+                c[k] = v[i * n:(i + 1) * n]
+            else:
+                c[k] = v
+        out.append(c)
+    return out
+
+
+def shuffle_sequence_dict(d: dict[str, Any], generator: torch.Generator | None = None) -> dict[str, Any]:
+    """One random permutation applied to every tensor / list along dim 0 (utils.py:930-957)."""
+    first = next(v for v in d.values() if (torch.is_tensor(v) and v.ndim > 0) or isinstance(v, list))
+    n = len(first)
+    perm = torch.randperm(n, generator=generator)
+
+    def p(v):
+        if v is None:
+            return None
+        if torch.is_tensor(v) and v.ndim == 0:
+            return v
+        if torch.is_tensor(v):
+            return v[perm.to(v.device)]
+        if isinstance(v, list):
+            return [v[i] for i in perm.tolist()]
+        return v
+    return {k: p(v) for k, v in d.items()}
+
+
+def split_pixel_values_by_grid(batch: dict) -> dict:
+    """Split flattened ``pixel_values`` into per-sample tensors using ``image_grid_thw`` (utils.py:995-1040)."""
+    if "image_grid_thw" not in batch or "pixel_values" not in batch or "num_images" not in batch:
+        return batch
+    lens = batch["image_grid_thw"].prod(-1).tolist()
+    pv = list(torch.split(batch["pixel_values"], lens, 0))
+    grids = list(torch.split(batch["image_grid_thw"], 1, 0))
+    out_pv, out_g, i = [], [], 0
+    for n in batch["num_images"]:
+        out_pv.append(torch.cat(pv[i:i + n], 0) if n else batch["pixel_values"].new_zeros((0,) + batch["pixel_values"].shape[1:]))
+        out_g.append(torch.cat(grids[i:i + n], 0) if n else batch["image_grid_thw"].new_zeros((0, 3)))
+        i += n
+    return {**batch, "pixel_values": out_pv, "image_grid_thw": out_g}
+
+
+def unsplit_pixel_values_by_grid(batch: dict) -> dict:
+    pv, g = batch.get("pixel_values"), batch.get("image_grid_thw")
+    if isinstance(pv, list) and isinstance(g, list):
+        return {**batch, "pixel_values": torch.cat(pv, 0), "image_grid_thw": torch.cat(g, 0)}
+    return batch
+
+
+def hash_module(module: nn.Module) -> str:
+    """sha256 over the sorted state dict: cache key for precomputed reference log-probs (utils.py:1173-1181)."""
+    h = hashlib.sha256()
+    for k, v in sorted(module.state_dict().items()):
+        h.update(k.encode())
+        h.update(str(v.dtype).encode())
+        t = v.detach().cpu()
+        if t.dtype in (torch.bfloat16,) or "float8" in str(t.dtype):
+            t = t.float()
+        h.update(t.contiguous().numpy().tobytes())
+    return h.hexdigest()
+
+
+@contextlib.contextmanager
+def use_adapter(model, adapter_name: str | None):
+    """``None`` disables LoRA inside the block (frozen reference policy); a name activates that
+    adapter and restores the previous one afterwards (utils.py:1199-1236)."""
+    if not hasattr(model, "set_adapter_enabled") and not hasattr(model, "active_adapter"):
+        yield
+        return
+    if adapter_name is None:
+        model.set_adapter_enabled(False)
+        try:
+            yield
+        finally:
+            model.set_adapter_enabled(True)
+    else:
+        prev = getattr(model, "active_adapter", "default")
+        model.set_adapter(adapter_name)
+        try:
+            yield
+        finally:
+            model.set_adapter(prev)
+
+
+# ---- a daemon asyncio loop for async reward functions / tools (utils.py:1239-1288) ----
+_loop = None
+_loop_lock = threading.Lock()
+
+
+def get_daemon_loop() -> asyncio.AbstractEventLoop:
+    global _loop
+    with _loop_lock:
+        if _loop is None or _loop.is_closed():
+            _loop = asyncio.new_event_loop()
+            threading.Thread(target=_loop.run_forever, daemon=True, name="trl-b200-async").start()
+    return _loop
+
+
+def run_coroutine_sync(coro):
+    return asyncio.run_coroutine_threadsafe(coro, get_daemon_loop()).result()
+
+
+# ---- FLOP accounting (utils.py:1520-1630) --------------------------------------------
+B200_PEAK_BF16_FLOPS = 2.25e15
+H100_PEAK_BF16_FLOPS = 989.5e12
+
+
+def compute_flops_per_token(config, seq_len: int) -> float:
+    """Training FLOPs per token = 3 x forward (2 FLOPs per MAC); MoE counts router + top-k experts."""
+    c = config
+    h, L = c.hidden_size, c.num_hidden_layers
+    hd = getattr(c, "head_dim", None) or h // c.num_attention_heads
+    q, kv = c.num_attention_heads * hd, c.num_key_value_heads * hd
+    attn_proj = 2 * h * (q + 2 * kv) + 2 * q * h
+    attn_score = 2 * 2 * q * seq_len / 2  # causal: half the square
+    n_exp = getattr(c, "num_experts", 0) or 0
+    if n_exp:
+        k = c.num_experts_per_tok
+        mlp = 2 * 3 * h * c.moe_intermediate_size * k + 2 * h * n_exp
+    else:
+        mlp = 2 * 3 * h * c.intermediate_size
+    head = 2 * h * c.vocab_size
+    return 3.0 * (L * (attn_proj + attn_score + mlp) + head)
+
+
+def compute_mfu(config, tokens_per_second: float, seq_len: int, num_devices: int = 1,
+                peak_flops_per_device: float = B200_PEAK_BF16_FLOPS) -> float:
+    return compute_flops_per_token(config, seq_len) * tokens_per_second / (num_devices * peak_flops_per_device)
+
+
+def adjusted_mfu(config, tokens_per_second: float, seq_len: int, num_devices: int = 1, gradient_checkpointing=True,
+                 peak_flops_per_device: float = B200_PEAK_BF16_FLOPS) -> float:
+    """With full recomputation the hardware does 4x forward, not 3x."""
+    m = compute_mfu(config, tokens_per_second, seq_len, num_devices, peak_flops_per_device)
+    return m * (4.0 / 3.0) if gradient_checkpointing else m
+
+
+def print_prompt_completions_sample(prompts: list, completions: list, rewards: dict[str, list[float]],
+                                    advantages: list[float], step: int, num_samples: int | None = None,
+                                    extra: dict[str, list] | None = None) -> None:
+    """Rich table of sampled rollouts (utils.py:563-692); plain text when rich is unavailable."""
+    n = len(prompts)
+    idx = list(range(n))
+    if num_samples is not None and 0 < num_samples < n:
+        import random
+
+        idx = random.sample(idx, num_samples)
+
+    def text(x):
+        if isinstance(x, list):
+            return "\n".join(f"{m.get('role', '?').upper()}: {m.get('content', '')}" for m in x)
+        return str(x)
+    try:
+        from rich.console import Console
+        from rich.panel import Panel
+        from rich.table import Table
+        from rich.text import Text
+
+        table = Table(show_header=True, header_style="bold white", expand=True)
+        table.add_column("Prompt", style="bright_yellow")
+        table.add_column("Completion", style="bright_green")
+        for k in rewards:
+            table.add_column(k, style="bold cyan", justify="right")
+        for k in (extra or {}):
+            table.add_column(k, style="magenta")
+        table.add_column("Advantage", style="bold magenta", justify="right")
+        for i in idx:
+            table.add_row(Text(text(prompts[i])), Text(text(completions[i])), *[f"{rewards[k][i]:.2f}" for k in rewards],
+                          *[str(v[i]) for v in (extra or {}).values()], f"{advantages[i]:.2f}")
+            table.add_section()
+        Console().print(Panel(table, expand=False, title=f"Step {step}", border_style="bold white"))
+    except Exception:
+        for i in idx:
+            print(f"[step {step}] prompt={text(prompts[i])!r} completion={text(completions[i])!r} "
+                  f"rewards={ {k: v[i] for k, v in rewards.items()} } adv={advantages[i]:.3f}")
+
+
+def get_peft_config(model_args):
+    """ModelConfig -> LoraConfig (utils.py:254-277)."""
+    if not getattr(model_args, "use_peft", False):
+        return None
+    from ..models.lora import LoraConfig
+
+    return LoraConfig(task_type=model_args.lora_task_type, r=model_args.lora_r,
+                      target_modules=model_args.lora_target_modules, target_parameters=model_args.lora_target_parameters,
+                      lora_alpha=model_args.lora_alpha, lora_dropout=model_args.lora_dropout, bias="none",
+                      use_rslora=model_args.use_rslora, use_dora=model_args.use_dora,
+                      modules_to_save=model_args.lora_modules_to_save)
+
+
+def get_quantization_config(model_args):
+    """4/8-bit loading needs bitsandbytes kernels, which this build does not carry."""
+    if getattr(model_args, "load_in_4bit", False) or getattr(model_args, "load_in_8bit", False):
+        raise NotImplementedError("load_in_4bit / load_in_8bit: no quantised-weight kernels in this build")
+    return None
+
+
+def create_model_from_path(model_id: str, architecture=None, **kwargs):
+    """dtype defaults to float32 (utils.py:1123-1170); ``model_id`` is a local directory or a preset name."""
+    from ..models.hf_io import load_model
+
+    dtype = kwargs.pop("dtype", kwargs.pop("torch_dtype", "float32"))
+    kwargs.pop("device_map", None)
+    kwargs.pop("trust_remote_code", None)
+    kwargs.pop("attn_implementation", None)
+    kwargs.pop("revision", None)
+    return load_model(model_id, dtype=dtype, **kwargs)
+
+
+def maybe_gather_lm_head_ctx(model, engine=None):
+    """Fused lm-head losses read the weight directly: under full-shard the head bucket must be
+    materialised first (utils.py:188-221)."""
+    if engine is not None and hasattr(engine, "gathered"):
+        return engine.gathered(["lm_head", "embed_tokens"])
+    return contextlib.nullcontext()
