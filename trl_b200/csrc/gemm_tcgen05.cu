@@ -1,0 +1,420 @@
+// Persistent warp-specialised bf16 GEMM on 5th-gen tensor cores (sm_100a):
+//
+//     acc[M,N] = A[M,K] . B[N,K]^T        (both operands K-major: y = x W^T of nn.Linear)
+//
+// * one CTA per SM, 192 threads: warp 0 = TMA producer, warp 1 = tcgen05.mma issuer,
+//   warps 2-5 = epilogue (each owns one 32-lane quarter of TMEM);
+// * A/B tiles (128x64 and 256x64 bf16, 128-byte swizzle) arrive through a 4-stage TMA
+//   ring; accumulators (128x256 fp32) are double-buffered in TMEM (2 x 256 columns) so the
+//   epilogue of tile i overlaps the MMAs of tile i+1;
+// * three epilogues share the main loop:
+//     EPI_STORE  C = bf16(acc + bias)
+//     EPI_LSE    vocabulary-chunked online log-sum-exp for the fused lm_head: per row running
+//                max / sum-exp / sum(z e^z) / label logit / argmax, never writing logits
+//     EPI_DZ     d(logits) = g * (1[label] - softmax) / T written as bf16 (lm_head backward)
+//
+// Replaces: cuBLAS GEMM + eager softmax of trl/trainer/utils.py:1291-1424 and the chunked
+// cross-entropy of trl/trainer/sft_trainer.py:117-234.
+#include "common.cuh"
+
+namespace trlb {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr size_t GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+
+enum { EPI_STORE = 0, EPI_LSE = 1, EPI_DZ = 2 };
+
+struct GemmParams {
+  int M, N, K;
+  int m_tiles, n_tiles, k_blocks;
+  int n_splits, tiles_per_split;  // work item = (m_tile, split); a split covers tiles_per_split N tiles
+  // EPI_STORE
+  __nv_bfloat16* C;
+  long long ldc;
+  const __nv_bfloat16* bias;
+  // EPI_LSE / EPI_DZ
+  const long long* labels;  // [M], may hold negative (ignored) entries
+  float inv_temp;
+  float4* part_stats;  // [n_splits, M]: (max2, sumexp, sum z*e^z, label logit)
+  int* part_arg;       // [n_splits, M]: argmax column
+  const float* lse;    // [M]  (EPI_DZ)
+  const float* grow;   // [M]  dL/dlogp per row (EPI_DZ)
+  int* status;
+};
+
+__device__ __forceinline__ void item_to_coords(const GemmParams& p, int item, int& m_tile, int& n_begin, int& n_end) {
+  m_tile = item % p.m_tiles;
+  int split = item / p.m_tiles;
+  n_begin = split * p.tiles_per_split;
+  n_end = min(n_begin + p.tiles_per_split, p.n_tiles);
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;                 // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;       // [STAGES]
+  uint64_t* tfull_bar = bars + 2 * STAGES;   // [2]
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_items = p.m_tiles * p.n_splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        int m_tile, n0, n1;
+        item_to_coords(p, item, m_tile, n0, n1);
+        for (int nt = n0; nt < n1 && ok; ++nt) {
+          for (int kb = 0; kb < p.k_blocks; ++kb) {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 100 + stage)) { ok = false; break; }
+            uint8_t* sa = tiles + stage * STAGE_BYTES;
+            uint8_t* sb = sa + A_BYTES;
+            mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m_tile * BM);
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, nt * BN);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        int m_tile, n0, n1;
+        item_to_coords(p, item, m_tile, n0, n1);
+        for (int nt = n0; nt < n1 && ok; ++nt) {
+          if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, 200 + acc)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t tacc = tmem_base + (uint32_t)acc * BN;
+          for (int kb = 0; kb < p.k_blocks; ++kb) {
+            if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 300 + stage)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
+            const uint64_t adesc = umma_desc_kmajor_sw128(sa);
+            const uint64_t bdesc = umma_desc_kmajor_sw128(sa + A_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+              // advancing K by 16 bf16 = 32 bytes = 2 descriptor address units inside the swizzle atom
+              umma_bf16_ss(tacc, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) != 0);
+            }
+            umma_commit(&empty_bar[stage]);  // smem stage reusable once these MMAs retire
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+          if (!ok) break;
+          umma_commit(&tfull_bar[acc]);  // accumulator complete
+          if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue warps (2..5) ----------------
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+    const int row_in_tile = quarter * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    constexpr float LOG2E = 1.4426950408889634f;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      int m_tile, n0, n1;
+      item_to_coords(p, item, m_tile, n0, n1);
+      const int row = m_tile * BM + row_in_tile;
+      const bool row_ok = row < p.M;
+      // per-row running statistics (EPI_LSE)
+      float run_max = -INFINITY, run_sum = 0.f, run_zsum = 0.f, tgt = 0.f;
+      int arg = 0;
+      long long label = -1;
+      float lse_row = 0.f, g_row = 0.f;
+      if (EPI != EPI_STORE && row_ok) {
+        label = p.labels[row];
+        if (EPI == EPI_DZ) { lse_row = p.lse[row]; g_row = p.grow[row]; }
+      }
+      for (int nt = n0; nt < n1 && ok; ++nt) {
+        if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, 400 + acc)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tacc = tmem_base + (uint32_t)acc * BN + ((uint32_t)(quarter * 32) << 16);
+        const int col0 = nt * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          float v[32];
+          tmem_ld_32x32(tacc + c, v);
+          tmem_ld_wait();
+          const int cbase = col0 + c;
+          if (EPI == EPI_STORE) {
+            if (row_ok && cbase < p.N) {
+              __nv_bfloat16* dst = p.C + (long long)row * p.ldc + cbase;
+              if (p.bias != nullptr) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (cbase + i < p.N) v[i] += __bfloat162float(p.bias[cbase + i]);
+              }
+              if (cbase + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                  uint4 o;
+                  o.x = pack_bf16(v[i], v[i + 1]);
+                  o.y = pack_bf16(v[i + 2], v[i + 3]);
+                  o.z = pack_bf16(v[i + 4], v[i + 5]);
+                  o.w = pack_bf16(v[i + 6], v[i + 7]);
+                  *reinterpret_cast<uint4*>(dst + i) = o;
+                }
+              } else {
+                for (int i = 0; i < 32; ++i)
+                  if (cbase + i < p.N) dst[i] = __float2bfloat16(v[i]);
+              }
+            }
+          } else if (EPI == EPI_LSE) {
+            if (cbase < p.N) {
+              const float sc = p.inv_temp;
+              float cmax = -INFINITY;
+              const int rel = (int)(label - cbase);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                float z = (cbase + i < p.N) ? v[i] * sc : -INFINITY;
+                v[i] = z;
+                if (z > cmax) cmax = z;
+                if (i == rel) tgt = z;
+              }
+              if (cmax > run_max) {
+                // first column reaching the new maximum (ties: lowest index, like torch.argmax)
+                int a = 0;
+#pragma unroll
+                for (int i = 31; i >= 0; --i)
+                  if (v[i] == cmax) a = i;
+                arg = cbase + a;
+                const float scale = exp2f((run_max - cmax) * LOG2E);
+                run_sum *= scale;
+                run_zsum *= scale;
+                run_max = cmax;
+              }
+              const float mb = run_max * LOG2E;
+              float s = 0.f, zs = 0.f;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float e = exp2f(fmaf(v[i], LOG2E, -mb));
+                s += e;
+                zs = fmaf(e, (cbase + i < p.N) ? v[i] : 0.f, zs);
+              }
+              run_sum += s;
+              run_zsum += zs;
+            }
+          } else {  // EPI_DZ
+            if (row_ok && cbase < p.N) {
+              __nv_bfloat16* dst = p.C + (long long)row * p.ldc + cbase;
+              const float sc = p.inv_temp;
+              const float gs = g_row * sc;
+              const int rel = (int)(label - cbase);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float pr = __expf(fmaf(v[i], sc, -lse_row));
+                v[i] = gs * ((i == rel ? 1.f : 0.f) - pr);
+              }
+              if (cbase + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                  uint4 o;
+                  o.x = pack_bf16(v[i], v[i + 1]);
+                  o.y = pack_bf16(v[i + 2], v[i + 3]);
+                  o.z = pack_bf16(v[i + 4], v[i + 5]);
+                  o.w = pack_bf16(v[i + 6], v[i + 7]);
+                  *reinterpret_cast<uint4*>(dst + i) = o;
+                }
+              } else {
+                for (int i = 0; i < 32; ++i)
+                  if (cbase + i < p.N) dst[i] = __float2bfloat16(v[i]);
+              }
+            }
+          }
+        }
+        // release this accumulator to the MMA warp
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (EPI == EPI_LSE && ok && row_ok) {
+        const int split = item / p.m_tiles;
+        p.part_stats[(long long)split * p.M + row] = make_float4(run_max, run_sum, run_zsum, tgt);
+        p.part_arg[(long long)split * p.M + row] = arg;
+      }
+    }
+  }
+
+  // ---------------- teardown (also the abort path) ----------------
+  __syncthreads();
+  if (*abort_flag) {
+    // give TMA copies that may still be in flight time to land before shared memory is released
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// Combine per-split statistics into log p(label), entropy, log-sum-exp and argmax.
+__global__ void lse_combine_kernel(const float4* __restrict__ part, const int* __restrict__ part_arg, int n_splits, int M,
+                                   float* __restrict__ logp, float* __restrict__ entropy, float* __restrict__ lse_out,
+                                   int* __restrict__ argmax_out) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= M) return;
+  float mx = -INFINITY;
+  int arg = 0;
+  for (int s = 0; s < n_splits; ++s) {
+    const float m = part[(long long)s * M + row].x;
+    if (m > mx) { mx = m; arg = part_arg[(long long)s * M + row]; }
+  }
+  float sum = 0.f, zsum = 0.f, tgt = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float4 q = part[(long long)s * M + row];
+    const float sc = __expf(q.x - mx);
+    sum += q.y * sc;
+    zsum += q.z * sc;
+    tgt += q.w;  // exactly one split holds the label column, the others contribute 0
+  }
+  const float lse = mx + __logf(sum);
+  if (logp) logp[row] = tgt - lse;
+  if (entropy) entropy[row] = lse - zsum / sum;
+  if (lse_out) lse_out[row] = lse;
+  if (argmax_out) argmax_out[row] = arg;
+}
+
+}  // namespace trlb
+
+// ------------------------------------------------------------------------------------------------
+// host launchers (C ABI)
+// ------------------------------------------------------------------------------------------------
+using namespace trlb;
+
+template <int EPI>
+static int launch_gemm(const void* A, const void* B, GemmParams p, long long lda, long long ldb, cudaStream_t stream) {
+  if (p.M <= 0 || p.N <= 0 || p.K <= 0) return 0;
+  if ((p.K % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0) return -100;  // 16-byte TMA stride rule
+  CUtensorMap ta, tb;
+  int r = trlb_host::make_tmap_2d_bf16(&ta, A, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)lda, BM, BK);
+  if (r) return -101;
+  r = trlb_host::make_tmap_2d_bf16(&tb, B, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)ldb, BN, BK);
+  if (r) return -102;
+  p.m_tiles = (p.M + BM - 1) / BM;
+  p.n_tiles = (p.N + BN - 1) / BN;
+  p.k_blocks = (p.K + BK - 1) / BK;
+  if (EPI == EPI_STORE || EPI == EPI_DZ) {
+    p.n_splits = p.n_tiles;
+    p.tiles_per_split = 1;
+  } else {
+    p.tiles_per_split = (p.n_tiles + p.n_splits - 1) / p.n_splits;
+  }
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm_tn_kernel<EPI_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_tn_kernel<EPI_LSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+    cudaFuncSetAttribute(gemm_tn_kernel<EPI_DZ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+    attr_set = true;
+  }
+  const int items = p.m_tiles * p.n_splits;
+  const int grid = items < trlb_host::sm_count() ? items : trlb_host::sm_count();
+  gemm_tn_kernel<EPI><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ta, tb, p);
+  return (int)cudaGetLastError();
+}
+
+// C[M,N] (bf16, row stride ldc) = A[M,K] . B[N,K]^T (+ bias[N])
+TRLB_API int trlb_gemm_bf16_tn(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                               long long lda, long long ldb, long long ldc, int* status, cudaStream_t stream) {
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.C = (__nv_bfloat16*)C; p.ldc = ldc; p.bias = (const __nv_bfloat16*)bias;
+  p.status = status;
+  return launch_gemm<EPI_STORE>(A, B, p, lda, ldb, stream);
+}
+
+// Number of vocabulary splits the forward uses for M rows (so callers can size the scratch).
+TRLB_API int trlb_lmhead_num_splits(int M, int V) {
+  const int m_tiles = (M + BM - 1) / BM, n_tiles = (V + BN - 1) / BN;
+  const int sms = trlb_host::sm_count();
+  int splits = (2 * sms + m_tiles - 1) / m_tiles;
+  if (splits < 1) splits = 1;
+  if (splits > n_tiles) splits = n_tiles;
+  if (splits > 64) splits = 64;
+  // normalise so that no split is empty
+  const int tps = (n_tiles + splits - 1) / splits;
+  return (n_tiles + tps - 1) / tps;
+}
+
+// Fused lm_head forward.  H[M,K] bf16, W[V,K] bf16, labels[M] int64.
+// scratch: part_stats float4[n_splits*M], part_arg int[n_splits*M] with n_splits = trlb_lmhead_num_splits(M,V).
+// Outputs (each may be null): logp[M], entropy[M], lse[M] fp32, argmax[M] int32.
+TRLB_API int trlb_lmhead_fwd(const void* H, const void* W, const long long* labels, int M, int V, int K, long long ldh,
+                             long long ldw, float inv_temp, void* part_stats, int* part_arg, int n_splits, float* logp,
+                             float* entropy, float* lse, int* argmax, int* status, cudaStream_t stream) {
+  GemmParams p = {};
+  p.M = M; p.N = V; p.K = K;
+  p.labels = labels; p.inv_temp = inv_temp;
+  p.part_stats = (float4*)part_stats; p.part_arg = part_arg;
+  p.n_splits = n_splits;
+  p.status = status;
+  int r = launch_gemm<EPI_LSE>(H, W, p, ldh, ldw, stream);
+  if (r) return r;
+  lse_combine_kernel<<<(M + 255) / 256, 256, 0, stream>>>((const float4*)part_stats, part_arg, n_splits, M, logp, entropy,
+                                                         lse, argmax);
+  return (int)cudaGetLastError();
+}
+
+// Fused lm_head backward, stage 1: dZ[M,V] (bf16, row stride ldz) = grow * (1[label] - softmax(z/T)) / T
+TRLB_API int trlb_lmhead_dz(const void* H, const void* W, const long long* labels, const float* lse, const float* grow,
+                            void* dZ, int M, int V, int K, long long ldh, long long ldw, long long ldz, float inv_temp,
+                            int* status, cudaStream_t stream) {
+  GemmParams p = {};
+  p.M = M; p.N = V; p.K = K;
+  p.labels = labels; p.inv_temp = inv_temp; p.lse = lse; p.grow = grow;
+  p.C = (__nv_bfloat16*)dZ; p.ldc = ldz;
+  p.status = status;
+  return launch_gemm<EPI_DZ>(H, W, p, ldh, ldw, stream);
+}
