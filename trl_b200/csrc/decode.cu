@@ -1,0 +1,440 @@
+// Rollout-engine decode kernels (one new token per running sequence):
+//
+//  rope_kv_write      RoPE on q and k of the fused QKV row, k/v appended to the paged cache
+//  kv_write_prefill   k/v of a packed prefill written to the paged cache
+//  paged_decode_attn  split-KV attention of 1 query token against the paged cache (GQA)
+//  sample_tokens      temperature / min-p / EOS-probability-floor sampling by Gumbel-max with
+//                     the sampled token's log-probability in the processed distribution
+//
+// They stand where the reference uses vLLM's CUDA kernels (trl/generation/vllm_generation.py:351-368,680).
+#include "common.cuh"
+
+namespace trlb {
+
+// ------------------------------------------------------------------------------------------
+// cache layout: K and V are [num_blocks, block_size, Hk, D] bf16; block_table [max_seqs, max_blocks]
+// ------------------------------------------------------------------------------------------
+__global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, long long row_stride,
+                                     const int* __restrict__ seq_lens, const int* __restrict__ slot_ids,
+                                     const int* __restrict__ block_table, int max_blocks, int block_size,
+                                     __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ kc,
+                                     __nv_bfloat16* __restrict__ vc, int B, int Hq, int Hk, int D, float log2_theta) {
+  const int half = D >> 1;
+  const int per_tok = (Hq + 2 * Hk) * half;
+  const long long total = (long long)B * per_tok;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int b = (int)(idx / per_tok);
+    int r = (int)(idx % per_tok);
+    const int head = r / half, f = r % half;
+    const int slot = slot_ids ? slot_ids[b] : b;
+    const int pos = seq_lens[slot];  // position of the new token = current length
+    if (pos < 0) continue;            // inactive slot
+    const __nv_bfloat16* src = qkv + (size_t)b * row_stride + (size_t)head * D;
+    const int blk = block_table[(size_t)slot * max_blocks + pos / block_size];
+    const size_t cache_row = ((size_t)blk * block_size + pos % block_size) * Hk;
+    if (head < Hq + Hk) {
+      const float inv = exp2f(-log2_theta * (float)(2 * f) / (float)D);
+      float s, c;
+      sincosf((float)pos * inv, &s, &c);
+      const float lo = __bfloat162float(src[f]), hi = __bfloat162float(src[half + f]);
+      const float o0 = lo * c - hi * s, o1 = hi * c + lo * s;
+      __nv_bfloat16* dst = head < Hq ? q_out + ((size_t)b * Hq + head) * D : kc + (cache_row + (head - Hq)) * D;
+      dst[f] = __float2bfloat16(o0);
+      dst[half + f] = __float2bfloat16(o1);
+    } else {
+      __nv_bfloat16* dst = vc + (cache_row + (head - Hq - Hk)) * D;
+      dst[f] = src[f];
+      dst[half + f] = src[half + f];
+    }
+  }
+}
+
+// k,v [T,Hk,D] (already rotated) of packed prompts -> cache.  tok_slot[t], tok_pos[t] give the
+// destination sequence slot and position of token t.
+__global__ void kv_write_prefill_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                                        long long k_stride, long long v_stride, const int* __restrict__ tok_slot,
+                                        const int* __restrict__ tok_pos, const int* __restrict__ block_table,
+                                        int max_blocks, int block_size, __nv_bfloat16* __restrict__ kc,
+                                        __nv_bfloat16* __restrict__ vc, int T, int Hk, int D) {
+  const int vec_per_tok = Hk * D / 8;
+  const long long total = (long long)T * vec_per_tok;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / vec_per_tok), e = (int)(idx % vec_per_tok);
+    const int slot = tok_slot[t], pos = tok_pos[t];
+    if (slot < 0) continue;
+    const int blk = block_table[(size_t)slot * max_blocks + pos / block_size];
+    const size_t row = ((size_t)blk * block_size + pos % block_size) * Hk * D;
+    reinterpret_cast<uint4*>(kc + row)[e] = reinterpret_cast<const uint4*>(k + (size_t)t * k_stride)[e];
+    reinterpret_cast<uint4*>(vc + row)[e] = reinterpret_cast<const uint4*>(v + (size_t)t * v_stride)[e];
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Split-KV decode attention.  grid = (B, Hk, splits), 128 threads.  G = Hq/Hk query heads share a
+// kv head.  Partials (m, l, o) go to scratch; paged_attn_combine_kernel merges the splits.
+// ------------------------------------------------------------------------------------------
+constexpr int DEC_THREADS = 128;
+constexpr int DEC_CHUNK = 128;
+constexpr int MAX_G = 8;
+
+template <int D>
+__global__ void __launch_bounds__(DEC_THREADS)
+paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q,  // [B, Hq, D]
+                         const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
+                         const int* __restrict__ seq_lens, const int* __restrict__ slot_ids,
+                         const int* __restrict__ block_table, int max_blocks, int block_size, int Hq, int Hk,
+                         float scale, int splits, float* __restrict__ part_o,  // [B, Hq, splits, D]
+                         float* __restrict__ part_ml) {                       // [B, Hq, splits, 2]
+  const int b = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
+  const int G = Hq / Hk;
+  const int slot = slot_ids ? slot_ids[b] : b;
+  const int len = seq_lens[slot] + 1;  // the new token was appended before attention
+  const int tid = threadIdx.x;
+  __shared__ float q_s[MAX_G][D];
+  __shared__ float p_s[MAX_G][DEC_CHUNK];
+  __shared__ float red[MAX_G][4];
+  __shared__ float o_half[MAX_G][D];
+
+  const int per_split = ((len + splits - 1) / splits + DEC_CHUNK - 1) / DEC_CHUNK * DEC_CHUNK;
+  const int t_begin = sp * per_split, t_end = min(len, t_begin + per_split);
+
+  for (int i = tid; i < G * D; i += DEC_THREADS) {
+    const int g = i / D, d = i % D;
+    q_s[g][d] = __bfloat162float(q[((size_t)b * Hq + kvh * G + g) * D + d]) * scale;
+  }
+  float m_run[MAX_G], l_run[MAX_G], o_acc[MAX_G][2];
+#pragma unroll
+  for (int g = 0; g < MAX_G; ++g) { m_run[g] = -INFINITY; l_run[g] = 0.f; o_acc[g][0] = o_acc[g][1] = 0.f; }
+  __syncthreads();
+  const int* bt = block_table + (size_t)slot * max_blocks;
+  const int dp = tid & 63, half_id = tid >> 6;  // PV mapping: dim pair, token parity
+
+  for (int t0 = t_begin; t0 < t_end; t0 += DEC_CHUNK) {
+    // ---- scores: thread = token ----
+    const int tok = t0 + tid;
+    float s[MAX_G];
+#pragma unroll
+    for (int g = 0; g < MAX_G; ++g) s[g] = -INFINITY;
+    if (tok < t_end) {
+      const int blk = bt[tok / block_size];
+      const uint4* kr = reinterpret_cast<const uint4*>(kc + (((size_t)blk * block_size + tok % block_size) * Hk + kvh) * D);
+#pragma unroll
+      for (int g = 0; g < MAX_G; ++g) s[g] = 0.f;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        const uint4 kv4 = kr[i];
+        const uint32_t* ku = reinterpret_cast<const uint32_t*>(&kv4);
+        float kf[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16(ku[j]); kf[2 * j] = f.x; kf[2 * j + 1] = f.y; }
+#pragma unroll
+        for (int g = 0; g < MAX_G; ++g) {
+          if (g < G) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s[g] = fmaf(q_s[g][i * 8 + j], kf[j], s[g]);
+          }
+        }
+      }
+    }
+    // ---- chunk max per head ----
+    const int lane = tid & 31, wid = tid >> 5;
+#pragma unroll
+    for (int g = 0; g < MAX_G; ++g) {
+      if (g < G) {
+        const float mx = warp_max(s[g]);
+        if (lane == 0) red[g][wid] = mx;
+      }
+    }
+    __syncthreads();
+    float corr[MAX_G];
+#pragma unroll
+    for (int g = 0; g < MAX_G; ++g) {
+      if (g < G) {
+        const float cm = fmaxf(fmaxf(red[g][0], red[g][1]), fmaxf(red[g][2], red[g][3]));
+        const float mn = fmaxf(m_run[g], cm);
+        corr[g] = __expf(m_run[g] - mn);
+        m_run[g] = mn;
+        const float p = (tok < t_end) ? __expf(s[g] - mn) : 0.f;
+        p_s[g][tid] = p;
+        l_run[g] = l_run[g] * corr[g];  // per-thread partial of l: own token's p added below
+        l_run[g] += p;
+        o_acc[g][0] *= corr[g];
+        o_acc[g][1] *= corr[g];
+      }
+    }
+    __syncthreads();
+    // ---- PV: thread = (dim pair, token parity) ----
+    const int nt = min(DEC_CHUNK, t_end - t0);
+    for (int j = half_id; j < nt; j += 2) {
+      const int tk = t0 + j;
+      const int blk = bt[tk / block_size];
+      const uint32_t vv = *reinterpret_cast<const uint32_t*>(
+          vc + (((size_t)blk * block_size + tk % block_size) * Hk + kvh) * D + dp * 2);
+      const float2 vf = unpack_bf16(vv);
+#pragma unroll
+      for (int g = 0; g < MAX_G; ++g) {
+        if (g < G) {
+          const float p = p_s[g][j];
+          o_acc[g][0] = fmaf(p, vf.x, o_acc[g][0]);
+          o_acc[g][1] = fmaf(p, vf.y, o_acc[g][1]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  // ---- reduce l over threads, o over the two token-parity halves ----
+  const int lane = tid & 31, wid = tid >> 5;
+#pragma unroll
+  for (int g = 0; g < MAX_G; ++g) {
+    if (g < G) {
+      // every thread scaled its partial l by the same corr sequence, so a plain sum is exact
+      const float ls = warp_sum(l_run[g]);
+      if (lane == 0) red[g][wid] = ls;
+    }
+  }
+  if (half_id == 1) {
+#pragma unroll
+    for (int g = 0; g < MAX_G; ++g)
+      if (g < G) { o_half[g][dp * 2] = o_acc[g][0]; o_half[g][dp * 2 + 1] = o_acc[g][1]; }
+  }
+  __syncthreads();
+  if (half_id == 0) {
+#pragma unroll
+    for (int g = 0; g < MAX_G; ++g) {
+      if (g < G) {
+        const size_t base = (((size_t)b * Hq + kvh * G + g) * splits + sp);
+        float* po = part_o + base * D;
+        po[dp * 2] = o_acc[g][0] + o_half[g][dp * 2];
+        po[dp * 2 + 1] = o_acc[g][1] + o_half[g][dp * 2 + 1];
+        if (dp == 0) {
+          part_ml[base * 2] = m_run[g];
+          part_ml[base * 2 + 1] = red[g][0] + red[g][1] + red[g][2] + red[g][3];
+        }
+      }
+    }
+  }
+}
+
+template <int D>
+__global__ void paged_attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits,
+                                          __nv_bfloat16* __restrict__ out, int total_heads) {
+  const int h = blockIdx.x;  // b * Hq + head
+  if (h >= total_heads) return;
+  const int d = threadIdx.x;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[((size_t)h * splits + s) * 2]);
+  float l = 0.f, o = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_ml[((size_t)h * splits + s) * 2];
+    const float w = (ms == -INFINITY) ? 0.f : __expf(ms - m);
+    l += part_ml[((size_t)h * splits + s) * 2 + 1] * w;
+    o += part_o[((size_t)h * splits + s) * D + d] * w;
+  }
+  out[(size_t)h * D + d] = __float2bfloat16(l > 0.f ? o / l : 0.f);
+}
+
+// ------------------------------------------------------------------------------------------
+// Sampler.  One CTA per row.  Pass 1: max and log-sum-exp of the processed logits without the
+// EOS column.  Pass 2: Gumbel-max over the final distribution.  Outputs token id and its log-prob.
+// Processing order: repetition handled by caller; temperature; min-p; EOS probability floor.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t hash_u32(uint32_t x) {
+  x ^= x >> 16; x *= 0x7feb352dU; x ^= x >> 15; x *= 0x846ca68bU; x ^= x >> 16;
+  return x;
+}
+__device__ __forceinline__ float uniform01(uint32_t seed, uint32_t step, uint32_t row, uint32_t col) {
+  uint32_t h = hash_u32(seed ^ hash_u32(step * 0x9E3779B9U + row) ^ hash_u32(col * 0x85EBCA6BU + 0x165667B1U));
+  h = hash_u32(h + col);
+  return ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
+}
+
+template <typename T>
+__device__ __forceinline__ float ld_logit(const T* p, long long i);
+template <>
+__device__ __forceinline__ float ld_logit<float>(const float* p, long long i) { return p[i]; }
+template <>
+__device__ __forceinline__ float ld_logit<__nv_bfloat16>(const __nv_bfloat16* p, long long i) {
+  return __bfloat162float(p[i]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024)
+sample_kernel(const T* __restrict__ logits, long long row_stride, int V, float inv_temp, float min_p, int eos_id,
+              float eos_floor, uint32_t seed, const int* __restrict__ step_ptr, int greedy,
+              int* __restrict__ out_tok, float* __restrict__ out_logp) {
+  const int row = blockIdx.x;
+  const T* z = logits + (size_t)row * row_stride;
+  __shared__ float sh_a[32], sh_b[32];
+  __shared__ int sh_i[32];
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, nw = blockDim.x >> 5;
+  const uint32_t step = step_ptr ? (uint32_t)(*step_ptr) : 0u;
+  // pass 1: max over all, then sum-exp excluding eos
+  float mx = -INFINITY;
+  for (int i = tid; i < V; i += blockDim.x) mx = fmaxf(mx, ld_logit<T>(z, i) * inv_temp);
+  mx = warp_max(mx);
+  if (lane == 0) sh_a[wid] = mx;
+  __syncthreads();
+  mx = -INFINITY;
+  for (int w = 0; w < nw; ++w) mx = fmaxf(mx, sh_a[w]);
+  __syncthreads();
+  const float thresh = (min_p > 0.f) ? mx + __logf(min_p) : -INFINITY;  // keep p >= min_p * p_max
+  float se = 0.f;
+  for (int i = tid; i < V; i += blockDim.x) {
+    const float v = ld_logit<T>(z, i) * inv_temp;
+    if (i != eos_id && v >= thresh) se += __expf(v - mx);
+  }
+  se = warp_sum(se);
+  if (lane == 0) sh_a[wid] = se;
+  __syncthreads();
+  se = 0.f;
+  for (int w = 0; w < nw; ++w) se += sh_a[w];
+  __syncthreads();
+  // eos handling
+  float z_eos = -INFINITY;
+  if (eos_id >= 0 && eos_id < V) {
+    z_eos = ld_logit<T>(z, eos_id) * inv_temp;
+    if (z_eos < thresh) z_eos = -INFINITY;
+  }
+  const float lse_others = mx + __logf(fmaxf(se, 1e-30f));
+  float lse_all;
+  if (eos_floor > 0.f && eos_id >= 0) {
+    // p(eos) = max(p(eos), floor): raise the eos logit until softmax gives the floor
+    const float need = lse_others + __logf(eos_floor / (1.f - eos_floor));
+    if (z_eos < need) z_eos = need;
+  }
+  {
+    const float a = fmaxf(lse_others, z_eos);
+    lse_all = a + __logf(__expf(lse_others - a) + __expf(z_eos - a));
+  }
+  // pass 2: Gumbel-max (or plain argmax when greedy)
+  float best = -INFINITY;
+  int best_i = 0;
+  float best_z = 0.f;
+  for (int i = tid; i < V; i += blockDim.x) {
+    float v = (i == eos_id) ? z_eos : ld_logit<T>(z, i) * inv_temp;
+    if (v < thresh && i != eos_id) continue;
+    if (v == -INFINITY) continue;
+    float key = v;
+    if (!greedy) {
+      const float u = uniform01(seed, step, (uint32_t)row, (uint32_t)i);
+      key = v - __logf(-__logf(u));
+    }
+    if (key > best) { best = key; best_i = i; best_z = v; }
+  }
+  // block arg-max
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    const float oz = __shfl_xor_sync(0xffffffffu, best_z, o);
+    if (ob > best || (ob == best && oi < best_i)) { best = ob; best_i = oi; best_z = oz; }
+  }
+  if (lane == 0) { sh_a[wid] = best; sh_i[wid] = best_i; sh_b[wid] = best_z; }
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < nw; ++w)
+      if (sh_a[w] > best || (sh_a[w] == best && sh_i[w] < best_i)) { best = sh_a[w]; best_i = sh_i[w]; best_z = sh_b[w]; }
+    out_tok[row] = best_i;
+    out_logp[row] = best_z - lse_all;
+  }
+}
+
+// After sampling: append token to the output buffer, bump lengths, mark finished sequences.
+// out_tokens / out_logps are [max_seqs, max_new]; n_gen[slot] counts generated tokens.
+__global__ void advance_kernel(const int* __restrict__ tok, const float* __restrict__ logp, const int* __restrict__ slot_ids,
+                               int B, int* __restrict__ seq_lens, int* __restrict__ n_gen, int* __restrict__ finished,
+                               int* __restrict__ out_tokens, float* __restrict__ out_logps, int max_new, int eos_id,
+                               int max_total_len, long long* __restrict__ next_input, int* __restrict__ step_counter,
+                               int bump_len) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b == 0 && step_counter) atomicAdd(step_counter, 1);
+  if (b >= B) return;
+  const int slot = slot_ids ? slot_ids[b] : b;
+  if (seq_lens[slot] < 0) return;
+  if (finished[slot]) { next_input[b] = eos_id >= 0 ? eos_id : 0; return; }
+  const int t = tok[b];
+  const int g = n_gen[slot];
+  if (g < max_new) {
+    out_tokens[(size_t)slot * max_new + g] = t;
+    out_logps[(size_t)slot * max_new + g] = logp[b];
+  }
+  n_gen[slot] = g + 1;
+  seq_lens[slot] += bump_len;  // decode: the token whose K/V was just written now counts
+  next_input[b] = t;
+  if (t == eos_id || g + 1 >= max_new || seq_lens[slot] + 1 >= max_total_len) finished[slot] = 1;
+}
+
+}  // namespace trlb
+
+using namespace trlb;
+
+TRLB_API int trlb_rope_kv_write(const void* qkv, long long row_stride, const int* seq_lens, const int* slot_ids,
+                                const int* block_table, int max_blocks, int block_size, void* q_out, void* kc, void* vc,
+                                int B, int Hq, int Hk, int D, float theta, cudaStream_t st) {
+  if (B == 0) return 0;
+  const long long work = (long long)B * (Hq + 2 * Hk) * (D / 2);
+  int grid = (int)((work + 255) / 256);
+  rope_kv_write_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)qkv, row_stride, seq_lens, slot_ids, block_table,
+                                             max_blocks, block_size, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kc,
+                                             (__nv_bfloat16*)vc, B, Hq, Hk, D, log2f(theta));
+  return (int)cudaGetLastError();
+}
+
+TRLB_API int trlb_kv_write_prefill(const void* k, const void* v, long long k_stride, long long v_stride,
+                                   const int* tok_slot, const int* tok_pos, const int* block_table, int max_blocks,
+                                   int block_size, void* kc, void* vc, int T, int Hk, int D, cudaStream_t st) {
+  if (T == 0) return 0;
+  if ((Hk * D) % 8 != 0) return -1;
+  const long long work = (long long)T * (Hk * D / 8);
+  long long grid = (work + 255) / 256;
+  if (grid > 148 * 16) grid = 148 * 16;
+  kv_write_prefill_kernel<<<(int)grid, 256, 0, st>>>((const __nv_bfloat16*)k, (const __nv_bfloat16*)v, k_stride, v_stride,
+                                                     tok_slot, tok_pos, block_table, max_blocks, block_size,
+                                                     (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, T, Hk, D);
+  return (int)cudaGetLastError();
+}
+
+// scratch sizes: part_o = B*Hq*splits*D floats, part_ml = B*Hq*splits*2 floats
+TRLB_API int trlb_paged_decode_attn(const void* q, const void* kc, const void* vc, const int* seq_lens,
+                                    const int* slot_ids, const int* block_table, int max_blocks, int block_size, int B,
+                                    int Hq, int Hk, int D, float scale, int splits, float* part_o, float* part_ml,
+                                    void* out, cudaStream_t st) {
+  if (B == 0) return 0;
+  if (D != 128 && D != 64) return -1;
+  if (Hq % Hk != 0 || Hq / Hk > MAX_G) return -2;
+  dim3 grid(B, Hk, splits);
+  if (D == 128) {
+    paged_decode_attn_kernel<128><<<grid, DEC_THREADS, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc,
+                                                                (const __nv_bfloat16*)vc, seq_lens, slot_ids, block_table,
+                                                                max_blocks, block_size, Hq, Hk, scale, splits, part_o,
+                                                                part_ml);
+    paged_attn_combine_kernel<128><<<B * Hq, 128, 0, st>>>(part_o, part_ml, splits, (__nv_bfloat16*)out, B * Hq);
+  } else {
+    return -3;
+  }
+  return (int)cudaGetLastError();
+}
+
+TRLB_API int trlb_sample(const void* logits, int is_bf16, long long row_stride, int B, int V, float inv_temp, float min_p,
+                         int eos_id, float eos_floor, unsigned seed, const int* step_ptr, int greedy, int* out_tok,
+                         float* out_logp, cudaStream_t st) {
+  if (B == 0) return 0;
+  if (is_bf16)
+    sample_kernel<__nv_bfloat16><<<B, 1024, 0, st>>>((const __nv_bfloat16*)logits, row_stride, V, inv_temp, min_p, eos_id,
+                                                    eos_floor, seed, step_ptr, greedy, out_tok, out_logp);
+  else
+    sample_kernel<float><<<B, 1024, 0, st>>>((const float*)logits, row_stride, V, inv_temp, min_p, eos_id, eos_floor,
+                                            seed, step_ptr, greedy, out_tok, out_logp);
+  return (int)cudaGetLastError();
+}
+
+TRLB_API int trlb_advance(const int* tok, const float* logp, const int* slot_ids, int B, int* seq_lens, int* n_gen,
+                          int* finished, int* out_tokens, float* out_logps, int max_new, int eos_id, int max_total_len,
+                          long long* next_input, int* step_counter, int bump_len, cudaStream_t st) {
+  if (B == 0) return 0;
+  advance_kernel<<<(B + 127) / 128, 128, 0, st>>>(tok, logp, slot_ids, B, seq_lens, n_gen, finished, out_tokens,
+                                                  out_logps, max_new, eos_id, max_total_len, next_input, step_counter, bump_len);
+  return (int)cudaGetLastError();
+}

@@ -170,3 +170,256 @@ def lm_head_ce(hidden, weight, labels, ignore_index=-100):
         correct = ((amax.long() == labels) & valid).sum()
         ent_sum = (ent * vf).sum()
     return loss_sum, correct, ent_sum, valid.sum()
+
+
+# -------------------------------------------------------------------------------------------
+# memory-bound fused ops
+# -------------------------------------------------------------------------------------------
+class RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        shp = x.shape
+        H = shp[-1]
+        x2 = x.reshape(-1, H)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        T = x2.shape[0]
+        y = torch.empty_like(x2)
+        rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+        w = weight if weight.dtype == torch.bfloat16 else weight.to(torch.bfloat16)
+        _chk(lib().trlb_rmsnorm_fwd(_p(x2), _p(w), _p(y), _p(rstd), c_int(T), c_int(H), c_float(eps), _s()), "rmsnorm_fwd")
+        ctx.save_for_backward(x2, w, rstd)
+        ctx.shp = shp
+        ctx.wdtype = weight.dtype
+        return y.view(shp)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, rstd = ctx.saved_tensors
+        T, H = x2.shape
+        dy2 = dy.reshape(T, H)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = torch.empty_like(x2)
+        L = lib()
+        parts = L.trlb_rmsnorm_bwd_parts(c_int(T))
+        scratch = _scratch_buf("rms_dw", parts * H * 4, x2.device)
+        dw = torch.empty(H, dtype=torch.float32, device=x2.device)
+        _chk(L.trlb_rmsnorm_bwd(_p(dy2), _p(x2), _p(w), _p(rstd), _p(dx), _p(scratch), _p(dw), None, c_int(T), c_int(H),
+                                _s()), "rmsnorm_bwd")
+        return dx.view(ctx.shp), dw.to(ctx.wdtype), None
+
+
+class RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, positions, theta):
+        T, Hq, D = q.shape
+        Hk = k.shape[1]
+        assert q.stride(2) == 1 and q.stride(1) == D and k.stride(2) == 1 and k.stride(1) == D
+        pos = positions if positions.dtype == torch.int32 else positions.to(torch.int32)
+        qo = torch.empty(T, Hq, D, dtype=q.dtype, device=q.device)
+        ko = torch.empty(T, Hk, D, dtype=k.dtype, device=k.device)
+        _chk(lib().trlb_rope(_p(q), _p(k), c_longlong(q.stride(0)), c_longlong(k.stride(0)), _p(pos), _p(qo), _p(ko),
+                             c_int(T), c_int(Hq), c_int(Hk), c_int(D), c_float(theta), c_float(1.0), _s()), "rope")
+        ctx.save_for_backward(pos)
+        ctx.theta = theta
+        return qo, ko
+
+    @staticmethod
+    def backward(ctx, dq, dk):
+        (pos,) = ctx.saved_tensors
+        dq, dk = dq.contiguous(), dk.contiguous()
+        T, Hq, D = dq.shape
+        Hk = dk.shape[1]
+        gq, gk = torch.empty_like(dq), torch.empty_like(dk)
+        _chk(lib().trlb_rope(_p(dq), _p(dk), c_longlong(dq.stride(0)), c_longlong(dk.stride(0)), _p(pos), _p(gq), _p(gk),
+                             c_int(T), c_int(Hq), c_int(Hk), c_int(D), c_float(ctx.theta), c_float(-1.0), _s()), "rope_bwd")
+        return gq, gk, None, None
+
+
+class SwigluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate_up):
+        shp = gate_up.shape
+        I = shp[-1] // 2
+        gu = gate_up.reshape(-1, 2 * I)
+        if not gu.is_contiguous():
+            gu = gu.contiguous()
+        out = torch.empty(gu.shape[0], I, dtype=gu.dtype, device=gu.device)
+        _chk(lib().trlb_swiglu_fwd(_p(gu), _p(out), c_longlong(gu.shape[0]), c_int(I), _s()), "swiglu_fwd")
+        ctx.save_for_backward(gu)
+        ctx.shp = shp
+        return out.view(shp[:-1] + (I,))
+
+    @staticmethod
+    def backward(ctx, dout):
+        (gu,) = ctx.saved_tensors
+        I = gu.shape[1] // 2
+        d = dout.reshape(-1, I)
+        if not d.is_contiguous():
+            d = d.contiguous()
+        dgu = torch.empty_like(gu)
+        _chk(lib().trlb_swiglu_bwd(_p(d), _p(gu), _p(dgu), c_longlong(gu.shape[0]), c_int(I), _s()), "swiglu_bwd")
+        return dgu.view(ctx.shp)
+
+
+def adamw_flat(master, grad, m, v, step, lr, b1, b2, eps, wd, grad_scale=1.0, shadow=None):
+    """Fused AdamW over a flat fp32 shard; ``grad_scale`` may be a 0-dim CUDA tensor (no host sync)."""
+    gs_ptr, gs = None, 1.0
+    if torch.is_tensor(grad_scale):
+        gs_t = grad_scale.reshape(1).float()
+        gs_ptr = gs_t
+    else:
+        gs = float(grad_scale)
+    assert grad.dtype in (torch.float32, torch.bfloat16) and master.dtype == torch.float32
+    _chk(lib().trlb_adamw(_p(master), _p(grad), c_int(int(grad.dtype == torch.bfloat16)), _p(m), _p(v), _p(shadow),
+                          c_longlong(master.numel()), c_int(step), c_float(lr), c_float(b1), c_float(b2), c_float(eps),
+                          c_float(wd), c_float(gs), _p(gs_ptr), _s()), "adamw")
+
+
+def sumsq(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    if out is None:
+        out = torch.zeros(1, dtype=torch.float32, device=x.device)
+    _chk(lib().trlb_sumsq(_p(x), c_int(int(x.dtype == torch.bfloat16)), c_longlong(x.numel()), _p(out), _s()), "sumsq")
+    return out
+
+
+# -------------------------------------------------------------------------------------------
+# attention
+# -------------------------------------------------------------------------------------------
+def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True):
+    """Causal GQA attention over packed documents [T, H, D]."""
+    from torch.nn.attention.varlen import varlen_attn
+
+    cu = cu_seqlens.to(torch.int32)
+    Hq, Hk = q.shape[1], k.shape[1]
+    if Hq != Hk:
+        rep = Hq // Hk
+        k = k.repeat_interleave(rep, dim=1)
+        v = v.repeat_interleave(rep, dim=1)
+    return varlen_attn(q.contiguous(), k.contiguous(), v.contiguous(), cu, cu, int(max_seqlen), int(max_seqlen),
+                       window_size=(-1, 0) if causal else (-1, -1))
+
+
+def moe_experts(hidden, gate_up_w, down_w, topk_w, topk_idx):
+    from ..oracle.ops import moe_experts as ref
+
+    return ref(hidden, gate_up_w, down_w, topk_w, topk_idx)
+
+
+# -------------------------------------------------------------------------------------------
+# fused losses
+# -------------------------------------------------------------------------------------------
+class GrpoLossFn(torch.autograd.Function):
+    """Clipped-ratio + KL token loss, reduced with per-row scales; returns (loss, stats[8])."""
+
+    @staticmethod
+    def forward(ctx, logp, old_logp, ref_logp, adv, mask, row_scale, entropy, eps_low, eps_high, beta, delta):
+        B, T = logp.shape
+        dev = logp.device
+        f = lambda t: None if t is None else t.float().contiguous()
+        logp_c = f(logp)
+        dlogp = torch.empty(B, T, dtype=torch.float32, device=dev)
+        stats = torch.zeros(8, dtype=torch.float32, device=dev)
+        _chk(lib().trlb_grpo_loss(_p(logp_c), _p(f(old_logp)), _p(f(ref_logp)), _p(f(adv)), _p(f(mask)), _p(f(row_scale)),
+                                  _p(f(entropy)), _p(dlogp), None, _p(stats), c_int(B), c_int(T), c_float(eps_low),
+                                  c_float(eps_high), c_float(beta), c_float(delta if delta else 0.0), c_float(1.0), _s()),
+             "grpo_loss")
+        ctx.save_for_backward(dlogp)
+        ctx.mark_non_differentiable(stats)
+        return stats[0].clone(), stats
+
+    @staticmethod
+    def backward(ctx, g_loss, _g_stats):
+        (dlogp,) = ctx.saved_tensors
+        return (dlogp * g_loss,) + (None,) * 10
+
+
+def grpo_loss(logp, old_logp, ref_logp, adv, mask, row_scale, entropy, eps_low, eps_high, beta, delta=None):
+    return GrpoLossFn.apply(logp, old_logp, ref_logp, adv, mask, row_scale, entropy, eps_low, eps_high, beta, delta)
+
+
+class DpoLossFn(torch.autograd.Function):
+    """Sigmoid DPO over a packed token stream; returns (mean loss, per-pair metrics [P, 8])."""
+
+    @staticmethod
+    def forward(ctx, pol_logp, ref_logp, mask, cu_seqlens, beta, label_smoothing):
+        P = (cu_seqlens.numel() - 1) // 2
+        dev = pol_logp.device
+        pol = pol_logp.float().contiguous()
+        dpol = torch.empty_like(pol)
+        out = torch.empty(P, 8, dtype=torch.float32, device=dev)
+        _chk(lib().trlb_dpo_loss(_p(pol), _p(ref_logp.float().contiguous()), _p(mask.float().contiguous()),
+                                 _p(cu_seqlens.to(torch.int32).contiguous()), c_int(P), c_float(beta),
+                                 c_float(label_smoothing), c_float(1.0 / max(P, 1)), _p(dpol), _p(out), _s()), "dpo_loss")
+        ctx.save_for_backward(dpol)
+        ctx.mark_non_differentiable(out)
+        return out[:, 0].mean(), out
+
+    @staticmethod
+    def backward(ctx, g, _go):
+        (dpol,) = ctx.saved_tensors
+        return dpol * g, None, None, None, None, None
+
+
+def dpo_loss(pol_logp, ref_logp, mask, cu_seqlens, beta, label_smoothing=0.0):
+    return DpoLossFn.apply(pol_logp, ref_logp, mask, cu_seqlens, beta, label_smoothing)
+
+
+# -------------------------------------------------------------------------------------------
+# rollout-engine decode kernels (no autograd)
+# -------------------------------------------------------------------------------------------
+def rmsnorm_infer(x, w, eps, out=None):
+    T, H = x.shape
+    out = torch.empty_like(x) if out is None else out
+    _chk(lib().trlb_rmsnorm_fwd(_p(x), _p(w), _p(out), None, c_int(T), c_int(H), c_float(eps), _s()), "rmsnorm_fwd")
+    return out
+
+
+def swiglu_infer(gu, out=None):
+    T, I2 = gu.shape
+    out = torch.empty(T, I2 // 2, dtype=gu.dtype, device=gu.device) if out is None else out
+    _chk(lib().trlb_swiglu_fwd(_p(gu), _p(out), c_longlong(T), c_int(I2 // 2), _s()), "swiglu_fwd")
+    return out
+
+
+def rope_kv_write(qkv, seq_lens, slot_ids, block_table, block_size, q_out, k_cache, v_cache, Hq, Hk, D, theta):
+    B = qkv.shape[0]
+    _chk(lib().trlb_rope_kv_write(_p(qkv), c_longlong(qkv.stride(0)), _p(seq_lens), _p(slot_ids), _p(block_table),
+                                  c_int(block_table.shape[1]), c_int(block_size), _p(q_out), _p(k_cache), _p(v_cache),
+                                  c_int(B), c_int(Hq), c_int(Hk), c_int(D), c_float(theta), _s()), "rope_kv_write")
+
+
+def kv_write_prefill(k, v, tok_slot, tok_pos, block_table, block_size, k_cache, v_cache):
+    T, Hk, D = k.shape
+    _chk(lib().trlb_kv_write_prefill(_p(k), _p(v), c_longlong(k.stride(0)), c_longlong(v.stride(0)), _p(tok_slot),
+                                     _p(tok_pos), _p(block_table), c_int(block_table.shape[1]), c_int(block_size),
+                                     _p(k_cache), _p(v_cache), c_int(T), c_int(Hk), c_int(D), _s()), "kv_write_prefill")
+
+
+def paged_decode_attn(q, k_cache, v_cache, seq_lens, slot_ids, block_table, block_size, scale, splits, part_o, part_ml,
+                      out):
+    B, Hq, D = q.shape
+    Hk = k_cache.shape[2]
+    _chk(lib().trlb_paged_decode_attn(_p(q), _p(k_cache), _p(v_cache), _p(seq_lens), _p(slot_ids), _p(block_table),
+                                      c_int(block_table.shape[1]), c_int(block_size), c_int(B), c_int(Hq), c_int(Hk),
+                                      c_int(D), c_float(scale), c_int(splits), _p(part_o), _p(part_ml), _p(out), _s()),
+         "paged_decode_attn")
+    return out
+
+
+def sample_tokens(logits, inv_temp, min_p, eos_id, eos_floor, seed, step_ptr, greedy, out_tok, out_logp):
+    B, V = logits.shape
+    _chk(lib().trlb_sample(_p(logits), c_int(int(logits.dtype == torch.bfloat16)), c_longlong(logits.stride(0)), c_int(B),
+                           c_int(V), c_float(inv_temp), c_float(min_p or 0.0), c_int(-1 if eos_id is None else eos_id),
+                           c_float(eos_floor or 0.0), ctypes.c_uint(seed & 0xFFFFFFFF), _p(step_ptr), c_int(int(greedy)),
+                           _p(out_tok), _p(out_logp), _s()), "sample")
+
+
+def advance(tok, logp, slot_ids, seq_lens, n_gen, finished, out_tokens, out_logps, eos_id, max_total_len, next_input,
+            step_counter, bump_len=1):
+    B = tok.shape[0]
+    _chk(lib().trlb_advance(_p(tok), _p(logp), _p(slot_ids), c_int(B), _p(seq_lens), _p(n_gen), _p(finished),
+                            _p(out_tokens), _p(out_logps), c_int(out_tokens.shape[1]),
+                            c_int(-1 if eos_id is None else eos_id), c_int(max_total_len), _p(next_input),
+                            _p(step_counter), c_int(bump_len), _s()), "advance")

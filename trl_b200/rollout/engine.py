@@ -1,0 +1,374 @@
+"""In-box rollout engine: paged KV cache, continuous batching, CUDA-graph decode.
+
+This replaces the reference's vLLM colocate/server modes
+(trl/generation/vllm_generation.py:111-704).  One engine lives in each training
+process and reads the policy's bf16 weights in place (TP=1: zero-copy "weight
+sync"; TP>1: :mod:`trl_b200.rollout.tp` holds resharded copies that the
+weight-sync kernel refreshes).
+
+GPU path
+    prefill   packed varlen forward of the admitted prompts; K/V written straight into the
+              paged cache; completions sampled from one prompt share its full prompt blocks.
+    decode    one CUDA graph per engine: embed -> L x (RMSNorm, QKV GEMM, RoPE+KV-append,
+              split-KV paged attention, O GEMM, RMSNorm, gate/up GEMM, SwiGLU, down GEMM)
+              -> RMSNorm -> lm_head GEMM -> fused sampler -> advance.  No per-step host work:
+              the host polls the ``finished`` flags every ``poll_every`` steps.
+    scheduler C++ (``csrc/host_runtime.cpp``): waiting queue, slots, ref-counted block pool.
+
+CPU path (tests, tiny models): :class:`EagerGenerator`, same sampling semantics.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..models.decoder import CausalLM, SeqCtx
+from .sampling import SamplingParams, apply_repetition_penalty, filter_top_k_top_p, sample_reference
+
+
+@dataclass
+class Completion:
+    prompt_ids: list
+    token_ids: list
+    logprobs: list
+    finish_reason: str = "length"
+
+
+class EagerGenerator:
+    """Reference generator: recomputes the full forward every step (fine for tiny CPU models)."""
+
+    def __init__(self, model: CausalLM):
+        self.model = model
+
+    @torch.no_grad()
+    def generate(self, prompts: Sequence[Sequence[int]], sp: SamplingParams) -> list[Completion]:
+        dev = self.model.device
+        g = torch.Generator(device="cpu").manual_seed(sp.seed)
+        seqs = [list(p) for p in prompts for _ in range(sp.n)]
+        outs = [Completion(list(s), [], []) for s in seqs]
+        alive = list(range(len(seqs)))
+        was_training = self.model.training
+        self.model.eval()
+        seen = None
+        if sp.repetition_penalty != 1.0:
+            seen = torch.zeros(len(seqs), self.model.config.vocab_size, dtype=torch.bool)
+            for i, s in enumerate(seqs):
+                seen[i, torch.tensor(s, dtype=torch.long)] = True
+        for _ in range(sp.max_tokens):
+            if not alive:
+                break
+            lens = [len(seqs[i]) for i in alive]
+            flat = torch.tensor([t for i in alive for t in seqs[i]], dtype=torch.long, device=dev)
+            ctx = SeqCtx.from_lengths(lens, dev)
+            hidden = self.model.forward_hidden(flat, ctx)
+            last = (ctx.cu_seqlens[1:] - 1).long()
+            logits = (hidden[last].float() @ self.model.lm_head_weight.float().t()).cpu()
+            tok, lp = sample_reference(logits, sp, g, None if seen is None else seen[alive])
+            nxt = []
+            for j, i in enumerate(alive):
+                t = int(tok[j])
+                seqs[i].append(t)
+                outs[i].token_ids.append(t)
+                outs[i].logprobs.append(float(lp[j]))
+                if seen is not None:
+                    seen[i, t] = True
+                if sp.eos_token_id is not None and (t == sp.eos_token_id or t in sp.stop_token_ids):
+                    outs[i].finish_reason = "stop"
+                else:
+                    nxt.append(i)
+            alive = nxt
+        if was_training:
+            self.model.train()
+        return outs
+
+
+class _PrefillKV:
+    """Attention hook used during prefill: append K/V to the paged cache, then varlen attention."""
+
+    def __init__(self, engine: "RolloutEngine", tok_slot, tok_pos):
+        self.e, self.tok_slot, self.tok_pos = engine, tok_slot, tok_pos
+
+    def attend(self, layer_idx, q, k, v, ctx):
+        from ..ops import cuda as K
+
+        e = self.e
+        K.kv_write_prefill(k.contiguous(), v.contiguous(), self.tok_slot, self.tok_pos, e.block_table, e.block_size,
+                           e.k_cache[layer_idx], e.v_cache[layer_idx])
+        return K.attention_varlen(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, True)
+
+
+class RolloutEngine:
+    def __init__(self, model: CausalLM, max_num_seqs: int = 64, max_model_len: int = 2048, block_size: int = 16,
+                 num_blocks: int | None = None, poll_every: int = 16, use_cuda_graph: bool = True, kv_splits: int = 0):
+        cfg = model.config
+        self.model, self.cfg = model, cfg
+        self.dev = model.device
+        if self.dev.type != "cuda":
+            raise RuntimeError("RolloutEngine needs a CUDA device; use EagerGenerator on CPU")
+        from .._native import host_runtime
+
+        rt = host_runtime()
+        if rt is None:
+            raise RuntimeError("libtrl_b200_host.so missing: run python -m trl_b200.csrc.build")
+        self.max_seqs, self.max_len, self.block_size = max_num_seqs, max_model_len, block_size
+        self.max_blocks = (max_model_len + block_size - 1) // block_size
+        self.num_blocks = num_blocks or max_num_seqs * self.max_blocks
+        self.sched = rt.scheduler(max_num_seqs, self.num_blocks, block_size, self.max_blocks)
+        L, Hk, D = cfg.num_hidden_layers, cfg.num_key_value_heads, cfg.head_dim
+        dt = torch.bfloat16
+        self.k_cache = [torch.zeros(self.num_blocks, block_size, Hk, D, dtype=dt, device=self.dev) for _ in range(L)]
+        self.v_cache = [torch.zeros(self.num_blocks, block_size, Hk, D, dtype=dt, device=self.dev) for _ in range(L)]
+        i32 = dict(dtype=torch.int32, device=self.dev)
+        self.block_table = torch.zeros(max_num_seqs, self.max_blocks, **i32)
+        self.block_table_host = torch.zeros(max_num_seqs, self.max_blocks, dtype=torch.int32).pin_memory()
+        self.seq_lens = torch.full((max_num_seqs,), -1, **i32)
+        self.n_gen = torch.zeros(max_num_seqs, **i32)
+        self.finished = torch.zeros(max_num_seqs, **i32)
+        self.next_input = torch.zeros(max_num_seqs, dtype=torch.int64, device=self.dev)
+        self.step_counter = torch.zeros(1, **i32)
+        self.tok = torch.zeros(max_num_seqs, **i32)
+        self.logp = torch.zeros(max_num_seqs, dtype=torch.float32, device=self.dev)
+        self.poll_every, self.use_graph = poll_every, use_cuda_graph and not cfg.is_moe
+        self.kv_splits = kv_splits or max(1, min(8, (2 * 148) // max(1, max_num_seqs * Hk)))
+        self.part_o = torch.empty(max_num_seqs * cfg.num_attention_heads * self.kv_splits * D, dtype=torch.float32,
+                                  device=self.dev)
+        self.part_ml = torch.empty(max_num_seqs * cfg.num_attention_heads * self.kv_splits * 2, dtype=torch.float32,
+                                   device=self.dev)
+        self.q_buf = torch.empty(max_num_seqs, cfg.num_attention_heads, D, dtype=dt, device=self.dev)
+        self.attn_buf = torch.empty(max_num_seqs, cfg.num_attention_heads, D, dtype=dt, device=self.dev)
+        self.seen = None
+        self.out_tokens = self.out_logps = None
+        self._graph = None
+        self._graph_key = None
+        self.stats = {"decode_steps": 0, "prefill_tokens": 0, "generated_tokens": 0}
+
+    # ---- weights ------------------------------------------------------------------------------
+    def sync_weights(self, model: CausalLM | None = None):
+        """TP=1 shares storage with the policy, so there is nothing to copy; the captured graph
+        reads the live parameter storage, hence optimizer updates are visible immediately."""
+        if model is not None and model is not self.model:
+            with torch.no_grad():
+                for (n, p), (_, q) in zip(self.model.named_parameters(), model.named_parameters()):
+                    p.copy_(q)
+
+    def reset_prefix_cache(self):
+        pass  # prefix blocks live only for the duration of one generate() call
+
+    # ---- one decode step (graph body) --------------------------------------------------------------
+    def _decode_step(self, sp: SamplingParams, max_total_len: int):
+        from ..ops import cuda as K
+
+        cfg, m = self.cfg, self.model
+        eps = cfg.rms_norm_eps
+        x = torch.nn.functional.embedding(self.next_input, m.embed_tokens)
+        scale = 1.0 / math.sqrt(cfg.head_dim)
+        for li, l in enumerate(m.layers):
+            h = K.rmsnorm_infer(x, l.input_layernorm, eps)
+            qkv = torch.nn.functional.linear(h, l.qkv_proj, l.qkv_bias)
+            if cfg.qk_norm:
+                qs, ks = cfg.q_size, cfg.kv_size
+                qn = K.rmsnorm_infer(qkv[:, :qs].reshape(-1, cfg.head_dim).contiguous(), l.q_norm, eps)
+                kn = K.rmsnorm_infer(qkv[:, qs:qs + ks].reshape(-1, cfg.head_dim).contiguous(), l.k_norm, eps)
+                qkv = torch.cat([qn.view(-1, qs), kn.view(-1, ks), qkv[:, qs + ks:]], dim=1)
+            K.rope_kv_write(qkv, self.seq_lens, None, self.block_table, self.block_size, self.q_buf, self.k_cache[li],
+                            self.v_cache[li], cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+                            cfg.rope_theta)
+            K.paged_decode_attn(self.q_buf, self.k_cache[li], self.v_cache[li], self.seq_lens, None, self.block_table,
+                                self.block_size, scale, self.kv_splits, self.part_o, self.part_ml, self.attn_buf)
+            x = x + torch.nn.functional.linear(self.attn_buf.view(self.max_seqs, -1), l.o_proj)
+            h = K.rmsnorm_infer(x, l.post_attention_layernorm, eps)
+            if cfg.is_moe:
+                from ..ops import functional as F_
+
+                y, _, _ = F_.moe_mlp(h, l.router, l.experts_gate_up, l.experts_down, cfg.num_experts_per_tok,
+                                     cfg.norm_topk_prob)
+                x = x + y
+            else:
+                gu = torch.nn.functional.linear(h, l.gate_up_proj)
+                x = x + torch.nn.functional.linear(K.swiglu_infer(gu), l.down_proj)
+        hN = K.rmsnorm_infer(x, m.norm, eps)
+        logits = torch.nn.functional.linear(hN, m.lm_head_weight)
+        self._sample(logits, sp)
+        K.advance(self.tok, self.logp, None, self.seq_lens, self.n_gen, self.finished, self.out_tokens, self.out_logps,
+                  sp.eos_token_id, max_total_len, self.next_input, self.step_counter, 1)
+        if self.seen is not None:
+            self.seen.scatter_(1, self.next_input[:, None], 1)
+
+    def _sample(self, logits, sp: SamplingParams, rows: Optional[torch.Tensor] = None, tok=None, logp=None):
+        from ..ops import cuda as K
+
+        tok = self.tok if tok is None else tok
+        logp = self.logp if logp is None else logp
+        z = logits
+        if self.seen is not None and sp.repetition_penalty != 1.0:
+            seen = self.seen if rows is None else self.seen[rows]
+            z = apply_repetition_penalty(z.float(), seen, sp.repetition_penalty)
+        if sp.needs_filter_pass:
+            z = filter_top_k_top_p(z.float() / max(sp.temperature, 1e-6), sp.top_k, sp.top_p).contiguous()
+            inv_t = 1.0
+        else:
+            inv_t = 1.0 / max(sp.temperature, 1e-6)
+        K.sample_tokens(z, inv_t, sp.min_p, sp.eos_token_id, sp.eos_prob_floor, sp.seed, self.step_counter,
+                        sp.greedy or sp.temperature == 0, tok, logp)
+
+    # ---- prefill -------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def _prefill(self, owners: list[tuple[int, list]]) -> torch.Tensor:
+        """owners: [(slot, prompt_ids)].  Returns last-token hidden states [len(owners), H]."""
+        lens = [len(p) for _, p in owners]
+        flat = torch.tensor([t for _, p in owners for t in p], dtype=torch.long).pin_memory().to(self.dev, non_blocking=True)
+        tok_slot = torch.tensor([s for (s, p) in owners for _ in p], dtype=torch.int32).to(self.dev, non_blocking=True)
+        ctx = SeqCtx.from_lengths(lens, self.dev)
+        ctx.kv = _PrefillKV(self, tok_slot, ctx.positions.to(torch.int32))
+        self.stats["prefill_tokens"] += int(flat.numel())
+        was = self.model.training
+        self.model.eval()
+        hidden = self.model.forward_hidden(flat, ctx)
+        if was:
+            self.model.train()
+        return hidden[(ctx.cu_seqlens[1:] - 1).long()]
+
+    # ---- public API -----------------------------------------------------------------------------------
+    @torch.no_grad()
+    def generate(self, prompts: Sequence[Sequence[int]], sp: SamplingParams) -> list[Completion]:
+        from ..ops import cuda as K
+
+        n_req = len(prompts) * sp.n
+        max_new = sp.max_tokens
+        max_prompt = max(len(p) for p in prompts)
+        max_total = min(self.max_len, max_prompt + max_new)
+        if max_prompt + 1 > self.max_len:
+            raise ValueError(f"prompt of {max_prompt} tokens does not fit max_model_len={self.max_len}")
+        dev = self.dev
+        if self.out_tokens is None or self.out_tokens.shape[1] != max_new:
+            self.out_tokens = torch.zeros(self.max_seqs, max_new, dtype=torch.int32, device=dev)
+            self.out_logps = torch.zeros(self.max_seqs, max_new, dtype=torch.float32, device=dev)
+            self._graph = None
+        if sp.repetition_penalty != 1.0 and self.seen is None:
+            self.seen = torch.zeros(self.max_seqs, self.cfg.vocab_size, dtype=torch.uint8, device=dev)
+            self._graph = None
+        reqs = []
+        for pi, p in enumerate(prompts):
+            for j in range(sp.n):
+                rid = len(reqs)
+                reqs.append((list(p), pi))
+                self.sched.add(rid, len(p), min(max_new, self.max_len - len(p)), pi)
+        results: list[Optional[Completion]] = [None] * n_req
+        slot_req = [-1] * self.max_seqs
+        self.seq_lens.fill_(-1)
+        self.finished.zero_()
+        self.n_gen.zero_()
+        bt_np = self.block_table_host.numpy()
+        graph_key = (sp.temperature, sp.top_p, sp.top_k, sp.min_p, sp.repetition_penalty, sp.eos_token_id,
+                     sp.eos_prob_floor, sp.seed, sp.greedy, max_total, max_new)
+        while True:
+            admitted = self.sched.admit(bt_np)
+            if admitted:
+                self.block_table.copy_(self.block_table_host, non_blocking=True)
+                owners = [(slot, reqs[rid][0]) for rid, slot, pre, _ in admitted if pre]
+                group_row = {reqs[rid][1]: i for i, (rid, slot, pre, _) in enumerate([a for a in admitted if a[2]])}
+                last_h = self._prefill(owners) if owners else None
+                # sharers: copy the partial tail block of the prompt from the group's owner
+                for rid, slot, pre, copy_blk in admitted:
+                    plen = len(reqs[rid][0])
+                    if not pre and copy_blk >= 0:
+                        dst = int(bt_np[slot, plen // self.block_size])
+                        for li in range(self.cfg.num_hidden_layers):
+                            self.k_cache[li][dst].copy_(self.k_cache[li][copy_blk])
+                            self.v_cache[li][dst].copy_(self.v_cache[li][copy_blk])
+                slots = torch.tensor([a[1] for a in admitted], dtype=torch.int32, device=dev)
+                plen_t = torch.tensor([len(reqs[a[0]][0]) for a in admitted], dtype=torch.int32, device=dev)
+                self.seq_lens[slots.long()] = plen_t
+                self.finished[slots.long()] = 0
+                self.n_gen[slots.long()] = 0
+                if self.seen is not None:
+                    self.seen[slots.long()] = 0
+                    for a in admitted:
+                        self.seen[a[1], torch.tensor(reqs[a[0]][0], device=dev)] = 1
+                # first token of every admitted request from its group's last-prompt-token logits
+                if last_h is not None and len(group_row) == len(set(reqs[a[0]][1] for a in admitted)):
+                    rows = torch.tensor([group_row[reqs[a[0]][1]] for a in admitted], device=dev)
+                    h_rows = last_h[rows]
+                else:  # a sharer admitted after its owner's batch: recompute the prompt's last hidden state
+                    need = {}
+                    for a in admitted:
+                        need.setdefault(reqs[a[0]][1], a)
+                    tmp = self._prefill_hidden_only([reqs[a[0]][0] for a in need.values()])
+                    gi = {g: i for i, g in enumerate(need)}
+                    h_rows = tmp[torch.tensor([gi[reqs[a[0]][1]] for a in admitted], device=dev)]
+                logits = torch.nn.functional.linear(h_rows, self.model.lm_head_weight)
+                tok = torch.empty(len(admitted), dtype=torch.int32, device=dev)
+                lp = torch.empty(len(admitted), dtype=torch.float32, device=dev)
+                self._sample(logits, sp, rows=slots.long(), tok=tok, logp=lp)
+                K.advance(tok, lp, slots, self.seq_lens, self.n_gen, self.finished, self.out_tokens, self.out_logps,
+                          sp.eos_token_id, max_total, self._scatter_next(slots), self.step_counter, 0)
+                self.next_input[slots.long()] = self._tmp_next[: len(admitted)]
+                if self.seen is not None:
+                    self.seen.scatter_(1, self.next_input[:, None], 1)
+                for rid, slot, _, _ in admitted:
+                    slot_req[slot] = rid
+            if self.sched.num_running == 0:
+                break
+            # ---- decode until the next poll ----
+            if self.use_graph:
+                if self._graph is None or self._graph_key != graph_key:
+                    self._capture(sp, max_total, graph_key)
+                for _ in range(self.poll_every):
+                    self._graph.replay()
+            else:
+                for _ in range(self.poll_every):
+                    self._decode_step(sp, max_total)
+            self.stats["decode_steps"] += self.poll_every
+            fin = self.finished.cpu().numpy()  # host sync: the only one per poll
+            done_slots = [s for s in range(self.max_seqs) if slot_req[s] >= 0 and fin[s]]
+            if done_slots:
+                ds = torch.tensor(done_slots, device=dev)
+                ng = self.n_gen[ds].cpu().numpy()
+                toks = self.out_tokens[ds].cpu().numpy()
+                lps = self.out_logps[ds].cpu().numpy()
+                for j, s in enumerate(done_slots):
+                    rid = slot_req[s]
+                    n = int(min(ng[j], max_new))
+                    t = toks[j, :n].tolist()
+                    reason = "stop" if (sp.eos_token_id is not None and n and t[-1] == sp.eos_token_id) else "length"
+                    results[rid] = Completion(reqs[rid][0], t, lps[j, :n].tolist(), reason)
+                    self.stats["generated_tokens"] += n
+                    self.sched.retire(s, reqs[rid][1])
+                    slot_req[s] = -1
+                self.seq_lens[ds] = -1
+                self.finished[ds] = 0
+        K.check_status(dev)
+        return results  # type: ignore[return-value]
+
+    def _scatter_next(self, slots):
+        self._tmp_next = torch.zeros(self.max_seqs, dtype=torch.int64, device=self.dev)
+        return self._tmp_next
+
+    def _prefill_hidden_only(self, prompts):
+        lens = [len(p) for p in prompts]
+        flat = torch.tensor([t for p in prompts for t in p], dtype=torch.long, device=self.dev)
+        ctx = SeqCtx.from_lengths(lens, self.dev)
+        hidden = self.model.forward_hidden(flat, ctx)
+        return hidden[(ctx.cu_seqlens[1:] - 1).long()]
+
+    def _capture(self, sp, max_total, key):
+        # one eager step on a side stream warms every allocation and scratch buffer, but it also
+        # advances the state: snapshot and restore the mutable tensors around warm-up and capture.
+        state = [t.clone() for t in (self.seq_lens, self.n_gen, self.finished, self.next_input, self.step_counter,
+                                     self.out_tokens, self.out_logps)]
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._decode_step(sp, max_total)
+        torch.cuda.current_stream().wait_stream(s)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._decode_step(sp, max_total)
+        for t, o in zip((self.seq_lens, self.n_gen, self.finished, self.next_input, self.step_counter, self.out_tokens,
+                         self.out_logps), state):
+            t.copy_(o)
+        self._graph, self._graph_key = g, key

@@ -1,0 +1,446 @@
+"""Group Relative Policy Optimization.
+
+Algorithm and option surface of trl/trainer/grpo_trainer.py: generation + scoring
+(:2260-2853), advantages (:2679-2738), loss variants grpo/bnpo/dr_grpo/dapo/cispo/
+sapo/luspo/vespo (:3054-3150), token- or sequence-level importance sampling, k3 KL,
+two-sided clip, off-policy sequence mask, top-entropy-quantile mask, entropy bonus
+(static / adaptive with a checkpointed controller), rollout importance-sampling
+correction.  On GPUs the default loss family (token-level ratio, clip, KL, masked
+normalisation and all metric sums) is one fused kernel (`ops.cuda.grpo_loss`).
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Any
+
+import torch
+
+from ..data_utils import is_conversational
+from ..parallel import dist as D
+from .grpo_config import GRPOConfig
+from .online_base import OnlineTrainer
+from .utils import nanmax, nanmin, nanstd, pad
+
+
+class GRPOTrainer(OnlineTrainer):
+    _tag_names = ["trl", "grpo"]
+    _name = "GRPO"
+
+    def __init__(self, model, reward_funcs, args: GRPOConfig | None = None, train_dataset=None, eval_dataset=None,
+                 processing_class=None, reward_processing_classes=None, callbacks=None, optimizers=(None, None),
+                 quantization_config=None, peft_config=None, tools=None, rollout_func=None, environment_factory=None):
+        if args is None:
+            name = model if isinstance(model, str) else getattr(model, "name_or_path", "model")
+            args = GRPOConfig(f"{os.path.basename(str(name).rstrip('/'))}-GRPO")
+        if quantization_config is not None:
+            raise NotImplementedError("quantised policies: no 4/8-bit weight kernels in this build")
+        super().__init__(model, reward_funcs, args, train_dataset, eval_dataset, processing_class,
+                         reward_processing_classes, callbacks, optimizers, peft_config, tools, rollout_func,
+                         environment_factory)
+        a = args
+        self.loss_type, self.scale_rewards = a.loss_type, a.scale_rewards
+        self.importance_sampling_level = a.importance_sampling_level
+        self.multi_objective_aggregation = a.multi_objective_aggregation
+        self.top_entropy_quantile = a.top_entropy_quantile
+        self.off_policy_mask_threshold = a.off_policy_mask_threshold
+        self.vllm_importance_sampling_correction = a.vllm_importance_sampling_correction
+        self.entropy_coef = a.entropy_coef
+        self._entropy_bonus_enabled = a.entropy_coef != 0.0 or a.use_adaptive_entropy
+        if self.tools and not self.rollout_func:
+            from .tool_loop import ToolLoop
+
+            self._tool_loop = ToolLoop(self, self.tools, a.max_tool_calling_iterations)
+        else:
+            self._tool_loop = None
+
+    # ---- generation + scoring ------------------------------------------------------------------------------
+    def _generate_and_score_completions(self, inputs: list[dict]) -> dict[str, Any]:
+        a = self.args
+        dev = a.device
+        mode = "train" if self.model.training else "eval"
+        prompts = [x["prompt"] for x in inputs]
+        if self._tool_loop is not None:
+            prompt_ids, completion_ids, sampling_logps, extras = self._tool_loop.generate(prompts)
+        else:
+            prompt_ids, completion_ids, sampling_logps, extras = self._generate(prompts)
+        tool_mask = extras.pop("env_mask", extras.pop("tool_mask", None))
+        B = len(prompts)
+        comp_lens = torch.tensor([len(c) for c in completion_ids], device=dev)
+        Tc = max(1, int(comp_lens.max()))
+        completion_mask = (torch.arange(Tc, device=dev)[None] < comp_lens[:, None]).int()
+        eos_or_pad = {self.eos_token_id, self.pad_token_id}
+        is_trunc = torch.tensor([len(c) == 0 or c[-1] not in eos_or_pad for c in completion_ids], device=dev)
+        if self.mask_truncated_completions:
+            completion_mask = completion_mask * (~is_trunc)[:, None].int()
+        if tool_mask is not None:
+            tm = pad([torch.tensor(t, device=dev) for t in tool_mask], 0, "right")
+            tm = torch.nn.functional.pad(tm, (0, Tc - tm.shape[1]))
+        else:
+            tm = None
+        loss_mask = completion_mask if tm is None else completion_mask * tm
+        num_items_in_batch = D.gather(loss_mask.sum().reshape(1)).sum().float()
+        bs = a.per_device_train_batch_size if mode == "train" else a.per_device_eval_batch_size
+        out: dict[str, Any] = {}
+        with torch.no_grad():
+            generate_every = a.steps_per_generation * self.num_iterations
+            need_old = a.gradient_accumulation_steps % generate_every != 0 or (
+                self.use_vllm and self.vllm_importance_sampling_correction and sampling_logps is not None)
+            old_logps = None
+            if need_old:
+                old_logps, _ = self._get_per_token_logps_and_entropies(self.model, prompt_ids, completion_ids, bs)
+            if self.use_vllm and self.vllm_importance_sampling_correction and sampling_logps is not None:
+                slp = pad([torch.tensor(l, dtype=torch.float32, device=dev) for l in sampling_logps], 0.0, "right")
+                slp = torch.nn.functional.pad(slp, (0, Tc - slp.shape[1]))
+                out["sampling_per_token_logps"] = slp
+                out["importance_sampling_ratio"] = self._rollout_is_ratio(old_logps, slp, loss_mask)
+            if self.beta != 0.0:
+                out["ref_per_token_logps"] = self._ref_logps(prompt_ids, completion_ids, bs)
+            if old_logps is not None:
+                out["old_per_token_logps"] = old_logps
+        # ---- rewards and advantages -------------------------------------------------------------------------------
+        tok = self.processing_class
+        completions_text = tok.batch_decode(completion_ids, skip_special_tokens=True)
+        if prompts and is_conversational(inputs[0]):
+            completions = [[{"role": "assistant", "content": c}] for c in completions_text]
+        else:
+            completions = completions_text
+        for k, v in extras.items():
+            if isinstance(v, list) and len(v) == B:
+                for ex, val in zip(inputs, v):
+                    ex[k] = val
+        rewards_per_func = self._calculate_rewards(inputs, prompts, completions, completion_ids)
+        ng = self.num_generations if mode == "train" else self.num_generations_eval
+        advantages, rewards, std_rewards, is_std_zero = self._advantages(rewards_per_func, ng)
+        sl = slice(D.rank() * B, (D.rank() + 1) * B)
+        all_adv = advantages.clone()
+        advantages = advantages[sl]
+        # ---- metrics ----------------------------------------------------------------------------------------------
+        m = self._metrics[mode]
+        if mode == "train":
+            self._total_train_tokens += int(D.gather((torch.tensor([len(p) for p in prompt_ids], device=dev).sum()
+                                                      + comp_lens.sum()).reshape(1)).sum())
+        m["num_tokens"].append(float(self._total_train_tokens))
+        agg_len = D.gather(comp_lens.float())
+        m["completions/mean_length"].append(agg_len.mean())
+        m["completions/min_length"].append(agg_len.min())
+        m["completions/max_length"].append(agg_len.max())
+        agg_trunc = D.gather(is_trunc.float())
+        term = agg_len[agg_trunc == 0]
+        m["completions/clipped_ratio"].append(agg_trunc.mean())
+        if term.numel() == 0:
+            term = torch.zeros(1, device=dev)
+        m["completions/mean_terminated_length"].append(term.mean())
+        m["completions/min_terminated_length"].append(term.min())
+        m["completions/max_terminated_length"].append(term.max())
+        for i, name in enumerate(self.reward_func_names):
+            col = rewards_per_func[:, i]
+            m[f"rewards/{name}/mean"].append(torch.nanmean(col))
+            m[f"rewards/{name}/std"].append(nanstd(col))
+        m["reward"].append(torch.nanmean(rewards))
+        m["reward_std"].append(torch.nanmean(std_rewards))
+        m["frac_reward_zero_std"].append(is_std_zero.float().mean())
+        for k, v in getattr(self, "_extra_metrics", {}).items():
+            m[k].append(sum(v) / max(1, len(v)))
+        if "importance_sampling_ratio" in out:
+            r = out["importance_sampling_ratio"]
+            flat = r[loss_mask.bool()] if r.shape == loss_mask.shape else r.flatten()
+            if flat.numel():
+                m["sampling/importance_sampling_ratio/min"].append(flat.min())
+                m["sampling/importance_sampling_ratio/mean"].append(flat.mean())
+                m["sampling/importance_sampling_ratio/max"].append(flat.max())
+            d = (out["old_per_token_logps"] - out["sampling_per_token_logps"]).abs()[loss_mask.bool()]
+            if d.numel():
+                m["sampling/sampling_logp_difference/mean"].append(d.mean())
+                m["sampling/sampling_logp_difference/max"].append(d.max())
+        if self.log_completions:
+            pt = D.gather_object([p if isinstance(p, str) else p for p in prompts])
+            ct = D.gather_object(completions_text)
+            self._logs["prompt"].extend(pt)
+            self._logs["completion"].extend(ct)
+            for i, name in enumerate(self.reward_func_names):
+                self._logs["rewards"][name].extend(rewards_per_func[:, i].tolist())
+            self._logs["advantages"].extend(all_adv.tolist())
+            for k, v in getattr(self, "_extra_cols", {}).items():
+                self._logs["extra"][k].extend(D.gather_object(v))
+        out.update({
+            "prompt_ids": prompt_ids, "completion_ids_list": completion_ids,
+            "completion_mask": completion_mask, "advantages": advantages,
+            "num_items_in_batch": num_items_in_batch,
+        })
+        if tm is not None:
+            out["tool_mask"] = tm
+        return out
+
+    def _advantages(self, rewards_per_func, ng):
+        dev = rewards_per_func.device
+        w = self.reward_weights.to(dev)
+        unscorable = torch.isnan(rewards_per_func).all(dim=1)
+        if self.multi_objective_aggregation == "sum_then_normalize":
+            rewards = (rewards_per_func * w[None]).nansum(dim=1)
+            rewards[unscorable] = float("nan")
+            mean_g = torch.nanmean(rewards.view(-1, ng), dim=1).repeat_interleave(ng)
+            if self.scale_rewards in ("group", "none"):
+                std = nanstd(rewards.view(-1, ng), dim=1).repeat_interleave(ng) if ng > 1 else torch.zeros_like(rewards)
+            else:
+                std = nanstd(rewards).expand_as(rewards) if rewards.numel() > 1 else torch.zeros_like(rewards)
+            adv = rewards - mean_g
+            if self.scale_rewards != "none":
+                adv = adv / (std + 1e-4)
+        elif self.multi_objective_aggregation == "normalize_then_sum":
+            g = rewards_per_func.view(-1, ng, rewards_per_func.shape[1])
+            mean_k = torch.nanmean(g, dim=1, keepdim=True)
+            std_k = nanstd(g, dim=1, keepdim=True) if ng > 1 else torch.zeros_like(mean_k)
+            rk = ((g - mean_k) / (std_k + 1e-4)).view(-1, rewards_per_func.shape[1])
+            rewards = (rk * w[None]).nansum(dim=1)
+            rewards[unscorable] = float("nan")
+            std = nanstd(rewards).expand_as(rewards) if rewards.numel() > 1 else torch.zeros_like(rewards)
+            adv = (rewards - torch.nanmean(rewards)) / (std + 1e-4)
+        else:
+            raise ValueError(f"Invalid multi_objective_aggregation: {self.multi_objective_aggregation}")
+        is_std_zero = torch.isclose(std, torch.zeros_like(std))
+        return torch.nan_to_num(adv, nan=0.0), rewards, std, is_std_zero
+
+    def _rollout_is_ratio(self, train_logps, sampling_logps, mask):
+        """Correction for the mismatch between the rollout engine's and the trainer's log-probs
+        (modes of grpo_trainer.py:2579-2623)."""
+        a = self.args
+        mode = a.vllm_importance_sampling_mode
+        diff = (train_logps - sampling_logps) * mask
+        if mode.startswith("sequence"):
+            lr = diff.sum(-1, keepdim=True)
+        else:
+            lr = diff
+        ratio = torch.exp(lr)
+        cmax, cmin = a.vllm_importance_sampling_clip_max, a.vllm_importance_sampling_clip_min
+        if mode.endswith("truncate"):
+            ratio = torch.clamp(ratio, max=cmax)
+            if cmin is not None:
+                ratio = torch.clamp(ratio, min=cmin)
+        else:
+            bad = ratio > cmax
+            if cmin is not None:
+                bad = bad | (ratio < cmin)
+            ratio = ratio.masked_fill(bad, 0.0)
+        return ratio.expand_as(mask) if ratio.shape != mask.shape else ratio
+
+    # ---- loss ----------------------------------------------------------------------------------------------------------
+    def compute_loss(self, model, inputs, return_outputs=False, num_items_in_batch=None):
+        if return_outputs:
+            raise ValueError("The GRPOTrainer does not support returning outputs")
+        return self._compute_loss(model, inputs)
+
+    @staticmethod
+    def get_off_policy_mask(advantages, per_token_logps, sampling_per_token_logps, mask, off_policy_threshold):
+        kl = ((sampling_per_token_logps - per_token_logps.detach()) * mask).sum(-1, keepdim=True) / mask.sum(
+            -1, keepdim=True).clamp(min=1.0)
+        keep = (advantages >= 0) | (kl <= off_policy_threshold)
+        return keep.to(per_token_logps.dtype)
+
+    @staticmethod
+    def get_gamma_weights(advantages, log_ratio_per_token, mask, importance_sampling_ratio, k_pos, lambda_pos, k_neg,
+                          lambda_neg):
+        """VESPO sequence weights: phi(w) = w^k exp(lambda (1 - w)) on the detached sequence ratio."""
+        lr = log_ratio_per_token.detach()
+        if importance_sampling_ratio is not None:
+            lr = lr + torch.log(importance_sampling_ratio.clamp_min(1e-8))
+        seq = (lr * mask).sum(-1, keepdim=True)
+        k = torch.where(advantages >= 0, torch.full_like(advantages, k_pos), torch.full_like(advantages, k_neg))
+        lam = torch.where(advantages >= 0, torch.full_like(advantages, lambda_pos), torch.full_like(advantages, lambda_neg))
+        logphi = k * seq + lam * (1 - torch.exp(seq))
+        return torch.exp(logphi).detach()
+
+    def _compute_loss(self, model, inputs):
+        a = self.args
+        mode = "train" if self.model.training else "eval"
+        m = self._metrics[mode]
+        prompt_ids, completion_ids = inputs["prompt_ids"], inputs["completion_ids_list"]
+        completion_mask = inputs["completion_mask"]
+        mask = completion_mask if "tool_mask" not in inputs else completion_mask * inputs["tool_mask"]
+        maskf = mask.float()
+        logps, entropies = self._get_per_token_logps_and_entropies(model, prompt_ids, completion_ids,
+                                                                   compute_entropy=True)
+        Tc = logps.shape[1]
+        if maskf.shape[1] != Tc:  # the buffered mask is padded to the generation batch's longest completion
+            maskf = maskf[:, :Tc] if maskf.shape[1] > Tc else torch.nn.functional.pad(maskf, (0, Tc - maskf.shape[1]))
+
+        def fit(t):
+            if t is None or t.ndim < 2 or t.shape[1] == Tc or t.shape[1] == 1:
+                return t
+            return t[:, :Tc] if t.shape[1] > Tc else torch.nn.functional.pad(t, (0, Tc - t.shape[1]))
+        entropy_mask = None
+        if self.top_entropy_quantile < 1.0:
+            entropy_mask = self.get_high_entropy_mask(entropies, maskf, 1 - self.top_entropy_quantile)
+        advantages = inputs["advantages"]
+        adv2 = advantages[:, None] if advantages.ndim == 1 else advantages
+        old = fit(inputs.get("old_per_token_logps"))
+        ref = fit(inputs.get("ref_per_token_logps"))
+        isr = fit(inputs.get("importance_sampling_ratio"))
+        B = logps.shape[0]
+        ga = self.current_gradient_accumulation_steps if mode == "train" else 1.0
+        simple = (self.loss_type in ("grpo", "bnpo", "dr_grpo", "dapo") and self.importance_sampling_level == "token"
+                  and entropy_mask is None and self.off_policy_mask_threshold is None and isr is None
+                  and not a.use_bias_correction_kl and not self._entropy_bonus_enabled and advantages.ndim == 1)
+        if simple and logps.is_cuda:
+            from ..ops import cuda as K
+
+            if self.loss_type == "grpo":
+                row_scale = 1.0 / (maskf.sum(-1).clamp(min=1.0) * B * ga)
+            elif self.loss_type == "bnpo":
+                row_scale = (1.0 / (maskf.sum().clamp(min=1.0) * ga)).expand(B)
+            elif self.loss_type == "dr_grpo":
+                row_scale = torch.full((B,), 1.0 / (B * self.max_completion_length * ga), device=logps.device)
+            else:
+                row_scale = (D.world_size() / inputs["num_items_in_batch"].clamp(min=1.0)).expand(B)
+            loss, stats = K.grpo_loss(logps, old, ref if self.beta != 0.0 else None, advantages, maskf, row_scale.float(),
+                                      entropies, self.epsilon_low, self.epsilon_high, self.beta, a.delta)
+            n = stats[4].clamp(min=1.0)
+            red = torch.stack([stats[1], stats[2], stats[3], stats[6], stats[7], stats[4]]).clone()
+            if D.world_size() > 1:
+                D.all_reduce(red, "sum")
+            tot = red[5].clamp(min=1.0)
+            if self.beta != 0.0:
+                m["kl"].append(red[0] / tot)
+            m["clip_ratio/low_mean"].append(red[1] / tot)
+            m["clip_ratio/high_mean"].append(red[2] / tot)
+            m["clip_ratio/region_mean"].append(red[3] / tot)
+            m["entropy"].append(red[4] / tot)
+            return self._add_aux(loss, m)
+        # ---- general path (autograd over PyTorch ops) -----------------------------------------------------------------
+        old = logps.detach() if old is None else old
+        off_mask = None
+        if self.off_policy_mask_threshold is not None:
+            samp = fit(inputs.get("sampling_per_token_logps"))
+            off_mask = self.get_off_policy_mask(adv2, logps, samp if samp is not None else old, maskf,
+                                                self.off_policy_mask_threshold)
+        log_ratio = logps - old
+        if self.importance_sampling_level == "token":
+            liw = log_ratio
+        else:
+            liw = ((log_ratio * maskf).sum(-1) / maskf.sum(-1).clamp(min=1.0))[:, None]
+        coef_1 = torch.exp(liw)
+        kl = None
+        if self.beta != 0.0:
+            kl = torch.exp(ref - logps) - (ref - logps) - 1
+            if a.use_bias_correction_kl:
+                kl = kl * coef_1
+        if self.loss_type == "cispo":
+            per_tok = -torch.clamp(coef_1, max=self.epsilon_high).detach() * adv2 * logps
+        elif self.loss_type in ("grpo", "bnpo", "dr_grpo", "dapo", "luspo"):
+            coef_2 = torch.clamp(coef_1, 1 - self.epsilon_low, 1 + self.epsilon_high)
+            c1 = torch.clamp(coef_1, max=a.delta) if a.delta is not None else coef_1
+            per_tok = -torch.min(c1 * adv2, coef_2 * adv2)
+        elif self.loss_type == "sapo":
+            temps = torch.where(adv2 > 0, torch.full_like(adv2, a.sapo_temperature_pos),
+                                torch.full_like(adv2, a.sapo_temperature_neg))
+            per_tok = -(torch.sigmoid(temps * (coef_1 - 1)) * 4 / temps) * adv2
+        elif self.loss_type == "vespo":
+            phi = self.get_gamma_weights(adv2, log_ratio, maskf, isr, a.vespo_k_pos, a.vespo_lambda_pos, a.vespo_k_neg,
+                                         a.vespo_lambda_neg)
+            m["vespo/phi_seq_mean"].append(phi.mean().detach())
+            per_tok = -phi * adv2 * logps
+        else:
+            raise ValueError(f"Unknown loss type: {self.loss_type}")
+        if off_mask is not None:
+            per_tok = per_tok * off_mask
+        if entropy_mask is not None:
+            per_tok = per_tok * entropy_mask
+        if isr is not None and self.loss_type != "vespo":
+            per_tok = per_tok * isr
+        if kl is not None:
+            per_tok = per_tok + self.beta * kl
+        if self.loss_type in ("grpo", "sapo"):
+            loss = ((per_tok * maskf).sum(-1) / maskf.sum(-1).clamp(min=1.0)).mean() / ga
+        elif self.loss_type == "bnpo":
+            loss = (per_tok * maskf).sum() / maskf.sum().clamp(min=1.0) / ga
+        elif self.loss_type == "dr_grpo":
+            loss = (per_tok * maskf).sum() / (B * self.max_completion_length) / ga
+        elif self.loss_type in ("cispo", "dapo", "vespo"):
+            loss = (per_tok * maskf).sum() / (inputs["num_items_in_batch"].clamp(min=1.0) / D.world_size())
+        else:  # luspo
+            loss = (per_tok * maskf.sum(1, keepdim=True)).mean() / ga
+        if self._entropy_bonus_enabled:
+            eff = maskf if entropy_mask is None else maskf * entropy_mask
+            sums = torch.stack([(entropies * eff).sum(), eff.sum()])
+            g = D.all_reduce(sums.clone(), "sum") if D.world_size() > 1 else sums
+            mean_ent = g[0] / g[1].clamp(min=1.0)
+            # entropy carries no gradient through the fused head: the bonus acts through the
+            # score-function surrogate -(H_t + log p_t) * log p_t, detached in its first factor
+            surrogate = (-(logps.detach() + entropies) * logps * eff).sum() / g[1].clamp(min=1.0) * D.world_size()
+            loss = loss - self.entropy_coef * surrogate / ga
+            m["entropy_coef"].append(self.entropy_coef)
+            if a.use_adaptive_entropy and mode == "train":
+                self._pending_entropy = float(mean_ent)
+
+        def mmean(x):
+            s = torch.stack([(x * maskf).sum(), maskf.sum()])
+            if D.world_size() > 1:
+                D.all_reduce(s, "sum")
+            return s[0] / s[1].clamp(min=1.0)
+        m["entropy"].append(mmean(entropies))
+        if kl is not None:
+            m["kl"].append(mmean(kl.detach()))
+        if self.loss_type in ("grpo", "bnpo", "dr_grpo", "dapo", "luspo"):
+            low = ((coef_1 < 1 - self.epsilon_low) & (adv2 < 0)).float().expand_as(maskf)
+            high = ((coef_1 > 1 + self.epsilon_high) & (adv2 > 0)).float().expand_as(maskf)
+            m["clip_ratio/low_mean"].append(mmean(low))
+            m["clip_ratio/high_mean"].append(mmean(high))
+            m["clip_ratio/region_mean"].append(mmean(((low + high) > 0).float()))
+        elif self.loss_type == "cispo":
+            m["cispo_clip_ratio"].append(mmean(((coef_1 > self.epsilon_high) & (adv2 > 0)).float().expand_as(maskf)))
+        return self._add_aux(loss, m)
+
+    def _add_aux(self, loss, m):
+        aux = getattr(self, "_last_aux_loss", None)
+        if aux is not None:
+            loss = loss + self.args.router_aux_loss_coef * aux / self.current_gradient_accumulation_steps
+            m["aux_loss"].append(aux.detach())
+        return loss
+
+    def get_high_entropy_mask(self, entropies, mask, threshold: float):
+        """Keep tokens whose entropy is at or above the global ``threshold`` quantile (:1396-1432)."""
+        local = entropies[mask.bool()].float()
+        if D.world_size() > 1:
+            n = torch.tensor([local.numel()], device=local.device)
+            mx = int(D.all_reduce(n.clone(), "max"))
+            padded = torch.cat([local, local.new_full((mx - local.numel(),), float("nan"))])
+            allv = D.gather(padded)
+            allv = allv[~torch.isnan(allv)]
+        else:
+            allv = local
+        if allv.numel() == 0:
+            return torch.zeros_like(entropies)
+        thr = torch.quantile(allv, threshold)
+        return ((entropies >= thr) & mask.bool()).float()
+
+    # ---- adaptive entropy controller --------------------------------------------------------------------------------
+    def training_step(self, model, inputs, num_items_in_batch=None):
+        out = super().training_step(model, inputs, num_items_in_batch)
+        a = self.args
+        if a.use_adaptive_entropy and getattr(self, "_pending_entropy", None) is not None:
+            if self._pending_entropy < a.entropy_target:
+                self.entropy_coef = min(a.entropy_coef_max, self.entropy_coef + a.entropy_coef_delta)
+            else:
+                self.entropy_coef = max(a.entropy_coef_min, self.entropy_coef - a.entropy_coef_delta)
+            self._pending_entropy = None
+        return out
+
+    def prediction_step(self, model, inputs, prediction_loss_only=True, ignore_keys=None):
+        inputs = self._prepare_inputs(inputs)
+        with torch.no_grad():
+            loss = self._compute_loss(model, inputs)
+        return loss.detach(), None, None
+
+    def _save_checkpoint(self, model, trial=None, metrics=None):
+        super()._save_checkpoint(model, trial, metrics)
+        if self.args.use_adaptive_entropy and self.args.should_save:
+            folder = os.path.join(self.args.output_dir, f"checkpoint-{self.state.global_step}")
+            with open(os.path.join(folder, "entropy_ctrl_state.json"), "w") as f:
+                json.dump({"entropy_coef": self.entropy_coef}, f)
+
+    def _on_checkpoint_loaded(self, folder: str):
+        p = os.path.join(folder, "entropy_ctrl_state.json")
+        if os.path.exists(p):
+            with open(p) as f:
+                self.entropy_coef = json.load(f)["entropy_coef"]
+        self._buffered_inputs = None  # a resumed run regenerates (grpo_trainer.py:1572-1574)

@@ -1,0 +1,380 @@
+"""Shared machinery of the online-RL trainers (GRPO, RLOO): prompt sampling schedule,
+generation through the rollout engine, reward evaluation, per-token log-probabilities.
+
+Follows the skeleton of trl/trainer/grpo_trainer.py (dataloader/sampler :1213-1271,
+``_prepare_inputs`` buffering :1555-1584, ``_generate`` :2143-2258, ``_calculate_rewards``
+:1612-1703, ``_get_per_token_logps_and_entropies`` :1435-1541) with the forward kept
+padding-free and the lm_head fused with the log-softmax gather.
+"""
+from __future__ import annotations
+
+import asyncio
+import copy
+import inspect
+import os
+import warnings
+from collections import defaultdict, deque
+from typing import Any, Callable, Optional
+
+import torch
+import torch.nn as nn
+
+from ..data_utils import apply_chat_template, is_conversational, maybe_apply_chat_template
+from ..loop.trainer import Trainer
+from ..models.decoder import CausalLM, SeqCtx
+from ..ops import functional as ops
+from ..parallel import dist as D
+from ..rollout.sampling import SamplingParams
+from .utils import (RepeatSampler, create_model_from_path, disable_dropout_in_model, nanmax, nanmin, nanstd, pad,
+                    print_prompt_completions_sample, run_coroutine_sync, shuffle_sequence_dict, split_tensor_dict,
+                    use_adapter)
+
+RewardFunc = Any
+
+
+def _identity(x):
+    return x
+
+
+class OnlineTrainer(Trainer):
+    _name = "Online"
+
+    def __init__(self, model, reward_funcs, args, train_dataset=None, eval_dataset=None, processing_class=None,
+                 reward_processing_classes=None, callbacks=None, optimizers=(None, None), peft_config=None,
+                 tools=None, rollout_func=None, environment_factory=None):
+        if isinstance(model, str):
+            kw = dict(args.model_init_kwargs or {})
+            model_id = model
+            model = create_model_from_path(model, **kw)
+        else:
+            model_id = getattr(model, "name_or_path", "")
+        if peft_config is not None:
+            from ..models.lora import get_peft_model
+
+            model = get_peft_model(model, peft_config)
+        if processing_class is None:
+            from transformers import AutoTokenizer
+
+            processing_class = AutoTokenizer.from_pretrained(model_id, padding_side="left")
+        tok = processing_class
+        if tok.pad_token is None:
+            tok.pad_token = tok.eos_token
+        self.pad_token_id, self.eos_token_id = tok.pad_token_id, tok.eos_token_id
+        # ---- reward functions -------------------------------------------------------------------
+        if not isinstance(reward_funcs, list):
+            reward_funcs = [reward_funcs]
+        self.reward_func_names = []
+        for i, rf in enumerate(reward_funcs):
+            if isinstance(rf, str):
+                reward_funcs[i] = create_model_from_path(rf, num_labels=1, **dict(args.model_init_kwargs or {}))
+                reward_funcs[i].name_or_path = rf
+            if isinstance(reward_funcs[i], nn.Module):
+                self.reward_func_names.append(os.path.basename(str(getattr(reward_funcs[i], "name_or_path", f"reward_model_{i}"))) or f"reward_model_{i}")
+            else:
+                self.reward_func_names.append(getattr(reward_funcs[i], "__name__", type(reward_funcs[i]).__name__))
+        self.reward_funcs = reward_funcs
+        if args.reward_weights is not None:
+            if len(args.reward_weights) != len(reward_funcs):
+                raise ValueError(f"Number of reward weights ({len(args.reward_weights)}) must match number of reward "
+                                 f"functions ({len(reward_funcs)})")
+            self.reward_weights = torch.tensor(args.reward_weights, dtype=torch.float32)
+        else:
+            self.reward_weights = torch.ones(len(reward_funcs), dtype=torch.float32)
+        if reward_processing_classes is None:
+            reward_processing_classes = [None] * len(reward_funcs)
+        elif not isinstance(reward_processing_classes, list):
+            reward_processing_classes = [reward_processing_classes]
+        if len(reward_processing_classes) != len(reward_funcs):
+            raise ValueError("The number of reward processing classes must match the number of reward functions.")
+        for i, rf in enumerate(reward_funcs):
+            if isinstance(rf, nn.Module) and reward_processing_classes[i] is None:
+                reward_processing_classes[i] = tok
+        self.reward_processing_classes = reward_processing_classes
+        # ---- generation settings -------------------------------------------------------------------
+        self.tools, self.rollout_func, self.environment_factory = tools or [], rollout_func, environment_factory
+        self.max_completion_length = args.max_completion_length
+        self.num_generations = args.num_generations
+        self.num_generations_eval = args.num_generations_eval or args.num_generations
+        self.temperature, self.top_p, self.top_k, self.min_p = args.temperature, args.top_p, args.top_k, args.min_p
+        self.repetition_penalty = args.repetition_penalty
+        self.chat_template_kwargs = args.chat_template_kwargs or {}
+        self.num_iterations, self.beta = args.num_iterations, args.beta
+        self.epsilon_low = args.epsilon
+        self.epsilon_high = args.epsilon_high if args.epsilon_high is not None else args.epsilon
+        self.mask_truncated_completions = args.mask_truncated_completions
+        self.shuffle_dataset = args.shuffle_dataset
+        self.use_vllm = args.use_vllm
+        self._step = 0
+        self._buffered_inputs = None
+        self._last_loaded_step = -1
+        self.num_completions_to_print = args.num_completions_to_print
+        self.log_completions = args.log_completions
+        self._logs = {"prompt": deque(), "completion": deque(), "rewards": defaultdict(deque), "advantages": deque(),
+                      "extra": defaultdict(deque)}
+        self._total_train_tokens = 0
+        if args.disable_dropout:
+            disable_dropout_in_model(model)
+        super().__init__(model=model, args=args, data_collator=_identity, train_dataset=train_dataset,
+                         eval_dataset=eval_dataset, processing_class=tok, callbacks=callbacks)
+        self.model_accepts_loss_kwargs = False
+        self.compute_loss_func = "non-None: the trainer divides by the accumulation steps itself"
+        # ---- reference policy ---------------------------------------------------------------------------
+        self.ref_model = None
+        self._ref_is_adapter_off = False
+        if self.beta != 0.0 or getattr(args, "_needs_ref", False):
+            if getattr(self.model, "peft_config", None) is not None:
+                self._ref_is_adapter_off = True
+            else:
+                self.ref_model = copy.deepcopy(self.model).eval().requires_grad_(False)
+        for i, rf in enumerate(self.reward_funcs):
+            if isinstance(rf, nn.Module):
+                self.reward_funcs[i] = rf.to(self.args.device).eval().requires_grad_(False)
+        if args.sync_ref_model and self.ref_model is not None:
+            from .callbacks import SyncRefModelCallback
+
+            self.add_callback(SyncRefModelCallback(ref_model=self.ref_model))
+        self._rollout = None
+
+    # ---- sampling schedule --------------------------------------------------------------------------------
+    def _get_train_sampler(self, dataset=None):
+        ds = dataset if dataset is not None else self.train_dataset
+        a = self.args
+        return RepeatSampler(ds, mini_repeat_count=self.num_generations,
+                             batch_size=a.generation_batch_size // self.num_generations,
+                             repeat_count=self.num_iterations * a.steps_per_generation, shuffle=self.shuffle_dataset,
+                             seed=a.seed)
+
+    def _get_eval_sampler(self, dataset):
+        return RepeatSampler(dataset, mini_repeat_count=self.num_generations_eval, seed=self.args.seed, shuffle=False)
+
+    def get_train_dataloader(self):
+        self._train_batch_size = self.args.per_device_train_batch_size * self.args.steps_per_generation
+        return super().get_train_dataloader()
+
+    def _count_items(self, batches):
+        return None
+
+    def _prepare_inputs(self, generation_batch):
+        """Generate once per ``steps_per_generation * num_iterations`` calls; serve slices in between."""
+        mode = "train" if self.model.training else "eval"
+        if mode == "train":
+            a = self.args
+            generate_every = a.steps_per_generation * self.num_iterations
+            if self._step % generate_every == 0 or self._buffered_inputs is None:
+                batch = self._generate_and_score_completions(generation_batch)
+                batch = shuffle_sequence_dict(batch)
+                self._buffered_inputs = split_tensor_dict(batch, a.steps_per_generation)
+            inputs = self._buffered_inputs[self._step % a.steps_per_generation]
+        else:
+            inputs = self._generate_and_score_completions(generation_batch)
+        return inputs
+
+    def training_step(self, model, inputs, num_items_in_batch=None):
+        import time
+
+        t0 = time.perf_counter()
+        out = super().training_step(model, inputs, num_items_in_batch)
+        self._step += 1
+        self._metrics["train"]["step_time"].append(time.perf_counter() - t0)
+        return out
+
+    # ---- generation ---------------------------------------------------------------------------------------------
+    def _sampling_params(self, n: int = 1) -> SamplingParams:
+        a = self.args
+        return SamplingParams(n=n, temperature=self.temperature, top_p=self.top_p, top_k=self.top_k or 0,
+                              min_p=self.min_p or 0.0, repetition_penalty=self.repetition_penalty,
+                              max_tokens=self.max_completion_length, eos_token_id=self.eos_token_id,
+                              eos_prob_floor=a.eos_prob_floor, seed=a.seed + 7919 * self.state.global_step + D.rank(),
+                              **(a.generation_kwargs or {}))
+
+    def _get_rollout(self):
+        if self._rollout is None:
+            if self.args.device.type == "cuda":
+                from ..rollout.engine import RolloutEngine
+
+                a = self.args
+                max_len = a.vllm_max_model_length or (self._max_prompt_len_seen + self.max_completion_length + 8)
+                bs = a.rollout_block_size
+                max_len = (max_len + bs - 1) // bs * bs
+                self._rollout = RolloutEngine(self.model, max_num_seqs=a.per_device_train_batch_size * a.steps_per_generation,
+                                              max_model_len=max_len, block_size=bs, poll_every=a.rollout_poll_every)
+            else:
+                from ..rollout.engine import EagerGenerator
+
+                self._rollout = EagerGenerator(self.model)
+        return self._rollout
+
+    def _tokenize_prompts(self, prompts: list):
+        tok = self.processing_class
+        if prompts and is_conversational({"prompt": prompts[0]}):
+            ids = [tok.apply_chat_template(p, tools=self.tools or None, add_generation_prompt=True, tokenize=True,
+                                           return_dict=True, **self.chat_template_kwargs)["input_ids"] for p in prompts]
+            ids = [i[0] if i and isinstance(i[0], list) else i for i in ids]
+        else:
+            ids = tok(text=list(prompts), add_special_tokens=False)["input_ids"] if not getattr(
+                tok, "add_bos_token", False) else tok(text=list(prompts))["input_ids"]
+        return ids
+
+    def _generate(self, prompts: list):
+        """Returns (prompt_ids, completion_ids, sampling logprobs | None, extras)."""
+        extras = {}
+        if self.rollout_func is not None:
+            out = self.rollout_func(prompts, self)
+            for k in ("prompt_ids", "completion_ids", "logprobs"):
+                if k not in out:
+                    raise ValueError(f"rollout_func must return {k!r}")
+            extras = {k: v for k, v in out.items() if k not in ("prompt_ids", "completion_ids", "logprobs")}
+            return out["prompt_ids"], out["completion_ids"], out["logprobs"], extras
+        prompt_ids = self._tokenize_prompts(prompts)
+        self._max_prompt_len_seen = max([len(p) for p in prompt_ids] + [getattr(self, "_max_prompt_len_seen", 0)])
+        # identical consecutive prompts (the num_generations copies) are sent once with n>1 so that
+        # the engine shares their prompt KV blocks
+        uniq, counts = [], []
+        for p in prompt_ids:
+            if uniq and uniq[-1] == p and counts[-1] < self.num_generations:
+                counts[-1] += 1
+            else:
+                uniq.append(p)
+                counts.append(1)
+        eng = self._get_rollout()
+        with self._profile("rollout.generate"):
+            if len(set(counts)) == 1:
+                outs = eng.generate(uniq, self._sampling_params(counts[0]))
+            else:
+                outs = []
+                for p, c in zip(uniq, counts):
+                    outs.extend(eng.generate([p], self._sampling_params(c)))
+        completion_ids = [o.token_ids for o in outs]
+        logprobs = [o.logprobs for o in outs]
+        return prompt_ids, completion_ids, logprobs, extras
+
+    def _profile(self, name):
+        from ..extras.profiling import profiling_context
+
+        return profiling_context(self, name)
+
+    # ---- rewards ---------------------------------------------------------------------------------------------------
+    def _calculate_rewards(self, inputs, prompts, completions, completion_ids_list):
+        dev = self.args.device
+        rewards = torch.zeros(len(prompts), len(self.reward_funcs), device=dev)
+        keys = [k for k in inputs[0] if k not in ("prompt", "completion", "completion_ids")]
+        kwargs = {k: [ex[k] for ex in inputs] for k in keys}
+        kwargs["trainer_state"] = self.state
+        extra_cols, extra_metrics = defaultdict(list), defaultdict(list)
+        kwargs["log_extra"] = lambda name, values: extra_cols[name].extend(values)
+        kwargs["log_metric"] = lambda name, value: extra_metrics[name].append(float(value))
+        for i, (rf, rpc, name) in enumerate(zip(self.reward_funcs, self.reward_processing_classes, self.reward_func_names)):
+            with self._profile(name):
+                if isinstance(rf, nn.Module):
+                    if is_conversational(inputs[0]):
+                        texts = [apply_chat_template({"messages": p + c}, rpc)["text"] for p, c in zip(prompts, completions)]
+                    else:
+                        texts = [p + c for p, c in zip(prompts, completions)]
+                    enc = rpc(text=texts, return_tensors="pt", padding=True, padding_side="right", add_special_tokens=False)
+                    with torch.inference_mode():
+                        out = rf(input_ids=enc["input_ids"].to(dev), attention_mask=enc["attention_mask"].to(dev))
+                    rewards[:, i] = out.logits[:, 0].float()
+                else:
+                    sig_kwargs = dict(prompts=prompts, completions=completions, completion_ids=completion_ids_list, **kwargs)
+                    try:
+                        params = inspect.signature(rf).parameters
+                        if not any(p.kind == p.VAR_KEYWORD for p in params.values()):
+                            sig_kwargs = {k: v for k, v in sig_kwargs.items() if k in params}
+                    except (TypeError, ValueError):
+                        pass
+                    res = rf(**sig_kwargs)
+                    if asyncio.iscoroutine(res):
+                        res = run_coroutine_sync(res)
+                    res = [r if r is not None else float("nan") for r in res]
+                    rewards[:, i] = torch.tensor(res, dtype=torch.float32, device=dev)
+        if torch.isnan(rewards).all(dim=1).any():
+            idx = int(torch.isnan(rewards).all(dim=1).nonzero()[0])
+            warnings.warn(f"All reward functions returned None for prompt={prompts[idx]!r}; it carries no signal.")
+        self._extra_cols, self._extra_metrics = extra_cols, extra_metrics
+        return D.gather(rewards)
+
+    # ---- log-probabilities --------------------------------------------------------------------------------------------
+    def _get_per_token_logps_and_entropies(self, model, prompt_ids, completion_ids, batch_size=None,
+                                           compute_entropy=False, temperature=None):
+        """prompt_ids / completion_ids: lists of id lists.  Returns padded [B, Tc] log-probs (and entropies)."""
+        temperature = self.temperature if temperature is None else temperature
+        dev = self.args.device
+        B = len(prompt_ids)
+        Tc = max(1, max(len(c) for c in completion_ids))
+        bs = batch_size or B
+        logps = torch.zeros(B, Tc, dtype=torch.float32, device=dev)
+        ents = torch.zeros(B, Tc, dtype=torch.float32, device=dev) if compute_entropy else None
+        aux_total = None
+        for s in range(0, B, bs):
+            seqs = [list(p) + list(c) for p, c in zip(prompt_ids[s:s + bs], completion_ids[s:s + bs])]
+            lens = [len(x) for x in seqs]
+            flat = torch.tensor([t for x in seqs for t in x], dtype=torch.long, device=dev)
+            ctx = SeqCtx.from_lengths(lens, dev)
+            hidden = model.forward_hidden(flat, ctx)
+            # rows that predict completion tokens: positions p-1 .. p+c-2 of every sequence
+            sel, rows, cols = [], [], []
+            off = 0
+            for j, (p, c) in enumerate(zip(prompt_ids[s:s + bs], completion_ids[s:s + bs])):
+                n = len(c)
+                sel.extend(range(off + len(p) - 1, off + len(p) - 1 + n))
+                rows.extend([s + j] * n)
+                cols.extend(range(n))
+                off += len(p) + n
+            if not sel:
+                continue
+            sel_t = torch.tensor(sel, device=dev)
+            tgt = flat[sel_t + 1]
+            lp, en = ops.lm_head_logprobs(hidden[sel_t], model.lm_head_weight, tgt, temperature,
+                                          softcap=model.config.final_logit_softcapping, compute_entropy=compute_entropy)
+            r, c_ = torch.tensor(rows, device=dev), torch.tensor(cols, device=dev)
+            logps = logps.index_put((r, c_), lp)
+            if compute_entropy:
+                ents = ents.index_put((r, c_), en)
+            if model.config.is_moe and torch.is_grad_enabled():
+                a = model.aux_loss(ctx)
+                aux_total = a if aux_total is None else aux_total + a
+        self._last_aux_loss = aux_total
+        return logps, ents
+
+    def _ref_logps(self, prompt_ids, completion_ids, batch_size):
+        with torch.no_grad():
+            if self.ref_model is not None:
+                return self._get_per_token_logps_and_entropies(self.ref_model, prompt_ids, completion_ids, batch_size)[0]
+            with use_adapter(self.model, None):
+                return self._get_per_token_logps_and_entropies(self.model, prompt_ids, completion_ids, batch_size)[0]
+
+    # ---- logging --------------------------------------------------------------------------------------------------------
+    def log(self, logs: dict, start_time: float | None = None):
+        mode = "train" if self.model.training else "eval"
+        m = self._metrics[mode]
+        for k in list(m.keys()):
+            vals = [float(v) for v in m[k]]
+            vals = [v for v in vals if v == v]  # drop NaN
+            if vals:
+                m[k] = vals
+            else:
+                del m[k]
+        super().log(logs, start_time)
+        if self.log_completions and D.is_main() and self._logs["prompt"]:
+            print_prompt_completions_sample(list(self._logs["prompt"]), list(self._logs["completion"]),
+                                            {k: list(v) for k, v in self._logs["rewards"].items()},
+                                            list(self._logs["advantages"]), self.state.global_step,
+                                            self.num_completions_to_print,
+                                            {k: list(v) for k, v in self._logs["extra"].items()})
+            try:
+                import pandas as pd
+
+                d = os.path.join(self.args.output_dir, "completions")
+                os.makedirs(d, exist_ok=True)
+                table = {"step": [self.state.global_step] * len(self._logs["prompt"]),
+                         "prompt": [str(p) for p in self._logs["prompt"]],
+                         "completion": [str(c) for c in self._logs["completion"]],
+                         **{k: list(v) for k, v in self._logs["rewards"].items()},
+                         "advantage": list(self._logs["advantages"])}
+                pd.DataFrame(table).to_parquet(os.path.join(d, f"completions_{self.state.global_step:05d}.parquet"))
+            except Exception:
+                pass
+            for v in (self._logs["prompt"], self._logs["completion"], self._logs["advantages"]):
+                v.clear()
+            self._logs["rewards"].clear()
+            self._logs["extra"].clear()
