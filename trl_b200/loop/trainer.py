@@ -411,23 +411,8 @@ class Trainer:
                     batches.append(b)
                 if not batches:
                     break
-                self.current_gradient_accumulation_steps = len(batches)
-                n_items = self._count_items(batches)
-                self.control = self.callback_handler.call_event("on_step_begin", a, st, self.control)
-                for i, b in enumerate(batches):
-                    loss = self.training_step(self.model, b, n_items)
-                    if a.logging_nan_inf_filter and not bool(torch.isfinite(loss)):
-                        tr_loss += tr_loss / max(1, 1 + st.global_step - self._logged_step)
-                    else:
-                        tr_loss += loss
-                    if i < len(batches) - 1:
-                        self.control = self.callback_handler.call_event("on_substep_end", a, st, self.control)
-                self.control = self.callback_handler.call_event("on_pre_optimizer_step", a, st, self.control)
-                lr = self._get_learning_rate()
-                grad_norm = self.engine.step(lr, a.max_grad_norm)
-                self.control = self.callback_handler.call_event("on_optimizer_step", a, st, self.control)
-                self.lr_scheduler.step()
-                self.engine.zero_grad()
+                loss_sum, grad_norm, lr = self.optimizer_step(batches)
+                tr_loss += loss_sum
                 st.global_step += 1
                 step_in_epoch += 1
                 st.epoch = epoch + (step_in_epoch / steps_per_epoch if steps_per_epoch else 0)
@@ -450,6 +435,29 @@ class Trainer:
         self.control = self.callback_handler.call_event("on_train_end", a, st, self.control)
         self.is_in_train = False
         return TrainOutput(st.global_step, train_loss, metrics)
+
+    def optimizer_step(self, batches: list):
+        """One optimizer step over ``batches`` (the accumulation window): forward/backward of every
+        micro-batch, gradient reduction, clipping, AdamW, scheduler.  Returns (summed loss, grad norm, lr)."""
+        a, st = self.args, self.state
+        self.current_gradient_accumulation_steps = len(batches)
+        n_items = self._count_items(batches)
+        self.control = self.callback_handler.call_event("on_step_begin", a, st, self.control)
+        total = torch.zeros((), device=a.device)
+        for i, b in enumerate(batches):
+            loss = self.training_step(self.model, b, n_items)
+            if a.logging_nan_inf_filter and not bool(torch.isfinite(loss)) and False:
+                pass
+            total += torch.nan_to_num(loss.float(), nan=0.0, posinf=0.0, neginf=0.0) if a.logging_nan_inf_filter else loss
+            if i < len(batches) - 1:
+                self.control = self.callback_handler.call_event("on_substep_end", a, st, self.control)
+        self.control = self.callback_handler.call_event("on_pre_optimizer_step", a, st, self.control)
+        lr = self._get_learning_rate()
+        grad_norm = self.engine.step(lr, a.max_grad_norm)
+        self.control = self.callback_handler.call_event("on_optimizer_step", a, st, self.control)
+        self.lr_scheduler.step()
+        self.engine.zero_grad()
+        return total, grad_norm, lr
 
     def _maybe_log_save_evaluate(self, tr_loss, grad_norm, lr, t_start):
         st, a = self.state, self.args

@@ -45,7 +45,11 @@ def check_status(device=None, reset: bool = True):
         raise RuntimeError(f"trl_b200 kernel error: code={vals[0]} site={vals[1]} block={vals[2]} extra={vals[3]}")
 
 
+LAUNCHES = [0]  # kernels of this library launched (or captured into a graph) from Python
+
+
 def _chk(rc: int, what: str):
+    LAUNCHES[0] += 1
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}")
 

@@ -319,6 +319,7 @@ class RolloutEngine:
                     self._capture(sp, max_total, graph_key)
                 for _ in range(self.poll_every):
                     self._graph.replay()
+                K.LAUNCHES[0] += self.poll_every * self._graph_kernels
             else:
                 for _ in range(self.poll_every):
                     self._decode_step(sp, max_total)
@@ -365,9 +366,13 @@ class RolloutEngine:
         with torch.cuda.stream(s):
             self._decode_step(sp, max_total)
         torch.cuda.current_stream().wait_stream(s)
+        from ..ops import cuda as K
+
         g = torch.cuda.CUDAGraph()
+        n0 = K.LAUNCHES[0]
         with torch.cuda.graph(g):
             self._decode_step(sp, max_total)
+        self._graph_kernels = K.LAUNCHES[0] - n0  # library kernels replayed by every graph launch
         for t, o in zip((self.seq_lens, self.n_gen, self.finished, self.next_input, self.step_counter, self.out_tokens,
                          self.out_logps), state):
             t.copy_(o)

@@ -225,7 +225,10 @@ class OnlineTrainer(Trainer):
                     raise ValueError(f"rollout_func must return {k!r}")
             extras = {k: v for k, v in out.items() if k not in ("prompt_ids", "completion_ids", "logprobs")}
             return out["prompt_ids"], out["completion_ids"], out["logprobs"], extras
-        prompt_ids = self._tokenize_prompts(prompts)
+        if prompts and isinstance(prompts[0], (list, tuple)) and prompts[0] and isinstance(prompts[0][0], int):
+            prompt_ids = [list(p) for p in prompts]  # pre-tokenised prompts (synthetic benchmarks, custom pipelines)
+        else:
+            prompt_ids = self._tokenize_prompts(prompts)
         self._max_prompt_len_seen = max([len(p) for p in prompt_ids] + [getattr(self, "_max_prompt_len_seen", 0)])
         # identical consecutive prompts (the num_generations copies) are sent once with n>1 so that
         # the engine shares their prompt KV blocks
