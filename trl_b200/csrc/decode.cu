@@ -438,3 +438,69 @@ TRLB_API int trlb_advance(const int* tok, const float* logp, const int* slot_ids
                                                   out_logps, max_new, eos_id, max_total_len, next_input, step_counter, bump_len);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free entry point (declared and documented in trlb_no_alloc.h).
+//
+// For callers that cannot allocate while they launch: a serving loop with a fixed memory budget and
+// no allocator, code running where an allocation would synchronise or fail, C programs that link this
+// library without PyTorch.  The per-split partials live in the two file-scope arrays below instead of
+// in caller-provided buffers.  Every GPU that loads the library carries them (4 MiB + 64 KiB).
+// ------------------------------------------------------------------------------------------------
+#include <cstdio>
+
+#include "trlb_no_alloc.h"
+
+namespace {
+constexpr int kNoAllocD = 128;
+static __device__ __align__(256) float g_noalloc_part_o[(size_t)TRLB_NOALLOC_MAX_PARTS * kNoAllocD];
+static __device__ __align__(256) float g_noalloc_part_ml[(size_t)TRLB_NOALLOC_MAX_PARTS * 2];
+
+constexpr int kMaxDevices = 64;
+// Host-side cache of the arrays' device addresses, one pair per device.  In host code the array names
+// above are only stand-ins; the address a kernel may use comes from cudaGetSymbolAddress.
+float* g_part_o_addr[kMaxDevices] = {nullptr};
+float* g_part_ml_addr[kMaxDevices] = {nullptr};
+}  // namespace
+
+TRLB_API int trlb_paged_decode_attn_noalloc(const void* q, const void* kc, const void* vc, const int* seq_lens,
+                                            const int* slot_ids, const int* block_table, int max_blocks,
+                                            int block_size, int B, int Hq, int Hk, int D, float scale, int splits,
+                                            void* out, cudaStream_t st) {
+  if (B == 0) return 0;
+  if (D != kNoAllocD || Hk <= 0 || Hq % Hk != 0 || Hq / Hk > MAX_G || splits < 1) {
+    fprintf(stderr, "trlb_paged_decode_attn_noalloc: unsupported shape (D=%d must be 128, Hq=%d, Hk=%d, splits=%d)\n", D,
+            Hq, Hk, splits);
+    return TRLB_NOALLOC_ERR_BAD_SHAPE;
+  }
+  const long long parts = (long long)B * Hq * splits;
+  if (parts > TRLB_NOALLOC_MAX_PARTS) {
+    fprintf(stderr,
+            "trlb_paged_decode_attn_noalloc: B*Hq*splits = %lld exceeds the built-in scratch (%d); use fewer splits, "
+            "a smaller batch, or trlb_paged_decode_attn with your own scratch\n",
+            parts, TRLB_NOALLOC_MAX_PARTS);
+    return TRLB_NOALLOC_ERR_TOO_LARGE;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return TRLB_NOALLOC_ERR_SYMBOL;
+  if (g_part_o_addr[dev] == nullptr) {
+    // first call on this device: resolve the device addresses (do this before any stream capture)
+    float *po = nullptr, *pml = nullptr;
+    if (cudaGetSymbolAddress((void**)&po, g_noalloc_part_o) != cudaSuccess ||
+        cudaGetSymbolAddress((void**)&pml, g_noalloc_part_ml) != cudaSuccess || po == nullptr || pml == nullptr) {
+      fprintf(stderr, "trlb_paged_decode_attn_noalloc: cudaGetSymbolAddress failed on device %d\n", dev);
+      return TRLB_NOALLOC_ERR_SYMBOL;
+    }
+    g_part_ml_addr[dev] = pml;
+    g_part_o_addr[dev] = po;
+  }
+  float* part_o = g_part_o_addr[dev];
+  float* part_ml = g_part_ml_addr[dev];
+  dim3 grid(B, Hk, splits);
+  paged_decode_attn_kernel<128><<<grid, DEC_THREADS, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc,
+                                                              (const __nv_bfloat16*)vc, seq_lens, slot_ids, block_table,
+                                                              max_blocks, block_size, Hq, Hk, scale, splits, part_o,
+                                                              part_ml);
+  paged_attn_combine_kernel<128><<<B * Hq, 128, 0, st>>>(part_o, part_ml, splits, (__nv_bfloat16*)out, B * Hq);
+  return (int)cudaGetLastError();
+}
