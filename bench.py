@@ -254,6 +254,11 @@ def main():
         }
         if e2e is not None:
             line["e2e"] = e2e
+            hist = [h for h in trainer.state.log_history if any(k.startswith("profiling/") for k in h)]
+            if hist:
+                keys = sorted({k for h in hist for k in h if k.startswith("profiling/") or k == "step_time"})
+                line["phases_s"] = {k.replace("profiling/Time taken: GRPOTrainer.", ""): round(
+                    sum(h.get(k, 0.0) for h in hist[-a.steps:]) / max(1, len(hist[-a.steps:])), 3) for k in keys}
         print(json.dumps(line))
     D.barrier()
     return 0

@@ -82,3 +82,19 @@ def test_adamw_flat_matches_reference(gdtype):
     assert torch.allclose(shadow.float(), pr, atol=1e-2, rtol=1e-2)
     ss = K.sumsq(grad)
     assert torch.allclose(ss[0], grad.float().pow(2).sum(), rtol=1e-3)
+
+
+@pytest.mark.parametrize("T,H", [(64, 3584), (5, 8192), (1000, 2048)])
+def test_add_rmsnorm_infer(T, H):
+    from trl_b200.ops import cuda as K
+    from trl_b200.oracle import ops as ref
+
+    torch.manual_seed(0)
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    d = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).to(torch.bfloat16)
+    res = x.clone()
+    y = K.add_rmsnorm_infer(res, d, w, 1e-6)
+    s = (x + d)
+    assert torch.equal(res, s)
+    assert torch.allclose(y.float(), ref.rms_norm(s, w, 1e-6).float(), atol=3e-2, rtol=2e-2)

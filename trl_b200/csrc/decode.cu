@@ -8,6 +8,7 @@
 //
 // They stand where the reference uses vLLM's CUDA kernels (trl/generation/vllm_generation.py:351-368,680).
 #include "common.cuh"
+#include "decode_attn.cuh"
 
 namespace trlb {
 
@@ -69,170 +70,6 @@ __global__ void kv_write_prefill_kernel(const __nv_bfloat16* __restrict__ k, con
     reinterpret_cast<uint4*>(kc + row)[e] = reinterpret_cast<const uint4*>(k + (size_t)t * k_stride)[e];
     reinterpret_cast<uint4*>(vc + row)[e] = reinterpret_cast<const uint4*>(v + (size_t)t * v_stride)[e];
   }
-}
-
-// ------------------------------------------------------------------------------------------
-// Split-KV decode attention.  grid = (B, Hk, splits), 128 threads.  G = Hq/Hk query heads share a
-// kv head.  Partials (m, l, o) go to scratch; paged_attn_combine_kernel merges the splits.
-// ------------------------------------------------------------------------------------------
-constexpr int DEC_THREADS = 128;
-constexpr int DEC_CHUNK = 128;
-constexpr int MAX_G = 8;
-
-template <int D>
-__global__ void __launch_bounds__(DEC_THREADS)
-paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q,  // [B, Hq, D]
-                         const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
-                         const int* __restrict__ seq_lens, const int* __restrict__ slot_ids,
-                         const int* __restrict__ block_table, int max_blocks, int block_size, int Hq, int Hk,
-                         float scale, int splits, float* __restrict__ part_o,  // [B, Hq, splits, D]
-                         float* __restrict__ part_ml) {                       // [B, Hq, splits, 2]
-  const int b = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
-  const int G = Hq / Hk;
-  const int slot = slot_ids ? slot_ids[b] : b;
-  const int len = seq_lens[slot] + 1;  // the new token was appended before attention
-  const int tid = threadIdx.x;
-  __shared__ float q_s[MAX_G][D];
-  __shared__ float p_s[MAX_G][DEC_CHUNK];
-  __shared__ float red[MAX_G][4];
-  __shared__ float o_half[MAX_G][D];
-
-  const int per_split = ((len + splits - 1) / splits + DEC_CHUNK - 1) / DEC_CHUNK * DEC_CHUNK;
-  const int t_begin = sp * per_split, t_end = min(len, t_begin + per_split);
-
-  for (int i = tid; i < G * D; i += DEC_THREADS) {
-    const int g = i / D, d = i % D;
-    q_s[g][d] = __bfloat162float(q[((size_t)b * Hq + kvh * G + g) * D + d]) * scale;
-  }
-  float m_run[MAX_G], l_run[MAX_G], o_acc[MAX_G][2];
-#pragma unroll
-  for (int g = 0; g < MAX_G; ++g) { m_run[g] = -INFINITY; l_run[g] = 0.f; o_acc[g][0] = o_acc[g][1] = 0.f; }
-  __syncthreads();
-  const int* bt = block_table + (size_t)slot * max_blocks;
-  const int dp = tid & 63, half_id = tid >> 6;  // PV mapping: dim pair, token parity
-
-  for (int t0 = t_begin; t0 < t_end; t0 += DEC_CHUNK) {
-    // ---- scores: thread = token ----
-    const int tok = t0 + tid;
-    float s[MAX_G];
-#pragma unroll
-    for (int g = 0; g < MAX_G; ++g) s[g] = -INFINITY;
-    if (tok < t_end) {
-      const int blk = bt[tok / block_size];
-      const uint4* kr = reinterpret_cast<const uint4*>(kc + (((size_t)blk * block_size + tok % block_size) * Hk + kvh) * D);
-#pragma unroll
-      for (int g = 0; g < MAX_G; ++g) s[g] = 0.f;
-#pragma unroll
-      for (int i = 0; i < D / 8; ++i) {
-        const uint4 kv4 = kr[i];
-        const uint32_t* ku = reinterpret_cast<const uint32_t*>(&kv4);
-        float kf[8];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16(ku[j]); kf[2 * j] = f.x; kf[2 * j + 1] = f.y; }
-#pragma unroll
-        for (int g = 0; g < MAX_G; ++g) {
-          if (g < G) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) s[g] = fmaf(q_s[g][i * 8 + j], kf[j], s[g]);
-          }
-        }
-      }
-    }
-    // ---- chunk max per head ----
-    const int lane = tid & 31, wid = tid >> 5;
-#pragma unroll
-    for (int g = 0; g < MAX_G; ++g) {
-      if (g < G) {
-        const float mx = warp_max(s[g]);
-        if (lane == 0) red[g][wid] = mx;
-      }
-    }
-    __syncthreads();
-    float corr[MAX_G];
-#pragma unroll
-    for (int g = 0; g < MAX_G; ++g) {
-      if (g < G) {
-        const float cm = fmaxf(fmaxf(red[g][0], red[g][1]), fmaxf(red[g][2], red[g][3]));
-        const float mn = fmaxf(m_run[g], cm);
-        corr[g] = __expf(m_run[g] - mn);
-        m_run[g] = mn;
-        const float p = (tok < t_end) ? __expf(s[g] - mn) : 0.f;
-        p_s[g][tid] = p;
-        l_run[g] = l_run[g] * corr[g];  // per-thread partial of l: own token's p added below
-        l_run[g] += p;
-        o_acc[g][0] *= corr[g];
-        o_acc[g][1] *= corr[g];
-      }
-    }
-    __syncthreads();
-    // ---- PV: thread = (dim pair, token parity) ----
-    const int nt = min(DEC_CHUNK, t_end - t0);
-    for (int j = half_id; j < nt; j += 2) {
-      const int tk = t0 + j;
-      const int blk = bt[tk / block_size];
-      const uint32_t vv = *reinterpret_cast<const uint32_t*>(
-          vc + (((size_t)blk * block_size + tk % block_size) * Hk + kvh) * D + dp * 2);
-      const float2 vf = unpack_bf16(vv);
-#pragma unroll
-      for (int g = 0; g < MAX_G; ++g) {
-        if (g < G) {
-          const float p = p_s[g][j];
-          o_acc[g][0] = fmaf(p, vf.x, o_acc[g][0]);
-          o_acc[g][1] = fmaf(p, vf.y, o_acc[g][1]);
-        }
-      }
-    }
-    __syncthreads();
-  }
-  // ---- reduce l over threads, o over the two token-parity halves ----
-  const int lane = tid & 31, wid = tid >> 5;
-#pragma unroll
-  for (int g = 0; g < MAX_G; ++g) {
-    if (g < G) {
-      // every thread scaled its partial l by the same corr sequence, so a plain sum is exact
-      const float ls = warp_sum(l_run[g]);
-      if (lane == 0) red[g][wid] = ls;
-    }
-  }
-  if (half_id == 1) {
-#pragma unroll
-    for (int g = 0; g < MAX_G; ++g)
-      if (g < G) { o_half[g][dp * 2] = o_acc[g][0]; o_half[g][dp * 2 + 1] = o_acc[g][1]; }
-  }
-  __syncthreads();
-  if (half_id == 0) {
-#pragma unroll
-    for (int g = 0; g < MAX_G; ++g) {
-      if (g < G) {
-        const size_t base = (((size_t)b * Hq + kvh * G + g) * splits + sp);
-        float* po = part_o + base * D;
-        po[dp * 2] = o_acc[g][0] + o_half[g][dp * 2];
-        po[dp * 2 + 1] = o_acc[g][1] + o_half[g][dp * 2 + 1];
-        if (dp == 0) {
-          part_ml[base * 2] = m_run[g];
-          part_ml[base * 2 + 1] = red[g][0] + red[g][1] + red[g][2] + red[g][3];
-        }
-      }
-    }
-  }
-}
-
-template <int D>
-__global__ void paged_attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits,
-                                          __nv_bfloat16* __restrict__ out, int total_heads) {
-  const int h = blockIdx.x;  // b * Hq + head
-  if (h >= total_heads) return;
-  const int d = threadIdx.x;
-  float m = -INFINITY;
-  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[((size_t)h * splits + s) * 2]);
-  float l = 0.f, o = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float ms = part_ml[((size_t)h * splits + s) * 2];
-    const float w = (ms == -INFINITY) ? 0.f : __expf(ms - m);
-    l += part_ml[((size_t)h * splits + s) * 2 + 1] * w;
-    o += part_o[((size_t)h * splits + s) * D + d] * w;
-  }
-  out[(size_t)h * D + d] = __float2bfloat16(l > 0.f ? o / l : 0.f);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -363,7 +200,12 @@ __global__ void advance_kernel(const int* __restrict__ tok, const float* __restr
   n_gen[slot] = g + 1;
   seq_lens[slot] += bump_len;  // decode: the token whose K/V was just written now counts
   next_input[b] = t;
-  if (t == eos_id || g + 1 >= max_new || seq_lens[slot] + 1 >= max_total_len) finished[slot] = 1;
+  if (t == eos_id || g + 1 >= max_new || seq_lens[slot] + 1 >= max_total_len) {
+    finished[slot] = 1;
+    // a finished slot stops costing KV traffic at once: negative length = inactive for the
+    // RoPE/KV-append and attention kernels (the host reads n_gen and the output rows, not seq_lens)
+    seq_lens[slot] = -1;
+  }
 }
 
 }  // namespace trlb

@@ -64,6 +64,128 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* _
   }
 }
 
+// Residual add fused with RMSNorm (inference): res += delta (in place), y = rmsnorm(res) * w.
+template <int VEC_PER_LANE>
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(__nv_bfloat16* __restrict__ res,
+                                                         const __nv_bfloat16* __restrict__ delta,
+                                                         const __nv_bfloat16* __restrict__ w,
+                                                         __nv_bfloat16* __restrict__ y, int T, int H, float eps) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int nvec = H >> 3;
+  for (int row = warp; row < T; row += nwarps) {
+    uint4* xr = reinterpret_cast<uint4*>(res + (size_t)row * H);
+    const uint4* dr = reinterpret_cast<const uint4*>(delta + (size_t)row * H);
+    float buf[VEC_PER_LANE][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC_PER_LANE; ++i) {
+      const int v = lane + i * 32;
+      if (v < nvec) {
+        const uint4 a = xr[v], d = dr[v];
+        const uint32_t* au = reinterpret_cast<const uint32_t*>(&a);
+        const uint32_t* du = reinterpret_cast<const uint32_t*>(&d);
+        uint4 o;
+        uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16(au[j]), g = unpack_bf16(du[j]);
+          ou[j] = pack_bf16(f.x + g.x, f.y + g.y);
+          const float2 r = unpack_bf16(ou[j]);  // norm of the value as stored (bf16), like the unfused path
+          buf[i][2 * j] = r.x; buf[i][2 * j + 1] = r.y;
+          ss += r.x * r.x + r.y * r.y;
+        }
+        xr[v] = o;
+      }
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)H + eps);
+    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * H);
+    const uint4* wr = reinterpret_cast<const uint4*>(w);
+#pragma unroll
+    for (int i = 0; i < VEC_PER_LANE; ++i) {
+      const int v = lane + i * 32;
+      if (v < nvec) {
+        const uint4 wv = wr[v];
+        const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wv);
+        uint4 o;
+        uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 g = unpack_bf16(wu[j]);
+          ou[j] = pack_bf16(buf[i][2 * j] * rstd * g.x, buf[i][2 * j + 1] * rstd * g.y);
+        }
+        yr[v] = o;
+      }
+    }
+  }
+}
+
+// Same op for few rows (decode batches): one CTA per row, so 64 rows still occupy 64 SMs with 8
+// warps each instead of 8 CTAs.  delta may be null (plain RMSNorm).  H <= 256 * 8 * VPT.
+template <int VPT>
+__global__ void __launch_bounds__(256) add_rmsnorm_row_kernel(__nv_bfloat16* __restrict__ res,
+                                                             const __nv_bfloat16* __restrict__ delta,
+                                                             const __nv_bfloat16* __restrict__ w,
+                                                             __nv_bfloat16* __restrict__ y, int H, float eps) {
+  __shared__ float red[8];
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int nvec = H >> 3;
+  uint4* xr = reinterpret_cast<uint4*>(res + (size_t)row * H);
+  float buf[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * 256;
+    if (v < nvec) {
+      uint4 a = xr[v];
+      uint32_t* au = reinterpret_cast<uint32_t*>(&a);
+      if (delta != nullptr) {
+        const uint4 d = reinterpret_cast<const uint4*>(delta + (size_t)row * H)[v];
+        const uint32_t* du = reinterpret_cast<const uint32_t*>(&d);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16(au[j]), g = unpack_bf16(du[j]);
+          au[j] = pack_bf16(f.x + g.x, f.y + g.y);
+        }
+        xr[v] = a;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 r = unpack_bf16(au[j]);
+        buf[i][2 * j] = r.x; buf[i][2 * j + 1] = r.y;
+        ss += r.x * r.x + r.y * r.y;
+      }
+    }
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) red[wid] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) tot += red[k];
+  const float rstd = rsqrtf(tot / (float)H + eps);
+  uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * H);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * 256;
+    if (v < nvec) {
+      const uint4 wv = wr[v];
+      const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wv);
+      uint4 o;
+      uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 g = unpack_bf16(wu[j]);
+        ou[j] = pack_bf16(buf[i][2 * j] * rstd * g.x, buf[i][2 * j + 1] * rstd * g.y);
+      }
+      yr[v] = o;
+    }
+  }
+}
+
 // RMSNorm backward.  dx = rstd * (w*dy - x * rstd^2 * mean(w*dy*x)).  A CTA walks its rows one at a
 // time; thread t owns the same columns for every row, so the dw partial sums stay in registers.
 // Per-CTA partials go to fp32 scratch [gridDim.x, H], reduced by rmsnorm_dw_reduce_kernel.
@@ -326,6 +448,32 @@ TRLB_API int trlb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd
   else if (vec <= 8) rmsnorm_fwd_kernel<8><<<grid, threads, 0, st>>>(X, W, Y, rstd, T, H, eps);
   else if (vec <= 16) rmsnorm_fwd_kernel<16><<<grid, threads, 0, st>>>(X, W, Y, rstd, T, H, eps);
   else rmsnorm_fwd_kernel<32><<<grid, threads, 0, st>>>(X, W, Y, rstd, T, H, eps);
+  return (int)cudaGetLastError();
+}
+
+// res[T,H] += delta[T,H] in place, y = rmsnorm(res) * w  (H <= 8192)
+TRLB_API int trlb_add_rmsnorm(void* res, const void* delta, const void* w, void* y, int T, int H, float eps,
+                              cudaStream_t st) {
+  if (T == 0) return 0;
+  if (H % 8 != 0 || H > 8192) return -1;
+  if (T <= 4 * trlb_host::sm_count() || H > 4096) {
+    auto R = (__nv_bfloat16*)res; auto Dl = (const __nv_bfloat16*)delta; auto W = (const __nv_bfloat16*)w;
+    auto Y = (__nv_bfloat16*)y;
+    const int vpt = (H / 8 + 255) / 256;
+    if (vpt <= 1) add_rmsnorm_row_kernel<1><<<T, 256, 0, st>>>(R, Dl, W, Y, H, eps);
+    else if (vpt <= 2) add_rmsnorm_row_kernel<2><<<T, 256, 0, st>>>(R, Dl, W, Y, H, eps);
+    else add_rmsnorm_row_kernel<4><<<T, 256, 0, st>>>(R, Dl, W, Y, H, eps);
+    return (int)cudaGetLastError();
+  }
+  const int threads = 256;
+  const int grid = grid_for((long long)T * 32, threads);
+  const int vec = (H / 8 + 31) / 32;
+  auto R = (__nv_bfloat16*)res; auto Dl = (const __nv_bfloat16*)delta; auto W = (const __nv_bfloat16*)w;
+  auto Y = (__nv_bfloat16*)y;
+  if (vec <= 2) add_rmsnorm_kernel<2><<<grid, threads, 0, st>>>(R, Dl, W, Y, T, H, eps);
+  else if (vec <= 4) add_rmsnorm_kernel<4><<<grid, threads, 0, st>>>(R, Dl, W, Y, T, H, eps);
+  else if (vec <= 8) add_rmsnorm_kernel<8><<<grid, threads, 0, st>>>(R, Dl, W, Y, T, H, eps);
+  else add_rmsnorm_kernel<16><<<grid, threads, 0, st>>>(R, Dl, W, Y, T, H, eps);
   return (int)cudaGetLastError();
 }
 

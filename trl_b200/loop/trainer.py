@@ -446,14 +446,15 @@ class Trainer:
         total = torch.zeros((), device=a.device)
         for i, b in enumerate(batches):
             loss = self.training_step(self.model, b, n_items)
-            if a.logging_nan_inf_filter and not bool(torch.isfinite(loss)) and False:
-                pass
             total += torch.nan_to_num(loss.float(), nan=0.0, posinf=0.0, neginf=0.0) if a.logging_nan_inf_filter else loss
             if i < len(batches) - 1:
                 self.control = self.callback_handler.call_event("on_substep_end", a, st, self.control)
         self.control = self.callback_handler.call_event("on_pre_optimizer_step", a, st, self.control)
         lr = self._get_learning_rate()
-        grad_norm = self.engine.step(lr, a.max_grad_norm)
+        from ..extras.profiling import profiling_context
+
+        with profiling_context(self, "optimizer"):
+            grad_norm = self.engine.step(lr, a.max_grad_norm)
         self.control = self.callback_handler.call_event("on_optimizer_step", a, st, self.control)
         self.lr_scheduler.step()
         self.engine.zero_grad()

@@ -380,6 +380,14 @@ def rmsnorm_infer(x, w, eps, out=None):
     return out
 
 
+def add_rmsnorm_infer(res, delta, w, eps, out=None):
+    """res += delta (in place); returns rmsnorm(res) * w."""
+    T, H = res.shape
+    out = torch.empty_like(res) if out is None else out
+    _chk(lib().trlb_add_rmsnorm(_p(res), _p(delta), _p(w), _p(out), c_int(T), c_int(H), c_float(eps), _s()), "add_rmsnorm")
+    return out
+
+
 def swiglu_infer(gu, out=None):
     T, I2 = gu.shape
     out = torch.empty(T, I2 // 2, dtype=gu.dtype, device=gu.device) if out is None else out

@@ -133,7 +133,8 @@ class RolloutEngine:
         self.tok = torch.zeros(max_num_seqs, **i32)
         self.logp = torch.zeros(max_num_seqs, dtype=torch.float32, device=self.dev)
         self.poll_every, self.use_graph = poll_every, use_cuda_graph and not cfg.is_moe
-        self.kv_splits = kv_splits or max(1, min(8, (2 * 148) // max(1, max_num_seqs * Hk)))
+        # enough CTAs for ~4 per SM: the kernel is latency-bound on KV loads, occupancy hides it
+        self.kv_splits = kv_splits or max(1, min(8, -(-(4 * 148) // max(1, max_num_seqs * Hk))))
         self.part_o = torch.empty(max_num_seqs * cfg.num_attention_heads * self.kv_splits * D, dtype=torch.float32,
                                   device=self.dev)
         self.part_ml = torch.empty(max_num_seqs * cfg.num_attention_heads * self.kv_splits * 2, dtype=torch.float32,
@@ -166,8 +167,14 @@ class RolloutEngine:
         eps = cfg.rms_norm_eps
         x = torch.nn.functional.embedding(self.next_input, m.embed_tokens)
         scale = 1.0 / math.sqrt(cfg.head_dim)
+        fuse = cfg.hidden_size <= 8192  # residual add folded into the following RMSNorm
+        pending = None  # block output not yet added to the residual stream
         for li, l in enumerate(m.layers):
-            h = K.rmsnorm_infer(x, l.input_layernorm, eps)
+            if pending is None:
+                h = K.rmsnorm_infer(x, l.input_layernorm, eps)
+            else:
+                h = K.add_rmsnorm_infer(x, pending, l.input_layernorm, eps)
+                pending = None
             qkv = torch.nn.functional.linear(h, l.qkv_proj, l.qkv_bias)
             if cfg.qk_norm:
                 qs, ks = cfg.q_size, cfg.kv_size
@@ -179,18 +186,25 @@ class RolloutEngine:
                             cfg.rope_theta)
             K.paged_decode_attn(self.q_buf, self.k_cache[li], self.v_cache[li], self.seq_lens, None, self.block_table,
                                 self.block_size, scale, self.kv_splits, self.part_o, self.part_ml, self.attn_buf)
-            x = x + torch.nn.functional.linear(self.attn_buf.view(self.max_seqs, -1), l.o_proj)
-            h = K.rmsnorm_infer(x, l.post_attention_layernorm, eps)
+            attn_out = torch.nn.functional.linear(self.attn_buf.view(self.max_seqs, -1), l.o_proj)
+            if fuse:
+                h = K.add_rmsnorm_infer(x, attn_out, l.post_attention_layernorm, eps)
+            else:
+                x = x + attn_out
+                h = K.rmsnorm_infer(x, l.post_attention_layernorm, eps)
             if cfg.is_moe:
                 from ..ops import functional as F_
 
                 y, _, _ = F_.moe_mlp(h, l.router, l.experts_gate_up, l.experts_down, cfg.num_experts_per_tok,
                                      cfg.norm_topk_prob)
-                x = x + y
             else:
                 gu = torch.nn.functional.linear(h, l.gate_up_proj)
-                x = x + torch.nn.functional.linear(K.swiglu_infer(gu), l.down_proj)
-        hN = K.rmsnorm_infer(x, m.norm, eps)
+                y = torch.nn.functional.linear(K.swiglu_infer(gu), l.down_proj)
+            if fuse:
+                pending = y
+            else:
+                x = x + y
+        hN = K.rmsnorm_infer(x, m.norm, eps) if pending is None else K.add_rmsnorm_infer(x, pending, m.norm, eps)
         logits = torch.nn.functional.linear(hN, m.lm_head_weight)
         self._sample(logits, sp)
         K.advance(self.tok, self.logp, None, self.seq_lens, self.n_gen, self.finished, self.out_tokens, self.out_logps,
@@ -265,7 +279,16 @@ class RolloutEngine:
         bt_np = self.block_table_host.numpy()
         graph_key = (sp.temperature, sp.top_p, sp.top_k, sp.min_p, sp.repetition_penalty, sp.eos_token_id,
                      sp.eos_prob_floor, sp.seed, sp.greedy, max_total, max_new)
+        # every request retires after at most max_new decode steps; a generous bound on the number of
+        # polls turns a scheduling or kernel fault into an error instead of an endless host loop
+        max_polls = (n_req // max(1, self.max_seqs) + 2) * (max_new // self.poll_every + 2) + 8
+        polls = 0
         while True:
+            polls += 1
+            if polls > max_polls:
+                K.check_status(dev)
+                raise RuntimeError(f"rollout did not finish within {max_polls} polls "
+                                   f"(running={self.sched.num_running}, waiting={self.sched.num_waiting})")
             admitted = self.sched.admit(bt_np)
             if admitted:
                 self.block_table.copy_(self.block_table_host, non_blocking=True)

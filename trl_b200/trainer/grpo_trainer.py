@@ -88,14 +88,16 @@ class GRPOTrainer(OnlineTrainer):
                 self.use_vllm and self.vllm_importance_sampling_correction and sampling_logps is not None)
             old_logps = None
             if need_old:
-                old_logps, _ = self._get_per_token_logps_and_entropies(self.model, prompt_ids, completion_ids, bs)
+                with self._profile("old_logps"):
+                    old_logps, _ = self._get_per_token_logps_and_entropies(self.model, prompt_ids, completion_ids, bs)
             if self.use_vllm and self.vllm_importance_sampling_correction and sampling_logps is not None:
                 slp = pad([torch.tensor(l, dtype=torch.float32, device=dev) for l in sampling_logps], 0.0, "right")
                 slp = torch.nn.functional.pad(slp, (0, Tc - slp.shape[1]))
                 out["sampling_per_token_logps"] = slp
                 out["importance_sampling_ratio"] = self._rollout_is_ratio(old_logps, slp, loss_mask)
             if self.beta != 0.0:
-                out["ref_per_token_logps"] = self._ref_logps(prompt_ids, completion_ids, bs)
+                with self._profile("ref_logps"):
+                    out["ref_per_token_logps"] = self._ref_logps(prompt_ids, completion_ids, bs)
             if old_logps is not None:
                 out["old_per_token_logps"] = old_logps
         # ---- rewards and advantages -------------------------------------------------------------------------------
