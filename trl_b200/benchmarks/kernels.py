@@ -1,0 +1,154 @@
+"""Kernel micro-benchmarks (CUDA-event timing, L2 flushed between iterations).
+
+    python -m trl_b200.benchmarks.kernels gemm --m 8192 --n 4608 --k 3584
+    python -m trl_b200.benchmarks.kernels lmhead --m 8192 --v 152064 --k 3584
+    python -m trl_b200.benchmarks.kernels decode_attn --batch 64 --ctx 1024
+    python -m trl_b200.benchmarks.kernels rmsnorm --t 16384 --h 3584
+    python -m trl_b200.benchmarks.kernels adamw --n 268435456
+
+Each prints one JSON line with the achieved rate and, when ``MEASURED_PEAKS.json`` sits at the
+repository root, the fraction of the measured copy bandwidth / cuBLAS bf16 throughput.  ``--iters 1
+--warmup 1`` gives a run small enough to sit under ``ncu``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+
+
+def _peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+_flush = None
+
+
+def flush_l2():
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _flush.zero_()
+
+
+def timeit(fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush_l2()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm", "lmhead", "lmhead_bwd", "decode_attn", "rmsnorm", "adamw", "grpo_loss"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=4608)
+    ap.add_argument("--k", type=int, default=3584)
+    ap.add_argument("--v", type=int, default=152064)
+    ap.add_argument("--t", type=int, default=16384)
+    ap.add_argument("--h", type=int, default=3584)
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=1024)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--baseline", action="store_true", help="also time the library (cuBLAS / eager) path")
+    a = ap.parse_args()
+    from ..ops import cuda as K
+
+    hbm, tfl, src = _peaks()
+    dev = "cuda"
+    out = {"kernel": a.kernel, "peaks": src}
+    if a.kernel == "gemm":
+        A = torch.randn(a.m, a.k, device=dev, dtype=torch.bfloat16)
+        B = torch.randn(a.n, a.k, device=dev, dtype=torch.bfloat16)
+        C = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
+        ms = timeit(lambda: K.gemm_bf16_tn(A, B, out=C), a.iters, a.warmup)
+        fl = 2.0 * a.m * a.n * a.k
+        out.update(shape=[a.m, a.n, a.k], ms=ms, tflops=fl / ms / 1e9, frac_of_cublas_peak=fl / ms / 1e9 / tfl)
+        if a.baseline:
+            ms2 = timeit(lambda: torch.matmul(A, B.t(), out=C), a.iters, a.warmup)
+            out.update(cublas_ms=ms2, cublas_tflops=fl / ms2 / 1e9)
+    elif a.kernel in ("lmhead", "lmhead_bwd"):
+        H = torch.randn(a.m, a.k, device=dev, dtype=torch.bfloat16)
+        W = (torch.randn(a.v, a.k, device=dev) * 0.02).to(torch.bfloat16)
+        y = torch.randint(0, a.v, (a.m,), device=dev)
+        fl = 2.0 * a.m * a.v * a.k
+        if a.kernel == "lmhead":
+            ms = timeit(lambda: K.lmhead_forward(H, W, y, 1.0, True, True), a.iters, a.warmup)
+        else:
+            _, _, lse, _ = K.lmhead_forward(H, W, y, 1.0, False, False)
+            g = torch.ones(a.m, device=dev)
+            dz = torch.empty(a.m, a.v, device=dev, dtype=torch.bfloat16)
+            ms = timeit(lambda: K.lmhead_dz(H, W, y, lse, g, 1.0, out=dz), a.iters, a.warmup)
+        out.update(shape=[a.m, a.v, a.k], ms=ms, tflops=fl / ms / 1e9, frac_of_cublas_peak=fl / ms / 1e9 / tfl)
+        if a.baseline and a.kernel == "lmhead":
+            def eager():
+                for hc, yc in zip(H.split(2048), y.split(2048)):
+                    lg = (hc @ W.t()).float()
+                    torch.log_softmax(lg, -1).gather(-1, yc[:, None])
+            out["eager_chunked_ms"] = timeit(eager, max(2, a.iters // 3), 1)
+    elif a.kernel == "decode_attn":
+        Hq, Hk, D, bs = 28, 4, 128, 16
+        nb = a.batch * ((a.ctx + bs) // bs + 1)
+        kc = torch.randn(nb, bs, Hk, D, device=dev, dtype=torch.bfloat16)
+        vc = torch.randn(nb, bs, Hk, D, device=dev, dtype=torch.bfloat16)
+        mb = nb // a.batch
+        table = torch.randperm(nb, device=dev).reshape(a.batch, mb).to(torch.int32)
+        q = torch.randn(a.batch, Hq, D, device=dev, dtype=torch.bfloat16)
+        lens = torch.full((a.batch,), a.ctx - 1, device=dev, dtype=torch.int32)
+        splits = max(1, min(8, -(-(4 * 148) // (a.batch * Hk))))
+        po = torch.empty(a.batch * Hq * splits * D, device=dev)
+        pml = torch.empty(a.batch * Hq * splits * 2, device=dev)
+        o = torch.empty(a.batch, Hq, D, device=dev, dtype=torch.bfloat16)
+        ms = timeit(lambda: K.paged_decode_attn(q, kc, vc, lens, None, table, bs, 1 / math.sqrt(D), splits, po, pml, o),
+                    a.iters, a.warmup)
+        byt = 2.0 * a.batch * a.ctx * Hk * D * 2
+        out.update(batch=a.batch, ctx=a.ctx, splits=splits, ms=ms, gbs=byt / ms / 1e6, frac_of_copy_bw=byt / ms / 1e6 / hbm)
+    elif a.kernel == "rmsnorm":
+        x = torch.randn(a.t, a.h, device=dev, dtype=torch.bfloat16)
+        w = torch.ones(a.h, device=dev, dtype=torch.bfloat16)
+        y = torch.empty_like(x)
+        ms = timeit(lambda: K.rmsnorm_infer(x, w, 1e-6, out=y), a.iters, a.warmup)
+        byt = 2.0 * a.t * a.h * 2
+        out.update(shape=[a.t, a.h], ms=ms, gbs=byt / ms / 1e6, frac_of_copy_bw=byt / ms / 1e6 / hbm)
+    elif a.kernel == "adamw":
+        n = a.n if a.n > 1 << 20 else 1 << 28
+        p, g = torch.randn(n, device=dev), torch.randn(n, device=dev)
+        m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        sh = torch.empty(n, device=dev, dtype=torch.bfloat16)
+        ms = timeit(lambda: K.adamw_flat(p, g, m, v, 1, 1e-4, 0.9, 0.999, 1e-8, 0.0, 1.0, sh), a.iters, a.warmup)
+        byt = n * (4 * 4 + 3 * 4 + 2.0)
+        out.update(n=n, ms=ms, gbs=byt / ms / 1e6, frac_of_copy_bw=byt / ms / 1e6 / hbm)
+    elif a.kernel == "grpo_loss":
+        B, T = a.batch, a.ctx
+        lp = -torch.rand(B, T, device=dev)
+        old, ref = lp + 0.1 * torch.randn_like(lp), lp + 0.1 * torch.randn_like(lp)
+        adv, mask = torch.randn(B, device=dev), torch.ones(B, T, device=dev)
+        rs = torch.full((B,), 1.0 / (B * T), device=dev)
+        ms = timeit(lambda: K.grpo_loss(lp, old, ref, adv, mask, rs, lp, 0.2, 0.2, 0.04, None), a.iters, a.warmup)
+        byt = B * T * 4 * 6.0
+        out.update(shape=[B, T], ms=ms, gbs=byt / ms / 1e6)
+    K.check_status()
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
