@@ -1,0 +1,35 @@
+"""Distributed equivalence on CPU (gloo): the same global batch trained with world_size 1 and 2, in
+ddp and zero2 modes, must give the same loss / grad-norm trajectory."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(world, mode, out, steps=4, port=29611):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
+    if world == 1:
+        cmd = [sys.executable, os.path.join(HERE, "dist_worker_sft.py"), out, mode, str(steps)]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+               "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "dist_worker_sft.py"), out,
+               mode, str(steps)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    with open(out) as f:
+        return json.load(f)
+
+
+@pytest.mark.parametrize("mode,port", [("ddp", 29611), ("zero2", 29612)])
+def test_sft_world1_vs_world2(tmp_path, mode, port):
+    ref = _run(1, "ddp", str(tmp_path / "w1.json"))
+    two = _run(2, mode, str(tmp_path / f"w2_{mode}.json"), port=port)
+    assert len(ref) == len(two) == 4
+    for a, b in zip(ref, two):
+        assert abs(a["loss"] - b["loss"]) < 2e-4, (ref, two)
+        assert abs(a["grad_norm"] - b["grad_norm"]) < 1e-3 * max(1.0, a["grad_norm"]), (ref, two)
+    assert ref[-1]["loss"] < ref[0]["loss"] + 0.05
