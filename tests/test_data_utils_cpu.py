@@ -1,0 +1,113 @@
+"""Dataset-format helpers, packing and collators (literal expected outputs)."""
+import pytest
+import torch
+
+from trl_b200.data_utils import (_SegmentTree, apply_chat_template, extract_prompt, is_conversational,
+                                 maybe_convert_to_chatml, maybe_extract_prompt, maybe_unpair_preference_dataset,
+                                 pack_dataset, unpair_preference_dataset, bfd_assign)
+from trl_b200.trainer.sft_trainer import DataCollatorForLanguageModeling
+
+
+def test_padding_free_collate():
+    c = DataCollatorForLanguageModeling(pad_token_id=0, padding_free=True)
+    out = c([{"input_ids": [1, 2, 3]}, {"input_ids": [4, 5]}])
+    assert out["input_ids"].tolist() == [[1, 2, 3, 4, 5]]
+    assert out["position_ids"].tolist() == [[0, 1, 2, 0, 1]]
+    assert out["labels"].tolist() == [[-100, 2, 3, -100, 5]]
+    assert "attention_mask" not in out
+
+
+def test_packed_collate_with_seq_lengths_and_pad_multiple():
+    c = DataCollatorForLanguageModeling(pad_token_id=0, padding_free=True)
+    out = c([{"input_ids": [1, 2, 3, 4, 5, 6], "seq_lengths": [3, 3]}, {"input_ids": [7, 8, 9, 10, 11], "seq_lengths": [4, 1]}])
+    assert out["position_ids"].tolist() == [[0, 1, 2, 0, 1, 2, 0, 1, 2, 3, 0]]
+    assert out["labels"].tolist() == [[-100, 2, 3, -100, 5, 6, -100, 8, 9, 10, -100]]
+    c2 = DataCollatorForLanguageModeling(pad_token_id=99, padding_free=True, pad_to_multiple_of=4)
+    o2 = c2([{"input_ids": [1, 2, 3]}, {"input_ids": [4, 5]}])
+    assert o2["input_ids"].tolist() == [[1, 2, 3, 4, 5, 99, 99, 99]]
+    assert o2["position_ids"].tolist() == [[0, 1, 2, 0, 1, 0, 0, 0]] and o2["labels"][0, 5:].tolist() == [-100] * 3
+
+
+def test_padded_collate_and_completion_mask():
+    c = DataCollatorForLanguageModeling(pad_token_id=0)
+    out = c([{"input_ids": [1, 2, 3], "completion_mask": [0, 1, 1]}, {"input_ids": [4, 5], "completion_mask": [0, 1]}])
+    assert out["input_ids"].tolist() == [[1, 2, 3], [4, 5, 0]] and out["attention_mask"].tolist() == [[1, 1, 1], [1, 1, 0]]
+    assert out["labels"].tolist() == [[-100, 2, 3], [-100, 5, -100]]
+
+
+def test_bfd_packing_literal():
+    rows = [{"input_ids": [1, 2, 3]}, {"input_ids": [4, 5, 6, 7]}, {"input_ids": [8]}]
+    out = pack_dataset(rows, 4, "bfd")
+    assert [r["input_ids"] for r in out] == [[4, 5, 6, 7], [1, 2, 3, 8]]
+    assert [r["seq_lengths"] for r in out] == [[4], [3, 1]]
+
+
+def test_bfd_truncates_and_bfd_split_requeues():
+    rows = [{"input_ids": [1, 2, 3, 4, 5]}, {"input_ids": [6, 7]}, {"input_ids": [8, 9, 10, 11]}, {"input_ids": [12]},
+            {"input_ids": []}]
+    a = pack_dataset(rows, 4, "bfd")
+    assert [r["input_ids"] for r in a] == [[1, 2, 3, 4], [8, 9, 10, 11], [6, 7, 12]]
+    assert [r["seq_lengths"] for r in a] == [[4], [4], [2, 1]]
+    b = pack_dataset(rows, 4, "bfd_split")
+    assert [r["input_ids"] for r in b] == [[1, 2, 3, 4], [8, 9, 10, 11], [6, 7, 5, 12]]
+    assert [r["seq_lengths"] for r in b] == [[4], [4], [2, 1, 1]]
+    w = pack_dataset(rows, 4, "wrapped")
+    assert [r["input_ids"] for r in w] == [[1, 2, 3, 4], [5, 6, 7, 8], [9, 10, 11, 12]]
+
+
+def test_pack_dataset_hf_dataset_and_native_matches_python():
+    from datasets import Dataset
+    import random
+
+    ds = Dataset.from_dict({"input_ids": [[1, 2, 3], [4, 5, 6, 7], [8]], "completion_mask": [[0, 1, 1], [0, 0, 1, 1], [1]]})
+    out = pack_dataset(ds, 4, "bfd")
+    assert out["input_ids"] == [[4, 5, 6, 7], [1, 2, 3, 8]] and out["completion_mask"] == [[0, 0, 1, 1], [0, 1, 1, 1]]
+    rng = random.Random(0)
+    lens = [rng.randint(1, 64) for _ in range(500)]
+    bins = bfd_assign(lens, 64)
+    assert sorted(i for b in bins for i in b) == list(range(500))
+    assert all(sum(lens[i] for i in b) <= 64 for b in bins)
+    assert len(bins) <= int(sum(lens) / 64 * 1.1) + 1
+
+
+def test_segment_tree():
+    t = _SegmentTree(10)
+    for v in (5, 2, 8):
+        t.add(v)
+    assert t.search(3) == 5 and t.search(6) == 8 and t.search(1) == 2
+    t.remove(5)
+    assert t.search(3) == 8 and t.search(9) == 0
+
+
+def test_conversational_and_chatml_conversion():
+    assert is_conversational({"prompt": [{"role": "user", "content": "hi"}]})
+    assert not is_conversational({"prompt": "hi"})
+    ex = maybe_convert_to_chatml({"conversations": [{"from": "user", "value": "a"}, {"from": "assistant", "value": "b"}]})
+    assert ex == {"messages": [{"role": "user", "content": "a"}, {"role": "assistant", "content": "b"}]}
+
+
+def test_unpair_and_extract_prompt():
+    rows = [{"prompt": "p", "chosen": "c", "rejected": "r"}]
+    un = unpair_preference_dataset(rows)
+    assert un == [{"prompt": "p", "completion": "c", "label": True}, {"prompt": "p", "completion": "r", "label": False}]
+    assert maybe_unpair_preference_dataset([{"prompt": "p", "completion": "c", "label": True}])[0]["label"] is True
+    e = extract_prompt({"chosen": "The sky is blue", "rejected": "The sky is green"})
+    assert e == {"prompt": "The sky is", "chosen": " blue", "rejected": " green"}
+    conv = {"chosen": [{"role": "user", "content": "q"}, {"role": "assistant", "content": "a"}],
+            "rejected": [{"role": "user", "content": "q"}, {"role": "assistant", "content": "b"}]}
+    m = maybe_extract_prompt(conv)
+    assert m["prompt"] == [{"role": "user", "content": "q"}] and m["chosen"] == [{"role": "assistant", "content": "a"}]
+
+
+def test_apply_chat_template_variants(tiny_tokenizer):
+    tok = tiny_tokenizer
+    p = [{"role": "user", "content": "the sky"}]
+    c = [{"role": "assistant", "content": "is good"}]
+    out = apply_chat_template({"prompt": p, "completion": c}, tok)
+    assert out["prompt"].endswith("<|im_start|>assistant\n") and out["completion"].startswith("is good<|im_end|>")
+    full = apply_chat_template({"messages": p + c}, tok)["text"]
+    assert full == out["prompt"] + out["completion"]
+    pref = apply_chat_template({"prompt": p, "chosen": c, "rejected": [{"role": "assistant", "content": "no"}]}, tok)
+    assert pref["chosen"].startswith("is good") and pref["rejected"].startswith("no")
+    with pytest.raises(KeyError):
+        apply_chat_template({"prompt": p, "messages": p}, tok)

@@ -1,0 +1,252 @@
+"""Trainer integration on CPU with tiny random-init models and synthetic datasets.  Criterion (as in the
+reference's smoke tests): ``train_loss`` is logged and every trainable parameter changed."""
+import json
+import os
+
+import pytest
+import torch
+
+from trl_b200.testing import make_dataset, make_tiny_model
+from trl_b200 import (DPOConfig, DPOTrainer, GRPOConfig, GRPOTrainer, KTOConfig, KTOTrainer, RewardConfig,
+                      RewardTrainer, RLOOConfig, RLOOTrainer, SFTConfig, SFTTrainer)
+
+COMMON = dict(per_device_train_batch_size=4, max_steps=2, logging_steps=1, learning_rate=1e-3, use_cpu=True,
+              save_strategy="no", report_to="none")
+
+
+def _changed(model, before):
+    return [n for n, p in model.named_parameters() if p.requires_grad and torch.equal(before[n], p)]
+
+
+def _snap(model):
+    return {n: p.detach().clone() for n, p in model.named_parameters()}
+
+
+@pytest.mark.parametrize("kind,extra", [
+    ("standard_language_modeling", {}),
+    ("conversational_language_modeling", {"assistant_only_loss": True}),
+    ("standard_prompt_completion", {"padding_free": True}),
+    ("conversational_prompt_completion", {"packing": True, "max_length": 64}),
+    ("standard_language_modeling", {"loss_type": "dft"}),
+    ("standard_language_modeling", {"packing": True, "packing_strategy": "wrapped", "max_length": 32}),
+])
+def test_sft_trains(tmp_path, tiny_tokenizer, kind, extra):
+    model = make_tiny_model()
+    before = _snap(model)
+    tr = SFTTrainer(model, SFTConfig(output_dir=str(tmp_path), **COMMON, **extra), train_dataset=make_dataset(kind, 24),
+                    processing_class=tiny_tokenizer)
+    tr.train()
+    assert tr.state.log_history[-1]["train_loss"] is not None
+    assert _changed(model, before) == []
+    logged = [h for h in tr.state.log_history if "entropy" in h]
+    assert logged and "num_tokens" in logged[-1]
+
+
+def test_sft_moe_aux_loss(tmp_path, tiny_tokenizer):
+    model = make_tiny_model("tiny-qwen3-moe")
+    before = _snap(model)
+    tr = SFTTrainer(model, SFTConfig(output_dir=str(tmp_path), **COMMON), train_dataset=make_dataset("standard_language_modeling", 16),
+                    processing_class=tiny_tokenizer)
+    tr.train()
+    assert _changed(model, before) == []
+    assert any("aux_loss" in h for h in tr.state.log_history)
+
+
+def test_sft_eval_and_checkpoint_resume(tmp_path, tiny_tokenizer):
+    ds = make_dataset("standard_language_modeling", 32)
+    cfg = dict(COMMON, max_steps=4, save_strategy="steps", save_steps=2, eval_strategy="steps", eval_steps=2,
+               lr_scheduler_type="constant", train_sampling_strategy="sequential")
+    m1 = make_tiny_model()
+    t1 = SFTTrainer(m1, SFTConfig(output_dir=str(tmp_path / "a"), **cfg), train_dataset=ds, eval_dataset=ds.select(range(8)),
+                    processing_class=tiny_tokenizer)
+    t1.train()
+    ck = tmp_path / "a" / "checkpoint-2"
+    for f in ("model.safetensors", "config.json", "trainer_state.json", "optimizer.pt", "scheduler.pt", "rng_state.pth"):
+        assert (ck / f).exists(), f
+    assert any("eval_loss" in h for h in t1.state.log_history)
+    state = json.load(open(ck / "trainer_state.json"))
+    assert state["global_step"] == 2
+    m2 = make_tiny_model(seed=123)  # different init: everything must come from the checkpoint
+    t2 = SFTTrainer(m2, SFTConfig(output_dir=str(tmp_path / "a"), **cfg), train_dataset=ds, eval_dataset=ds.select(range(8)),
+                    processing_class=tiny_tokenizer)
+    t2.train(resume_from_checkpoint=str(ck))
+    assert t2.state.global_step == 4
+    for (n, p), (_, q) in zip(m1.named_parameters(), m2.named_parameters()):
+        assert torch.allclose(p, q, atol=1e-6), n
+
+
+@pytest.mark.parametrize("kind,extra", [
+    ("standard_preference", {}),
+    ("conversational_implicit_prompt_preference", {"loss_type": ["sigmoid", "bco_pair", "sft"], "loss_weights": [0.8, 0.2, 1.0]}),
+    ("standard_preference", {"loss_type": "ipo", "precompute_ref_log_probs": True}),
+    ("standard_preference", {"loss_type": "aot", "use_weighting": True, "ld_alpha": 0.5}),
+    ("standard_preference", {"f_divergence_type": "js_divergence", "label_smoothing": 0.1}),
+])
+def test_dpo_trains(tmp_path, tiny_tokenizer, kind, extra):
+    model = make_tiny_model()
+    before = _snap(model)
+    tr = DPOTrainer(model, args=DPOConfig(output_dir=str(tmp_path), **COMMON, **extra), train_dataset=make_dataset(kind, 16),
+                    processing_class=tiny_tokenizer)
+    tr.train()
+    assert _changed(model, before) == []
+    h = [x for x in tr.state.log_history if "rewards/chosen" in x][-1]
+    for k in ("rewards/rejected", "rewards/accuracies", "rewards/margins", "logps/chosen", "logps/rejected", "entropy"):
+        assert k in h
+
+
+def test_dpo_first_step_loss_is_log2(tmp_path, tiny_tokenizer):
+    model = make_tiny_model()
+    tr = DPOTrainer(model, args=DPOConfig(output_dir=str(tmp_path), **dict(COMMON, max_steps=1)),
+                    train_dataset=make_dataset("standard_preference", 8), processing_class=tiny_tokenizer)
+    tr.train()
+    first = [x for x in tr.state.log_history if "loss" in x][0]["loss"]
+    assert abs(first - 0.6931) < 1e-3  # policy == reference at step 1
+
+
+def test_dpo_with_lora_uses_adapter_off_reference(tmp_path, tiny_tokenizer):
+    from trl_b200.models.lora import LoraConfig
+
+    model = make_tiny_model()
+    tr = DPOTrainer(model, args=DPOConfig(output_dir=str(tmp_path), **COMMON), train_dataset=make_dataset("standard_preference", 16),
+                    processing_class=tiny_tokenizer, peft_config=LoraConfig(r=4, target_modules=["q_proj", "v_proj"]))
+    assert tr.ref_model is None and tr._ref_adapter_off
+    tr.train()
+    tr.save_model(str(tmp_path / "out"))
+    assert (tmp_path / "out" / "adapter_model.safetensors").exists()
+
+
+def test_kto_kl_rotation_and_training(tmp_path, tiny_tokenizer):
+    model = make_tiny_model()
+    before = _snap(model)
+    tr = KTOTrainer(model, args=KTOConfig(output_dir=str(tmp_path), **COMMON), train_dataset=make_dataset("standard_unpaired_preference", 16),
+                    processing_class=tiny_tokenizer)
+    rows = [tr.train_dataset[i] for i in range(8)]
+    for s in (0, 4):  # completions rotated by one inside every per-device batch
+        comps = [r["completion_ids"] for r in rows[s:s + 4]]
+        assert [r["KL_completion_ids"] for r in rows[s:s + 4]] == [comps[-1]] + comps[:-1]
+    tr.train()
+    assert _changed(model, before) == []
+    assert any("kl" in h for h in tr.state.log_history)
+    with pytest.raises(ValueError):
+        KTOTrainer(make_tiny_model(), args=KTOConfig(output_dir=str(tmp_path), **dict(COMMON, per_device_train_batch_size=1)),
+                   train_dataset=make_dataset("standard_unpaired_preference", 8), processing_class=tiny_tokenizer)
+
+
+def test_reward_trainer(tmp_path, tiny_tokenizer):
+    model = make_tiny_model(num_labels=1)
+    before = _snap(model)
+    tr = RewardTrainer(model, args=RewardConfig(output_dir=str(tmp_path), center_rewards_coefficient=0.01, **COMMON),
+                       train_dataset=make_dataset("conversational_preference", 16), processing_class=tiny_tokenizer)
+    tr.train()
+    assert _changed(model, before) == []
+    h = [x for x in tr.state.log_history if "accuracy" in x][-1]
+    assert {"min_reward", "mean_reward", "max_reward", "margin", "num_tokens"} <= set(h)
+
+
+def _len_reward(completions, completion_ids=None, **kw):
+    if completion_ids is not None:  # works for text and conversational completions alike
+        return [float(sum(ids)) % 7 / 7 + len(ids) / 10 for ids in completion_ids]
+    return [float(len(c)) / 10 for c in completions]
+
+
+def _none_reward(completions, **kw):
+    return [None for _ in completions]
+
+
+@pytest.mark.parametrize("extra", [
+    {"loss_type": "dapo"}, {"loss_type": "grpo", "beta": 0.04}, {"loss_type": "bnpo", "num_iterations": 2},
+    {"loss_type": "dr_grpo", "scale_rewards": "batch"}, {"loss_type": "cispo"}, {"loss_type": "sapo"},
+    {"loss_type": "luspo", "importance_sampling_level": "sequence"}, {"loss_type": "vespo"},
+    {"top_entropy_quantile": 0.5}, {"entropy_coef": 0.01, "use_adaptive_entropy": True},
+    {"multi_objective_aggregation": "normalize_then_sum"}, {"mask_truncated_completions": True, "delta": 2.0},
+])
+def test_grpo_variants_train(tmp_path, tiny_tokenizer, extra):
+    model = make_tiny_model()
+    before = _snap(model)
+    args = GRPOConfig(output_dir=str(tmp_path), **dict(COMMON, learning_rate=1e-2), num_generations=4,
+                      max_completion_length=8, gradient_accumulation_steps=2, **extra)
+    rf = [_len_reward, _len_reward] if "multi_objective_aggregation" in extra else _len_reward
+    tr = GRPOTrainer(model, rf, args, train_dataset=make_dataset("standard_prompt_only", 16), processing_class=tiny_tokenizer)
+    tr.train()
+    if not extra.get("mask_truncated_completions"):
+        assert _changed(model, before) == []
+    h = [x for x in tr.state.log_history if "reward" in x][-1]
+    assert "completions/mean_length" in h and "rewards/_len_reward/mean" in h
+
+
+def test_grpo_unscorable_completions_get_zero_advantage(tmp_path, tiny_tokenizer):
+    model = make_tiny_model()
+    before = _snap(model)
+    args = GRPOConfig(output_dir=str(tmp_path), **COMMON, num_generations=4, max_completion_length=4, loss_type="grpo")
+    tr = GRPOTrainer(model, _none_reward, args, train_dataset=make_dataset("standard_prompt_only", 8), processing_class=tiny_tokenizer)
+    tr.train()
+    assert len(_changed(model, before)) == len(before)  # no signal -> no update
+
+
+def test_grpo_generation_batch_schedule(tmp_path, tiny_tokenizer):
+    """per_device_bs=6, steps_per_generation=4, num_generations=4, num_iterations=2, GA=3: one generation batch of
+    24 rows = 6 prompts x 4 serves 8 consecutive training steps; 48 training_step calls for 3 epochs over 12 prompts."""
+    ds = make_dataset("standard_prompt_only", 12)
+    args = GRPOConfig(output_dir=str(tmp_path), per_device_train_batch_size=6, steps_per_generation=4, num_generations=4,
+                      num_iterations=2, gradient_accumulation_steps=3, num_train_epochs=3, max_completion_length=4,
+                      use_cpu=True, save_strategy="no", report_to="none", shuffle_dataset=False)
+    assert args.generation_batch_size == 24
+    tr = GRPOTrainer(make_tiny_model(), _len_reward, args, train_dataset=ds, processing_class=tiny_tokenizer)
+    seen, gens = [], []
+    orig_gen = tr._generate_and_score_completions
+
+    def spy_gen(inputs):
+        gens.append([x["prompt"] for x in inputs])
+        return orig_gen(inputs)
+    tr._generate_and_score_completions = spy_gen
+    orig_step = type(tr).training_step
+
+    def spy_step(self, model, inputs, n=None):
+        seen.append([x["prompt"] for x in inputs])
+        return orig_step(self, model, inputs, n)
+    tr.training_step = spy_step.__get__(tr)
+    tr.train()
+    assert len(seen) == 48
+    assert all(seen[i] == seen[0] for i in range(8)) and seen[8] != seen[0]
+    assert len(gens) == 6 and len(gens[0]) == 24
+    prompts = [r["prompt"] for r in ds]
+    assert gens[0] == [p for p in prompts[:6] for _ in range(4)]
+
+
+def test_rloo_trains(tmp_path, tiny_tokenizer):
+    model = make_tiny_model()
+    before = _snap(model)
+    tr = RLOOTrainer(model, _len_reward, RLOOConfig(output_dir=str(tmp_path), **COMMON, num_generations=4, max_completion_length=8),
+                     train_dataset=make_dataset("conversational_prompt_only", 16), processing_class=tiny_tokenizer)
+    tr.train()
+    assert _changed(model, before) == []
+
+
+def test_grpo_reward_model_and_rollout_func(tmp_path, tiny_tokenizer):
+    rm = make_tiny_model(num_labels=1, seed=5)
+    calls = []
+
+    def rollout(prompts, trainer):
+        calls.append(len(prompts))
+        ids = trainer._tokenize_prompts(prompts)
+        return {"prompt_ids": ids, "completion_ids": [[7, 8, 9, trainer.eos_token_id] for _ in ids],
+                "logprobs": [[-1.0] * 4 for _ in ids]}
+    args = GRPOConfig(output_dir=str(tmp_path), **COMMON, num_generations=4, max_completion_length=8)
+    tr = GRPOTrainer(make_tiny_model(), [rm, _len_reward], args, train_dataset=make_dataset("standard_prompt_only", 8),
+                     processing_class=tiny_tokenizer, rollout_func=rollout)
+    tr.train()
+    assert calls and any("rewards/_len_reward/mean" in h for h in tr.state.log_history)
+
+
+def test_config_validation():
+    with pytest.raises(ValueError):
+        GRPOConfig(output_dir="x", per_device_train_batch_size=3, num_generations=4, use_cpu=True)
+    with pytest.raises(ValueError):
+        GRPOConfig(output_dir="x", num_generations=1, per_device_train_batch_size=4, use_cpu=True)
+    with pytest.raises(ValueError):
+        GRPOConfig(output_dir="x", parallelism_config={"cp_size": 2}, use_cpu=True)
+    with pytest.raises(ValueError):
+        DPOConfig(output_dir="x", loss_type="nope")
+    c = SFTConfig(output_dir="x", packing_strategy="bfd-requeue")
+    assert c.packing_strategy == "bfd_split" and c.loss_type == "chunked_nll" and c.logging_steps == 10
+    assert GRPOConfig(output_dir="x", use_cpu=True).loss_type == "dapo"

@@ -1,0 +1,127 @@
+"""Pure-function specifications (literal vectors taken from the behaviour the reference documents)."""
+import math
+
+import pytest
+import torch
+
+from trl_b200.oracle import ops as ref
+from trl_b200.ops import functional as F_
+from trl_b200.trainer.utils import (RepeatSampler, entropy_from_logits, flush_left, nanmax, nanmin, nanstd, pad,
+                                    selective_log_softmax, shuffle_sequence_dict, split_tensor_dict,
+                                    compute_flops_per_token, hash_module)
+
+
+def test_pad_right_left_multiple():
+    a, b = torch.tensor([1, 2, 3]), torch.tensor([4, 5])
+    assert pad([a, b], 0).tolist() == [[1, 2, 3], [4, 5, 0]]
+    assert pad([a, b], 0, "left").tolist() == [[1, 2, 3], [0, 4, 5]]
+    assert pad([a, b], 9, "right", pad_to_multiple_of=4).tolist() == [[1, 2, 3, 9], [4, 5, 9, 9]]
+    x = pad([torch.ones(2, 2), torch.ones(1, 3)], -1)
+    assert x.shape == (2, 2, 3) and x[1, 1, 0] == -1
+
+
+def test_flush_left():
+    mask = torch.tensor([[0, 0, 1, 1, 1], [0, 1, 1, 0, 0]])
+    t = torch.tensor([[0, 0, 2, 3, 4], [0, 5, 6, 0, 0]])
+    m2, t2 = flush_left(mask, t)
+    assert m2.tolist() == [[1, 1, 1], [1, 1, 0]] and t2.tolist() == [[2, 3, 4], [5, 6, 0]]
+
+
+def test_repeat_sampler_order():
+    s = RepeatSampler(list("abcdefg"), mini_repeat_count=2, batch_size=3, repeat_count=2, shuffle=False)
+    out = list(s)
+    assert out == [0, 0, 1, 1, 2, 2] * 2 + [3, 3, 4, 4, 5, 5] * 2  # index 6: incomplete chunk dropped
+    assert len(s) == len(out)
+    a = list(RepeatSampler(range(10), 1, 5, 1, seed=3))
+    b = list(RepeatSampler(range(10), 1, 5, 1, seed=3))
+    assert a == b and sorted(a) == list(range(10))
+
+
+def test_selective_log_softmax_and_entropy():
+    torch.manual_seed(0)
+    logits = torch.randn(3, 5, 11)
+    idx = torch.randint(0, 11, (3, 5))
+    want = torch.log_softmax(logits, -1).gather(-1, idx[..., None]).squeeze(-1)
+    assert torch.allclose(selective_log_softmax(logits, idx), want, atol=1e-6)
+    assert torch.allclose(selective_log_softmax(logits.bfloat16(), idx).float(), want, atol=5e-2)
+    k = torch.randint(0, 11, (3, 5, 2))
+    assert selective_log_softmax(logits, k).shape == (3, 5, 2)
+    lp = torch.log_softmax(logits, -1)
+    assert torch.allclose(entropy_from_logits(logits, chunk_size=4), -(lp.exp() * lp).sum(-1), atol=1e-6)
+
+
+def test_nan_helpers():
+    t = torch.tensor([1.0, 2.0, float("nan"), 4.0])
+    assert torch.isclose(nanstd(t), torch.tensor([1.0, 2.0, 4.0]).std())
+    assert nanmin(t) == 1.0 and nanmax(t) == 4.0
+    assert torch.isnan(nanstd(torch.tensor([float("nan"), 3.0])))
+    g = torch.tensor([[1.0, 3.0], [float("nan"), 2.0]])
+    out = nanstd(g, dim=1)
+    assert torch.isclose(out[0], torch.tensor(math.sqrt(2.0))) and torch.isnan(out[1])
+
+
+def test_split_and_shuffle_tensor_dict():
+    d = {"a": torch.arange(12).reshape(6, 2), "b": torch.arange(6), "s": torch.tensor(3.0), "n": None,
+         "l": list("uvwxyz")}
+    parts = split_tensor_dict(d, 3)
+    assert len(parts) == 3 and parts[1]["a"].tolist() == [[4, 5], [6, 7]] and parts[2]["l"] == ["y", "z"]
+    assert parts[0]["s"] == 3.0 and parts[0]["n"] is None
+    sh = shuffle_sequence_dict(d)
+    perm = sh["b"].tolist()
+    assert sorted(perm) == list(range(6)) and sh["a"][:, 0].tolist() == [2 * i for i in perm]
+    assert sh["l"] == [d["l"][i] for i in perm]
+
+
+@pytest.mark.parametrize("temp", [1.0, 0.7])
+def test_chunked_logprob_forward_backward_vs_naive(temp):
+    torch.manual_seed(0)
+    N, H, V = 64, 32, 128
+    h = torch.randn(N, H, requires_grad=True)
+    w = torch.randn(V, H, requires_grad=True)
+    y = torch.randint(0, V, (N,))
+    lp, ent = F_.lm_head_logprobs(h, w, y, temp, chunk_tokens=16)
+    g = torch.randn(N)
+    (lp * g).sum().backward()
+    h2, w2 = h.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+    logits = (h2 @ w2.t()) / temp
+    lp2 = torch.log_softmax(logits, -1).gather(-1, y[:, None]).squeeze(-1)
+    (lp2 * g).sum().backward()
+    p = torch.softmax(logits, -1)
+    assert torch.allclose(lp, lp2, atol=1e-5) and torch.allclose(ent, -(p * torch.log(p)).sum(-1).detach(), atol=1e-4)
+    assert torch.allclose(h.grad, h2.grad, atol=1e-5) and torch.allclose(w.grad, w2.grad, atol=1e-5)
+
+
+def test_lm_head_ce_matches_cross_entropy_and_zero_valid():
+    torch.manual_seed(0)
+    h = torch.randn(20, 16, requires_grad=True)
+    w = torch.randn(50, 16, requires_grad=True)
+    y = torch.randint(0, 50, (20,))
+    y[::3] = -100
+    loss_sum, correct, ent_sum, n = F_.lm_head_ce(h, w, y)
+    want = torch.nn.functional.cross_entropy(h @ w.t(), y, ignore_index=-100, reduction="sum")
+    assert torch.allclose(loss_sum, want, atol=1e-5) and int(n) == int((y != -100).sum())
+    z, c, e, n0 = F_.lm_head_ce(h, w, torch.full((20,), -100))
+    assert float(z) == 0.0 and int(n0) == 0
+    z.backward()  # the graph stays connected so every rank still runs backward
+    assert h.grad is not None and float(h.grad.abs().sum()) == 0.0
+
+
+def test_grpo_token_loss_reference_properties():
+    lp = torch.tensor([[-1.0, -2.0]])
+    loss, ratio, kl = ref.grpo_token_loss(lp, lp.clone(), lp - 0.5, torch.tensor([[2.0]]), 0.2, 0.2, 0.1)
+    assert torch.allclose(ratio, torch.ones_like(ratio))
+    assert torch.allclose(kl, torch.exp(torch.tensor(-0.5)) + 0.5 - 1)
+    assert torch.allclose(loss, -2.0 + 0.1 * kl)
+
+
+def test_flops_and_hash():
+    from trl_b200.models.configuration import preset
+    from trl_b200.models.decoder import CausalLM
+
+    f = compute_flops_per_token(preset("qwen2.5-7b"), 1280)
+    assert 4.0e10 < f < 6.0e10  # ~6 * 7.6e9 parameters
+    m = CausalLM(preset("tiny-qwen2"))
+    h1 = hash_module(m)
+    with torch.no_grad():
+        m.norm.add_(1)
+    assert hash_module(m) != h1

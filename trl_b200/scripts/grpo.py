@@ -2,7 +2,17 @@
 load the tokenizer and dataset from local paths, train, save.  Skeleton of trl/scripts/grpo.py."""
 from __future__ import annotations
 
+import dataclasses
 import os
+from typing import Optional
+
+from trl_b200.scripts.utils import ScriptArguments
+
+
+@dataclasses.dataclass
+class GRPOScriptArguments(ScriptArguments):
+    reward_model_name_or_path: Optional[str] = None
+    reward_funcs: Optional[list] = None
 
 
 def main(script_args, training_args, model_args, dataset_args):
@@ -71,14 +81,6 @@ def resolve_reward_funcs(script_args):
 def make_parser(subparsers=None):
     from trl_b200 import DatasetMixtureConfig, ModelConfig, TrlParser, GRPOConfig
     from trl_b200.scripts.utils import ScriptArguments
-
-    import dataclasses
-    from typing import Optional
-
-    @dataclasses.dataclass
-    class GRPOScriptArguments(ScriptArguments):
-        reward_model_name_or_path: Optional[str] = None
-        reward_funcs: Optional[list] = None
 
     dataclass_types = (GRPOScriptArguments, GRPOConfig, ModelConfig, DatasetMixtureConfig)
     if subparsers is not None:

@@ -96,42 +96,48 @@ class EngineHolder:
             sd[name].copy_(tensor.to(sd[name].device, sd[name].dtype))  # HF-named views alias the fused storage
 
 
+try:  # request models live at module level so FastAPI can resolve the postponed annotations
+    from pydantic import BaseModel
+except Exception:  # pragma: no cover
+    BaseModel = object
+
+
+class GenerateRequest(BaseModel):
+    prompts: list
+    n: int = 1
+    repetition_penalty: float = 1.0
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = 0
+    min_p: float = 0.0
+    max_tokens: int = 16
+    logprobs: Optional[int] = 0
+    generation_kwargs: dict = {}
+
+class ChatRequest(GenerateRequest):
+    prompts: list = []
+    messages: list = []
+    chat_template_kwargs: dict = {}
+    tools: Optional[list] = None
+
+class LogprobRequest(BaseModel):
+    sequences: list
+    prompt_lengths: list
+    temperature: float = 1.0
+
+class UpdateRequest(BaseModel):
+    name: str
+    dtype: str
+    shape: list
+    data: Optional[str] = None
+
+
 def build_app(holder: EngineHolder):
     from fastapi import FastAPI
-    from pydantic import BaseModel
 
     from ..rollout.sampling import SamplingParams
 
     app = FastAPI()
-
-    class GenerateRequest(BaseModel):
-        prompts: list
-        n: int = 1
-        repetition_penalty: float = 1.0
-        temperature: float = 1.0
-        top_p: float = 1.0
-        top_k: int = 0
-        min_p: float = 0.0
-        max_tokens: int = 16
-        logprobs: Optional[int] = 0
-        generation_kwargs: dict = {}
-
-    class ChatRequest(GenerateRequest):
-        prompts: list = []
-        messages: list = []
-        chat_template_kwargs: dict = {}
-        tools: Optional[list] = None
-
-    class LogprobRequest(BaseModel):
-        sequences: list
-        prompt_lengths: list
-        temperature: float = 1.0
-
-    class UpdateRequest(BaseModel):
-        name: str
-        dtype: str
-        shape: list
-        data: Optional[str] = None
 
     def _run(prompt_ids, r):
         eos = getattr(holder.tok, "eos_token_id", None) if holder.tok is not None else holder.model.config.eos_token_id
