@@ -1,0 +1,504 @@
+// Collectives fused with their compute, over NVLink peer memory (symmetric buffers mapped by every
+// rank of the node).  Peer data is reached with plain ld/st on peer pointers or with multimem.*
+// (NVSwitch reduce / broadcast) on the multicast mapping of the same buffers.  There is no TMA in
+// this file.
+//
+//   rs_reduce        gradient reduce-scatter fused with the fp32 cast, the 1/world scale and the
+//                    squared-norm partial of this rank's shard
+//   adamw_bcast      sharded AdamW on the reduced shard, writing the updated bf16 parameters straight
+//                    into every rank's replica (the parameter all-gather happens in the store)
+//   shard_allgather  parameter all-gather by pull (peer loads) or push (multimem.st)
+//   allreduce_add_rmsnorm   TP decode: sum of the ranks' partial GEMM outputs + residual add + RMSNorm
+//   norm_allreduce   grad-norm partials of all ranks -> clip coefficient on every rank, no host sync
+//
+// Cross-GPU ordering uses a signal pad (one 32-bit word per (channel, peer)) written with
+// st.release.sys and polled with ld.acquire.sys.  Every poll is bounded by time: when it runs out the
+// kernel records ERR_WAIT_TIMEOUT in the status words and returns, the context stays usable.
+//
+// They replace NCCL reduce-scatter + torch fused AdamW + NCCL all-gather of the reference's
+// DeepSpeed/FSDP engines (trl/models/utils.py:236-321, trl/accelerate_configs/zero*.yaml) and the
+// per-layer all-reduce inside vLLM's tensor-parallel decode (trl/generation/vllm_generation.py:324-332).
+#include "common.cuh"
+
+namespace trlb {
+
+constexpr int MAX_PEERS = 8;
+struct Peers {
+  void* buf[MAX_PEERS];       // the same symmetric buffer on every rank
+  uint32_t* pad[MAX_PEERS];   // signal pads
+  int rank, world;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+constexpr uint64_t kPeerWaitNs = 1000ull * 1000ull * 1000ull;  // 1 s: a peer that is this late is gone
+
+// All ranks meet: block 0 announces `epoch` on `channel` to every peer and waits for theirs, then
+// releases the other blocks of this grid through `local_gate`.  The grid must be co-resident
+// (launchers cap it at the SM count).  Returns false if a wait timed out.
+__device__ bool peers_barrier(const Peers& P, int channel, uint32_t epoch, uint32_t* local_gate, int* status, int site) {
+  __shared__ int ok_s;
+  if (blockIdx.x == 0) {
+    if (threadIdx.x == 0) ok_s = 1;
+    __syncthreads();
+    if (threadIdx.x < P.world) {
+      __threadfence_system();
+      st_release_sys(P.pad[threadIdx.x] + channel * MAX_PEERS + P.rank, epoch);
+      const uint32_t* mine = P.pad[P.rank] + channel * MAX_PEERS + threadIdx.x;
+      const uint64_t t0 = globaltimer_ns();
+      while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+        if (globaltimer_ns() - t0 > kPeerWaitNs) {
+          report_error(status, ERR_WAIT_TIMEOUT, site, (int)threadIdx.x);
+          ok_s = 0;
+          break;
+        }
+        __nanosleep(64);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      atomicExch(local_gate, ok_s ? epoch : 0xFFFFFFFFu);
+    }
+    return ok_s != 0;
+  }
+  if (threadIdx.x == 0) {
+    ok_s = 1;
+    const uint64_t t0 = globaltimer_ns();
+    while (true) {
+      const uint32_t g = ld_acquire_gpu(local_gate);
+      if (g == 0xFFFFFFFFu) { ok_s = 0; break; }
+      if ((int32_t)(g - epoch) >= 0) break;
+      if (globaltimer_ns() - t0 > 2 * kPeerWaitNs) {
+        report_error(status, ERR_WAIT_TIMEOUT, site + 1, (int)blockIdx.x);
+        ok_s = 0;
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  return ok_s != 0;
+}
+
+// True in exactly one block of the grid: the last one to get here.  Used to publish the new epoch only
+// after every block has read the old one (a block that starts late must not see the bumped counter).
+__device__ bool grid_last_block(uint32_t* counter) {
+  __shared__ unsigned last_s;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last_s = atomicAdd(counter, 1u);
+  __syncthreads();
+  if (last_s == gridDim.x - 1) {
+    if (threadIdx.x == 0) *counter = 0;
+    return true;
+  }
+  return false;
+}
+
+// ------------------------------------------------------------------------------------------------
+// rs_reduce: out[i] = (1/world) * sum_p grad_p[lo + i]  (fp32), sumsq += out[i]^2.
+// grad buffers are fp32 (GradT=float) or bf16.  When `mc` is given (multicast mapping of the gradient
+// buffer) the sum is done by the switch: multimem.ld_reduce.
+// ------------------------------------------------------------------------------------------------
+template <typename GradT>
+__global__ void __launch_bounds__(512)
+rs_reduce_kernel(Peers P, const void* mc, long long lo, long long n, float* __restrict__ out, float* __restrict__ sumsq,
+                 uint32_t* epoch_ctr, uint32_t* local_gate, int channel, int* status) {
+  const uint32_t epoch = *epoch_ctr + 1;
+  if (!peers_barrier(P, channel, epoch, local_gate, status, 500)) return;
+  const float inv = 1.f / (float)P.world;
+  float ss = 0.f;
+  constexpr int VEC = 16 / sizeof(GradT);  // elements per 16-byte access
+  const long long nvec = n / VEC;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+    float acc[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+    if (mc != nullptr && sizeof(GradT) == 4) {
+      const float* src = reinterpret_cast<const float*>(mc) + lo + v * VEC;
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(acc[0]), "=f"(acc[1]), "=f"(acc[2]), "=f"(acc[3])
+                   : "l"(src)
+                   : "memory");
+    } else {
+      uint4 raw[MAX_PEERS];
+#pragma unroll
+      for (int p = 0; p < MAX_PEERS; ++p)
+        if (p < P.world) raw[p] = reinterpret_cast<const uint4*>(reinterpret_cast<const GradT*>(P.buf[p]) + lo)[v];
+#pragma unroll
+      for (int p = 0; p < MAX_PEERS; ++p) {
+        if (p < P.world) {
+          if constexpr (sizeof(GradT) == 4) {
+            const float* f = reinterpret_cast<const float*>(&raw[p]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[j] += f[j];
+          } else {
+            const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw[p]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = unpack_bf16(u[j]);
+              acc[2 * j] += f.x;
+              acc[2 * j + 1] += f.y;
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      acc[j] *= inv;
+      ss += acc[j] * acc[j];
+    }
+    float4* dst = reinterpret_cast<float4*>(out + v * VEC);
+    dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    if constexpr (VEC == 8) dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
+  ss = warp_sum(ss);
+  __shared__ float ws[16];
+  if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += ws[w];
+    atomicAdd(sumsq, t);
+  }
+  if (grid_last_block(local_gate + 1) && threadIdx.x == 0) *epoch_ctr = epoch;
+}
+
+// ------------------------------------------------------------------------------------------------
+// norm_allreduce: every rank publishes its sum of squares into slot [rank] of every peer's `slots`
+// (symmetric, world floats), then computes norm and clip coefficient locally.  One CTA.
+// ------------------------------------------------------------------------------------------------
+__global__ void norm_allreduce_kernel(Peers P, const float* __restrict__ my_sumsq, float max_norm,
+                                      float* __restrict__ norm_out, float* __restrict__ clip_out, uint32_t* epoch_ctr,
+                                      uint32_t* local_gate, int channel, int* status) {
+  const uint32_t epoch = *epoch_ctr + 1;
+  if (threadIdx.x < P.world) reinterpret_cast<float*>(P.buf[threadIdx.x])[P.rank] = *my_sumsq;
+  __syncthreads();
+  if (!peers_barrier(P, channel, epoch, local_gate, status, 520)) return;
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    const float* mine = reinterpret_cast<const float*>(P.buf[P.rank]);
+    for (int p = 0; p < P.world; ++p) t += mine[p];
+    const float nrm = sqrtf(t);
+    *norm_out = nrm;
+    *clip_out = (max_norm > 0.f) ? fminf(1.f, max_norm / (nrm + 1e-6f)) : 1.f;
+    *epoch_ctr = epoch;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// adamw_bcast: AdamW on this rank's shard; the refreshed bf16 values go to every rank's replica of
+// the flat parameter buffer (P.buf = flat_param on each rank) at [lo, lo+n).  With `mc` the store is
+// one multimem.st that NVSwitch replicates.  A closing barrier tells the peers their replica is whole.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(512)
+adamw_bcast_kernel(Peers P, void* mc, long long lo, long long n, float* __restrict__ master,
+                   const float* __restrict__ grad, float* __restrict__ m, float* __restrict__ v, float lr, float b1,
+                   float b2, float eps, float wd, float bc1, float bc2_sqrt, const float* __restrict__ clip,
+                   uint32_t* epoch_ctr, uint32_t* local_gate, int channel, int* status) {
+  const uint32_t epoch = *epoch_ctr + 1;
+  const float gs = clip ? *clip : 1.f;
+  const long long nvec = n / 8;
+  for (long long q = blockIdx.x * (long long)blockDim.x + threadIdx.x; q < nvec; q += (long long)gridDim.x * blockDim.x) {
+    float pv[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const long long i = q * 8 + h * 4;
+      const float4 g4 = *reinterpret_cast<const float4*>(grad + i);
+      float4 m4 = *reinterpret_cast<const float4*>(m + i), v4 = *reinterpret_cast<const float4*>(v + i);
+      float4 p4 = *reinterpret_cast<const float4*>(master + i);
+      const float g[4] = {g4.x * gs, g4.y * gs, g4.z * gs, g4.w * gs};
+      float* mm = reinterpret_cast<float*>(&m4);
+      float* vv = reinterpret_cast<float*>(&v4);
+      float* pp = reinterpret_cast<float*>(&p4);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        mm[j] = mm[j] * b1 + (1.f - b1) * g[j];
+        vv[j] = vv[j] * b2 + (1.f - b2) * g[j] * g[j];
+        float p = pp[j];
+        p -= lr * wd * p;
+        p -= (lr / bc1) * mm[j] / (sqrtf(vv[j]) / bc2_sqrt + eps);
+        pp[j] = p;
+        pv[h * 4 + j] = p;
+      }
+      *reinterpret_cast<float4*>(m + i) = m4;
+      *reinterpret_cast<float4*>(v + i) = v4;
+      *reinterpret_cast<float4*>(master + i) = p4;
+    }
+    uint4 o;
+    o.x = pack_bf16(pv[0], pv[1]);
+    o.y = pack_bf16(pv[2], pv[3]);
+    o.z = pack_bf16(pv[4], pv[5]);
+    o.w = pack_bf16(pv[6], pv[7]);
+    if (mc != nullptr) {
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(mc) + lo + q * 8;
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(o.x)),
+                   "f"(__uint_as_float(o.y)), "f"(__uint_as_float(o.z)), "f"(__uint_as_float(o.w))
+                   : "memory");
+    } else {
+#pragma unroll
+      for (int p = 0; p < MAX_PEERS; ++p)
+        if (p < P.world) reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(P.buf[p]) + lo)[q] = o;
+    }
+  }
+  // all of this grid's stores must be visible to the peers before the barrier word is released
+  __threadfence_system();
+  __shared__ unsigned last;
+  __syncthreads();
+  // every block arrives on the gate counter in the high half of local_gate's neighbour word
+  if (threadIdx.x == 0) last = atomicAdd(local_gate + 1, 1u);
+  __syncthreads();
+  if (last == gridDim.x - 1) {  // the last block to finish runs the cross-GPU barrier on behalf of the grid
+    if (threadIdx.x == 0) local_gate[1] = 0;
+    __shared__ int ok_s;
+    if (threadIdx.x == 0) ok_s = 1;
+    __syncthreads();
+    if (threadIdx.x < P.world) {
+      st_release_sys(P.pad[threadIdx.x] + channel * MAX_PEERS + P.rank, epoch);
+      const uint32_t* mine = P.pad[P.rank] + channel * MAX_PEERS + threadIdx.x;
+      const uint64_t t0 = globaltimer_ns();
+      while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+        if (globaltimer_ns() - t0 > kPeerWaitNs) {
+          report_error(status, ERR_WAIT_TIMEOUT, 540, (int)threadIdx.x);
+          break;
+        }
+        __nanosleep(64);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *epoch_ctr = epoch;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// shard_allgather: every rank owns elements [rank*per, (rank+1)*per) of a bf16 buffer of world*per
+// elements (P.buf = that buffer on each rank).  mode 0: pull the other shards from their owners;
+// mode 1: push the own shard to everyone with multimem.st (mc = multicast mapping).
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(512)
+shard_allgather_kernel(Peers P, void* mc, long long per, uint32_t* epoch_ctr, uint32_t* local_gate, int channel,
+                       int* status) {
+  const uint32_t epoch = *epoch_ctr + 1;
+  // entry barrier: the owners' shards are final (their producing kernels ran earlier on their streams)
+  if (!peers_barrier(P, channel, epoch, local_gate, status, 560)) return;
+  const long long nvec = per / 8;
+  if (mc != nullptr) {
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(P.buf[P.rank]) + P.rank * per);
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(mc) + P.rank * per;
+    for (long long q = blockIdx.x * (long long)blockDim.x + threadIdx.x; q < nvec; q += (long long)gridDim.x * blockDim.x) {
+      const uint4 o = src[q];
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + q * 8),
+                   "f"(__uint_as_float(o.x)), "f"(__uint_as_float(o.y)), "f"(__uint_as_float(o.z)),
+                   "f"(__uint_as_float(o.w))
+                   : "memory");
+    }
+  } else {
+    uint4* mine = reinterpret_cast<uint4*>(P.buf[P.rank]);
+    for (int s = 1; s < P.world; ++s) {
+      const int owner = (P.rank + s) % P.world;  // staggered so the ranks do not all hit one owner at once
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(P.buf[owner]) + owner * per);
+      uint4* dst = mine + owner * nvec;
+      for (long long q = blockIdx.x * (long long)blockDim.x + threadIdx.x; q < nvec; q += (long long)gridDim.x * blockDim.x)
+        dst[q] = src[q];
+    }
+  }
+  __threadfence_system();
+  __shared__ unsigned last;
+  __syncthreads();
+  if (threadIdx.x == 0) last = atomicAdd(local_gate + 1, 1u);
+  __syncthreads();
+  if (last == gridDim.x - 1) {
+    if (threadIdx.x == 0) local_gate[1] = 0;
+    // closing barrier (pushed data has landed everywhere / nobody overwrites a shard still being pulled)
+    const uint32_t e2 = epoch + 1;
+    if (threadIdx.x < P.world) {
+      st_release_sys(P.pad[threadIdx.x] + channel * MAX_PEERS + P.rank, e2);
+      const uint32_t* w = P.pad[P.rank] + channel * MAX_PEERS + threadIdx.x;
+      const uint64_t t0 = globaltimer_ns();
+      while ((int32_t)(ld_acquire_sys(w) - e2) < 0) {
+        if (globaltimer_ns() - t0 > kPeerWaitNs) {
+          report_error(status, ERR_WAIT_TIMEOUT, 580, (int)threadIdx.x);
+          break;
+        }
+        __nanosleep(64);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *epoch_ctr = e2;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// allreduce_add_rmsnorm (TP decode): res[T,H] += sum_p partial_p[T,H]; y = rmsnorm(res) * w.
+// P.buf[p] = base of rank p's partial buffers (two buffers of T*H bf16, used alternately so a fast rank's
+// next GEMM never overwrites a buffer a slow peer still reads).  One CTA per row; the sum runs in rank
+// order on every rank, so all ranks compute bit-identical residual streams.
+// ------------------------------------------------------------------------------------------------
+template <int VPT>
+__global__ void __launch_bounds__(256)
+allreduce_add_rmsnorm_kernel(Peers P, long long buf_elems, __nv_bfloat16* __restrict__ res,
+                             const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int H, float eps,
+                             uint32_t* epoch_ctr, uint32_t* local_gate, int channel, int* status) {
+  const uint32_t epoch = *epoch_ctr + 1;
+  if (!peers_barrier(P, channel, epoch, local_gate, status, 600)) return;
+  const long long which = (long long)(epoch & 1u) * buf_elems;
+  __shared__ float red[8];
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int nvec = H >> 3;
+  uint4* xr = reinterpret_cast<uint4*>(res + (size_t)row * H);
+  float buf[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * 256;
+    if (v < nvec) {
+      uint4 a = xr[v];
+      uint32_t* au = reinterpret_cast<uint32_t*>(&a);
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16(au[j]); acc[2 * j] = f.x; acc[2 * j + 1] = f.y; }
+      float part[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int p = 0; p < MAX_PEERS; ++p) {
+        if (p < P.world) {
+          const uint4 d = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(P.buf[p]) + which +
+                                                        (size_t)row * H)[v];
+          const uint32_t* du = reinterpret_cast<const uint32_t*>(&d);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16(du[j]); part[2 * j] += f.x; part[2 * j + 1] += f.y; }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        // the summed block output is rounded to bf16 first (what an unfused all-reduce would hand over)
+        const float2 s = unpack_bf16(pack_bf16(part[2 * j], part[2 * j + 1]));
+        au[j] = pack_bf16(acc[2 * j] + s.x, acc[2 * j + 1] + s.y);
+        const float2 r = unpack_bf16(au[j]);
+        buf[i][2 * j] = r.x; buf[i][2 * j + 1] = r.y;
+        ss += r.x * r.x + r.y * r.y;
+      }
+      xr[v] = a;
+    }
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) red[wid] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) tot += red[k];
+  const float rstd = rsqrtf(tot / (float)H + eps);
+  uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * H);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * 256;
+    if (v < nvec) {
+      const uint4 wv = wr[v];
+      const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wv);
+      uint4 o;
+      uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 g = unpack_bf16(wu[j]);
+        ou[j] = pack_bf16(buf[i][2 * j] * rstd * g.x, buf[i][2 * j + 1] * rstd * g.y);
+      }
+      yr[v] = o;
+    }
+  }
+  if (grid_last_block(local_gate + 1) && threadIdx.x == 0) *epoch_ctr = epoch;
+}
+
+}  // namespace trlb
+
+using namespace trlb;
+
+static Peers make_peers(const unsigned long long* bufs, const unsigned long long* pads, int rank, int world) {
+  Peers P;
+  for (int i = 0; i < MAX_PEERS; ++i) {
+    P.buf[i] = i < world ? reinterpret_cast<void*>(bufs[i]) : nullptr;
+    P.pad[i] = i < world ? reinterpret_cast<uint32_t*>(pads[i]) : nullptr;
+  }
+  P.rank = rank;
+  P.world = world;
+  return P;
+}
+
+static int capped_grid(long long work_items, int threads) {
+  long long g = (work_items + threads - 1) / threads;
+  const int cap = trlb_host::sm_count();  // co-resident: blocks wait on block 0's barrier
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+// sync words: epoch_ctr (1 word) and local_gate (2 words) live in caller-provided device memory, zeroed once.
+TRLB_API int trlb_rs_reduce(const unsigned long long* bufs, const unsigned long long* pads, int rank, int world,
+                            const void* mc, int grad_is_bf16, long long lo, long long n, float* out, float* sumsq,
+                            unsigned* epoch_ctr, unsigned* local_gate, int channel, int* status, cudaStream_t st) {
+  if (world > MAX_PEERS || n % 8 != 0 || lo % 8 != 0) return -1;
+  Peers P = make_peers(bufs, pads, rank, world);
+  const int grid = capped_grid(n / 4, 512);
+  if (grad_is_bf16)
+    rs_reduce_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(P, nullptr, lo, n, out, sumsq, epoch_ctr, local_gate, channel, status);
+  else
+    rs_reduce_kernel<float><<<grid, 512, 0, st>>>(P, mc, lo, n, out, sumsq, epoch_ctr, local_gate, channel, status);
+  return (int)cudaGetLastError();
+}
+
+TRLB_API int trlb_norm_allreduce(const unsigned long long* bufs, const unsigned long long* pads, int rank, int world,
+                                 const float* my_sumsq, float max_norm, float* norm_out, float* clip_out,
+                                 unsigned* epoch_ctr, unsigned* local_gate, int channel, int* status, cudaStream_t st) {
+  if (world > MAX_PEERS) return -1;
+  Peers P = make_peers(bufs, pads, rank, world);
+  norm_allreduce_kernel<<<1, 32, 0, st>>>(P, my_sumsq, max_norm, norm_out, clip_out, epoch_ctr, local_gate, channel, status);
+  return (int)cudaGetLastError();
+}
+
+TRLB_API int trlb_adamw_bcast(const unsigned long long* bufs, const unsigned long long* pads, int rank, int world, void* mc,
+                              long long lo, long long n, float* master, const float* grad, float* m, float* v, int step,
+                              float lr, float b1, float b2, float eps, float wd, const float* clip, unsigned* epoch_ctr,
+                              unsigned* local_gate, int channel, int* status, cudaStream_t st) {
+  if (world > MAX_PEERS || n % 8 != 0 || lo % 8 != 0) return -1;
+  Peers P = make_peers(bufs, pads, rank, world);
+  const float bc1 = 1.f - powf(b1, (float)step), bc2s = sqrtf(1.f - powf(b2, (float)step));
+  const int grid = capped_grid(n / 8, 512);
+  adamw_bcast_kernel<<<grid, 512, 0, st>>>(P, mc, lo, n, master, grad, m, v, lr, b1, b2, eps, wd, bc1, bc2s, clip,
+                                           epoch_ctr, local_gate, channel, status);
+  return (int)cudaGetLastError();
+}
+
+TRLB_API int trlb_shard_allgather(const unsigned long long* bufs, const unsigned long long* pads, int rank, int world,
+                                  void* mc, long long per, unsigned* epoch_ctr, unsigned* local_gate, int channel,
+                                  int* status, cudaStream_t st) {
+  if (world > MAX_PEERS || per % 8 != 0) return -1;
+  Peers P = make_peers(bufs, pads, rank, world);
+  const int grid = capped_grid(per / 8, 512);
+  shard_allgather_kernel<<<grid, 512, 0, st>>>(P, mc, per, epoch_ctr, local_gate, channel, status);
+  return (int)cudaGetLastError();
+}
+
+TRLB_API int trlb_allreduce_add_rmsnorm(const unsigned long long* bufs, const unsigned long long* pads, int rank, int world,
+                                        long long buf_elems, void* res, const void* w, void* y, int T, int H, float eps,
+                                        unsigned* epoch_ctr, unsigned* local_gate, int channel, int* status,
+                                        cudaStream_t st) {
+  if (world > MAX_PEERS || H % 8 != 0 || H > 8192 || T > trlb_host::sm_count()) return -1;  // co-resident grid
+  Peers P = make_peers(bufs, pads, rank, world);
+  const int vpt = (H / 8 + 255) / 256;
+  auto R = (__nv_bfloat16*)res; auto W = (const __nv_bfloat16*)w; auto Y = (__nv_bfloat16*)y;
+  if (vpt <= 1) allreduce_add_rmsnorm_kernel<1><<<T, 256, 0, st>>>(P, buf_elems, R, W, Y, H, eps, epoch_ctr, local_gate, channel, status);
+  else if (vpt <= 2) allreduce_add_rmsnorm_kernel<2><<<T, 256, 0, st>>>(P, buf_elems, R, W, Y, H, eps, epoch_ctr, local_gate, channel, status);
+  else allreduce_add_rmsnorm_kernel<4><<<T, 256, 0, st>>>(P, buf_elems, R, W, Y, H, eps, epoch_ctr, local_gate, channel, status);
+  return (int)cudaGetLastError();
+}

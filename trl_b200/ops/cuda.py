@@ -435,3 +435,49 @@ def advance(tok, logp, slot_ids, seq_lens, n_gen, finished, out_tokens, out_logp
                             _p(out_tokens), _p(out_logps), c_int(out_tokens.shape[1]),
                             c_int(-1 if eos_id is None else eos_id), c_int(max_total_len), _p(next_input),
                             _p(step_counter), c_int(bump_len), _s()), "advance")
+
+
+# -------------------------------------------------------------------------------------------
+# collectives fused with compute (csrc/comm.cu); `arena` is a parallel.symm.SymmArena
+# -------------------------------------------------------------------------------------------
+def rs_reduce(arena, byte_offset, grad_is_bf16, lo, n, out, sumsq, sync, use_multimem=False):
+    """out[n] (fp32) = mean over ranks of grad[lo:lo+n]; sumsq += |out|^2.  Reads peers' buffers in place."""
+    mc = arena.mc(byte_offset) if (use_multimem and not grad_is_bf16) else None
+    _chk(lib().trlb_rs_reduce(arena.peers(byte_offset), arena.pads(), c_int(arena.rank), c_int(arena.world), mc,
+                              c_int(int(grad_is_bf16)), c_longlong(lo), c_longlong(n), _p(out), _p(sumsq),
+                              sync.epoch_ptr, sync.gate_ptr, c_int(sync.channel), _p(status_buffer(out.device)), _s()),
+         "rs_reduce")
+
+
+def norm_allreduce(arena, byte_offset, my_sumsq, max_norm, norm_out, clip_out, sync):
+    _chk(lib().trlb_norm_allreduce(arena.peers(byte_offset), arena.pads(), c_int(arena.rank), c_int(arena.world),
+                                   _p(my_sumsq), c_float(max_norm or 0.0), _p(norm_out), _p(clip_out), sync.epoch_ptr,
+                                   sync.gate_ptr, c_int(sync.channel), _p(status_buffer(norm_out.device)), _s()),
+         "norm_allreduce")
+
+
+def adamw_bcast(arena, byte_offset, lo, n, master, grad, m, v, step, lr, b1, b2, eps, wd, clip, sync, use_multimem=False):
+    """AdamW on the shard; refreshed bf16 parameters are stored into every rank's replica at [lo, lo+n)."""
+    mc = arena.mc(byte_offset) if use_multimem else None
+    _chk(lib().trlb_adamw_bcast(arena.peers(byte_offset), arena.pads(), c_int(arena.rank), c_int(arena.world), mc,
+                                c_longlong(lo), c_longlong(n), _p(master), _p(grad), _p(m), _p(v), c_int(step), c_float(lr),
+                                c_float(b1), c_float(b2), c_float(eps), c_float(wd), _p(clip), sync.epoch_ptr, sync.gate_ptr,
+                                c_int(sync.channel), _p(status_buffer(master.device)), _s()), "adamw_bcast")
+
+
+def shard_allgather(arena, byte_offset, per, sync, use_multimem=False):
+    mc = arena.mc(byte_offset) if use_multimem else None
+    _chk(lib().trlb_shard_allgather(arena.peers(byte_offset), arena.pads(), c_int(arena.rank), c_int(arena.world), mc,
+                                    c_longlong(per), sync.epoch_ptr, sync.gate_ptr, c_int(sync.channel),
+                                    _p(status_buffer(arena.buf.device)), _s()), "shard_allgather")
+
+
+def allreduce_add_rmsnorm(arena, byte_offset, buf_elems, res, w, eps, sync, out=None):
+    """res += sum over ranks of their partial [T,H] (in the arena, double-buffered); returns rmsnorm(res) * w."""
+    T, H = res.shape
+    out = torch.empty_like(res) if out is None else out
+    _chk(lib().trlb_allreduce_add_rmsnorm(arena.peers(byte_offset), arena.pads(), c_int(arena.rank), c_int(arena.world),
+                                          c_longlong(buf_elems), _p(res), _p(w), _p(out), c_int(T), c_int(H), c_float(eps),
+                                          sync.epoch_ptr, sync.gate_ptr, c_int(sync.channel),
+                                          _p(status_buffer(res.device)), _s()), "allreduce_add_rmsnorm")
+    return out

@@ -30,8 +30,13 @@ import torch
 import torch.distributed as td
 import torch.nn as nn
 
-from ..loop.optim import adamw_flat
 from . import dist as D
+
+
+def adamw_flat(*a, **k):  # imported on use: loop/ imports this module
+    from ..loop.optim import adamw_flat as f
+
+    return f(*a, **k)
 
 _ALIGN = 256  # elements; keeps every shard 16-byte aligned for TMA / vector access
 
@@ -77,8 +82,30 @@ class TrainEngine:
         self.betas, self.eps, self.weight_decay = betas, eps, weight_decay
         self.step_count = 0
         self.sharded = self.mode in ("zero1", "zero2", "full_shard") and self.world > 1
+        first = next((p for p in model.parameters() if p.requires_grad), None)
+        on_gpu = first is not None and first.is_cuda
+        if use_symm_kernels is None:
+            from .symm import symmetric_available
+            import os
+
+            use_symm_kernels = (self.sharded and on_gpu and first.dtype == torch.bfloat16 and symmetric_available()
+                                and weight_decay == 0.0 and os.environ.get("TRL_B200_NCCL_OPTIMIZER", "0") != "1")
+        self.use_symm = bool(use_symm_kernels)
+        self.use_multimem = False
+        self._arenas = {}
         self._build_buckets(bucket_of, grad_dtype)
-        self.use_symm = bool(use_symm_kernels) if use_symm_kernels is not None else False
+        if self.use_symm:
+            from .symm import SyncWords
+
+            dev = self.buckets[0].flat_param.device
+            self._sync = SyncWords(dev, channel=0)
+            self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+            self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
+            self._clip = torch.ones(1, dtype=torch.float32, device=dev)
+            self._reduced = [torch.empty(b.hi - b.lo, dtype=torch.float32, device=dev) for b in self.buckets]
+            import os
+
+            self.use_multimem = bool(self._arenas["param"].multicast_ptr) and os.environ.get("TRL_B200_MULTIMEM", "1") == "1"
         self._hooks = []
         self._install_grad_views()
 
@@ -93,6 +120,23 @@ class TrainEngine:
             groups.setdefault((bucket_of(n), p.dtype), []).append((n, p))
         self.buckets: list[Bucket] = []
         unit = self.world * _ALIGN
+        if self.use_symm:
+            # one symmetric arena for all parameter buckets and one for all gradient buckets:
+            # a single rendezvous each, peer address = peer base + the bucket's byte offset
+            from .symm import SymmArena
+
+            gd0 = grad_dtype or torch.float32
+            tot_p = tot_g = 0
+            for (_, dtype), items in groups.items():
+                cur = sum((p.numel() + 15) // 16 * 16 for _, p in items)
+                numel = (cur + unit - 1) // unit * unit
+                tot_p += numel * torch.empty(0, dtype=dtype).element_size() + 256
+                tot_g += numel * torch.empty(0, dtype=gd0).element_size() + 256
+            dev0 = next(iter(groups.values()))[0][1].device
+            self._arenas["param"] = SymmArena(tot_p, dev0, self.group)
+            self._arenas["grad"] = SymmArena(tot_g + 4096, dev0, self.group)
+            self._norm_slots, self._norm_off = self._arenas["grad"].carve(64, torch.float32)
+        self._offsets = {}
         for (bname, dtype), items in groups.items():
             offs, cur = [], 0
             for _, p in items:
@@ -101,14 +145,14 @@ class TrainEngine:
             numel = (cur + unit - 1) // unit * unit
             dev = items[0][1].device
             b = Bucket(bname, [n for n, _ in items], [p for _, p in items], offs, numel)
-            b.flat_param = torch.zeros(numel, dtype=dtype, device=dev)
+            b.flat_param = self._alloc("param", b, numel, dtype, dev)
             for (n, p), o in zip(items, offs):
                 b.flat_param[o:o + p.numel()].view_as(p).copy_(p.data)
                 p.data = b.flat_param[o:o + p.numel()].view_as(p)
                 if p.ndim <= 1:  # biases and norm weights: no weight decay (HF convention)
                     b.no_decay_ranges.append((o, o + p.numel()))
             gd = grad_dtype or torch.float32
-            b.flat_grad = torch.zeros(numel, dtype=gd, device=dev)
+            b.flat_grad = self._alloc("grad", b, numel, gd, dev)
             if self.sharded:
                 per = numel // self.world
                 b.lo, b.hi = self.rank * per, (self.rank + 1) * per
@@ -127,6 +171,13 @@ class TrainEngine:
                     mask[lo:hi] = 0
                 b.decay_mask = mask[b.lo:b.hi].contiguous()
             self.buckets.append(b)
+
+    def _alloc(self, kind, bucket, numel, dtype, dev):
+        if not self.use_symm:
+            return torch.zeros(numel, dtype=dtype, device=dev)
+        t, off = self._arenas[kind].carve(numel, dtype)
+        self._offsets[(kind, bucket.name, str(bucket.params[0].dtype))] = off
+        return t
 
     def _install_grad_views(self):
         for b in self.buckets:
@@ -175,6 +226,8 @@ class TrainEngine:
     def step(self, lr: float, max_grad_norm: float | None = None) -> torch.Tensor:
         """Reduce, clip by global norm, AdamW, refresh the compute copy.  Returns the pre-clip norm."""
         self.step_count += 1
+        if self.use_symm:
+            return self._step_fused(lr, max_grad_norm)
         reduced = [self._reduce(b) for b in self.buckets]
         sq = torch.zeros((), dtype=torch.float32, device=reduced[0].device)
         for g in reduced:
@@ -197,6 +250,27 @@ class TrainEngine:
             if self.sharded:
                 td.all_gather_into_tensor(b.flat_param, b.flat_param[b.lo:b.hi].clone(), group=self.group)
         return norm
+
+    def _step_fused(self, lr: float, max_grad_norm: float | None) -> torch.Tensor:
+        """Optimizer step on the comm kernels: per bucket a reduce-scatter that reads the peers' gradient
+        buffers in place (fp32 cast, 1/world, norm partial), one exchange of the norm partials, then AdamW
+        whose bf16 output is stored into every rank's parameter replica.  No NCCL call, no host sync."""
+        from ..ops import cuda as K
+
+        ga, pa = self._arenas["grad"], self._arenas["param"]
+        self._sumsq.zero_()
+        for b, red in zip(self.buckets, self._reduced):
+            key = (b.name, str(b.params[0].dtype))
+            K.rs_reduce(ga, self._offsets[("grad",) + key], b.flat_grad.dtype == torch.bfloat16, b.lo, b.hi - b.lo, red,
+                        self._sumsq, self._sync, use_multimem=self.use_multimem)
+        K.norm_allreduce(ga, self._norm_off, self._sumsq, max_grad_norm or 0.0, self._norm, self._clip, self._sync)
+        b1, b2 = self.betas
+        for b, red in zip(self.buckets, self._reduced):
+            key = (b.name, str(b.params[0].dtype))
+            K.adamw_bcast(pa, self._offsets[("param",) + key], b.lo, b.hi - b.lo, b.master, red, b.exp_avg, b.exp_avg_sq,
+                          self.step_count, lr, b1, b2, self.eps, self.weight_decay, self._clip, self._sync,
+                          use_multimem=self.use_multimem)
+        return self._norm[0].clone()
 
     def _masked_adamw(self, b: Bucket, g, lr, gs, shadow):
         b1, b2 = self.betas
