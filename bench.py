@@ -46,6 +46,7 @@ def parse():
     ap.add_argument("--max-new", type=int, default=1024)
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--rollout-tp", type=int, default=0, help="0 = 2 when more than one GPU, else 1")
     ap.add_argument("--layers", type=int, default=None, help="debug only: truncating the model invalidates the number")
     return ap.parse_args()
 
@@ -158,12 +159,14 @@ def main():
     per_rank = a.prompts_per_gpu * a.num_generations
     ga = per_rank // a.micro_batch
     out_dir = tempfile.mkdtemp(prefix="bench_grpo_")
+    rollout_tp = a.rollout_tp or (2 if world > 1 else 1)
     args = GRPOConfig(output_dir=out_dir, per_device_train_batch_size=a.micro_batch, gradient_accumulation_steps=ga,
                       num_generations=a.num_generations, max_completion_length=a.max_new, temperature=1.0, beta=0.04,
                       epsilon=0.2, learning_rate=1e-6, max_steps=a.steps, logging_steps=1, save_strategy="no",
                       bf16=True, use_vllm=True, vllm_mode="colocate", eos_prob_floor=1.0 / 512, shuffle_dataset=False,
                       shard_mode="zero2" if world > 1 else "ddp", report_to="none", seed=7,
-                      vllm_importance_sampling_correction=False, gradient_checkpointing=True)
+                      vllm_importance_sampling_correction=False, gradient_checkpointing=True,
+                      vllm_tensor_parallel_size=rollout_tp)
     trainer = GRPOTrainer(model, even_fraction_reward, args, train_dataset=rows, processing_class=tok)
     trainer.callback_handler.callbacks = [c for c in trainer.callback_handler.callbacks
                                           if type(c).__name__ != "PrinterCallback"]
@@ -245,8 +248,8 @@ def main():
                        "num_generations": a.num_generations, "seq_len": a.prompt_len + a.max_new,
                        "prompt_len": a.prompt_len, "max_new_tokens": a.max_new, "eos_prob_floor": 1.0 / 512,
                        "beta": 0.04, "epsilon": 0.2, "loss_type": "dapo", "micro_batch": a.micro_batch,
-                       "parallelism": f"dp{world} {args.shard_mode}, rollout tp1 x {world} replicas (colocated, "
-                                      f"weights shared in place)",
+                       "parallelism": f"dp{world} {args.shard_mode}, rollout tp{rollout_tp} x {world // rollout_tp} replicas "
+                                      f"(colocated)",
                        "l2_policy": "inputs larger than L2: every step streams >=15 GB of weights",
                        "tokens_counted": "generated completion tokens + trained (prompt+completion) tokens"},
             "gpu_launches": int(launches), "clocks": clk, "peak_mem_gib": round(peak_gb, 1),
@@ -261,6 +264,10 @@ def main():
                     sum(h.get(k, 0.0) for h in hist[-a.steps:]) / max(1, len(hist[-a.steps:])), 3) for k in keys}
         print(json.dumps(line))
     D.barrier()
+    if D.is_initialized():
+        import torch.distributed as td
+
+        td.destroy_process_group()
     return 0
 
 

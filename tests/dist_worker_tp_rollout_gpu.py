@@ -1,0 +1,57 @@
+"""2-GPU worker: tensor-parallel rollout engine vs the single-GPU engine (greedy decoding)."""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import torch
+import torch.distributed as td
+
+from trl_b200.ops import cuda as K
+from trl_b200.parallel import dist as D
+from trl_b200.rollout.engine import RolloutEngine
+from trl_b200.rollout.sampling import SamplingParams
+from trl_b200.rollout.tp_engine import TPRolloutEngine
+from trl_b200.testing import make_tiny_model
+
+
+def main():
+    D.init_process_group()
+    rank = D.rank()
+    dev = torch.device("cuda", D.local_rank())
+    model = make_tiny_model("tiny-qwen2", dtype=torch.bfloat16, device=dev, hidden_size=512, num_attention_heads=4,
+                            num_key_value_heads=2, head_dim=128, intermediate_size=1024, seed=0)
+    g = torch.Generator().manual_seed(5)
+    all_prompts = [torch.randint(5, 1000, (n,), generator=g).tolist() for n in (9, 20, 33, 16)]
+    mine = all_prompts[2 * rank:2 * rank + 2]
+    sp = SamplingParams(n=2, max_tokens=10, greedy=True, eos_token_id=2)
+    ref = RolloutEngine(model, max_num_seqs=4, max_model_len=64, poll_every=4).generate(mine, sp)
+    group = td.new_group([0, 1])
+    eng = TPRolloutEngine(model, group, max_num_seqs=4, max_model_len=64, poll_every=4)
+    out = eng.generate(mine, sp)
+    torch.cuda.synchronize()
+    K.check_status(dev)
+    assert len(out) == len(ref) == 4
+    agree = sum(o.token_ids[:3] == r.token_ids[:3] for o, r in zip(out, ref))
+    assert agree >= 3, [(o.token_ids, r.token_ids) for o, r in zip(out, ref)]
+    # sampled decoding: both ranks of the group must produce identical tokens for the shared batch
+    sp2 = SamplingParams(n=2, max_tokens=12, temperature=1.0, eos_token_id=2, eos_prob_floor=0.05, seed=11)
+    out2 = eng.generate(mine, sp2)
+    allo = [None, None]
+    td.all_gather_object(allo, [o.token_ids for o in out2])
+    assert all(1 <= len(t) <= 12 for t in allo[rank])
+    # weight refresh: after changing the policy weights and sync_weights() the engine must follow
+    with torch.no_grad():
+        for p in model.parameters():
+            p.mul_(0.5)
+    eng.sync_weights()
+    ref3 = RolloutEngine(model, max_num_seqs=4, max_model_len=64, poll_every=4).generate(mine, sp)
+    out3 = eng.generate(mine, sp)
+    assert sum(o.token_ids[:3] == r.token_ids[:3] for o, r in zip(out3, ref3)) >= 3
+    td.barrier()
+    if rank == 0:
+        print("TP_ROLLOUT_OK")
+    td.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -96,15 +96,25 @@ class _PrefillKV:
         from ..ops import cuda as K
 
         e = self.e
-        K.kv_write_prefill(k.contiguous(), v.contiguous(), self.tok_slot, self.tok_pos, e.block_table, e.block_size,
+        if e.tp > 1:  # this rank caches only its own KV heads
+            sl = slice(e.tp_rank * e.hk_local, (e.tp_rank + 1) * e.hk_local)
+            kw, vw = k[:, sl].contiguous(), v[:, sl].contiguous()
+        else:
+            kw, vw = k.contiguous(), v.contiguous()
+        K.kv_write_prefill(kw, vw, self.tok_slot, self.tok_pos, e.block_table, e.block_size,
                            e.k_cache[layer_idx], e.v_cache[layer_idx])
         return K.attention_varlen(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, True)
 
 
 class RolloutEngine:
     def __init__(self, model: CausalLM, max_num_seqs: int = 64, max_model_len: int = 2048, block_size: int = 16,
-                 num_blocks: int | None = None, poll_every: int = 16, use_cuda_graph: bool = True, kv_splits: int = 0):
+                 num_blocks: int | None = None, poll_every: int = 16, use_cuda_graph: bool = True, kv_splits: int = 0,
+                 tp: int = 1, tp_rank: int = 0):
         cfg = model.config
+        if cfg.num_attention_heads % tp or cfg.num_key_value_heads % tp:
+            raise ValueError(f"tensor parallel size {tp} must divide the head counts")
+        self.tp, self.tp_rank = tp, tp_rank
+        self.hq_local, self.hk_local = cfg.num_attention_heads // tp, cfg.num_key_value_heads // tp
         self.model, self.cfg = model, cfg
         self.dev = model.device
         if self.dev.type != "cuda":
@@ -118,7 +128,7 @@ class RolloutEngine:
         self.max_blocks = (max_model_len + block_size - 1) // block_size
         self.num_blocks = num_blocks or max_num_seqs * self.max_blocks
         self.sched = rt.scheduler(max_num_seqs, self.num_blocks, block_size, self.max_blocks)
-        L, Hk, D = cfg.num_hidden_layers, cfg.num_key_value_heads, cfg.head_dim
+        L, Hk, D = cfg.num_hidden_layers, self.hk_local, cfg.head_dim
         dt = torch.bfloat16
         self.k_cache = [torch.zeros(self.num_blocks, block_size, Hk, D, dtype=dt, device=self.dev) for _ in range(L)]
         self.v_cache = [torch.zeros(self.num_blocks, block_size, Hk, D, dtype=dt, device=self.dev) for _ in range(L)]
@@ -135,12 +145,10 @@ class RolloutEngine:
         self.poll_every, self.use_graph = poll_every, use_cuda_graph and not cfg.is_moe
         # enough CTAs for ~4 per SM: the kernel is latency-bound on KV loads, occupancy hides it
         self.kv_splits = kv_splits or max(1, min(8, -(-(4 * 148) // max(1, max_num_seqs * Hk))))
-        self.part_o = torch.empty(max_num_seqs * cfg.num_attention_heads * self.kv_splits * D, dtype=torch.float32,
-                                  device=self.dev)
-        self.part_ml = torch.empty(max_num_seqs * cfg.num_attention_heads * self.kv_splits * 2, dtype=torch.float32,
-                                   device=self.dev)
-        self.q_buf = torch.empty(max_num_seqs, cfg.num_attention_heads, D, dtype=dt, device=self.dev)
-        self.attn_buf = torch.empty(max_num_seqs, cfg.num_attention_heads, D, dtype=dt, device=self.dev)
+        self.part_o = torch.empty(max_num_seqs * self.hq_local * self.kv_splits * D, dtype=torch.float32, device=self.dev)
+        self.part_ml = torch.empty(max_num_seqs * self.hq_local * self.kv_splits * 2, dtype=torch.float32, device=self.dev)
+        self.q_buf = torch.empty(max_num_seqs, self.hq_local, D, dtype=dt, device=self.dev)
+        self.attn_buf = torch.empty(max_num_seqs, self.hq_local, D, dtype=dt, device=self.dev)
         self.seen = None
         self.out_tokens = self.out_logps = None
         self._graph = None

@@ -196,8 +196,20 @@ class OnlineTrainer(Trainer):
                 max_len = a.vllm_max_model_length or (self._max_prompt_len_seen + self.max_completion_length + 8)
                 bs = a.rollout_block_size
                 max_len = (max_len + bs - 1) // bs * bs
-                self._rollout = RolloutEngine(self.model, max_num_seqs=a.per_device_train_batch_size * a.steps_per_generation,
-                                              max_model_len=max_len, block_size=bs, poll_every=a.rollout_poll_every)
+                tp = int(a.vllm_tensor_parallel_size or 1)
+                nseq = a.per_device_train_batch_size * a.steps_per_generation
+                if tp > 1 and D.world_size() > 1:
+                    from ..rollout.tp_engine import TPRolloutEngine
+
+                    if D.world_size() % tp != 0:
+                        raise ValueError(f"vllm_tensor_parallel_size ({tp}) must divide the world size ({D.world_size()})")
+                    groups = [list(range(i, i + tp)) for i in range(0, D.world_size(), tp)]
+                    self._tp_group = D.new_subgroups_by_enumeration(groups)
+                    self._rollout = TPRolloutEngine(self.model, self._tp_group, max_num_seqs=nseq, max_model_len=max_len,
+                                                    block_size=bs, poll_every=a.rollout_poll_every)
+                else:
+                    self._rollout = RolloutEngine(self.model, max_num_seqs=nseq, max_model_len=max_len, block_size=bs,
+                                                  poll_every=a.rollout_poll_every)
             else:
                 from ..rollout.engine import EagerGenerator
 
@@ -240,6 +252,10 @@ class OnlineTrainer(Trainer):
                 uniq.append(p)
                 counts.append(1)
         eng = self._get_rollout()
+        if self.state.global_step != self._last_loaded_step and hasattr(eng, "sync_weights"):
+            with self._profile("sync_weights"):  # trainer -> generator weights (no-op when storage is shared)
+                eng.sync_weights()
+            self._last_loaded_step = self.state.global_step
         with self._profile("rollout.generate"):
             if len(set(counts)) == 1:
                 outs = eng.generate(uniq, self._sampling_params(counts[0]))
