@@ -185,7 +185,7 @@ def main():
     for _ in range(a.warmup):
         one_step()
     K.check_status(dev)
-    gen0 = trainer._rollout.stats["generated_tokens"]
+    gen0 = trainer._total_generated_tokens
     torch.cuda.synchronize()
     D.barrier()
     clocks = ClockSampler(D.local_rank())
@@ -204,8 +204,7 @@ def main():
     D.barrier()
     ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
     D.all_reduce(ms, "max")
-    gen_local = torch.tensor([float(trainer._rollout.stats["generated_tokens"] - gen0)], device=dev)
-    D.all_reduce(gen_local, "sum")
+    gen_local = torch.tensor([float(trainer._total_generated_tokens - gen0)], device=dev)  # already job-wide
     clk = clocks.stop() if rank == 0 else {}
     launches = K.LAUNCHES[0] - launches0
     K.check_status(dev)
@@ -219,7 +218,7 @@ def main():
         # public API: GRPOTrainer.train() for `steps` more optimizer steps, wall clock
         trainer.args.max_steps = trainer.state.global_step + a.steps
         trainer._buffered_inputs = None
-        t_tok0, g0 = trainer._total_train_tokens, trainer._rollout.stats["generated_tokens"]
+        t_tok0, g0 = trainer._total_train_tokens, trainer._total_generated_tokens
         start_step = trainer.state.global_step
 
         torch.cuda.synchronize()
@@ -230,8 +229,7 @@ def main():
         D.barrier()
         dt = torch.tensor([time.perf_counter() - t0], device=dev)
         D.all_reduce(dt, "max")
-        gl = torch.tensor([float(trainer._rollout.stats["generated_tokens"] - g0)], device=dev)
-        D.all_reduce(gl, "sum")
+        gl = torch.tensor([float(trainer._total_generated_tokens - g0)], device=dev)
         e_tokens = float(trainer._total_train_tokens - t_tok0) + float(gl)
         h2d = per_rank // a.num_generations * a.prompt_len * 8 + trainer._rollout.block_table_host.numel() * 4
         e2e = {"value": e_tokens / float(dt), "unit": "tokens/s", "step_s": float(dt) / a.steps,

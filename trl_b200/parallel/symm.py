@@ -76,8 +76,9 @@ def symmetric_available() -> bool:
     if not (D.is_initialized() and torch.cuda.is_available() and D.world_size() > 1):
         return False
     try:
-        import torch.distributed._symmetric_memory  # noqa: F401
+        import importlib
 
+        importlib.import_module("torch.distributed._symmetric_memory")
         return True
     except Exception:
         return False

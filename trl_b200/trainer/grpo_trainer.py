@@ -124,6 +124,8 @@ class GRPOTrainer(OnlineTrainer):
                                                       + comp_lens.sum()).reshape(1)).sum())
         m["num_tokens"].append(float(self._total_train_tokens))
         agg_len = D.gather(comp_lens.float())
+        if mode == "train":  # completion tokens produced by the whole job (each completion counted once)
+            self._total_generated_tokens = getattr(self, "_total_generated_tokens", 0) + int(agg_len.sum())
         m["completions/mean_length"].append(agg_len.mean())
         m["completions/min_length"].append(agg_len.min())
         m["completions/max_length"].append(agg_len.max())
