@@ -97,6 +97,39 @@ def main():
         g = res.clone()
         td.broadcast(g, 0)
         assert torch.equal(g, res)  # bit-identical residual stream on all ranks
+    # ---- all-gather fused into the GEMM ------------------------------------------------------------------
+    from trl_b200.ops.cuda_comm import AgGemmState, ag_gemm
+
+    for (M, N, Kd, extra) in [(512, 1024, 512, 4096), (300, 1536 + 256, 256, 0)]:
+        total = N * Kd + extra
+        total = (total + world * 256 - 1) // (world * 256) * (world * 256)
+        per = total // world
+        ar = SymmArena(total * 2 + 4096, dev)
+        buf, off = ar.carve(total, torch.bfloat16)
+        full = (torch.randn(total, device=dev, generator=torch.Generator(device=dev).manual_seed(42)) * 0.1).to(torch.bfloat16)
+        buf.zero_()
+        buf[rank * per:(rank + 1) * per] = full[rank * per:(rank + 1) * per]  # only the own shard is valid
+        x = torch.randn(M, Kd, device=dev, generator=torch.Generator(device=dev).manual_seed(9)).to(torch.bfloat16)
+        w_off = extra // 2 // 8 * 8
+        st = AgGemmState(dev)
+        torch.cuda.synchronize()
+        td.barrier()
+        for call in range(2):
+            if call == 1:  # second call on the same buffer: remote parts wiped again
+                td.barrier()
+                keep = buf[rank * per:(rank + 1) * per].clone()
+                buf.zero_()
+                buf[rank * per:(rank + 1) * per] = keep
+                torch.cuda.synchronize()
+                td.barrier()
+            y = ag_gemm(x, ar, off, per, total, w_off, N, st)
+            torch.cuda.synchronize()
+            K.check_status(dev)
+            W = full[w_off:w_off + N * Kd].view(N, Kd)
+            want = x.float() @ W.float().t()
+            assert torch.allclose(y.float(), want, atol=3e-2 * want.abs().max().item() + 1e-2, rtol=2e-2), (M, N, Kd, call)
+            assert torch.equal(buf, full), "local buffer not completed by the kernel"
+        td.barrier()
     td.barrier()
     if rank == 0:
         print("COMM_OK multicast=%d" % int(bool(arena.multicast_ptr)))

@@ -43,13 +43,82 @@ struct GemmParams {
   const float* lse;    // [M]  (EPI_DZ)
   const float* grow;   // [M]  dL/dlogp per row (EPI_DZ)
   int* status;
+  // ---- all-gather fused into the GEMM (EPI_STORE only; ag_world == 0 disables) ----
+  // B (the weight) lives at element offset ag_w_off of a bf16 buffer of ag_total elements that every rank
+  // maps; rank r owns elements [r*ag_per, (r+1)*ag_per).  CTAs >= gemm_ctas are copiers: they pull the
+  // remote parts into the local buffer, the weight's 256-row tiles first (arrival counted per tile in
+  // ag_count), then the rest of the buffer.  GEMM CTAs visit N tiles starting at the first locally owned
+  // one and wait (bounded) on ag_count[tile] >= ag_target before the TMA load of a tile with remote rows.
+  int ag_world, ag_rank, gemm_ctas, ag_first_tile;
+  long long ag_per, ag_w_off, ag_total;
+  uint32_t* ag_count;
+  uint32_t ag_target;
+  const __nv_bfloat16* ag_peer[8];
+  __nv_bfloat16* ag_local;
 };
+
+__device__ __forceinline__ int ag_tile(const GemmParams& p, int nt) {
+  return p.ag_world ? (nt + p.ag_first_tile) % p.n_tiles : nt;
+}
 
 __device__ __forceinline__ void item_to_coords(const GemmParams& p, int item, int& m_tile, int& n_begin, int& n_end) {
   m_tile = item % p.m_tiles;
   int split = item / p.m_tiles;
   n_begin = split * p.tiles_per_split;
   n_end = min(n_begin + p.tiles_per_split, p.n_tiles);
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// element range [e0, e1) of the shared buffer covered by weight tile nt
+__device__ __forceinline__ void ag_tile_range(const GemmParams& p, int nt, long long& e0, long long& e1) {
+  e0 = p.ag_w_off + (long long)nt * BN * p.K;
+  const long long end = p.ag_w_off + (long long)p.N * p.K;
+  e1 = e0 + (long long)BN * p.K;
+  if (e1 > end) e1 = end;
+}
+__device__ __forceinline__ bool ag_tile_is_local(const GemmParams& p, int nt) {
+  long long e0, e1;
+  ag_tile_range(p, nt, e0, e1);
+  return e0 / p.ag_per == p.ag_rank && (e1 - 1) / p.ag_per == p.ag_rank;
+}
+
+// Copy [e0, e1) (16-byte aligned element range) from its owners into the local buffer, skipping what this
+// rank owns; this CTA takes slice `part` of `parts`.
+__device__ void ag_copy_range(const GemmParams& p, long long e0, long long e1, int part, int parts) {
+  const long long nvec = (e1 - e0) / 8;
+  const long long per_part = (nvec + parts - 1) / parts;
+  const long long v0 = part * per_part, v1 = min(nvec, v0 + per_part);
+  for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+    const long long e = e0 + v * 8;
+    const int owner = (int)(e / p.ag_per);
+    if (owner == p.ag_rank) continue;
+    *reinterpret_cast<uint4*>(p.ag_local + e) = *reinterpret_cast<const uint4*>(p.ag_peer[owner] + e);
+  }
+}
+
+// Copier CTAs: weight tiles in the order the GEMM CTAs consume them (arrival counted per tile), then the
+// rest of the buffer (the layer's other weights), which only has to be complete when the kernel ends.
+__device__ void ag_copier(const GemmParams& p) {
+  const int part = (int)blockIdx.x, parts = (int)gridDim.x - p.gemm_ctas;
+  for (int i = 0; i < p.n_tiles; ++i) {
+    const int nt = ag_tile(p, i);
+    if (ag_tile_is_local(p, nt)) continue;
+    long long e0, e1;
+    ag_tile_range(p, nt, e0, e1);
+    ag_copy_range(p, e0, e1, part, parts);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) atomicAdd(p.ag_count + nt, 1u);
+  }
+  const long long w_end = p.ag_w_off + (long long)p.N * p.K;
+  ag_copy_range(p, 0, p.ag_w_off, part, parts);
+  ag_copy_range(p, w_end, p.ag_total, part, parts);
+  __threadfence();
 }
 
 template <int EPI>
@@ -69,6 +138,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_items = p.m_tiles * p.n_splits;
+  // copier CTAs take the lowest block indices so that they are scheduled first
+  const int n_cop = p.ag_world > 0 ? (int)gridDim.x - p.gemm_ctas : 0;
+  const bool copier = (int)blockIdx.x < n_cop;
+  const int item_stride = p.ag_world > 0 ? p.gemm_ctas : (int)gridDim.x;
+  const int first_item = copier ? total_items : (int)blockIdx.x - n_cop;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -93,23 +167,42 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (copier) {
+    ag_copier(p);
+  } else if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      for (int item = first_item; item < total_items && ok; item += item_stride) {
         int m_tile, n0, n1;
         item_to_coords(p, item, m_tile, n0, n1);
         for (int nt = n0; nt < n1 && ok; ++nt) {
+          const int nta = ag_tile(p, nt);
+          if (p.ag_world > 0 && !ag_tile_is_local(p, nta)) {
+            // rows of this tile come from peers: wait until every copier has delivered its slice
+            const uint64_t t0 = globaltimer_ns();
+            while ((int32_t)(ld_acquire_gpu_u32(p.ag_count + nta) - p.ag_target) < 0) {
+              if (*abort_flag) { ok = false; break; }
+              if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+                *abort_flag = 1;
+                report_error(p.status, ERR_WAIT_TIMEOUT, 150, nta);
+                ok = false;
+                break;
+              }
+              __nanosleep(32);
+            }
+            if (!ok) break;
+            asm volatile("fence.proxy.async.global;" ::: "memory");  // copier stores (generic proxy) -> TMA reads
+          }
           for (int kb = 0; kb < p.k_blocks; ++kb) {
             if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 100 + stage)) { ok = false; break; }
             uint8_t* sa = tiles + stage * STAGE_BYTES;
             uint8_t* sb = sa + A_BYTES;
             mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
             tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m_tile * BM);
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, nt * BN);
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, nta * BN);
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
         }
@@ -125,7 +218,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      for (int item = first_item; item < total_items && ok; item += item_stride) {
         int m_tile, n0, n1;
         item_to_coords(p, item, m_tile, n0, n1);
         for (int nt = n0; nt < n1 && ok; ++nt) {
@@ -161,7 +254,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     uint32_t acc_phase = 0;
     bool ok = true;
     constexpr float LOG2E = 1.4426950408889634f;
-    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+    for (int item = first_item; item < total_items && ok; item += item_stride) {
       int m_tile, n0, n1;
       item_to_coords(p, item, m_tile, n0, n1);
       const int row = m_tile * BM + row_in_tile;
@@ -179,7 +272,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, 400 + acc)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tacc = tmem_base + (uint32_t)acc * BN + ((uint32_t)(quarter * 32) << 16);
-        const int col0 = nt * BN;
+        const int col0 = ag_tile(p, nt) * BN;
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
           float v[32];
@@ -360,7 +453,15 @@ static int launch_gemm(const void* A, const void* B, GemmParams p, long long lda
     attr_set = true;
   }
   const int items = p.m_tiles * p.n_splits;
-  const int grid = items < trlb_host::sm_count() ? items : trlb_host::sm_count();
+  int grid = items < trlb_host::sm_count() ? items : trlb_host::sm_count();
+  if (p.ag_world > 0) {
+    const int copiers = p.gemm_ctas;  // the caller passed the copier count here
+    int workers = trlb_host::sm_count() - copiers;
+    if (workers > items) workers = items;
+    if (workers < 1) return -103;
+    p.gemm_ctas = workers;
+    grid = workers + copiers;
+  }
   gemm_tn_kernel<EPI><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ta, tb, p);
   return (int)cudaGetLastError();
 }
@@ -417,4 +518,36 @@ TRLB_API int trlb_lmhead_dz(const void* H, const void* W, const long long* label
   p.C = (__nv_bfloat16*)dZ; p.ldc = ldz;
   p.status = status;
   return launch_gemm<EPI_DZ>(H, W, p, ldh, ldw, stream);
+}
+
+// All-gather fused into the GEMM: C[M,N] = A[M,K] . W[N,K]^T where W sits at element offset w_off of a bf16
+// buffer of `total` elements that every rank maps (peers[r] = rank r's address of the buffer, peers[rank] is
+// local) and rank r holds valid data only for elements [r*per, (r+1)*per).  On return (stream order) the
+// whole local buffer is complete.  ag_count: zero-initialised uint32 per N tile (256 rows), reused across
+// calls with a target that grows by `copiers` per call (pass the call number in `call_index`, from 1).
+TRLB_API int trlb_ag_gemm_bf16_tn(const void* A, void* C, const void* bias, int M, int N, int K, long long lda,
+                                  long long ldc, const unsigned long long* peers, int rank, int world, long long per,
+                                  long long w_off, long long total, unsigned* ag_count, int call_index, int copiers,
+                                  int* status, cudaStream_t stream) {
+  if (world < 1 || world > 8 || per % 8 != 0 || w_off % 8 != 0 || total % 8 != 0 || (long long)N * K % 8 != 0) return -110;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.C = (__nv_bfloat16*)C; p.ldc = ldc; p.bias = (const __nv_bfloat16*)bias;
+  p.status = status;
+  p.ag_world = world; p.ag_rank = rank; p.ag_per = per; p.ag_w_off = w_off; p.ag_total = total;
+  p.ag_count = ag_count; p.ag_target = (unsigned)call_index * (unsigned)copiers;
+  for (int i = 0; i < 8; ++i) p.ag_peer[i] = i < world ? reinterpret_cast<const __nv_bfloat16*>(peers[i]) : nullptr;
+  p.ag_local = reinterpret_cast<__nv_bfloat16*>(peers[rank]);
+  p.gemm_ctas = copiers;
+  // first locally owned tile of W (or tile 0 when this rank owns none of W)
+  const long long own0 = (long long)rank * per, own1 = own0 + per, wend = w_off + (long long)N * K;
+  long long first = 0;
+  if (own1 > w_off && own0 < wend) {
+    const long long s = own0 > w_off ? own0 - w_off : 0;
+    first = (s + (long long)BN * K - 1) / ((long long)BN * K);
+  }
+  const int n_tiles = (N + BN - 1) / BN;
+  p.ag_first_tile = (int)(first % n_tiles);
+  const void* B = reinterpret_cast<const __nv_bfloat16*>(peers[rank]) + w_off;
+  return launch_gemm<EPI_STORE>(A, B, p, lda, (long long)K, stream);
 }
