@@ -53,6 +53,8 @@ struct GemmParams {
   long long ag_per, ag_w_off, ag_total;
   uint32_t* ag_count;
   uint32_t ag_target;
+  uint32_t* ag_rest_ctr;   // dynamic chunk counter for the rest of the buffer
+  uint32_t ag_rest_base;   // counter value at which this call's chunk 0 starts
   const __nv_bfloat16* ag_peer[8];
   __nv_bfloat16* ag_local;
 };
@@ -87,38 +89,152 @@ __device__ __forceinline__ bool ag_tile_is_local(const GemmParams& p, int nt) {
   return e0 / p.ag_per == p.ag_rank && (e1 - 1) / p.ag_per == p.ag_rank;
 }
 
-// Copy [e0, e1) (16-byte aligned element range) from its owners into the local buffer, skipping what this
-// rank owns; this CTA takes slice `part` of `parts`.
-__device__ void ag_copy_range(const GemmParams& p, long long e0, long long e1, int part, int parts) {
-  const long long nvec = (e1 - e0) / 8;
-  const long long per_part = (nvec + parts - 1) / parts;
-  const long long v0 = part * per_part, v1 = min(nvec, v0 + per_part);
-  for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
-    const long long e = e0 + v * 8;
-    const int owner = (int)(e / p.ag_per);
-    if (owner == p.ag_rank) continue;
-    *reinterpret_cast<uint4*>(p.ag_local + e) = *reinterpret_cast<const uint4*>(p.ag_peer[owner] + e);
+// ---- copier CTAs: peer -> shared memory -> local global memory with bulk async copies ----------------
+// One thread drives a ring of COPY_STAGES x COPY_CHUNK bytes in the (otherwise unused) tile ring of this CTA:
+// cp.async.bulk loads from the owner's memory complete on an mbarrier, cp.async.bulk stores write the local
+// buffer.  About 160 KB are in flight per copier CTA, which is what NVLink latency needs; no registers or
+// warps are spent on the data.  Weight tiles are signalled (arrival counter per tile) once the bulk group
+// holding their last chunk has completed.
+constexpr int COPY_STAGES = 6;
+constexpr uint32_t COPY_CHUNK = 32768;
+
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+
+struct CopyRing {
+  uint8_t* smem;
+  uint64_t* bars;
+  int issued = 0;     // loads issued
+  int stored = 0;     // stores issued (= bulk groups committed)
+  // pending loads (ring order)
+  __nv_bfloat16* dst[COPY_STAGES];
+  uint32_t bytes[COPY_STAGES];
+  int tile_of[COPY_STAGES];  // weight tile to signal after this chunk's store, or -1
+};
+
+// Signals are delayed until the store's bulk group has completed: group g is known complete once
+// wait_group<k> ran after committing group g + k.
+struct PendingSignal { int group, tile; };
+
+__device__ bool ag_copy_stream(const GemmParams& p, CopyRing& R, PendingSignal* sig, int& n_sig, long long e0,
+                               long long e1, int tile, volatile int* abort_flag) {
+  // splits [e0, e1) into chunks that do not cross an owner boundary; own data is skipped
+  long long e = e0;
+  while (true) {
+    const bool more = e < e1;
+    // keep COPY_STAGES - 2 loads in flight; drain when there is nothing more to issue
+    if (more && R.issued - R.stored < COPY_STAGES - 1) {
+      const int owner = (int)(e / p.ag_per);
+      long long lim = min(e1, (long long)(owner + 1) * p.ag_per);
+      long long n = min(lim - e, (long long)(COPY_CHUNK / 2));
+      if (owner != p.ag_rank) {
+        const int s = R.issued % COPY_STAGES;
+        // stage s was used by chunk issued - COPY_STAGES: its store (group issued - COPY_STAGES) must have
+        // finished reading shared memory; at most 2 groups are younger than it
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        mbar_expect_tx(&R.bars[s], (uint32_t)(n * 2));
+        bulk_load(R.smem + (size_t)s * COPY_CHUNK, p.ag_peer[owner] + e, (uint32_t)(n * 2), &R.bars[s]);
+        R.dst[s] = p.ag_local + e;
+        R.bytes[s] = (uint32_t)(n * 2);
+        R.tile_of[s] = (e + n >= e1) ? tile : -1;
+        ++R.issued;
+      } else if (e + n >= e1 && tile >= 0) {
+        // the tail of this tile slice is local data: signal after everything issued so far has landed
+        sig[n_sig++] = PendingSignal{R.issued - 1, tile};
+      }
+      e += n;
+      continue;
+    }
+    if (!more) return true;  // loads may stay in flight: the next range (or ag_drain) continues the ring
+    {
+      const int s = R.stored % COPY_STAGES;
+      if (!mbar_wait(&R.bars[s], (uint32_t)((R.stored / COPY_STAGES) & 1), abort_flag, p.status, 160)) return false;
+      bulk_store(R.dst[s], R.smem + (size_t)s * COPY_CHUNK, R.bytes[s]);
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      if (R.tile_of[s] >= 0) sig[n_sig++] = PendingSignal{R.stored, R.tile_of[s]};
+      ++R.stored;
+      asm volatile("cp.async.bulk.wait_group 2;" ::: "memory");  // groups <= stored - 3 are complete
+      int k = 0;
+      for (int i = 0; i < n_sig; ++i) {
+        if (sig[i].group <= R.stored - 3) {
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          __threadfence();
+          atomicAdd(p.ag_count + sig[i].tile, 1u);
+        } else {
+          sig[k++] = sig[i];
+        }
+      }
+      n_sig = k;
+    }
+  }
+  return true;
+}
+
+// Store every pending load, wait for all stores, publish the remaining tile arrivals.
+__device__ void ag_drain(const GemmParams& p, CopyRing& R, PendingSignal* sig, int& n_sig, volatile int* abort_flag,
+                         bool ok) {
+  while (ok && R.stored < R.issued) {
+    const int s = R.stored % COPY_STAGES;
+    if (!mbar_wait(&R.bars[s], (uint32_t)((R.stored / COPY_STAGES) & 1), abort_flag, p.status, 161)) { ok = false; break; }
+    bulk_store(R.dst[s], R.smem + (size_t)s * COPY_CHUNK, R.bytes[s]);
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    if (R.tile_of[s] >= 0) sig[n_sig++] = PendingSignal{R.stored, R.tile_of[s]};
+    ++R.stored;
+  }
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+  __threadfence();
+  for (int i = 0; i < n_sig; ++i) atomicAdd(p.ag_count + sig[i].tile, 1u);
+  n_sig = 0;
+}
+
+// The rest of the buffer (the layer's other weights) is cut into 256 KB work items handed out by an atomic
+// counter, so dedicated copiers and GEMM CTAs that have run out of tiles share it evenly.
+constexpr long long REST_ITEM = 131072;  // elements
+
+__device__ bool ag_help_rest(const GemmParams& p, CopyRing& R, PendingSignal* sig, int& n_sig, volatile int* abort_flag) {
+  const long long w_end = p.ag_w_off + (long long)p.N * p.K;
+  const long long n_a = (p.ag_w_off + REST_ITEM - 1) / REST_ITEM, n_b = (p.ag_total - w_end + REST_ITEM - 1) / REST_ITEM;
+  while (true) {
+    const long long id = (long long)(atomicAdd(p.ag_rest_ctr, 1u) - p.ag_rest_base);
+    if (id >= n_a + n_b) return true;
+    long long e0, e1;
+    if (id < n_a) { e0 = id * REST_ITEM; e1 = min(p.ag_w_off, e0 + REST_ITEM); }
+    else { e0 = w_end + (id - n_a) * REST_ITEM; e1 = min(p.ag_total, e0 + REST_ITEM); }
+    if (!ag_copy_stream(p, R, sig, n_sig, e0, e1, -1, abort_flag)) return false;
   }
 }
 
-// Copier CTAs: weight tiles in the order the GEMM CTAs consume them (arrival counted per tile), then the
-// rest of the buffer (the layer's other weights), which only has to be complete when the kernel ends.
-__device__ void ag_copier(const GemmParams& p) {
+__device__ void ag_copier(const GemmParams& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag) {
+  if (threadIdx.x != 0) return;
   const int part = (int)blockIdx.x, parts = (int)gridDim.x - p.gemm_ctas;
-  for (int i = 0; i < p.n_tiles; ++i) {
+  CopyRing R;
+  R.smem = smem;
+  R.bars = bars;
+  PendingSignal sig[16];
+  int n_sig = 0;
+  bool ok = true;
+  for (int i = 0; i < p.n_tiles && ok; ++i) {
     const int nt = ag_tile(p, i);
     if (ag_tile_is_local(p, nt)) continue;
     long long e0, e1;
     ag_tile_range(p, nt, e0, e1);
-    ag_copy_range(p, e0, e1, part, parts);
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) atomicAdd(p.ag_count + nt, 1u);
+    const long long nvec = (e1 - e0) / 8, per_part = (nvec + parts - 1) / parts;
+    const long long v0 = min(nvec, part * per_part), v1 = min(nvec, v0 + per_part);
+    if (v1 > v0) ok = ag_copy_stream(p, R, sig, n_sig, e0 + v0 * 8, e0 + v1 * 8, nt, abort_flag);
+    else sig[n_sig++] = PendingSignal{R.issued - 1, nt};  // empty slice: still counts as an arrival
   }
-  const long long w_end = p.ag_w_off + (long long)p.N * p.K;
-  ag_copy_range(p, 0, p.ag_w_off, part, parts);
-  ag_copy_range(p, w_end, p.ag_total, part, parts);
-  __threadfence();
+  if (ok) ok = ag_help_rest(p, R, sig, n_sig, abort_flag);
+  ag_drain(p, R, sig, n_sig, abort_flag, ok);
 }
 
 template <int EPI>
@@ -168,7 +284,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
 
   if (copier) {
-    ag_copier(p);
+    ag_copier(p, tiles, bars, abort_flag);
   } else if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
@@ -381,6 +497,24 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   // ---------------- teardown (also the abort path) ----------------
   __syncthreads();
+  if (p.ag_world > 0 && !copier && !*abort_flag) {
+    // this CTA has no tiles left: its tile ring becomes a copy ring and it joins the gather
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < COPY_STAGES; ++s) {
+        asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(&bars[s])) : "memory");
+        mbar_init(&bars[s], 1);
+      }
+      mbar_fence_init();
+      CopyRing R;
+      R.smem = tiles;
+      R.bars = bars;
+      PendingSignal sig[16];
+      int n_sig = 0;
+      const bool ok = ag_help_rest(p, R, sig, n_sig, abort_flag);
+      ag_drain(p, R, sig, n_sig, abort_flag, ok);
+    }
+    __syncthreads();
+  }
   if (*abort_flag) {
     // give TMA copies that may still be in flight time to land before shared memory is released
     const uint64_t t0 = globaltimer_ns();
@@ -536,6 +670,17 @@ TRLB_API int trlb_ag_gemm_bf16_tn(const void* A, void* C, const void* bias, int 
   p.status = status;
   p.ag_world = world; p.ag_rank = rank; p.ag_per = per; p.ag_w_off = w_off; p.ag_total = total;
   p.ag_count = ag_count; p.ag_target = (unsigned)call_index * (unsigned)copiers;
+  {
+    // the last word of the counter array hands out rest-of-buffer work items; every CTA of the grid makes one
+    // failing grab at the end, so a call advances the counter by items + grid
+    const long long wend0 = w_off + (long long)N * K;
+    const long long items = (w_off + 131071) / 131072 + (total - wend0 + 131071) / 131072;
+    int workers = trlb_host::sm_count() - copiers;
+    const int tiles_mn = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    if (workers > tiles_mn) workers = tiles_mn;
+    p.ag_rest_ctr = ag_count + 4095;
+    p.ag_rest_base = (unsigned)(call_index - 1) * (unsigned)(items + workers + copiers);
+  }
   for (int i = 0; i < 8; ++i) p.ag_peer[i] = i < world ? reinterpret_cast<const __nv_bfloat16*>(peers[i]) : nullptr;
   p.ag_local = reinterpret_cast<__nv_bfloat16*>(peers[rank]);
   p.gemm_ctas = copiers;
