@@ -670,17 +670,11 @@ TRLB_API int trlb_ag_gemm_bf16_tn(const void* A, void* C, const void* bias, int 
   p.status = status;
   p.ag_world = world; p.ag_rank = rank; p.ag_per = per; p.ag_w_off = w_off; p.ag_total = total;
   p.ag_count = ag_count; p.ag_target = (unsigned)call_index * (unsigned)copiers;
-  {
-    // the last word of the counter array hands out rest-of-buffer work items; every CTA of the grid makes one
-    // failing grab at the end, so a call advances the counter by items + grid
-    const long long wend0 = w_off + (long long)N * K;
-    const long long items = (w_off + 131071) / 131072 + (total - wend0 + 131071) / 131072;
-    int workers = trlb_host::sm_count() - copiers;
-    const int tiles_mn = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    if (workers > tiles_mn) workers = tiles_mn;
-    p.ag_rest_ctr = ag_count + 4095;
-    p.ag_rest_base = (unsigned)(call_index - 1) * (unsigned)(items + workers + copiers);
-  }
+  // the last word of the counter array hands out rest-of-buffer work items; zeroed (stream order) per call
+  p.ag_rest_ctr = ag_count + 4095;
+  p.ag_rest_base = 0;
+  if ((N + BN - 1) / BN > 4095) return -111;
+  if (cudaMemsetAsync(p.ag_rest_ctr, 0, sizeof(unsigned), stream) != cudaSuccess) return -112;
   for (int i = 0; i < 8; ++i) p.ag_peer[i] = i < world ? reinterpret_cast<const __nv_bfloat16*>(peers[i]) : nullptr;
   p.ag_local = reinterpret_cast<__nv_bfloat16*>(peers[rank]);
   p.gemm_ctas = copiers;

@@ -301,10 +301,15 @@ class Trainer:
         a = self.args
         mode = a.shard_mode
         if mode == "full_shard" and D.world_size() > 1:
-            from ..parallel.fullshard import FullShardEngine
+            from ..parallel.symm import symmetric_available
 
-            return FullShardEngine(self.model, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
-                                   weight_decay=a.weight_decay, offload_activations=a.activation_offloading)
+            first = next(self.model.parameters())
+            if first.is_cuda and first.dtype == torch.bfloat16 and symmetric_available():
+                from ..parallel.fullshard import FullShardEngine
+
+                return FullShardEngine(self.model, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
+                                       weight_decay=a.weight_decay)
+            # CPU / fp32: same sharding of gradients and optimizer state through the backend collectives
         return TrainEngine(self.model, mode=mode, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
                            weight_decay=a.weight_decay)
 

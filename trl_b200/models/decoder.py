@@ -141,7 +141,12 @@ class DecoderLayer(nn.Module):
     def attn_block(self, x, ctx: SeqCtx):
         c = self.cfg
         T = x.shape[0]
-        qkv = ops.linear(x, self.qkv_proj, self.qkv_bias)
+        gather = getattr(self, "_shard_gather", None)
+        if gather is not None and x.is_cuda:
+            # full-shard engine: this GEMM also pulls the layer's missing parameter shards over NVLink
+            qkv = gather.qkv(x, self.qkv_proj, self.qkv_bias)
+        else:
+            qkv = ops.linear(x, self.qkv_proj, self.qkv_bias)
         qkv = self._lora_add(qkv, x, ("q_proj", "k_proj", "v_proj"))
         q = qkv[:, : c.q_size].reshape(T, c.num_attention_heads, c.head_dim)
         k = qkv[:, c.q_size: c.q_size + c.kv_size].reshape(T, c.num_key_value_heads, c.head_dim)

@@ -254,6 +254,8 @@ class OnlineTrainer(Trainer):
         eng = self._get_rollout()
         if self.state.global_step != self._last_loaded_step and hasattr(eng, "sync_weights"):
             with self._profile("sync_weights"):  # trainer -> generator weights (no-op when storage is shared)
+                if getattr(self, "engine", None) is not None and hasattr(self.engine, "gather_full_params"):
+                    self.engine.gather_full_params()  # full-shard: the generator reads the buffers directly
                 eng.sync_weights()
             self._last_loaded_step = self.state.global_step
         with self._profile("rollout.generate"):
