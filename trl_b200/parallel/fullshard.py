@@ -44,8 +44,12 @@ class _AgLinearFn(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
             x2 = x2.contiguous()
-        y = ag_gemm(x2, gather.arena, gather.byte_offset, gather.per, gather.total, gather.w_off, weight.shape[0],
-                    gather.state, bias=bias)
+        if gather.fresh:  # later micro-batches and the recompute in backward: the buffer is still complete
+            y = x2 @ weight.t()
+        else:
+            y = ag_gemm(x2, gather.arena, gather.byte_offset, gather.per, gather.total, gather.w_off, weight.shape[0],
+                        gather.state, bias=None)
+            gather.fresh = True
         ctx.save_for_backward(x2, weight)
         ctx.has_bias = bias is not None
         ctx.shape = x.shape
@@ -69,9 +73,12 @@ class LayerGather:
 
         self.arena, self.byte_offset, self.per, self.total, self.w_off = arena, byte_offset, per, total, w_off
         self.state = AgGemmState(device, copiers=copiers)
+        self.fresh = False  # True from the first gather after an optimizer step until the next step
 
     def qkv(self, x, weight, bias):
-        return _AgLinearFn.apply(x, weight, bias, self)
+        # one autograd node on both paths (gathering or not), so activation checkpointing sees the same graph
+        y = _AgLinearFn.apply(x, weight, None, self)
+        return y if bias is None else y + bias  # the bias lives in the vector bucket, complete since the last step
 
 
 class FullShardEngine(TrainEngine):
@@ -109,6 +116,9 @@ class FullShardEngine(TrainEngine):
                 K.shard_allgather(pa, self._offsets[key], b.hi - b.lo, self._sync, use_multimem=False)
             else:
                 torch.distributed.all_gather_into_tensor(b.flat_param, b.flat_param[b.lo:b.hi].clone(), group=self.group)
+        for layer in getattr(self.model, "layers", []):
+            if getattr(layer, "_shard_gather", None) is not None:
+                layer._shard_gather.fresh = False
         if self.poison:  # prove that nothing reads a stale remote slice
             for b in self._layer_buckets:
                 b.flat_param[:b.lo].fill_(float("nan"))  # the owned slice is never touched: peers may be reading it
@@ -122,6 +132,9 @@ class FullShardEngine(TrainEngine):
         for b in self._layer_buckets:
             key = ("param", b.name, str(b.params[0].dtype))
             K.shard_allgather(pa, self._offsets[key], b.hi - b.lo, self._sync, use_multimem=False)
+        for layer in getattr(self.model, "layers", []):
+            if getattr(layer, "_shard_gather", None) is not None:
+                layer._shard_gather.fresh = True
 
     def _step_fused(self, lr, max_grad_norm):
         from ..ops import cuda as K
