@@ -260,6 +260,10 @@ def main():
                 keys = sorted({k for h in hist for k in h if k.startswith("profiling/") or k == "step_time"})
                 line["phases_s"] = {k.replace("profiling/Time taken: GRPOTrainer.", ""): round(
                     sum(h.get(k, 0.0) for h in hist[-a.steps:]) / max(1, len(hist[-a.steps:])), 3) for k in keys}
+        rs = getattr(trainer._rollout, "stats", None)
+        if rs and "t_decode" in rs:  # only with TRL_B200_ROLLOUT_TIMING=1 (diagnostic: it adds host syncs)
+            line["rollout_sections_s_total"] = {k: round(v, 3) for k, v in rs.items() if k.startswith("t_")}
+            line["rollout_decode_steps_total"] = rs.get("decode_steps")
         print(json.dumps(line))
     D.barrier()
     if D.is_initialized():

@@ -60,7 +60,8 @@ def test_sampler_matches_distribution_and_logprob():
     assert (tok.long() == row.argmax()).all()
 
 
-def test_engine_greedy_matches_eager_generator():
+@pytest.mark.parametrize("block_size", [16, None])  # None: 64-token pages + tensor-core decode attention
+def test_engine_greedy_matches_eager_generator(block_size):
     from trl_b200.rollout.engine import EagerGenerator, RolloutEngine
     from trl_b200.rollout.sampling import SamplingParams
     from trl_b200.testing import make_tiny_model
@@ -68,9 +69,10 @@ def test_engine_greedy_matches_eager_generator():
     model = make_tiny_model("tiny-qwen2", dtype=torch.bfloat16, device="cuda", hidden_size=256, num_attention_heads=2,
                             num_key_value_heads=1, head_dim=128, intermediate_size=512)
     torch.manual_seed(0)
-    prompts = [torch.randint(5, 1000, (n,)).tolist() for n in (5, 23, 16, 40)]
+    prompts = [torch.randint(5, 1000, (n,)).tolist() for n in (5, 70, 16, 130)]
     sp = SamplingParams(n=2, max_tokens=12, greedy=True, temperature=1.0, eos_token_id=2)
-    eng = RolloutEngine(model, max_num_seqs=4, max_model_len=64, block_size=16, poll_every=4)
+    eng = RolloutEngine(model, max_num_seqs=4, max_model_len=192, block_size=block_size, poll_every=4)
+    assert eng.attn_tc == (block_size is None)
     outs = eng.generate(prompts, sp)
     ref = EagerGenerator(model).generate(prompts, sp)
     assert len(outs) == 8
@@ -81,19 +83,49 @@ def test_engine_greedy_matches_eager_generator():
             assert max(abs(a - b) for a, b in zip(o.logprobs, r.logprobs)) < 0.15
 
 
-def test_engine_sampling_with_shared_prefix_and_continuous_batching():
+@pytest.mark.parametrize("block_size", [16, None])
+def test_engine_sampling_with_shared_prefix_and_continuous_batching(block_size):
     from trl_b200.rollout.engine import RolloutEngine
     from trl_b200.rollout.sampling import SamplingParams
     from trl_b200.testing import make_tiny_model
 
     model = make_tiny_model("tiny-qwen2", dtype=torch.bfloat16, device="cuda", hidden_size=256, num_attention_heads=2,
                             num_key_value_heads=1, head_dim=128, intermediate_size=512)
-    prompts = [list(range(10, 10 + n)) for n in (7, 16, 33)]
+    prompts = [list(range(10, 10 + n)) for n in (7, 16, 33 if block_size else 90)]
     sp = SamplingParams(n=4, max_tokens=20, temperature=1.0, eos_token_id=2, eos_prob_floor=0.1, seed=5)
-    eng = RolloutEngine(model, max_num_seqs=5, max_model_len=64, block_size=16, poll_every=4)  # 12 requests > 5 slots
+    eng = RolloutEngine(model, max_num_seqs=5, max_model_len=128, block_size=block_size, poll_every=4)  # 12 requests > 5 slots
     outs = eng.generate(prompts, sp)
     assert len(outs) == 12 and all(o is not None for o in outs)
     assert all(1 <= len(o.token_ids) <= 20 and len(o.logprobs) == len(o.token_ids) for o in outs)
     assert any(o.finish_reason == "stop" for o in outs)
     assert eng.sched.num_free_blocks == eng.num_blocks  # everything released
     assert len({tuple(o.token_ids) for o in outs[:4]}) > 1  # samples of one prompt differ
+
+
+@pytest.mark.parametrize("B", [64, 16])  # 2 and 8 CTAs per row
+def test_split_sampler_matches_distribution_and_logprob(B):
+    from trl_b200.ops import cuda as K
+    from trl_b200.rollout.sampling import SamplingParams, process_logits
+
+    torch.manual_seed(0)
+    V = 1024
+    row = (torch.randn(V, device="cuda") * 3).to(torch.bfloat16)
+    logits = row[None].repeat(B, 1).contiguous()
+    sp = SamplingParams(temperature=0.7, eos_token_id=5, eos_prob_floor=0.1)
+    ref_logp = torch.log_softmax(process_logits(row[None].float(), sp), -1)[0]
+    tok = torch.full((B,), -1, dtype=torch.int32, device="cuda")
+    lp = torch.empty(B, dtype=torch.float32, device="cuda")
+    step = torch.zeros(1, dtype=torch.int32, device="cuda")
+    counts = torch.zeros(V, device="cuda")
+    n_calls = 4096 // B
+    for i in range(n_calls):
+        step.fill_(i)
+        K.sample_tokens(logits, 1 / sp.temperature, 0.0, sp.eos_token_id, sp.eos_prob_floor, 77, step, False, tok, lp)
+        assert 0 <= int(tok.min()) and int(tok.max()) < V  # checked on the host before it is used as an index
+        assert torch.allclose(lp, ref_logp[tok.long()], atol=2e-3)
+        counts += torch.bincount(tok.long(), minlength=V).float()
+    freq = counts / (B * n_calls)
+    assert (freq - ref_logp.exp()).abs().max() < 0.03
+    assert abs(freq[5].item() - max(0.1, ref_logp.exp()[5].item())) < 0.03
+    K.sample_tokens(logits, 1.0, 0.0, None, 0.0, 0, step, True, tok, lp)
+    assert (tok.long() == row.float().argmax()).all()

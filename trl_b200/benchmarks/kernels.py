@@ -121,7 +121,21 @@ def main():
         ms = timeit(lambda: K.paged_decode_attn(q, kc, vc, lens, None, table, bs, 1 / math.sqrt(D), splits, po, pml, o),
                     a.iters, a.warmup)
         byt = 2.0 * a.batch * a.ctx * Hk * D * 2
-        out.update(batch=a.batch, ctx=a.ctx, splits=splits, ms=ms, gbs=byt / ms / 1e6, frac_of_copy_bw=byt / ms / 1e6 / hbm)
+        out.update(batch=a.batch, ctx=a.ctx, splits=splits, cuda_core_ms=ms, cuda_core_frac_of_copy_bw=byt / ms / 1e6 / hbm)
+        # tensor-core kernel: 64-token pages, V transposed inside a page
+        bs2 = 64
+        nb2 = a.batch * ((a.ctx + bs2) // bs2 + 1)
+        kc2 = torch.randn(nb2, bs2, Hk, D, device=dev, dtype=torch.bfloat16)
+        vt2 = torch.randn(nb2, Hk, D, bs2, device=dev, dtype=torch.bfloat16)
+        table2 = torch.randperm(nb2, device=dev).reshape(a.batch, nb2 // a.batch).to(torch.int32)
+        for sp in sorted({1, 2, splits}):
+            po2 = torch.empty(a.batch * Hq * sp * D, device=dev)
+            pml2 = torch.empty(a.batch * Hq * sp * 2, device=dev)
+            ms2 = timeit(lambda: K.paged_decode_attn_tc(q, kc2, vt2, lens, None, table2, 1 / math.sqrt(D), sp, po2, pml2, o),
+                         a.iters, a.warmup)
+            out[f"tcgen05_splits{sp}_ms"] = ms2
+            out[f"tcgen05_splits{sp}_frac_of_copy_bw"] = byt / ms2 / 1e6 / hbm
+        K.check_status(dev)
     elif a.kernel == "rmsnorm":
         x = torch.randn(a.t, a.h, device=dev, dtype=torch.bfloat16)
         w = torch.ones(a.h, device=dev, dtype=torch.bfloat16)

@@ -19,7 +19,8 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, long
                                      const int* __restrict__ seq_lens, const int* __restrict__ slot_ids,
                                      const int* __restrict__ block_table, int max_blocks, int block_size,
                                      __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ kc,
-                                     __nv_bfloat16* __restrict__ vc, int B, int Hq, int Hk, int D, float log2_theta) {
+                                     __nv_bfloat16* __restrict__ vc, int B, int Hq, int Hk, int D, float log2_theta,
+                                     int v_t) {
   const int half = D >> 1;
   const int per_tok = (Hq + 2 * Hk) * half;
   const long long total = (long long)B * per_tok;
@@ -43,6 +44,11 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, long
       __nv_bfloat16* dst = head < Hq ? q_out + ((size_t)b * Hq + head) * D : kc + (cache_row + (head - Hq)) * D;
       dst[f] = __float2bfloat16(o0);
       dst[half + f] = __float2bfloat16(o1);
+    } else if (v_t) {
+      // V transposed inside the page: [block, head, dim, token]
+      __nv_bfloat16* dst = vc + (((size_t)blk * Hk + (head - Hq - Hk)) * D) * block_size + pos % block_size;
+      dst[(size_t)f * block_size] = src[f];
+      dst[(size_t)(half + f) * block_size] = src[half + f];
     } else {
       __nv_bfloat16* dst = vc + (cache_row + (head - Hq - Hk)) * D;
       dst[f] = src[f];
@@ -57,7 +63,7 @@ __global__ void kv_write_prefill_kernel(const __nv_bfloat16* __restrict__ k, con
                                         long long k_stride, long long v_stride, const int* __restrict__ tok_slot,
                                         const int* __restrict__ tok_pos, const int* __restrict__ block_table,
                                         int max_blocks, int block_size, __nv_bfloat16* __restrict__ kc,
-                                        __nv_bfloat16* __restrict__ vc, int T, int Hk, int D) {
+                                        __nv_bfloat16* __restrict__ vc, int T, int Hk, int D, int v_t) {
   const int vec_per_tok = Hk * D / 8;
   const long long total = (long long)T * vec_per_tok;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
@@ -68,7 +74,16 @@ __global__ void kv_write_prefill_kernel(const __nv_bfloat16* __restrict__ k, con
     const int blk = block_table[(size_t)slot * max_blocks + pos / block_size];
     const size_t row = ((size_t)blk * block_size + pos % block_size) * Hk * D;
     reinterpret_cast<uint4*>(kc + row)[e] = reinterpret_cast<const uint4*>(k + (size_t)t * k_stride)[e];
-    reinterpret_cast<uint4*>(vc + row)[e] = reinterpret_cast<const uint4*>(v + (size_t)t * v_stride)[e];
+    if (!v_t) {
+      reinterpret_cast<uint4*>(vc + row)[e] = reinterpret_cast<const uint4*>(v + (size_t)t * v_stride)[e];
+    } else {
+      const uint4 u = reinterpret_cast<const uint4*>(v + (size_t)t * v_stride)[e];
+      const __nv_bfloat16* vals = reinterpret_cast<const __nv_bfloat16*>(&u);
+      const int h = (e * 8) / D, d0 = (e * 8) % D;
+      __nv_bfloat16* dst = vc + (((size_t)blk * Hk + h) * D + d0) * block_size + pos % block_size;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dst[(size_t)i * block_size] = vals[i];
+    }
   }
 }
 
@@ -178,6 +193,105 @@ sample_kernel(const T* __restrict__ logits, long long row_stride, int V, float i
   }
 }
 
+// Single-pass sampler for the common case (bf16 logits, no min-p): gridDim.y CTAs share a row, each keeps an
+// online (max, sum-exp) and its Gumbel-max candidate over its slice of the vocabulary; the CTA that arrives
+// last on the row's counter merges the partials, applies the EOS floor, scores the EOS column and writes the
+// token and its log-prob.  The counter is left at zero for the next call.
+__device__ __forceinline__ float uniform01_pre(uint32_t base, uint32_t col) {
+  uint32_t h = hash_u32(base ^ hash_u32(col * 0x85EBCA6BU + 0x165667B1U));
+  h = hash_u32(h + col);
+  return ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
+}
+
+__global__ void __launch_bounds__(512)
+sample_split_kernel(const __nv_bfloat16* __restrict__ logits, long long row_stride, int V, float inv_temp, int eos_id,
+                    float eos_floor, uint32_t seed, const int* __restrict__ step_ptr, int greedy,
+                    float4* __restrict__ part, int* __restrict__ part_i, unsigned* __restrict__ counter,
+                    int* __restrict__ out_tok, float* __restrict__ out_logp) {
+  const int row = blockIdx.x, sp = blockIdx.y, S = gridDim.y;
+  const __nv_bfloat16* z = logits + (size_t)row * row_stride;
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, nw = blockDim.x >> 5;
+  const uint32_t step = step_ptr ? (uint32_t)(*step_ptr) : 0u;
+  const uint32_t base = seed ^ hash_u32(step * 0x9E3779B9U + (uint32_t)row);
+  const int nvec = V >> 3, per = (nvec + S - 1) / S;
+  const int v0 = sp * per, v1 = min(nvec, v0 + per);
+  float m = -INFINITY, se = 0.f, best = -INFINITY, best_z = 0.f;
+  int best_i = -1;
+  for (int i = v0 + tid; i < v1; i += blockDim.x) {
+    const uint4 u = reinterpret_cast<const uint4*>(z)[i];
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float2 f = unpack_bf16(w[k >> 1]);
+      const float x = ((k & 1) ? f.y : f.x) * inv_temp;
+      const int col = i * 8 + k;
+      if (col == eos_id || x == -INFINITY) continue;
+      if (x > m) { se = se * __expf(m - x) + 1.f; m = x; } else { se += __expf(x - m); }
+      const float key = greedy ? x : x - __logf(-__logf(uniform01_pre(base, (uint32_t)col)));
+      if (key > best) { best = key; best_i = col; best_z = x; }
+    }
+  }
+  // block reduction
+  __shared__ float sh_m[16], sh_s[16], sh_b[16], sh_z[16];
+  __shared__ int sh_i[16];
+  __shared__ int is_last;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, m, o), os = __shfl_xor_sync(0xffffffffu, se, o);
+    const float nm = fmaxf(m, om);
+    se = (nm == -INFINITY) ? 0.f : se * __expf(m - nm) + os * __expf(om - nm);
+    m = nm;
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o), oz = __shfl_xor_sync(0xffffffffu, best_z, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ob > best || (ob == best && oi >= 0 && (best_i < 0 || oi < best_i))) { best = ob; best_i = oi; best_z = oz; }
+  }
+  if (lane == 0) { sh_m[wid] = m; sh_s[wid] = se; sh_b[wid] = best; sh_z[wid] = best_z; sh_i[wid] = best_i; }
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < nw; ++w) {
+      const float nm = fmaxf(m, sh_m[w]);
+      se = (nm == -INFINITY) ? 0.f : se * __expf(m - nm) + sh_s[w] * __expf(sh_m[w] - nm);
+      m = nm;
+      if (sh_b[w] > best || (sh_b[w] == best && sh_i[w] >= 0 && (best_i < 0 || sh_i[w] < best_i))) {
+        best = sh_b[w]; best_i = sh_i[w]; best_z = sh_z[w];
+      }
+    }
+    part[(size_t)row * 8 + sp] = make_float4(m, se, best, best_z);
+    part_i[(size_t)row * 8 + sp] = best_i;
+    __threadfence();
+    is_last = (atomicAdd(&counter[row], 1u) == (unsigned)(S - 1));
+    if (is_last) {
+      __threadfence();
+      float M = -INFINITY;
+      for (int q = 0; q < S; ++q) M = fmaxf(M, __ldcg(&part[(size_t)row * 8 + q]).x);
+      float tot = 0.f;
+      best = -INFINITY; best_i = -1; best_z = 0.f;
+      for (int q = 0; q < S; ++q) {
+        const float4 pq = __ldcg(&part[(size_t)row * 8 + q]);
+        const int pi = __ldcg(&part_i[(size_t)row * 8 + q]);
+        if (pq.x != -INFINITY) tot += pq.y * __expf(pq.x - M);
+        if (pi >= 0 && (pq.z > best || (pq.z == best && (best_i < 0 || pi < best_i)))) { best = pq.z; best_i = pi; best_z = pq.w; }
+      }
+      const float lse_others = M + __logf(fmaxf(tot, 1e-30f));
+      float z_eos = -INFINITY;
+      if (eos_id >= 0 && eos_id < V) z_eos = __bfloat162float(z[eos_id]) * inv_temp;
+      if (eos_floor > 0.f && eos_id >= 0 && eos_id < V) {
+        const float need = lse_others + __logf(eos_floor / (1.f - eos_floor));
+        if (z_eos < need) z_eos = need;
+      }
+      const float a = fmaxf(lse_others, z_eos);
+      const float lse_all = a + __logf(__expf(lse_others - a) + __expf(z_eos - a));
+      if (z_eos != -INFINITY) {
+        const float key = greedy ? z_eos : z_eos - __logf(-__logf(uniform01_pre(base, (uint32_t)eos_id)));
+        if (key > best || (key == best && eos_id < best_i) || best_i < 0) { best = key; best_i = eos_id; best_z = z_eos; }
+      }
+      out_tok[row] = best_i < 0 ? 0 : best_i;
+      out_logp[row] = best_z - lse_all;
+      counter[row] = 0;
+    }
+  }
+}
+
 // After sampling: append token to the output buffer, bump lengths, mark finished sequences.
 // out_tokens / out_logps are [max_seqs, max_new]; n_gen[slot] counts generated tokens.
 __global__ void advance_kernel(const int* __restrict__ tok, const float* __restrict__ logp, const int* __restrict__ slot_ids,
@@ -214,19 +328,19 @@ using namespace trlb;
 
 TRLB_API int trlb_rope_kv_write(const void* qkv, long long row_stride, const int* seq_lens, const int* slot_ids,
                                 const int* block_table, int max_blocks, int block_size, void* q_out, void* kc, void* vc,
-                                int B, int Hq, int Hk, int D, float theta, cudaStream_t st) {
+                                int B, int Hq, int Hk, int D, float theta, int v_t, cudaStream_t st) {
   if (B == 0) return 0;
   const long long work = (long long)B * (Hq + 2 * Hk) * (D / 2);
   int grid = (int)((work + 255) / 256);
   rope_kv_write_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)qkv, row_stride, seq_lens, slot_ids, block_table,
                                              max_blocks, block_size, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kc,
-                                             (__nv_bfloat16*)vc, B, Hq, Hk, D, log2f(theta));
+                                             (__nv_bfloat16*)vc, B, Hq, Hk, D, log2f(theta), v_t);
   return (int)cudaGetLastError();
 }
 
 TRLB_API int trlb_kv_write_prefill(const void* k, const void* v, long long k_stride, long long v_stride,
                                    const int* tok_slot, const int* tok_pos, const int* block_table, int max_blocks,
-                                   int block_size, void* kc, void* vc, int T, int Hk, int D, cudaStream_t st) {
+                                   int block_size, void* kc, void* vc, int T, int Hk, int D, int v_t, cudaStream_t st) {
   if (T == 0) return 0;
   if ((Hk * D) % 8 != 0) return -1;
   const long long work = (long long)T * (Hk * D / 8);
@@ -234,7 +348,7 @@ TRLB_API int trlb_kv_write_prefill(const void* k, const void* v, long long k_str
   if (grid > 148 * 16) grid = 148 * 16;
   kv_write_prefill_kernel<<<(int)grid, 256, 0, st>>>((const __nv_bfloat16*)k, (const __nv_bfloat16*)v, k_stride, v_stride,
                                                      tok_slot, tok_pos, block_table, max_blocks, block_size,
-                                                     (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, T, Hk, D);
+                                                     (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, T, Hk, D, v_t);
   return (int)cudaGetLastError();
 }
 
@@ -261,8 +375,24 @@ TRLB_API int trlb_paged_decode_attn(const void* q, const void* kc, const void* v
 
 TRLB_API int trlb_sample(const void* logits, int is_bf16, long long row_stride, int B, int V, float inv_temp, float min_p,
                          int eos_id, float eos_floor, unsigned seed, const int* step_ptr, int greedy, int* out_tok,
-                         float* out_logp, cudaStream_t st) {
+                         float* out_logp, void* scratch, long long scratch_bytes, cudaStream_t st) {
   if (B == 0) return 0;
+  // scratch (optional, zero-initialised once by the caller).  The layout does not depend on B, so calls with
+  // different batch sizes never put partials where another call expects its zeroed counters:
+  // [4096] row counters | [4096, 8] float4 partials | [4096, 8] int partials
+  constexpr long long kRows = 4096, kNeed = kRows * 4 + kRows * 8 * 16 + kRows * 8 * 4;
+  if (is_bf16 && min_p <= 0.f && (V % 8) == 0 && (row_stride % 8) == 0 && scratch != nullptr && B <= kRows &&
+      scratch_bytes >= kNeed) {
+    int S = trlb_host::sm_count() / B;
+    S = S < 1 ? 1 : (S > 8 ? 8 : S);
+    unsigned* counter = (unsigned*)scratch;
+    float4* part = (float4*)((char*)scratch + kRows * 4);
+    int* part_i = (int*)(part + kRows * 8);
+    sample_split_kernel<<<dim3(B, S), 512, 0, st>>>((const __nv_bfloat16*)logits, row_stride, V, inv_temp, eos_id,
+                                                    eos_floor, seed, step_ptr, greedy, part, part_i, counter, out_tok,
+                                                    out_logp);
+    return (int)cudaGetLastError();
+  }
   if (is_bf16)
     sample_kernel<__nv_bfloat16><<<B, 1024, 0, st>>>((const __nv_bfloat16*)logits, row_stride, V, inv_temp, min_p, eos_id,
                                                     eos_floor, seed, step_ptr, greedy, out_tok, out_logp);

@@ -395,18 +395,23 @@ def swiglu_infer(gu, out=None):
     return out
 
 
-def rope_kv_write(qkv, seq_lens, slot_ids, block_table, block_size, q_out, k_cache, v_cache, Hq, Hk, D, theta):
+def rope_kv_write(qkv, seq_lens, slot_ids, block_table, block_size, q_out, k_cache, v_cache, Hq, Hk, D, theta,
+                  v_transposed=False):
+    """RoPE on q/k of the new tokens, q -> q_out, k/v appended to the paged cache.  ``v_transposed``: the V cache is
+    [block, head, dim, token] (layout of the tensor-core decode attention) instead of [block, token, head, dim]."""
     B = qkv.shape[0]
     _chk(lib().trlb_rope_kv_write(_p(qkv), c_longlong(qkv.stride(0)), _p(seq_lens), _p(slot_ids), _p(block_table),
                                   c_int(block_table.shape[1]), c_int(block_size), _p(q_out), _p(k_cache), _p(v_cache),
-                                  c_int(B), c_int(Hq), c_int(Hk), c_int(D), c_float(theta), _s()), "rope_kv_write")
+                                  c_int(B), c_int(Hq), c_int(Hk), c_int(D), c_float(theta), c_int(int(v_transposed)), _s()),
+         "rope_kv_write")
 
 
-def kv_write_prefill(k, v, tok_slot, tok_pos, block_table, block_size, k_cache, v_cache):
+def kv_write_prefill(k, v, tok_slot, tok_pos, block_table, block_size, k_cache, v_cache, v_transposed=False):
     T, Hk, D = k.shape
     _chk(lib().trlb_kv_write_prefill(_p(k), _p(v), c_longlong(k.stride(0)), c_longlong(v.stride(0)), _p(tok_slot),
                                      _p(tok_pos), _p(block_table), c_int(block_table.shape[1]), c_int(block_size),
-                                     _p(k_cache), _p(v_cache), c_int(T), c_int(Hk), c_int(D), _s()), "kv_write_prefill")
+                                     _p(k_cache), _p(v_cache), c_int(T), c_int(Hk), c_int(D), c_int(int(v_transposed)), _s()),
+         "kv_write_prefill")
 
 
 def paged_decode_attn(q, k_cache, v_cache, seq_lens, slot_ids, block_table, block_size, scale, splits, part_o, part_ml,
@@ -420,12 +425,43 @@ def paged_decode_attn(q, k_cache, v_cache, seq_lens, slot_ids, block_table, bloc
     return out
 
 
+def paged_decode_attn_tc(q, k_cache, v_cache_t, seq_lens, slot_ids, block_table, scale, splits, part_o, part_ml, out):
+    """Tensor-core (tcgen05) decode attention.  k_cache [blocks, 64, Hk, 128]; v_cache_t [blocks, Hk, 128, 64]."""
+    B, Hq, D = q.shape
+    nb, bs, Hk, Dk = k_cache.shape
+    if D != 128 or Dk != 128 or bs != 64 or tuple(v_cache_t.shape) != (nb, Hk, 128, 64):
+        raise ValueError("paged_decode_attn_tc needs head_dim 128, 64-token pages and a transposed V cache")
+    _chk(lib().trlb_paged_decode_attn_tc(_p(q), _p(k_cache), _p(v_cache_t), _p(seq_lens), _p(slot_ids), _p(block_table),
+                                         c_int(block_table.shape[1]), c_int(nb), c_int(B), c_int(Hq), c_int(Hk),
+                                         c_float(scale), c_int(splits), _p(part_o), _p(part_ml), _p(out),
+                                         _p(status_buffer(q.device)), _s()), "paged_decode_attn_tc")
+    return out
+
+
+_SAMPLE_SCRATCH: dict = {}
+
+
+def _sample_scratch(device, B):
+    """Row counters + per-slice partials of the split sampler; zeroed once, the kernel leaves the counters at zero.
+    One buffer per device: sampler calls of one process are expected on one stream."""
+    need = 4096 * (4 + 8 * 16 + 8 * 4)  # fixed layout for up to 4096 rows (see trlb_sample)
+    buf = _SAMPLE_SCRATCH.get(device)
+    if buf is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None  # no allocation during capture: the one-CTA-per-row kernel is used instead
+        buf = torch.zeros(need, dtype=torch.uint8, device=device)
+        _SAMPLE_SCRATCH[device] = buf
+    return buf
+
+
 def sample_tokens(logits, inv_temp, min_p, eos_id, eos_floor, seed, step_ptr, greedy, out_tok, out_logp):
     B, V = logits.shape
+    scratch = _sample_scratch(logits.device, B)
     _chk(lib().trlb_sample(_p(logits), c_int(int(logits.dtype == torch.bfloat16)), c_longlong(logits.stride(0)), c_int(B),
                            c_int(V), c_float(inv_temp), c_float(min_p or 0.0), c_int(-1 if eos_id is None else eos_id),
                            c_float(eos_floor or 0.0), ctypes.c_uint(seed & 0xFFFFFFFF), _p(step_ptr), c_int(int(greedy)),
-                           _p(out_tok), _p(out_logp), _s()), "sample")
+                           _p(out_tok), _p(out_logp), _p(scratch), c_longlong(0 if scratch is None else scratch.numel()),
+                           _s()), "sample")
 
 
 def advance(tok, logp, slot_ids, seq_lens, n_gen, finished, out_tokens, out_logps, eos_id, max_total_len, next_input,

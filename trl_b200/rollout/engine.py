@@ -19,6 +19,9 @@ CPU path (tests, tiny models): :class:`EagerGenerator`, same sampling semantics.
 """
 from __future__ import annotations
 
+import os
+import time
+
 import math
 from dataclasses import dataclass
 from typing import Optional, Sequence
@@ -102,12 +105,23 @@ class _PrefillKV:
         else:
             kw, vw = k.contiguous(), v.contiguous()
         K.kv_write_prefill(kw, vw, self.tok_slot, self.tok_pos, e.block_table, e.block_size,
-                           e.k_cache[layer_idx], e.v_cache[layer_idx])
+                           e.k_cache[layer_idx], e.v_cache[layer_idx], v_transposed=e.attn_tc)
         return K.attention_varlen(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, True)
 
 
 class RolloutEngine:
-    def __init__(self, model: CausalLM, max_num_seqs: int = 64, max_model_len: int = 2048, block_size: int = 16,
+    def _decode_attention(self, li: int, scale: float):
+        """q_buf x paged KV of layer ``li`` -> attn_buf (tcgen05 kernel when the cache layout allows it)."""
+        from ..ops import cuda as K
+
+        if self.attn_tc:
+            K.paged_decode_attn_tc(self.q_buf, self.k_cache[li], self.v_cache[li], self.seq_lens, None, self.block_table,
+                                   scale, self.kv_splits, self.part_o, self.part_ml, self.attn_buf)
+        else:
+            K.paged_decode_attn(self.q_buf, self.k_cache[li], self.v_cache[li], self.seq_lens, None, self.block_table,
+                                self.block_size, scale, self.kv_splits, self.part_o, self.part_ml, self.attn_buf)
+
+    def __init__(self, model: CausalLM, max_num_seqs: int = 64, max_model_len: int = 2048, block_size: int | None = None,
                  num_blocks: int | None = None, poll_every: int = 16, use_cuda_graph: bool = True, kv_splits: int = 0,
                  tp: int = 1, tp_rank: int = 0):
         cfg = model.config
@@ -124,6 +138,12 @@ class RolloutEngine:
         rt = host_runtime()
         if rt is None:
             raise RuntimeError("libtrl_b200_host.so missing: run python -m trl_b200.csrc.build")
+        # head_dim 128 with at most 8 query heads per KV head: tensor-core decode attention, which wants 64-token
+        # pages and V transposed inside a page; anything else keeps 16-token pages and the CUDA-core kernel
+        tc_ok = cfg.head_dim == 128 and self.hq_local // self.hk_local <= 8
+        if not block_size:
+            block_size = 64 if tc_ok else 16
+        self.attn_tc = tc_ok and block_size == 64
         self.max_seqs, self.max_len, self.block_size = max_num_seqs, max_model_len, block_size
         self.max_blocks = (max_model_len + block_size - 1) // block_size
         self.num_blocks = num_blocks or max_num_seqs * self.max_blocks
@@ -131,7 +151,8 @@ class RolloutEngine:
         L, Hk, D = cfg.num_hidden_layers, self.hk_local, cfg.head_dim
         dt = torch.bfloat16
         self.k_cache = [torch.zeros(self.num_blocks, block_size, Hk, D, dtype=dt, device=self.dev) for _ in range(L)]
-        self.v_cache = [torch.zeros(self.num_blocks, block_size, Hk, D, dtype=dt, device=self.dev) for _ in range(L)]
+        v_shape = (self.num_blocks, Hk, D, block_size) if self.attn_tc else (self.num_blocks, block_size, Hk, D)
+        self.v_cache = [torch.zeros(*v_shape, dtype=dt, device=self.dev) for _ in range(L)]
         i32 = dict(dtype=torch.int32, device=self.dev)
         self.block_table = torch.zeros(max_num_seqs, self.max_blocks, **i32)
         self.block_table_host = torch.zeros(max_num_seqs, self.max_blocks, dtype=torch.int32).pin_memory()
@@ -145,6 +166,8 @@ class RolloutEngine:
         self.poll_every, self.use_graph = poll_every, use_cuda_graph and not cfg.is_moe
         # enough CTAs for ~4 per SM: the kernel is latency-bound on KV loads, occupancy hides it
         self.kv_splits = kv_splits or max(1, min(8, -(-(4 * 148) // max(1, max_num_seqs * Hk))))
+        if self.attn_tc and not kv_splits:  # persistent CTAs, one per SM: split only to give every SM an item
+            self.kv_splits = max(1, min(8, 148 // max(1, max_num_seqs * Hk)))
         self.part_o = torch.empty(max_num_seqs * self.hq_local * self.kv_splits * D, dtype=torch.float32, device=self.dev)
         self.part_ml = torch.empty(max_num_seqs * self.hq_local * self.kv_splits * 2, dtype=torch.float32, device=self.dev)
         self.q_buf = torch.empty(max_num_seqs, self.hq_local, D, dtype=dt, device=self.dev)
@@ -191,9 +214,8 @@ class RolloutEngine:
                 qkv = torch.cat([qn.view(-1, qs), kn.view(-1, ks), qkv[:, qs + ks:]], dim=1)
             K.rope_kv_write(qkv, self.seq_lens, None, self.block_table, self.block_size, self.q_buf, self.k_cache[li],
                             self.v_cache[li], cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
-                            cfg.rope_theta)
-            K.paged_decode_attn(self.q_buf, self.k_cache[li], self.v_cache[li], self.seq_lens, None, self.block_table,
-                                self.block_size, scale, self.kv_splits, self.part_o, self.part_ml, self.attn_buf)
+                            cfg.rope_theta, v_transposed=self.attn_tc)
+            self._decode_attention(li, scale)
             attn_out = torch.nn.functional.linear(self.attn_buf.view(self.max_seqs, -1), l.o_proj)
             if fuse:
                 h = K.add_rmsnorm_infer(x, attn_out, l.post_attention_layernorm, eps)
@@ -285,6 +307,7 @@ class RolloutEngine:
         self.finished.zero_()
         self.n_gen.zero_()
         bt_np = self.block_table_host.numpy()
+        timing = os.environ.get("TRL_B200_ROLLOUT_TIMING", "0") == "1"  # wall-clock sections in self.stats (adds syncs)
         graph_key = (sp.temperature, sp.top_p, sp.top_k, sp.min_p, sp.repetition_penalty, sp.eos_token_id,
                      sp.eos_prob_floor, sp.seed, sp.greedy, max_total, max_new)
         # every request retires after at most max_new decode steps; a generous bound on the number of
@@ -298,6 +321,7 @@ class RolloutEngine:
                 raise RuntimeError(f"rollout did not finish within {max_polls} polls "
                                    f"(running={self.sched.num_running}, waiting={self.sched.num_waiting})")
             admitted = self.sched.admit(bt_np)
+            t_sec = time.perf_counter() if timing else 0.0
             if admitted:
                 self.block_table.copy_(self.block_table_host, non_blocking=True)
                 owners = [(slot, reqs[rid][0]) for rid, slot, pre, _ in admitted if pre]
@@ -342,8 +366,12 @@ class RolloutEngine:
                     self.seen.scatter_(1, self.next_input[:, None], 1)
                 for rid, slot, _, _ in admitted:
                     slot_req[slot] = rid
+            if timing and admitted:
+                torch.cuda.synchronize()
+                self.stats["t_admit_prefill"] = self.stats.get("t_admit_prefill", 0.0) + time.perf_counter() - t_sec
             if self.sched.num_running == 0:
                 break
+            t_sec = time.perf_counter() if timing else 0.0
             # ---- decode until the next poll ----
             if self.use_graph:
                 if self._graph is None or self._graph_key != graph_key:
@@ -356,6 +384,9 @@ class RolloutEngine:
                     self._decode_step(sp, max_total)
             self.stats["decode_steps"] += self.poll_every
             fin = self.finished.cpu().numpy()  # host sync: the only one per poll
+            if timing:
+                self.stats["t_decode"] = self.stats.get("t_decode", 0.0) + time.perf_counter() - t_sec
+                t_sec = time.perf_counter()
             done_slots = [s for s in range(self.max_seqs) if slot_req[s] >= 0 and fin[s]]
             if done_slots:
                 ds = torch.tensor(done_slots, device=dev)
@@ -373,6 +404,8 @@ class RolloutEngine:
                     slot_req[s] = -1
                 self.seq_lens[ds] = -1
                 self.finished[ds] = 0
+            if timing:
+                self.stats["t_collect"] = self.stats.get("t_collect", 0.0) + time.perf_counter() - t_sec
         K.check_status(dev)
         return results  # type: ignore[return-value]
 

@@ -94,9 +94,9 @@ class TPRolloutEngine(RolloutEngine):
                                             l.input_layernorm, eps, self.sync)
             qkv = F.linear(h, w["qkv"], w["qkv_b"])
             K.rope_kv_write(qkv, self.seq_lens, None, self.block_table, self.block_size, self.q_buf, self.k_cache[li],
-                            self.v_cache[li], self.hq_local, self.hk_local, cfg.head_dim, cfg.rope_theta)
-            K.paged_decode_attn(self.q_buf, self.k_cache[li], self.v_cache[li], self.seq_lens, None, self.block_table,
-                                self.block_size, scale, self.kv_splits, self.part_o, self.part_ml, self.attn_buf)
+                            self.v_cache[li], self.hq_local, self.hk_local, cfg.head_dim, cfg.rope_theta,
+                            v_transposed=self.attn_tc)
+            self._decode_attention(li, scale)
             torch.matmul(self.attn_buf.view(self.max_seqs, -1), w["o"].t(), out=self._site(site))
             h = K.allreduce_add_rmsnorm(self.arena, self.partials_off + site * self.site_elems * 2, 0, x,
                                         l.post_attention_layernorm, eps, self.sync)

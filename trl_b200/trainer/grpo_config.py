@@ -71,7 +71,7 @@ class _OnlineConfig(_BaseConfig):
     log_completions_hub_repo: Optional[str] = None
     # synthetic-benchmark knob: floor on the end-of-sequence probability during sampling
     eos_prob_floor: float = 0.0
-    rollout_block_size: int = 16
+    rollout_block_size: int = 0  # 0 = chosen by the engine (64-token pages for the tensor-core decode attention)
     rollout_poll_every: int = 16
 
     def _derive_generation_batch(self):

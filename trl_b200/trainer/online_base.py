@@ -194,8 +194,8 @@ class OnlineTrainer(Trainer):
 
                 a = self.args
                 max_len = a.vllm_max_model_length or (self._max_prompt_len_seen + self.max_completion_length + 8)
-                bs = a.rollout_block_size
-                max_len = (max_len + bs - 1) // bs * bs
+                bs = a.rollout_block_size or None  # None: the engine picks the page size
+                max_len = (max_len + 63) // 64 * 64
                 tp = int(a.vllm_tensor_parallel_size or 1)
                 nseq = a.per_device_train_batch_size * a.steps_per_generation
                 if tp > 1 and D.world_size() > 1:
