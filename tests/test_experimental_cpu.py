@@ -1,0 +1,138 @@
+"""Experimental trainers: two optimizer steps each on the tiny fixtures (CPU, fp32), parameters move, metrics logged."""
+import pytest
+import torch
+
+from trl_b200.testing import make_dataset, make_tiny_model
+
+COMMON = dict(per_device_train_batch_size=4, max_steps=2, logging_steps=1, learning_rate=1e-3, use_cpu=True,
+              save_strategy="no", report_to="none")
+
+
+def _snap(model):
+    return {n: p.detach().clone() for n, p in model.named_parameters()}
+
+
+def _unchanged(model, before):
+    return [n for n, p in model.named_parameters() if p.requires_grad and torch.equal(before[n], p)]
+
+
+@pytest.mark.parametrize("loss_type,extra", [("sigmoid", {}), ("simpo", {"cpo_alpha": 0.0}), ("ipo", {}), ("hinge", {}),
+                                             ("sigmoid", {"alpha": 0.5})])
+def test_cpo_family(tmp_path, tiny_tokenizer, loss_type, extra):
+    from trl_b200.experimental.cpo import CPOConfig, CPOTrainer
+
+    model = make_tiny_model()
+    before = _snap(model)
+    tr = CPOTrainer(model, CPOConfig(output_dir=str(tmp_path), loss_type=loss_type, **COMMON, **extra),
+                    train_dataset=make_dataset("standard_preference", 16), processing_class=tiny_tokenizer)
+    assert tr.ref_model is None
+    tr.train()
+    assert _unchanged(model, before) == []
+    h = [x for x in tr.state.log_history if "rewards/chosen" in x][-1]
+    assert "nll_loss" in h and "rewards/margins" in h
+
+
+def test_orpo(tmp_path, tiny_tokenizer):
+    from trl_b200.experimental.orpo import ORPOConfig, ORPOTrainer
+    from trl_b200.experimental.orpo.orpo_trainer import log1mexp
+
+    x = torch.tensor([-1e-3, -0.5, -5.0, -30.0], dtype=torch.float64)
+    assert torch.allclose(log1mexp(x), torch.log(1 - torch.exp(x)), atol=1e-9)
+    model = make_tiny_model()
+    before = _snap(model)
+    tr = ORPOTrainer(model, ORPOConfig(output_dir=str(tmp_path), **COMMON),
+                     train_dataset=make_dataset("conversational_preference", 16), processing_class=tiny_tokenizer)
+    tr.train()
+    assert _unchanged(model, before) == []
+    h = [x for x in tr.state.log_history if "log_odds_ratio" in x][-1]
+    assert h["log_odds_ratio"] < 0
+
+
+def test_tpo_three_branches(tmp_path, tiny_tokenizer):
+    from trl_b200.experimental.tpo import TPOConfig, TPOTrainer
+
+    ds = [dict(ex, reference=ex["chosen"] + " indeed") for ex in make_dataset("standard_preference", 16)]
+    model = make_tiny_model()
+    before = _snap(model)
+    tr = TPOTrainer(model, TPOConfig(output_dir=str(tmp_path), loss_type="tpo-l", **COMMON), train_dataset=ds,
+                    processing_class=tiny_tokenizer)
+    batch = next(iter(tr.get_train_dataloader()))
+    assert batch["input_ids"].shape[0] == 12  # chosen, rejected and gold rows of 4 examples
+    tr.train()
+    assert _unchanged(model, before) == []
+    assert any("gold_nll_loss" in h for h in tr.state.log_history)
+
+
+def test_bco_running_moments_and_training(tmp_path, tiny_tokenizer):
+    from trl_b200.experimental.bco import BCOConfig, BCOTrainer, RunningMoments
+
+    rm = RunningMoments()
+    xs = torch.randn(1000, dtype=torch.float64) * 3 + 2
+    for chunk in xs.split(100):
+        rm.update(chunk)
+    assert abs(rm.mean - float(xs.mean())) < 1e-4 and abs(rm.std - float(xs.std())) < 1e-3
+    model = make_tiny_model()
+    before = _snap(model)
+    tr = BCOTrainer(model, args=BCOConfig(output_dir=str(tmp_path), **COMMON),
+                    train_dataset=make_dataset("standard_unpaired_preference", 24), processing_class=tiny_tokenizer)
+    tr.train()
+    assert _unchanged(model, before) == []
+    assert any("delta" in h for h in tr.state.log_history)
+    with pytest.warns(FutureWarning):
+        import importlib
+
+        import trl_b200.experimental.kto as shim
+        importlib.reload(shim)
+    assert shim.KTOTrainer is not None
+
+
+def _reward_len(completion_ids, **kw):
+    return [float(sum(c) % 5) for c in completion_ids]
+
+
+GR = dict(per_device_train_batch_size=4, num_generations=4, max_completion_length=8, max_steps=2, logging_steps=1,
+          learning_rate=1e-3, use_cpu=True, save_strategy="no", report_to="none", beta=0.0)
+
+
+def test_gmpo_and_gspo_token(tmp_path, tiny_tokenizer):
+    from trl_b200.experimental.gmpo import GMPOConfig, GMPOTrainer
+    from trl_b200.experimental.gspo_token import GRPOTrainer as GSPOTokenTrainer
+    from trl_b200.trainer.grpo_config import GRPOConfig
+
+    ds = make_dataset("standard_prompt_only", 16)
+    model = make_tiny_model()
+    before = _snap(model)
+    tr = GMPOTrainer(model, _reward_len, GMPOConfig(output_dir=str(tmp_path / "a"), num_iterations=2, **GR), train_dataset=ds,
+                     processing_class=tiny_tokenizer)
+    tr.train()
+    assert _unchanged(model, before) == []
+    model = make_tiny_model()
+    before = _snap(model)
+    tr = GSPOTokenTrainer(model, _reward_len, GRPOConfig(output_dir=str(tmp_path / "b"), num_iterations=2, loss_type="grpo", **GR),
+                          train_dataset=ds, processing_class=tiny_tokenizer)
+    assert tr.importance_sampling_level == "sequence_token"
+    tr.train()
+    assert _unchanged(model, before) == []
+
+
+def test_replay_buffer_replaces_flat_groups(tmp_path, tiny_tokenizer):
+    from trl_b200.experimental.grpo_with_replay_buffer import (GRPOWithReplayBufferConfig, GRPOWithReplayBufferTrainer,
+                                                               ReplayBuffer)
+
+    rb = ReplayBuffer(2)
+    rb.add([1.0, 3.0, 2.0], [{"i": 0}, {"i": 1}, {"i": 2}])
+    assert sorted(h[2]["i"] for h in rb.heap) == [1, 2]
+    assert len(rb.sample(4)) == 4
+    calls = {"n": 0}
+
+    def reward(completion_ids, **kw):  # first generation batch has variance, later ones are flat
+        calls["n"] += 1
+        return [float(i % 3) for i in range(len(completion_ids))] if calls["n"] == 1 else [1.0] * len(completion_ids)
+
+    model = make_tiny_model()
+    tr = GRPOWithReplayBufferTrainer(model, reward, GRPOWithReplayBufferConfig(output_dir=str(tmp_path), replay_buffer_size=4,
+                                                                              **dict(GR, max_steps=3)),
+                                     train_dataset=make_dataset("standard_prompt_only", 16), processing_class=tiny_tokenizer)
+    tr.train()
+    assert len(tr.replay_buffer) >= 1
+    assert any(h.get("replay_buffer/replaced_groups", 0) > 0 for h in tr.state.log_history)

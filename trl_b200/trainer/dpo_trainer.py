@@ -74,6 +74,7 @@ class DataCollatorForVisionPreference:
 class DPOTrainer(Trainer):
     _tag_names = ["trl", "dpo"]
     _name = "DPO"
+    _needs_ref = True  # reference-free subclasses (CPO, ORPO, ...) turn the frozen copy off
 
     def __init__(self, model, ref_model=None, args: DPOConfig | None = None, data_collator=None, train_dataset=None,
                  eval_dataset=None, processing_class=None, compute_metrics=None, callbacks=None,
@@ -131,7 +132,9 @@ class DPOTrainer(Trainer):
                          callbacks=callbacks)
         self.model_accepts_loss_kwargs = False  # loss is divided by the accumulation steps by the loop
         self._ref_adapter_off = False
-        if ref_model is not None:
+        if not self._needs_ref:
+            self.ref_model = None
+        elif ref_model is not None:
             self.ref_model = ref_model.to(self.args.device, dtype=self.model.dtype).eval().requires_grad_(False)
         elif getattr(self.model, "peft_config", None) is not None:
             self.ref_model, self._ref_adapter_off = None, True

@@ -111,6 +111,8 @@ class _OnlineConfig(_BaseConfig):
 
 @dataclass
 class GRPOConfig(_OnlineConfig):
+    _LOSS_TYPES = ("grpo", "bnpo", "dr_grpo", "dapo", "cispo", "sapo", "luspo", "vespo")
+
     delta: Optional[float] = None
     sapo_temperature_neg: float = 1.05
     sapo_temperature_pos: float = 1.0
@@ -148,10 +150,10 @@ class GRPOConfig(_OnlineConfig):
             self.scale_rewards = "group" if self.scale_rewards else "none"
         if self.scale_rewards not in ("group", "batch", "none"):
             raise ValueError("scale_rewards must be one of 'group', 'batch', 'none'")
-        if self.loss_type not in ("grpo", "bnpo", "dr_grpo", "dapo", "cispo", "sapo", "luspo", "vespo"):
+        if self.loss_type not in self._LOSS_TYPES:
             raise ValueError(f"Unknown loss type: {self.loss_type}")
-        if self.importance_sampling_level not in ("token", "sequence"):
-            raise ValueError("importance_sampling_level must be 'token' or 'sequence'")
+        if self.importance_sampling_level not in ("token", "sequence", "sequence_token"):
+            raise ValueError("importance_sampling_level must be 'token', 'sequence' or 'sequence_token'")
         if self.vllm_importance_sampling_cap is not None:
             warnings.warn("vllm_importance_sampling_cap is deprecated; use vllm_importance_sampling_clip_max.", FutureWarning)
             self.vllm_importance_sampling_clip_max = self.vllm_importance_sampling_cap

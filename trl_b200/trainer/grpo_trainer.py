@@ -117,6 +117,7 @@ class GRPOTrainer(OnlineTrainer):
         sl = slice(D.rank() * B, (D.rank() + 1) * B)
         all_adv = advantages.clone()
         advantages = advantages[sl]
+        self._last_group_std = std_rewards[sl] if std_rewards.ndim and std_rewards.shape[0] == all_adv.shape[0] else None
         # ---- metrics ----------------------------------------------------------------------------------------------
         m = self._metrics[mode]
         if mode == "train":
@@ -320,6 +321,10 @@ class GRPOTrainer(OnlineTrainer):
         log_ratio = logps - old
         if self.importance_sampling_level == "token":
             liw = log_ratio
+        elif self.importance_sampling_level == "sequence_token":
+            # GSPO-token: the sequence-level weight as value, the token's own log-prob as gradient path
+            seq = ((log_ratio * maskf).sum(-1) / maskf.sum(-1).clamp(min=1.0))[:, None]
+            liw = logps - logps.detach() + seq.detach()
         else:
             liw = ((log_ratio * maskf).sum(-1) / maskf.sum(-1).clamp(min=1.0))[:, None]
         coef_1 = torch.exp(liw)
@@ -334,6 +339,14 @@ class GRPOTrainer(OnlineTrainer):
             coef_2 = torch.clamp(coef_1, 1 - self.epsilon_low, 1 + self.epsilon_high)
             c1 = torch.clamp(coef_1, max=a.delta) if a.delta is not None else coef_1
             per_tok = -torch.min(c1 * adv2, coef_2 * adv2)
+        elif self.loss_type == "gmpo":
+            # geometric mean of the token ratios: clip in log space on the side the advantage pushes towards,
+            # average over the sequence, exponentiate once (one weight per sequence)
+            sgn = torch.where(adv2 > 0, torch.ones_like(adv2), -torch.ones_like(adv2))
+            lo, hi = -float(getattr(a, "gmpo_log_clip", 0.4)), float(getattr(a, "gmpo_log_clip", 0.4))
+            clipped = sgn * torch.minimum(sgn * log_ratio, sgn * torch.clamp(log_ratio, lo, hi))
+            seq_w = torch.exp((clipped * maskf).sum(-1, keepdim=True) / maskf.sum(-1, keepdim=True).clamp(min=1.0))
+            per_tok = (-seq_w * adv2).expand_as(logps)
         elif self.loss_type == "sapo":
             temps = torch.where(adv2 > 0, torch.full_like(adv2, a.sapo_temperature_pos),
                                 torch.full_like(adv2, a.sapo_temperature_neg))
@@ -353,7 +366,7 @@ class GRPOTrainer(OnlineTrainer):
             per_tok = per_tok * isr
         if kl is not None:
             per_tok = per_tok + self.beta * kl
-        if self.loss_type in ("grpo", "sapo"):
+        if self.loss_type in ("grpo", "sapo", "gmpo"):
             loss = ((per_tok * maskf).sum(-1) / maskf.sum(-1).clamp(min=1.0)).mean() / ga
         elif self.loss_type == "bnpo":
             loss = (per_tok * maskf).sum() / maskf.sum().clamp(min=1.0) / ga

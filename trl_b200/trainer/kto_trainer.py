@@ -34,6 +34,7 @@ from .utils import create_model_from_path, disable_dropout_in_model, pad, use_ad
 @dataclass
 class KTOConfig(_BaseConfig):
     _VALID_DICT_FIELDS = _BaseConfig._VALID_DICT_FIELDS + ["model_init_kwargs"]
+    _LOSS_TYPES = ("kto", "apo_zero_unpaired")
 
     learning_rate: float = 1e-6
     train_sampling_strategy: str = "sequential"
@@ -57,8 +58,8 @@ class KTOConfig(_BaseConfig):
 
     def __post_init__(self):
         super().__post_init__()
-        if self.loss_type not in ("kto", "apo_zero_unpaired"):
-            raise ValueError("loss_type must be 'kto' or 'apo_zero_unpaired'")
+        if self.loss_type not in self._LOSS_TYPES:
+            raise ValueError(f"loss_type must be one of {self._LOSS_TYPES}")
 
 
 @dataclass
@@ -263,12 +264,7 @@ class KTOTrainer(Trainer):
                 kl = torch.zeros((), device=logps.device)
         logratio = logps - ref_logps
         c_lr, r_lr = logratio[label], logratio[~label]
-        if self.loss_type == "kto":
-            c_loss = 1 - torch.sigmoid(self.beta * (c_lr - kl))
-            r_loss = 1 - torch.sigmoid(self.beta * (kl - r_lr))
-        else:
-            c_loss = 1 - torch.sigmoid(self.beta * c_lr)
-            r_loss = torch.sigmoid(self.beta * r_lr)
+        c_loss, r_loss = self._unpaired_losses(c_lr, r_lr, kl, mode)
         losses = torch.cat([self.desirable_weight * c_loss, self.undesirable_weight * r_loss], 0)
         loss = losses.nanmean() if losses.numel() else (logps.sum() * 0.0)
         if aux is not None:
@@ -296,6 +292,12 @@ class KTOTrainer(Trainer):
                 self._num_tokens += float(s[8])
             m["num_tokens"].append(self._num_tokens)
         return (loss, None) if return_outputs else loss
+
+    def _unpaired_losses(self, c_lr, r_lr, kl, mode):
+        """Per-example losses of the desirable / undesirable completions from their policy-vs-reference log-ratios."""
+        if self.loss_type == "kto":
+            return 1 - torch.sigmoid(self.beta * (c_lr - kl)), 1 - torch.sigmoid(self.beta * (kl - r_lr))
+        return 1 - torch.sigmoid(self.beta * c_lr), torch.sigmoid(self.beta * r_lr)
 
     def prediction_step(self, model, inputs, prediction_loss_only=True, ignore_keys=None):
         inputs = self._prepare_inputs(inputs)
