@@ -136,3 +136,62 @@ def test_replay_buffer_replaces_flat_groups(tmp_path, tiny_tokenizer):
     tr.train()
     assert len(tr.replay_buffer) >= 1
     assert any(h.get("replay_buffer/replaced_groups", 0) > 0 for h in tr.state.log_history)
+
+
+def test_generalized_jsd_limits():
+    from trl_b200.experimental.gkd import GKDTrainer
+
+    torch.manual_seed(0)
+    s, t = torch.randn(2, 5, 11), torch.randn(2, 5, 11)
+    ls, lt = torch.log_softmax(s, -1), torch.log_softmax(t, -1)
+    fwd = (lt.exp() * (lt - ls)).sum(-1).sum() / 10
+    rev = (ls.exp() * (ls - lt)).sum(-1).sum() / 10
+    assert torch.allclose(GKDTrainer.generalized_jsd_loss(s, t, beta=0.0), fwd, atol=1e-6)
+    assert torch.allclose(GKDTrainer.generalized_jsd_loss(s, t, beta=1.0), rev, atol=1e-6)
+    mid = GKDTrainer.generalized_jsd_loss(s, t, beta=0.5)
+    assert 0 < float(mid) < max(float(fwd), float(rev))
+    assert float(GKDTrainer.generalized_jsd_loss(s, s, beta=0.3)) < 1e-7
+
+
+@pytest.mark.parametrize("lmbda,seq_kd", [(0.0, False), (1.0, False), (0.0, True)])
+def test_gkd(tmp_path, tiny_tokenizer, lmbda, seq_kd):
+    from trl_b200.experimental.gkd import GKDConfig, GKDTrainer
+
+    model, teacher = make_tiny_model(seed=0), make_tiny_model(seed=1)
+    before = _snap(model)
+    tr = GKDTrainer(model, teacher, GKDConfig(output_dir=str(tmp_path), lmbda=lmbda, seq_kd=seq_kd, max_new_tokens=6,
+                                              **COMMON),
+                    train_dataset=make_dataset("standard_prompt_completion", 16), processing_class=tiny_tokenizer)
+    tr.train()
+    assert _unchanged(model, before) == []
+    assert any("jsd" in h for h in tr.state.log_history)
+
+
+ON = dict(per_device_train_batch_size=4, max_new_tokens=6, max_steps=2, logging_steps=1, learning_rate=1e-3, use_cpu=True,
+          save_strategy="no", report_to="none")
+
+
+def _reward_ids(completion_ids, **kw):
+    return [float(sum(c) % 7) for c in completion_ids]
+
+
+@pytest.mark.parametrize("kind", ["online_dpo", "xpo", "nash_md"])
+def test_online_preference_trainers(tmp_path, tiny_tokenizer, kind):
+    if kind == "online_dpo":
+        from trl_b200.experimental.online_dpo import OnlineDPOConfig as C, OnlineDPOTrainer as T
+        extra = dict(missing_eos_penalty=1.0, loss_type="ipo")
+    elif kind == "xpo":
+        from trl_b200.experimental.xpo import XPOConfig as C, XPOTrainer as T
+        extra = dict(alpha=[1e-3, 1e-4])
+    else:
+        from trl_b200.experimental.nash_md import NashMDConfig as C, NashMDTrainer as T
+        extra = dict(mixture_coef=0.3)
+    model = make_tiny_model()
+    before = _snap(model)
+    tr = T(model, reward_funcs=_reward_ids, args=C(output_dir=str(tmp_path), **ON, **extra),
+           train_dataset=make_dataset("standard_prompt_only", 16), processing_class=tiny_tokenizer)
+    assert tr.ref_model is not None
+    tr.train()
+    assert _unchanged(model, before) == []
+    h = [x for x in tr.state.log_history if "objective/kl" in x]
+    assert h and "beta" in h[-1]

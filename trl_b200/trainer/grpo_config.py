@@ -91,7 +91,7 @@ class _OnlineConfig(_BaseConfig):
             self.generation_batch_size = self.per_device_train_batch_size * world * self.steps_per_generation
         else:
             raise ValueError("'generation_batch_size' and 'steps_per_generation' can not be both configured at the same time")
-        if self.num_generations < 2 and type(self).__name__ != "OnlineDPOConfig":
+        if self.num_generations < getattr(self, "_MIN_GENERATIONS", 2):
             raise ValueError(f"{type(self).__name__[:-6]} requires at least 2 generations per prompt to calculate the "
                              f"advantages. You provided {self.num_generations}, which is less than the minimum required.")
         if self.generation_batch_size % self.num_generations != 0:
