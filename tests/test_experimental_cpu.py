@@ -13,7 +13,7 @@ def _snap(model):
 
 
 def _unchanged(model, before):
-    return [n for n, p in model.named_parameters() if p.requires_grad and torch.equal(before[n], p)]
+    return [n for n, p in model.named_parameters() if p.requires_grad and n in before and torch.equal(before[n], p)]
 
 
 @pytest.mark.parametrize("loss_type,extra", [("sigmoid", {}), ("simpo", {"cpo_alpha": 0.0}), ("ipo", {}), ("hinge", {}),
@@ -195,3 +195,31 @@ def test_online_preference_trainers(tmp_path, tiny_tokenizer, kind):
     assert _unchanged(model, before) == []
     h = [x for x in tr.state.log_history if "objective/kl" in x]
     assert h and "beta" in h[-1]
+
+
+@pytest.mark.parametrize("separate_value_model", [False, True])
+def test_ppo(tmp_path, tiny_tokenizer, separate_value_model):
+    from trl_b200.experimental.ppo import AutoModelForCausalLMWithValueHead, PPOConfig, PPOTrainer
+    from trl_b200.experimental.ppo.ppo_trainer import masked_whiten
+
+    x, mk = torch.randn(4, 9), (torch.rand(4, 9) > 0.3).float()
+    w = masked_whiten(x, mk)
+    assert abs(float((w * mk).sum() / mk.sum())) < 1e-5
+    model = make_tiny_model()
+    value_model = make_tiny_model(seed=3, num_labels=1) if separate_value_model else None
+    before = _snap(model)
+    cfg = PPOConfig(output_dir=str(tmp_path), per_device_train_batch_size=4, num_mini_batches=2, num_ppo_epochs=2,
+                    response_length=6, max_steps=4, learning_rate=1e-3, use_cpu=True, save_strategy="no", report_to="none",
+                    missing_eos_penalty=0.5, kl_estimator="k3")
+    assert cfg.local_batch_size == 8 and cfg.local_mini_batch_size == 4
+    tr = PPOTrainer(cfg, tiny_tokenizer, model, reward_funcs=_reward_ids, value_model=value_model,
+                    train_dataset=make_dataset("standard_prompt_only", 32))
+    tr.train()
+    assert [n for n in _unchanged(model, before) if not n.startswith("value_model.")] == []
+    assert any("loss/policy_avg" in x for x in tr.state.log_history)
+    assert any("objective/rlhf_reward" in x for x in tr.state.log_history)
+    wrapped = AutoModelForCausalLMWithValueHead(make_tiny_model())
+    ids = torch.randint(5, 100, (2, 7))
+    logits, _, values = wrapped(input_ids=ids, attention_mask=torch.ones_like(ids))
+    assert logits.shape[:2] == (2, 7) and values.shape == (2, 7)
+    assert any(k.startswith("v_head.") for k in wrapped.state_dict())

@@ -348,6 +348,8 @@ class OnlineTrainer(Trainer):
             lp, en = ops.lm_head_logprobs(hidden[sel_t], model.lm_head_weight, tgt, temperature,
                                           softcap=model.config.final_logit_softcapping, compute_entropy=compute_entropy)
             r, c_ = torch.tensor(rows, device=dev), torch.tensor(cols, device=dev)
+            if getattr(self, "_keep_selected_hidden", False):  # value heads read the same rows (PPO)
+                self._selected_hidden = (hidden[sel_t], r, c_, flat, ctx, sel_t)
             logps = logps.index_put((r, c_), lp)
             if compute_entropy:
                 ents = ents.index_put((r, c_), en)
