@@ -223,3 +223,49 @@ def test_ppo(tmp_path, tiny_tokenizer, separate_value_model):
     logits, _, values = wrapped(input_ids=ids, attention_mask=torch.ones_like(ids))
     assert logits.shape[:2] == (2, 7) and values.shape == (2, 7)
     assert any(k.startswith("v_head.") for k in wrapped.state_dict())
+
+
+def test_prm(tmp_path, tiny_tokenizer):
+    from trl_b200.experimental.prm import PRMConfig, PRMTrainer
+
+    row = PRMTrainer.tokenize_row({"prompt": "a b", "completions": ["c d", "e"], "labels": [True, False]}, tiny_tokenizer,
+                                  "\n", None, None, False, False)
+    assert len(row["input_ids"]) == len(row["labels"])
+    assert [l for l in row["labels"] if l != -100] == [1, 0]
+    last = PRMTrainer.tokenize_row({"prompt": "a b", "completions": ["c d", "e"], "labels": [True, False]}, tiny_tokenizer,
+                                   "\n", None, None, True, False)
+    assert [l for l in last["labels"] if l != -100] == [0]
+    model = make_tiny_model(num_labels=2)
+    before = _snap(model)
+    tr = PRMTrainer(model, PRMConfig(output_dir=str(tmp_path), **COMMON),
+                    train_dataset=make_dataset("standard_stepwise_supervision", 16), processing_class=tiny_tokenizer)
+    tr.train()
+    assert "score" not in _unchanged(model, before)
+    assert any("accuracy" in h for h in tr.state.log_history)
+
+
+def test_minillm_and_a2po(tmp_path, tiny_tokenizer):
+    from trl_b200.experimental.a2po import A2POConfig, A2POTrainer
+    from trl_b200.experimental.minillm import MiniLLMConfig, MiniLLMTrainer
+
+    ds = make_dataset("standard_prompt_only", 16)
+    model, teacher = make_tiny_model(seed=0), make_tiny_model(seed=2)
+    before = _snap(model)
+    tr = MiniLLMTrainer(model, teacher, args=MiniLLMConfig(output_dir=str(tmp_path / "m"), gamma=0.9, **GR), train_dataset=ds,
+                        processing_class=tiny_tokenizer)
+    adv = tr._compute_advantage(torch.zeros(1, 3), torch.tensor([[1.0, 2.0, 3.0]]), torch.ones(1, 3))
+    g = 0.9
+    expect0 = (1 + g * 2 + g * g * 3) / (1 + g + g * g)
+    assert abs(float(adv[0, 0]) - expect0) < 1e-5
+    tr.train()
+    assert _unchanged(model, before) == []
+    assert any("single_step_rkl" in h for h in tr.state.log_history)
+    model = make_tiny_model()
+    before = _snap(model)
+    cfg = A2POConfig(output_dir=str(tmp_path / "a"), per_device_train_batch_size=4, max_completion_length=6, max_steps=2,
+                     num_value_samples=3, logging_steps=1, learning_rate=1e-3, use_cpu=True, save_strategy="no",
+                     report_to="none", beta2=0.1)
+    tr = A2POTrainer(model, _reward_ids, cfg, train_dataset=ds, processing_class=tiny_tokenizer)
+    tr.train()
+    assert len(tr._optimal_values) == 16
+    assert _unchanged(model, before) == []
