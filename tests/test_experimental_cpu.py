@@ -269,3 +269,63 @@ def test_minillm_and_a2po(tmp_path, tiny_tokenizer):
     tr.train()
     assert len(tr._optimal_values) == 16
     assert _unchanged(model, before) == []
+
+
+def test_self_distillation_losses():
+    from trl_b200.experimental.sdft import loss_utils as L
+
+    torch.manual_seed(0)
+    s, t = torch.randn(6, 50), torch.randn(6, 50)
+    full = L.compute_full_logit_self_distillation_loss(s, t, distillation_alpha=1.0)
+    ls, lt = torch.log_softmax(s, -1), torch.log_softmax(t, -1)
+    assert torch.allclose(full, (ls.exp() * (ls - lt)).sum(-1), atol=1e-5)
+    topk_all = L.compute_topk_self_distillation_loss(s, t, distillation_topk=50, distillation_alpha=1.0, distillation_add_tail=False)
+    assert torch.allclose(topk_all, full, atol=1e-4)
+    tail = L.add_tail_bucket(torch.log_softmax(s, -1)[:, :10])
+    assert torch.allclose(tail.exp().sum(-1), torch.ones(6), atol=1e-5)
+    with pytest.raises(ValueError):
+        L.compute_sampled_token_self_distillation_loss(s, t, torch.zeros(6, dtype=torch.long), distillation_alpha=0.5)
+
+
+def test_sdft_sdpo_ssd_distillation(tmp_path, tiny_tokenizer):
+    from trl_b200.experimental.distillation import DistillationConfig, DistillationTrainer
+    from trl_b200.experimental.sdft import SDFTConfig, SDFTTrainer
+    from trl_b200.experimental.sdpo import SDPOConfig, SDPOTrainer
+    from trl_b200.experimental.ssd import SSDConfig, SSDTrainer
+
+    base = dict(per_device_train_batch_size=4, max_completion_length=6, max_steps=2, logging_steps=1, learning_rate=1e-3,
+                use_cpu=True, save_strategy="no", report_to="none")
+    ds = [dict(ex, privileged_context="the answer is " + str(i)) for i, ex in enumerate(make_dataset("standard_prompt_only", 16))]
+    model = make_tiny_model()
+    before = _snap(model)
+    tr = SDFTTrainer(model, SDFTConfig(output_dir=str(tmp_path / "f"), num_generations=2, teacher_model_kind="ema",
+                                       distillation_topk=20, distillation_add_tail=True, **base),
+                     train_dataset=ds, processing_class=tiny_tokenizer)
+    tr.train()
+    assert _unchanged(model, before) == []
+    assert any("distillation_loss" in h for h in tr.state.log_history)
+
+    model = make_tiny_model()
+    before = _snap(model)
+    tr = SDPOTrainer(model, lambda completion_ids, **kw: [float(sum(c) % 2) for c in completion_ids],
+                     SDPOConfig(output_dir=str(tmp_path / "p"), num_generations=4, distillation_weight=0.5,
+                                distillation_mode="full_logits", beta=0.0, **base),
+                     train_dataset=ds, processing_class=tiny_tokenizer)
+    tr.train()
+    assert _unchanged(model, before) == []
+    assert any("sdpo/teacher_coverage" in h for h in tr.state.log_history)
+
+    model = make_tiny_model()
+    before = _snap(model)
+    tr = SSDTrainer(model, SSDConfig(output_dir=str(tmp_path / "s"), temperature=1.3, **base), train_dataset=ds,
+                    processing_class=tiny_tokenizer)
+    tr.train()
+    assert _unchanged(model, before) == []
+
+    model, teacher = make_tiny_model(seed=0), make_tiny_model(seed=1)
+    before = _snap(model)
+    tr = DistillationTrainer(model, teacher, DistillationConfig(output_dir=str(tmp_path / "d"), max_completion_length=6,
+                                                                num_generations=2, **COMMON),
+                             train_dataset=make_dataset("standard_prompt_completion", 16), processing_class=tiny_tokenizer)
+    tr.train()
+    assert _unchanged(model, before) == []
