@@ -329,3 +329,52 @@ def test_sdft_sdpo_ssd_distillation(tmp_path, tiny_tokenizer):
                              train_dataset=make_dataset("standard_prompt_completion", 16), processing_class=tiny_tokenizer)
     tr.train()
     assert _unchanged(model, before) == []
+
+
+def test_iw_opd_weights_and_training(tmp_path, tiny_tokenizer):
+    from trl_b200.experimental.iw_opd import IWOPDConfig, IWOPDTrainer
+    from trl_b200.experimental.iw_opd.iw_opd_trainer import iw_opd_weights
+
+    a = torch.tensor([[1.0, -1.0, 2.0, 0.0]])
+    w = iw_opd_weights(a, torch.tensor([[1.0, 1.0, 1.0, 0.0]]), gamma=0.5, eps=1e-8)
+    assert torch.allclose(w[0, :3], torch.tensor([1.5, 1.5 - 0.5 * 0.25, 1.5 - 0.5 * 0.5]))
+    model, teacher = make_tiny_model(seed=0), make_tiny_model(seed=1)
+    before = _snap(model)
+    tr = IWOPDTrainer(model, teacher, IWOPDConfig(output_dir=str(tmp_path), max_completion_length=6, **COMMON),
+                      train_dataset=make_dataset("standard_prompt_completion", 16), processing_class=tiny_tokenizer)
+    tr.train()
+    assert _unchanged(model, before) == []
+    assert any("iw_opd/mean_weight" in h for h in tr.state.log_history)
+
+
+def test_gold_uld_and_server_distillation(tmp_path, tiny_tokenizer):
+    import numpy as np
+
+    from trl_b200.experimental.gold import GOLDConfig, GOLDTrainer
+    from trl_b200.experimental.gold.gold_trainer import ULDLoss, align_spans
+    from trl_b200.experimental.server_distillation import ServerDistillationConfig, ServerDistillationTrainer
+
+    assert align_spans(["ab", "c", "de"], ["a", "bc", "d", "e"]) == [([0, 1], [0, 1]), ([2], [2, 3])]
+    p = torch.softmax(torch.randn(3, 7), -1)
+    assert float(ULDLoss._sorted_l1(p, p[:, torch.randperm(7)]).abs().max()) < 1e-6  # permutation invariant
+    ds = make_dataset("standard_prompt_completion", 16)
+    model, teacher = make_tiny_model(seed=0), make_tiny_model(seed=1)
+    before = _snap(model)
+    tr = GOLDTrainer(model, teacher, GOLDConfig(output_dir=str(tmp_path / "g"), use_uld_loss=True, lmbda=0.0,
+                                                uld_use_hybrid_loss=True, uld_crossentropy_weight=0.1, **COMMON),
+                     teacher_processing_class=tiny_tokenizer, train_dataset=ds, processing_class=tiny_tokenizer)
+    tr.train()
+    assert _unchanged(model, before) == []
+
+    class FakeTeacherClient:  # stands in for the HTTP client: uniform teacher
+        def get_sequence_logprobs(self, sequences, prompt_lengths, temperature=1.0):
+            return [np.full(len(s) - p, -np.log(1024.0), dtype=np.float32) for s, p in zip(sequences, prompt_lengths)]
+
+    model = make_tiny_model()
+    before = _snap(model)
+    cfg = ServerDistillationConfig(output_dir=str(tmp_path / "s"), teacher_model_server_url="http://127.0.0.1:1", lmbda=0.0,
+                                   **COMMON)
+    tr = ServerDistillationTrainer(model, cfg, teacher_client=FakeTeacherClient(), train_dataset=ds,
+                                   processing_class=tiny_tokenizer)
+    tr.train()
+    assert _unchanged(model, before) == []
