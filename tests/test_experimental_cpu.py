@@ -378,3 +378,131 @@ def test_gold_uld_and_server_distillation(tmp_path, tiny_tokenizer):
                                    processing_class=tiny_tokenizer)
     tr.train()
     assert _unchanged(model, before) == []
+
+
+def test_token_budget_batcher_balances_squared_lengths():
+    from trl_b200.experimental.async_grpo import RolloutSample, TokenBudgetBatcher
+
+    def mk(n):
+        return RolloutSample([0] * 2, [1] * (n - 2), [0.0] * (n - 2), 0.0, 0.0, 0, 0)
+    lens = [50, 40, 30, 30, 20, 10, 10, 10]
+    rows, left = TokenBudgetBatcher(world=2, token_budget=100, per_rank=4).assign([mk(n) for n in lens])
+    assert left == [] and all(sum(len(s) for s in r) <= 100 for r in rows)
+    sq = [sum(len(s) ** 2 for s in r) for r in rows]
+    assert abs(sq[0] - sq[1]) <= 0.35 * max(sq)
+    rows, left = TokenBudgetBatcher(world=2, token_budget=0, per_rank=2).assign([mk(n) for n in lens])
+    assert [len(r) for r in rows] == [2, 2] and len(left) == 4
+
+
+def test_async_grpo_trains_from_queue_and_drops_stale(tmp_path, tiny_tokenizer):
+    from trl_b200.experimental.async_grpo import AsyncGRPOConfig, AsyncGRPOTrainer
+
+    model = make_tiny_model()
+    before = _snap(model)
+    cfg = AsyncGRPOConfig(output_dir=str(tmp_path), per_device_train_batch_size=4, num_generations=2, max_completion_length=6,
+                          max_steps=3, learning_rate=1e-3, use_cpu=True, save_strategy="no", report_to="none",
+                          vllm_server_base_url=None, max_staleness=1, heartbeat_stale_after_s=60.0)
+    tr = AsyncGRPOTrainer(model, lambda completion_ids, **kw: [float(sum(c) % 3) for c in completion_ids], cfg,
+                          train_dataset=make_dataset("standard_prompt_only", 16), processing_class=tiny_tokenizer)
+    tr.train()
+    assert _unchanged(model, before) == []
+    assert tr.worker.groups_done > 0 and not tr.worker._thread.is_alive()
+    assert any("async/staleness_mean" in h for h in tr.state.log_history)
+
+
+def test_async_worker_failure_is_reported():
+    from trl_b200.experimental.async_grpo import AsyncRolloutWorker
+
+    def broken(prompts, n):
+        raise ValueError("generation backend down")
+    w = AsyncRolloutWorker([{"prompt": "x"}], broken, lambda *a: [], 2)
+    w.start()
+    w._thread.join(timeout=5)
+    with pytest.raises(RuntimeError):
+        w.check_health(60.0)
+
+
+def test_merge_methods(tmp_path):
+    from safetensors.torch import load_file
+
+    from trl_b200.experimental.merge_model_callback import MergeConfig, merge_models
+
+    a, b = make_tiny_model(seed=0), make_tiny_model(seed=1)
+    a.save_pretrained(str(tmp_path / "a"))
+    b.save_pretrained(str(tmp_path / "b"))
+    A, B = load_file(str(tmp_path / "a" / "model.safetensors")), load_file(str(tmp_path / "b" / "model.safetensors"))
+    key = next(k for k in A if "q_proj" in k or "qkv" in k or "gate_proj" in k)
+    for method in ("linear", "slerp", "ties", "dare_ties"):
+        cfg = MergeConfig(method)
+        cfg.policy_model_path, cfg.target_model_path, cfg.dtype = str(tmp_path / "a"), str(tmp_path / "b"), "float32"
+        merge_models(cfg, str(tmp_path / method))
+        M = load_file(str(tmp_path / method / "model.safetensors"))
+        assert set(M) == set(A) and (tmp_path / method / "config.json").exists()
+        if method == "linear":
+            assert torch.allclose(M[key], 0.5 * (A[key] + B[key]), atol=1e-6)
+        if method == "ties":  # densities < 1 keep only the largest task-vector entries
+            assert torch.isfinite(M[key]).all()
+    cfg = MergeConfig("slerp")
+    cfg.policy_model_path = cfg.target_model_path = str(tmp_path / "a")
+    cfg.dtype = "float32"
+    merge_models(cfg, str(tmp_path / "same"))
+    assert torch.allclose(load_file(str(tmp_path / "same" / "model.safetensors"))[key], A[key], atol=1e-5)
+
+
+def test_harbor_local_and_openreward_adapter(tmp_path):
+    from trl_b200.experimental.harbor import HarborSpec
+    from trl_b200.experimental.openreward import OpenRewardSpec
+
+    t = tmp_path / "suite" / "tasks" / "t0"
+    (t / "tests").mkdir(parents=True)
+    (t / "environment").mkdir()
+    (t / "instruction.md").write_text("Create a file named done.txt")
+    (t / "task.toml").write_text('[metadata]\ndifficulty = "easy"\n')
+    (t / "tests" / "test.sh").write_text("test -f done.txt\n")
+    spec = HarborSpec(str(tmp_path / "suite"), environment_type="local")
+    rows = spec.dataset
+    assert len(rows) == 1 and rows[0]["difficulty"] == "easy"
+    env = spec.environment_factory()
+    text = env.reset(task_dir=rows[0]["task_dir"])
+    assert "done.txt" in text
+    assert "[exit code" in env.bash("ls missing_file")
+    env.bash("touch done.txt")
+    assert spec.reward_funcs[0](environments=[env]) == [1.0]
+    env.close()
+
+    class Session:
+        def __init__(self, **row):
+            self.row, self.calls = row, 0
+
+        def call_tool(self, name, arguments):
+            self.calls += 1
+            return {"blocks": [{"text": f"{name}:{arguments}"}], "reward": 0.5, "finished": self.calls >= 2}
+    tools = [{"name": "lookup", "description": "Look something up.",
+              "input_schema": {"properties": {"query": {"type": "string", "description": "what"}}, "required": ["query"]}}]
+    ors = OpenRewardSpec.from_session_factory(lambda **row: Session(**row), tools, [{"task_id": 1, "prompt": "hi"}])
+    e = ors.environment_factory()
+    e.reset(**{k: v for k, v in ors.dataset[0].items() if k != "prompt"})
+    assert "lookup" in e.lookup(query="x") and "Args:" in type(e).lookup.__doc__
+    e.lookup(query="y")
+    assert e.reward == 1.0 and e.lookup(query="z").startswith("error")
+
+
+def test_experimental_utils(tiny_tokenizer):
+    from trl_b200.experimental import utils as U
+
+    b = torch.tensor([[False, True, True], [False, False, False]])
+    assert U.first_true_indices(b).tolist() == [1, 3]
+    ids, mask = U.truncate_right(torch.tensor([[5, 6, 2, 7, 8]]), 2, 0)
+    assert ids.tolist() == [[5, 6, 2, 0, 0]] and mask.tolist() == [[1, 1, 1, 0, 0]]
+    assert U.pad_to_length(torch.ones(2, 3), 5, -1).shape == (2, 5)
+    assert U.pad_byte_offsets([(0, 2), (2, 5)], 4, "left").tolist() == [[-1, -1], [-1, -1], [0, 2], [2, 5]]
+    col = U.DPODataCollatorWithPadding(pad_token_id=0)
+    out = col([{"prompt_input_ids": [1, 2], "chosen_labels": [3], "tag": "a"}, {"prompt_input_ids": [1], "chosen_labels": [3, 4], "tag": "b"}])
+    assert out["prompt_input_ids"].tolist() == [[1, 2], [0, 1]] and out["chosen_labels"].tolist() == [[3, -100], [3, 4]]
+    model = make_tiny_model(num_labels=1)
+    q = torch.randint(5, 100, (2, 6))
+    q[1, 4:] = 0
+    per_tok, score, lens = U.get_reward(model, q, 0, 2)
+    assert per_tok.shape == (2, 6) and lens.tolist() == [5, 3] and torch.allclose(score[1], per_tok[1, 3])
+    ref = U.create_reference_model(make_tiny_model(), num_shared_layers=1)
+    assert not any(p.requires_grad for p in ref.parameters())
