@@ -1,0 +1,269 @@
+// Grouped (per-expert) bf16 GEMM on the 5th-generation tensor cores for mixture-of-experts layers.
+//
+//     C[r, :] = A[r, :] . W[e(r)]^T      rows of A are sorted by expert; offsets[e] .. offsets[e+1] belong to expert e
+//
+// Same persistent warp-specialised pipeline as the dense GEMM (warp 0 TMA producer, warp 1 tcgen05.mma issuer,
+// warps 2-5 epilogue, 128x256x64 tiles, 4-stage ring, two TMEM accumulators).  What differs:
+//   * the tile list is derived on the device from `offsets` (token counts per expert are only known on the GPU, and
+//     the launch must be capturable in a CUDA graph): every CTA builds the prefix of 128-row tiles per expert in shared
+//     memory and maps its work items through it;
+//   * the weight tile comes from a 3D tensor map (K, N, experts); the activation tile starts at the expert's first
+//     row, wherever that is; rows of the tile that belong to the next expert are computed and thrown away;
+//   * optional SwiGLU epilogue for the gate/up projection: the B tile is 128 gate rows + the matching 128 up rows, the
+//     epilogue writes silu(gate) * up, so the [tokens, 2I] intermediate never reaches memory.
+//
+// Replaces the per-expert loop of transformers' MoE blocks that the reference trains through
+// (trl/trainer/grpo_trainer.py forward of Qwen3-MoE style models).
+#include "common.cuh"
+
+namespace trlb {
+
+constexpr int GBM = 128, GBN = 256, GBK = 64, GSTAGES = 4;
+constexpr uint32_t GA_BYTES = GBM * GBK * 2, GB_BYTES = GBN * GBK * 2, GSTAGE_BYTES = GA_BYTES + GB_BYTES;
+constexpr int G_THREADS = 192;
+constexpr int G_MAX_EXPERTS = 1024;
+constexpr size_t G_SMEM = GSTAGES * GSTAGE_BYTES + 1024 + 256 + (G_MAX_EXPERTS + 1) * 4;
+
+struct GroupedParams {
+  int E, N, K, n_tiles, k_blocks;
+  int swiglu;          // 1: W is [E, 2*N, K] (gate rows then up rows), C gets N columns
+  const int* offsets;  // [E + 1] row offsets into A / C
+  __nv_bfloat16* C;
+  long long ldc;
+  int* status;
+};
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+
+__global__ void __launch_bounds__(G_THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const GroupedParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GSTAGES * GSTAGE_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + GSTAGES;
+  uint64_t* tfull_bar = bars + 2 * GSTAGES;
+  uint64_t* tempty_bar = bars + 2 * GSTAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * GSTAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* mt_prefix = reinterpret_cast<int*>(tmem_slot + 4);  // [E + 1] prefix of 128-row tiles per expert
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < GSTAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    int acc = 0;
+    mt_prefix[0] = 0;
+    for (int e = 0; e < p.E; ++e) {
+      const int cnt = p.offsets[e + 1] - p.offsets[e];
+      acc += (cnt + GBM - 1) / GBM;
+      mt_prefix[e + 1] = acc;
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_items = mt_prefix[p.E] * p.n_tiles;
+
+  // item -> (expert, first row, valid rows, n tile)
+  auto decode = [&](int item, int& e, int& row0, int& rows, int& nt) {
+    const int mt = item / p.n_tiles;
+    nt = item % p.n_tiles;
+    int lo = 0, hi = p.E;  // largest e with mt_prefix[e] <= mt
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (mt_prefix[mid] <= mt) lo = mid; else hi = mid;
+    }
+    e = lo;
+    row0 = p.offsets[e] + (mt - mt_prefix[e]) * GBM;
+    rows = min(GBM, p.offsets[e + 1] - row0);
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        int e, row0, rows, nt;
+        decode(item, e, row0, rows, nt);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 800 + stage)) { ok = false; break; }
+          uint8_t* sa = tiles + stage * GSTAGE_BYTES;
+          uint8_t* sb = sa + GA_BYTES;
+          mbar_expect_tx(&full_bar[stage], GSTAGE_BYTES);
+          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * GBK, row0);
+          if (p.swiglu) {  // 128 gate rows, then the 128 up rows of the same output columns
+            tma_load_3d(sb, &tmap_b, &full_bar[stage], kb * GBK, nt * 128, e);
+            tma_load_3d(sb + GB_BYTES / 2, &tmap_b, &full_bar[stage], kb * GBK, p.N + nt * 128, e);
+          } else {
+            tma_load_3d(sb, &tmap_b, &full_bar[stage], kb * GBK, nt * GBN, e);
+            tma_load_3d(sb + GB_BYTES / 2, &tmap_b, &full_bar[stage], kb * GBK, nt * GBN + 128, e);
+          }
+          if (++stage == GSTAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(GBM, GBN);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, 810 + acc)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tacc = tmem_base + (uint32_t)acc * GBN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 820 + stage)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + stage * GSTAGE_BYTES);
+          const uint64_t adesc = umma_desc_kmajor_sw128(sa);
+          const uint64_t bdesc = umma_desc_kmajor_sw128(sa + GA_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < GBK / 16; ++kk) umma_bf16_ss(tacc, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) != 0);
+          umma_commit(&empty_bar[stage]);
+          if (++stage == GSTAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull_bar[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      int e, row0, rows, nt;
+      decode(item, e, row0, rows, nt);
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, 830 + acc)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t tacc = tmem_base + (uint32_t)acc * GBN + ((uint32_t)(quarter * 32) << 16);
+      const bool row_ok = r < rows;
+      if (p.swiglu) {
+        const int col0 = nt * 128;
+#pragma unroll 1
+        for (int c = 0; c < 128; c += 32) {
+          float g[32], u[32];
+          tmem_ld_32x32(tacc + c, g);
+          tmem_ld_32x32(tacc + 128 + c, u);
+          tmem_ld_wait();
+          if (row_ok && col0 + c < p.N) {
+            __nv_bfloat16* dst = p.C + (long long)(row0 + r) * p.ldc + col0 + c;
+            if (col0 + c + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                uint4 o;
+                o.x = pack_bf16(silu_f(g[i]) * u[i], silu_f(g[i + 1]) * u[i + 1]);
+                o.y = pack_bf16(silu_f(g[i + 2]) * u[i + 2], silu_f(g[i + 3]) * u[i + 3]);
+                o.z = pack_bf16(silu_f(g[i + 4]) * u[i + 4], silu_f(g[i + 5]) * u[i + 5]);
+                o.w = pack_bf16(silu_f(g[i + 6]) * u[i + 6], silu_f(g[i + 7]) * u[i + 7]);
+                *reinterpret_cast<uint4*>(dst + i) = o;
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col0 + c + i < p.N) dst[i] = __float2bfloat16(silu_f(g[i]) * u[i]);
+            }
+          }
+        }
+      } else {
+        const int col0 = nt * GBN;
+#pragma unroll 1
+        for (int c = 0; c < GBN; c += 32) {
+          float v[32];
+          tmem_ld_32x32(tacc + c, v);
+          tmem_ld_wait();
+          if (row_ok && col0 + c < p.N) {
+            __nv_bfloat16* dst = p.C + (long long)(row0 + r) * p.ldc + col0 + c;
+            if (col0 + c + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                uint4 o;
+                o.x = pack_bf16(v[i], v[i + 1]);
+                o.y = pack_bf16(v[i + 2], v[i + 3]);
+                o.z = pack_bf16(v[i + 4], v[i + 5]);
+                o.w = pack_bf16(v[i + 6], v[i + 7]);
+                *reinterpret_cast<uint4*>(dst + i) = o;
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col0 + c + i < p.N) dst[i] = __float2bfloat16(v[i]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace trlb
+
+using namespace trlb;
+
+// A [rows, K] bf16 (row stride lda), rows sorted by expert; W [E, Nw, K] bf16 contiguous with Nw = N (plain) or
+// 2 * N (swiglu: gate rows then up rows); offsets [E + 1] int32 on the device; C [rows, N] bf16 (row stride ldc).
+// `rows` is the allocated row count of A and C (an upper bound of offsets[E]).
+TRLB_API int trlb_grouped_gemm_bf16(const void* A, const void* W, const int* offsets, void* C, long long rows, int E, int N,
+                                    int K, long long lda, long long ldc, int swiglu, int* status, cudaStream_t st) {
+  if (rows <= 0 || E <= 0) return 0;
+  if (E > G_MAX_EXPERTS || (K % 8) != 0 || (lda % 8) != 0) return -130;
+  const long long Nw = swiglu ? 2LL * N : N;
+  CUtensorMap ta, tb;
+  int r = trlb_host::make_tmap_2d_bf16(&ta, A, (uint64_t)rows, (uint64_t)K, (uint64_t)lda, GBM, GBK);
+  if (r) return -131;
+  r = trlb_host::make_tmap_3d_bf16(&tb, W, (uint64_t)K, (uint64_t)Nw, (uint64_t)E, (uint64_t)K, (uint64_t)Nw * K, GBK, 128, 1);
+  if (r) return -132;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G_SMEM);
+    attr_set = true;
+  }
+  GroupedParams p;
+  p.E = E; p.N = N; p.K = K; p.swiglu = swiglu;
+  p.n_tiles = swiglu ? (N + 127) / 128 : (N + GBN - 1) / GBN;
+  p.k_blocks = (K + GBK - 1) / GBK;
+  p.offsets = offsets; p.C = (__nv_bfloat16*)C; p.ldc = ldc; p.status = status;
+  // the number of items depends on device data: launch one CTA per SM (an idle CTA costs a few microseconds)
+  long long max_items = ((rows + GBM - 1) / GBM + E) * p.n_tiles;
+  int grid = trlb_host::sm_count();
+  if (max_items < grid) grid = (int)max_items;
+  grouped_gemm_kernel<<<grid, G_THREADS, G_SMEM, st>>>(ta, tb, p);
+  return (int)cudaGetLastError();
+}

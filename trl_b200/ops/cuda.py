@@ -305,10 +305,99 @@ def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True):
                        window_size=(-1, 0) if causal else (-1, -1))
 
 
-def moe_experts(hidden, gate_up_w, down_w, topk_w, topk_idx):
-    from ..oracle.ops import moe_experts as ref
+def grouped_gemm(a, w, offsets, n_out, swiglu=False, out=None):
+    """Per-expert GEMM on tcgen05: rows of ``a`` [R, K] are sorted by expert, ``offsets`` [E + 1] int32 on the device,
+    ``w`` [E, n_out (or 2 * n_out with swiglu), K].  Returns [R, n_out]; with ``swiglu`` the gate / up halves are
+    combined in the epilogue."""
+    R, Kd = a.shape
+    E = w.shape[0]
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and a.stride(1) == 1
+    assert w.shape[1] == (2 * n_out if swiglu else n_out) and w.shape[2] == Kd
+    if out is None:
+        out = torch.empty(R, n_out, dtype=torch.bfloat16, device=a.device)
+    _chk(lib().trlb_grouped_gemm_bf16(_p(a), _p(w), _p(offsets), _p(out), c_longlong(R), c_int(E), c_int(n_out), c_int(Kd),
+                                      c_longlong(a.stride(0)), c_longlong(out.stride(0)), c_int(int(swiglu)),
+                                      _p(status_buffer(a.device)), _s()), "grouped_gemm")
+    return out
 
-    return ref(hidden, gate_up_w, down_w, topk_w, topk_idx)
+
+def _grouped_mm_ref(a, b, offsets_host, transpose_b):
+    """Library fallback for the backward products: per-expert cuBLAS on row slices."""
+    outs = []
+    for e in range(len(offsets_host) - 1):
+        s, t = offsets_host[e], offsets_host[e + 1]
+        outs.append(a[s:t] @ (b[e].t() if transpose_b else b[e]))
+    return torch.cat(outs) if outs else a.new_zeros(0, b.shape[1 if transpose_b else 2])
+
+
+class _MoeExpertsFn(torch.autograd.Function):
+    """Sort tokens by expert, gate/up grouped GEMM with SwiGLU epilogue, down grouped GEMM, weighted combine.
+    Backward recomputes the gate/up pre-activations with the same kernel and uses library GEMMs per expert for the
+    transposed products."""
+
+    @staticmethod
+    def forward(ctx, hidden, gate_up_w, down_w, topk_w, topk_idx):
+        T, H = hidden.shape
+        k = topk_idx.shape[1]
+        E, I2, _ = gate_up_w.shape
+        I = I2 // 2
+        flat_e = topk_idx.reshape(-1)
+        order = torch.argsort(flat_e, stable=True)
+        counts = torch.bincount(flat_e, minlength=E)
+        offsets = torch.zeros(E + 1, dtype=torch.int32, device=hidden.device)
+        offsets[1:] = counts.cumsum(0)
+        tok = order // k
+        x_perm = hidden.index_select(0, tok)
+        act = grouped_gemm(x_perm, gate_up_w, offsets, I, swiglu=True)
+        y_perm = grouped_gemm(act, down_w, offsets, H)
+        w_perm = topk_w.reshape(-1).index_select(0, order).float()
+        out = torch.zeros(T, H, dtype=torch.float32, device=hidden.device)
+        out.index_add_(0, tok, y_perm.float() * w_perm[:, None])
+        ctx.save_for_backward(hidden, gate_up_w, down_w, topk_w, order, offsets, act, y_perm)
+        ctx.k = k
+        return out.to(hidden.dtype)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        hidden, gate_up_w, down_w, topk_w, order, offsets, act, y_perm = ctx.saved_tensors
+        k = ctx.k
+        E, I2, H = gate_up_w.shape
+        I = I2 // 2
+        tok = order // k
+        offs = offsets.tolist()  # host copy for the per-expert library GEMMs
+        w_perm = topk_w.reshape(-1).index_select(0, order).float()
+        d_rows = d_out.index_select(0, tok)
+        d_w_perm = (d_rows.float() * y_perm.float()).sum(-1)
+        d_topk_w = torch.zeros(topk_w.numel(), dtype=torch.float32, device=d_out.device)
+        d_topk_w[order] = d_w_perm
+        d_y = (d_rows.float() * w_perm[:, None]).to(hidden.dtype)
+        # down projection: y = act @ Wd[e]^T, Wd[e] is [H, I]
+        d_act = _grouped_mm_ref(d_y, down_w, offs, transpose_b=False)
+        d_down = torch.zeros_like(down_w)
+        x_perm = hidden.index_select(0, tok)
+        gu = grouped_gemm(x_perm, gate_up_w, offsets, I2, swiglu=False)  # recompute the pre-activations
+        g, u = gu[:, :I].float(), gu[:, I:].float()
+        sg = torch.sigmoid(g)
+        d_g = d_act.float() * u * sg * (1 + g * (1 - sg))
+        d_u = d_act.float() * g * sg
+        d_gu = torch.cat([d_g, d_u], 1).to(hidden.dtype)
+        d_x = _grouped_mm_ref(d_gu, gate_up_w, offs, transpose_b=False)
+        d_gate_up = torch.zeros_like(gate_up_w)
+        for e in range(E):
+            s, t = offs[e], offs[e + 1]
+            if t > s:
+                d_down[e] = d_y[s:t].t() @ act[s:t]
+                d_gate_up[e] = d_gu[s:t].t() @ x_perm[s:t]
+        d_hidden = torch.zeros(hidden.shape, dtype=torch.float32, device=d_out.device).index_add_(0, tok, d_x.float())
+        return d_hidden.to(hidden.dtype), d_gate_up, d_down, d_topk_w.view_as(topk_w).to(topk_w.dtype), None
+
+
+def moe_experts(hidden, gate_up_w, down_w, topk_w, topk_idx):
+    if hidden.dtype != torch.bfloat16 or hidden.shape[1] % 8 or (gate_up_w.shape[1] // 2) % 8:
+        from ..oracle.ops import moe_experts as ref
+
+        return ref(hidden, gate_up_w, down_w, topk_w, topk_idx)
+    return _MoeExpertsFn.apply(hidden.contiguous(), gate_up_w, down_w, topk_w, topk_idx)
 
 
 # -------------------------------------------------------------------------------------------
