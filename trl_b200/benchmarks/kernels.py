@@ -58,7 +58,7 @@ def timeit(fn, iters, warmup):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "lmhead", "lmhead_bwd", "decode_attn", "rmsnorm", "adamw", "grpo_loss"])
+    ap.add_argument("kernel", choices=["gemm", "lmhead", "lmhead_bwd", "decode_attn", "rmsnorm", "adamw", "grpo_loss", "moe"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4608)
     ap.add_argument("--k", type=int, default=3584)
@@ -136,6 +136,37 @@ def main():
             out[f"tcgen05_splits{sp}_ms"] = ms2
             out[f"tcgen05_splits{sp}_frac_of_copy_bw"] = byt / ms2 / 1e6 / hbm
         K.check_status(dev)
+    elif a.kernel == "moe":
+        # Qwen3-30B-A3B expert shapes: 128 experts, hidden 2048, expert FFN 768, top-8; a.t tokens
+        E, H, I, k = 128, 2048, 768, 8
+        x = (torch.randn(a.t, H, device=dev) * 0.5).to(torch.bfloat16)
+        gu = (torch.randn(E, 2 * I, H, device=dev) / H ** 0.5).to(torch.bfloat16)
+        dw = (torch.randn(E, H, I, device=dev) / I ** 0.5).to(torch.bfloat16)
+        tw, ti = torch.softmax(torch.randn(a.t, E, device=dev), -1).topk(k, -1)
+        with torch.no_grad():
+            ms = timeit(lambda: K.moe_experts(x, gu, dw, tw, ti), a.iters, a.warmup)
+        flops = 2.0 * a.t * k * H * 3 * I
+        out.update(tokens=a.t, experts=E, top_k=k, moe_block_ms=ms, tflops=flops / ms / 1e9,
+                   frac_of_cublas_burst=flops / ms / 1e9 / tfl)
+        flat = ti.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        offsets = torch.zeros(E + 1, dtype=torch.int32, device=dev)
+        offsets[1:] = torch.bincount(flat, minlength=E).cumsum(0)
+        xp = x[order // k]
+        ms1 = timeit(lambda: K.grouped_gemm(xp, gu, offsets, I, swiglu=True), a.iters, a.warmup)
+        out.update(gate_up_swiglu_ms=ms1, gate_up_tflops=2.0 * a.t * k * H * 2 * I / ms1 / 1e9)
+        if a.baseline:
+            from trl_b200.oracle.ops import moe_experts as loop
+
+            with torch.no_grad():
+                out["expert_loop_ms"] = timeit(lambda: loop(x, gu, dw, tw, ti), max(2, a.iters // 3), 1)
+            if hasattr(torch, "_grouped_mm"):
+                try:
+                    offs = offsets[1:].contiguous()
+                    gut = gu.transpose(1, 2)
+                    out["torch_grouped_mm_gate_up_ms"] = timeit(lambda: torch._grouped_mm(xp, gut, offs=offs), a.iters, a.warmup)
+                except Exception as e:  # library kernel not built for this GPU
+                    out["torch_grouped_mm"] = f"unavailable: {type(e).__name__}"
     elif a.kernel == "rmsnorm":
         x = torch.randn(a.t, a.h, device=dev, dtype=torch.bfloat16)
         w = torch.ones(a.h, device=dev, dtype=torch.bfloat16)

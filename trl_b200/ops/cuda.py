@@ -343,19 +343,22 @@ class _MoeExpertsFn(torch.autograd.Function):
         I = I2 // 2
         flat_e = topk_idx.reshape(-1)
         order = torch.argsort(flat_e, stable=True)
-        counts = torch.bincount(flat_e, minlength=E)
+        counts = torch.zeros(E, dtype=torch.int32, device=hidden.device)
+        counts.scatter_add_(0, flat_e, torch.ones_like(flat_e, dtype=torch.int32))  # no host sync: graph-capturable
         offsets = torch.zeros(E + 1, dtype=torch.int32, device=hidden.device)
         offsets[1:] = counts.cumsum(0)
         tok = order // k
         x_perm = hidden.index_select(0, tok)
         act = grouped_gemm(x_perm, gate_up_w, offsets, I, swiglu=True)
         y_perm = grouped_gemm(act, down_w, offsets, H)
-        w_perm = topk_w.reshape(-1).index_select(0, order).float()
-        out = torch.zeros(T, H, dtype=torch.float32, device=hidden.device)
-        out.index_add_(0, tok, y_perm.float() * w_perm[:, None])
+        inv = torch.empty(T * k, dtype=torch.int32, device=hidden.device)
+        inv[order] = torch.arange(T * k, dtype=torch.int32, device=hidden.device)
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=hidden.device)
+        _chk(lib().trlb_moe_combine(_p(y_perm), _p(inv), _p(topk_w.float().contiguous()), _p(out), c_int(T), c_int(k),
+                                    c_int(H), _s()), "moe_combine")
         ctx.save_for_backward(hidden, gate_up_w, down_w, topk_w, order, offsets, act, y_perm)
         ctx.k = k
-        return out.to(hidden.dtype)
+        return out
 
     @staticmethod
     def backward(ctx, d_out):

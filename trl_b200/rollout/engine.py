@@ -163,7 +163,7 @@ class RolloutEngine:
         self.step_counter = torch.zeros(1, **i32)
         self.tok = torch.zeros(max_num_seqs, **i32)
         self.logp = torch.zeros(max_num_seqs, dtype=torch.float32, device=self.dev)
-        self.poll_every, self.use_graph = poll_every, use_cuda_graph and not cfg.is_moe
+        self.poll_every, self.use_graph = poll_every, use_cuda_graph
         # enough CTAs for ~4 per SM: the kernel is latency-bound on KV loads, occupancy hides it
         self.kv_splits = kv_splits or max(1, min(8, -(-(4 * 148) // max(1, max_num_seqs * Hk))))
         if self.attn_tc and not kv_splits:  # persistent CTAs, one per SM: split only to give every SM an item
