@@ -9,6 +9,10 @@
 //     memory and maps its work items through it;
 //   * the weight tile comes from a 3D tensor map (K, N, experts); the activation tile starts at the expert's first
 //     row, wherever that is; rows of the tile that belong to the next expert are computed and thrown away;
+//   * segment mode (expert parallelism): a segment is (local expert, source rank); its activation rows are read with TMA
+//     straight from the source rank's buffer over NVLink (no cluster sharing of those tiles), and the output rows are
+//     stored straight into a destination rank's buffer, so the dispatch all-to-all rides on the loads of the first GEMM
+//     and the combine all-to-all on the stores of the second;
 //   * optional SwiGLU epilogue for the gate/up projection: the B tile is 128 gate rows + the matching 128 up rows, the
 //     epilogue writes silu(gate) * up, so the [tokens, 2I] intermediate never reaches memory.
 //
@@ -24,19 +28,33 @@ constexpr int G_THREADS = 192;
 constexpr int G_MAX_EXPERTS = 1024;
 constexpr size_t G_SMEM = GSTAGES * GSTAGE_BYTES + 1024 + 256 + (G_MAX_EXPERTS + 1) * 4;
 
+struct TmapArray {
+  CUtensorMap m[8];
+};
+
 struct GroupedParams {
   int E, N, K, n_tiles, k_blocks;
   int swiglu;          // 1: W is [E, 2*N, K] (gate rows then up rows), C gets N columns
-  const int* offsets;  // [E + 1] row offsets into A / C
+  const int* offsets;  // [E + 1] row offsets into A / C (plain mode)
   __nv_bfloat16* C;
   long long ldc;
   int* status;
+  // segment mode (n_seg > 0): E counts segments; per segment: rows, A source (tensor-map index) and first row,
+  // C destination (index into c_dst) and first row, weight index
+  int n_seg;
+  const int* seg_rows;
+  const int* seg_a_src;
+  const int* seg_a_row;
+  const int* seg_c_dst;
+  const int* seg_c_row;
+  const int* seg_w;
+  __nv_bfloat16* c_dst[8];
 };
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 
 __global__ void __launch_bounds__(G_THREADS, 1)
-grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+grouped_gemm_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GroupedParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -62,15 +80,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     *abort_flag = 0;
     mbar_fence_init();
-    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmaps_a.m[0]);
     tma_prefetch_desc(&tmap_b);
-    int acc = 0;
+  }
+  // 128-row tiles per group (expert or segment), then their prefix
+  for (int e = threadIdx.x; e < p.E; e += G_THREADS) {
+    const int cnt = p.n_seg ? p.seg_rows[e] : p.offsets[e + 1] - p.offsets[e];
+    mt_prefix[e + 1] = (cnt + GBM - 1) / GBM;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
     mt_prefix[0] = 0;
-    for (int e = 0; e < p.E; ++e) {
-      const int cnt = p.offsets[e + 1] - p.offsets[e];
-      acc += (cnt + GBM - 1) / GBM;
-      mt_prefix[e + 1] = acc;
-    }
+    for (int e = 0; e < p.E; ++e) mt_prefix[e + 1] += mt_prefix[e];
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -82,8 +103,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const uint32_t tmem_base = *tmem_slot;
   const int total_items = mt_prefix[p.E] * p.n_tiles;
 
-  // item -> (expert, first row, valid rows, n tile)
-  auto decode = [&](int item, int& e, int& row0, int& rows, int& nt) {
+  // item -> (group, first A row, valid rows, n tile, first C row)
+  auto decode = [&](int item, int& e, int& row0, int& rows, int& nt, int& crow0) {
     const int mt = item / p.n_tiles;
     nt = item % p.n_tiles;
     int lo = 0, hi = p.E;  // largest e with mt_prefix[e] <= mt
@@ -92,8 +113,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (mt_prefix[mid] <= mt) lo = mid; else hi = mid;
     }
     e = lo;
-    row0 = p.offsets[e] + (mt - mt_prefix[e]) * GBM;
-    rows = min(GBM, p.offsets[e + 1] - row0);
+    const int m_off = (mt - mt_prefix[e]) * GBM;
+    if (p.n_seg) {
+      row0 = p.seg_a_row[e] + m_off;
+      crow0 = p.seg_c_row[e] + m_off;
+      rows = min(GBM, p.seg_rows[e] - m_off);
+    } else {
+      row0 = p.offsets[e] + m_off;
+      crow0 = row0;
+      rows = min(GBM, p.offsets[e + 1] - row0);
+    }
   };
 
   if (warp == 0) {
@@ -102,20 +131,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t phase = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        int e, row0, rows, nt;
-        decode(item, e, row0, rows, nt);
+        int e, row0, rows, nt, crow0;
+        decode(item, e, row0, rows, nt, crow0);
+        const CUtensorMap* ta = &tmaps_a.m[p.n_seg ? p.seg_a_src[e] : 0];  // segment mode: possibly a peer's buffer
+        const int we = p.n_seg ? p.seg_w[e] : e;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 800 + stage)) { ok = false; break; }
           uint8_t* sa = tiles + stage * GSTAGE_BYTES;
           uint8_t* sb = sa + GA_BYTES;
           mbar_expect_tx(&full_bar[stage], GSTAGE_BYTES);
-          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * GBK, row0);
+          tma_load_2d(sa, ta, &full_bar[stage], kb * GBK, row0);
           if (p.swiglu) {  // 128 gate rows, then the 128 up rows of the same output columns
-            tma_load_3d(sb, &tmap_b, &full_bar[stage], kb * GBK, nt * 128, e);
-            tma_load_3d(sb + GB_BYTES / 2, &tmap_b, &full_bar[stage], kb * GBK, p.N + nt * 128, e);
+            tma_load_3d(sb, &tmap_b, &full_bar[stage], kb * GBK, nt * 128, we);
+            tma_load_3d(sb + GB_BYTES / 2, &tmap_b, &full_bar[stage], kb * GBK, p.N + nt * 128, we);
           } else {
-            tma_load_3d(sb, &tmap_b, &full_bar[stage], kb * GBK, nt * GBN, e);
-            tma_load_3d(sb + GB_BYTES / 2, &tmap_b, &full_bar[stage], kb * GBK, nt * GBN + 128, e);
+            tma_load_3d(sb, &tmap_b, &full_bar[stage], kb * GBK, nt * GBN, we);
+            tma_load_3d(sb + GB_BYTES / 2, &tmap_b, &full_bar[stage], kb * GBK, nt * GBN + 128, we);
           }
           if (++stage == GSTAGES) { stage = 0; phase ^= 1; }
         }
@@ -156,8 +187,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-      int e, row0, rows, nt;
-      decode(item, e, row0, rows, nt);
+      int e, row0, rows, nt, crow0;
+      decode(item, e, row0, rows, nt, crow0);
+      __nv_bfloat16* cbase = p.n_seg ? p.c_dst[p.seg_c_dst[e]] : p.C;  // segment mode: possibly a peer's buffer
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, 830 + acc)) { ok = false; break; }
       tc_fence_after();
       const uint32_t tacc = tmem_base + (uint32_t)acc * GBN + ((uint32_t)(quarter * 32) << 16);
@@ -171,7 +203,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           tmem_ld_32x32(tacc + 128 + c, u);
           tmem_ld_wait();
           if (row_ok && col0 + c < p.N) {
-            __nv_bfloat16* dst = p.C + (long long)(row0 + r) * p.ldc + col0 + c;
+            __nv_bfloat16* dst = cbase + (long long)(crow0 + r) * p.ldc + col0 + c;
             if (col0 + c + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
               for (int i = 0; i < 32; i += 8) {
@@ -196,7 +228,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           tmem_ld_32x32(tacc + c, v);
           tmem_ld_wait();
           if (row_ok && col0 + c < p.N) {
-            __nv_bfloat16* dst = p.C + (long long)(row0 + r) * p.ldc + col0 + c;
+            __nv_bfloat16* dst = cbase + (long long)(crow0 + r) * p.ldc + col0 + c;
             if (col0 + c + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
               for (int i = 0; i < 32; i += 8) {
@@ -245,9 +277,11 @@ TRLB_API int trlb_grouped_gemm_bf16(const void* A, const void* W, const int* off
   if (rows <= 0 || E <= 0) return 0;
   if (E > G_MAX_EXPERTS || (K % 8) != 0 || (lda % 8) != 0) return -130;
   const long long Nw = swiglu ? 2LL * N : N;
-  CUtensorMap ta, tb;
-  int r = trlb_host::make_tmap_2d_bf16(&ta, A, (uint64_t)rows, (uint64_t)K, (uint64_t)lda, GBM, GBK);
+  TmapArray ta;
+  CUtensorMap tb;
+  int r = trlb_host::make_tmap_2d_bf16(&ta.m[0], A, (uint64_t)rows, (uint64_t)K, (uint64_t)lda, GBM, GBK);
   if (r) return -131;
+  for (int i = 1; i < 8; ++i) ta.m[i] = ta.m[0];
   r = trlb_host::make_tmap_3d_bf16(&tb, W, (uint64_t)K, (uint64_t)Nw, (uint64_t)E, (uint64_t)K, (uint64_t)Nw * K, GBK, 128, 1);
   if (r) return -132;
   static bool attr_set = false;
@@ -255,13 +289,54 @@ TRLB_API int trlb_grouped_gemm_bf16(const void* A, const void* W, const int* off
     cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G_SMEM);
     attr_set = true;
   }
-  GroupedParams p;
+  GroupedParams p = {};
   p.E = E; p.N = N; p.K = K; p.swiglu = swiglu;
   p.n_tiles = swiglu ? (N + 127) / 128 : (N + GBN - 1) / GBN;
   p.k_blocks = (K + GBK - 1) / GBK;
   p.offsets = offsets; p.C = (__nv_bfloat16*)C; p.ldc = ldc; p.status = status;
   // the number of items depends on device data: launch one CTA per SM (an idle CTA costs a few microseconds)
   long long max_items = ((rows + GBM - 1) / GBM + E) * p.n_tiles;
+  int grid = trlb_host::sm_count();
+  if (max_items < grid) grid = (int)max_items;
+  grouped_gemm_kernel<<<grid, G_THREADS, G_SMEM, st>>>(ta, tb, p);
+  return (int)cudaGetLastError();
+}
+
+// Segment mode for expert parallelism.  a_bases[i] / c_bases[i] (i < n_bufs <= 8): buffers that the segment tables index
+// (this rank's own and its peers' mappings of the same symmetric buffers); every A buffer is [a_rows, K] with row stride
+// lda, every C buffer has row stride ldc.  seg_* are int32 device arrays of length n_seg; W [E_local, Nw, K].
+// max_rows bounds the total number of rows over all segments (sizes the grid only).
+TRLB_API int trlb_grouped_gemm_seg_bf16(const unsigned long long* a_bases, const unsigned long long* c_bases, int n_bufs,
+                                        long long a_rows, const void* W, int E_local, int n_seg, const int* seg_rows,
+                                        const int* seg_a_src, const int* seg_a_row, const int* seg_c_dst,
+                                        const int* seg_c_row, const int* seg_w, long long max_rows, int N, int K,
+                                        long long lda, long long ldc, int swiglu, int* status, cudaStream_t st) {
+  if (n_seg <= 0 || max_rows <= 0) return 0;
+  if (n_seg > G_MAX_EXPERTS || n_bufs < 1 || n_bufs > 8 || (K % 8) != 0 || (lda % 8) != 0) return -133;
+  const long long Nw = swiglu ? 2LL * N : N;
+  TmapArray ta;
+  CUtensorMap tb;
+  for (int i = 0; i < 8; ++i) {
+    const void* base = reinterpret_cast<const void*>(a_bases[i < n_bufs ? i : 0]);
+    if (trlb_host::make_tmap_2d_bf16(&ta.m[i], base, (uint64_t)a_rows, (uint64_t)K, (uint64_t)lda, GBM, GBK)) return -134;
+  }
+  if (trlb_host::make_tmap_3d_bf16(&tb, W, (uint64_t)K, (uint64_t)Nw, (uint64_t)E_local, (uint64_t)K, (uint64_t)Nw * K, GBK,
+                                   128, 1))
+    return -135;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G_SMEM);
+    attr_set = true;
+  }
+  GroupedParams p = {};
+  p.E = n_seg; p.n_seg = n_seg; p.N = N; p.K = K; p.swiglu = swiglu;
+  p.n_tiles = swiglu ? (N + 127) / 128 : (N + GBN - 1) / GBN;
+  p.k_blocks = (K + GBK - 1) / GBK;
+  p.ldc = ldc; p.status = status;
+  p.seg_rows = seg_rows; p.seg_a_src = seg_a_src; p.seg_a_row = seg_a_row;
+  p.seg_c_dst = seg_c_dst; p.seg_c_row = seg_c_row; p.seg_w = seg_w;
+  for (int i = 0; i < 8; ++i) p.c_dst[i] = reinterpret_cast<__nv_bfloat16*>(c_bases[i < n_bufs ? i : 0]);
+  long long max_items = ((max_rows + GBM - 1) / GBM + n_seg) * p.n_tiles;
   int grid = trlb_host::sm_count();
   if (max_items < grid) grid = (int)max_items;
   grouped_gemm_kernel<<<grid, G_THREADS, G_SMEM, st>>>(ta, tb, p);

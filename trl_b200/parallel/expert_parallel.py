@@ -1,0 +1,169 @@
+"""Expert-parallel MoE block: experts are split over the ranks of a group, tokens stay where they are.
+
+Forward on every rank, for its local experts and every source rank s (a *segment*):
+
+    x_perm  this rank's tokens, sorted by global expert, in a symmetric buffer
+    GEMM 1  act[segment rows] = swiglu(x_perm_of_rank_s[rows of expert e] . W_gate_up[e]^T)   A tiles: TMA from rank s
+    GEMM 2  y_perm_of_rank_s[rows of expert e] = act[segment rows] . W_down[e]^T              C rows: stored to rank s
+    combine out[t] = sum_j w[t, j] * y_perm[position of (t, j)]                               local
+
+so the dispatch all-to-all is the loads of the first grouped GEMM and the combine all-to-all is the stores of the second
+(``trlb_grouped_gemm_seg_bf16``).  Only the per-expert row offsets ([E + 1] int32 per rank) travel through NCCL.
+The reference reaches expert parallelism through DeepSpeed / accelerate sharding of transformers MoE blocks
+(trl/accelerate_configs/*.yaml); it has no fused path.
+
+Backward (training) moves rows with ``all_to_all_single`` and uses library GEMMs per expert; the gate/up
+pre-activations are recomputed with the fused kernel."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_longlong
+
+import torch
+import torch.distributed as td
+
+from .symm import SymmArena
+
+
+class ExpertParallelMoE:
+    def __init__(self, group, num_experts: int, hidden: int, intermediate: int, top_k: int, max_tokens: int, device):
+        self.group = group if group is not None else td.group.WORLD
+        self.world, self.rank = td.get_world_size(self.group), td.get_rank(self.group)
+        if num_experts % self.world:
+            raise ValueError("the number of experts must be divisible by the expert-parallel size")
+        self.E, self.E_loc, self.H, self.I, self.k = num_experts, num_experts // self.world, hidden, intermediate, top_k
+        self.max_rows = max_tokens * top_k
+        self.dev = device
+        row_bytes = hidden * 2
+        self.arena = SymmArena(2 * (self.max_rows * row_bytes + 256) + 4096, device, self.group)
+        self.x_buf, self.x_off = self.arena.carve(self.max_rows * hidden, torch.bfloat16)
+        self.y_buf, self.y_off = self.arena.carve(self.max_rows * hidden, torch.bfloat16)
+        self.x_buf, self.y_buf = self.x_buf.view(self.max_rows, hidden), self.y_buf.view(self.max_rows, hidden)
+        self.act = torch.empty(self.world * self.max_rows, intermediate, dtype=torch.bfloat16, device=device)
+        self._sync = torch.zeros(1, dtype=torch.float32, device=device)
+        self._a_x = (ctypes.c_ulonglong * self.world)(*[p + self.x_off for p in self.arena.peer_ptrs])
+        self._c_y = (ctypes.c_ulonglong * self.world)(*[p + self.y_off for p in self.arena.peer_ptrs])
+        self._self_act = (ctypes.c_ulonglong * 1)(self.act.data_ptr())
+
+    # ---- routing tables ---------------------------------------------------------------------------------------------
+    def _route(self, topk_idx):
+        T, k = topk_idx.shape
+        flat = topk_idx.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        counts = torch.zeros(self.E, dtype=torch.int32, device=self.dev)
+        counts.scatter_add_(0, flat, torch.ones_like(flat, dtype=torch.int32))
+        offsets = torch.zeros(self.E + 1, dtype=torch.int32, device=self.dev)
+        offsets[1:] = counts.cumsum(0)
+        all_off = torch.empty(self.world, self.E + 1, dtype=torch.int32, device=self.dev)
+        td.all_gather_into_tensor(all_off, offsets, group=self.group)
+        e0 = self.rank * self.E_loc
+        loc = all_off[:, e0:e0 + self.E_loc + 1]                         # [W, E_loc + 1]
+        cnt = (loc[:, 1:] - loc[:, :-1]).t().contiguous()                # [E_loc, W] segment order: expert-major
+        seg_rows = cnt.reshape(-1)
+        seg_act_row = (seg_rows.cumsum(0) - seg_rows).to(torch.int32)    # compact local layout of act
+        seg_src = torch.arange(self.world, dtype=torch.int32, device=self.dev).repeat(self.E_loc)
+        seg_src_row = loc[:, :-1].t().contiguous().reshape(-1)           # first row of the segment in the source's buffers
+        seg_w = torch.arange(self.E_loc, dtype=torch.int32, device=self.dev).repeat_interleave(self.world)
+        zeros = torch.zeros_like(seg_src)
+        return order, offsets, all_off, dict(rows=seg_rows.contiguous(), act_row=seg_act_row, src=seg_src,
+                                             src_row=seg_src_row, w=seg_w, zeros=zeros)
+
+    def _seg_gemm(self, a_bases, c_bases, n_bufs, a_rows, w, seg, a_src, a_row, c_dst, c_row, n_out, k_dim, lda, ldc, swiglu):
+        from ..ops.cuda import _chk, _p, _s, lib, status_buffer
+
+        _chk(lib().trlb_grouped_gemm_seg_bf16(a_bases, c_bases, c_int(n_bufs), c_longlong(a_rows), _p(w), c_int(w.shape[0]),
+                                              c_int(seg["rows"].numel()), _p(seg["rows"]), _p(a_src), _p(a_row), _p(c_dst),
+                                              _p(c_row), _p(seg["w"]), c_longlong(self.world * self.max_rows), c_int(n_out),
+                                              c_int(k_dim), c_longlong(lda), c_longlong(ldc), c_int(int(swiglu)),
+                                              _p(status_buffer(self.dev)), _s()), "grouped_gemm_seg")
+
+    def _device_barrier(self):
+        td.all_reduce(self._sync, group=self.group)  # stream-ordered: completes when every rank has reached it
+
+    # ---- forward ----------------------------------------------------------------------------------------------------------
+    def forward_nograd(self, hidden, gate_up_local, down_local, topk_w, topk_idx, keep=None):
+        from ..ops.cuda import _chk, _p, _s, lib
+
+        T, H = hidden.shape
+        k = topk_idx.shape[1]
+        if T * k > self.max_rows:
+            raise ValueError(f"{T} tokens x top-{k} exceeds the expert-parallel buffers ({self.max_rows} rows)")
+        order, offsets, all_off, seg = self._route(topk_idx)
+        tok = order // k
+        torch.index_select(hidden, 0, tok, out=self.x_buf[:T * k])
+        self._device_barrier()  # every rank's x rows are in place (and nobody still reads the previous layer's)
+        self._seg_gemm(self._a_x, self._self_act, self.world, self.max_rows, gate_up_local, seg, seg["src"], seg["src_row"],
+                       seg["zeros"], seg["act_row"], self.I, H, H, self.I, True)
+        self._seg_gemm(self._self_act, self._c_y, self.world, self.world * self.max_rows, down_local, seg, seg["zeros"],
+                       seg["act_row"], seg["src"], seg["src_row"], H, self.I, self.I, H, False)
+        self._device_barrier()  # all peers have stored my y rows
+        inv = torch.empty(T * k, dtype=torch.int32, device=self.dev)
+        inv[order] = torch.arange(T * k, dtype=torch.int32, device=self.dev)
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=self.dev)
+        _chk(lib().trlb_moe_combine(_p(self.y_buf), _p(inv), _p(topk_w.float().contiguous()), _p(out), c_int(T), c_int(k),
+                                    c_int(H), _s()), "moe_combine")
+        if keep is not None:
+            keep.update(order=order, offsets=offsets, all_off=all_off, seg=seg, y_perm=self.y_buf[:T * k].clone())
+        return out
+
+    def __call__(self, hidden, gate_up_local, down_local, topk_w, topk_idx):
+        if not torch.is_grad_enabled() or not (hidden.requires_grad or gate_up_local.requires_grad):
+            return self.forward_nograd(hidden, gate_up_local, down_local, topk_w, topk_idx)
+        return _EpMoeFn.apply(hidden, gate_up_local, down_local, topk_w, topk_idx, self)
+
+
+class _EpMoeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, gate_up_local, down_local, topk_w, topk_idx, ep: ExpertParallelMoE):
+        keep: dict = {}
+        out = ep.forward_nograd(hidden, gate_up_local, down_local, topk_w, topk_idx, keep)
+        ctx.ep, ctx.keep, ctx.k = ep, keep, topk_idx.shape[1]
+        ctx.save_for_backward(hidden, gate_up_local, down_local, topk_w)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        ep, keep, k = ctx.ep, ctx.keep, ctx.k
+        hidden, gu_w, dn_w, topk_w = ctx.saved_tensors
+        W, E_loc, I, H = ep.world, ep.E_loc, ep.I, ep.H
+        order, all_off = keep["order"], keep["all_off"].cpu()
+        tok = order // k
+        w_perm = topk_w.reshape(-1).index_select(0, order).float()
+        d_rows = d_out.index_select(0, tok)
+        d_topk = torch.zeros(topk_w.numel(), dtype=torch.float32, device=d_out.device)
+        d_topk[order] = (d_rows.float() * keep["y_perm"].float()).sum(-1)
+        d_y = (d_rows.float() * w_perm[:, None]).to(hidden.dtype)
+        x_perm = hidden.index_select(0, tok)
+        # rows this rank sends to rank r: its tokens for r's experts (contiguous in expert-sorted order)
+        mine = all_off[ep.rank]
+        send = [int(mine[(r + 1) * E_loc] - mine[r * E_loc]) for r in range(W)]
+        e0 = ep.rank * E_loc
+        recv = [int(all_off[s, e0 + E_loc] - all_off[s, e0]) for s in range(W)]
+
+        def exchange(t, send_counts, recv_counts):
+            out = torch.empty(sum(recv_counts), t.shape[1], dtype=t.dtype, device=t.device)
+            td.all_to_all_single(out, t.contiguous(), recv_counts, send_counts, group=ep.group)
+            return out
+        d_y_in, x_in = exchange(d_y, send, recv), exchange(x_perm, send, recv)  # layout: source-major, expert-minor
+        d_x_in = torch.empty_like(x_in)
+        d_gu_w, d_dn_w = torch.zeros_like(gu_w), torch.zeros_like(dn_w)
+        base = [sum(recv[:s]) for s in range(W)]
+        for e in range(E_loc):
+            idx = torch.cat([torch.arange(base[s] + int(all_off[s, e0 + e] - all_off[s, e0]),
+                                          base[s] + int(all_off[s, e0 + e + 1] - all_off[s, e0]), device=d_out.device)
+                             for s in range(W)])
+            if idx.numel() == 0:
+                continue
+            xe, dye = x_in[idx], d_y_in[idx]
+            gu = xe @ gu_w[e].t()
+            g, u = gu[:, :I].float(), gu[:, I:].float()
+            sg = torch.sigmoid(g)
+            act = (g * sg * u).to(xe.dtype)
+            d_dn_w[e] = dye.t() @ act
+            d_act = (dye @ dn_w[e]).float()
+            d_gu = torch.cat([d_act * u * sg * (1 + g * (1 - sg)), d_act * g * sg], 1).to(xe.dtype)
+            d_gu_w[e] = d_gu.t() @ xe
+            d_x_in[idx] = d_gu @ gu_w[e]
+        d_x = exchange(d_x_in, recv, send)
+        d_hidden = torch.zeros(hidden.shape, dtype=torch.float32, device=d_out.device).index_add_(0, tok, d_x.float())
+        return d_hidden.to(hidden.dtype), d_gu_w, d_dn_w, d_topk.view_as(topk_w).to(topk_w.dtype), None, None
