@@ -48,6 +48,7 @@ def main():
     ap.add_argument("--model", default="llama-3-8b")
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--copiers", type=int, default=16)
+    ap.add_argument("--moe-tokens", type=int, default=8192, help="tokens per rank for the expert-parallel MoE block")
     a = ap.parse_args()
     D.init_process_group()
     rank, world = D.rank(), D.world_size()
@@ -117,6 +118,54 @@ def main():
     out["rs_adamw"]["nccl_rs_fused_adamw_nccl_ag_ms"] = timed(nccl_opt)
     rs_bytes = total * 4 * (world - 1) / world + total * 2 * (world - 1) / world
     out["rs_adamw"]["link_floor_ms"] = rs_bytes / (NVLINK_GBS * 1e6)
+    # ---- expert-parallel MoE block (Qwen3-30B-A3B expert shapes): dispatch/combine fused into the grouped GEMMs ----
+    E, Hm, Im, k = 128, 2048, 768, 8
+    if E % world == 0:
+        from ..parallel.expert_parallel import ExpertParallelMoE
+
+        Tm = a.moe_tokens
+        e_loc = E // world
+        gu = (torch.randn(e_loc, 2 * Im, Hm, device=dev) / Hm ** 0.5).to(torch.bfloat16)
+        dn = (torch.randn(e_loc, Hm, Im, device=dev) / Im ** 0.5).to(torch.bfloat16)
+        xh = (torch.randn(Tm, Hm, device=dev) * 0.5).to(torch.bfloat16)
+        tw, ti = torch.softmax(torch.randn(Tm, E, device=dev), -1).topk(k, -1)
+        ep = ExpertParallelMoE(None, E, Hm, Im, k, max_tokens=Tm, device=dev)
+        with torch.no_grad():
+            t_ep = timed(lambda: ep(xh, gu, dn, tw, ti))
+
+        def nccl_ep():  # all-to-all rows out, local grouped GEMMs, all-to-all rows back, combine
+            flat = ti.reshape(-1)
+            order = torch.argsort(flat, stable=True)
+            cnt = torch.bincount(flat, minlength=E)
+            send = cnt.view(world, e_loc).sum(1)
+            recv = torch.empty_like(send)
+            td.all_to_all_single(recv, send)
+            cnt_in = torch.empty(world, e_loc, dtype=cnt.dtype, device=dev)
+            td.all_to_all_single(cnt_in.view(-1), cnt)
+            sl, rl = send.tolist(), recv.tolist()
+            xp = xh[order // k]
+            xin = torch.empty(sum(rl), Hm, dtype=xh.dtype, device=dev)
+            td.all_to_all_single(xin, xp, rl, sl)
+            # received rows are source-major; sort them by local expert for the grouped GEMM
+            eid = torch.repeat_interleave(torch.arange(e_loc, device=dev).repeat(world), cnt_in.reshape(-1))
+            o2 = torch.argsort(eid, stable=True)
+            offs = torch.zeros(e_loc + 1, dtype=torch.int32, device=dev)
+            offs[1:] = torch.bincount(eid, minlength=e_loc).cumsum(0)
+            act = K.grouped_gemm(xin[o2], gu, offs, Im, swiglu=True)
+            yin = torch.empty_like(xin)
+            yin[o2] = K.grouped_gemm(act, dn, offs, Hm)
+            yp = torch.empty_like(xp)
+            td.all_to_all_single(yp, yin, sl, rl)
+            inv = torch.empty_like(order)
+            inv[order] = torch.arange(order.numel(), device=dev)
+            return (yp[inv].view(Tm, k, Hm).float() * tw[..., None]).sum(1).to(xh.dtype)
+        with torch.no_grad():
+            t_nccl = timed(nccl_ep)
+        flops = 2.0 * Tm * k * Hm * 3 * Im
+        link_bytes = 2.0 * Tm * k * Hm * 2 * (world - 1) / world  # rows in + rows out
+        roof = max(flops / (tfl * 1e9), link_bytes / (NVLINK_GBS * 1e6))
+        out["ep_moe"] = {"tokens_per_rank": Tm, "fused_ms": t_ep, "nccl_all_to_all_plus_grouped_gemm_ms": t_nccl,
+                         "roofline_ms": roof, "frac_of_roofline": roof / t_ep}
     K.check_status(dev)
     if rank == 0:
         print(json.dumps(out))

@@ -34,9 +34,44 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const in
   }
 }
 
+// Expert-parallel dispatch by pulling: segment g = rows [src_row[g], src_row[g] + rows[g]) of rank src[g]'s buffer go to
+// rows [dst_row[g], ...) of the local buffer.  One row (H bf16) per CTA iteration, 16 bytes per thread, so a full grid
+// keeps a few MB in flight, which is what the NVLink round trip needs.  Each remote row crosses the link once; the
+// grouped GEMM then reads the local copy as often as it has N tiles.
+struct PullParams {
+  const __nv_bfloat16* src[8];
+};
+
+__global__ void __launch_bounds__(256)
+moe_pull_rows_kernel(const PullParams pp, const int* __restrict__ seg_rows, const int* __restrict__ seg_src,
+                     const int* __restrict__ seg_src_row, const int* __restrict__ seg_dst_row, int n_seg,
+                     __nv_bfloat16* __restrict__ dst, int H) {
+  const int nvec = H >> 3;
+  for (int g = 0; g < n_seg; ++g) {
+    const int rows = seg_rows[g];
+    if (rows == 0) continue;
+    const uint4* s = reinterpret_cast<const uint4*>(pp.src[seg_src[g]] + (size_t)seg_src_row[g] * H);
+    uint4* d = reinterpret_cast<uint4*>(dst + (size_t)seg_dst_row[g] * H);
+    for (int r = blockIdx.x; r < rows; r += gridDim.x)
+      for (int v = threadIdx.x; v < nvec; v += blockDim.x) d[(size_t)r * nvec + v] = s[(size_t)r * nvec + v];
+  }
+}
+
 }  // namespace trlb
 
 using namespace trlb;
+
+TRLB_API int trlb_moe_pull_rows(const unsigned long long* src_bases, int n_src, const int* seg_rows, const int* seg_src,
+                                const int* seg_src_row, const int* seg_dst_row, int n_seg, void* dst, int H,
+                                cudaStream_t st) {
+  if (n_seg <= 0) return 0;
+  if (H % 8 || n_src < 1 || n_src > 8) return -141;
+  PullParams pp;
+  for (int i = 0; i < 8; ++i) pp.src[i] = reinterpret_cast<const __nv_bfloat16*>(src_bases[i < n_src ? i : 0]);
+  moe_pull_rows_kernel<<<148 * 4, 256, 0, st>>>(pp, seg_rows, seg_src, seg_src_row, seg_dst_row, n_seg,
+                                                (__nv_bfloat16*)dst, H);
+  return (int)cudaGetLastError();
+}
 
 TRLB_API int trlb_moe_combine(const void* y, const int* inv, const float* w, void* out, int T, int k, int H,
                               cudaStream_t st) {

@@ -3,12 +3,15 @@
 Forward on every rank, for its local experts and every source rank s (a *segment*):
 
     x_perm  this rank's tokens, sorted by global expert, in a symmetric buffer
-    GEMM 1  act[segment rows] = swiglu(x_perm_of_rank_s[rows of expert e] . W_gate_up[e]^T)   A tiles: TMA from rank s
+    pull    x_in[segment rows] = x_perm_of_rank_s[rows of expert e]                           peer loads, each row once
+    GEMM 1  act = swiglu(x_in . W_gate_up[e]^T)                                               local grouped GEMM
     GEMM 2  y_perm_of_rank_s[rows of expert e] = act[segment rows] . W_down[e]^T              C rows: stored to rank s
     combine out[t] = sum_j w[t, j] * y_perm[position of (t, j)]                               local
 
-so the dispatch all-to-all is the loads of the first grouped GEMM and the combine all-to-all is the stores of the second
-(``trlb_grouped_gemm_seg_bf16``).  Only the per-expert row offsets ([E + 1] int32 per rank) travel through NCCL.
+The combine all-to-all is the stores of the second grouped GEMM (``trlb_grouped_gemm_seg_bf16``).  The dispatch can
+ride on the loads of the first one too (``fused_dispatch=True``: A tiles by TMA from rank s), but every N tile of the
+gate/up projection then re-reads its rows over NVLink (6x for I = 768), so the default pulls the rows once with a copy
+kernel and runs the first GEMM on the local copy.  Only the per-expert row offsets travel through NCCL.
 The reference reaches expert parallelism through DeepSpeed / accelerate sharding of transformers MoE blocks
 (trl/accelerate_configs/*.yaml); it has no fused path.
 
@@ -26,7 +29,9 @@ from .symm import SymmArena
 
 
 class ExpertParallelMoE:
-    def __init__(self, group, num_experts: int, hidden: int, intermediate: int, top_k: int, max_tokens: int, device):
+    def __init__(self, group, num_experts: int, hidden: int, intermediate: int, top_k: int, max_tokens: int, device,
+                 fused_dispatch: bool = False):
+        self.fused_dispatch = fused_dispatch
         self.group = group if group is not None else td.group.WORLD
         self.world, self.rank = td.get_world_size(self.group), td.get_rank(self.group)
         if num_experts % self.world:
@@ -40,6 +45,8 @@ class ExpertParallelMoE:
         self.y_buf, self.y_off = self.arena.carve(self.max_rows * hidden, torch.bfloat16)
         self.x_buf, self.y_buf = self.x_buf.view(self.max_rows, hidden), self.y_buf.view(self.max_rows, hidden)
         self.act = torch.empty(self.world * self.max_rows, intermediate, dtype=torch.bfloat16, device=device)
+        self.x_in = None if fused_dispatch else torch.empty(self.world * self.max_rows, hidden, dtype=torch.bfloat16,
+                                                            device=device)
         self._sync = torch.zeros(1, dtype=torch.float32, device=device)
         self._a_x = (ctypes.c_ulonglong * self.world)(*[p + self.x_off for p in self.arena.peer_ptrs])
         self._c_y = (ctypes.c_ulonglong * self.world)(*[p + self.y_off for p in self.arena.peer_ptrs])
@@ -65,8 +72,10 @@ class ExpertParallelMoE:
         seg_src_row = loc[:, :-1].t().contiguous().reshape(-1)           # first row of the segment in the source's buffers
         seg_w = torch.arange(self.E_loc, dtype=torch.int32, device=self.dev).repeat_interleave(self.world)
         zeros = torch.zeros_like(seg_src)
+        loc_off = torch.zeros(self.E_loc + 1, dtype=torch.int32, device=self.dev)  # rows per local expert, all sources
+        loc_off[1:] = cnt.sum(1).cumsum(0)
         return order, offsets, all_off, dict(rows=seg_rows.contiguous(), act_row=seg_act_row, src=seg_src,
-                                             src_row=seg_src_row, w=seg_w, zeros=zeros)
+                                             src_row=seg_src_row, w=seg_w, zeros=zeros, loc_off=loc_off)
 
     def _seg_gemm(self, a_bases, c_bases, n_bufs, a_rows, w, seg, a_src, a_row, c_dst, c_row, n_out, k_dim, lda, ldc, swiglu):
         from ..ops.cuda import _chk, _p, _s, lib, status_buffer
@@ -92,8 +101,16 @@ class ExpertParallelMoE:
         tok = order // k
         torch.index_select(hidden, 0, tok, out=self.x_buf[:T * k])
         self._device_barrier()  # every rank's x rows are in place (and nobody still reads the previous layer's)
-        self._seg_gemm(self._a_x, self._self_act, self.world, self.max_rows, gate_up_local, seg, seg["src"], seg["src_row"],
-                       seg["zeros"], seg["act_row"], self.I, H, H, self.I, True)
+        if self.fused_dispatch:
+            self._seg_gemm(self._a_x, self._self_act, self.world, self.max_rows, gate_up_local, seg, seg["src"],
+                           seg["src_row"], seg["zeros"], seg["act_row"], self.I, H, H, self.I, True)
+        else:
+            from ..ops.cuda import grouped_gemm
+
+            _chk(lib().trlb_moe_pull_rows(self._a_x, c_int(self.world), _p(seg["rows"]), _p(seg["src"]), _p(seg["src_row"]),
+                                          _p(seg["act_row"]), c_int(seg["rows"].numel()), _p(self.x_in), c_int(H), _s()),
+                 "moe_pull_rows")
+            grouped_gemm(self.x_in, gate_up_local, seg["loc_off"], self.I, swiglu=True, out=self.act)
         self._seg_gemm(self._self_act, self._c_y, self.world, self.world * self.max_rows, down_local, seg, seg["zeros"],
                        seg["act_row"], seg["src"], seg["src_row"], H, self.I, self.I, H, False)
         self._device_barrier()  # all peers have stored my y rows
