@@ -125,3 +125,44 @@ def test_flops_and_hash():
     with torch.no_grad():
         m.norm.add_(1)
     assert hash_module(m) != h1
+
+
+def test_plumbing_modules(tmp_path):
+    import trl_b200
+    from trl_b200 import import_utils
+    from trl_b200.cli.commands import CommandContext, TrainingCommand
+    from trl_b200.distributed import DistributedBackend
+    from trl_b200.models.utils import _ForwardRedirection
+    from trl_b200.trainer.utils import generate_model_card
+
+    assert import_utils.is_pydantic_available() and not import_utils.is_unsloth_available()
+    assert CommandContext(["sft", "--x", "1"]).argv_after("sft") == ["--x", "1"]
+    assert TrainingCommand("dpo").name == "dpo"
+    be = DistributedBackend(None)
+    assert not be.is_zero3
+    with be.gather_params():
+        pass
+    text = generate_model_card(base_model="org/base", model_name="m", dataset_name="org/ds", trainer_name="DPO",
+                               paper_title="Direct Preference Optimization", paper_id="2305.18290", tags=["dpo"])
+    assert "org/base" in text and "2305.18290" in text and "- dpo" in text
+
+    class Inner(torch.nn.Module):
+        def forward(self, x):
+            return x + 1
+
+        def other(self, x):
+            return x * 10
+
+    class Wrapper(torch.nn.Module):
+        def __init__(self, m):
+            super().__init__()
+            self.m, self.calls = m, 0
+
+        def forward(self, *a, **k):
+            self.calls += 1
+            return self.m(*a, **k)
+    inner = Inner()
+    w = Wrapper(inner)
+    assert float(_ForwardRedirection()(w, inner, inner.other, torch.tensor(2.0))) == 20.0 and w.calls == 1
+    assert float(inner(torch.tensor(2.0))) == 3.0
+    assert trl_b200.__version__

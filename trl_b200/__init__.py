@@ -36,7 +36,10 @@ _import_structure = {
     "loop.state": ["TrainerCallback", "TrainerState", "TrainerControl"],
 }
 
+from . import _compat as _compat_mod  # noqa: E402
 from ._lazy_module import _LazyModule  # noqa: E402
+
+_compat_mod.apply()
 
 sys.modules[__name__] = _LazyModule(__name__, globals()["__file__"], _import_structure, module_spec=__spec__,
                                     extra_objects={"__version__": __version__})

@@ -98,24 +98,18 @@ def main(argv: list[str] | None = None) -> int:
     if not argv or argv[0] in ("-h", "--help"):
         ap.print_help()
         return 0
-    cmd, rest = argv[0], argv[1:]
-    if cmd in TRAINING:
-        return run_training(cmd, rest)
-    if cmd == "env":
-        from ..scripts.env import print_env
+    from .commands import CommandContext, EnvCommand, SkillsCommand, TrainingCommand, VllmServeCommand
 
-        print_env()
-        return 0
-    if cmd == "skills":
-        from ..skills.cli import main as skills_main
-
-        return skills_main(rest)
-    if cmd in ("vllm-serve", "rollout-serve"):
-        from ..scripts.rollout_serve import main as serve_main
-
-        return serve_main(rest)
-    ap.parse_args([cmd])
-    return 2
+    cmd = argv[0]
+    commands = {n: TrainingCommand(n) for n in TRAINING}
+    commands.update({"env": EnvCommand(), "skills": SkillsCommand(), "vllm-serve": VllmServeCommand()})
+    serve = VllmServeCommand()
+    serve.name = "rollout-serve"
+    commands["rollout-serve"] = serve
+    if cmd not in commands:
+        ap.parse_args([cmd])
+        return 2
+    return commands[cmd].run(None, CommandContext(argv))
 
 
 if __name__ == "__main__":

@@ -655,8 +655,25 @@ class Trainer:
     def _on_checkpoint_loaded(self, folder: str):
         pass
 
-    def create_model_card(self, *a, **k):
-        pass
+    def create_model_card(self, model_name: str | None = None, dataset_name: str | None = None, tags=None):
+        """Writes ``README.md`` into ``output_dir`` from the packaged template (trl/trainer/base_trainer.py:127-191)."""
+        if not self.is_world_process_zero():
+            return
+        from ..trainer.utils import generate_model_card
+
+        base = getattr(self.model, "name_or_path", None) or getattr(getattr(self.model, "config", None), "_name_or_path", None)
+        if base and os.path.isdir(str(base)):
+            base = None
+        paper = getattr(self, "_paper", {}) or {}
+        text = generate_model_card(base_model=base, model_name=model_name or os.path.basename(self.args.output_dir.rstrip("/")),
+                                   dataset_name=dataset_name, tags=list(getattr(self, "_tag_names", [])) + list(tags or []),
+                                   trainer_name=getattr(self, "_name", type(self).__name__),
+                                   trainer_citation=paper.get("citation"), paper_title=paper.get("title"),
+                                   paper_id=paper.get("id"),
+                                   template_file=getattr(self, "_template_file", "lm_model_card.md"))
+        os.makedirs(self.args.output_dir, exist_ok=True)
+        with open(os.path.join(self.args.output_dir, "README.md"), "w") as f:
+            f.write(text)
 
     def push_to_hub(self, *a, **k):
         raise RuntimeError("push_to_hub needs network access, which this build does not assume")

@@ -73,3 +73,31 @@ def remove_hooks(model):  # the native engine installs no forward hooks
 
 def add_hooks(model):
     return None
+
+
+class _ForwardRedirection:
+    """Runs an arbitrary method through a wrapper module's ``forward`` so that the wrapper's pre/post hooks fire
+    (counterpart of trl/models/utils.py:324-372, where FSDP / ZeRO-3 hooks gather parameters).  The native engines hang
+    no hooks on ``forward`` (full-shard gathers happen inside the layer's QKV GEMM), so this only swaps the call."""
+
+    def __call__(self, wrapper_module, original_module, method, *args, **kwargs):
+        original_forward = original_module.forward
+
+        def wrapped_forward(*a, **k):
+            original_module.forward = original_forward
+            out = method(*a, **k)
+            self.on_after_inner_forward(wrapper_module, original_module)
+            return out
+        original_module.forward = wrapped_forward
+        try:
+            out = wrapper_module(*args, **kwargs)
+        finally:
+            original_module.forward = original_forward
+        self.on_after_outer_forward(wrapper_module, original_module)
+        return out
+
+    def on_after_inner_forward(self, wrapper_module, original_module):
+        pass
+
+    def on_after_outer_forward(self, wrapper_module, original_module):
+        pass

@@ -171,6 +171,11 @@ class RolloutEngine:
         self.part_o = torch.empty(max_num_seqs * self.hq_local * self.kv_splits * D, dtype=torch.float32, device=self.dev)
         self.part_ml = torch.empty(max_num_seqs * self.hq_local * self.kv_splits * 2, dtype=torch.float32, device=self.dev)
         self.q_buf = torch.empty(max_num_seqs, self.hq_local, D, dtype=dt, device=self.dev)
+        self._fused_gate_up = (os.environ.get("TRL_B200_DECODE_FUSED_GATE_UP", "1") == "1" and not cfg.is_moe and tp == 1
+                               and cfg.hidden_size % 8 == 0 and cfg.intermediate_size % 8 == 0)
+        if self._fused_gate_up:
+            self._one_group = torch.tensor([0, max_num_seqs], dtype=torch.int32, device=self.dev)
+            self._act_buf = torch.empty(max_num_seqs, cfg.intermediate_size, dtype=dt, device=self.dev)
         self.attn_buf = torch.empty(max_num_seqs, self.hq_local, D, dtype=dt, device=self.dev)
         self.seen = None
         self.out_tokens = self.out_logps = None
@@ -227,6 +232,12 @@ class RolloutEngine:
 
                 y, _, _ = F_.moe_mlp(h, l.router, l.experts_gate_up, l.experts_down, cfg.num_experts_per_tok,
                                      cfg.norm_topk_prob)
+            elif self._fused_gate_up:
+                # gate/up GEMM with the SwiGLU epilogue (the grouped kernel with one group): the [B, 2I] intermediate
+                # and one launch per layer disappear
+                act = K.grouped_gemm(h, l.gate_up_proj.unsqueeze(0), self._one_group, cfg.intermediate_size, swiglu=True,
+                                     out=self._act_buf)
+                y = torch.nn.functional.linear(act, l.down_proj)
             else:
                 gu = torch.nn.functional.linear(h, l.gate_up_proj)
                 y = torch.nn.functional.linear(K.swiglu_infer(gu), l.down_proj)

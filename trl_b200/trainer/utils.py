@@ -372,3 +372,30 @@ def maybe_gather_lm_head_ctx(model, engine=None):
     if engine is not None and hasattr(engine, "gathered"):
         return engine.gathered(["lm_head", "embed_tokens"])
     return contextlib.nullcontext()
+
+
+def generate_model_card(base_model=None, model_name="model", hub_model_id=None, dataset_name=None, tags=None,
+                        trainer_name="Trainer", trainer_citation=None, template_file="lm_model_card.md", paper_title=None,
+                        paper_id=None, wandb_url=None, comet_url=None, **_):
+    """Renders ``trl_b200/templates/<template_file>`` (counterpart of trl/trainer/utils.py:280-411); returns the text."""
+    import os
+    import sys
+
+    import jinja2
+
+    import torch
+
+    from .. import __version__
+
+    here = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "templates", template_file)
+    with open(here) as f:
+        template = jinja2.Template(f.read())
+    tags = list(dict.fromkeys((tags or []) + ["generated_from_trainer", "trl_b200"]))
+    card = [f"base_model: {base_model}" if base_model else None, f"datasets: {dataset_name}" if dataset_name else None,
+            "library_name: transformers", f"model_name: {model_name}", "tags:"] + [f"- {t}" for t in tags] + ["licence: license"]
+    versions = "\n".join([f"- trl_b200: {__version__}", f"- PyTorch: {torch.__version__}",
+                           f"- Python: {sys.version.split()[0]}"])
+    return template.render(card_data="\n".join(c for c in card if c), model_name=model_name, base_model=base_model,
+                           hub_model_id=hub_model_id or model_name, dataset_name=dataset_name, trainer_name=trainer_name,
+                           trainer_citation=trainer_citation, paper_title=paper_title, paper_id=paper_id,
+                           versions=versions, wandb_url=wandb_url, comet_url=comet_url)
