@@ -47,11 +47,16 @@ def clone_chat_template(model, tokenizer, source_tokenizer_path, resize_to_multi
     return model, tokenizer, list(range(before, len(tokenizer)))
 
 
-_FAMILY_MARKERS = [
+_FAMILY_MARKERS = [  # first match wins: more specific markers first
     ("<think>", "<|im_start|>", "qwen3_training.jinja"),
+    ("You are Qwen, created by Alibaba Cloud", "<|im_start|>", "qwen2_5_training.jinja"),
     ("<|im_start|>", None, "chatml_training.jinja"),
     ("<|start_header_id|>", None, "llama3_training.jinja"),
+    ("<start_of_turn>", "tool_code", "gemma3_training.jinja"),
     ("<start_of_turn>", None, "gemma_training.jinja"),
+    ("[gMASK]", "<|assistant|>", "glm4moe_training.jinja"),
+    ("<|START_OF_TURN_TOKEN|>", None, "cohere_training.jinja"),
+    ("<|start|>", "<|message|>", "gptoss_training.jinja"),
     ("<|assistant|>", None, "phi3_training.jinja"),
     ("<｜Assistant｜>", None, "deepseekv3_training.jinja"),
 ]
@@ -69,7 +74,7 @@ def get_training_chat_template(tokenizer) -> str | None:
             with open(os.path.join(_TEMPLATE_DIR, fn), encoding="utf-8") as f:
                 return f.read()
     raise ValueError("The tokenizer's chat template does not match a known family (ChatML/Qwen, Qwen3, Llama 3, Gemma, "
-                     "Phi-3, DeepSeek-V3); pass a training template with {% generation %} markers explicitly.")
+                     "GLM-4, Command-R, gpt-oss, Phi-3, DeepSeek-V3); pass a training template with {% generation %} markers explicitly.")
 
 
 def _render(tok, messages, **kw):
