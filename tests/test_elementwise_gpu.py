@@ -98,3 +98,17 @@ def test_add_rmsnorm_infer(T, H):
     s = (x + d)
     assert torch.equal(res, s)
     assert torch.allclose(y.float(), ref.rms_norm(s, w, 1e-6).float(), atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("n", [8 * 1000 + 5, 64, 3, 1 << 20])
+def test_accum_bf16_into_fp32(n):
+    from trl_b200.ops import cuda as K
+
+    torch.manual_seed(0)
+    buf = torch.randn(n + 8, device="cuda")
+    dst = buf[:n]
+    src = torch.randn(n, device="cuda").to(torch.bfloat16)
+    want = dst + src.float()
+    K.accum_grad(dst, src)
+    assert torch.equal(dst, want)
+    assert float(buf[n:].abs().sum()) == float(buf[n:].abs().sum())

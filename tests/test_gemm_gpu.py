@@ -57,3 +57,30 @@ def test_lmhead_backward_matches_autograd():
     (rl * g).sum().backward()
     assert torch.allclose(h.grad.float(), h2.grad, atol=3e-2, rtol=3e-2), (h.grad.float() - h2.grad).abs().max()
     assert torch.allclose(w.grad.float(), w2.grad, atol=3e-2, rtol=3e-2), (w.grad.float() - w2.grad).abs().max()
+
+
+@pytest.mark.parametrize("B,N,K", [(64, 3584, 18944), (7, 1000, 520), (33, 4608, 3584)])
+def test_smallm_splitk_gemm_and_fp32_add_rmsnorm(B, N, K):
+    from trl_b200.ops import cuda as Kc
+
+    torch.manual_seed(0)
+    x = (torch.randn(B, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    bias = torch.randn(N, device="cuda").to(torch.bfloat16)
+    y = torch.zeros(B, N, device="cuda")
+    Kc.smallm_gemm_accumulate(x, w, y, bias=bias)
+    want = x.float() @ w.float().t() + bias.float()
+    assert (y - want).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item())
+    Kc.smallm_gemm_accumulate(x, w, y)  # accumulates
+    assert (y - (2 * want - bias.float())).abs().max().item() < 4e-2 * max(1.0, want.abs().max().item())
+    if N % 8 == 0:
+        res = torch.randn(B, N, device="cuda").to(torch.bfloat16)
+        gamma = torch.randn(N, device="cuda").to(torch.bfloat16)
+        r0, d0 = res.clone(), y.clone()
+        out = Kc.add_rmsnorm_f32_infer(res, y, gamma, 1e-6)
+        s = (r0.float() + d0).to(torch.bfloat16).float()
+        ref = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.float()
+        assert (out.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
+        assert float(y.abs().max()) == 0.0 and torch.equal(res.float(), s)
+    torch.cuda.synchronize()
+    Kc.check_status(torch.device("cuda"))

@@ -186,6 +186,71 @@ __global__ void __launch_bounds__(256) add_rmsnorm_row_kernel(__nv_bfloat16* __r
   }
 }
 
+// Variant for the split-K decode GEMM: delta holds fp32 sums; they are consumed (added to the residual stream) and
+// cleared here, so the next GEMM that accumulates into the same buffer starts from zero without a memset launch.
+template <int VPT>
+__global__ void __launch_bounds__(256) add_rmsnorm_f32_row_kernel(__nv_bfloat16* __restrict__ res,
+                                                                 float* __restrict__ delta,
+                                                                 const __nv_bfloat16* __restrict__ w,
+                                                                 __nv_bfloat16* __restrict__ y, int H, float eps) {
+  __shared__ float red[8];
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int nvec = H >> 3;
+  uint4* xr = reinterpret_cast<uint4*>(res + (size_t)row * H);
+  float4* dr = reinterpret_cast<float4*>(delta + (size_t)row * H);
+  float buf[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * 256;
+    if (v < nvec) {
+      uint4 a = xr[v];
+      uint32_t* au = reinterpret_cast<uint32_t*>(&a);
+      const float4 d0 = dr[2 * v], d1 = dr[2 * v + 1];
+      dr[2 * v] = make_float4(0.f, 0.f, 0.f, 0.f);
+      dr[2 * v + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float dv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16(au[j]);
+        au[j] = pack_bf16(f.x + dv[2 * j], f.y + dv[2 * j + 1]);
+      }
+      xr[v] = a;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 r = unpack_bf16(au[j]);
+        buf[i][2 * j] = r.x; buf[i][2 * j + 1] = r.y;
+        ss += r.x * r.x + r.y * r.y;
+      }
+    }
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) red[wid] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) tot += red[k];
+  const float rstd = rsqrtf(tot / (float)H + eps);
+  uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * H);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * 256;
+    if (v < nvec) {
+      const uint4 wv = wr[v];
+      const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wv);
+      uint4 o;
+      uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 g = unpack_bf16(wu[j]);
+        ou[j] = pack_bf16(buf[i][2 * j] * rstd * g.x, buf[i][2 * j + 1] * rstd * g.y);
+      }
+      yr[v] = o;
+    }
+  }
+}
+
 // RMSNorm backward.  dx = rstd * (w*dy - x * rstd^2 * mean(w*dy*x)).  A CTA walks its rows one at a
 // time; thread t owns the same columns for every row, so the dw partial sums stay in registers.
 // Per-CTA partials go to fp32 scratch [gridDim.x, H], reduced by rmsnorm_dw_reduce_kernel.
@@ -448,6 +513,50 @@ TRLB_API int trlb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd
   else if (vec <= 8) rmsnorm_fwd_kernel<8><<<grid, threads, 0, st>>>(X, W, Y, rstd, T, H, eps);
   else if (vec <= 16) rmsnorm_fwd_kernel<16><<<grid, threads, 0, st>>>(X, W, Y, rstd, T, H, eps);
   else rmsnorm_fwd_kernel<32><<<grid, threads, 0, st>>>(X, W, Y, rstd, T, H, eps);
+  return (int)cudaGetLastError();
+}
+
+// main-gradient accumulation: dst (fp32) += src (bf16), 8 elements per thread iteration
+__global__ void __launch_bounds__(256) accum_bf16_f32_kernel(float* __restrict__ dst, const __nv_bfloat16* __restrict__ src,
+                                                            long long n) {
+  const long long nvec = n >> 3;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += stride) {
+    const uint4 s = reinterpret_cast<const uint4*>(src)[v];
+    const uint32_t su[4] = {s.x, s.y, s.z, s.w};
+    float4 a = reinterpret_cast<float4*>(dst)[2 * v], b = reinterpret_cast<float4*>(dst)[2 * v + 1];
+    const float2 f0 = unpack_bf16(su[0]), f1 = unpack_bf16(su[1]), f2 = unpack_bf16(su[2]), f3 = unpack_bf16(su[3]);
+    a.x += f0.x; a.y += f0.y; a.z += f1.x; a.w += f1.y;
+    b.x += f2.x; b.y += f2.y; b.z += f3.x; b.w += f3.y;
+    reinterpret_cast<float4*>(dst)[2 * v] = a;
+    reinterpret_cast<float4*>(dst)[2 * v + 1] = b;
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (n & 7)) {
+    const long long i = (nvec << 3) + threadIdx.x;
+    dst[i] += __bfloat162float(src[i]);
+  }
+}
+
+TRLB_API int trlb_accum_bf16_f32(float* dst, const void* src, long long n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(dst) & 15) || (reinterpret_cast<uintptr_t>(src) & 15)) return -2;
+  long long blocks = ((n >> 3) + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  accum_bf16_f32_kernel<<<(int)blocks, 256, 0, st>>>(dst, (const __nv_bfloat16*)src, n);
+  return (int)cudaGetLastError();
+}
+
+// res[T,H] += delta32[T,H] (fp32 sums, cleared afterwards), y = rmsnorm(res) * w  (H <= 8192, few rows)
+TRLB_API int trlb_add_rmsnorm_f32(void* res, float* delta, const void* w, void* y, int T, int H, float eps,
+                                  cudaStream_t st) {
+  if (T == 0) return 0;
+  if (H % 8 != 0 || H > 8192) return -1;
+  auto R = (__nv_bfloat16*)res; auto W = (const __nv_bfloat16*)w; auto Y = (__nv_bfloat16*)y;
+  const int vpt = (H / 8 + 255) / 256;
+  if (vpt <= 1) add_rmsnorm_f32_row_kernel<1><<<T, 256, 0, st>>>(R, delta, W, Y, H, eps);
+  else if (vpt <= 2) add_rmsnorm_f32_row_kernel<2><<<T, 256, 0, st>>>(R, delta, W, Y, H, eps);
+  else add_rmsnorm_f32_row_kernel<4><<<T, 256, 0, st>>>(R, delta, W, Y, H, eps);
   return (int)cudaGetLastError();
 }
 

@@ -480,6 +480,33 @@ def add_rmsnorm_infer(res, delta, w, eps, out=None):
     return out
 
 
+def add_rmsnorm_f32_infer(res, delta32, w, eps, out=None):
+    """res += delta32 (fp32 partial sums of the split-K decode GEMM, cleared here); returns rmsnorm(res) * w."""
+    T, H = res.shape
+    assert delta32.dtype == torch.float32 and delta32.is_contiguous()
+    out = torch.empty_like(res) if out is None else out
+    _chk(lib().trlb_add_rmsnorm_f32(_p(res), _p(delta32), _p(w), _p(out), c_int(T), c_int(H), c_float(eps), _s()),
+         "add_rmsnorm_f32")
+    return out
+
+
+def accum_grad(dst32, src_bf16):
+    """dst32 (fp32 main gradient, contiguous) += src (bf16 gradient of one micro-batch)."""
+    _chk(lib().trlb_accum_bf16_f32(_p(dst32), _p(src_bf16), c_longlong(dst32.numel()), _s()), "accum_grad")
+
+
+def smallm_gemm_accumulate(x, w, y32, bias=None):
+    """y32[B, N] (fp32) += x[B, K] @ w[N, K]^T for decode batches (B <= 64): split-K weight-streaming tcgen05 kernel."""
+    B, Kd = x.shape
+    N = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and y32.dtype == torch.float32
+    assert x.stride(1) == 1 and w.stride(1) == 1 and y32.stride(1) == 1 and y32.shape == (B, N)
+    _chk(lib().trlb_smallm_gemm_bf16(_p(x), _p(w), _p(bias), _p(y32), c_int(B), c_int(N), c_int(Kd), c_longlong(x.stride(0)),
+                                     c_longlong(w.stride(0)), c_longlong(y32.stride(0)), _p(status_buffer(x.device)), _s()),
+         "smallm_gemm")
+    return y32
+
+
 def swiglu_infer(gu, out=None):
     T, I2 = gu.shape
     out = torch.empty(T, I2 // 2, dtype=gu.dtype, device=gu.device) if out is None else out

@@ -190,7 +190,14 @@ class TrainEngine:
                     p.grad = None
 
                     def hook(param, gview=gview):
-                        gview.add_(param.grad)
+                        g = param.grad
+                        if (g.is_cuda and g.dtype == torch.bfloat16 and gview.dtype == torch.float32 and g.is_contiguous()
+                                and g.data_ptr() % 16 == 0 and gview.data_ptr() % 16 == 0):
+                            from ..ops.cuda import accum_grad  # one vectorised pass instead of a mixed-dtype add
+
+                            accum_grad(gview, g)
+                        else:
+                            gview.add_(g)
                         param.grad = None
 
                     self._hooks.append(p.register_post_accumulate_grad_hook(hook))
