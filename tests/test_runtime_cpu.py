@@ -181,3 +181,56 @@ def test_cli_and_parser(tmp_path):
                  "--reward_funcs", "think_format_reward", "--max_steps", "1", "--output_dir", str(tmp_path / "g"), "--use_cpu",
                  "--save_strategy", "no", "--per_device_train_batch_size", "4", "--num_generations", "4",
                  "--max_completion_length", "4"]) == 0
+
+
+def test_rank_watchdog_detects_a_silent_peer(tmp_path):
+    import time
+
+    from trl_b200.utils.watchdog import PeerFailure, RankWatchdog
+
+    w0 = RankWatchdog(str(tmp_path), 0, 2, interval_s=0.05, stale_after_s=0.4).start()
+    w1 = RankWatchdog(str(tmp_path), 1, 2, interval_s=0.05, stale_after_s=0.4).start()
+    time.sleep(0.2)
+    w0.check_peers()
+    w1.check_peers()
+    w1.stop(remove=False)  # rank 1 goes silent (a crashed process leaves its last heartbeat behind)
+    time.sleep(0.7)
+    with pytest.raises(PeerFailure, match=r"rank\(s\) \[1\]"):
+        w0.check_peers()
+    w0.stop()
+
+
+def test_watchdog_callback_and_model_card_in_training(tmp_path, monkeypatch, tiny_tokenizer):
+    from trl_b200.testing import make_dataset, make_tiny_model
+    from trl_b200.trainer.callbacks import WatchdogCallback
+    from trl_b200.trainer.sft_config import SFTConfig
+    from trl_b200.trainer.sft_trainer import SFTTrainer
+
+    monkeypatch.setenv("TRL_B200_WATCHDOG_DIR", str(tmp_path / "hb"))
+    tr = SFTTrainer(make_tiny_model(), SFTConfig(output_dir=str(tmp_path / "out"), per_device_train_batch_size=4, max_steps=2,
+                                                 save_strategy="steps", save_steps=2, use_cpu=True, report_to="none"),
+                    train_dataset=make_dataset("standard_language_modeling", 16), processing_class=tiny_tokenizer)
+    assert any(isinstance(c, WatchdogCallback) for c in tr.callback_handler.callbacks)
+    tr.train()
+    assert (tmp_path / "out" / "README.md").exists() and "SFT" in (tmp_path / "out" / "README.md").read_text()
+    assert not any((tmp_path / "hb").iterdir())  # heartbeat removed at the end of training
+
+
+def test_host_runtime_under_address_and_ub_sanitizers(tmp_path):
+    import shutil
+    import subprocess
+
+    if shutil.which("g++") is None:
+        pytest.skip("no g++")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / "host_runtime_sanitize")
+    cmd = ["g++", "-std=c++17", "-O1", "-g", "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined", "-pthread",
+           os.path.join(root, "tests", "host_runtime_sanitize.cpp"), os.path.join(root, "trl_b200", "csrc", "host_runtime.cpp"),
+           "-o", exe]
+    b = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    if b.returncode != 0 and "sanitize" in (b.stderr or "").lower() and "cannot find" in b.stderr.lower():
+        pytest.skip("sanitizer runtime libraries are not installed")
+    assert b.returncode == 0, b.stderr[-2000:]
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=120,
+                       env=dict(os.environ, ASAN_OPTIONS="detect_leaks=1:abort_on_error=0"))
+    assert r.returncode == 0 and "SANITIZE_OK" in r.stdout, (r.stdout[-1000:], r.stderr[-3000:])

@@ -58,7 +58,7 @@ def timeit(fn, iters, warmup):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "lmhead", "lmhead_bwd", "decode_attn", "rmsnorm", "adamw", "grpo_loss", "moe"])
+    ap.add_argument("kernel", choices=["gemm", "lmhead", "lmhead_bwd", "decode_attn", "rmsnorm", "adamw", "grpo_loss", "moe", "decode_gemm"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4608)
     ap.add_argument("--k", type=int, default=3584)
@@ -136,6 +136,19 @@ def main():
             out[f"tcgen05_splits{sp}_ms"] = ms2
             out[f"tcgen05_splits{sp}_frac_of_copy_bw"] = byt / ms2 / 1e6 / hbm
         K.check_status(dev)
+    elif a.kernel == "decode_gemm":
+        # the weight-streaming GEMMs of one Qwen2.5-7B decode step at batch a.batch: cuBLAS vs the split-K kernel
+        rows = []
+        for name, N, Kd in (("qkv", 4608, 3584), ("o_proj", 3584, 3584), ("gate_up", 37888, 3584), ("down", 3584, 18944)):
+            x = (torch.randn(a.batch, Kd, device=dev) * 0.5).to(torch.bfloat16)
+            w = (torch.randn(N, Kd, device=dev) / Kd ** 0.5).to(torch.bfloat16)
+            y32 = torch.zeros(a.batch, N, device=dev)
+            t_lib = timeit(lambda: torch.nn.functional.linear(x, w), a.iters, a.warmup)
+            t_own = timeit(lambda: K.smallm_gemm_accumulate(x, w, y32), a.iters, a.warmup)
+            byt = N * Kd * 2.0
+            rows.append({"gemm": name, "weight_MB": round(byt / 1e6, 1), "cublas_us": round(t_lib * 1e3, 1),
+                         "splitk_us": round(t_own * 1e3, 1), "floor_us": round(byt / hbm / 1e3, 1)})
+        out.update(batch=a.batch, gemms=rows)
     elif a.kernel == "moe":
         # Qwen3-30B-A3B expert shapes: 128 experts, hidden 2048, expert FFN 768, top-8; a.t tokens
         E, H, I, k = 128, 2048, 768, 8

@@ -422,6 +422,21 @@ allreduce_add_rmsnorm_kernel(Peers P, long long buf_elems, __nv_bfloat16* __rest
   if (grid_last_block(local_gate + 1) && threadIdx.x == 0) *epoch_ctr = epoch;
 }
 
+// Self-test of the bounded-wait discipline: one thread polls a flag with a time budget, exactly like the peer
+// waits above; when nothing sets the flag the kernel records ERR_WAIT_TIMEOUT and returns, and the context stays
+// usable.  Used by the failure-detection test.
+__global__ void bounded_wait_selftest_kernel(const uint32_t* flag, uint32_t expect, uint64_t budget_ns, int* status) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const uint64_t t0 = globaltimer_ns();
+  while ((int32_t)(ld_acquire_sys(flag) - expect) < 0) {
+    if (globaltimer_ns() - t0 > budget_ns) {
+      report_error(status, ERR_WAIT_TIMEOUT, 999, (int)expect);
+      return;
+    }
+    __nanosleep(64);
+  }
+}
+
 }  // namespace trlb
 
 using namespace trlb;
@@ -500,5 +515,11 @@ TRLB_API int trlb_allreduce_add_rmsnorm(const unsigned long long* bufs, const un
   if (vpt <= 1) allreduce_add_rmsnorm_kernel<1><<<T, 256, 0, st>>>(P, buf_elems, R, W, Y, H, eps, epoch_ctr, local_gate, channel, status);
   else if (vpt <= 2) allreduce_add_rmsnorm_kernel<2><<<T, 256, 0, st>>>(P, buf_elems, R, W, Y, H, eps, epoch_ctr, local_gate, channel, status);
   else allreduce_add_rmsnorm_kernel<4><<<T, 256, 0, st>>>(P, buf_elems, R, W, Y, H, eps, epoch_ctr, local_gate, channel, status);
+  return (int)cudaGetLastError();
+}
+
+TRLB_API int trlb_bounded_wait_selftest(const void* flag, unsigned expect, int budget_ms, int* status, cudaStream_t st) {
+  if (budget_ms < 1 || budget_ms > 1000) return -160;  // the budget is what keeps this from being a hang
+  bounded_wait_selftest_kernel<<<1, 32, 0, st>>>((const uint32_t*)flag, expect, (uint64_t)budget_ms * 1000000ull, status);
   return (int)cudaGetLastError();
 }

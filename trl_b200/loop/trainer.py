@@ -193,6 +193,7 @@ class Trainer:
         self.lr_scheduler: LRScheduler | None = None
         self.optimizer = None
         self._metrics = {"train": defaultdict(list), "eval": defaultdict(list)}
+        self._watchdog_dir = os.environ.get("TRL_B200_WATCHDOG_DIR")
         self._train_batch_size = self.args.per_device_train_batch_size
         self.is_in_train = False
         self._place_model()
@@ -202,6 +203,10 @@ class Trainer:
                 cbs.append(_SINKS[r]())
         if not any(isinstance(c, PrinterCallback) for c in cbs) and self.args.disable_tqdm:
             cbs.append(PrinterCallback())
+        if self._watchdog_dir:
+            from ..trainer.callbacks import WatchdogCallback
+
+            cbs.append(WatchdogCallback(self._watchdog_dir, stale_after_s=float(os.environ.get("TRL_B200_WATCHDOG_STALE_S", 60))))
         self.callback_handler = CallbackHandler(cbs, self.model, self.processing_class, None, None)
         self.control = self.callback_handler.call_event("on_init_end", self.args, self.state, self.control)
 
@@ -581,6 +586,11 @@ class Trainer:
         folder = os.path.join(a.output_dir, f"{PREFIX_CHECKPOINT_DIR}-{st.global_step}")
         self.save_model(folder, _internal_call=True)
         os.makedirs(folder, exist_ok=True)
+        if a.should_save:
+            try:
+                self.create_model_card()  # README.md next to the checkpoints, refreshed at every save
+            except Exception:  # a missing template engine must not lose the checkpoint
+                pass
         if not a.save_only_model:
             sharded = self.engine.sharded
             if sharded or a.should_save:

@@ -45,6 +45,12 @@ def check_status(device=None, reset: bool = True):
         raise RuntimeError(f"trl_b200 kernel error: code={vals[0]} site={vals[1]} block={vals[2]} extra={vals[3]}")
 
 
+def bounded_wait_selftest(flag: torch.Tensor, expect: int, budget_ms: int = 50):
+    """Launches the one-thread bounded wait on ``flag`` (uint32/int32 tensor); the outcome is read with check_status."""
+    _chk(lib().trlb_bounded_wait_selftest(_p(flag), ctypes.c_uint(expect), c_int(budget_ms), _p(status_buffer(flag.device)),
+                                          _s()), "bounded_wait_selftest")
+
+
 LAUNCHES = [0]  # kernels of this library launched (or captured into a graph) from Python
 
 

@@ -169,3 +169,28 @@ class BEMACallback(TrainerCallback):
             model.save_pretrained(out)
         for p, b in zip(params, backup):
             p.data.copy_(b.to(p.device, p.dtype))
+
+
+class WatchdogCallback(TrainerCallback):
+    """Heartbeat files per rank (``utils/watchdog.py``): started with training, peers checked before every optimizer
+    step, so a rank that died between steps stops the others with a clear error instead of a collective timeout.
+    Added automatically when ``TRL_B200_WATCHDOG_DIR`` is set."""
+
+    def __init__(self, directory: str, interval_s: float = 1.0, stale_after_s: float = 60.0):
+        self.directory, self.interval_s, self.stale_after_s = directory, interval_s, stale_after_s
+        self.watchdog = None
+
+    def on_train_begin(self, args, state, control, **kw):
+        from ..parallel import dist as D
+        from ..utils.watchdog import RankWatchdog
+
+        self.watchdog = RankWatchdog(self.directory, D.rank(), D.world_size(), self.interval_s, self.stale_after_s).start()
+
+    def on_step_begin(self, args, state, control, **kw):
+        if self.watchdog is not None:
+            self.watchdog.check_peers()
+
+    def on_train_end(self, args, state, control, **kw):
+        if self.watchdog is not None:
+            self.watchdog.stop()
+            self.watchdog = None
