@@ -250,3 +250,60 @@ def test_config_validation():
     c = SFTConfig(output_dir="x", packing_strategy="bfd-requeue")
     assert c.packing_strategy == "bfd_split" and c.loss_type == "chunked_nll" and c.logging_steps == 10
     assert GRPOConfig(output_dir="x", use_cpu=True).loss_type == "dapo"
+
+
+def test_grpo_generation_batch_schedule(tmp_path, tiny_tokenizer):
+    """per_device_bs=6, steps_per_generation=4, num_generations=4, num_iterations=2, GA=3: a generation batch is 24 rows
+    (6 prompts x 4) and serves 8 consecutive training_step calls; 48 calls for 3 epochs over 12 prompts."""
+    from trl_b200.trainer.grpo_config import GRPOConfig
+    from trl_b200.trainer.grpo_trainer import GRPOTrainer
+
+    calls = {"gen": 0, "rows": []}
+    model = make_tiny_model()
+    cfg = GRPOConfig(output_dir=str(tmp_path), per_device_train_batch_size=6, steps_per_generation=4, num_generations=4,
+                     num_iterations=2, gradient_accumulation_steps=3, max_completion_length=4, num_train_epochs=3, logging_steps=1,
+                     learning_rate=1e-4, use_cpu=True, save_strategy="no", report_to="none", beta=0.0)
+    assert cfg.generation_batch_size == 24
+    tr = GRPOTrainer(model, lambda completion_ids, **kw: [float(sum(c) % 3) for c in completion_ids], cfg,
+                     train_dataset=make_dataset("standard_prompt_only", 12), processing_class=tiny_tokenizer)
+    orig = tr._generate_and_score_completions
+
+    def spy(inputs):
+        calls["gen"] += 1
+        calls["rows"].append(len(inputs))
+        assert len({str(x["prompt"]) for x in inputs}) == 6
+        return orig(inputs)
+    tr._generate_and_score_completions = spy
+    tr.train()
+    # 12 prompts -> 2 generation batches per epoch, each served by 8 training_step calls: 16 per epoch, 48 in total
+    assert tr._step == 48 and calls["gen"] == 6 and set(calls["rows"]) == {24}
+
+
+def test_grpo_unscorable_and_truncated_completions(tmp_path, tiny_tokenizer):
+    from trl_b200.trainer.grpo_config import GRPOConfig
+    from trl_b200.trainer.grpo_trainer import GRPOTrainer
+
+    def reward(completion_ids, **kw):  # every second completion cannot be scored
+        return [None if i % 2 else float(sum(c) % 5) for i, c in enumerate(completion_ids)]
+    model = make_tiny_model()
+    cfg = GRPOConfig(output_dir=str(tmp_path), per_device_train_batch_size=4, num_generations=4, max_completion_length=5,
+                     max_steps=1, logging_steps=1, learning_rate=1e-4, use_cpu=True, save_strategy="no", report_to="none",
+                     beta=0.0, mask_truncated_completions=True)
+    tr = GRPOTrainer(model, reward, cfg, train_dataset=make_dataset("standard_prompt_only", 8), processing_class=tiny_tokenizer)
+    batch = next(iter(tr.get_train_dataloader()))
+    out = tr._generate_and_score_completions(batch)
+    adv = out["advantages"]
+    assert torch.isfinite(adv).all() and float(adv[1::2].abs().max()) == 0.0  # unscorable rows carry no signal
+    eos, pad_id = tiny_tokenizer.eos_token_id, tiny_tokenizer.pad_token_id
+    for ids, row in zip(out["completion_ids_list"], out["completion_mask"]):
+        if ids[-1] not in (eos, pad_id):  # truncated: the whole row is masked out
+            assert float(row.sum()) == 0.0
+
+
+def test_fused_lm_head_losses_reject_an_adapted_lm_head(tmp_path, tiny_tokenizer):
+    from trl_b200.models.lora import LoraConfig
+
+    with pytest.raises(ValueError, match="lm_head"):
+        SFTTrainer(make_tiny_model(), SFTConfig(output_dir=str(tmp_path), **COMMON),
+                   train_dataset=make_dataset("standard_language_modeling", 8), processing_class=tiny_tokenizer,
+                   peft_config=LoraConfig(r=4, target_modules=["q_proj", "lm_head"]))

@@ -63,6 +63,13 @@ def get_peft_model(model, peft_config, adapter_name: str = "default"):
     from .decoder import LoraSlot
 
     cfg = _as_config(peft_config)
+    if "lm_head" in (cfg.target_modules or []):
+        # every loss here reads lm_head.weight inside a fused GEMM + log-softmax kernel: a low-rank delta on the head
+        # would be silently ignored (the reference raises for its fused losses too: trl/trainer/sft_trainer.py:1306-1318)
+        raise ValueError("LoRA on lm_head is not supported: the fused lm_head losses read lm_head.weight directly; "
+                         "train the head fully with modules_to_save=['lm_head'] instead")
+    if getattr(cfg, "peft_type", "LORA") not in ("LORA", None):
+        raise ValueError("only LoRA adapters are supported (prompt-learning methods change the input sequence)")
     save = set(cfg.modules_to_save or [])
     for n, p in model.named_parameters():
         top = n.split(".")[0]
