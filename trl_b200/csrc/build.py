@@ -24,7 +24,7 @@ OBJ = os.path.join(LIB, "obj")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-Xptxas", "-v", "--expt-relaxed-constexpr"]
-# kernels that only 1-GPU calls may use live in files listed in .gpurunignore.multi; none exist at present.
+# every source here builds into the one library used at any GPU count (no loads shared across a thread-block cluster)
 
 
 def _nvcc() -> str:
