@@ -437,6 +437,25 @@ __global__ void bounded_wait_selftest_kernel(const uint32_t* flag, uint32_t expe
   }
 }
 
+// Trainer -> generator weight sync from sharded parameters: a list of contiguous ranges, each read from the rank that
+// owns it (a peer mapping of the symmetric parameter arena, or local memory) and written into this rank's
+// tensor-parallel weight buffers.  One CTA per range at a time, 16 bytes per thread and iteration.  The list is built
+// once on the host (the layout of buckets and TP slices does not change during training).
+struct CopyEntry {
+  unsigned long long src, dst;
+  unsigned long long bytes;  // multiple of 16; src and dst 16-byte aligned
+};
+
+__global__ void __launch_bounds__(256) copy_list_kernel(const CopyEntry* __restrict__ list, int n) {
+  for (int e = blockIdx.x; e < n; e += gridDim.x) {
+    const CopyEntry c = list[e];
+    const uint4* s = reinterpret_cast<const uint4*>(c.src);
+    uint4* d = reinterpret_cast<uint4*>(c.dst);
+    const unsigned long long nv = c.bytes >> 4;
+    for (unsigned long long v = threadIdx.x; v < nv; v += blockDim.x) d[v] = s[v];
+  }
+}
+
 }  // namespace trlb
 
 using namespace trlb;
@@ -521,5 +540,13 @@ TRLB_API int trlb_allreduce_add_rmsnorm(const unsigned long long* bufs, const un
 TRLB_API int trlb_bounded_wait_selftest(const void* flag, unsigned expect, int budget_ms, int* status, cudaStream_t st) {
   if (budget_ms < 1 || budget_ms > 1000) return -160;  // the budget is what keeps this from being a hang
   bounded_wait_selftest_kernel<<<1, 32, 0, st>>>((const uint32_t*)flag, expect, (uint64_t)budget_ms * 1000000ull, status);
+  return (int)cudaGetLastError();
+}
+
+// list: device array of n {src, dst, bytes} triples (uint64 each).
+TRLB_API int trlb_copy_list(const void* list, int n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  int grid = n < 148 * 8 ? n : 148 * 8;
+  copy_list_kernel<<<grid, 256, 0, st>>>((const CopyEntry*)list, n);
   return (int)cudaGetLastError();
 }

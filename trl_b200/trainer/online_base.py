@@ -254,9 +254,18 @@ class OnlineTrainer(Trainer):
         eng = self._get_rollout()
         if self.state.global_step != self._last_loaded_step and hasattr(eng, "sync_weights"):
             with self._profile("sync_weights"):  # trainer -> generator weights (no-op when storage is shared)
-                if getattr(self, "engine", None) is not None and hasattr(self.engine, "gather_full_params"):
-                    self.engine.gather_full_params()  # full-shard: the generator reads the buffers directly
-                eng.sync_weights()
+                sharded = getattr(self, "engine", None) is not None and hasattr(self.engine, "gather_full_params")
+                if sharded and hasattr(eng, "w") and getattr(eng, "tp", 1) > 1:
+                    # full shard -> TP layout: every TP rank pulls exactly its slices from the owners' shards
+                    if getattr(self, "_resharder", None) is None:
+                        from ..parallel.reshard import WeightResharder
+
+                        self._resharder = WeightResharder(self.engine, eng)
+                    self._resharder.run()
+                else:
+                    if sharded:
+                        self.engine.gather_full_params()  # the generator reads the policy's buffers directly
+                    eng.sync_weights()
             self._last_loaded_step = self.state.global_step
         with self._profile("rollout.generate"):
             if len(set(counts)) == 1:
