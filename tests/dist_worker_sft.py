@@ -30,8 +30,12 @@ def main():
     torch.manual_seed(0)
     model = make_tiny_model("tiny-qwen2", seed=0)
     rows = synthetic_token_batches(1024, 4 * steps, 128, seed=3)
-    args = SFTConfig(output_dir=out + "_o", per_device_train_batch_size=4 // world, max_steps=steps, logging_steps=1,
+    sp = 2 if mode == "sp2" else 1  # "sp2": Ulysses sequence parallelism over both ranks, plain data-parallel engine
+    pc = {"sp_size": sp} if sp > 1 else None
+    mode = "ddp" if sp > 1 else mode
+    args = SFTConfig(output_dir=out + "_o", per_device_train_batch_size=4 // (world // sp), max_steps=steps, logging_steps=1,
                      learning_rate=1e-4, use_cpu=True, save_strategy="no", padding_free=True, shard_mode=mode,
+                     parallelism_config=pc,
                      lr_scheduler_type="constant", train_sampling_strategy="sequential", completion_only_loss=True,
                      dataset_kwargs={"skip_prepare_dataset": True}, gradient_checkpointing=False, max_length=None)
     tr = SFTTrainer(model, args, train_dataset=rows, processing_class=Tok())

@@ -260,14 +260,35 @@ class Trainer:
     def _shard_train_batches(self) -> bool:
         return True
 
+    @property
+    def sp_size(self) -> int:
+        pc = self.args.parallelism_config
+        sp = int((pc or {}).get("sp_size", 1)) if isinstance(pc, dict) else 1
+        if sp > 1 and D.world_size() % sp:
+            raise ValueError(f"sp_size ({sp}) must divide the world size ({D.world_size()})")
+        return sp if D.world_size() > 1 else 1
+
+    def sp_info(self):
+        """Sequence-parallel group of this rank (consecutive ranks), or None."""
+        sp = self.sp_size
+        if sp <= 1:
+            return None
+        if getattr(self, "_sp_info", None) is None:
+            from ..parallel.ulysses import SpInfo
+
+            groups = [list(range(i, i + sp)) for i in range(0, D.world_size(), sp)]
+            self._sp_info = SpInfo(D.new_subgroups_by_enumeration(groups), sp, D.rank() % sp)
+        return self._sp_info
+
     def get_train_dataloader(self):
         ds = self.train_dataset
         if ds is None:
             raise ValueError("Trainer: training requires a train_dataset.")
         if not hasattr(ds, "__len__") or not hasattr(ds, "__getitem__"):
             return DataLoaderLite(ds, None, self.data_collator, self._train_batch_size, D.rank(), D.world_size())
+        sp = self.sp_size  # ranks of one sequence-parallel group read the same batches
         bs = ShardedBatchSampler(self._get_train_sampler(ds), self._train_batch_size, self.args.dataloader_drop_last,
-                                 D.rank(), D.world_size(), self._shard_train_batches())
+                                 D.rank() // sp, D.world_size() // sp, self._shard_train_batches())
         return DataLoaderLite(ds, bs, self.data_collator,
                               pin_memory=self.args.dataloader_pin_memory and self.args.device.type == "cuda")
 
@@ -349,6 +370,8 @@ class Trainer:
         t = torch.tensor(n, dtype=torch.long, device=self.args.device)
         if self.args.average_tokens_across_devices and D.world_size() > 1:
             D.all_reduce(t, "sum")
+            if self.sp_size > 1:  # every batch was counted once per rank of its sequence-parallel group
+                t = t // self.sp_size
         return t
 
     # ---- main loop ------------------------------------------------------------------------

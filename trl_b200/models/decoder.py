@@ -33,6 +33,8 @@ class SeqCtx:
     # rollout-only: paged KV cache handles (see trl_b200.rollout.kv_cache)
     kv: Any = None
     router_records: list = field(default_factory=list)
+    # sequence parallelism (parallel/ulysses.py): positions are this rank's chunk, cu_seqlens / max_seqlen are global
+    sp: Any = None
 
     @staticmethod
     def from_lengths(lengths, device) -> "SeqCtx":
@@ -157,6 +159,11 @@ class DecoderLayer(nn.Module):
         q, k = ops.apply_rope_qk(q, k, ctx.positions, c.rope_theta)
         if ctx.kv is not None:
             o = ctx.kv.attend(self.layer_idx, q, k, v, ctx)
+        elif ctx.sp is not None:
+            from ..parallel import ulysses
+
+            o = ulysses.attention(q, k, v, ctx, lambda a, b, d: ops.attention_varlen(a, b, d, ctx.cu_seqlens, ctx.max_seqlen,
+                                                                                   causal=True))
         else:
             o = ops.attention_varlen(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, causal=True)
         o = o.reshape(T, c.q_size)

@@ -319,6 +319,11 @@ class SFTTrainer(Trainer):
 
     def compute_loss(self, model, inputs, return_outputs=False, num_items_in_batch=None):
         flat, ctx, tgt = self._flat_labels(model, inputs)
+        sp = self.sp_info()
+        if sp is not None:  # Ulysses: this rank keeps one chunk of the packed stream
+            from ..parallel.ulysses import shard_sequence
+
+            flat, tgt, ctx = shard_sequence(flat, tgt, ctx, sp, self.processing_class.pad_token_id or 0)
         if model.training:
             n_tok = torch.tensor(float(flat.numel()), device=flat.device)
             self._metrics["train"]["_num_tokens"].append(n_tok)
