@@ -7,36 +7,32 @@ KL used by trl/experimental/minillm and trl/experimental/distillation."""
 from __future__ import annotations
 
 import torch
-import torch.nn.functional as F
 
 
 def generalized_jsd_loss(student_logits, teacher_logits, labels=None, beta: float = 0.5, temperature: float = 1.0,
                          reduction: str = "batchmean", num_items_in_batch=None):
-    """JSD(beta) with beta=0 -> KL(teacher || student) (forward KL), beta=1 -> KL(student || teacher) (reverse KL),
-    otherwise beta * KL(teacher || M) + (1 - beta) * KL(student || M), M = beta * teacher + (1 - beta) * student."""
-    s = F.log_softmax(student_logits / temperature, dim=-1)
-    t = F.log_softmax(teacher_logits / temperature, dim=-1)
-    if beta == 0:
-        jsd = F.kl_div(s, t, reduction="none", log_target=True)
-    elif beta == 1:
-        jsd = F.kl_div(t, s, reduction="none", log_target=True)
-    else:
-        b = torch.tensor(beta, dtype=s.dtype, device=s.device)
-        mix = torch.logsumexp(torch.stack([s + torch.log1p(-b), t + torch.log(b)]), dim=0)
-        jsd = b * F.kl_div(mix, t, reduction="none", log_target=True) + (1 - b) * F.kl_div(mix, s, reduction="none",
-                                                                                         log_target=True)
+    """JSD(beta) per position, then reduced.  beta = 0: KL(teacher || student) (forward KL); beta = 1: KL(student ||
+    teacher) (reverse KL); otherwise beta * KL(teacher || M) + (1 - beta) * KL(student || M) with the mixture
+    M = beta * teacher + (1 - beta) * student.  ``labels == -100`` positions are left out."""
+    from .sdft.loss_utils import compute_divergence
+
+    per_pos = compute_divergence(torch.log_softmax(student_logits / temperature, -1),
+                                 torch.log_softmax(teacher_logits / temperature, -1), float(beta))
     if labels is not None:
-        jsd = jsd[labels != -100]
+        keep = labels != -100
+        per_pos = per_pos[keep]
+        count = keep.sum()
+    else:
+        count = per_pos.numel()
     if num_items_in_batch is not None:
-        return jsd.sum() / num_items_in_batch
+        return per_pos.sum() / num_items_in_batch
     if reduction == "batchmean":
-        n = (labels != -100).sum() if labels is not None else jsd.shape[0] * (jsd.shape[1] if jsd.ndim == 3 else 1)
-        return jsd.sum() / n
+        return per_pos.sum() / count
     if reduction == "sum":
-        return jsd.sum()
+        return per_pos.sum()
     if reduction == "mean":
-        return jsd.mean()
-    return jsd
+        return per_pos.mean()
+    return per_pos
 
 
 def chunked_token_divergence(h_student, w_student, h_teacher, w_teacher, beta: float = 0.5, temperature: float = 1.0,
@@ -52,7 +48,7 @@ def chunked_token_divergence(h_student, w_student, h_teacher, w_teacher, beta: f
             zt = h_teacher[sl].float() @ w_teacher.float().t()
         if softcap:
             zs, zt = torch.tanh(zs / softcap) * softcap, torch.tanh(zt / softcap) * softcap
-        d = generalized_jsd_loss(zs, zt, beta=beta, temperature=temperature, reduction="none").sum(-1)
+        d = generalized_jsd_loss(zs, zt, beta=beta, temperature=temperature, reduction="none")
         per_row.append(d.detach())
         total = total + (d * weights[sl] if weights is not None else d).sum()
     return total, (torch.cat(per_row) if per_row else h_student.new_zeros(0))

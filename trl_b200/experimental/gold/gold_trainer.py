@@ -84,7 +84,7 @@ class ULDLoss:
                 qs, qt = ps[:, ms], pt[:, mt]
                 matched_mass = 0.5 * (qs.sum(-1) + qt.sum(-1)).detach()
                 jsd = generalized_jsd_loss(torch.log(qs.clamp_min(1e-12)), torch.log(qt.clamp_min(1e-12)), beta=c.beta,
-                                           reduction="none").sum(-1)
+                                           reduction="none")
                 wm = c.uld_hybrid_matched_weight if c.uld_hybrid_matched_weight is not None else matched_mass
                 wu = c.uld_hybrid_unmatched_weight if c.uld_hybrid_unmatched_weight is not None else 1 - matched_mass
                 keep_s = torch.ones(ps.shape[1], dtype=torch.bool, device=ps.device)

@@ -17,7 +17,7 @@ from ...parallel import dist as D
 from ...trainer.grpo_trainer import GRPOTrainer
 from .._self_distill import SelfDistillMixin
 from .sdpo_config import SDPOConfig
-from .teacher_sync import build_teacher
+from ..sdft.teacher_sync import build_teacher
 
 _THINK = re.compile(r"<think>.*?</think>", re.S)
 
