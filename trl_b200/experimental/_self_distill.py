@@ -4,9 +4,6 @@ from __future__ import annotations
 
 import torch
 
-from .sdft.loss_utils import (apply_importance_sampling_clipping, compute_full_logit_self_distillation_loss,
-                              compute_sampled_token_self_distillation_loss, compute_topk_self_distillation_loss)
-
 
 class SelfDistillMixin:
     """Needs ``self._get_per_token_logps_and_entropies`` (online trainer), ``self.teacher`` (module or None) and the
@@ -25,6 +22,9 @@ class SelfDistillMixin:
     def self_distillation_loss(self, model, prompt_ids, teacher_prompt_ids, completion_ids, old_logps=None,
                                row_weight=None, chunk: int = 1024):
         """Mean over completion tokens (of rows with weight > 0) of the configured divergence."""
+        from .sdft.loss_utils import (apply_importance_sampling_clipping, compute_full_logit_self_distillation_loss,
+                                      compute_sampled_token_self_distillation_loss, compute_topk_self_distillation_loss)
+
         a = self.args
         lp, h_s, r, c = self._selected(model, prompt_ids, completion_ids, grad=True)
         teacher = self.teacher if self.teacher is not None else model
