@@ -41,12 +41,23 @@ def main():
     assert all(1 <= len(t) <= 12 for t in allo[rank])
     # weight refresh: after changing the policy weights and sync_weights() the engine must follow
     with torch.no_grad():
+        gen = torch.Generator(device=dev).manual_seed(3)  # same perturbation on both ranks
         for p in model.parameters():
-            p.mul_(0.5)
+            if p.ndim == 2:
+                p.add_(torch.randn(p.shape, generator=gen, device=dev, dtype=torch.float32).to(p.dtype) * 0.02)
     eng.sync_weights()
+    cfg = model.config
+    ql = eng.hq_local * cfg.head_dim
+    il = cfg.intermediate_size // 2
+    for l, w in zip(model.layers, eng.w):  # the TP buffers are exact slices of the new weights
+        assert torch.equal(w["qkv"][:ql], l.qkv_proj[rank * ql:(rank + 1) * ql])
+        assert torch.equal(w["o"], l.o_proj[:, rank * ql:(rank + 1) * ql])
+        assert torch.equal(w["gu"][:il], l.gate_up_proj[rank * il:(rank + 1) * il])
+        assert torch.equal(w["down"], l.down_proj[:, rank * il:(rank + 1) * il])
     ref3 = RolloutEngine(model, max_num_seqs=4, max_model_len=64, poll_every=4).generate(mine, sp)
     out3 = eng.generate(mine, sp)
-    assert sum(o.token_ids[:3] == r.token_ids[:3] for o, r in zip(out3, ref3)) >= 3
+    # greedy decoding of a tiny random model sits on near-ties, and the two engines round differently: most, not all
+    assert sum(o.token_ids[:2] == r.token_ids[:2] for o, r in zip(out3, ref3)) >= 2, [(o.token_ids, r.token_ids) for o, r in zip(out3, ref3)]
     td.barrier()
     if rank == 0:
         print("TP_ROLLOUT_OK")
