@@ -21,6 +21,7 @@ _FAMILY_ARCH = {
     "qwen3": "Qwen3ForCausalLM",
     "qwen3_moe": "Qwen3MoeForCausalLM",
     "mistral": "MistralForCausalLM",
+    "phi3": "Phi3ForCausalLM",
 }
 
 
@@ -212,6 +213,12 @@ PRESETS: dict[str, dict] = {
     "tiny-qwen3-moe": dict(model_type="qwen3_moe", vocab_size=1024, hidden_size=64, intermediate_size=256,
                            num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
                            num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64),
+    "tiny-mistral": dict(model_type="mistral", vocab_size=1024, hidden_size=64, intermediate_size=256,
+                         num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2),
+    "tiny-phi3": dict(model_type="phi3", vocab_size=1024, hidden_size=64, intermediate_size=256,
+                      num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2),
+    "tiny-qwen3": dict(model_type="qwen3", vocab_size=1024, hidden_size=64, intermediate_size=256,
+                       num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32),
     "llama-3-8b": dict(model_type="llama", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
                        num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
                        rope_theta=5e5, rms_norm_eps=1e-5, max_position_embeddings=8192),

@@ -34,8 +34,12 @@ def to_hf_state_dict(model, include_lora: bool = False) -> dict[str, torch.Tenso
     for i, l in enumerate(model.layers):
         p = f"model.layers.{i}."
         qkv = l.qkv_proj.detach()
-        q, k, v = qkv.split([c.q_size, c.kv_size, c.kv_size], dim=0)
-        sd[p + "self_attn.q_proj.weight"], sd[p + "self_attn.k_proj.weight"], sd[p + "self_attn.v_proj.weight"] = q, k, v
+        fused_on_disk = c.model_type == "phi3"  # Phi-3 checkpoints keep qkv_proj and gate_up_proj fused, like memory here
+        if fused_on_disk:
+            sd[p + "self_attn.qkv_proj.weight"] = qkv
+        else:
+            q, k, v = qkv.split([c.q_size, c.kv_size, c.kv_size], dim=0)
+            sd[p + "self_attn.q_proj.weight"], sd[p + "self_attn.k_proj.weight"], sd[p + "self_attn.v_proj.weight"] = q, k, v
         if l.qkv_bias is not None:
             bq, bk, bv = l.qkv_bias.detach().split([c.q_size, c.kv_size, c.kv_size])
             sd[p + "self_attn.q_proj.bias"], sd[p + "self_attn.k_proj.bias"], sd[p + "self_attn.v_proj.bias"] = bq, bk, bv
@@ -54,8 +58,11 @@ def to_hf_state_dict(model, include_lora: bool = False) -> dict[str, torch.Tenso
                 sd[p + f"mlp.experts.{e}.down_proj.weight"] = l.experts_down.detach()[e]
         else:
             I = c.intermediate_size
-            sd[p + "mlp.gate_proj.weight"] = l.gate_up_proj.detach()[:I]
-            sd[p + "mlp.up_proj.weight"] = l.gate_up_proj.detach()[I:]
+            if fused_on_disk:
+                sd[p + "mlp.gate_up_proj.weight"] = l.gate_up_proj.detach()
+            else:
+                sd[p + "mlp.gate_proj.weight"] = l.gate_up_proj.detach()[:I]
+                sd[p + "mlp.up_proj.weight"] = l.gate_up_proj.detach()[I:]
             sd[p + "mlp.down_proj.weight"] = l.down_proj.detach()
     sd["model.norm.weight"] = model.norm.detach()
     if c.num_labels:
@@ -86,9 +93,13 @@ def load_hf_state_dict(model, sd: dict[str, torch.Tensor], strict: bool = True) 
     put(model.embed_tokens, take("model.embed_tokens.weight"))
     for i, l in enumerate(model.layers):
         p = f"model.layers.{i}."
-        put(l.qkv_proj[: c.q_size], take(p + "self_attn.q_proj.weight"))
-        put(l.qkv_proj[c.q_size: c.q_size + c.kv_size], take(p + "self_attn.k_proj.weight"))
-        put(l.qkv_proj[c.q_size + c.kv_size:], take(p + "self_attn.v_proj.weight"))
+        fused_qkv = take(p + "self_attn.qkv_proj.weight", required=False)
+        if fused_qkv is not None:  # Phi-3 layout
+            put(l.qkv_proj, fused_qkv)
+        else:
+            put(l.qkv_proj[: c.q_size], take(p + "self_attn.q_proj.weight"))
+            put(l.qkv_proj[c.q_size: c.q_size + c.kv_size], take(p + "self_attn.k_proj.weight"))
+            put(l.qkv_proj[c.q_size + c.kv_size:], take(p + "self_attn.v_proj.weight"))
         if l.qkv_bias is not None:
             put(l.qkv_bias[: c.q_size], take(p + "self_attn.q_proj.bias"))
             put(l.qkv_bias[c.q_size: c.q_size + c.kv_size], take(p + "self_attn.k_proj.bias"))
@@ -113,8 +124,12 @@ def load_hf_state_dict(model, sd: dict[str, torch.Tensor], strict: bool = True) 
                     put(l.experts_down[e], take(p + f"mlp.experts.{e}.down_proj.weight"))
         else:
             I = c.intermediate_size
-            put(l.gate_up_proj[:I], take(p + "mlp.gate_proj.weight"))
-            put(l.gate_up_proj[I:], take(p + "mlp.up_proj.weight"))
+            fused_gate_up = take(p + "mlp.gate_up_proj.weight", required=False)
+            if fused_gate_up is not None:
+                put(l.gate_up_proj, fused_gate_up)
+            else:
+                put(l.gate_up_proj[:I], take(p + "mlp.gate_proj.weight"))
+                put(l.gate_up_proj[I:], take(p + "mlp.up_proj.weight"))
             put(l.down_proj, take(p + "mlp.down_proj.weight"))
     put(model.norm, take("model.norm.weight"))
     if c.num_labels:
