@@ -21,7 +21,7 @@ def _hf_model(cfg: ModelArch):
     return hf
 
 
-@pytest.mark.parametrize("name", ["tiny-qwen2", "tiny-llama", "tiny-qwen3-moe", "tiny-mistral", "tiny-phi3", "tiny-qwen3"])
+@pytest.mark.parametrize("name", ["tiny-qwen2", "tiny-llama", "tiny-qwen3-moe", "tiny-mistral", "tiny-phi3", "tiny-qwen3", "tiny-gemma"])
 def test_logits_match_transformers(name, tmp_path):
     torch.manual_seed(0)
     cfg = preset(name)

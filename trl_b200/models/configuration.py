@@ -22,6 +22,7 @@ _FAMILY_ARCH = {
     "qwen3_moe": "Qwen3MoeForCausalLM",
     "mistral": "MistralForCausalLM",
     "phi3": "Phi3ForCausalLM",
+    "gemma": "GemmaForCausalLM",
 }
 
 
@@ -54,6 +55,10 @@ class ModelArch:
     bos_token_id: int | None = None
     eos_token_id: int | None = None
     final_logit_softcapping: float | None = None
+    # Gemma: GeGLU instead of SwiGLU, RMSNorm scales by (1 + w), embeddings multiplied by sqrt(hidden)
+    hidden_act: str = "silu"
+    norm_plus_one: bool = False
+    embed_scale: float = 1.0
     extra: dict = field(default_factory=dict)
 
     def __post_init__(self):
@@ -65,6 +70,11 @@ class ModelArch:
             self.qk_norm = self.model_type in ("qwen3", "qwen3_moe")
         if self.num_key_value_heads is None:
             self.num_key_value_heads = self.num_attention_heads
+        if self.model_type == "gemma":
+            self.norm_plus_one, self.embed_scale = True, float(self.hidden_size) ** 0.5
+            self.tie_word_embeddings = True
+            if self.hidden_act == "silu":
+                self.hidden_act = "gelu_pytorch_tanh"
 
     # ---- derived sizes -------------------------------------------------
     @property
@@ -107,7 +117,8 @@ class ModelArch:
             "num_attention_heads": self.num_attention_heads,
             "num_key_value_heads": self.num_key_value_heads,
             "head_dim": self.head_dim,
-            "hidden_act": "silu",
+            "hidden_act": self.hidden_act,
+            **({"hidden_activation": self.hidden_act} if self.model_type == "gemma" else {}),
             "rms_norm_eps": self.rms_norm_eps,
             "rope_theta": self.rope_theta,
             "rope_parameters": {"rope_type": "default", "rope_theta": self.rope_theta},
@@ -156,6 +167,7 @@ class ModelArch:
             nl = int(d.get("num_labels", len(d.get("id2label", {"0": 0})) or 1))
         return cls(
             model_type=mt,
+            hidden_act=(d.get("hidden_activation") or d.get("hidden_act") or "silu") if mt == "gemma" else "silu",
             vocab_size=d["vocab_size"],
             hidden_size=d["hidden_size"],
             intermediate_size=d.get("intermediate_size", 4 * d["hidden_size"]),
@@ -217,6 +229,8 @@ PRESETS: dict[str, dict] = {
                          num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2),
     "tiny-phi3": dict(model_type="phi3", vocab_size=1024, hidden_size=64, intermediate_size=256,
                       num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2),
+    "tiny-gemma": dict(model_type="gemma", vocab_size=1024, hidden_size=64, intermediate_size=256,
+                       num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=1, head_dim=32, rope_theta=10000.0),
     "tiny-qwen3": dict(model_type="qwen3", vocab_size=1024, hidden_size=64, intermediate_size=256,
                        num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32),
     "llama-3-8b": dict(model_type="llama", vocab_size=128256, hidden_size=4096, intermediate_size=14336,

@@ -179,14 +179,21 @@ class DecoderLayer(nn.Module):
             return out
         gu = ops.linear(x, self.gate_up_proj)
         gu = self._lora_add(gu, x, ("gate_proj", "up_proj"))
-        a = ops.swiglu(gu)
+        if c.hidden_act == "silu":
+            a = ops.swiglu(gu)
+        else:  # GeGLU (Gemma): gelu(gate) * up
+            g, u = gu.chunk(2, dim=-1)
+            a = torch.nn.functional.gelu(g, approximate="tanh" if "tanh" in c.hidden_act else "none") * u
         out = ops.linear(a, self.down_proj)
         return self._lora_add(out, a, ("down_proj",))
 
     def forward(self, x, ctx: SeqCtx):
         c = self.cfg
-        x = x + self.attn_block(ops.rms_norm(x, self.input_layernorm, c.rms_norm_eps), ctx)
-        x = x + self.mlp_block(ops.rms_norm(x, self.post_attention_layernorm, c.rms_norm_eps), ctx)
+        w1, w2 = self.input_layernorm, self.post_attention_layernorm
+        if c.norm_plus_one:  # Gemma stores w - 1
+            w1, w2 = w1 + 1.0, w2 + 1.0
+        x = x + self.attn_block(ops.rms_norm(x, w1, c.rms_norm_eps), ctx)
+        x = x + self.mlp_block(ops.rms_norm(x, w2, c.rms_norm_eps), ctx)
         return x
 
 
@@ -298,10 +305,14 @@ class CausalLM(nn.Module):
 
     # ---- stages (used directly by the sharded engine) -----------------------
     def embed(self, input_ids: torch.Tensor) -> torch.Tensor:
-        return torch.nn.functional.embedding(input_ids, self.embed_tokens)
+        x = torch.nn.functional.embedding(input_ids, self.embed_tokens)
+        if self.config.embed_scale != 1.0:
+            x = x * torch.tensor(self.config.embed_scale, dtype=x.dtype)  # rounded to the model dtype like the reference model
+        return x
 
     def final_norm(self, x):
-        return ops.rms_norm(x, self.norm, self.config.rms_norm_eps)
+        w = self.norm + 1.0 if self.config.norm_plus_one else self.norm
+        return ops.rms_norm(x, w, self.config.rms_norm_eps)
 
     def forward_hidden(self, input_ids: torch.Tensor, ctx: SeqCtx) -> torch.Tensor:
         """Flat ids [T] -> final-norm hidden [T, H]."""

@@ -133,6 +133,9 @@ class RolloutEngine:
         self.dev = model.device
         if self.dev.type != "cuda":
             raise RuntimeError("RolloutEngine needs a CUDA device; use EagerGenerator on CPU")
+        if cfg.hidden_act != "silu" or cfg.norm_plus_one or cfg.embed_scale != 1.0 or cfg.head_dim not in (64, 128):
+            raise NotImplementedError("the decode kernels cover SwiGLU models with head_dim 64 or 128; use EagerGenerator "
+                                      f"for model_type={cfg.model_type!r}")
         from .._native import host_runtime
 
         rt = host_runtime()

@@ -208,8 +208,16 @@ class OnlineTrainer(Trainer):
                     self._rollout = TPRolloutEngine(self.model, self._tp_group, max_num_seqs=nseq, max_model_len=max_len,
                                                     block_size=bs, poll_every=a.rollout_poll_every)
                 else:
-                    self._rollout = RolloutEngine(self.model, max_num_seqs=nseq, max_model_len=max_len, block_size=bs,
-                                                  poll_every=a.rollout_poll_every)
+                    try:
+                        self._rollout = RolloutEngine(self.model, max_num_seqs=nseq, max_model_len=max_len, block_size=bs,
+                                                      poll_every=a.rollout_poll_every)
+                    except NotImplementedError as e:  # e.g. GeGLU models: correct but slow eager generation
+                        import warnings
+
+                        from ..rollout.engine import EagerGenerator
+
+                        warnings.warn(f"{e}; falling back to the eager generator")
+                        self._rollout = EagerGenerator(self.model)
             else:
                 from ..rollout.engine import EagerGenerator
 
