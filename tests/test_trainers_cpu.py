@@ -307,3 +307,13 @@ def test_fused_lm_head_losses_reject_an_adapted_lm_head(tmp_path, tiny_tokenizer
         SFTTrainer(make_tiny_model(), SFTConfig(output_dir=str(tmp_path), **COMMON),
                    train_dataset=make_dataset("standard_language_modeling", 8), processing_class=tiny_tokenizer,
                    peft_config=LoraConfig(r=4, target_modules=["q_proj", "lm_head"]))
+
+
+@pytest.mark.parametrize("name", ["tiny-gemma", "tiny-phi3", "tiny-mistral"])
+def test_sft_trains_other_families(tmp_path, tiny_tokenizer, name):
+    model = make_tiny_model(name)
+    before = _snap(model)
+    tr = SFTTrainer(model, SFTConfig(output_dir=str(tmp_path), **COMMON), train_dataset=make_dataset("standard_language_modeling", 16),
+                    processing_class=tiny_tokenizer)
+    tr.train()
+    assert _changed(model, before) == []
