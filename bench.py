@@ -48,8 +48,11 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--rollout-tp", type=int, default=0, help="0 = 2 when more than one GPU, else 1")
     ap.add_argument("--layers", type=int, default=None, help="debug only: truncating the model invalidates the number")
-    ap.add_argument("--grad-ckpt", default="on", choices=["on", "off"],
-                    help="activation checkpointing (off keeps activations: faster when the sharded state leaves room)")
+    ap.add_argument("--grad-ckpt", default="auto", choices=["auto", "on", "off"],
+                    help="activation checkpointing; auto = off when the optimizer state is sharded over >= 2 ranks "
+                         "(it leaves room for the activations), else on; an out-of-memory warm-up step switches it on")
+    ap.add_argument("--ckpt-layers", type=int, default=None,
+                    help="with checkpointing on: recompute only the first n layers, keep the activations of the rest")
     return ap.parse_args()
 
 
@@ -162,13 +165,15 @@ def main():
     ga = per_rank // a.micro_batch
     out_dir = tempfile.mkdtemp(prefix="bench_grpo_")
     rollout_tp = a.rollout_tp or (2 if world > 1 else 1)
-    grad_ckpt = a.grad_ckpt == "on"
+    grad_ckpt = a.grad_ckpt == "on" or (a.grad_ckpt == "auto" and world == 1)
+    ckpt_kwargs = {"num_layers": a.ckpt_layers} if a.ckpt_layers is not None else None
     args = GRPOConfig(output_dir=out_dir, per_device_train_batch_size=a.micro_batch, gradient_accumulation_steps=ga,
                       num_generations=a.num_generations, max_completion_length=a.max_new, temperature=1.0, beta=0.04,
                       epsilon=0.2, learning_rate=1e-6, max_steps=a.steps, logging_steps=1, save_strategy="no",
                       bf16=True, use_vllm=True, vllm_mode="colocate", eos_prob_floor=1.0 / 512, shuffle_dataset=False,
                       shard_mode="zero2" if world > 1 else "ddp", report_to="none", seed=7,
                       vllm_importance_sampling_correction=False, gradient_checkpointing=grad_ckpt,
+                      gradient_checkpointing_kwargs=ckpt_kwargs,
                       vllm_tensor_parallel_size=rollout_tp)
     trainer = GRPOTrainer(model, even_fraction_reward, args, train_dataset=rows, processing_class=tok)
     trainer.callback_handler.callbacks = [c for c in trainer.callback_handler.callbacks
@@ -263,7 +268,7 @@ def main():
                        "global_batch": per_rank * world, "prompts_per_step": a.prompts_per_gpu * world,
                        "num_generations": a.num_generations, "seq_len": a.prompt_len + a.max_new,
                        "prompt_len": a.prompt_len, "max_new_tokens": a.max_new, "eos_prob_floor": 1.0 / 512,
-                       "beta": 0.04, "epsilon": 0.2, "loss_type": "dapo", "micro_batch": a.micro_batch, "activation_checkpointing": bool(grad_ckpt),
+                       "beta": 0.04, "epsilon": 0.2, "loss_type": "dapo", "micro_batch": a.micro_batch, "activation_checkpointing": (bool(grad_ckpt) if not (grad_ckpt and getattr(model, "checkpoint_num_layers", None) is not None) else f"first {model.checkpoint_num_layers} layers"),
                        "parallelism": f"dp{world} {args.shard_mode}, rollout tp{rollout_tp} x {world // rollout_tp} replicas "
                                       f"(colocated)",
                        "l2_policy": "inputs larger than L2: every step streams >=15 GB of weights",

@@ -106,3 +106,24 @@ def test_lora_adapters_train_and_round_trip(tmp_path):
     m.merge_adapter()
     m.set_adapter_enabled(False)
     assert torch.allclose(m(input_ids=ids).logits, tuned, atol=1e-4)
+
+
+def test_partial_gradient_checkpointing_matches_full_activations():
+    torch.manual_seed(0)
+    m = CausalLM(preset("tiny-qwen2")).train()
+    ids = torch.randint(0, 1024, (2, 12))
+
+    def grads():
+        m.zero_grad()
+        m(input_ids=ids).logits.float().logsumexp(-1).sum().backward()
+        return [p.grad.clone() for p in m.parameters()]
+
+    ref = grads()
+    m.gradient_checkpointing_enable({"num_layers": 1})  # recompute layer 0 only
+    assert m.checkpoint_num_layers == 1
+    part = grads()
+    m.gradient_checkpointing_enable()  # back to all layers
+    assert m.checkpoint_num_layers is None
+    full = grads()
+    for a, b, c in zip(ref, part, full):
+        assert torch.allclose(a, b, atol=1e-6) and torch.allclose(a, c, atol=1e-6)

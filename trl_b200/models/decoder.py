@@ -275,7 +275,11 @@ class CausalLM(nn.Module):
         return sum(p.numel() for p in self.parameters() if p.requires_grad or not only_trainable)
 
     def gradient_checkpointing_enable(self, gradient_checkpointing_kwargs=None):
+        """``gradient_checkpointing_kwargs={"num_layers": n}`` recomputes only the first n layers and keeps the
+        activations of the rest (a memory/time dial between "off" and "all layers")."""
         self.gradient_checkpointing = True
+        n = (gradient_checkpointing_kwargs or {}).get("num_layers")
+        self.checkpoint_num_layers = None if n is None else int(n)
 
     def gradient_checkpointing_disable(self):
         self.gradient_checkpointing = False
@@ -317,8 +321,10 @@ class CausalLM(nn.Module):
     def forward_hidden(self, input_ids: torch.Tensor, ctx: SeqCtx) -> torch.Tensor:
         """Flat ids [T] -> final-norm hidden [T, H]."""
         x = self.embed(input_ids)
-        for layer in self.layers:
-            if self.gradient_checkpointing and self.training and torch.is_grad_enabled():
+        n_ckpt = getattr(self, "checkpoint_num_layers", None)
+        for li, layer in enumerate(self.layers):
+            if (self.gradient_checkpointing and self.training and torch.is_grad_enabled()
+                    and (n_ckpt is None or li < n_ckpt)):
                 from torch.utils.checkpoint import checkpoint
 
                 x = checkpoint(layer, x, ctx, use_reentrant=False)
