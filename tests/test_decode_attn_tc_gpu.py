@@ -26,8 +26,9 @@ def _reference(q, kc, vct, lens, table, scale):
     return out
 
 
+@pytest.mark.parametrize("groups", [1, 2])
 @pytest.mark.parametrize("Hq,Hk,splits", [(28, 4, 3), (8, 2, 1), (14, 2, 2)])
-def test_decode_attention_tc_matches_reference(Hq, Hk, splits):
+def test_decode_attention_tc_matches_reference(Hq, Hk, splits, groups):
     from trl_b200.ops import cuda as K
 
     torch.manual_seed(0)
@@ -46,7 +47,7 @@ def test_decode_attention_tc_matches_reference(Hq, Hk, splits):
     seq_lens = (lens - 1).cuda()  # the kernel attends over seq_lens + 1 tokens; -1 marks an inactive slot
     scale = 1 / math.sqrt(D)
     for _ in range(2):  # second call: barriers, TMEM and partial buffers are reusable
-        K.paged_decode_attn_tc(q, kc, vct, seq_lens, None, table, scale, splits, part_o, part_ml, out)
+        K.paged_decode_attn_tc(q, kc, vct, seq_lens, None, table, scale, splits, part_o, part_ml, out, groups=groups)
     torch.cuda.synchronize()
     K.check_status(q.device)
     ref = _reference(q, kc, vct, lens, table, scale)

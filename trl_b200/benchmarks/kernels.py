@@ -135,6 +135,10 @@ def main():
                          a.iters, a.warmup)
             out[f"tcgen05_splits{sp}_ms"] = ms2
             out[f"tcgen05_splits{sp}_frac_of_copy_bw"] = byt / ms2 / 1e6 / hbm
+            ms3 = timeit(lambda: K.paged_decode_attn_tc(q, kc2, vt2, lens, None, table2, 1 / math.sqrt(D), sp, po2, pml2, o,
+                                                        groups=2), a.iters, a.warmup)
+            out[f"tcgen05_2groups_splits{sp}_ms"] = ms3
+            out[f"tcgen05_2groups_splits{sp}_frac_of_copy_bw"] = byt / ms3 / 1e6 / hbm
         K.check_status(dev)
     elif a.kernel == "decode_gemm":
         # the weight-streaming GEMMs of one Qwen2.5-7B decode step at batch a.batch: cuBLAS vs the split-K kernel

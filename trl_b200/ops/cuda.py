@@ -550,13 +550,16 @@ def paged_decode_attn(q, k_cache, v_cache, seq_lens, slot_ids, block_table, bloc
     return out
 
 
-def paged_decode_attn_tc(q, k_cache, v_cache_t, seq_lens, slot_ids, block_table, scale, splits, part_o, part_ml, out):
-    """Tensor-core (tcgen05) decode attention.  k_cache [blocks, 64, Hk, 128]; v_cache_t [blocks, Hk, 128, 64]."""
+def paged_decode_attn_tc(q, k_cache, v_cache_t, seq_lens, slot_ids, block_table, scale, splits, part_o, part_ml, out,
+                         groups: int = 1):
+    """Tensor-core (tcgen05) decode attention.  k_cache [blocks, 64, Hk, 128]; v_cache_t [blocks, Hk, 128, 64].
+    ``groups=2`` runs the variant with two softmax warp groups per CTA that take alternate 128-token tiles."""
     B, Hq, D = q.shape
     nb, bs, Hk, Dk = k_cache.shape
     if D != 128 or Dk != 128 or bs != 64 or tuple(v_cache_t.shape) != (nb, Hk, 128, 64):
         raise ValueError("paged_decode_attn_tc needs head_dim 128, 64-token pages and a transposed V cache")
-    _chk(lib().trlb_paged_decode_attn_tc(_p(q), _p(k_cache), _p(v_cache_t), _p(seq_lens), _p(slot_ids), _p(block_table),
+    fn = lib().trlb_paged_decode_attn_tc2 if groups == 2 else lib().trlb_paged_decode_attn_tc
+    _chk(fn(_p(q), _p(k_cache), _p(v_cache_t), _p(seq_lens), _p(slot_ids), _p(block_table),
                                          c_int(block_table.shape[1]), c_int(nb), c_int(B), c_int(Hq), c_int(Hk),
                                          c_float(scale), c_int(splits), _p(part_o), _p(part_ml), _p(out),
                                          _p(status_buffer(q.device)), _s()), "paged_decode_attn_tc")

@@ -116,7 +116,8 @@ class RolloutEngine:
 
         if self.attn_tc:
             K.paged_decode_attn_tc(self.q_buf, self.k_cache[li], self.v_cache[li], self.seq_lens, None, self.block_table,
-                                   scale, self.kv_splits, self.part_o, self.part_ml, self.attn_buf)
+                                   scale, self.kv_splits, self.part_o, self.part_ml, self.attn_buf,
+                                   groups=self.attn_groups)
         else:
             K.paged_decode_attn(self.q_buf, self.k_cache[li], self.v_cache[li], self.seq_lens, None, self.block_table,
                                 self.block_size, scale, self.kv_splits, self.part_o, self.part_ml, self.attn_buf)
@@ -147,6 +148,7 @@ class RolloutEngine:
         if not block_size:
             block_size = 64 if tc_ok else 16
         self.attn_tc = tc_ok and block_size == 64
+        self.attn_groups = int(os.environ.get("TRL_B200_DECODE_ATTN_GROUPS", "1"))  # 2: two softmax groups per CTA
         self.max_seqs, self.max_len, self.block_size = max_num_seqs, max_model_len, block_size
         self.max_blocks = (max_model_len + block_size - 1) // block_size
         self.num_blocks = num_blocks or max_num_seqs * self.max_blocks
