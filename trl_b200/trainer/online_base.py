@@ -11,11 +11,13 @@ from __future__ import annotations
 import asyncio
 import copy
 import inspect
+import itertools
 import os
 import warnings
 from collections import defaultdict, deque
 from typing import Any, Callable, Optional
 
+import numpy as np
 import torch
 import torch.nn as nn
 
@@ -344,27 +346,40 @@ class OnlineTrainer(Trainer):
         ents = torch.zeros(B, Tc, dtype=torch.float32, device=dev) if compute_entropy else None
         aux_total = None
         for s in range(0, B, bs):
-            seqs = [list(p) + list(c) for p, c in zip(prompt_ids[s:s + bs], completion_ids[s:s + bs])]
-            lens = [len(x) for x in seqs]
-            flat = torch.tensor([t for x in seqs for t in x], dtype=torch.long, device=dev)
-            ctx = SeqCtx.from_lengths(lens, dev)
-            hidden = model.forward_hidden(flat, ctx)
-            # rows that predict completion tokens: positions p-1 .. p+c-2 of every sequence
-            sel, rows, cols = [], [], []
-            off = 0
-            for j, (p, c) in enumerate(zip(prompt_ids[s:s + bs], completion_ids[s:s + bs])):
-                n = len(c)
-                sel.extend(range(off + len(p) - 1, off + len(p) - 1 + n))
-                rows.extend([s + j] * n)
-                cols.extend(range(n))
-                off += len(p) + n
-            if not sel:
+            # all index vectors of the micro-batch are built on the host with numpy and travel in ONE pinned buffer
+            # (asynchronous copy), so the host prepares the next micro-batch while the GPU is still on this one
+            P, C = prompt_ids[s:s + bs], completion_ids[s:s + bs]
+            lp_ = np.fromiter((len(x) for x in P), dtype=np.int64, count=len(P))
+            lc_ = np.fromiter((len(x) for x in C), dtype=np.int64, count=len(C))
+            lens = lp_ + lc_
+            total, n_sel = int(lens.sum()), int(lc_.sum())
+            if n_sel == 0:
                 continue
-            sel_t = torch.tensor(sel, device=dev)
+            starts = np.concatenate([[0], np.cumsum(lens)])
+            c_starts = np.concatenate([[0], np.cumsum(lc_)])[:-1]
+            k = len(P)
+            packed = np.empty(2 * total + (k + 1) + 3 * n_sel, dtype=np.int64)
+            o_pos, o_cu, o_sel, o_row, o_col = total, 2 * total, 2 * total + k + 1, 2 * total + k + 1 + n_sel, \
+                2 * total + k + 1 + 2 * n_sel
+            packed[:total] = np.fromiter(itertools.chain.from_iterable(itertools.chain.from_iterable(zip(P, C))),
+                                         dtype=np.int64, count=total)
+            packed[o_pos:o_cu] = np.arange(total) - np.repeat(starts[:-1], lens)
+            packed[o_cu:o_sel] = starts
+            within = np.arange(n_sel) - np.repeat(c_starts, lc_)
+            # rows that predict completion tokens: positions p-1 .. p+c-2 of every sequence
+            packed[o_sel:o_row] = np.repeat(starts[:-1] + lp_ - 1, lc_) + within
+            packed[o_row:o_col] = np.repeat(np.arange(s, s + k), lc_)
+            packed[o_col:] = within
+            host = torch.from_numpy(packed)
+            if dev.type == "cuda":
+                host = host.pin_memory()
+            buf = host.to(dev, non_blocking=True)
+            flat, sel_t, r, c_ = buf[:total], buf[o_sel:o_row], buf[o_row:o_col], buf[o_col:]
+            ctx = SeqCtx(buf[o_pos:o_cu].to(torch.int32), buf[o_cu:o_sel].to(torch.int32), int(lens.max()))
+            hidden = model.forward_hidden(flat, ctx)
             tgt = flat[sel_t + 1]
             lp, en = ops.lm_head_logprobs(hidden[sel_t], model.lm_head_weight, tgt, temperature,
                                           softcap=model.config.final_logit_softcapping, compute_entropy=compute_entropy)
-            r, c_ = torch.tensor(rows, device=dev), torch.tensor(cols, device=dev)
             if getattr(self, "_keep_selected_hidden", False):  # value heads read the same rows (PPO)
                 self._selected_hidden = (hidden[sel_t], r, c_, flat, ctx, sel_t)
             logps = logps.index_put((r, c_), lp)
