@@ -30,8 +30,9 @@ def main():
     torch.manual_seed(0)
     model = make_tiny_model("tiny-qwen2", seed=0)
     rows = synthetic_token_batches(1024, 4 * steps, 128, seed=3)
-    sp = 2 if mode == "sp2" else 1  # "sp2": Ulysses sequence parallelism over both ranks, plain data-parallel engine
-    pc = {"sp_size": sp} if sp > 1 else None
+    # "sp2": Ulysses sequence parallelism over both ranks; "cp2": context parallel (gathered K/V); plain DP engine
+    sp = 2 if mode in ("sp2", "cp2") else 1
+    pc = {"sp_size" if mode == "sp2" else "cp_size": sp} if sp > 1 else None
     mode = "ddp" if sp > 1 else mode
     args = SFTConfig(output_dir=out + "_o", per_device_train_batch_size=4 // (world // sp), max_steps=steps, logging_steps=1,
                      learning_rate=1e-4, use_cpu=True, save_strategy="no", padding_free=True, shard_mode=mode,

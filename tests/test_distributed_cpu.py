@@ -24,7 +24,7 @@ def _run(world, mode, out, steps=4, port=29611):
         return json.load(f)
 
 
-@pytest.mark.parametrize("mode,port", [("ddp", 29611), ("zero2", 29612), ("sp2", 29613)])
+@pytest.mark.parametrize("mode,port", [("ddp", 29611), ("zero2", 29612), ("sp2", 29613), ("cp2", 29614)])
 def test_sft_world1_vs_world2(tmp_path, mode, port):
     ref = _run(1, "ddp", str(tmp_path / "w1.json"))
     two = _run(2, mode, str(tmp_path / f"w2_{mode}.json"), port=port)

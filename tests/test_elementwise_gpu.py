@@ -112,3 +112,20 @@ def test_accum_bf16_into_fp32(n):
     K.accum_grad(dst, src)
     assert torch.equal(dst, want)
     assert float(buf[n:].abs().sum()) == float(buf[n:].abs().sum())
+
+
+def test_attention_varlen_qk_mask_is_aligned_to_key_segment_end():
+    """The library varlen kernel behind context parallelism: a query segment that is the tail of its key segment."""
+    from trl_b200.oracle import ops as O
+    from trl_b200.ops import cuda as K
+
+    torch.manual_seed(0)
+    Hq, Hk, D = 8, 2, 128
+    cu_q = torch.tensor([0, 40, 41, 170], dtype=torch.int32, device="cuda")
+    cu_k = torch.tensor([0, 300, 301, 430], dtype=torch.int32, device="cuda")  # first segment: 260 keys of prefix
+    q = torch.randn(170, Hq, D, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(430, Hk, D, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(430, Hk, D, device="cuda", dtype=torch.bfloat16)
+    out = K.attention_varlen_qk(q, k, v, cu_q, cu_k, 129, 300)
+    ref = O.attention_varlen_qk(q.float(), k.float(), v.float(), cu_q, cu_k)
+    assert (out.float() - ref).abs().max().item() < 2e-2

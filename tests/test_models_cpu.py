@@ -127,3 +127,26 @@ def test_partial_gradient_checkpointing_matches_full_activations():
     full = grads()
     for a, b, c in zip(ref, part, full):
         assert torch.allclose(a, b, atol=1e-6) and torch.allclose(a, c, atol=1e-6)
+
+
+def test_context_parallel_attention_segments_match_full_attention():
+    """A chunk's queries against the gathered keys (mask aligned to the end of each key segment) equal the same rows
+    of full packed attention."""
+    from trl_b200.oracle import ops as O
+    from trl_b200.parallel import context_parallel as cp
+    from trl_b200.parallel.ulysses import SpInfo
+
+    torch.manual_seed(0)
+    cu = torch.tensor([0, 5, 19, 24, 32], dtype=torch.int32)  # four documents in a 32-token stream
+    T, Hq, Hk, D = 32, 4, 2, 8
+    q, k, v = torch.randn(T, Hq, D), torch.randn(T, Hk, D), torch.randn(T, Hk, D)
+    full = O.attention_varlen(q, k, v, cu)
+    for size in (2, 4):
+        tl = T // size
+        for r in range(size):
+            ctx = SeqCtx(torch.zeros(tl, dtype=torch.int32), cu, 14)
+            ctx.sp = SpInfo(None, size, r, "allgather_kv")
+            p = cp.plan(ctx)
+            out = O.attention_varlen_qk(q[r * tl:(r + 1) * tl], k[p["k_start"]:p["k_end"]], v[p["k_start"]:p["k_end"]],
+                                        p["cu_q"], p["cu_k"])
+            assert torch.allclose(out, full[r * tl:(r + 1) * tl], atol=1e-5), (size, r)

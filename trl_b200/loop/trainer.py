@@ -262,10 +262,16 @@ class Trainer:
 
     @property
     def sp_size(self) -> int:
+        """Ranks per sequence-sharded group: ``parallelism_config["sp_size"]`` (Ulysses, heads are exchanged) or
+        ``["cp_size"]`` (context parallel, keys / values are gathered); one of the two."""
         pc = self.args.parallelism_config
-        sp = int((pc or {}).get("sp_size", 1)) if isinstance(pc, dict) else 1
+        pc = pc if isinstance(pc, dict) else {}
+        sp, cp = int(pc.get("sp_size", 1) or 1), int(pc.get("cp_size", 1) or 1)
+        if sp > 1 and cp > 1:
+            raise ValueError("sp_size and cp_size cannot be combined: pick Ulysses (sp_size) or context parallel (cp_size)")
+        sp = max(sp, cp)
         if sp > 1 and D.world_size() % sp:
-            raise ValueError(f"sp_size ({sp}) must divide the world size ({D.world_size()})")
+            raise ValueError(f"sp_size / cp_size ({sp}) must divide the world size ({D.world_size()})")
         return sp if D.world_size() > 1 else 1
 
     def sp_info(self):
@@ -277,7 +283,9 @@ class Trainer:
             from ..parallel.ulysses import SpInfo
 
             groups = [list(range(i, i + sp)) for i in range(0, D.world_size(), sp)]
-            self._sp_info = SpInfo(D.new_subgroups_by_enumeration(groups), sp, D.rank() % sp)
+            pc = self.args.parallelism_config
+            mode = "allgather_kv" if isinstance(pc, dict) and int(pc.get("cp_size", 1) or 1) > 1 else "ulysses"
+            self._sp_info = SpInfo(D.new_subgroups_by_enumeration(groups), sp, D.rank() % sp, mode)
         return self._sp_info
 
     def get_train_dataloader(self):

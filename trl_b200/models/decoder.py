@@ -159,6 +159,10 @@ class DecoderLayer(nn.Module):
         q, k = ops.apply_rope_qk(q, k, ctx.positions, c.rope_theta)
         if ctx.kv is not None:
             o = ctx.kv.attend(self.layer_idx, q, k, v, ctx)
+        elif ctx.sp is not None and ctx.sp.mode == "allgather_kv":
+            from ..parallel import context_parallel
+
+            o = context_parallel.attention(q, k, v, ctx, ops.attention_varlen_qk)
         elif ctx.sp is not None:
             from ..parallel import ulysses
 

@@ -311,6 +311,20 @@ def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True):
                        window_size=(-1, 0) if causal else (-1, -1))
 
 
+def attention_varlen_qk(q, k, v, cu_q, cu_k, max_q, max_k):
+    """Causal GQA attention with separate query / key segments [Tq, H, D] x [Tk, Hk, D]; the library kernel aligns the
+    causal mask to the end of each key segment (query i sees keys up to i + len_k - len_q)."""
+    from torch.nn.attention.varlen import varlen_attn
+
+    Hq, Hk = q.shape[1], k.shape[1]
+    if Hq != Hk:
+        rep = Hq // Hk
+        k = k.repeat_interleave(rep, dim=1)
+        v = v.repeat_interleave(rep, dim=1)
+    return varlen_attn(q.contiguous(), k.contiguous(), v.contiguous(), cu_q.to(torch.int32), cu_k.to(torch.int32),
+                       int(max_q), int(max_k), window_size=(-1, 0))
+
+
 def grouped_gemm(a, w, offsets, n_out, swiglu=False, out=None):
     """Per-expert GEMM on tcgen05: rows of ``a`` [R, K] are sorted by expert, ``offsets`` [E + 1] int32 on the device,
     ``w`` [E, n_out (or 2 * n_out with swiglu), K].  Returns [R, n_out]; with ``swiglu`` the gate / up halves are

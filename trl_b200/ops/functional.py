@@ -57,6 +57,14 @@ def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True):
     return _ref.attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal)
 
 
+def attention_varlen_qk(q, k, v, cu_q, cu_k, max_q, max_k):
+    """Causal varlen attention with separate query / key segmentation; the mask is aligned to the END of each key
+    segment (a query segment is the tail of its key segment).  Used by context parallelism."""
+    if q.is_cuda:
+        return _cuda().attention_varlen_qk(q, k, v, cu_q, cu_k, max_q, max_k)
+    return _ref.attention_varlen_qk(q, k, v, cu_q, cu_k)
+
+
 def lm_head_logprobs(hidden, weight, labels, temperature=1.0, bias=None, softcap=None,
                      compute_entropy=True, chunk_tokens: int = 4096):
     """Fused lm_head GEMM + log-softmax gather (+entropy); logits never materialise."""

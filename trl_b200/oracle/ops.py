@@ -66,6 +66,30 @@ def attention_varlen(q, k, v, cu_seqlens, max_seqlen=None, causal=True, scale=No
     return o.transpose(0, 1).to(q.dtype).contiguous()
 
 
+def attention_varlen_qk(q, k, v, cu_q, cu_k, scale=None):
+    """Causal GQA attention, query segment i (``cu_q``) against key segment i (``cu_k``), mask aligned to the end of the
+    key segment: query j of a segment with lq queries and lk keys sees keys 0 .. j + lk - lq.  Dense mask, oracle only."""
+    Tq, Hq, D = q.shape
+    Tk, Hkv = k.shape[0], k.shape[1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    cq, ck = cu_q.to(q.device).long(), cu_k.to(q.device).long()
+    iq, ik = torch.arange(Tq, device=q.device), torch.arange(Tk, device=q.device)
+    sq = torch.bucketize(iq, cq[1:], right=True)
+    sk = torch.bucketize(ik, ck[1:], right=True)
+    # position of every query / key counted from the END of its segment
+    q_from_end = cq[1:][sq] - iq
+    k_from_end = ck[1:][sk] - ik
+    mask = (sq[:, None] == sk[None, :]) & (k_from_end[None, :] >= q_from_end[:, None])
+    rep = Hq // Hkv
+    qf = q.float().transpose(0, 1)
+    kf = k.float().transpose(0, 1).repeat_interleave(rep, dim=0)
+    vf = v.float().transpose(0, 1).repeat_interleave(rep, dim=0)
+    s = torch.matmul(qf, kf.transpose(1, 2)) * scale
+    s = s.masked_fill(~mask[None], float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    return torch.matmul(p, vf).transpose(0, 1).to(q.dtype).contiguous()
+
+
 def lm_head_logprobs(hidden, weight, labels, temperature=1.0, bias=None, softcap=None,
                      compute_entropy=True):
     """Per-token log p(label) and entropy from ``hidden[N,H] @ weight[V,H]^T``.

@@ -27,6 +27,7 @@ class SpInfo:
     group: Any
     size: int
     rank: int
+    mode: str = "ulysses"  # "ulysses": heads are exchanged; "allgather_kv": context parallel (context_parallel.py)
 
 
 def _a2a(x: torch.Tensor, group) -> torch.Tensor:
