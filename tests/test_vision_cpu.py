@@ -1,0 +1,118 @@
+"""Vision-language model (CLIP tower + projector + native decoder) vs transformers' LLaVA, checkpoints, SFT."""
+import torch
+
+from trl_b200.models.vision import VisionLanguageModel, tiny_vlm_arch
+
+
+def _ids_with_images(cfg, n_images_per_row, length, gen):
+    ids = torch.randint(10, cfg.vocab_size, (len(n_images_per_row), length), generator=gen)
+    for r, n in enumerate(n_images_per_row):
+        for j in range(n):
+            s = 2 + j * (cfg.image_seq_length + 1)
+            ids[r, s:s + cfg.image_seq_length] = cfg.image_token_index
+    return ids
+
+
+def test_vlm_logits_match_transformers_llava(tmp_path):
+    import transformers as tf
+
+    torch.manual_seed(0)
+    cfg = tiny_vlm_arch("tiny-llama")
+    ours = VisionLanguageModel(cfg).eval()
+    for p in ours.vision_tower.parameters():  # biases and norms away from their init values
+        if p.ndim == 1:
+            p.data.add_(torch.randn_like(p) * 0.05)
+    ours.save_pretrained(str(tmp_path))
+    hf = tf.LlavaForConditionalGeneration.from_pretrained(str(tmp_path), dtype=torch.float32,
+                                                          attn_implementation="eager").eval()
+    g = torch.Generator().manual_seed(1)
+    ids = _ids_with_images(cfg, [1, 2], 20, g)
+    am = torch.ones_like(ids)
+    am[0, 15:] = 0
+    pix = torch.randn(3, 3, 28, 28, generator=g)
+    with torch.no_grad():
+        a = ours(input_ids=ids, attention_mask=am, pixel_values=pix).logits
+        b = hf(input_ids=ids, attention_mask=am, pixel_values=pix).logits
+    m = am.bool()
+    assert torch.allclose(a[m], b[m], atol=3e-4, rtol=1e-3), (a[m] - b[m]).abs().max()
+
+
+def test_vlm_checkpoint_round_trip_and_gradients(tmp_path):
+    torch.manual_seed(0)
+    cfg = tiny_vlm_arch("tiny-qwen2")
+    m = VisionLanguageModel(cfg)
+    m.save_pretrained(str(tmp_path))
+    m2 = VisionLanguageModel.from_pretrained(str(tmp_path))
+    for (n1, p1), (n2, p2) in zip(m.named_parameters(), m2.named_parameters()):
+        assert n1 == n2 and torch.equal(p1, p2), n1
+    g = torch.Generator().manual_seed(2)
+    ids = _ids_with_images(cfg, [1], 12, g)
+    pix = torch.randn(1, 3, 28, 28, generator=g)
+    out = m2(input_ids=ids, pixel_values=pix, labels=ids)
+    out.loss.backward()
+    assert m2.vision_tower.patch_embedding.grad.abs().sum() > 0 and m2.proj1_w.grad.abs().sum() > 0
+    assert m2.vision_tower.layers[-1].qkv_w.grad is None  # feature layer -2: the last tower layer is never run
+
+
+def _vlm_and_processor():
+    from trl_b200.models.vision_processing import VisionProcessor
+    from trl_b200.testing import make_tiny_tokenizer
+
+    tok = make_tiny_tokenizer()
+    proc = VisionProcessor(tok, image_size=28, image_seq_length=4)
+    torch.manual_seed(0)
+    model = VisionLanguageModel(tiny_vlm_arch("tiny-qwen2", image_token_index=proc.image_token_id))
+    assert VisionProcessor.for_model(tok, model).image_token_id == proc.image_token_id
+    return model, proc
+
+
+def test_vision_collator_language_modeling_and_prompt_completion():
+    import numpy as np
+
+    from trl_b200.trainer.sft_trainer import DataCollatorForVisionLanguageModeling
+
+    _, proc = _vlm_and_processor()
+    img = (np.random.RandomState(0).rand(40, 30, 3) * 255).astype("uint8")
+    ex = [{"images": [img], "messages": [{"role": "user", "content": "what is this"},
+                                         {"role": "assistant", "content": "a simple idea"}]},
+          {"images": [img, img], "messages": [{"role": "user", "content": "explain"},
+                                              {"role": "assistant", "content": "two"}]}]
+    out = DataCollatorForVisionLanguageModeling(proc)(ex)
+    assert out["pixel_values"].shape == (3, 3, 28, 28)
+    n_img_tok = (out["input_ids"] == proc.image_token_id).sum(1).tolist()
+    assert n_img_tok == [4, 8]
+    assert (out["labels"][out["attention_mask"] == 0] == -100).all()
+    # prompt-completion with completion-only loss: prompt (and its images) masked, completion kept
+    pc = [{"image": img, "prompt": [{"role": "user", "content": "what is this"}],
+           "completion": [{"role": "assistant", "content": "a simple idea"}]}]
+    out = DataCollatorForVisionLanguageModeling(proc, completion_only_loss=True)(pc)
+    lab, ids = out["labels"][0], out["input_ids"][0]
+    assert (lab[ids == proc.image_token_id] == -100).all() and (lab != -100).sum() >= 3
+    assert out["pixel_values"].shape[0] == 1
+
+
+def test_sft_trains_vision_language_model(tmp_path):
+    import numpy as np
+
+    from trl_b200 import SFTConfig, SFTTrainer
+
+    model, proc = _vlm_and_processor()
+    rs = np.random.RandomState(1)
+    rows = []
+    for i in range(8):
+        bright = i % 2
+        img = (rs.rand(28, 28, 3) * 60 + (160 if bright else 10)).astype("uint8")
+        rows.append({"images": [img], "messages": [{"role": "user", "content": "is it day or night"},
+                                                   {"role": "assistant", "content": "day" if bright else "night"}]})
+    args = SFTConfig(output_dir=str(tmp_path), per_device_train_batch_size=4, max_steps=6, logging_steps=1,
+                     learning_rate=3e-3, use_cpu=True, save_strategy="no", report_to="none", max_length=None,
+                     lr_scheduler_type="constant")
+    tr = SFTTrainer(model, args, train_dataset=rows, processing_class=proc)
+    w0 = model.vision_tower.patch_embedding.detach().clone()
+    tr.train()
+    losses = [h["loss"] for h in tr.state.log_history if "loss" in h]
+    assert losses[-1] < losses[0]
+    assert not torch.equal(w0, model.vision_tower.patch_embedding)  # the tower trains through the projector
+    tr.save_model(str(tmp_path / "final"))
+    re = VisionLanguageModel.from_pretrained(str(tmp_path / "final"))
+    assert torch.equal(re.proj1_w, model.proj1_w)

@@ -13,6 +13,8 @@ _import_structure = {
                    "prepare_multimodal_messages_vllm", "unpair_preference_dataset", "truncate_dataset"],
     "models.utils": ["create_reference_model", "unwrap_model_for_generation"],
     "models.decoder": ["CausalLM"],
+    "models.vision": ["VisionLanguageModel", "VlmArch", "VisionArch"],
+    "models.vision_processing": ["VisionProcessor"],
     "models.configuration": ["ModelArch", "preset"],
     "models.lora": ["LoraConfig", "get_peft_model"],
     "scripts.utils": ["DatasetMixtureConfig", "ScriptArguments", "TrlParser", "get_dataset", "init_zero_verbose"],

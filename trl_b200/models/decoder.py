@@ -322,9 +322,10 @@ class CausalLM(nn.Module):
         w = self.norm + 1.0 if self.config.norm_plus_one else self.norm
         return ops.rms_norm(x, w, self.config.rms_norm_eps)
 
-    def forward_hidden(self, input_ids: torch.Tensor, ctx: SeqCtx) -> torch.Tensor:
-        """Flat ids [T] -> final-norm hidden [T, H]."""
-        x = self.embed(input_ids)
+    def forward_hidden(self, input_ids: torch.Tensor, ctx: SeqCtx, inputs_embeds: torch.Tensor | None = None) -> torch.Tensor:
+        """Flat ids [T] -> final-norm hidden [T, H].  ``inputs_embeds`` [T, H] replaces the embedding lookup (vision-
+        language models splice image features into it)."""
+        x = self.embed(input_ids) if inputs_embeds is None else inputs_embeds
         n_ckpt = getattr(self, "checkpoint_num_layers", None)
         for li, layer in enumerate(self.layers):
             if (self.gradient_checkpointing and self.training and torch.is_grad_enabled()

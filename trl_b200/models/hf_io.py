@@ -210,6 +210,12 @@ def load_model(path_or_name, dtype=None, device=None, num_labels: int | None = N
         config, path_or_name = path_or_name, ""
     name = str(path_or_name)
     is_dir = os.path.isdir(name)
+    if is_dir and config is None and os.path.exists(os.path.join(name, "config.json")):
+        with open(os.path.join(name, "config.json")) as f:
+            if json.load(f).get("model_type") == "llava":  # vision tower + projector + decoder
+                from .vision import VisionLanguageModel
+
+                return VisionLanguageModel.from_pretrained(name, dtype=dtype, device=device)
     if config is None:
         if is_dir:
             config = ModelArch.from_pretrained(name)

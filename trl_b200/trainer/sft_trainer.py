@@ -68,14 +68,100 @@ class DataCollatorForLanguageModeling:
 
 
 class DataCollatorForVisionLanguageModeling:
-    """Vision-language collation needs an image processor and a vision tower; the native decoder
-    families are text-only, so this collator refuses rather than silently dropping images."""
+    """Tokenises text and converts images on the fly, batch by batch (image conversion is too heavy to do for the
+    whole dataset up front).  Examples carry ``images`` (list) or ``image`` plus either ``messages`` / a text field
+    (language modelling) or ``prompt`` + ``completion``.  Output: ``input_ids``, ``attention_mask``, ``pixel_values``,
+    ``labels`` (padding masked; with ``completion_only_loss`` the prompt too) and whatever else the processor returns.
+    ``processor`` is a transformers ``ProcessorMixin`` or ``models.vision_processing.VisionProcessor``
+    (trl/trainer/sft_trainer.py:538-760)."""
 
-    def __init__(self, processor=None, **kw):
+    def __init__(self, processor, max_length: int | None = None, completion_only_loss: bool = False,
+                 pad_to_multiple_of: int | None = None, dataset_text_field: str = "text", return_tensors: str = "pt"):
         self.processor = processor
+        self.max_length = max_length
+        self.completion_only_loss = completion_only_loss
+        self.pad_to_multiple_of = pad_to_multiple_of
+        self.dataset_text_field = dataset_text_field
+        self.return_tensors = return_tensors
+
+    @staticmethod
+    def _images(examples):
+        examples = [dict(e) for e in examples]
+        for e in examples:
+            if "image" in e:
+                e["images"] = [e.pop("image")]
+            e.setdefault("images", [])
+        imgs = [list(e["images"]) for e in examples]
+        return examples, (None if all(not i for i in imgs) else imgs)  # processors reject an all-empty image batch
 
     def __call__(self, examples):
-        raise NotImplementedError("vision-language SFT: no native vision tower in this build")
+        first = examples[0]
+        if "messages" in first or self.dataset_text_field in first:
+            if self.completion_only_loss:
+                raise ValueError("The `completion_only_loss` argument is not supported for language modeling datasets.")
+            return self._language_modeling(examples)
+        if "prompt" in first and "completion" in first:
+            return self._prompt_completion(examples)
+        raise KeyError(f"Unexpected input keys in examples: {list(first.keys())}.")
+
+    torch_call = __call__
+
+    def _language_modeling(self, examples):
+        from ..data_utils import prepare_multimodal_messages
+
+        examples, images = self._images(examples)
+        if "messages" in examples[0]:
+            msgs = [prepare_multimodal_messages(e["messages"], images=e["images"]) for e in examples]
+            texts = self.processor.apply_chat_template(msgs, tokenize=False)
+        else:
+            texts = [e[self.dataset_text_field] for e in examples]
+        out = dict(self.processor(images=images, text=texts, padding=True, padding_side="right",
+                                  pad_to_multiple_of=self.pad_to_multiple_of, truncation=self.max_length is not None,
+                                  max_length=self.max_length, return_tensors=self.return_tensors,
+                                  add_special_tokens=False))
+        labels = out["input_ids"].clone()
+        labels[out["attention_mask"] == 0] = -100
+        out["labels"] = labels
+        return out
+
+    def _prompt_completion(self, examples):
+        from ..data_utils import apply_chat_template, is_conversational, prepare_multimodal_messages
+        from .utils import flush_left
+
+        if self.pad_to_multiple_of is not None:
+            raise NotImplementedError("Padding to a multiple of a value is not yet implemented for vision-language "
+                                      "modeling and prompt-completion data.")
+        examples, images = self._images(examples)
+        if is_conversational(examples[0]):
+            rendered = []
+            for e in examples:
+                e = {**e, "prompt": prepare_multimodal_messages(e["prompt"], images=e["images"]),
+                     "completion": prepare_multimodal_messages(e["completion"])}
+                rendered.append(apply_chat_template({k: e[k] for k in ("prompt", "completion")}, self.processor))
+            examples = rendered
+        kw = dict(return_tensors=self.return_tensors, add_special_tokens=False, padding=True)
+        pp = self.processor(images=images, text=[e["prompt"] for e in examples], padding_side="left", **kw)
+        pc = self.processor(text=[e["completion"] for e in examples], padding_side="right", **kw)
+        ids = torch.cat([pp["input_ids"], pc["input_ids"]], dim=1)
+        am = torch.cat([pp["attention_mask"], pc["attention_mask"]], dim=1)
+        cm = torch.cat([torch.zeros_like(pp["attention_mask"]), pc["attention_mask"]], dim=1)
+        extras = {}
+        for k in ("token_type_ids", "mm_token_type_ids"):
+            if k in pp:
+                tail = pc[k] if k in pc else torch.zeros_like(pc["input_ids"])
+                extras[k] = torch.cat([pp[k], tail], dim=1)
+        am, ids, cm, *rest = flush_left(am, ids, cm, *extras.values())
+        extras = dict(zip(extras.keys(), rest))
+        if self.max_length is not None:
+            ids, am, cm = ids[:, :self.max_length], am[:, :self.max_length], cm[:, :self.max_length]
+            extras = {k: v[:, :self.max_length] for k, v in extras.items()}
+        labels = ids.clone()
+        labels[am == 0] = -100
+        if self.completion_only_loss:
+            labels[cm == 0] = -100
+        out = {k: v for k, v in pp.items() if k not in ("input_ids", "attention_mask", "token_type_ids", "mm_token_type_ids")}
+        out.update(input_ids=ids, attention_mask=am, labels=labels, **extras)
+        return out
 
 
 def dft_loss(logp: torch.Tensor, valid: torch.Tensor, num_items_in_batch=None) -> torch.Tensor:
@@ -120,7 +206,8 @@ class SFTTrainer(Trainer):
             if not os.path.isdir(model_id):
                 raise ValueError("processing_class is required when the model is not a local checkpoint directory")
             processing_class = AutoTokenizer.from_pretrained(model_id)
-        tok = processing_class
+        # a processor (vision-language models) wraps the text tokenizer
+        tok = getattr(processing_class, "tokenizer", processing_class)
         if args.eos_token is not None:
             if tok.convert_tokens_to_ids(args.eos_token) is None:
                 raise ValueError(f"eos_token {args.eos_token!r} is not in the vocabulary")
@@ -148,7 +235,15 @@ class SFTTrainer(Trainer):
             self.completion_only_loss = args.completion_only_loss
         if data_collator is None:
             if self._is_vlm:
-                data_collator = DataCollatorForVisionLanguageModeling(tok)
+                if not hasattr(processing_class, "tokenizer"):
+                    raise ValueError("a dataset with images needs a processor (image processor + tokenizer) as "
+                                     "processing_class, e.g. models.vision_processing.VisionProcessor")
+                if self.padding_free or args.packing:
+                    raise ValueError("packing / padding_free are not supported for vision-language datasets")
+                data_collator = DataCollatorForVisionLanguageModeling(
+                    processing_class, max_length=args.max_length, completion_only_loss=bool(self.completion_only_loss),
+                    pad_to_multiple_of=args.pad_to_multiple_of, dataset_text_field=args.dataset_text_field)
+                args.remove_unused_columns = False  # the collator reads the raw columns
             else:
                 data_collator = DataCollatorForLanguageModeling(tok.pad_token_id, self.completion_only_loss,
                                                                 self.padding_free, args.pad_to_multiple_of)
@@ -168,7 +263,8 @@ class SFTTrainer(Trainer):
         self._total_train_tokens = 0
         self.aux_loss_enabled = getattr(getattr(model, "config", None), "is_moe", False)
         super().__init__(model=model, args=args, data_collator=data_collator, train_dataset=train_dataset,
-                         eval_dataset=eval_dataset, processing_class=tok, compute_loss_func=compute_loss_func,
+                         eval_dataset=eval_dataset, processing_class=processing_class if self._is_vlm else tok,
+                         compute_loss_func=compute_loss_func,
                          compute_metrics=compute_metrics, callbacks=callbacks,
                          preprocess_logits_for_metrics=preprocess_logits_for_metrics)
         self.model_accepts_loss_kwargs = True
@@ -327,8 +423,12 @@ class SFTTrainer(Trainer):
         if model.training:
             n_tok = torch.tensor(float(flat.numel()), device=flat.device)
             self._metrics["train"]["_num_tokens"].append(n_tok)
+        extra = {}
+        if getattr(model, "is_vlm", False):
+            extra["pixel_values"] = inputs.get("pixel_values")
+            tgt = tgt.masked_fill(tgt == model.config.image_token_index, -100)  # placeholders carry no target
         with self.maybe_activation_offload_context:
-            hidden = model.forward_hidden(flat, ctx)
+            hidden = model.forward_hidden(flat, ctx, **extra)
         loss = self.loss_from_hidden(model, hidden, ctx, tgt, num_items_in_batch)
         return (loss, None) if return_outputs else loss
 
