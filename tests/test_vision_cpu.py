@@ -116,3 +116,32 @@ def test_sft_trains_vision_language_model(tmp_path):
     tr.save_model(str(tmp_path / "final"))
     re = VisionLanguageModel.from_pretrained(str(tmp_path / "final"))
     assert torch.equal(re.proj1_w, model.proj1_w)
+
+
+def test_dpo_trains_vision_language_model(tmp_path):
+    import numpy as np
+
+    from trl_b200 import DPOConfig, DPOTrainer
+    from trl_b200.trainer.dpo_trainer import DataCollatorForVisionPreference
+
+    model, proc = _vlm_and_processor()
+    rs = np.random.RandomState(2)
+    rows = []
+    for i in range(8):
+        bright = i % 2
+        img = (rs.rand(28, 28, 3) * 60 + (160 if bright else 10)).astype("uint8")
+        good, bad = ("day", "night") if bright else ("night", "day")
+        rows.append({"images": [img], "prompt": [{"role": "user", "content": "is it day or night"}],
+                     "chosen": [{"role": "assistant", "content": good}],
+                     "rejected": [{"role": "assistant", "content": bad}]})
+    batch = DataCollatorForVisionPreference(proc)(rows[:2])
+    assert batch["input_ids"].shape[0] == 4 and batch["pixel_values"].shape[0] == 4
+    assert (batch["completion_mask"].sum(1) > 0).all()
+    args = DPOConfig(output_dir=str(tmp_path), per_device_train_batch_size=4, max_steps=5, logging_steps=1,
+                     learning_rate=2e-3, use_cpu=True, save_strategy="no", report_to="none", beta=0.5,
+                     lr_scheduler_type="constant")
+    tr = DPOTrainer(model, args=args, train_dataset=rows, processing_class=proc)
+    tr.train()
+    hist = [h for h in tr.state.log_history if "rewards/margins" in h]
+    assert hist[-1]["rewards/margins"] > hist[0]["rewards/margins"]
+    assert hist[-1]["loss"] < hist[0]["loss"]

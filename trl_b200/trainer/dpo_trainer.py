@@ -64,11 +64,55 @@ class DataCollatorForPreference:
 
 
 class DataCollatorForVisionPreference:
-    def __init__(self, processor=None, **kw):
+    """Tokenises and converts images batch by batch.  Examples: ``images`` (or ``image``) + ``prompt`` / ``chosen`` /
+    ``rejected`` (text or conversations).  Output rows are [all chosen; all rejected] with ``completion_mask`` and the
+    images repeated for both halves (trl/trainer/dpo_trainer.py:217-370)."""
+
+    def __init__(self, processor, max_length: int | None = None, pad_to_multiple_of: int | None = None,
+                 return_tensors: str = "pt"):
         self.processor = processor
+        self.max_length = max_length
+        self.pad_to_multiple_of = pad_to_multiple_of
+        self.return_tensors = return_tensors
 
     def __call__(self, examples):
-        raise NotImplementedError("vision-language DPO: no native vision tower in this build")
+        from ..data_utils import apply_chat_template, prepare_multimodal_messages
+        from .utils import flush_left
+
+        if self.pad_to_multiple_of is not None:
+            raise NotImplementedError("Padding to a multiple of a value is not yet implemented for vision-language "
+                                      "modeling and prompt-completion data.")
+        examples = [dict(e) for e in examples]
+        for e in examples:
+            if "image" in e:
+                e["images"] = [e.pop("image")]
+            e.setdefault("images", [])
+        images = [list(e["images"]) for e in examples] * 2  # chosen rows, then rejected rows
+        if all(not i for i in images):
+            images = None
+        if is_conversational(examples[0]):
+            rendered = []
+            for e in examples:
+                e = {"prompt": prepare_multimodal_messages(e["prompt"], images=e["images"]),
+                     "chosen": prepare_multimodal_messages(e["chosen"]),
+                     "rejected": prepare_multimodal_messages(e["rejected"])}
+                rendered.append(apply_chat_template(e, self.processor))
+            examples = rendered
+        kw = dict(return_tensors=self.return_tensors, add_special_tokens=False, padding=True)
+        pp = self.processor(images=images, text=[e["prompt"] for e in examples] * 2, padding_side="left", **kw)
+        pc = self.processor(text=[e["chosen"] for e in examples] + [e["rejected"] for e in examples],
+                            padding_side="right", **kw)
+        ids = torch.cat([pp["input_ids"], pc["input_ids"]], dim=1)
+        am = torch.cat([pp["attention_mask"], pc["attention_mask"]], dim=1)
+        cm = torch.cat([torch.zeros_like(pp["attention_mask"]), pc["attention_mask"]], dim=1)
+        am, ids, cm = flush_left(am, ids, cm)
+        if self.max_length is not None:
+            ids, am, cm = ids[:, :self.max_length], am[:, :self.max_length], cm[:, :self.max_length]
+        out = {k: v for k, v in pp.items() if k not in ("input_ids", "attention_mask")}
+        out.update(input_ids=ids, attention_mask=am, completion_mask=cm)
+        return out
+
+    torch_call = __call__
 
 
 class DPOTrainer(Trainer):
@@ -95,7 +139,7 @@ class DPOTrainer(Trainer):
             from transformers import AutoTokenizer
 
             processing_class = AutoTokenizer.from_pretrained(model_id)
-        tok = processing_class
+        tok = getattr(processing_class, "tokenizer", processing_class)  # a processor wraps the text tokenizer
         if args.eos_token is not None:
             tok.eos_token = args.eos_token
         if tok.pad_token is None:
@@ -116,20 +160,33 @@ class DPOTrainer(Trainer):
         self.precompute_ref_log_probs = args.precompute_ref_log_probs
         self.aux_loss_enabled = getattr(getattr(model, "config", None), "is_moe", False)
         self.padding_free = args.padding_free
+        first = next(iter(train_dataset)) if train_dataset is not None else {}
+        self._is_vlm = "images" in first or "image" in first
+        if self._is_vlm:
+            if not hasattr(processing_class, "tokenizer"):
+                raise ValueError("a dataset with images needs a processor (image processor + tokenizer) as "
+                                 "processing_class, e.g. models.vision_processing.VisionProcessor")
+            if args.precompute_ref_log_probs or args.padding_free:
+                raise ValueError("precompute_ref_log_probs / padding_free are not supported for vision-language datasets")
+            if data_collator is None:
+                data_collator = DataCollatorForVisionPreference(processing_class, args.max_length, args.pad_to_multiple_of)
+            args.remove_unused_columns = False
         if data_collator is None:
             data_collator = DataCollatorForPreference(tok.pad_token_id, args.max_length, args.truncation_mode,
                                                       args.pad_to_multiple_of)
         with D.main_process_first():
-            if train_dataset is not None:
+            if self._is_vlm:
+                pass  # the collator reads the raw columns
+            elif train_dataset is not None:
                 train_dataset = self._prepare_dataset(train_dataset, tok, args, "train")
-            if eval_dataset is not None:
+            if eval_dataset is not None and not self._is_vlm:
                 if isinstance(eval_dataset, dict):
                     eval_dataset = {k: self._prepare_dataset(v, tok, args, k) for k, v in eval_dataset.items()}
                 else:
                     eval_dataset = self._prepare_dataset(eval_dataset, tok, args, "eval")
         super().__init__(model=model, args=args, data_collator=data_collator, train_dataset=train_dataset,
-                         eval_dataset=eval_dataset, processing_class=tok, compute_metrics=compute_metrics,
-                         callbacks=callbacks)
+                         eval_dataset=eval_dataset, processing_class=processing_class if self._is_vlm else tok,
+                         compute_metrics=compute_metrics, callbacks=callbacks)
         self.model_accepts_loss_kwargs = False  # loss is divided by the accumulation steps by the loop
         self._ref_adapter_off = False
         if not self._needs_ref:
@@ -232,8 +289,9 @@ class DPOTrainer(Trainer):
         pred[:, :-1] = cm[:, 1:] * am[:, 1:]
         tgt_f, pred_f = tgt.reshape(-1)[mask_flat], pred.reshape(-1)[mask_flat].bool()
         cmgr = use_adapter(model, None) if adapter_off else _null()
+        extra = {"pixel_values": inputs.get("pixel_values")} if getattr(model, "is_vlm", False) else {}
         with cmgr:
-            hidden = model.forward_hidden(flat, ctx)
+            hidden = model.forward_hidden(flat, ctx, **extra)
         sel = pred_f.nonzero().flatten()
         lp, ent = ops.lm_head_logprobs(hidden[sel], model.lm_head_weight, tgt_f[sel], 1.0,
                                        softcap=model.config.final_logit_softcapping, compute_entropy=need_stats)
