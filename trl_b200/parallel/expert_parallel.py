@@ -50,7 +50,8 @@ class ExpertParallelMoE:
         self._sync = torch.zeros(1, dtype=torch.float32, device=device)
         self._a_x = (ctypes.c_ulonglong * self.world)(*[p + self.x_off for p in self.arena.peer_ptrs])
         self._c_y = (ctypes.c_ulonglong * self.world)(*[p + self.y_off for p in self.arena.peer_ptrs])
-        self._self_act = (ctypes.c_ulonglong * 1)(self.act.data_ptr())
+        # indexed with up to `world` buffer ids by the segment GEMM's host code: one entry per rank, all the local buffer
+        self._self_act = (ctypes.c_ulonglong * self.world)(*([self.act.data_ptr()] * self.world))
 
     # ---- routing tables ---------------------------------------------------------------------------------------------
     def _route(self, topk_idx):
