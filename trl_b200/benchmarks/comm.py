@@ -118,6 +118,8 @@ def main():
     out["rs_adamw"]["nccl_rs_fused_adamw_nccl_ag_ms"] = timed(nccl_opt)
     rs_bytes = total * 4 * (world - 1) / world + total * 2 * (world - 1) / world
     out["rs_adamw"]["link_floor_ms"] = rs_bytes / (NVLINK_GBS * 1e6)
+    if rank == 0:  # the sections above are complete: keep them even if the next one fails
+        print(json.dumps({**out, "partial": "before ep_moe"}), flush=True)
     # ---- expert-parallel MoE block (Qwen3-30B-A3B expert shapes): dispatch/combine fused into the grouped GEMMs ----
     E, Hm, Im, k = 128, 2048, 768, 8
     if E % world == 0:
