@@ -147,3 +147,39 @@ def test_engine_moe_decode_under_cuda_graph_matches_eager():
     ref = EagerGenerator(model).generate(prompts, sp)
     agree = sum(o.token_ids[:3] == r.token_ids[:3] for o, r in zip(outs, ref))
     assert agree >= 4, [(o.token_ids, r.token_ids) for o, r in zip(outs, ref)]
+
+
+def test_engine_generates_from_image_prompts_like_the_eager_generator():
+    """Vision-language model: image features are spliced into the prefill embeddings; decode is the text path."""
+    from trl_b200.models.configuration import preset
+    from trl_b200.models.vision import VisionArch, VisionLanguageModel, VlmArch
+    from trl_b200.rollout.engine import EagerGenerator, RolloutEngine
+    from trl_b200.rollout.sampling import SamplingParams
+
+    torch.manual_seed(0)
+    text = preset("tiny-qwen2", hidden_size=256, num_attention_heads=2, num_key_value_heads=1, head_dim=128,
+                  intermediate_size=512)
+    vis = VisionArch(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=2, image_size=28,
+                     patch_size=14)
+    cfg = VlmArch(text=text, vision=vis, image_token_index=7)
+    model = VisionLanguageModel(cfg, dtype=torch.bfloat16, device="cuda")
+    n_img_tok = cfg.image_seq_length
+    prompts, images = [], []
+    for n_img, tail in ((1, 9), (2, 40), (0, 12)):
+        p = [11, 12]
+        for _ in range(n_img):
+            p += [7] * n_img_tok + [13]
+        p += torch.randint(20, 1000, (tail,)).tolist()
+        prompts.append(p)
+        images.append(torch.randn(n_img, 3, 28, 28) if n_img else None)
+    sp = SamplingParams(n=2, max_tokens=8, greedy=True, temperature=1.0, eos_token_id=2)
+    eng = RolloutEngine(model, max_num_seqs=6, max_model_len=128, poll_every=4)
+    outs = eng.generate(prompts, sp, images=images)
+    ref = EagerGenerator(model).generate(prompts, sp, images=images)
+    assert len(outs) == 6
+    agree = sum(o.token_ids[:3] == r.token_ids[:3] for o, r in zip(outs, ref))
+    assert agree >= 4, [(o.token_ids, r.token_ids) for o, r in zip(outs, ref)]
+    # the images matter: other pixels, other continuation for at least one image prompt
+    other = [None if x is None else torch.randn_like(x) * 3 for x in images]
+    outs2 = eng.generate(prompts, sp, images=other)
+    assert any(a.token_ids != b.token_ids for a, b in zip(outs[:4], outs2[:4]))

@@ -145,3 +145,32 @@ def test_dpo_trains_vision_language_model(tmp_path):
     hist = [h for h in tr.state.log_history if "rewards/margins" in h]
     assert hist[-1]["rewards/margins"] > hist[0]["rewards/margins"]
     assert hist[-1]["loss"] < hist[0]["loss"]
+
+
+def test_grpo_trains_vision_language_model(tmp_path):
+    import numpy as np
+
+    from trl_b200 import GRPOConfig, GRPOTrainer
+
+    model, proc = _vlm_and_processor()
+    rs = np.random.RandomState(3)
+    rows = []
+    for i in range(8):
+        img = (rs.rand(28, 28, 3) * 255).astype("uint8")
+        rows.append({"image": img, "prompt": [{"role": "user", "content": "explain the idea"}]})
+    seen = {}
+
+    def reward_len(completion_ids, **kw):
+        seen["n"] = seen.get("n", 0) + len(completion_ids)
+        return [float(sum(c) % 7) for c in completion_ids]
+
+    args = GRPOConfig(output_dir=str(tmp_path), per_device_train_batch_size=4, num_generations=4, max_completion_length=6,
+                      max_steps=2, logging_steps=1, learning_rate=1e-3, use_cpu=True, save_strategy="no",
+                      report_to="none", beta=0.04, temperature=1.0)
+    tr = GRPOTrainer(model, reward_len, args, train_dataset=rows, processing_class=proc)
+    w0 = model.proj1_w.detach().clone()
+    tr.train()
+    assert seen["n"] >= 8
+    logs = [h for h in tr.state.log_history if "reward" in h]
+    assert logs and all(np.isfinite(h["loss"]) for h in logs) and "kl" in logs[-1]
+    assert not torch.equal(w0, model.proj1_w)  # gradients reach the projector through the image tokens

@@ -48,10 +48,12 @@ class EagerGenerator:
         self.model = model
 
     @torch.no_grad()
-    def generate(self, prompts: Sequence[Sequence[int]], sp: SamplingParams) -> list[Completion]:
+    def generate(self, prompts: Sequence[Sequence[int]], sp: SamplingParams, images=None) -> list[Completion]:
+        """``images``: per prompt the pixel tensor [n_images, C, S, S] of a vision-language model (or None)."""
         dev = self.model.device
         g = torch.Generator(device="cpu").manual_seed(sp.seed)
         seqs = [list(p) for p in prompts for _ in range(sp.n)]
+        pix = None if images is None else [x for x in images for _ in range(sp.n)]
         outs = [Completion(list(s), [], []) for s in seqs]
         alive = list(range(len(seqs)))
         was_training = self.model.training
@@ -67,7 +69,11 @@ class EagerGenerator:
             lens = [len(seqs[i]) for i in alive]
             flat = torch.tensor([t for i in alive for t in seqs[i]], dtype=torch.long, device=dev)
             ctx = SeqCtx.from_lengths(lens, dev)
-            hidden = self.model.forward_hidden(flat, ctx)
+            kw = {}
+            if pix is not None:
+                px = [pix[i] for i in alive if pix[i] is not None and pix[i].numel()]
+                kw["pixel_values"] = torch.cat(px).to(dev) if px else None
+            hidden = self.model.forward_hidden(flat, ctx, **kw)
             last = (ctx.cu_seqlens[1:] - 1).long()
             logits = (hidden[last].float() @ self.model.lm_head_weight.float().t()).cpu()
             tok, lp = sample_reference(logits, sp, g, None if seen is None else seen[alive])
@@ -125,6 +131,10 @@ class RolloutEngine:
     def __init__(self, model: CausalLM, max_num_seqs: int = 64, max_model_len: int = 2048, block_size: int | None = None,
                  num_blocks: int | None = None, poll_every: int = 16, use_cuda_graph: bool = True, kv_splits: int = 0,
                  tp: int = 1, tp_rank: int = 0):
+        # vision-language model: the decoder runs here; image features are spliced into the prefill embeddings
+        self.vlm = model if getattr(model, "is_vlm", False) else None
+        if self.vlm is not None:
+            model = model.language_model
         cfg = model.config
         if cfg.num_attention_heads % tp or cfg.num_key_value_heads % tp:
             raise ValueError(f"tensor parallel size {tp} must divide the head counts")
@@ -300,8 +310,9 @@ class RolloutEngine:
 
     # ---- prefill -------------------------------------------------------------------------------------
     @torch.no_grad()
-    def _prefill(self, owners: list[tuple[int, list]]) -> torch.Tensor:
-        """owners: [(slot, prompt_ids)].  Returns last-token hidden states [len(owners), H]."""
+    def _prefill(self, owners: list[tuple[int, list]], pixels: list | None = None) -> torch.Tensor:
+        """owners: [(slot, prompt_ids)]; pixels: per owner the pixel tensor of its images (vision-language models).
+        Returns last-token hidden states [len(owners), H]."""
         lens = [len(p) for _, p in owners]
         flat = torch.tensor([t for _, p in owners for t in p], dtype=torch.long).pin_memory().to(self.dev, non_blocking=True)
         tok_slot = torch.tensor([s for (s, p) in owners for _ in p], dtype=torch.int32).to(self.dev, non_blocking=True)
@@ -310,16 +321,29 @@ class RolloutEngine:
         self.stats["prefill_tokens"] += int(flat.numel())
         was = self.model.training
         self.model.eval()
-        hidden = self.model.forward_hidden(flat, ctx)
+        embeds = None
+        if self.vlm is not None and pixels is not None:
+            px = [x for x in pixels if x is not None and x.numel()]
+            if px:
+                embeds = self.model.embed(flat)
+                feats = self.vlm.image_features(torch.cat(px).to(self.dev, embeds.dtype)).to(embeds.dtype)
+                slots = (flat == self.vlm.config.image_token_index).nonzero().flatten()
+                if slots.numel() != feats.shape[0]:
+                    raise ValueError(f"{slots.numel()} image placeholder tokens for {feats.shape[0]} image features")
+                embeds.index_copy_(0, slots, feats)
+        hidden = self.model.forward_hidden(flat, ctx, inputs_embeds=embeds)
         if was:
             self.model.train()
         return hidden[(ctx.cu_seqlens[1:] - 1).long()]
 
     # ---- public API -----------------------------------------------------------------------------------
     @torch.no_grad()
-    def generate(self, prompts: Sequence[Sequence[int]], sp: SamplingParams) -> list[Completion]:
+    def generate(self, prompts: Sequence[Sequence[int]], sp: SamplingParams, images=None) -> list[Completion]:
+        """``images``: per prompt the pixel tensor [n_images, C, S, S] (vision-language models), or None."""
         from ..ops import cuda as K
 
+        if images is not None and self.vlm is None:
+            raise ValueError("images were passed to a text-only rollout engine")
         n_req = len(prompts) * sp.n
         max_new = sp.max_tokens
         max_prompt = max(len(p) for p in prompts)
@@ -368,7 +392,8 @@ class RolloutEngine:
                 self.block_table.copy_(self.block_table_host, non_blocking=True)
                 owners = [(slot, reqs[rid][0]) for rid, slot, pre, _ in admitted if pre]
                 group_row = {reqs[rid][1]: i for i, (rid, slot, pre, _) in enumerate([a for a in admitted if a[2]])}
-                last_h = self._prefill(owners) if owners else None
+                own_px = None if images is None else [images[reqs[rid][1]] for rid, slot, pre, _ in admitted if pre]
+                last_h = self._prefill(owners, own_px) if owners else None
                 # sharers: copy the partial tail block of the prompt from the group's owner
                 for rid, slot, pre, copy_blk in admitted:
                     plen = len(reqs[rid][0])

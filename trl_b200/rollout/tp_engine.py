@@ -114,8 +114,10 @@ class TPRolloutEngine(RolloutEngine):
             self.seen.scatter_(1, self.next_input[:, None], 1)
 
     @torch.no_grad()
-    def generate(self, prompts, sp: SamplingParams) -> list[Completion]:
+    def generate(self, prompts, sp: SamplingParams, images=None) -> list[Completion]:
         """Every rank passes its own prompts; the group runs the union; each rank gets its own completions."""
+        if images is not None:
+            raise NotImplementedError("tensor-parallel generation with image prompts")
         gathered = [None] * self.tp
         td.all_gather_object(gathered, [list(p) for p in prompts], group=self.group)
         counts = [len(g) for g in gathered]

@@ -60,10 +60,16 @@ class GRPOTrainer(OnlineTrainer):
         dev = a.device
         mode = "train" if self.model.training else "eval"
         prompts = [x["prompt"] for x in inputs]
+        images = [x.get("images") if "images" in x else ([x["image"]] if x.get("image") is not None else None)
+                  for x in inputs]
+        images = images if any(i for i in images) else None
         if self._tool_loop is not None:
+            if images is not None:
+                raise ValueError("tool calling and image prompts cannot be combined")
             prompt_ids, completion_ids, sampling_logps, extras = self._tool_loop.generate(prompts)
         else:
-            prompt_ids, completion_ids, sampling_logps, extras = self._generate(prompts)
+            prompt_ids, completion_ids, sampling_logps, extras = self._generate(prompts, images)
+        pixel_list = extras.pop("pixel_values_list", None)
         tool_mask = extras.pop("env_mask", extras.pop("tool_mask", None))
         B = len(prompts)
         comp_lens = torch.tensor([len(c) for c in completion_ids], device=dev)
@@ -89,7 +95,8 @@ class GRPOTrainer(OnlineTrainer):
             old_logps = None
             if need_old:
                 with self._profile("old_logps"):
-                    old_logps, _ = self._get_per_token_logps_and_entropies(self.model, prompt_ids, completion_ids, bs)
+                    old_logps, _ = self._get_per_token_logps_and_entropies(self.model, prompt_ids, completion_ids, bs,
+                                                                           pixel_values_list=pixel_list)
             if self.use_vllm and self.vllm_importance_sampling_correction and sampling_logps is not None:
                 slp = pad([torch.tensor(l, dtype=torch.float32, device=dev) for l in sampling_logps], 0.0, "right")
                 slp = torch.nn.functional.pad(slp, (0, Tc - slp.shape[1]))
@@ -97,7 +104,7 @@ class GRPOTrainer(OnlineTrainer):
                 out["importance_sampling_ratio"] = self._rollout_is_ratio(old_logps, slp, loss_mask)
             if self.beta != 0.0:
                 with self._profile("ref_logps"):
-                    out["ref_per_token_logps"] = self._ref_logps(prompt_ids, completion_ids, bs)
+                    out["ref_per_token_logps"] = self._ref_logps(prompt_ids, completion_ids, bs, pixel_list)
             if old_logps is not None:
                 out["old_per_token_logps"] = old_logps
         # ---- rewards and advantages -------------------------------------------------------------------------------
@@ -168,6 +175,8 @@ class GRPOTrainer(OnlineTrainer):
             self._logs["advantages"].extend(all_adv.tolist())
             for k, v in getattr(self, "_extra_cols", {}).items():
                 self._logs["extra"][k].extend(D.gather_object(v))
+        if pixel_list is not None:
+            out["pixel_values_list"] = pixel_list
         out.update({
             "prompt_ids": prompt_ids, "completion_ids_list": completion_ids,
             "completion_mask": completion_mask, "advantages": advantages,
@@ -264,7 +273,8 @@ class GRPOTrainer(OnlineTrainer):
         mask = completion_mask if "tool_mask" not in inputs else completion_mask * inputs["tool_mask"]
         maskf = mask.float()
         logps, entropies = self._get_per_token_logps_and_entropies(model, prompt_ids, completion_ids,
-                                                                   compute_entropy=True)
+                                                                   compute_entropy=True,
+                                                                   pixel_values_list=inputs.get("pixel_values_list"))
         Tc = logps.shape[1]
         if maskf.shape[1] != Tc:  # the buffered mask is padded to the generation batch's longest completion
             maskf = maskf[:, :Tc] if maskf.shape[1] > Tc else torch.nn.functional.pad(maskf, (0, Tc - maskf.shape[1]))

@@ -226,6 +226,30 @@ class OnlineTrainer(Trainer):
                 self._rollout = EagerGenerator(self.model)
         return self._rollout
 
+    def _tokenize_prompts_with_images(self, prompts: list, images: list):
+        """Vision-language prompts: the processor expands every image placeholder and converts the images.
+        Returns (prompt ids, per-prompt pixel tensors [n_images_i, C, S, S])."""
+        from ..data_utils import prepare_multimodal_messages
+
+        proc = self.processing_class
+        if not hasattr(proc, "tokenizer"):
+            raise ValueError("prompts with images need a processor (image processor + tokenizer) as processing_class")
+        imgs = [list(i) if i is not None else [] for i in images]
+        if prompts and is_conversational({"prompt": prompts[0]}):
+            msgs = [prepare_multimodal_messages(p, images=i) for p, i in zip(prompts, imgs)]
+            texts = proc.apply_chat_template(msgs, tools=self.tools or None, add_generation_prompt=True, tokenize=False,
+                                             **self.chat_template_kwargs)
+        else:
+            texts = list(prompts)
+        enc = proc(images=imgs if any(imgs) else None, text=texts, add_special_tokens=False, return_tensors=None)
+        ids = [list(x) for x in enc["input_ids"]]
+        pv = enc.get("pixel_values")
+        per, o = [], 0
+        for i in imgs:
+            per.append(pv[o:o + len(i)] if pv is not None else None)
+            o += len(i)
+        return ids, per
+
     def _tokenize_prompts(self, prompts: list):
         tok = self.processing_class
         if prompts and is_conversational({"prompt": prompts[0]}):
@@ -237,8 +261,9 @@ class OnlineTrainer(Trainer):
                 tok, "add_bos_token", False) else tok(text=list(prompts))["input_ids"]
         return ids
 
-    def _generate(self, prompts: list):
-        """Returns (prompt_ids, completion_ids, sampling logprobs | None, extras)."""
+    def _generate(self, prompts: list, images: list | None = None):
+        """Returns (prompt_ids, completion_ids, sampling logprobs | None, extras).  ``images``: per prompt a list of
+        images (vision-language models); their pixel tensors come back in ``extras["pixel_values_list"]``."""
         extras = {}
         if self.rollout_func is not None:
             out = self.rollout_func(prompts, self)
@@ -247,20 +272,31 @@ class OnlineTrainer(Trainer):
                     raise ValueError(f"rollout_func must return {k!r}")
             extras = {k: v for k, v in out.items() if k not in ("prompt_ids", "completion_ids", "logprobs")}
             return out["prompt_ids"], out["completion_ids"], out["logprobs"], extras
-        if prompts and isinstance(prompts[0], (list, tuple)) and prompts[0] and isinstance(prompts[0][0], int):
+        pixels = None
+        if images is not None and any(i for i in images):
+            if self.rollout_func is not None:
+                raise ValueError("rollout_func and image prompts cannot be combined")
+            prompt_ids, pixels = self._tokenize_prompts_with_images(prompts, images)
+            extras["pixel_values_list"] = pixels
+        elif prompts and isinstance(prompts[0], (list, tuple)) and prompts[0] and isinstance(prompts[0][0], int):
             prompt_ids = [list(p) for p in prompts]  # pre-tokenised prompts (synthetic benchmarks, custom pipelines)
         else:
             prompt_ids = self._tokenize_prompts(prompts)
         self._max_prompt_len_seen = max([len(p) for p in prompt_ids] + [getattr(self, "_max_prompt_len_seen", 0)])
         # identical consecutive prompts (the num_generations copies) are sent once with n>1 so that
         # the engine shares their prompt KV blocks
-        uniq, counts = [], []
-        for p in prompt_ids:
-            if uniq and uniq[-1] == p and counts[-1] < self.num_generations:
+        uniq, counts, uniq_px = [], [], []
+        for j, p in enumerate(prompt_ids):
+            px = pixels[j] if pixels is not None else None
+            same_px = px is None or (uniq_px and uniq_px[-1] is not None and uniq_px[-1].shape == px.shape
+                                     and torch.equal(uniq_px[-1], px))
+            if uniq and uniq[-1] == p and same_px and counts[-1] < self.num_generations:
                 counts[-1] += 1
             else:
                 uniq.append(p)
+                uniq_px.append(px)
                 counts.append(1)
+        gen_kw = {"images": uniq_px} if pixels is not None else {}
         eng = self._get_rollout()
         if self.state.global_step != self._last_loaded_step and hasattr(eng, "sync_weights"):
             with self._profile("sync_weights"):  # trainer -> generator weights (no-op when storage is shared)
@@ -279,11 +315,12 @@ class OnlineTrainer(Trainer):
             self._last_loaded_step = self.state.global_step
         with self._profile("rollout.generate"):
             if len(set(counts)) == 1:
-                outs = eng.generate(uniq, self._sampling_params(counts[0]))
+                outs = eng.generate(uniq, self._sampling_params(counts[0]), **gen_kw)
             else:
                 outs = []
-                for p, c in zip(uniq, counts):
-                    outs.extend(eng.generate([p], self._sampling_params(c)))
+                for j, (p, c) in enumerate(zip(uniq, counts)):
+                    kw1 = {"images": [uniq_px[j]]} if pixels is not None else {}
+                    outs.extend(eng.generate([p], self._sampling_params(c), **kw1))
         completion_ids = [o.token_ids for o in outs]
         logprobs = [o.logprobs for o in outs]
         return prompt_ids, completion_ids, logprobs, extras
@@ -335,8 +372,9 @@ class OnlineTrainer(Trainer):
 
     # ---- log-probabilities --------------------------------------------------------------------------------------------
     def _get_per_token_logps_and_entropies(self, model, prompt_ids, completion_ids, batch_size=None,
-                                           compute_entropy=False, temperature=None):
-        """prompt_ids / completion_ids: lists of id lists.  Returns padded [B, Tc] log-probs (and entropies)."""
+                                           compute_entropy=False, temperature=None, pixel_values_list=None):
+        """prompt_ids / completion_ids: lists of id lists.  Returns padded [B, Tc] log-probs (and entropies).
+        ``pixel_values_list``: per sequence the pixel tensor of its images (vision-language models)."""
         temperature = self.temperature if temperature is None else temperature
         dev = self.args.device
         B = len(prompt_ids)
@@ -376,7 +414,11 @@ class OnlineTrainer(Trainer):
             buf = host.to(dev, non_blocking=True)
             flat, sel_t, r, c_ = buf[:total], buf[o_sel:o_row], buf[o_row:o_col], buf[o_col:]
             ctx = SeqCtx(buf[o_pos:o_cu].to(torch.int32), buf[o_cu:o_sel].to(torch.int32), int(lens.max()))
-            hidden = model.forward_hidden(flat, ctx)
+            fwd_kw = {}
+            if pixel_values_list is not None and getattr(model, "is_vlm", False):
+                px = [x for x in pixel_values_list[s:s + bs] if x is not None and x.numel()]
+                fwd_kw["pixel_values"] = torch.cat(px).to(dev) if px else None
+            hidden = model.forward_hidden(flat, ctx, **fwd_kw)
             tgt = flat[sel_t + 1]
             lp, en = ops.lm_head_logprobs(hidden[sel_t], model.lm_head_weight, tgt, temperature,
                                           softcap=model.config.final_logit_softcapping, compute_entropy=compute_entropy)
@@ -391,12 +433,14 @@ class OnlineTrainer(Trainer):
         self._last_aux_loss = aux_total
         return logps, ents
 
-    def _ref_logps(self, prompt_ids, completion_ids, batch_size):
+    def _ref_logps(self, prompt_ids, completion_ids, batch_size, pixel_values_list=None):
+        kw = {"pixel_values_list": pixel_values_list}
         with torch.no_grad():
             if self.ref_model is not None:
-                return self._get_per_token_logps_and_entropies(self.ref_model, prompt_ids, completion_ids, batch_size)[0]
+                return self._get_per_token_logps_and_entropies(self.ref_model, prompt_ids, completion_ids, batch_size,
+                                                               **kw)[0]
             with use_adapter(self.model, None):
-                return self._get_per_token_logps_and_entropies(self.model, prompt_ids, completion_ids, batch_size)[0]
+                return self._get_per_token_logps_and_entropies(self.model, prompt_ids, completion_ids, batch_size, **kw)[0]
 
     # ---- logging --------------------------------------------------------------------------------------------------------
     def log(self, logs: dict, start_time: float | None = None):
