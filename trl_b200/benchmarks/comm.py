@@ -49,6 +49,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--copiers", type=int, default=16)
     ap.add_argument("--moe-tokens", type=int, default=8192, help="tokens per rank for the expert-parallel MoE block")
+    ap.add_argument("--copiers-sweep", default="", help="comma-separated copier-CTA counts: time only the fused "
+                                                        "all-gather + GEMM for each and exit")
     a = ap.parse_args()
     D.init_process_group()
     rank, world = D.rank(), D.world_size()
@@ -69,6 +71,25 @@ def main():
     buf.normal_(0, 0.02)
     x = torch.randn(a.tokens, H, device=dev, dtype=torch.bfloat16)
     y = torch.empty(a.tokens, nqkv, device=dev, dtype=torch.bfloat16)
+    if a.copiers_sweep:
+        sweep = {}
+        for c in [int(v) for v in a.copiers_sweep.split(",")]:
+            st_c = AgGemmState(dev, copiers=c)
+            sweep[str(c)] = timed(lambda: ag_gemm(x, arena, off, per, total, 0, nqkv, st_c, out=y))
+        K.check_status(dev)
+        full = torch.empty(total, device=dev, dtype=torch.bfloat16)
+        shard = buf[rank * per:(rank + 1) * per]
+
+        def nccl_ref():
+            td.all_gather_into_tensor(full, shard)
+            torch.matmul(x, full[:nqkv * H].view(nqkv, H).t(), out=y)
+        out["ag_gemm_copier_sweep_ms"] = sweep
+        out["nccl_allgather_then_cublas_ms"] = timed(nccl_ref)
+        if rank == 0:
+            print(json.dumps(out))
+        td.barrier()
+        td.destroy_process_group()
+        return
     st = AgGemmState(dev, copiers=a.copiers)
     t_fused = timed(lambda: ag_gemm(x, arena, off, per, total, 0, nqkv, st, out=y))
     full = torch.empty(total, device=dev, dtype=torch.bfloat16)

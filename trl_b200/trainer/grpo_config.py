@@ -16,7 +16,8 @@ from .base_config import _BaseConfig
 
 @dataclass
 class _OnlineConfig(_BaseConfig):
-    _VALID_DICT_FIELDS = _BaseConfig._VALID_DICT_FIELDS + ["model_init_kwargs", "generation_kwargs", "chat_template_kwargs"]
+    _VALID_DICT_FIELDS = _BaseConfig._VALID_DICT_FIELDS + ["model_init_kwargs", "generation_kwargs", "chat_template_kwargs",
+                                                            "transformers_continuous_batching_config"]
 
     learning_rate: float = 1e-6
     logging_steps: float = 10
@@ -26,6 +27,11 @@ class _OnlineConfig(_BaseConfig):
     disable_dropout: bool = False
     cast_lm_head_to_fp32: bool = False
     remove_unused_columns: Optional[bool] = False
+    # accepted for configuration parity; generation always runs in this framework's own engine (paged KV, continuous
+    # batching), so these select nothing (grpo_config.py / rloo_config.py "transformers continuous batching")
+    use_transformers_continuous_batching: bool = False
+    transformers_continuous_batching_config: Optional[Any] = None
+    use_transformers_paged: bool = False
     num_generations: Optional[int] = 8
     num_generations_eval: Optional[int] = None
     max_completion_length: Optional[int] = 512
@@ -107,6 +113,10 @@ class _OnlineConfig(_BaseConfig):
         pc = self.parallelism_config
         if isinstance(pc, dict) and (pc.get("cp_size", 1) > 1 or pc.get("sp_size", 1) > 1):
             raise ValueError(f"{type(self).__name__[:-6]} does not support context or sequence parallelism.")
+        if self.use_transformers_paged:
+            warnings.warn("`use_transformers_paged` is deprecated and will be removed in v2.0.0. Use "
+                          "`use_transformers_continuous_batching` instead.", FutureWarning)
+            self.use_transformers_continuous_batching = True
 
 
 @dataclass
@@ -138,9 +148,6 @@ class GRPOConfig(_OnlineConfig):
     vllm_importance_sampling_clip_min: Optional[float] = None
     off_policy_mask_threshold: Optional[float] = None
     use_bias_correction_kl: bool = False
-    use_transformers_continuous_batching: bool = False
-    transformers_continuous_batching_config: Optional[Any] = None
-    use_transformers_paged: bool = False
     vllm_importance_sampling_cap: Optional[float] = None
 
     def __post_init__(self):
@@ -162,8 +169,6 @@ class GRPOConfig(_OnlineConfig):
         cmin, cmax = self.vllm_importance_sampling_clip_min, self.vllm_importance_sampling_clip_max
         if cmin is not None and cmin > cmax:
             raise ValueError("vllm_importance_sampling_clip_min must not exceed vllm_importance_sampling_clip_max")
-        if self.use_transformers_paged:
-            warnings.warn("use_transformers_paged is deprecated.", FutureWarning)
         if self.delta is not None and self.use_liger_kernel and False:
             raise ValueError("delta is not supported with the fused loss")
         self._derive_generation_batch()
