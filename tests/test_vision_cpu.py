@@ -174,3 +174,21 @@ def test_grpo_trains_vision_language_model(tmp_path):
     logs = [h for h in tr.state.log_history if "reward" in h]
     assert logs and all(np.isfinite(h["loss"]) for h in logs) and "kl" in logs[-1]
     assert not torch.equal(w0, model.proj1_w)  # gradients reach the projector through the image tokens
+
+
+def test_rloo_runs_with_image_prompts(tmp_path):
+    import numpy as np
+
+    from trl_b200 import RLOOConfig, RLOOTrainer
+
+    model, proc = _vlm_and_processor()
+    rs = np.random.RandomState(4)
+    rows = [{"images": [(rs.rand(28, 28, 3) * 255).astype("uint8")], "prompt": "explain the idea <image>"} for _ in range(4)]
+    args = RLOOConfig(output_dir=str(tmp_path), per_device_train_batch_size=4, num_generations=2, max_completion_length=5,
+                      max_steps=2, logging_steps=1, learning_rate=1e-3, use_cpu=True, save_strategy="no",
+                      report_to="none", beta=0.05)
+    tr = RLOOTrainer(model, lambda completion_ids, **kw: [float(sum(c) % 5) for c in completion_ids], args,
+                     train_dataset=rows, processing_class=proc)
+    tr.train()
+    logs = [h for h in tr.state.log_history if "reward" in h]
+    assert len(logs) == 2 and all(np.isfinite(h["loss"]) for h in logs)

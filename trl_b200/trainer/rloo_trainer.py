@@ -39,7 +39,10 @@ class RLOOTrainer(OnlineTrainer):
         dev = a.device
         mode = "train" if self.model.training else "eval"
         prompts = [x["prompt"] for x in inputs]
-        prompt_ids, completion_ids, _, extras = self._generate(prompts)
+        images = [x.get("images") if "images" in x else ([x["image"]] if x.get("image") is not None else None)
+                  for x in inputs]
+        prompt_ids, completion_ids, _, extras = self._generate(prompts, images if any(i for i in images) else None)
+        pixel_list = extras.pop("pixel_values_list", None)  # vision-language prompts
         B = len(prompts)
         comp_lens = torch.tensor([len(c) for c in completion_ids], device=dev)
         Tc = max(1, int(comp_lens.max()))
@@ -51,10 +54,11 @@ class RLOOTrainer(OnlineTrainer):
         bs = a.per_device_train_batch_size if mode == "train" else a.per_device_eval_batch_size
         maskf = completion_mask.float()
         with torch.no_grad():
-            old_logps, _ = self._get_per_token_logps_and_entropies(self.model, prompt_ids, completion_ids, bs)
+            old_logps, _ = self._get_per_token_logps_and_entropies(self.model, prompt_ids, completion_ids, bs,
+                                                                   pixel_values_list=pixel_list)
             old_sum = (old_logps * maskf).sum(1)
             if self.beta != 0.0:
-                ref_logps = self._ref_logps(prompt_ids, completion_ids, bs)
+                ref_logps = self._ref_logps(prompt_ids, completion_ids, bs, pixel_list)
                 kl = ((old_logps - ref_logps) * maskf).sum(1)
             else:
                 kl = None
@@ -101,14 +105,18 @@ class RLOOTrainer(OnlineTrainer):
         m["frac_reward_zero_std"].append(torch.isclose(std, torch.zeros_like(std)).float().mean())
         if kl is not None:
             m["kl"].append(D.gather(kl / maskf.sum(1).clamp(min=1)).mean())
-        return {"prompt_ids": prompt_ids, "completion_ids_list": completion_ids, "completion_mask": completion_mask,
-                "advantages": adv[sl], "old_logps": old_sum}
+        out = {"prompt_ids": prompt_ids, "completion_ids_list": completion_ids, "completion_mask": completion_mask,
+               "advantages": adv[sl], "old_logps": old_sum}
+        if pixel_list is not None:
+            out["pixel_values_list"] = pixel_list
+        return out
 
     def compute_loss(self, model, inputs, return_outputs=False, num_items_in_batch=None):
         mode = "train" if model.training else "eval"
         m = self._metrics[mode]
         logps, ents = self._get_per_token_logps_and_entropies(model, inputs["prompt_ids"], inputs["completion_ids_list"],
-                                                              compute_entropy=True)
+                                                              compute_entropy=True,
+                                                              pixel_values_list=inputs.get("pixel_values_list"))
         Tc = logps.shape[1]
         maskf = inputs["completion_mask"].float()
         maskf = maskf[:, :Tc] if maskf.shape[1] >= Tc else torch.nn.functional.pad(maskf, (0, Tc - maskf.shape[1]))
