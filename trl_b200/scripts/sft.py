@@ -6,20 +6,13 @@ import os
 
 
 def main(script_args, training_args, model_args, dataset_args):
-    from transformers import AutoTokenizer
-
     from trl_b200 import SFTTrainer, get_peft_config, get_quantization_config
-    from trl_b200.scripts.utils import load_script_dataset
+    from trl_b200.scripts.utils import load_processing_class, load_script_dataset
 
     get_quantization_config(model_args)
     training_args.model_init_kwargs = dict(dtype=model_args.dtype)
-    tok_path = model_args.model_name_or_path
-    if os.path.isdir(str(tok_path)):
-        tokenizer = AutoTokenizer.from_pretrained(tok_path)
-    else:  # preset architectures have no tokenizer files: use the offline ChatML fixture
-        from trl_b200.testing import make_tiny_tokenizer
-
-        tokenizer = make_tiny_tokenizer()
+    # tokenizer, or a processor for vision-language checkpoints; presets get the offline ChatML fixture
+    tokenizer = load_processing_class(model_args.model_name_or_path)
     dataset = load_script_dataset(script_args, dataset_args)
     eval_ds = dataset[script_args.dataset_test_split] if (
         training_args.eval_strategy != "no" and script_args.dataset_test_split in dataset) else None

@@ -123,6 +123,39 @@ def load_script_dataset(script_args: ScriptArguments, dataset_args: DatasetMixtu
 # ---------------------------------------------------------------------------------------------------
 # dataclass -> argparse
 # ---------------------------------------------------------------------------------------------------
+def load_processing_class(path, **tokenizer_kwargs):
+    """Tokenizer for a text checkpoint directory; for a vision-language checkpoint (``model_type: llava``) a processor:
+    the framework's ``VisionProcessor`` when it was saved next to the model, else ``transformers.AutoProcessor``.
+    Presets (no files on disk) get the offline ChatML fixture tokenizer."""
+    import json
+    import os
+
+    path = str(path)
+    if not os.path.isdir(path):
+        from ..testing import make_tiny_tokenizer
+
+        return make_tiny_tokenizer()
+    from transformers import AutoTokenizer
+
+    cfg = os.path.join(path, "config.json")
+    is_vlm = False
+    if os.path.exists(cfg):
+        with open(cfg) as f:
+            is_vlm = json.load(f).get("model_type") == "llava"
+    if is_vlm:
+        pre = os.path.join(path, "preprocessor_config.json")
+        if os.path.exists(pre):
+            with open(pre) as f:
+                if json.load(f).get("processor_class") == "VisionProcessor":
+                    from ..models.vision_processing import VisionProcessor
+
+                    return VisionProcessor.from_pretrained(path)
+        from transformers import AutoProcessor
+
+        return AutoProcessor.from_pretrained(path)
+    return AutoTokenizer.from_pretrained(path, **tokenizer_kwargs)
+
+
 def _str2bool(v):
     if isinstance(v, bool):
         return v
