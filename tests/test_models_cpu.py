@@ -150,3 +150,27 @@ def test_context_parallel_attention_segments_match_full_attention():
             out = O.attention_varlen_qk(q[r * tl:(r + 1) * tl], k[p["k_start"]:p["k_end"]], v[p["k_start"]:p["k_end"]],
                                         p["cu_q"], p["cu_k"])
             assert torch.allclose(out, full[r * tl:(r + 1) * tl], atol=1e-5), (size, r)
+
+
+def test_sliding_window_attention_matches_transformers(tmp_path):
+    import transformers as tf
+
+    torch.manual_seed(0)
+    cfg = preset("tiny-mistral", sliding_window=6)
+    ours = CausalLM(cfg).eval()
+    ours.save_pretrained(str(tmp_path))
+    assert ModelArch.from_pretrained(str(tmp_path)).sliding_window == 6
+    hf = tf.AutoModelForCausalLM.from_pretrained(str(tmp_path), dtype=torch.float32, attn_implementation="eager").eval()
+    ids = torch.randint(0, cfg.vocab_size, (2, 19))
+    with torch.no_grad():
+        a = ours(input_ids=ids).logits
+        b = hf(input_ids=ids).logits
+        full = CausalLM(preset("tiny-mistral"))
+        full.load_state_dict(ours.state_dict())
+        c = full.eval()(input_ids=ids).logits
+    assert torch.allclose(a, b, atol=2e-4, rtol=1e-3), (a - b).abs().max()
+    assert not torch.allclose(a[:, 8:], c[:, 8:], atol=1e-3)  # the window really changes the later positions
+    # the Qwen families carry a sliding_window value that is off unless use_sliding_window is set
+    d = preset("tiny-qwen2").to_hf_dict()
+    d["sliding_window"] = 4096
+    assert ModelArch.from_hf_dict(d).sliding_window is None

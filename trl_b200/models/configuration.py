@@ -55,6 +55,8 @@ class ModelArch:
     bos_token_id: int | None = None
     eos_token_id: int | None = None
     final_logit_softcapping: float | None = None
+    # every token attends to itself and the sliding_window - 1 tokens before it (Mistral v0.1, Phi-3-mini; None = full)
+    sliding_window: int | None = None
     # Gemma: GeGLU instead of SwiGLU, RMSNorm scales by (1 + w), embeddings multiplied by sqrt(hidden)
     hidden_act: str = "silu"
     norm_plus_one: bool = False
@@ -146,6 +148,10 @@ class ModelArch:
             d["architectures"] = [d["architectures"][0].replace("ForCausalLM", "ForSequenceClassification")]
         if self.final_logit_softcapping:
             d["final_logit_softcapping"] = self.final_logit_softcapping
+        if self.model_type in ("mistral", "phi3") or self.sliding_window:
+            d["sliding_window"] = self.sliding_window
+            if self.model_type in ("qwen2", "qwen3", "qwen3_moe"):
+                d["use_sliding_window"] = bool(self.sliding_window)
         d.update(self.extra)
         return d
 
@@ -191,6 +197,9 @@ class ModelArch:
             bos_token_id=d.get("bos_token_id"),
             eos_token_id=d.get("eos_token_id") if not isinstance(d.get("eos_token_id"), list) else d["eos_token_id"][0],
             final_logit_softcapping=d.get("final_logit_softcapping"),
+            # the Qwen families carry a sliding_window value that only applies when use_sliding_window is set
+            sliding_window=(d.get("sliding_window") if (mt in ("mistral", "phi3") or d.get("use_sliding_window"))
+                            else None) or None,
         )
 
     @classmethod

@@ -162,14 +162,16 @@ class DecoderLayer(nn.Module):
         elif ctx.sp is not None and ctx.sp.mode == "allgather_kv":
             from ..parallel import context_parallel
 
+            if c.sliding_window:
+                raise NotImplementedError("context parallelism with sliding-window attention")
             o = context_parallel.attention(q, k, v, ctx, ops.attention_varlen_qk)
         elif ctx.sp is not None:
             from ..parallel import ulysses
 
             o = ulysses.attention(q, k, v, ctx, lambda a, b, d: ops.attention_varlen(a, b, d, ctx.cu_seqlens, ctx.max_seqlen,
-                                                                                   causal=True))
+                                                                                   causal=True, window=c.sliding_window))
         else:
-            o = ops.attention_varlen(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, causal=True)
+            o = ops.attention_varlen(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, causal=True, window=c.sliding_window)
         o = o.reshape(T, c.q_size)
         out = ops.linear(o, self.o_proj)
         return self._lora_add(out, o, ("o_proj",))

@@ -297,8 +297,8 @@ def sumsq(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
 # -------------------------------------------------------------------------------------------
 # attention
 # -------------------------------------------------------------------------------------------
-def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True):
-    """Causal GQA attention over packed documents [T, H, D]."""
+def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True, window=None):
+    """Causal GQA attention over packed documents [T, H, D]; ``window`` = sliding-window size or None."""
     from torch.nn.attention.varlen import varlen_attn
 
     cu = cu_seqlens.to(torch.int32)
@@ -307,8 +307,9 @@ def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True):
         rep = Hq // Hk
         k = k.repeat_interleave(rep, dim=1)
         v = v.repeat_interleave(rep, dim=1)
+    left = int(window) - 1 if window else -1
     return varlen_attn(q.contiguous(), k.contiguous(), v.contiguous(), cu, cu, int(max_seqlen), int(max_seqlen),
-                       window_size=(-1, 0) if causal else (-1, -1))
+                       window_size=(left, 0) if causal else (left, left))
 
 
 def attention_varlen_qk(q, k, v, cu_q, cu_k, max_q, max_k):

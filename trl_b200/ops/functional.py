@@ -51,10 +51,11 @@ def swiglu(gate_up):
     return _ref.swiglu(gate_up)
 
 
-def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True):
+def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True, window=None):
+    """``window``: sliding-window size (a token sees itself and the window - 1 tokens before it); None = full."""
     if q.is_cuda:
-        return _cuda().attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal)
-    return _ref.attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal)
+        return _cuda().attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal, window)
+    return _ref.attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal, window=window)
 
 
 def attention_varlen_qk(q, k, v, cu_q, cu_k, max_q, max_k):

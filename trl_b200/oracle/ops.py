@@ -41,7 +41,7 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     return (F.silu(g) * u).to(gate_up.dtype)
 
 
-def attention_varlen(q, k, v, cu_seqlens, max_seqlen=None, causal=True, scale=None):
+def attention_varlen(q, k, v, cu_seqlens, max_seqlen=None, causal=True, scale=None, window=None):
     """Causal GQA attention over packed documents.
 
     q [T, Hq, D]; k, v [T, Hkv, D]; ``cu_seqlens`` int tensor [n_docs + 1].
@@ -55,6 +55,11 @@ def attention_varlen(q, k, v, cu_seqlens, max_seqlen=None, causal=True, scale=No
     if causal:
         idx = torch.arange(T, device=q.device)
         mask = mask & (idx[:, None] >= idx[None, :])
+    if window:
+        idx = torch.arange(T, device=q.device)
+        mask = mask & (idx[:, None] - idx[None, :] < window)
+        if not causal:
+            mask = mask & (idx[None, :] - idx[:, None] < window)
     rep = Hq // Hkv
     qf = q.float().transpose(0, 1)  # [Hq, T, D]
     kf = k.float().transpose(0, 1).repeat_interleave(rep, dim=0)

@@ -147,6 +147,9 @@ class RolloutEngine:
         if cfg.hidden_act != "silu" or cfg.norm_plus_one or cfg.embed_scale != 1.0 or cfg.head_dim not in (64, 128):
             raise NotImplementedError("the decode kernels cover SwiGLU models with head_dim 64 or 128; use EagerGenerator "
                                       f"for model_type={cfg.model_type!r}")
+        if cfg.sliding_window and max_model_len > cfg.sliding_window:
+            raise NotImplementedError(f"the paged decode attention attends over the whole context: sliding_window="
+                                      f"{cfg.sliding_window} < max_model_len={max_model_len}; use EagerGenerator")
         from .._native import host_runtime
 
         rt = host_runtime()
