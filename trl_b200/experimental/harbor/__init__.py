@@ -1,5 +1,5 @@
 """Harbor task suites as rollout environments (trl/experimental/harbor/__init__.py)."""
-from ._env import HarborBashEnv, HarborEnv
+from ._env import AGENTS, HarborBashEnv, HarborEnv
 from ._spec import HarborSpec
 
-__all__ = ["HarborBashEnv", "HarborEnv", "HarborSpec"]
+__all__ = ["AGENTS", "HarborBashEnv", "HarborEnv", "HarborSpec"]

@@ -102,3 +102,7 @@ class HarborBashEnv(HarborEnv):
             command: The command line to execute.
         """
         return self._exec(command)
+
+
+# built-in agent harnesses by name (``HarborSpec(agent="bash")``); extend with ``AGENTS["name"] = MyEnv``
+AGENTS: dict[str, type[HarborEnv]] = {"bash": HarborBashEnv}

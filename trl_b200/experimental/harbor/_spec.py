@@ -12,7 +12,7 @@ from functools import cached_property
 from pathlib import Path
 from typing import Any
 
-from ._env import HarborBashEnv, HarborEnv
+from ._env import AGENTS, HarborBashEnv, HarborEnv
 
 
 def _outcome_reward_func(environments=None, environment_reward=None, **_) -> list[float]:
@@ -24,8 +24,8 @@ def _outcome_reward_func(environments=None, environment_reward=None, **_) -> lis
 def _resolve_agent(agent) -> type:
     if isinstance(agent, type) and issubclass(agent, HarborEnv):
         return agent
-    if agent == "bash":
-        return HarborBashEnv
+    if isinstance(agent, str) and agent in AGENTS:
+        return AGENTS[agent]
     if isinstance(agent, str) and ":" in agent:
         mod, cls = agent.rsplit(":", 1)
         if mod.endswith(".py"):
@@ -35,7 +35,8 @@ def _resolve_agent(agent) -> type:
         else:
             m = importlib.import_module(mod)
         return getattr(m, cls)
-    raise ValueError(f"Unknown agent {agent!r}: use 'bash', 'module:Class', 'file.py:Class' or a HarborEnv subclass")
+    raise ValueError(f"Unknown agent {agent!r}: use a built-in name ({sorted(AGENTS)}), 'module:Class', 'file.py:Class' "
+                     f"or a HarborEnv subclass")
 
 
 def _read_task_meta(task_dir: Path) -> dict[str, Any]:

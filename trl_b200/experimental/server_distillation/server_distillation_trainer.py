@@ -17,6 +17,34 @@ from ..sdft.loss_utils import add_tail_bucket, compute_divergence
 from .server_distillation_config import ServerDistillationConfig
 
 
+def build_teacher_request_inputs(input_ids: torch.Tensor, attention_mask: torch.Tensor,
+                                 prompt_attention_mask: torch.Tensor | None = None, labels: torch.Tensor | None = None):
+    """Padded batch -> what a teacher-server request needs: (unpadded token rows, prompt lengths, completion lengths).
+    The prompt length of a row comes from ``prompt_attention_mask`` or, without it, from the number of unmasked
+    ``labels`` (server_distillation_trainer.py:84-127)."""
+    if input_ids.shape != attention_mask.shape:
+        raise ValueError(f"input_ids and attention_mask must have the same shape, got {tuple(input_ids.shape)} and "
+                         f"{tuple(attention_mask.shape)}.")
+    ids, keep = input_ids.detach().cpu(), attention_mask.detach().cpu().bool()
+    if prompt_attention_mask is not None:
+        p_len = prompt_attention_mask.detach().cpu().sum(1).long()
+    else:
+        if labels is None:
+            raise ValueError("labels are required when prompt_attention_mask is not provided.")
+        if labels.shape != input_ids.shape:
+            raise ValueError(f"labels must match input_ids shape, got {tuple(labels.shape)} and {tuple(input_ids.shape)}.")
+        p_len = keep.sum(1).long() - (labels.detach().cpu() != -100).sum(1).long()
+    rows, plens, clens = [], [], []
+    for row, m, pl in zip(ids, keep, p_len.tolist()):
+        r = row[m].tolist()
+        if pl < 0 or pl > len(r):
+            raise ValueError(f"Invalid prompt length {pl} for trimmed sequence of length {len(r)}.")
+        rows.append(r)
+        plens.append(int(pl))
+        clens.append(len(r) - int(pl))
+    return rows, plens, clens
+
+
 class ServerDistillationTrainer(DistillationTrainer):
     _tag_names = ["trl", "server-distillation"]
     _name = "ServerDistillation"
