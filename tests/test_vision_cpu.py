@@ -192,3 +192,20 @@ def test_rloo_runs_with_image_prompts(tmp_path):
     tr.train()
     logs = [h for h in tr.state.log_history if "reward" in h]
     assert len(logs) == 2 and all(np.isfinite(h["loss"]) for h in logs)
+
+
+def test_processor_opens_image_files_and_byte_records(tmp_path):
+    import io
+
+    import numpy as np
+    from PIL import Image
+
+    _, proc = _vlm_and_processor()
+    arr = (np.random.RandomState(5).rand(31, 45, 3) * 255).astype("uint8")
+    f = tmp_path / "a.png"
+    Image.fromarray(arr).save(f)
+    buf = io.BytesIO()
+    Image.fromarray(arr).save(buf, format="PNG")
+    a = proc.preprocess_images([[str(f)], [{"bytes": buf.getvalue(), "path": None}], [arr]])
+    assert a.shape == (3, 3, 28, 28)
+    assert torch.allclose(a[0], a[1]) and torch.allclose(a[0], a[2], atol=1e-5)

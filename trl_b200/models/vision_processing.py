@@ -57,6 +57,17 @@ class VisionProcessor:
 
     # ---- images -----------------------------------------------------------------------------------------------------
     def _one_image(self, img: Any) -> torch.Tensor:
+        # file paths and the {"path": ..., "bytes": ...} records of an undecoded datasets.Image column are opened here
+        if isinstance(img, dict) and ("bytes" in img or "path" in img):
+            import io
+
+            from PIL import Image
+
+            img = Image.open(io.BytesIO(img["bytes"])) if img.get("bytes") else Image.open(img["path"])
+        elif isinstance(img, (str, os.PathLike)):
+            from PIL import Image
+
+            img = Image.open(img)
         if isinstance(img, torch.Tensor):
             t = img.float()
             if t.ndim == 3 and t.shape[0] not in (1, 3) and t.shape[-1] in (1, 3):
