@@ -38,7 +38,8 @@ def main():
                      learning_rate=1e-4, use_cpu=True, save_strategy="no", padding_free=True, shard_mode=mode,
                      parallelism_config=pc,
                      lr_scheduler_type="constant", train_sampling_strategy="sequential", completion_only_loss=True,
-                     dataset_kwargs={"skip_prepare_dataset": True}, gradient_checkpointing=False, max_length=None)
+                     dataset_kwargs={"skip_prepare_dataset": True}, gradient_checkpointing=mode == "full_shard_stream",
+                     max_length=None)
     tr = SFTTrainer(model, args, train_dataset=rows, processing_class=Tok())
     tr.train()
     if D.is_main():

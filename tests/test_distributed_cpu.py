@@ -24,7 +24,7 @@ def _run(world, mode, out, steps=4, port=29611):
         return json.load(f)
 
 
-@pytest.mark.parametrize("mode,port", [("ddp", 29611), ("zero2", 29612), ("sp2", 29613), ("cp2", 29614)])
+@pytest.mark.parametrize("mode,port", [("ddp", 29611), ("zero2", 29612), ("sp2", 29613), ("cp2", 29614), ("full_shard_stream", 29615)])
 def test_sft_world1_vs_world2(tmp_path, mode, port):
     ref = _run(1, "ddp", str(tmp_path / "w1.json"))
     two = _run(2, mode, str(tmp_path / f"w2_{mode}.json"), port=port)
@@ -33,3 +33,32 @@ def test_sft_world1_vs_world2(tmp_path, mode, port):
         assert abs(a["loss"] - b["loss"]) < 2e-4, (ref, two)
         assert abs(a["grad_norm"] - b["grad_norm"]) < 1e-3 * max(1.0, a["grad_norm"]), (ref, two)
     assert ref[-1]["loss"] < ref[0]["loss"] + 0.05
+
+
+def _run_stream(world, mode, variant, out, port):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
+    worker = os.path.join(HERE, "dist_worker_stream.py")
+    if world == 1:
+        cmd = [sys.executable, worker, out, mode, variant]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+               "--master-addr", "127.0.0.1", "--master-port", str(port), worker, out, mode, variant]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    from safetensors.torch import load_file
+
+    return load_file(os.path.join(out, "final", "model.safetensors"))
+
+
+def test_streamed_full_shard_saves_and_resumes_like_ddp(tmp_path):
+    """Weights after 3 steps (weight decay on): world-1 ddp == world-2 streamed shards == world-2 streamed shards with a
+    checkpoint after step 2 and a resume in a new trainer."""
+    import torch
+
+    ref = _run_stream(1, "ddp", "straight", str(tmp_path / "ddp"), 0)
+    a = _run_stream(2, "full_shard_stream", "straight", str(tmp_path / "s"), 29616)
+    b = _run_stream(2, "full_shard_stream", "resume", str(tmp_path / "r"), 29617)
+    assert set(ref) == set(a) == set(b)
+    for k in ref:
+        assert torch.allclose(ref[k], a[k], atol=2e-5), (k, (ref[k] - a[k]).abs().max())
+        assert torch.allclose(a[k], b[k], atol=1e-6), (k, (a[k] - b[k]).abs().max())

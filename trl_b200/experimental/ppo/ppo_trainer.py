@@ -161,13 +161,13 @@ class PPOTrainer(OnlineTrainer):
                 m[k].append(v)
         return (loss, None) if return_outputs else loss
 
-    def _save(self, output_dir: str):
+    def _save(self, output_dir: str, state_dict=None):
         """The checkpoint is the policy; the value parts are stored next to it."""
         import os
 
         held = {n: self.model._modules.pop(n) for n in ("value_model", "v_head") if n in self.model._modules}
         try:
-            super()._save(output_dir)
+            super()._save(output_dir, state_dict)
         finally:
             self.model._modules.update(held)
         for n, mod in held.items():

@@ -344,6 +344,11 @@ class Trainer:
                 return FullShardEngine(self.model, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
                                        weight_decay=a.weight_decay)
             # CPU / fp32: same sharding of gradients and optimizer state through the backend collectives
+        if mode == "full_shard_stream":
+            from ..parallel.streamshard import StreamShardEngine
+
+            return StreamShardEngine(self.model, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
+                                     weight_decay=a.weight_decay)
         return TrainEngine(self.model, mode=mode, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
                            weight_decay=a.weight_decay)
 
@@ -587,24 +592,29 @@ class Trainer:
 
     # ---- persistence ------------------------------------------------------------------------------
     def _full_state_dict(self):
+        """Makes the model's weights whole before saving (collective).  Engines that never hold the whole model return
+        the checkpoint tensors instead (host copies on the saving rank, nothing elsewhere)."""
         if self.engine is not None and hasattr(self.engine, "gather_full_params"):
             self.engine.gather_full_params()
+        if self.engine is not None and hasattr(self.engine, "streamed_hf_state_dict"):
+            sd = self.engine.streamed_hf_state_dict(to_cpu=self.args.should_save)
+            return sd if self.args.should_save else None
         return None
 
     def save_model(self, output_dir: str | None = None, _internal_call: bool = False):
         output_dir = output_dir or self.args.output_dir
-        self._full_state_dict()
+        state_dict = self._full_state_dict()
         if self.args.should_save:
             os.makedirs(output_dir, exist_ok=True)
-            self._save(output_dir)
+            self._save(output_dir, state_dict)
         D.barrier()
 
-    def _save(self, output_dir: str):
+    def _save(self, output_dir: str, state_dict=None):
         m = self.model
         if getattr(m, "peft_config", None) is not None and hasattr(m, "save_adapter"):
             m.save_adapter(output_dir)
         elif hasattr(m, "save_pretrained"):
-            m.save_pretrained(output_dir)
+            m.save_pretrained(output_dir, **({"state_dict": state_dict} if state_dict is not None else {}))
         else:
             torch.save(m.state_dict(), os.path.join(output_dir, "pytorch_model.bin"))
         if self.processing_class is not None and hasattr(self.processing_class, "save_pretrained"):
@@ -666,6 +676,8 @@ class Trainer:
         m = self.model
         if hasattr(m, "load_adapter") and os.path.exists(os.path.join(folder, "adapter_model.safetensors")):
             m.load_adapter(folder)
+        elif getattr(m, "_is_native", False) and hasattr(self.engine, "load_weights"):
+            self.engine.load_weights(load_state_dict_dir(folder))  # layer weights live as slices inside the engine
         elif getattr(m, "_is_native", False):
             load_hf_state_dict(m, load_state_dict_dir(folder), strict=True)
         sp = os.path.join(folder, "trainer_state.json")

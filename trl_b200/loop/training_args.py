@@ -140,8 +140,10 @@ class TrainingArguments:
     train_sampling_strategy: str = "random"
     # ---- engine selection (maps the reference's accelerate profiles) --------
     shard_mode: str = field(default="auto", metadata={
-        "help": "auto | ddp | zero1 | zero2 | full_shard.  The packaged accelerate profiles "
-                "(multi_gpu, zero1/2/3, fsdp1/2) map onto these."})
+        "help": "auto | ddp | zero1 | zero2 | full_shard | full_shard_stream.  The packaged accelerate profiles "
+                "(multi_gpu, zero1/2/3, fsdp1/2) map onto these.  full_shard keeps a full-size buffer per layer and "
+                "gathers once per optimizer step (fast, the model must fit one GPU in bf16); full_shard_stream holds "
+                "1 / world of every layer and gathers layer by layer (needs gradient_checkpointing)."})
     activation_offloading: bool = False
 
     def __post_init__(self):

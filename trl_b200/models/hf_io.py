@@ -28,11 +28,19 @@ def resolve_dtype(dtype):
     raise ValueError(f"Invalid dtype {dtype!r}; expected one of {sorted(k for k in _DTYPES if k)}")
 
 
-def to_hf_state_dict(model, include_lora: bool = False) -> dict[str, torch.Tensor]:
+def to_hf_state_dict(model, include_lora: bool = False, before_layer=None, copy_to=None) -> dict[str, torch.Tensor]:
+    """Checkpoint names -> tensors.  ``before_layer(i)`` is called before layer i is read and ``copy_to`` (a device)
+    makes a copy of every layer's tensors right after: the streamed full-shard engine holds one layer at a time.  With
+    ``before_layer`` set and ``copy_to`` None the layers are visited (the gathers are collective) but not kept."""
     c = model.config
     sd = {"model.embed_tokens.weight": model.embed_tokens.detach()}
     for i, l in enumerate(model.layers):
         p = f"model.layers.{i}."
+        if before_layer is not None:
+            before_layer(i)
+            if copy_to is None:
+                continue
+        n_before = len(sd)
         qkv = l.qkv_proj.detach()
         fused_on_disk = c.model_type == "phi3"  # Phi-3 checkpoints keep qkv_proj and gate_up_proj fused, like memory here
         if fused_on_disk:
@@ -64,6 +72,9 @@ def to_hf_state_dict(model, include_lora: bool = False) -> dict[str, torch.Tenso
                 sd[p + "mlp.gate_proj.weight"] = l.gate_up_proj.detach()[:I]
                 sd[p + "mlp.up_proj.weight"] = l.gate_up_proj.detach()[I:]
             sd[p + "mlp.down_proj.weight"] = l.down_proj.detach()
+        if before_layer is not None:
+            for k in list(sd)[n_before:]:
+                sd[k] = sd[k].to(copy_to, copy=True)
     sd["model.norm.weight"] = model.norm.detach()
     if c.num_labels:
         sd["score.weight"] = model.score.detach()
@@ -73,8 +84,9 @@ def to_hf_state_dict(model, include_lora: bool = False) -> dict[str, torch.Tenso
 
 
 @torch.no_grad()
-def load_hf_state_dict(model, sd: dict[str, torch.Tensor], strict: bool = True) -> list[str]:
-    """Copy tensors named the HF way into the fused native parameters."""
+def load_hf_state_dict(model, sd: dict[str, torch.Tensor], strict: bool = True, after_layer=None) -> list[str]:
+    """Copy tensors named the HF way into the fused native parameters.  ``after_layer(i)`` runs once layer i is
+    complete (the streamed full-shard engine re-slices its shard there, before the slot is reused)."""
     c = model.config
     used = set()
 
@@ -131,6 +143,8 @@ def load_hf_state_dict(model, sd: dict[str, torch.Tensor], strict: bool = True) 
                 put(l.gate_up_proj[:I], take(p + "mlp.gate_proj.weight"))
                 put(l.gate_up_proj[I:], take(p + "mlp.up_proj.weight"))
             put(l.down_proj, take(p + "mlp.down_proj.weight"))
+        if after_layer is not None:
+            after_layer(i)
     put(model.norm, take("model.norm.weight"))
     if c.num_labels:
         put(model.score, take("score.weight", required=False))

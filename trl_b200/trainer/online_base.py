@@ -190,6 +190,9 @@ class OnlineTrainer(Trainer):
                               **(a.generation_kwargs or {}))
 
     def _get_rollout(self):
+        if getattr(getattr(self, "engine", None), "mode", "") == "full_shard_stream":
+            raise NotImplementedError("generation reads whole weights; shard_mode='full_shard_stream' holds one layer "
+                                      "at a time - use full_shard or zero2 for online trainers")
         if self._rollout is None:
             if self.args.device.type == "cuda":
                 from ..rollout.engine import RolloutEngine
