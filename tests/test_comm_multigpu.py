@@ -48,3 +48,11 @@ def test_weight_reshard_from_full_shard_to_tp_layout():
            "--master-port", "29629", os.path.join(HERE, "dist_worker_reshard_gpu.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=200)
     assert r.returncode == 0 and "RESHARD_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_streamed_full_shard_engine_two_ranks():
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29631", os.path.join(HERE, "dist_worker_streamshard_gpu.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=200)
+    assert r.returncode == 0 and "STREAMSHARD_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
