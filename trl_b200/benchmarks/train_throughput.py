@@ -44,7 +44,11 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--task", choices=["dpo", "sft"], default="dpo")
     ap.add_argument("--model", default="llama-3-8b")
-    ap.add_argument("--shard", default=None, help="ddp | zero2 | full_shard (default: full_shard when world > 1)")
+    ap.add_argument("--shard", default=None, help="ddp | zero2 | full_shard | full_shard_stream (default: full_shard when "
+                                                  "world > 1)")
+    ap.add_argument("--meta-init", action="store_true",
+                    help="with full_shard_stream: build the model on the meta device and initialise every layer inside "
+                         "the engine's slots, so the whole model never exists on one GPU (Llama-3-70B)")
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--pairs-per-gpu", type=int, default=2)
@@ -65,7 +69,9 @@ def main():
         torch.cuda.set_device(dev)
     torch.manual_seed(1234)
     cfg = preset(a.model, **({"num_hidden_layers": a.layers} if a.layers else {}))
-    model = CausalLM(cfg, dtype=torch.bfloat16 if on_gpu else torch.float32, device=dev)
+    if a.meta_init and (a.task != "sft" or (a.shard or "") != "full_shard_stream"):
+        raise SystemExit("--meta-init goes with --task sft --shard full_shard_stream (DPO also needs a whole reference model)")
+    model = CausalLM(cfg, dtype=torch.bfloat16 if on_gpu else torch.float32, device="meta" if a.meta_init else dev)
     tok = SyntheticTokenizer(cfg.vocab_size)
     shard = a.shard or ("full_shard" if world > 1 else "ddp")
     out_dir = tempfile.mkdtemp(prefix="bench_train_")

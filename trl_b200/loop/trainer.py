@@ -215,8 +215,13 @@ class Trainer:
         if self.model is None:
             return
         dev = self.args.device
+        first = next(self.model.parameters(), None)
+        on_meta = first is not None and first.is_meta  # materialised slice by slice by the streamed engine
+        if on_meta and self.args.shard_mode != "full_shard_stream":
+            raise ValueError("a model on the meta device can only be trained with shard_mode='full_shard_stream'")
         if dev.type == "cuda":
             torch.cuda.set_device(dev)
+        if dev.type == "cuda" and not on_meta:
             dt = torch.bfloat16 if self.args.bf16 else (torch.float16 if self.args.fp16 else None)
             self.model.to(device=dev, dtype=dt) if dt is not None else self.model.to(dev)
         if self.args.gradient_checkpointing and hasattr(self.model, "gradient_checkpointing_enable"):
@@ -348,7 +353,7 @@ class Trainer:
             from ..parallel.streamshard import StreamShardEngine
 
             return StreamShardEngine(self.model, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
-                                     weight_decay=a.weight_decay)
+                                     weight_decay=a.weight_decay, device=a.device, init_seed=a.seed)
         return TrainEngine(self.model, mode=mode, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
                            weight_decay=a.weight_decay)
 

@@ -45,11 +45,39 @@ class _LayerShard:
         self.no_decay = []  # (lo, hi) ranges of 1-D parameters inside the flat layout
 
 
+def _rebind(root: nn.Module, dotted: str, value: torch.Tensor) -> nn.Parameter:
+    """Replaces the (meta) parameter ``root.<dotted>`` by a parameter over ``value``."""
+    *path, leaf = dotted.split(".")
+    mod = root
+    for part in path:
+        mod = getattr(mod, part)
+    p = nn.Parameter(value, requires_grad=True)
+    mod._parameters[leaf] = p
+    return p
+
+
+@torch.no_grad()
+def _init_param(name: str, v: torch.Tensor, std: float, gen: torch.Generator):
+    """Same rule as ``CausalLM.reset_parameters``: norm weights one, other vectors zero, matrices N(0, std)."""
+    leaf = name.rsplit(".", 1)[-1]
+    if v.ndim == 1 and ("layernorm" in leaf or leaf == "norm" or leaf.endswith("_norm")):
+        v.fill_(1.0)
+    elif v.ndim == 1:
+        v.zero_()
+    else:
+        v.normal_(0.0, std, generator=gen)
+
+
 class StreamShardEngine:
     sharded = True
     mode = "full_shard_stream"
 
-    def __init__(self, model: nn.Module, *, betas=(0.9, 0.999), eps=1e-8, weight_decay: float = 0.0, group=None):
+    def __init__(self, model: nn.Module, *, betas=(0.9, 0.999), eps=1e-8, weight_decay: float = 0.0, group=None,
+                 device=None, init_seed: int = 0, init_std: float = 0.02):
+        """``model`` may live on the meta device (``CausalLM(cfg, device="meta")``): then ``device`` names where the
+        slices go and every layer is initialised inside its slot with a generator seeded by (``init_seed``, layer), so
+        that all ranks draw the same weights and the whole model never exists anywhere (load real weights afterwards
+        with ``load_weights``)."""
         self.model, self.group = model, group
         self.world = td.get_world_size(group) if td.is_initialized() else 1
         self.rank = td.get_rank(group) if td.is_initialized() else 0
@@ -59,7 +87,10 @@ class StreamShardEngine:
         if layers is None or len(layers) == 0:
             raise ValueError("the streamed full-shard engine needs a model with a `layers` list")
         first = next(model.parameters())
-        self.dev, self.dtype = first.device, first.dtype
+        meta = first.is_meta
+        if meta and device is None:
+            raise ValueError("a model on the meta device needs `device`")
+        self.dev, self.dtype = (torch.device(device) if meta else first.device), first.dtype
         unit = self.world * _ALIGN
         self.layers: list[_LayerShard] = []
         in_layers = set()
@@ -84,20 +115,25 @@ class StreamShardEngine:
         for ls in self.layers:
             per = ls.numel // self.world
             lo = self.rank * per
-            flat = torch.zeros(ls.numel, dtype=self.dtype, device=self.dev)
-            for p, o in zip(ls.params, ls.offsets):
-                flat[o:o + p.numel()].copy_(p.data.reshape(-1))
-            ls.shard = flat[lo:lo + per].clone()
+            slot = self.slots[ls.slot]
+            views = [slot[o:o + p.numel()].view(p.shape) for p, o in zip(ls.params, ls.offsets)]
+            if meta:
+                gen = torch.Generator(device=self.dev).manual_seed(init_seed * 1000003 + ls.idx + 1)
+                ls.params = [_rebind(ls.module, n, v) for n, v in zip(ls.names, views)]
+                for n, v in zip(ls.names, views):
+                    _init_param(n, v, init_std, gen)
+            else:
+                for p, v in zip(ls.params, views):
+                    v.copy_(p.data)   # layers two apart share the slot: the slice is taken right below
+                    p.data = v        # the original storage is released here
+            ls.shard = slot[lo:lo + per].clone()
             ls.master = ls.shard if self.dtype == torch.float32 else ls.shard.float()
             ls.exp_avg = torch.zeros(per, dtype=torch.float32, device=self.dev)
             ls.exp_avg_sq = torch.zeros(per, dtype=torch.float32, device=self.dev)
             ls.grad_acc = torch.zeros(per, dtype=torch.float32, device=self.dev)
-            slot = self.slots[ls.slot]
-            for p, o in zip(ls.params, ls.offsets):
-                p.data = slot[o:o + p.numel()].view(p.shape)  # the original storage is released here
-            del flat
         # ---- everything outside the layers: whole on every rank, zero-2 style state ----
-        rest = [(n, p) for n, p in model.named_parameters() if p.requires_grad and id(p) not in in_layers]
+        rest = [(n, p) for n, p in model.named_parameters() if p.requires_grad and id(p) not in in_layers
+                and not any(p is q for l in self.layers for q in l.params)]
         seen, uniq = set(), []
         for n, p in rest:
             if id(p) not in seen:
@@ -111,9 +147,15 @@ class StreamShardEngine:
         self.rest_numel = (cur + unit - 1) // unit * unit if uniq else 0
         self.rest_flat = torch.zeros(self.rest_numel, dtype=self.dtype, device=self.dev)
         self.rest_grad = torch.zeros(self.rest_numel, dtype=torch.float32, device=self.dev)
-        for p, o in zip(self.rest_params, self.rest_offsets):
-            self.rest_flat[o:o + p.numel()].copy_(p.data.reshape(-1))
-            p.data = self.rest_flat[o:o + p.numel()].view(p.shape)
+        gen = torch.Generator(device=self.dev).manual_seed(init_seed * 1000003) if meta else None
+        for j, (n, p, o) in enumerate(zip(self.rest_names, list(self.rest_params), self.rest_offsets)):
+            v = self.rest_flat[o:o + p.numel()].view(p.shape)
+            if meta:
+                self.rest_params[j] = _rebind(model, n, v)
+                _init_param(n, v, init_std, gen)
+            else:
+                v.copy_(p.data)
+                p.data = v
         per = self.rest_numel // self.world
         self.rest_lo, self.rest_hi = self.rank * per, (self.rank + 1) * per
         sh = self.rest_flat[self.rest_lo:self.rest_hi]
