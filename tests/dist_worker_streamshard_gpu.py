@@ -57,7 +57,7 @@ def main():
         assert torch.isfinite(sd[k].float()).all(), k
         assert torch.allclose(sd[k].float().cpu(), v.float().cpu(), atol=3e-2, rtol=3e-2), k
     # parameter memory: one slice per layer + two slots, not the whole model
-    held = sum(l.shard.numel() for l in e_st.layers) + sum(s.numel() for s in e_st.slots)
+    held = sum(l.master.numel() for l in e_st.layers) + sum(s.numel() for s in e_st.slots)
     whole = sum(l.numel for l in e_st.layers)
     assert held < 0.5 * whole + 2 * e_st.slots[0].numel() + 1
     td.barrier()

@@ -352,8 +352,11 @@ class Trainer:
         if mode == "full_shard_stream":
             from ..parallel.streamshard import StreamShardEngine
 
+            # TRL_B200_STREAM_GRAD_DTYPE=bf16: keep the reduced layer gradients in bf16 (2 bytes / parameter less per
+            # rank; exact when gradient_accumulation_steps == 1, where the reduce-scatter already delivers bf16)
+            gd = {"bf16": torch.bfloat16, "fp32": torch.float32}[os.environ.get("TRL_B200_STREAM_GRAD_DTYPE", "fp32")]
             return StreamShardEngine(self.model, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
-                                     weight_decay=a.weight_decay, device=a.device, init_seed=a.seed)
+                                     weight_decay=a.weight_decay, device=a.device, init_seed=a.seed, grad_dtype=gd)
         return TrainEngine(self.model, mode=mode, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
                            weight_decay=a.weight_decay)
 

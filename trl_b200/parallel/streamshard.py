@@ -21,9 +21,10 @@ backward, which is what makes overwriting the slot legal.  Collectives are the b
 CPU); the overlap of the next layer's gather with the current layer's math is the job of the fused kernels in
 ``fullshard.py`` and is not repeated here.
 
-Per rank and per parameter of a streamed layer: 2 (bf16 slice) + 4 + 8 (master, moments) + 4 (gradient
-accumulator) = 18 bytes / world, plus 2 slots + 1 gradient buffer of one layer.  Llama-3-70B on 8 ranks: about
-155 GB of sharded state + 5 GB of slots, against 140 GB for the bf16 weights alone under ``FullShardEngine``.
+Per rank and per parameter of a streamed layer: 4 + 8 (fp32 master, moments; the bf16 copy exists only inside the
+slots) + 4 (gradient accumulator; 2 with ``grad_dtype=torch.bfloat16``) = 16 (14) bytes / world, plus 2 slots + 1
+gradient buffer of one layer.  Llama-3-70B on 8 ranks: about 141 (124) GB of sharded state + 5 GB of slots per GPU,
+against 140 GB for the bf16 weights alone under ``FullShardEngine``.
 """
 from __future__ import annotations
 
@@ -40,7 +41,7 @@ class _LayerShard:
     def __init__(self, idx, module, names, params, offsets, numel, slot):
         self.idx, self.module, self.names, self.params, self.offsets, self.numel, self.slot = (
             idx, module, names, params, offsets, numel, slot)
-        self.shard = self.master = self.exp_avg = self.exp_avg_sq = self.grad_acc = None
+        self.master = self.exp_avg = self.exp_avg_sq = self.grad_acc = None
         self.arrived = 0
         self.no_decay = []  # (lo, hi) ranges of 1-D parameters inside the flat layout
 
@@ -73,7 +74,7 @@ class StreamShardEngine:
     mode = "full_shard_stream"
 
     def __init__(self, model: nn.Module, *, betas=(0.9, 0.999), eps=1e-8, weight_decay: float = 0.0, group=None,
-                 device=None, init_seed: int = 0, init_std: float = 0.02):
+                 device=None, init_seed: int = 0, init_std: float = 0.02, grad_dtype: torch.dtype | None = None):
         """``model`` may live on the meta device (``CausalLM(cfg, device="meta")``): then ``device`` names where the
         slices go and every layer is initialised inside its slot with a generator seeded by (``init_seed``, layer), so
         that all ranks draw the same weights and the whole model never exists anywhere (load real weights afterwards
@@ -83,6 +84,9 @@ class StreamShardEngine:
         self.rank = td.get_rank(group) if td.is_initialized() else 0
         self.betas, self.eps, self.weight_decay = betas, eps, weight_decay
         self.step_count = 0
+        # accumulator of the reduced layer gradients.  fp32 by default; the compute dtype loses nothing when every
+        # optimizer step has one micro-batch (the reduce-scatter already delivers that dtype) and saves 2 bytes / param
+        self.grad_dtype = grad_dtype or torch.float32
         layers = getattr(model, "layers", None)
         if layers is None or len(layers) == 0:
             raise ValueError("the streamed full-shard engine needs a model with a `layers` list")
@@ -126,11 +130,10 @@ class StreamShardEngine:
                 for p, v in zip(ls.params, views):
                     v.copy_(p.data)   # layers two apart share the slot: the slice is taken right below
                     p.data = v        # the original storage is released here
-            ls.shard = slot[lo:lo + per].clone()
-            ls.master = ls.shard if self.dtype == torch.float32 else ls.shard.float()
+            ls.master = slot[lo:lo + per].to(torch.float32, copy=True)  # fp32 owned slice; the compute-dtype copy is made when gathering
             ls.exp_avg = torch.zeros(per, dtype=torch.float32, device=self.dev)
             ls.exp_avg_sq = torch.zeros(per, dtype=torch.float32, device=self.dev)
-            ls.grad_acc = torch.zeros(per, dtype=torch.float32, device=self.dev)
+            ls.grad_acc = torch.zeros(per, dtype=self.grad_dtype, device=self.dev)
         # ---- everything outside the layers: whole on every rank, zero-2 style state ----
         rest = [(n, p) for n, p in model.named_parameters() if p.requires_grad and id(p) not in in_layers
                 and not any(p is q for l in self.layers for q in l.params)]
@@ -180,7 +183,7 @@ class StreamShardEngine:
         ls = self.layers[idx]
         if self._resident[ls.slot] == idx:
             return
-        self._gather_into(self.slots[ls.slot][:ls.numel], ls.shard)
+        self._gather_into(self.slots[ls.slot][:ls.numel], ls.master.to(self.dtype))
         self._resident[ls.slot] = idx
 
     def _reduce_to_shard(self, flat: torch.Tensor, numel: int) -> torch.Tensor:
@@ -197,7 +200,7 @@ class StreamShardEngine:
         return buf[self.rank * per:(self.rank + 1) * per] / self.world
 
     def _flush_layer(self, ls: _LayerShard):
-        ls.grad_acc.add_(self._reduce_to_shard(self.gbuf, ls.numel))
+        ls.grad_acc.add_(self._reduce_to_shard(self.gbuf, ls.numel).to(ls.grad_acc.dtype))
         ls.arrived = 0
         self._pending = None
 
@@ -268,7 +271,7 @@ class StreamShardEngine:
         rest_g = self._reduce_to_shard(self.rest_grad, self.rest_numel) if self.rest_numel else None
         sq = torch.zeros((), dtype=torch.float32, device=self.dev)
         for ls in self.layers:
-            sq += ls.grad_acc.pow(2).sum()
+            sq += ls.grad_acc.float().pow(2).sum()
         if rest_g is not None:
             sq += rest_g.pow(2).sum()
         if self.world > 1:
@@ -278,9 +281,9 @@ class StreamShardEngine:
         if max_grad_norm is not None and max_grad_norm > 0:
             scale = torch.clamp(max_grad_norm / (norm + 1e-6), max=1.0)
         for ls in self.layers:
-            shadow = None if self.dtype == torch.float32 else ls.shard
             per = ls.numel // self.world
-            self._adamw(ls.master, ls.grad_acc, ls.exp_avg, ls.exp_avg_sq, shadow, lr, scale, ls.no_decay, self.rank * per)
+            g = ls.grad_acc if ls.grad_acc.dtype == torch.float32 else ls.grad_acc.float()
+            self._adamw(ls.master, g, ls.exp_avg, ls.exp_avg_sq, None, lr, scale, ls.no_decay, self.rank * per)
         if rest_g is not None:
             sh = self.rest_flat[self.rest_lo:self.rest_hi]
             shadow = None if self.dtype == torch.float32 else sh
@@ -306,8 +309,6 @@ class StreamShardEngine:
             l.master.copy_(s["master"])
             l.exp_avg.copy_(s["exp_avg"])
             l.exp_avg_sq.copy_(s["exp_avg_sq"])
-            if l.master is not l.shard:
-                l.shard.copy_(l.master)
         self.rest_master.copy_(sd["rest"]["master"])
         self.rest_exp_avg.copy_(sd["rest"]["exp_avg"])
         self.rest_exp_avg_sq.copy_(sd["rest"]["exp_avg_sq"])
@@ -334,9 +335,7 @@ class StreamShardEngine:
         def reslice(i):
             ls = self.layers[i]
             per = ls.numel // self.world
-            ls.shard.copy_(self.slots[ls.slot][self.rank * per:(self.rank + 1) * per])
-            if ls.master is not ls.shard:
-                ls.master.copy_(ls.shard)
+            ls.master.copy_(self.slots[ls.slot][self.rank * per:(self.rank + 1) * per])
             self._resident[ls.slot] = None
 
         lm = getattr(self.model, "language_model", self.model)
