@@ -183,7 +183,7 @@ def test_grpo_unscorable_completions_get_zero_advantage(tmp_path, tiny_tokenizer
     assert len(_changed(model, before)) == len(before)  # no signal -> no update
 
 
-def test_grpo_generation_batch_schedule(tmp_path, tiny_tokenizer):
+def test_grpo_generation_batch_schedule_prompts_seen_by_training_step(tmp_path, tiny_tokenizer):
     """per_device_bs=6, steps_per_generation=4, num_generations=4, num_iterations=2, GA=3: one generation batch of
     24 rows = 6 prompts x 4 serves 8 consecutive training steps; 48 training_step calls for 3 epochs over 12 prompts."""
     ds = make_dataset("standard_prompt_only", 12)
@@ -317,3 +317,49 @@ def test_sft_trains_other_families(tmp_path, tiny_tokenizer, name):
                     processing_class=tiny_tokenizer)
     tr.train()
     assert _changed(model, before) == []
+
+
+def _sft_trajectory(tmp_path, tag, **over):
+    g = torch.Generator().manual_seed(5)
+    rows = []
+    for _ in range(8 * 4):  # 4 optimizer steps of 8 single-document sequences of different lengths
+        n = int(torch.randint(16, 49, (1,), generator=g))
+        rows.append({"input_ids": torch.randint(0, 1024, (n,), generator=g).tolist(),
+                     "completion_mask": [0] * (n // 2) + [1] * (n - n // 2)})
+    torch.manual_seed(0)
+    kw = dict(output_dir=str(tmp_path / tag), per_device_train_batch_size=8, gradient_accumulation_steps=1, max_steps=4,
+              logging_steps=1, learning_rate=1e-3, use_cpu=True, save_strategy="no", report_to="none",
+              lr_scheduler_type="constant", train_sampling_strategy="sequential", padding_free=True,
+              completion_only_loss=True, dataset_kwargs={"skip_prepare_dataset": True}, gradient_checkpointing=True,
+              max_length=None)
+    kw.update(over)
+    tr = SFTTrainer(make_tiny_model(seed=0), SFTConfig(**kw), train_dataset=rows, processing_class=_Tok())
+    tr.train()
+    return [(h["loss"], h["grad_norm"]) for h in tr.state.log_history if "grad_norm" in h]
+
+
+class _Tok:
+    pad_token, eos_token, pad_token_id, eos_token_id, chat_template = "<pad>", "<eos>", 0, 1, None
+
+    def save_pretrained(self, p):
+        pass
+
+    def convert_tokens_to_ids(self, t):
+        return 1
+
+
+def test_sft_trajectory_equivalence_classes(tmp_path):
+    """One global batch, four ways to run it: the loss / grad-norm series must agree (the reference's invariant suite:
+    default == per-device batch 1 x accumulation 8 == no activation checkpointing; padding-free == padded)."""
+    base = _sft_trajectory(tmp_path, "base")
+    assert len(base) == 4
+    variants = {
+        "bs1_ga8": dict(per_device_train_batch_size=1, gradient_accumulation_steps=8),
+        "no_ckpt": dict(gradient_checkpointing=False),
+        "padded": dict(padding_free=False),
+        "partial_ckpt": dict(gradient_checkpointing_kwargs={"num_layers": 1}),
+    }
+    for name, over in variants.items():
+        got = _sft_trajectory(tmp_path, name, **over)
+        for (l0, g0), (l1, g1) in zip(base, got):
+            assert abs(l0 - l1) < 1e-4 and abs(g0 - g1) < 1e-3 * max(1.0, g0), (name, base, got)
