@@ -363,3 +363,29 @@ def test_sft_trajectory_equivalence_classes(tmp_path):
         got = _sft_trajectory(tmp_path, name, **over)
         for (l0, g0), (l1, g1) in zip(base, got):
             assert abs(l0 - l1) < 1e-4 and abs(g0 - g1) < 1e-3 * max(1.0, g0), (name, base, got)
+
+
+def _dpo_trajectory(tmp_path, tag, tok, **over):
+    torch.manual_seed(0)
+    kw = dict(output_dir=str(tmp_path / tag), per_device_train_batch_size=4, gradient_accumulation_steps=1, max_steps=3,
+              logging_steps=1, learning_rate=1e-3, use_cpu=True, save_strategy="no", report_to="none", beta=0.5,
+              lr_scheduler_type="constant", train_sampling_strategy="sequential", gradient_checkpointing=False)
+    kw.update(over)
+    tr = DPOTrainer(make_tiny_model(seed=0), args=DPOConfig(**kw), train_dataset=make_dataset("standard_preference", 12),
+                    processing_class=tok)
+    tr.train()
+    return [(h["loss"], h["grad_norm"], h["rewards/margins"]) for h in tr.state.log_history if "grad_norm" in h]
+
+
+def test_dpo_trajectory_equivalence_classes(tmp_path, tiny_tokenizer):
+    """Same pairs, same order: accumulation, precomputed reference log-probs, padding-free batches and activation
+    checkpointing must not change the loss / grad-norm / margin series."""
+    base = _dpo_trajectory(tmp_path, "base", tiny_tokenizer)
+    assert len(base) == 3 and abs(base[0][0] - 0.6931) < 1e-3
+    for name, over in {"bs1_ga4": dict(per_device_train_batch_size=1, gradient_accumulation_steps=4),
+                       "precomputed_ref": dict(precompute_ref_log_probs=True),
+                       "padding_free": dict(padding_free=True),
+                       "ckpt": dict(gradient_checkpointing=True)}.items():
+        got = _dpo_trajectory(tmp_path, name, tiny_tokenizer, **over)
+        for a, b in zip(base, got):
+            assert all(abs(x - y) < 2e-4 * max(1.0, abs(x)) for x, y in zip(a, b)), (name, base, got)
