@@ -18,8 +18,9 @@ profiles, trl/accelerate_configs/fsdp2.yaml and zero3.yaml):
 
 Activation checkpointing is required: with it autograd keeps no references to a layer's weights between forward and
 backward, which is what makes overwriting the slot legal.  Collectives are the backend's (NCCL on GPUs, gloo on
-CPU); the overlap of the next layer's gather with the current layer's math is the job of the fused kernels in
-``fullshard.py`` and is not repeated here.
+CPU), issued asynchronously: while a layer computes, the gather of the layer expected next already fills the other
+slot (2 L - 2 gathers per forward + backward of L layers, none wasted).  Gathering *inside* the consuming GEMM is the
+job of the fused kernels in ``fullshard.py`` and is not repeated here.
 
 Per rank and per parameter of a streamed layer: 4 + 8 (fp32 master, moments; the bf16 copy exists only inside the
 slots) + 4 (gradient accumulator; 2 with ``grad_dtype=torch.bfloat16``) = 16 (14) bytes / world, plus 2 slots + 1
@@ -74,7 +75,7 @@ class StreamShardEngine:
     mode = "full_shard_stream"
 
     def __init__(self, model: nn.Module, *, betas=(0.9, 0.999), eps=1e-8, weight_decay: float = 0.0, group=None,
-                 device=None, init_seed: int = 0, init_std: float = 0.02, grad_dtype: torch.dtype | None = None):
+                 device=None, init_seed: int = 0, init_std: float = 0.02, grad_dtype: torch.dtype | None = None, prefetch: bool = True):
         """``model`` may live on the meta device (``CausalLM(cfg, device="meta")``): then ``device`` names where the
         slices go and every layer is initialised inside its slot with a generator seeded by (``init_seed``, layer), so
         that all ranks draw the same weights and the whole model never exists anywhere (load real weights afterwards
@@ -115,7 +116,10 @@ class StreamShardEngine:
         # separate allocations: autograd tracks in-place writes per base tensor
         self.slots = [torch.zeros(slot_numel, dtype=self.dtype, device=self.dev) for _ in range(2)]
         self.gbuf = torch.zeros(slot_numel, dtype=self.dtype, device=self.dev)
-        self._resident = [None, None]  # layer index whose gathered weights a slot holds, or None
+        self._resident = [None, None]  # layer index whose gathered weights a slot holds (or is receiving), or None
+        self._inflight = [None, None]  # per slot: (layer, async work handle, send buffer) of a gather not yet waited for
+        self._last_idx = None
+        self.prefetch = prefetch
         for ls in self.layers:
             per = ls.numel // self.world
             lo = self.rank * per
@@ -177,14 +181,46 @@ class StreamShardEngine:
         else:
             td.all_gather_into_tensor(out, shard.contiguous(), group=self.group)
 
+    def _wait_slot(self, slot: int):
+        fl = self._inflight[slot]
+        if fl is not None:
+            fl[1].wait()  # stream-ordered on GPUs: later kernels of the current stream see the gathered weights
+            self._inflight[slot] = None
+
+    def _invalidate(self):
+        """The owned slices changed (optimizer step, checkpoint load): whatever the slots hold is stale."""
+        for slot in (0, 1):
+            self._wait_slot(slot)
+        self._resident = [None, None]
+        self._last_idx = None
+
+    def _start_gather(self, idx: int):
+        ls = self.layers[idx]
+        self._wait_slot(ls.slot)
+        src = ls.master.to(self.dtype)
+        work = td.all_gather_into_tensor(self.slots[ls.slot][:ls.numel], src, group=self.group, async_op=True)
+        self._inflight[ls.slot] = (idx, work, src)  # src must outlive the collective
+        self._resident[ls.slot] = idx
+
     @torch.no_grad()
     def materialize(self, idx: int):
-        """Makes layer ``idx``'s weights valid in its slot (collective: every rank calls it for the same layer)."""
+        """Makes layer ``idx``'s weights valid in its slot (collective: every rank calls it for the same layer), then
+        starts the gather of the layer expected next into the OTHER slot, so that it travels while this layer
+        computes: ``idx + 1`` when the layers are visited upwards (forward), ``idx - 1`` downwards or on a repeat
+        (the recompute order of the backward pass).  A wrong guess only costs one unused gather."""
         ls = self.layers[idx]
-        if self._resident[ls.slot] == idx:
-            return
-        self._gather_into(self.slots[ls.slot][:ls.numel], ls.master.to(self.dtype))
-        self._resident[ls.slot] = idx
+        if self._resident[ls.slot] != idx:
+            if self.world == 1:
+                self.slots[ls.slot][:ls.numel].copy_(ls.master)
+                self._resident[ls.slot] = idx
+            else:
+                self._start_gather(idx)
+        self._wait_slot(ls.slot)
+        last, self._last_idx = self._last_idx, idx
+        if self.prefetch and self.world > 1:
+            nxt = idx + 1 if (last is None or idx > last) else idx - 1
+            if 0 <= nxt < len(self.layers) and self._resident[self.layers[nxt].slot] != nxt:
+                self._start_gather(nxt)
 
     def _reduce_to_shard(self, flat: torch.Tensor, numel: int) -> torch.Tensor:
         """Average of ``flat[:numel]`` over the ranks, this rank's slice, fp32."""
@@ -290,7 +326,7 @@ class StreamShardEngine:
             self._adamw(self.rest_master, rest_g, self.rest_exp_avg, self.rest_exp_avg_sq, shadow, lr, scale,
                         self.rest_no_decay, self.rest_lo)
             self._gather_into(self.rest_flat, sh.clone())
-        self._resident = [None, None]  # the slices changed: the slots are stale
+        self._invalidate()
         return norm
 
     # ---- checkpoints ---------------------------------------------------------------------------------------------
@@ -313,7 +349,7 @@ class StreamShardEngine:
         self.rest_exp_avg.copy_(sd["rest"]["exp_avg"])
         self.rest_exp_avg_sq.copy_(sd["rest"]["exp_avg_sq"])
         self._publish_rest()
-        self._resident = [None, None]
+        self._invalidate()
 
     def _publish_rest(self):
         sh = self.rest_flat[self.rest_lo:self.rest_hi]
@@ -332,9 +368,12 @@ class StreamShardEngine:
         """Loads a complete checkpoint (HF names): every layer is written into its slot and sliced at once."""
         from ..models.hf_io import load_hf_state_dict
 
+        self._invalidate()  # no gather may still be writing into a slot
+
         def reslice(i):
             ls = self.layers[i]
             per = ls.numel // self.world
+            self._wait_slot(ls.slot)
             ls.master.copy_(self.slots[ls.slot][self.rank * per:(self.rank + 1) * per])
             self._resident[ls.slot] = None
 
