@@ -234,3 +234,27 @@ def test_host_runtime_under_address_and_ub_sanitizers(tmp_path):
     r = subprocess.run([exe], capture_output=True, text=True, timeout=120,
                        env=dict(os.environ, ASAN_OPTIONS="detect_leaks=1:abort_on_error=0"))
     assert r.returncode == 0 and "SANITIZE_OK" in r.stdout, (r.stdout[-1000:], r.stderr[-3000:])
+
+
+def test_cli_launches_two_processes_with_a_context_parallel_profile(tmp_path):
+    """`trl sft --accelerate_config <yaml with cp_size: 2>`: two gloo ranks, the profile's sequence sharding reaches the
+    trainer, rank 0 saves the model."""
+    import subprocess
+    import sys
+
+    from trl_b200.cli.main import resolve_profile
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    prof = os.path.join(root, "examples", "accelerate_configs", "context_parallel_2gpu.yaml")
+    assert resolve_profile(prof)["parallelism_config"] == {"cp_size": 2}
+    assert resolve_profile(os.path.join(root, "examples", "accelerate_configs", "alst_ulysses_4gpu.yaml"))[
+        "parallelism_config"] == {"sp_size": 4}
+    out = tmp_path / "cp"
+    cmd = [sys.executable, "-m", "trl_b200.cli.main", "sft", "--model_name_or_path", "tiny-qwen2", "--dataset_name",
+           "synthetic:standard_language_modeling:16", "--max_steps", "2", "--output_dir", str(out), "--use_cpu",
+           "--save_strategy", "no", "--per_device_train_batch_size", "2", "--padding_free", "--report_to", "none",
+           "--accelerate_config", prof, "--main_process_port", "29671"]
+    env = dict(os.environ, PYTHONPATH=root, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=str(tmp_path))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert (out / "model.safetensors").exists()

@@ -40,6 +40,14 @@ def resolve_profile(name_or_path: str) -> dict:
             cfg["shard_mode"] = "full_shard"
         else:
             cfg["shard_mode"] = "ddp"
+    # sequence sharding: our own keys (sp_size / cp_size) or accelerate's parallelism_config_* keys
+    pc = dict(cfg.get("parallelism_config") or {})
+    for ours, theirs in (("sp_size", "parallelism_config_sp_size"), ("cp_size", "parallelism_config_cp_size")):
+        v = cfg.get(ours, cfg.get(theirs))
+        if v is not None and int(v) > 1:
+            pc[ours] = int(v)
+    if pc:
+        cfg["parallelism_config"] = pc
     return cfg
 
 
@@ -81,6 +89,10 @@ def run_training(name: str, argv: list[str]) -> int:
         nproc = min(nproc, torch.cuda.device_count())
     if "shard_mode" in prof and "--shard_mode" not in script_argv:
         script_argv += ["--shard_mode", prof["shard_mode"]]
+    if prof.get("parallelism_config") and "--parallelism_config" not in script_argv:
+        import json
+
+        script_argv += ["--parallelism_config", json.dumps(prof["parallelism_config"])]
     if nproc <= 1:
         script_args, training_args, model_args, dataset_args = parser.parse_args_and_config(script_argv)[:4]
         mod.main(script_args, training_args, model_args, dataset_args)
