@@ -1,0 +1,47 @@
+"""Every example script runs end to end in its offline smoke mode; the tiny-model generator writes loadable checkpoints."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SCRIPTS = os.path.join(ROOT, "examples", "scripts")
+
+
+def _run(args, tmp_path, timeout=600):
+    env = dict(os.environ, PYTHONPATH=ROOT, TRL_EXPERIMENTAL_SILENCE="1", OMP_NUM_THREADS="2")
+    r = subprocess.run([sys.executable] + args, env=env, cwd=SCRIPTS, capture_output=True, text=True, timeout=timeout)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-3000:]
+    return r.stdout
+
+
+@pytest.mark.parametrize("name", ["kto", "reward_modeling", "rloo", "sft_lora", "gkd", "dpo_vlm", "grpo_vlm"])
+def test_example_smoke(name, tmp_path):
+    out = _run([f"{name}.py", "--smoke", "--out", str(tmp_path / name)], tmp_path)
+    assert "train_runtime" in out
+    saved = os.listdir(tmp_path / name)
+    assert any(f.endswith(".safetensors") for f in saved), saved
+
+
+def test_sft_vlm_example_smoke(tmp_path):
+    out = _run(["sft_vlm.py", "--steps", "2", "--out", str(tmp_path / "v")], tmp_path)
+    assert "train_runtime" in out and os.path.exists(tmp_path / "v" / "preprocessor_config.json")
+
+
+def test_generate_tiny_models_are_loadable(tmp_path):
+    _run(["generate_tiny_models.py", "--out", str(tmp_path), "--families", "tiny-qwen2", "tiny-qwen3-moe",
+          "--reward-heads"], tmp_path)
+    import transformers as tf
+
+    from trl_b200.models.hf_io import load_model
+    from trl_b200.scripts.utils import load_processing_class
+
+    m = load_model(str(tmp_path / "tiny-qwen2"))
+    hf = tf.AutoModelForCausalLM.from_pretrained(str(tmp_path / "tiny-qwen2"))
+    assert sum(p.numel() for p in hf.parameters()) == sum(p.numel() for p in m.parameters())
+    assert load_model(str(tmp_path / "tiny-qwen2-reward")).config.num_labels == 1
+    assert load_model(str(tmp_path / "tiny-qwen3-moe")).config.is_moe
+    vlm = load_model(str(tmp_path / "tiny-llava"))
+    proc = load_processing_class(str(tmp_path / "tiny-llava"))
+    assert vlm.config.image_token_index == proc.image_token_id
