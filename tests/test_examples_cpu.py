@@ -16,7 +16,7 @@ def _run(args, tmp_path, timeout=600):
     return r.stdout
 
 
-@pytest.mark.parametrize("name", ["kto", "reward_modeling", "rloo", "sft_lora", "gkd", "dpo_vlm", "grpo_vlm"])
+@pytest.mark.parametrize("name", ["kto", "reward_modeling", "rloo", "sft_lora", "gkd", "dpo_vlm", "grpo_vlm", "cpo_simpo", "orpo", "prm"])
 def test_example_smoke(name, tmp_path):
     out = _run([f"{name}.py", "--smoke", "--out", str(tmp_path / name)], tmp_path)
     assert "train_runtime" in out

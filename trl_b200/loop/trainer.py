@@ -551,6 +551,8 @@ class Trainer:
             own.clear()
         if self.state.epoch is not None:
             logs["epoch"] = round(self.state.epoch, 4) if isinstance(self.state.epoch, float) else self.state.epoch
+        # metrics are averaged as tensors to avoid a device sync per micro-step; they leave the trainer as numbers
+        logs = {k: (float(v) if torch.is_tensor(v) and v.numel() == 1 else v) for k, v in logs.items()}
         self.state.log_history.append({**logs, "step": self.state.global_step})
         self.control = self.callback_handler.call_event("on_log", self.args, self.state, self.control, logs=logs)
 
