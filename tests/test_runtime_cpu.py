@@ -258,3 +258,36 @@ def test_cli_launches_two_processes_with_a_context_parallel_profile(tmp_path):
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=str(tmp_path))
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert (out / "model.safetensors").exists()
+
+
+def test_sigterm_saves_a_checkpoint_and_stops(tmp_path, tiny_tokenizer):
+    """enable_jit_checkpoint: SIGTERM during training -> checkpoint at the next step boundary, clean stop, resumable."""
+    import signal
+
+    from trl_b200.loop.state import TrainerCallback
+    from trl_b200.testing import make_dataset, make_tiny_model
+    from trl_b200.trainer.sft_config import SFTConfig
+    from trl_b200.trainer.sft_trainer import SFTTrainer
+
+    class Preempt(TrainerCallback):
+        def on_step_begin(self, args, state, control, **kw):
+            if state.global_step == 2:
+                os.kill(os.getpid(), signal.SIGTERM)
+
+    def make(max_steps):
+        return SFTTrainer(make_tiny_model(), SFTConfig(output_dir=str(tmp_path), per_device_train_batch_size=4,
+                                                       max_steps=max_steps, save_strategy="no", use_cpu=True,
+                                                       report_to="none", enable_jit_checkpoint=True, logging_steps=1),
+                          train_dataset=make_dataset("standard_language_modeling", 64), processing_class=tiny_tokenizer,
+                          callbacks=[Preempt()])
+
+    before = signal.getsignal(signal.SIGTERM)
+    tr = make(10)
+    tr.train()
+    assert tr.state.global_step == 3  # the step in flight finished, then the loop stopped
+    assert os.path.exists(tmp_path / "checkpoint-3" / "model.safetensors")
+    assert signal.getsignal(signal.SIGTERM) is before  # the handler was restored
+    tr2 = make(5)
+    tr2.callback_handler.callbacks = [c for c in tr2.callback_handler.callbacks if not isinstance(c, Preempt)]
+    tr2.train(resume_from_checkpoint=True)
+    assert tr2.state.global_step == 5

@@ -203,6 +203,10 @@ class Trainer:
                 cbs.append(_SINKS[r]())
         if not any(isinstance(c, PrinterCallback) for c in cbs) and self.args.disable_tqdm:
             cbs.append(PrinterCallback())
+        if self.args.enable_jit_checkpoint:
+            from ..trainer.callbacks import JITCheckpointCallback
+
+            cbs.append(JITCheckpointCallback())
         if self._watchdog_dir:
             from ..trainer.callbacks import WatchdogCallback
 

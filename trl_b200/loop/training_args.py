@@ -112,6 +112,10 @@ class TrainingArguments:
     project: str = "huggingface"
     trackio_space_id: Optional[str] = None
     skip_memory_metrics: bool = True
+    # save a checkpoint and stop at the next step boundary when the job receives SIGTERM (preemption)
+    enable_jit_checkpoint: bool = False
+    # accepted for configuration parity ("underflow_overflow" / "tpu_metrics_debug" in transformers); selects nothing
+    debug: Any = ""
     push_to_hub: bool = False
     resume_from_checkpoint: Optional[str] = None
     hub_model_id: Optional[str] = None

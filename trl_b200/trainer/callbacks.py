@@ -194,3 +194,49 @@ class WatchdogCallback(TrainerCallback):
         if self.watchdog is not None:
             self.watchdog.stop()
             self.watchdog = None
+
+
+class JITCheckpointCallback(TrainerCallback):
+    """Checkpoint on SIGTERM (``enable_jit_checkpoint=True``): a preempted job saves at the next optimizer-step
+    boundary and stops cleanly, so ``resume_from_checkpoint=True`` loses at most one step.  The signal may reach only
+    some ranks; every step the ranks agree on the flag with one tiny all-reduce, so that all of them take part in the
+    (collective) save.  Same purpose as transformers' ``enable_jit_checkpoint`` training argument."""
+
+    def __init__(self, signals=None):
+        import signal
+
+        self.signals = tuple(signals) if signals is not None else (signal.SIGTERM,)
+        self.requested = False
+        self._previous = {}
+
+    def _handler(self, signum, frame):
+        self.requested = True
+
+    def on_train_begin(self, args, state, control, **kw):
+        import signal
+        import threading
+
+        if threading.current_thread() is threading.main_thread():  # handlers can only be installed there
+            for s in self.signals:
+                self._previous[s] = signal.signal(s, self._handler)
+
+    def on_step_end(self, args, state, control, **kw):
+        import torch
+
+        from ..parallel import dist as D
+
+        flag = torch.tensor([1.0 if self.requested else 0.0], device=args.device)
+        if D.world_size() > 1:
+            D.all_reduce(flag, "max")
+        if float(flag) > 0:
+            control.should_save = True
+            control.should_training_stop = True
+            self.requested = False
+        return control
+
+    def on_train_end(self, args, state, control, **kw):
+        import signal
+
+        for s, h in self._previous.items():
+            signal.signal(s, h)
+        self._previous = {}
