@@ -291,3 +291,18 @@ def test_sigterm_saves_a_checkpoint_and_stops(tmp_path, tiny_tokenizer):
     tr2.callback_handler.callbacks = [c for c in tr2.callback_handler.callbacks if not isinstance(c, Preempt)]
     tr2.train(resume_from_checkpoint=True)
     assert tr2.state.global_step == 5
+
+
+def test_debug_underflow_overflow_stops_at_a_non_finite_loss(tmp_path, tiny_tokenizer):
+    from trl_b200.testing import make_dataset, make_tiny_model
+    from trl_b200.trainer.sft_config import SFTConfig
+    from trl_b200.trainer.sft_trainer import SFTTrainer
+
+    model = make_tiny_model()
+    tr = SFTTrainer(model, SFTConfig(output_dir=str(tmp_path), per_device_train_batch_size=4, max_steps=3, use_cpu=True,
+                                     save_strategy="no", report_to="none", debug="underflow_overflow"),
+                    train_dataset=make_dataset("standard_language_modeling", 16), processing_class=tiny_tokenizer)
+    with torch.no_grad():
+        model.norm.fill_(float("inf"))
+    with pytest.raises(FloatingPointError, match="optimizer step 1"):
+        tr.train()

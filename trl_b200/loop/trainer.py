@@ -504,7 +504,8 @@ class Trainer:
         total = torch.zeros((), device=a.device)
         for i, b in enumerate(batches):
             loss = self.training_step(self.model, b, n_items)
-            total += torch.nan_to_num(loss.float(), nan=0.0, posinf=0.0, neginf=0.0) if a.logging_nan_inf_filter else loss
+            keep_nan = not a.logging_nan_inf_filter or "underflow_overflow" in str(a.debug)
+            total += loss if keep_nan else torch.nan_to_num(loss.float(), nan=0.0, posinf=0.0, neginf=0.0)
             if i < len(batches) - 1:
                 self.control = self.callback_handler.call_event("on_substep_end", a, st, self.control)
         self.control = self.callback_handler.call_event("on_pre_optimizer_step", a, st, self.control)
@@ -513,6 +514,10 @@ class Trainer:
 
         with profiling_context(self, "optimizer"):
             grad_norm = self.engine.step(lr, a.max_grad_norm)
+        if "underflow_overflow" in str(a.debug):  # costs a device sync per step: a debugging aid, off by default
+            if not (bool(torch.isfinite(total)) and bool(torch.isfinite(torch.as_tensor(grad_norm)))):
+                raise FloatingPointError(f"non-finite loss ({float(total)}) or gradient norm ({float(grad_norm)}) at "
+                                         f"optimizer step {st.global_step + 1}")
         self.control = self.callback_handler.call_event("on_optimizer_step", a, st, self.control)
         self.lr_scheduler.step()
         self.engine.zero_grad()

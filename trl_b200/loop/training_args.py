@@ -114,7 +114,7 @@ class TrainingArguments:
     skip_memory_metrics: bool = True
     # save a checkpoint and stop at the next step boundary when the job receives SIGTERM (preemption)
     enable_jit_checkpoint: bool = False
-    # accepted for configuration parity ("underflow_overflow" / "tpu_metrics_debug" in transformers); selects nothing
+    # "underflow_overflow": stop with an error at the first non-finite loss or gradient norm (one device sync per step)
     debug: Any = ""
     push_to_hub: bool = False
     resume_from_checkpoint: Optional[str] = None
