@@ -82,6 +82,10 @@ def test_adamw_flat_matches_reference(gdtype):
     assert torch.allclose(shadow.float(), pr, atol=1e-2, rtol=1e-2)
     ss = K.sumsq(grad)
     assert torch.allclose(ss[0], grad.float().pow(2).sum(), rtol=1e-3)
+    # views that start one element into their buffers are not 16-byte aligned: the scalar kernel takes them
+    K.adamw_flat(master[1:], grad[1:], m[1:], v[1:], 4, 1e-3, 0.9, 0.999, 1e-8, 0.01, scale, shadow[1:])
+    adamw_reference(pr[1:], grad[1:], mr[1:], vr[1:], 4, 1e-3, 0.9, 0.999, 1e-8, 0.01, 0.5)
+    assert torch.allclose(master, pr, atol=1e-5, rtol=1e-5) and torch.allclose(m, mr, atol=1e-6)
 
 
 @pytest.mark.parametrize("T,H", [(64, 3584), (5, 8192), (1000, 2048)])

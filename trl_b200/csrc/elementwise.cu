@@ -469,6 +469,56 @@ __global__ void adamw_kernel(float* __restrict__ master, const GradT* __restrict
   }
 }
 
+// Same update, four elements per thread and iteration through 16-byte loads / stores (8 bytes for bf16 operands):
+// the scalar kernel keeps only four 4-byte loads in flight per thread and reached 0.69 of the copy bandwidth; the
+// host picks this one when every pointer is 16-byte aligned (the tail of n % 4 elements goes to the scalar kernel).
+template <typename GradT>
+__global__ void __launch_bounds__(256)
+adamw_vec4_kernel(float* __restrict__ master, const GradT* __restrict__ grad, float* __restrict__ m,
+                  float* __restrict__ v, __nv_bfloat16* __restrict__ shadow, long long n4, float lr, float b1, float b2,
+                  float eps, float wd, float bc1, float bc2_sqrt, float grad_scale,
+                  const float* __restrict__ grad_scale_ptr) {
+  const float gs = grad_scale_ptr ? grad_scale * (*grad_scale_ptr) : grad_scale;
+  const float step = lr / bc1, decay = 1.f - lr * wd;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float g[4];
+    if constexpr (sizeof(GradT) == 2) {
+      const uint2 raw = reinterpret_cast<const uint2*>(grad)[i];
+      const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+      const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+      g[0] = __low2float(lo); g[1] = __high2float(lo); g[2] = __low2float(hi); g[3] = __high2float(hi);
+    } else {
+      const float4 r = reinterpret_cast<const float4*>(grad)[i];
+      g[0] = r.x; g[1] = r.y; g[2] = r.z; g[3] = r.w;
+    }
+    float4 m4 = reinterpret_cast<const float4*>(m)[i];
+    float4 v4 = reinterpret_cast<const float4*>(v)[i];
+    float4 p4 = reinterpret_cast<const float4*>(master)[i];
+    float* mm = reinterpret_cast<float*>(&m4);
+    float* vv = reinterpret_cast<float*>(&v4);
+    float* pp = reinterpret_cast<float*>(&p4);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float gj = g[j] * gs;
+      mm[j] = mm[j] * b1 + (1.f - b1) * gj;
+      vv[j] = vv[j] * b2 + (1.f - b2) * gj * gj;
+      float pj = pp[j] * decay;
+      pj -= step * mm[j] / (sqrtf(vv[j]) / bc2_sqrt + eps);
+      pp[j] = pj;
+    }
+    reinterpret_cast<float4*>(m)[i] = m4;
+    reinterpret_cast<float4*>(v)[i] = v4;
+    reinterpret_cast<float4*>(master)[i] = p4;
+    if (shadow) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(pp[0], pp[1]), hi = __floats2bfloat162_rn(pp[2], pp[3]);
+      uint2 o;
+      o.x = *reinterpret_cast<uint32_t*>(&lo);
+      o.y = *reinterpret_cast<uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(shadow)[i] = o;
+    }
+  }
+}
+
 // sum of squares of a flat gradient buffer -> out[0] (atomic accumulate; zero it first)
 template <typename T>
 __global__ void sumsq_kernel(const T* __restrict__ x, long long n, float* __restrict__ out) {
@@ -639,13 +689,32 @@ TRLB_API int trlb_adamw(float* master, const void* grad, int grad_is_bf16, float
   if (n == 0) return 0;
   const float bc1 = 1.f - powf(b1, (float)step);
   const float bc2s = sqrtf(1.f - powf(b2, (float)step));
-  const int grid = grid_for(n, 256, 16);
-  if (grad_is_bf16)
-    adamw_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(master, (const __nv_bfloat16*)grad, m, v, (__nv_bfloat16*)shadow,
-                                                     n, lr, b1, b2, eps, wd, bc1, bc2s, grad_scale, grad_scale_ptr);
-  else
-    adamw_kernel<float><<<grid, 256, 0, st>>>(master, (const float*)grad, m, v, (__nv_bfloat16*)shadow, n, lr, b1, b2,
-                                              eps, wd, bc1, bc2s, grad_scale, grad_scale_ptr);
+  const auto misaligned = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; };
+  const bool vec = n >= 4 && !misaligned(master, 16) && !misaligned(m, 16) && !misaligned(v, 16) &&
+                   !misaligned(grad, grad_is_bf16 ? 8 : 16) && (!shadow || !misaligned(shadow, 8));
+  const long long n4 = vec ? n / 4 : 0, done = n4 * 4;
+  if (n4 > 0) {
+    const int grid = grid_for(n4, 256, 8);
+    if (grad_is_bf16)
+      adamw_vec4_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(master, (const __nv_bfloat16*)grad, m, v,
+                                                            (__nv_bfloat16*)shadow, n4, lr, b1, b2, eps, wd, bc1, bc2s,
+                                                            grad_scale, grad_scale_ptr);
+    else
+      adamw_vec4_kernel<float><<<grid, 256, 0, st>>>(master, (const float*)grad, m, v, (__nv_bfloat16*)shadow, n4, lr, b1,
+                                                    b2, eps, wd, bc1, bc2s, grad_scale, grad_scale_ptr);
+  }
+  if (done < n) {  // unaligned buffers, or the last n % 4 elements
+    const long long r = n - done;
+    const int grid = grid_for(r, 256, 16);
+    __nv_bfloat16* sh = shadow ? (__nv_bfloat16*)shadow + done : nullptr;
+    if (grad_is_bf16)
+      adamw_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(master + done, (const __nv_bfloat16*)grad + done, m + done,
+                                                       v + done, sh, r, lr, b1, b2, eps, wd, bc1, bc2s, grad_scale,
+                                                       grad_scale_ptr);
+    else
+      adamw_kernel<float><<<grid, 256, 0, st>>>(master + done, (const float*)grad + done, m + done, v + done, sh, r, lr,
+                                                b1, b2, eps, wd, bc1, bc2s, grad_scale, grad_scale_ptr);
+  }
   return (int)cudaGetLastError();
 }
 
