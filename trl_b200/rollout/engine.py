@@ -398,13 +398,15 @@ class RolloutEngine:
                 own_px = None if images is None else [images[reqs[rid][1]] for rid, slot, pre, _ in admitted if pre]
                 last_h = self._prefill(owners, own_px) if owners else None
                 # sharers: copy the partial tail block of the prompt from the group's owner
-                for rid, slot, pre, copy_blk in admitted:
-                    plen = len(reqs[rid][0])
-                    if not pre and copy_blk >= 0:
-                        dst = int(bt_np[slot, plen // self.block_size])
-                        for li in range(self.cfg.num_hidden_layers):
-                            self.k_cache[li][dst].copy_(self.k_cache[li][copy_blk])
-                            self.v_cache[li][dst].copy_(self.v_cache[li][copy_blk])
+                # (all sharers of the batch at once: two gathers + scatters per layer instead of two copies per sharer)
+                pairs = [(int(bt_np[slot, len(reqs[rid][0]) // self.block_size]), copy_blk)
+                         for rid, slot, pre, copy_blk in admitted if not pre and copy_blk >= 0]
+                if pairs:
+                    dst_t = torch.tensor([p[0] for p in pairs], dtype=torch.long, device=dev)
+                    src_t = torch.tensor([p[1] for p in pairs], dtype=torch.long, device=dev)
+                    for li in range(self.cfg.num_hidden_layers):
+                        self.k_cache[li].index_copy_(0, dst_t, self.k_cache[li].index_select(0, src_t))
+                        self.v_cache[li].index_copy_(0, dst_t, self.v_cache[li].index_select(0, src_t))
                 slots = torch.tensor([a[1] for a in admitted], dtype=torch.int32, device=dev)
                 plen_t = torch.tensor([len(reqs[a[0]][0]) for a in admitted], dtype=torch.int32, device=dev)
                 self.seq_lens[slots.long()] = plen_t
