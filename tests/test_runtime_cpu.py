@@ -306,3 +306,27 @@ def test_debug_underflow_overflow_stops_at_a_non_finite_loss(tmp_path, tiny_toke
         model.norm.fill_(float("inf"))
     with pytest.raises(FloatingPointError, match="optimizer step 1"):
         tr.train()
+
+
+def test_phase_timers_are_written_as_a_chrome_trace(tmp_path, tiny_tokenizer, monkeypatch):
+    import json
+
+    from trl_b200.extras import profiling
+    from trl_b200.testing import make_dataset, make_tiny_model
+    from trl_b200.trainer.grpo_config import GRPOConfig
+    from trl_b200.trainer.grpo_trainer import GRPOTrainer
+
+    trace = tmp_path / "trace.json"
+    monkeypatch.setattr(profiling, "TRACE_PATH", str(trace))
+    profiling._TRACE.clear()
+    tr = GRPOTrainer(make_tiny_model(), lambda completion_ids, **kw: [float(len(c)) for c in completion_ids],
+                     GRPOConfig(output_dir=str(tmp_path), per_device_train_batch_size=4, num_generations=4, max_steps=2,
+                                max_completion_length=4, use_cpu=True, save_strategy="no", report_to="none", beta=0.04),
+                     train_dataset=make_dataset("standard_prompt_only", 8), processing_class=tiny_tokenizer)
+    tr.train()
+    ev = json.load(open(trace))["traceEvents"]
+    names = {e["name"] for e in ev}
+    assert {"GRPOTrainer.rollout.generate", "GRPOTrainer.ref_logps", "GRPOTrainer.optimizer"} <= names
+    assert all(e["ph"] == "X" and e["dur"] >= 0 and e["ts"] > 0 for e in ev)
+    gen = [e for e in ev if e["name"] == "GRPOTrainer.rollout.generate"]
+    assert len(gen) == 2  # one generation per optimizer step

@@ -491,6 +491,10 @@ class Trainer:
                    "train_loss": train_loss, "epoch": st.epoch}
         self.log(metrics)
         self.control = self.callback_handler.call_event("on_train_end", a, st, self.control)
+        from ..extras import profiling
+
+        if profiling.TRACE_PATH:  # TRL_B200_TRACE=<file>: Chrome trace of the phase timers, one file per rank
+            profiling.dump_trace(rank=D.rank())
         self.is_in_train = False
         return TrainOutput(st.global_step, train_loss, metrics)
 
@@ -554,6 +558,14 @@ class Trainer:
         own = self._metrics[mode]
         if own:
             avg = {k: sum(v) / len(v) for k, v in own.items() if len(v)}
+            if D.world_size() > 1 and os.environ.get("TRL_B200_PROFILE_MAX_OVER_RANKS", "0") == "1":
+                # a phase is as slow as its slowest rank: report the maximum of the phase timers (one small object
+                # gather per log call; every rank logs at the same steps)
+                prof = {k: float(v) for k, v in avg.items() if k.startswith("profiling/")}
+                for other in D.gather_object([prof]):
+                    for k, v in other.items():
+                        if k in avg:
+                            avg[k] = max(float(avg[k]), v)
             if mode == "eval":
                 avg = {f"eval_{k}": v for k, v in avg.items()}
             logs = {**logs, **avg}
