@@ -2,7 +2,7 @@
 :324-400, losses :402-425).
 
 The opponent is sampled from the geometric mixture  softmax(c * z_ref + (1 - c) * z_policy).  With P = the
-probability that the policy's sample is preferred (sigmoid of the score difference, or the judge's probability),
+probability that the policy's sample is preferred (sigmoid of the score difference, or a pairwise judge model's probability),
 loss = beta * sum_t (log pi - log pi_ref)_sg * log pi  -  (P - 1/2) * sum_t log pi   on the policy's own sample."""
 from __future__ import annotations
 
