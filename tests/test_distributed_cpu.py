@@ -62,3 +62,24 @@ def test_streamed_full_shard_saves_and_resumes_like_ddp(tmp_path):
     for k in ref:
         assert torch.allclose(ref[k], a[k], atol=2e-5), (k, (ref[k] - a[k]).abs().max())
         assert torch.allclose(a[k], b[k], atol=1e-6), (k, (a[k] - b[k]).abs().max())
+
+
+@pytest.mark.parametrize("kind,port", [("dense", 29618), ("moe", 29620)])
+def test_grpo_with_streamed_shards_matches_zero2(tmp_path, kind, port):
+    """Online RL on sharded weights: the generation replica refreshed from the slices must give the same samples, rewards
+    and updates as generation from the policy in place."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
+    res = {}
+    for j, mode in enumerate(("zero2", "full_shard_stream")):
+        out = str(tmp_path / f"{mode}.json")
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+               "127.0.0.1", "--master-port", str(port + j), os.path.join(HERE, "dist_worker_grpo_stream.py"), out, mode, kind]
+        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+        with open(out) as f:
+            res[mode] = json.load(f)
+    a, b = res["zero2"], res["full_shard_stream"]
+    assert len(a) == len(b) == 3
+    for x, y in zip(a, b):
+        assert x["reward"] == y["reward"], (a, b)  # same samples
+        assert abs(x["loss"] - y["loss"]) < 2e-4 and abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, x["grad_norm"]), (a, b)

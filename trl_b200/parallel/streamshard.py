@@ -382,6 +382,23 @@ class StreamShardEngine:
         self.refresh_master_from_params()
 
     @torch.no_grad()
+    def export_weights(self, target: nn.Module):
+        """Writes the current weights into ``target``, a whole copy of the same architecture (the generation replica
+        of the online trainers): layer by layer through the slots (collective), the parameters outside the layers
+        directly.  What the reference does with ``ds3_gather_for_generation`` (trl/models/utils.py
+        ``unwrap_model_for_generation``), without ever holding a second full copy on the training side."""
+        t_layers = getattr(target, "layers")
+        for ls in self.layers:
+            self.materialize(ls.idx)
+            tgt = dict(t_layers[ls.idx].named_parameters())
+            for n, p in zip(ls.names, ls.params):
+                tgt[n].data.copy_(p.data)
+        named = dict(target.named_parameters())
+        for n, p in zip(self.rest_names, self.rest_params):
+            if n in named and named[n].data_ptr() != p.data_ptr():
+                named[n].data.copy_(p.data)
+
+    @torch.no_grad()
     def streamed_hf_state_dict(self, to_cpu: bool = True) -> dict:
         """Complete checkpoint tensors, built one layer at a time (collective).  With ``to_cpu`` every layer is copied
         to host memory before its slot is reused; ranks that do not save pass False and get an empty dict."""

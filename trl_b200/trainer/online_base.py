@@ -190,9 +190,16 @@ class OnlineTrainer(Trainer):
                               **(a.generation_kwargs or {}))
 
     def _get_rollout(self):
+        gen_model = self.model
         if getattr(getattr(self, "engine", None), "mode", "") == "full_shard_stream":
-            raise NotImplementedError("generation reads whole weights; shard_mode='full_shard_stream' holds one layer "
-                                      "at a time - use full_shard or zero2 for online trainers")
+            # the training side holds one layer at a time: generation gets its own whole replica, refreshed from the
+            # slices before every generation batch (`export_weights`)
+            if getattr(self.model, "is_vlm", False):
+                raise NotImplementedError("streamed full shard with a vision-language generation replica")
+            if getattr(self, "_gen_model", None) is None:
+                self._gen_model = CausalLM(self.model.config, dtype=self.model.dtype, device=self.args.device, init=False)
+                self._gen_model.eval().requires_grad_(False)
+            gen_model = self._gen_model
         if self._rollout is None:
             if self.args.device.type == "cuda":
                 from ..rollout.engine import RolloutEngine
@@ -210,11 +217,11 @@ class OnlineTrainer(Trainer):
                         raise ValueError(f"vllm_tensor_parallel_size ({tp}) must divide the world size ({D.world_size()})")
                     groups = [list(range(i, i + tp)) for i in range(0, D.world_size(), tp)]
                     self._tp_group = D.new_subgroups_by_enumeration(groups)
-                    self._rollout = TPRolloutEngine(self.model, self._tp_group, max_num_seqs=nseq, max_model_len=max_len,
+                    self._rollout = TPRolloutEngine(gen_model, self._tp_group, max_num_seqs=nseq, max_model_len=max_len,
                                                     block_size=bs, poll_every=a.rollout_poll_every)
                 else:
                     try:
-                        self._rollout = RolloutEngine(self.model, max_num_seqs=nseq, max_model_len=max_len, block_size=bs,
+                        self._rollout = RolloutEngine(gen_model, max_num_seqs=nseq, max_model_len=max_len, block_size=bs,
                                                       poll_every=a.rollout_poll_every)
                     except NotImplementedError as e:  # e.g. GeGLU models: correct but slow eager generation
                         import warnings
@@ -222,11 +229,11 @@ class OnlineTrainer(Trainer):
                         from ..rollout.engine import EagerGenerator
 
                         warnings.warn(f"{e}; falling back to the eager generator")
-                        self._rollout = EagerGenerator(self.model)
+                        self._rollout = EagerGenerator(gen_model)
             else:
                 from ..rollout.engine import EagerGenerator
 
-                self._rollout = EagerGenerator(self.model)
+                self._rollout = EagerGenerator(gen_model)
         return self._rollout
 
     def _tokenize_prompts_with_images(self, prompts: list, images: list):
@@ -301,7 +308,13 @@ class OnlineTrainer(Trainer):
                 counts.append(1)
         gen_kw = {"images": uniq_px} if pixels is not None else {}
         eng = self._get_rollout()
-        if self.state.global_step != self._last_loaded_step and hasattr(eng, "sync_weights"):
+        if self.state.global_step != self._last_loaded_step and getattr(self, "_gen_model", None) is not None:
+            with self._profile("sync_weights"):  # slices of the streamed engine -> the whole generation replica
+                self.engine.export_weights(self._gen_model)
+                if hasattr(eng, "sync_weights"):
+                    eng.sync_weights()
+            self._last_loaded_step = self.state.global_step
+        elif self.state.global_step != self._last_loaded_step and hasattr(eng, "sync_weights"):
             with self._profile("sync_weights"):  # trainer -> generator weights (no-op when storage is shared)
                 sharded = getattr(self, "engine", None) is not None and hasattr(self.engine, "gather_full_params")
                 if sharded and hasattr(eng, "w") and getattr(eng, "tp", 1) > 1:
