@@ -28,6 +28,9 @@ def main():
     tr = GRPOTrainer(model, reward, args, train_dataset=make_dataset("standard_prompt_only", 16),
                      processing_class=make_tiny_tokenizer())
     tr.train()
+    if mode == "full_shard_stream":  # policy slices, a whole generation replica, and a sliced frozen reference
+        assert tr._gen_model is not None and tr._ref_stream is not None and tr._ref_stream.frozen
+        assert all(l.master.numel() == l.numel // 2 for l in tr._ref_stream.layers)
     if D.is_main():
         hist = [{k: h[k] for k in ("loss", "grad_norm", "reward", "kl")} for h in tr.state.log_history if "reward" in h]
         with open(out, "w") as f:

@@ -52,3 +52,17 @@ def test_backward_refuses_to_run_without_checkpointing():
     e = StreamShardEngine(m)
     with pytest.raises(RuntimeError, match="checkpointing"):
         e.backward(_loss(m))
+
+
+def test_frozen_mode_streams_a_reference_model_without_optimizer_state():
+    import copy
+
+    torch.manual_seed(0)
+    m = CausalLM(preset("tiny-qwen2", num_hidden_layers=3)).eval().requires_grad_(False)
+    whole = copy.deepcopy(m)
+    e = StreamShardEngine(m, frozen=True)
+    assert e.gbuf is None and all(l.exp_avg is None for l in e.layers)
+    with torch.no_grad():
+        a, b = _loss(m, 3), _loss(whole, 3)
+        c = _loss(m, 4)  # a second pass re-gathers the layers that were overwritten in their slots
+    assert torch.allclose(a, b, atol=1e-6) and torch.allclose(c, _loss(whole, 4), atol=1e-6)

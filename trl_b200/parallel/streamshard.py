@@ -75,12 +75,15 @@ class StreamShardEngine:
     mode = "full_shard_stream"
 
     def __init__(self, model: nn.Module, *, betas=(0.9, 0.999), eps=1e-8, weight_decay: float = 0.0, group=None,
-                 device=None, init_seed: int = 0, init_std: float = 0.02, grad_dtype: torch.dtype | None = None, prefetch: bool = True):
+                 device=None, init_seed: int = 0, init_std: float = 0.02, grad_dtype: torch.dtype | None = None, prefetch: bool = True,
+                 frozen: bool = False):
         """``model`` may live on the meta device (``CausalLM(cfg, device="meta")``): then ``device`` names where the
         slices go and every layer is initialised inside its slot with a generator seeded by (``init_seed``, layer), so
         that all ranks draw the same weights and the whole model never exists anywhere (load real weights afterwards
-        with ``load_weights``)."""
-        self.model, self.group = model, group
+        with ``load_weights``).  ``frozen=True`` shards a model that is only evaluated (a reference model): every
+        parameter is streamed, a slice is kept in the model's own dtype (2 bytes / parameter / world for bf16) and there
+        is no optimizer state, no gradient buffer and no gradient hook."""
+        self.model, self.group, self.frozen = model, group, frozen
         self.world = td.get_world_size(group) if td.is_initialized() else 1
         self.rank = td.get_rank(group) if td.is_initialized() else 0
         self.betas, self.eps, self.weight_decay = betas, eps, weight_decay
@@ -100,7 +103,7 @@ class StreamShardEngine:
         self.layers: list[_LayerShard] = []
         in_layers = set()
         for i, mod in enumerate(layers):
-            items = [(n, p) for n, p in mod.named_parameters() if p.requires_grad]
+            items = [(n, p) for n, p in mod.named_parameters() if p.requires_grad or frozen]
             if any(p.dtype != self.dtype for _, p in items):
                 raise ValueError("all parameters of a streamed layer must share one dtype")
             offs, cur = [], 0
@@ -115,7 +118,7 @@ class StreamShardEngine:
         slot_numel = max(l.numel for l in self.layers)
         # separate allocations: autograd tracks in-place writes per base tensor
         self.slots = [torch.zeros(slot_numel, dtype=self.dtype, device=self.dev) for _ in range(2)]
-        self.gbuf = torch.zeros(slot_numel, dtype=self.dtype, device=self.dev)
+        self.gbuf = None if frozen else torch.zeros(slot_numel, dtype=self.dtype, device=self.dev)
         self._resident = [None, None]  # layer index whose gathered weights a slot holds (or is receiving), or None
         self._inflight = [None, None]  # per slot: (layer, async work handle, send buffer) of a gather not yet waited for
         self._last_idx = None
@@ -134,11 +137,20 @@ class StreamShardEngine:
                 for p, v in zip(ls.params, views):
                     v.copy_(p.data)   # layers two apart share the slot: the slice is taken right below
                     p.data = v        # the original storage is released here
+            if frozen:
+                ls.master = slot[lo:lo + per].clone()  # the slice in the model's dtype is all a frozen model needs
+                continue
             ls.master = slot[lo:lo + per].to(torch.float32, copy=True)  # fp32 owned slice; the compute-dtype copy is made when gathering
             ls.exp_avg = torch.zeros(per, dtype=torch.float32, device=self.dev)
             ls.exp_avg_sq = torch.zeros(per, dtype=torch.float32, device=self.dev)
             ls.grad_acc = torch.zeros(per, dtype=self.grad_dtype, device=self.dev)
         # ---- everything outside the layers: whole on every rank, zero-2 style state ----
+        if frozen:  # embeddings / norm / lm_head of a frozen model stay as they are
+            self.rest_names, self.rest_params, self.rest_offsets, self.rest_numel = [], [], [], 0
+            self._hooks = [l.module.register_forward_pre_hook(lambda mod, args, i=l.idx: self.materialize(i))
+                           for l in self.layers]
+            self._pending = None
+            return
         rest = [(n, p) for n, p in model.named_parameters() if p.requires_grad and id(p) not in in_layers
                 and not any(p is q for l in self.layers for q in l.params)]
         seen, uniq = set(), []

@@ -451,6 +451,13 @@ class OnlineTrainer(Trainer):
 
     def _ref_logps(self, prompt_ids, completion_ids, batch_size, pixel_values_list=None):
         kw = {"pixel_values_list": pixel_values_list}
+        if (self.ref_model is not None and getattr(self, "_ref_stream", None) is None
+                and getattr(getattr(self, "engine", None), "mode", "") == "full_shard_stream"):
+            # the policy is trained on streamed slices because the whole model is too large to keep around: the frozen
+            # reference gets the same treatment (one slice per layer and rank, layers gathered as the forward reaches them)
+            from ..parallel.streamshard import StreamShardEngine
+
+            self._ref_stream = StreamShardEngine(self.ref_model, frozen=True)
         with torch.no_grad():
             if self.ref_model is not None:
                 return self._get_per_token_logps_and_entropies(self.ref_model, prompt_ids, completion_ids, batch_size,
