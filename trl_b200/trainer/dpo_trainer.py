@@ -324,6 +324,12 @@ class DPOTrainer(Trainer):
         if "ref_chosen_logps" in inputs:
             rc, rr = inputs["ref_chosen_logps"].to(pc), inputs["ref_rejected_logps"].to(pc)
         else:
+            if (self.ref_model is not None and getattr(self, "_ref_stream", None) is None
+                    and getattr(getattr(self, "engine", None), "mode", "") == "full_shard_stream"):
+                # streamed policy => streamed frozen reference (one slice per layer and rank, no optimizer state)
+                from ..parallel.streamshard import StreamShardEngine
+
+                self._ref_stream = StreamShardEngine(self.ref_model, frozen=True)
             with torch.no_grad():
                 ref = self.ref_model if self.ref_model is not None else model
                 rlp, _, rex = self._sequence_logps(ref, inputs, no_grad=True, adapter_off=self._ref_adapter_off)
