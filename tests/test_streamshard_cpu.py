@@ -66,3 +66,16 @@ def test_frozen_mode_streams_a_reference_model_without_optimizer_state():
         a, b = _loss(m, 3), _loss(whole, 3)
         c = _loss(m, 4)  # a second pass re-gathers the layers that were overwritten in their slots
     assert torch.allclose(a, b, atol=1e-6) and torch.allclose(c, _loss(whole, 4), atol=1e-6)
+
+
+def test_frozen_meta_copy_starts_equal_to_the_policy():
+    """A policy and its frozen reference, both built from meta models with the same seed, hold the same weights."""
+    cfg = preset("tiny-qwen2", num_hidden_layers=2)
+    pol = CausalLM(cfg, device="meta")
+    pol.gradient_checkpointing_enable()
+    ref = CausalLM(cfg, device="meta").eval().requires_grad_(False)
+    StreamShardEngine(pol, device="cpu", init_seed=5)
+    StreamShardEngine(ref, device="cpu", init_seed=5, frozen=True)
+    assert not any(p.is_meta for p in ref.parameters()) and not any(p.requires_grad for p in ref.parameters())
+    with torch.no_grad():
+        assert torch.allclose(_loss(pol.eval(), 1), _loss(ref, 1), atol=1e-6)

@@ -47,13 +47,13 @@ class _LayerShard:
         self.no_decay = []  # (lo, hi) ranges of 1-D parameters inside the flat layout
 
 
-def _rebind(root: nn.Module, dotted: str, value: torch.Tensor) -> nn.Parameter:
+def _rebind(root: nn.Module, dotted: str, value: torch.Tensor, requires_grad: bool = True) -> nn.Parameter:
     """Replaces the (meta) parameter ``root.<dotted>`` by a parameter over ``value``."""
     *path, leaf = dotted.split(".")
     mod = root
     for part in path:
         mod = getattr(mod, part)
-    p = nn.Parameter(value, requires_grad=True)
+    p = nn.Parameter(value, requires_grad=requires_grad)
     mod._parameters[leaf] = p
     return p
 
@@ -130,7 +130,7 @@ class StreamShardEngine:
             views = [slot[o:o + p.numel()].view(p.shape) for p, o in zip(ls.params, ls.offsets)]
             if meta:
                 gen = torch.Generator(device=self.dev).manual_seed(init_seed * 1000003 + ls.idx + 1)
-                ls.params = [_rebind(ls.module, n, v) for n, v in zip(ls.names, views)]
+                ls.params = [_rebind(ls.module, n, v, not frozen) for n, v in zip(ls.names, views)]
                 for n, v in zip(ls.names, views):
                     _init_param(n, v, init_std, gen)
             else:
@@ -145,7 +145,18 @@ class StreamShardEngine:
             ls.exp_avg_sq = torch.zeros(per, dtype=torch.float32, device=self.dev)
             ls.grad_acc = torch.zeros(per, dtype=self.grad_dtype, device=self.dev)
         # ---- everything outside the layers: whole on every rank, zero-2 style state ----
-        if frozen:  # embeddings / norm / lm_head of a frozen model stay as they are
+        if frozen:  # embeddings / norm / lm_head of a frozen model stay as they are (whole, own storage)
+            if meta:  # same generator and order as the trainable path below: a frozen copy starts equal to the policy
+                gen = torch.Generator(device=self.dev).manual_seed(init_seed * 1000003)
+                layer_params = {id(q) for l in self.layers for q in l.params}
+                seen = set()
+                for n, p in list(model.named_parameters()):
+                    if id(p) in layer_params or id(p) in seen or not p.is_meta:
+                        continue
+                    seen.add(id(p))
+                    v = torch.empty(p.shape, dtype=p.dtype, device=self.dev)
+                    _init_param(n, v, init_std, gen)
+                    _rebind(model, n, v, False)
             self.rest_names, self.rest_params, self.rest_offsets, self.rest_numel = [], [], [], 0
             self._hooks = [l.module.register_forward_pre_hook(lambda mod, args, i=l.idx: self.materialize(i))
                            for l in self.layers]

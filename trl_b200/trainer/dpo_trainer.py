@@ -329,7 +329,8 @@ class DPOTrainer(Trainer):
                 # streamed policy => streamed frozen reference (one slice per layer and rank, no optimizer state)
                 from ..parallel.streamshard import StreamShardEngine
 
-                self._ref_stream = StreamShardEngine(self.ref_model, frozen=True)
+                self._ref_stream = StreamShardEngine(self.ref_model, frozen=True, device=self.args.device,
+                                                    init_seed=self.args.seed)
             with torch.no_grad():
                 ref = self.ref_model if self.ref_model is not None else model
                 rlp, _, rex = self._sequence_logps(ref, inputs, no_grad=True, adapter_off=self._ref_adapter_off)

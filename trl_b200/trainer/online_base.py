@@ -457,7 +457,8 @@ class OnlineTrainer(Trainer):
             # reference gets the same treatment (one slice per layer and rank, layers gathered as the forward reaches them)
             from ..parallel.streamshard import StreamShardEngine
 
-            self._ref_stream = StreamShardEngine(self.ref_model, frozen=True)
+            self._ref_stream = StreamShardEngine(self.ref_model, frozen=True, device=self.args.device,
+                                                    init_seed=self.args.seed)
         with torch.no_grad():
             if self.ref_model is not None:
                 return self._get_per_token_logps_and_entropies(self.ref_model, prompt_ids, completion_ids, batch_size,
