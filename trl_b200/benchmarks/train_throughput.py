@@ -46,6 +46,8 @@ def main():
     ap.add_argument("--model", default="llama-3-8b")
     ap.add_argument("--shard", default=None, help="ddp | zero2 | full_shard | full_shard_stream (default: full_shard when "
                                                   "world > 1)")
+    ap.add_argument("--activation-offloading", action="store_true",
+                    help="SFT: keep the checkpointed layer inputs in pinned host memory between forward and backward")
     ap.add_argument("--meta-init", action="store_true",
                     help="with full_shard_stream: build the model on the meta device and initialise every layer inside "
                          "the engine's slots, so the whole model never exists on one GPU (Llama-3-70B)")
@@ -106,7 +108,7 @@ def main():
             ids = torch.randint(2, cfg.vocab_size, (a.tokens_per_gpu,), generator=g).tolist()
             rows.append({"input_ids": ids, "seq_lengths": docs})
         args = SFTConfig(per_device_train_batch_size=1, learning_rate=1e-5, max_length=a.tokens_per_gpu, packing=False,
-                         padding_free=True, **common)
+                         padding_free=True, activation_offloading=a.activation_offloading, **common)
         trainer = SFTTrainer(model, args, train_dataset=rows, processing_class=tok)
         metric = "sft_train_tokens_per_s"
     trainer.callback_handler.callbacks = [c for c in trainer.callback_handler.callbacks if type(c).__name__ != "PrinterCallback"]
