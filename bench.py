@@ -53,6 +53,11 @@ def parse():
                          "8.0 s): next to the symmetric arenas, both weight copies and the KV cache the kept "
                          "activations push the caching allocator into free-and-retry cycles; an out-of-memory warm-up "
                          "step switches it back on")
+    ap.add_argument("--shard", default=None,
+                    help="engine shard mode (default: zero2 with more than one GPU, else ddp); full_shard_stream holds "
+                         "1 / N of every layer per GPU for models whose training state does not fit otherwise")
+    ap.add_argument("--meta-init", action="store_true",
+                    help="with --shard full_shard_stream: build the policy on the meta device (initialised slice by slice)")
     ap.add_argument("--ckpt-layers", type=int, default=None,
                     help="with checkpointing on: recompute only the first n layers, keep the activations of the rest")
     return ap.parse_args()
@@ -158,7 +163,9 @@ def main():
     torch.manual_seed(1234)  # same weights on every rank
     overrides = {"num_hidden_layers": a.layers} if a.layers else {}
     cfg = preset(a.model, eos_token_id=1, pad_token_id=0, **overrides)
-    model = CausalLM(cfg, dtype=torch.bfloat16, device=dev)
+    if a.meta_init and a.shard != "full_shard_stream":
+        raise SystemExit("--meta-init needs --shard full_shard_stream")
+    model = CausalLM(cfg, dtype=torch.bfloat16, device="meta" if a.meta_init else dev)
     tok = SyntheticTokenizer(cfg.vocab_size)
     g = torch.Generator().manual_seed(99)
     n_prompts = a.prompts_per_gpu * world * (a.steps + a.warmup + a.steps + 2)
@@ -173,7 +180,7 @@ def main():
                       num_generations=a.num_generations, max_completion_length=a.max_new, temperature=1.0, beta=0.04,
                       epsilon=0.2, learning_rate=1e-6, max_steps=a.steps, logging_steps=1, save_strategy="no",
                       bf16=True, use_vllm=True, vllm_mode="colocate", eos_prob_floor=1.0 / 512, shuffle_dataset=False,
-                      shard_mode="zero2" if world > 1 else "ddp", report_to="none", seed=7,
+                      shard_mode=a.shard or ("zero2" if world > 1 else "ddp"), report_to="none", seed=7,
                       vllm_importance_sampling_correction=False, gradient_checkpointing=grad_ckpt,
                       gradient_checkpointing_kwargs=ckpt_kwargs,
                       vllm_tensor_parallel_size=rollout_tp)
