@@ -132,6 +132,25 @@ def test_chat_template_utils(tiny_tokenizer):
         assert supports_tool_calling(tok) and is_chat_template_prefix_preserving(tok)
     finally:
         tok.chat_template = plain
+    # other families are recognised by a marker of their own template and get a self-authored training template
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi there"},
+            {"role": "assistant", "content": "hello"}, {"role": "user", "content": "more"},
+            {"role": "assistant", "content": "ok"}]
+    try:
+        for marker, must in (("{{ '[INST] ' }}", "[INST] be brief\n\nhi there [/INST] hello"),
+                             ("USER: x ASSISTANT: y", "USER: hi there ASSISTANT: hello"),
+                             ("x<end_of_utterance>", "User: hi there<end_of_utterance>\nAssistant: hello<end_of_utterance>")):
+            tok.chat_template = marker
+            tok.chat_template = get_training_chat_template(tok)
+            assert must in tok.apply_chat_template(msgs, tokenize=False)
+            out = tok.apply_chat_template(msgs, tokenize=True, return_dict=True, return_assistant_tokens_mask=True)
+            assert sum(out["assistant_masks"]) >= 4 and is_chat_template_prefix_preserving(tok)
+        blocks = [{"role": "user", "content": [{"type": "image"}, {"type": "text", "text": "what is this"}]}]
+        tok.chat_template = "USER: x ASSISTANT: y"
+        tok.chat_template = get_training_chat_template(tok)
+        assert tok.apply_chat_template(blocks, tokenize=False, add_generation_prompt=True) == "USER: <image>\nwhat is this ASSISTANT:"
+    finally:
+        tok.chat_template = plain
     msg = parse_response(tok, 'ok <tool_call>\n{"name": "add", "arguments": {"a": 1}}\n</tool_call>')
     assert msg["tool_calls"][0]["function"] == {"name": "add", "arguments": {"a": 1}} and msg["content"] == "ok"
     bad = parse_response(tok, "<tool_call>{not json}</tool_call>")

@@ -59,6 +59,9 @@ _FAMILY_MARKERS = [  # first match wins: more specific markers first
     ("<|start|>", "<|message|>", "gptoss_training.jinja"),
     ("<|assistant|>", None, "phi3_training.jinja"),
     ("<｜Assistant｜>", None, "deepseekv3_training.jinja"),
+    ("<end_of_utterance>", None, "idefics3_training.jinja"),
+    ("[INST]", None, "mistral_training.jinja"),
+    ("USER:", "ASSISTANT:", "llava_training.jinja"),
 ]
 
 
@@ -74,7 +77,7 @@ def get_training_chat_template(tokenizer) -> str | None:
             with open(os.path.join(_TEMPLATE_DIR, fn), encoding="utf-8") as f:
                 return f.read()
     raise ValueError("The tokenizer's chat template does not match a known family (ChatML/Qwen, Qwen3, Llama 3, Gemma, "
-                     "GLM-4, Command-R, gpt-oss, Phi-3, DeepSeek-V3); pass a training template with {% generation %} markers explicitly.")
+                     "GLM-4, Command-R, gpt-oss, Phi-3, DeepSeek-V3, Idefics3 / SmolVLM, Mistral [INST], LLaVA-1.5); pass a training template with {% generation %} markers explicitly.")
 
 
 def _render(tok, messages, **kw):
