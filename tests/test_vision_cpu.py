@@ -209,3 +209,37 @@ def test_processor_opens_image_files_and_byte_records(tmp_path):
     a = proc.preprocess_images([[str(f)], [{"bytes": buf.getvalue(), "path": None}], [arr]])
     assert a.shape == (3, 3, 28, 28)
     assert torch.allclose(a[0], a[1]) and torch.allclose(a[0], a[2], atol=1e-5)
+
+
+def test_vision_collator_with_a_transformers_processor():
+    """The collators are written against the processor call contract, not against VisionProcessor: a genuine
+    transformers LlavaProcessor (CLIP image processor + tokenizer + block-aware chat template) gives the same layout."""
+    import os
+
+    import numpy as np
+    import transformers as tf
+
+    from trl_b200.testing import make_tiny_tokenizer
+    from trl_b200.trainer.sft_trainer import DataCollatorForVisionLanguageModeling
+
+    tok = make_tiny_tokenizer()
+    tok.add_special_tokens({"additional_special_tokens": ["<image>"]})
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with open(os.path.join(root, "trl_b200", "chat_templates", "llava_training.jinja")) as f:
+        tpl = f.read()
+    ip = tf.CLIPImageProcessor(size={"shortest_edge": 28}, crop_size={"height": 28, "width": 28})
+    proc = tf.LlavaProcessor(image_processor=ip, tokenizer=tok, patch_size=14, vision_feature_select_strategy="default",
+                             image_token="<image>", num_additional_image_tokens=1, chat_template=tpl)
+    img = (np.random.RandomState(0).rand(40, 30, 3) * 255).astype("uint8")
+    ex = [{"images": [img], "messages": [{"role": "user", "content": "what is this"},
+                                         {"role": "assistant", "content": "a simple idea"}]},
+          {"images": [img, img], "messages": [{"role": "user", "content": "explain"}, {"role": "assistant", "content": "two"}]}]
+    out = DataCollatorForVisionLanguageModeling(proc)(ex)
+    image_id = tok.convert_tokens_to_ids("<image>")
+    assert out["pixel_values"].shape == (3, 3, 28, 28)
+    assert (out["input_ids"] == image_id).sum(1).tolist() == [4, 8]
+    # the batch trains the native model when the ids agree
+    model = VisionLanguageModel(tiny_vlm_arch("tiny-qwen2", image_token_index=image_id))
+    loss = model(input_ids=out["input_ids"], attention_mask=out["attention_mask"], pixel_values=out["pixel_values"],
+                 labels=out["labels"]).loss
+    assert torch.isfinite(loss)
