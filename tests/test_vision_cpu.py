@@ -243,3 +243,27 @@ def test_vision_collator_with_a_transformers_processor():
     loss = model(input_ids=out["input_ids"], attention_mask=out["attention_mask"], pixel_values=out["pixel_values"],
                  labels=out["labels"]).loss
     assert torch.isfinite(loss)
+
+
+def test_vlm_loads_a_checkpoint_written_by_transformers(tmp_path):
+    import transformers as tf
+
+    torch.manual_seed(0)
+    vc = tf.CLIPVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, image_size=28,
+                             patch_size=14, projection_dim=16)
+    tc = tf.LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, vocab_size=1024, rms_norm_eps=1e-6)
+    hf = tf.LlavaForConditionalGeneration(tf.LlavaConfig(vision_config=vc, text_config=tc, image_token_index=5,
+                                                         vision_feature_layer=-2)).eval()
+    hf.save_pretrained(str(tmp_path))
+    from trl_b200.models.hf_io import load_model
+
+    ours = load_model(str(tmp_path)).eval()
+    assert isinstance(ours, VisionLanguageModel) and ours.config.image_token_index == 5
+    g = torch.Generator().manual_seed(1)
+    ids = _ids_with_images(ours.config, [1, 1], 14, g)
+    pix = torch.randn(2, 3, 28, 28, generator=g)
+    with torch.no_grad():
+        a = ours(input_ids=ids, pixel_values=pix).logits
+        b = hf(input_ids=ids, pixel_values=pix).logits
+    assert torch.allclose(a, b, atol=3e-4, rtol=1e-3), (a - b).abs().max()

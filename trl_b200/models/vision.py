@@ -351,14 +351,18 @@ class VisionLanguageModel(nn.Module):
     def load_hf_state_dict(self, sd: dict[str, torch.Tensor]) -> None:
         from .hf_io import load_hf_state_dict
 
+        # key layouts seen in the wild: "model.language_model.*" (in memory, transformers >= 4.52),
+        # "language_model.model.*" + "language_model.lm_head.weight" (older files) and the mix of both that
+        # transformers 5 writes ("model.language_model.model.*")
         text = {}
         for k, v in sd.items():
-            if k.startswith("model.language_model."):
-                text["model." + k[len("model.language_model."):]] = v
-            elif k.startswith("language_model.model."):  # older layout
-                text["model." + k[len("language_model.model."):]] = v
-            elif k in ("lm_head.weight", "language_model.lm_head.weight"):
+            if k in ("lm_head.weight", "language_model.lm_head.weight", "model.language_model.lm_head.weight"):
                 text["lm_head.weight"] = v
+                continue
+            for pre in ("model.language_model.model.", "language_model.model.", "model.language_model."):
+                if k.startswith(pre):
+                    text["model." + k[len(pre):]] = v
+                    break
         load_hf_state_dict(self.language_model, text, strict=True)
         vt, c = self.vision_tower, self.config.vision
         pre = "model.vision_tower.vision_model." if any(k.startswith("model.vision_tower.") for k in sd) \
