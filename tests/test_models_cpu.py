@@ -174,3 +174,23 @@ def test_sliding_window_attention_matches_transformers(tmp_path):
     d = preset("tiny-qwen2").to_hf_dict()
     d["sliding_window"] = 4096
     assert ModelArch.from_hf_dict(d).sliding_window is None
+
+
+@pytest.mark.parametrize("name", ["tiny-qwen2", "tiny-qwen3-moe", "tiny-phi3"])
+def test_loads_checkpoints_written_by_transformers(name, tmp_path):
+    """The other direction of the round trip: transformers saves, the native loader reads (per-expert or fused MoE
+    tensors, fused Phi-3 projections)."""
+    torch.manual_seed(0)
+    hf = _hf_model(preset(name)) if name != "tiny-phi3" else None
+    if hf is None:
+        import transformers as tf
+
+        d = preset(name).to_hf_dict()
+        d.pop("architectures", None)
+        hf = tf.Phi3ForCausalLM(tf.Phi3Config(**d, attn_implementation="eager")).eval()
+    hf.save_pretrained(str(tmp_path))
+    ours = load_model(str(tmp_path)).eval()
+    ids = torch.randint(0, ours.config.vocab_size, (2, 11))
+    with torch.no_grad():
+        a, b = ours(input_ids=ids).logits, hf(input_ids=ids).logits
+    assert torch.allclose(a, b, atol=2e-4, rtol=1e-3), (a - b).abs().max()
