@@ -194,3 +194,24 @@ def test_loads_checkpoints_written_by_transformers(name, tmp_path):
     with torch.no_grad():
         a, b = ours(input_ids=ids).logits, hf(input_ids=ids).logits
     assert torch.allclose(a, b, atol=2e-4, rtol=1e-3), (a - b).abs().max()
+
+
+def test_eager_generator_greedy_matches_transformers_generate(tmp_path):
+    import transformers as tf
+
+    from trl_b200.rollout.engine import EagerGenerator
+    from trl_b200.rollout.sampling import SamplingParams
+
+    torch.manual_seed(0)
+    m = CausalLM(preset("tiny-qwen2")).eval()
+    m.save_pretrained(str(tmp_path))
+    hf = tf.AutoModelForCausalLM.from_pretrained(str(tmp_path), dtype=torch.float32).eval()
+    prompt = torch.randint(5, 1000, (1, 9))
+    ref = hf.generate(prompt, max_new_tokens=8, do_sample=False, eos_token_id=None, pad_token_id=0)[0, 9:].tolist()
+    out = EagerGenerator(m).generate([prompt[0].tolist()], SamplingParams(n=1, max_tokens=8, greedy=True, eos_token_id=None))
+    assert out[0].token_ids == ref
+    # the reported log-probs are those of the chosen tokens under the model
+    with torch.no_grad():
+        full = torch.tensor([prompt[0].tolist() + ref])
+        lp = torch.log_softmax(hf(full).logits[0, 8:-1].float(), -1).gather(1, torch.tensor(ref)[:, None])[:, 0]
+    assert torch.allclose(torch.tensor(out[0].logprobs), lp, atol=1e-4)
