@@ -329,6 +329,9 @@ class DPOTrainer(Trainer):
                 # streamed policy => streamed frozen reference (one slice per layer and rank, no optimizer state)
                 from ..parallel.streamshard import StreamShardEngine
 
+                if getattr(self.args, "sync_ref_model", False):
+                    raise NotImplementedError("sync_ref_model copies whole parameters; it is not available with "
+                                              "shard_mode='full_shard_stream'")
                 self._ref_stream = StreamShardEngine(self.ref_model, frozen=True, device=self.args.device,
                                                     init_seed=self.args.seed)
             with torch.no_grad():
