@@ -33,6 +33,14 @@ def main():
     if variant == "straight":
         tr = make(out, mode, 3)
         tr.train()
+    elif variant == "phase1":  # elastic resume, first half: two steps, checkpoint, stop
+        tr = make(out, mode, 2, save_steps=2)
+        tr.train()
+        D.barrier()
+        return
+    elif variant == "phase2":  # second half, possibly with another world size / shard mode
+        tr = make(out, mode, 3)
+        tr.train(resume_from_checkpoint=os.path.join(out, "checkpoint-2"))
     else:
         tr = make(out, mode, 2, save_steps=2)
         tr.train()

@@ -35,7 +35,7 @@ def test_sft_world1_vs_world2(tmp_path, mode, port):
     assert ref[-1]["loss"] < ref[0]["loss"] + 0.05
 
 
-def _run_stream(world, mode, variant, out, port):
+def _run_stream(world, mode, variant, out, port, load=True):
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
     worker = os.path.join(HERE, "dist_worker_stream.py")
     if world == 1:
@@ -45,6 +45,8 @@ def _run_stream(world, mode, variant, out, port):
                "--master-addr", "127.0.0.1", "--master-port", str(port), worker, out, mode, variant]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    if not load:
+        return None
     from safetensors.torch import load_file
 
     return load_file(os.path.join(out, "final", "model.safetensors"))
@@ -83,3 +85,18 @@ def test_grpo_with_streamed_shards_matches_zero2(tmp_path, kind, port):
     for x, y in zip(a, b):
         assert x["reward"] == y["reward"], (a, b)  # same samples
         assert abs(x["loss"] - y["loss"]) < 2e-4 and abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, x["grad_norm"]), (a, b)
+
+
+@pytest.mark.parametrize("mode1,world1,mode2,world2,port", [("zero2", 2, "ddp", 1, 29622), ("ddp", 1, "zero2", 2, 29624),
+                                                             ("full_shard_stream", 2, "full_shard_stream", 1, 29626)])
+def test_elastic_resume_with_another_world_size(tmp_path, mode1, world1, mode2, world2, port):
+    """Two steps with one world size / shard mode, checkpoint, third step with another: the optimizer slices are put
+    back together and cut again, and the weights end where an uninterrupted run ends."""
+    import torch
+
+    ref = _run_stream(1, "ddp", "straight", str(tmp_path / "ref"), 0)
+    out = str(tmp_path / "el")
+    _run_stream(world1, mode1, "phase1", out, port, load=False)
+    got = _run_stream(world2, mode2, "phase2", out, port + 1)
+    for k in ref:
+        assert torch.allclose(ref[k], got[k], atol=2e-5), (k, (ref[k] - got[k]).abs().max())

@@ -717,7 +717,14 @@ class Trainer:
             old.is_world_process_zero, old.is_local_process_zero = self.state.is_world_process_zero, self.state.is_local_process_zero
             self.state = old
         op = os.path.join(folder, f"optimizer_rank{D.rank()}.pt" if self.engine.sharded else "optimizer.pt")
-        if os.path.exists(op):
+        saved = sorted(f for f in os.listdir(folder) if re.fullmatch(r"optimizer(_rank\d+)?\.pt", f))
+        expect = [f"optimizer_rank{r}.pt" for r in range(D.world_size())] if self.engine.sharded else ["optimizer.pt"]
+        if saved and sorted(expect) != saved and hasattr(self.engine, "load_optimizer_state_resharded"):
+            # elastic resume: the checkpoint was written with another world size or shard mode.  Every rank reads all
+            # optimizer files and keeps the slices it owns now.
+            shards = [torch.load(os.path.join(folder, f), map_location="cpu", weights_only=False) for f in saved]
+            self.engine.load_optimizer_state_resharded(shards)
+        elif os.path.exists(op):
             self.engine.load_optimizer_state_dict(torch.load(op, map_location="cpu", weights_only=False))
         elif getattr(m, "_is_native", False):
             self.engine.refresh_master_from_params() if hasattr(self.engine, "refresh_master_from_params") else None

@@ -308,6 +308,26 @@ class TrainEngine:
             b.exp_avg_sq.copy_(s["exp_avg_sq"])
 
     @torch.no_grad()
+    def load_optimizer_state_resharded(self, shards: list[dict]):
+        """Elastic resume: ``shards`` are the optimizer files of ALL ranks of the run that saved (one file for a
+        replicated run).  Every bucket is put back together in slice order and cut again for this run's world size
+        and mode; bucket lengths differ only in their zero padding (a multiple of world * 256 elements)."""
+        self.step_count = shards[0]["step"]
+        for b in self.buckets:
+            key = b.name + "|" + str(b.flat_param.dtype)
+            parts = sorted((s["buckets"][key] for s in shards), key=lambda x: x["lo"])
+            if parts[0]["names"] != b.names:
+                raise ValueError(f"bucket {b.name}: the checkpoint holds other parameters ({parts[0]['names'][:3]}...)")
+            for k, dst in (("master", b.master), ("exp_avg", b.exp_avg), ("exp_avg_sq", b.exp_avg_sq)):
+                full = torch.cat([p[k].reshape(-1).float() for p in parts])
+                buf = torch.zeros(b.numel, dtype=torch.float32)
+                n = min(full.numel(), b.numel)
+                buf[:n] = full[:n]
+                dst.copy_(buf[b.lo:b.hi].to(dst.dtype))
+            if b.master.data_ptr() != b.flat_param[b.lo:b.hi].data_ptr():
+                b.flat_param[b.lo:b.hi].copy_(b.master.to(b.flat_param.dtype))
+
+    @torch.no_grad()
     def refresh_master_from_params(self):
         """Re-derive the fp32 master shard after weights were loaded into the compute copy."""
         for b in self.buckets:

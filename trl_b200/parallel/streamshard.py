@@ -354,7 +354,7 @@ class StreamShardEngine:
 
     # ---- checkpoints ---------------------------------------------------------------------------------------------
     def optimizer_state_dict(self) -> dict:
-        return {"step": self.step_count, "mode": self.mode, "world": self.world,
+        return {"step": self.step_count, "mode": self.mode, "world": self.world, "rank": self.rank,
                 "layers": [{"master": l.master.cpu(), "exp_avg": l.exp_avg.cpu(), "exp_avg_sq": l.exp_avg_sq.cpu()}
                            for l in self.layers],
                 "rest": {"master": self.rest_master.cpu(), "exp_avg": self.rest_exp_avg.cpu(),
@@ -371,6 +371,31 @@ class StreamShardEngine:
         self.rest_master.copy_(sd["rest"]["master"])
         self.rest_exp_avg.copy_(sd["rest"]["exp_avg"])
         self.rest_exp_avg_sq.copy_(sd["rest"]["exp_avg_sq"])
+        self._publish_rest()
+        self._invalidate()
+
+    @torch.no_grad()
+    def load_optimizer_state_resharded(self, shards: list[dict]):
+        """Elastic resume from the per-rank files of a streamed run with another world size: slices are concatenated
+        in rank order and cut again (layer lengths differ only in their zero padding)."""
+        shards = sorted(shards, key=lambda s: s.get("rank", 0))
+        if any(s.get("mode") != self.mode for s in shards) or len(shards) != shards[0].get("world"):
+            raise ValueError("need the optimizer files of every rank of a streamed full-shard run")
+        self.step_count = shards[0]["step"]
+
+        def recut(parts, numel, lo, hi, dst):
+            full = torch.cat([p.reshape(-1).float() for p in parts])
+            buf = torch.zeros(numel, dtype=torch.float32)
+            n = min(full.numel(), numel)
+            buf[:n] = full[:n]
+            dst.copy_(buf[lo:hi].to(dst.dtype))
+
+        for i, l in enumerate(self.layers):
+            per = l.numel // self.world
+            for k, dst in (("master", l.master), ("exp_avg", l.exp_avg), ("exp_avg_sq", l.exp_avg_sq)):
+                recut([s["layers"][i][k] for s in shards], l.numel, self.rank * per, (self.rank + 1) * per, dst)
+        for k, dst in (("master", self.rest_master), ("exp_avg", self.rest_exp_avg), ("exp_avg_sq", self.rest_exp_avg_sq)):
+            recut([s["rest"][k] for s in shards], self.rest_numel, self.rest_lo, self.rest_hi, dst)
         self._publish_rest()
         self._invalidate()
 
