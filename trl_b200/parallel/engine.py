@@ -315,6 +315,9 @@ class TrainEngine:
         self.step_count = shards[0]["step"]
         for b in self.buckets:
             key = b.name + "|" + str(b.flat_param.dtype)
+            if any(key not in s["buckets"] for s in shards):
+                raise ValueError(f"the checkpoint's optimizer state has no bucket {key!r}: it was written by an engine with "
+                                 f"another bucket layout (mode {shards[0].get('mode')!r}, this run {self.mode!r})")
             parts = sorted((s["buckets"][key] for s in shards), key=lambda x: x["lo"])
             if parts[0]["names"] != b.names:
                 raise ValueError(f"bucket {b.name}: the checkpoint holds other parameters ({parts[0]['names'][:3]}...)")
