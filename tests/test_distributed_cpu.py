@@ -24,9 +24,14 @@ def _run(world, mode, out, steps=4, port=29611):
         return json.load(f)
 
 
+_SFT_REF = {}
+
+
 @pytest.mark.parametrize("mode,port", [("ddp", 29611), ("zero2", 29612), ("sp2", 29613), ("cp2", 29614), ("full_shard_stream", 29615)])
-def test_sft_world1_vs_world2(tmp_path, mode, port):
-    ref = _run(1, "ddp", str(tmp_path / "w1.json"))
+def test_sft_world1_vs_world2(tmp_path, tmp_path_factory, mode, port):
+    if "sft_w1" not in _SFT_REF:  # the single-process trajectory is the same for every mode: run it once
+        _SFT_REF["sft_w1"] = _run(1, "ddp", str(tmp_path_factory.mktemp("w1") / "w1.json"))
+    ref = _SFT_REF["sft_w1"]
     two = _run(2, mode, str(tmp_path / f"w2_{mode}.json"), port=port)
     assert len(ref) == len(two) == 4
     for a, b in zip(ref, two):
@@ -52,12 +57,22 @@ def _run_stream(world, mode, variant, out, port, load=True):
     return load_file(os.path.join(out, "final", "model.safetensors"))
 
 
-def test_streamed_full_shard_saves_and_resumes_like_ddp(tmp_path):
+_REF_CACHE = {}
+
+
+def _ddp_reference(tmp_path_factory):
+    """Weights of the uninterrupted world-1 ddp run (3 steps), computed once per session."""
+    if "ref" not in _REF_CACHE:
+        _REF_CACHE["ref"] = _run_stream(1, "ddp", "straight", str(tmp_path_factory.mktemp("ddp_ref")), 0)
+    return _REF_CACHE["ref"]
+
+
+def test_streamed_full_shard_saves_and_resumes_like_ddp(tmp_path, tmp_path_factory):
     """Weights after 3 steps (weight decay on): world-1 ddp == world-2 streamed shards == world-2 streamed shards with a
     checkpoint after step 2 and a resume in a new trainer."""
     import torch
 
-    ref = _run_stream(1, "ddp", "straight", str(tmp_path / "ddp"), 0)
+    ref = _ddp_reference(tmp_path_factory)
     a = _run_stream(2, "full_shard_stream", "straight", str(tmp_path / "s"), 29616)
     b = _run_stream(2, "full_shard_stream", "resume", str(tmp_path / "r"), 29617)
     assert set(ref) == set(a) == set(b)
@@ -89,12 +104,12 @@ def test_grpo_with_streamed_shards_matches_zero2(tmp_path, kind, port):
 
 @pytest.mark.parametrize("mode1,world1,mode2,world2,port", [("zero2", 2, "ddp", 1, 29622), ("ddp", 1, "zero2", 2, 29624),
                                                              ("full_shard_stream", 2, "full_shard_stream", 1, 29626)])
-def test_elastic_resume_with_another_world_size(tmp_path, mode1, world1, mode2, world2, port):
+def test_elastic_resume_with_another_world_size(tmp_path, tmp_path_factory, mode1, world1, mode2, world2, port):
     """Two steps with one world size / shard mode, checkpoint, third step with another: the optimizer slices are put
     back together and cut again, and the weights end where an uninterrupted run ends."""
     import torch
 
-    ref = _run_stream(1, "ddp", "straight", str(tmp_path / "ref"), 0)
+    ref = _ddp_reference(tmp_path_factory)
     out = str(tmp_path / "el")
     _run_stream(world1, mode1, "phase1", out, port, load=False)
     got = _run_stream(world2, mode2, "phase2", out, port + 1)

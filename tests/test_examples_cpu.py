@@ -16,12 +16,27 @@ def _run(args, tmp_path, timeout=600):
     return r.stdout
 
 
-@pytest.mark.parametrize("name", ["kto", "reward_modeling", "rloo", "sft_lora", "gkd", "dpo_vlm", "grpo_vlm", "cpo_simpo", "orpo", "prm"])
-def test_example_smoke(name, tmp_path):
-    out = _run([f"{name}.py", "--smoke", "--out", str(tmp_path / name)], tmp_path)
-    assert "train_runtime" in out
-    saved = os.listdir(tmp_path / name)
-    assert any(f.endswith(".safetensors") for f in saved), saved
+EXAMPLES = ["kto", "reward_modeling", "rloo", "sft_lora", "gkd", "dpo_vlm", "grpo_vlm", "cpo_simpo", "orpo", "prm"]
+
+_RUNNER = """
+import runpy, sys, os
+names, out = sys.argv[1].split(","), sys.argv[2]
+for n in names:
+    print("EXAMPLE", n, flush=True)
+    sys.argv = [n + ".py", "--smoke", "--out", os.path.join(out, n)]
+    runpy.run_path(n + ".py", run_name="__main__")
+    print("EXAMPLE_DONE", n, flush=True)
+"""
+
+
+def test_examples_smoke(tmp_path):
+    """All example scripts in their offline smoke mode, one after the other in ONE interpreter (start-up dominates)."""
+    out = _run(["-c", _RUNNER, ",".join(EXAMPLES), str(tmp_path)], tmp_path, timeout=900)
+    for name in EXAMPLES:
+        assert f"EXAMPLE_DONE {name}" in out, (name, out[-1500:])
+        saved = os.listdir(tmp_path / name)
+        assert any(f.endswith(".safetensors") for f in saved), (name, saved)
+    assert out.count("train_runtime") >= len(EXAMPLES)
 
 
 def test_sft_vlm_example_smoke(tmp_path):
