@@ -16,11 +16,17 @@ from trl_b200.parallel.symm import SymmArena, SyncWords
 from trl_b200.testing import make_tiny_model
 
 
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from _dist_util import Deadline  # noqa: E402
+
+
 def main():
     D.init_process_group()
+    DL = Deadline()  # the ranks leave on their own, between steps, before the parent's limit
     rank, world = D.rank(), D.world_size()
     dev = torch.device("cuda", D.local_rank())
     torch.manual_seed(0)
+    DL.check()
     # ---- fused optimizer step vs NCCL reduce-scatter + AdamW + all-gather -------------------------------
     base = make_tiny_model("tiny-qwen2", dtype=torch.bfloat16, device=dev, hidden_size=256, intermediate_size=512,
                            num_attention_heads=2, num_key_value_heads=1, head_dim=128)
@@ -53,6 +59,7 @@ def main():
     ref0 = flat.clone()
     td.broadcast(ref0, 0)
     assert torch.equal(flat, ref0)
+    DL.check()
     # ---- shard all-gather: pull and multimem push ---------------------------------------------------------
     per = 1 << 16
     arena = SymmArena(world * per * 2 + 4096, dev)
@@ -72,6 +79,7 @@ def main():
             want = torch.arange(per, device=dev).to(torch.bfloat16) + r
             assert torch.equal(buf[r * per:(r + 1) * per], want), (mm, r)
         td.barrier()
+    DL.check()
     # ---- TP decode: all-reduce + residual add + RMSNorm ----------------------------------------------------
     T, H = 64, 3584
     arena2 = SymmArena(2 * T * H * 2 + 4096, dev)
@@ -97,6 +105,7 @@ def main():
         g = res.clone()
         td.broadcast(g, 0)
         assert torch.equal(g, res)  # bit-identical residual stream on all ranks
+    DL.check()
     # ---- all-gather fused into the GEMM ------------------------------------------------------------------
     from trl_b200.ops.cuda_comm import AgGemmState, ag_gemm
 

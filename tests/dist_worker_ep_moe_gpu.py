@@ -12,8 +12,13 @@ from trl_b200.parallel import dist as D
 from trl_b200.parallel.expert_parallel import ExpertParallelMoE
 
 
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from _dist_util import Deadline  # noqa: E402
+
+
 def main():
     D.init_process_group()
+    DL = Deadline()  # the ranks leave on their own, between steps, before the parent's limit
     rank, world = D.rank(), D.world_size()
     dev = torch.device("cuda", D.local_rank())
     E, I, H, k = 8, 256, 512, 2
@@ -61,6 +66,7 @@ def main():
     td.barrier()
     if rank == 0:
         print("EP_MOE_OK")
+    DL.check()
     td.destroy_process_group()
 
 

@@ -35,8 +35,13 @@ def run(model, engine, rank, steps=3):
     return losses
 
 
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from _dist_util import Deadline  # noqa: E402
+
+
 def main():
     D.init_process_group()
+    DL = Deadline()  # the ranks leave on their own, between steps, before the parent's limit
     rank = D.rank()
     dev = torch.device("cuda", D.local_rank())
     base = make_tiny_model("tiny-qwen2", dtype=torch.bfloat16, device=dev, hidden_size=512, num_attention_heads=4,
@@ -50,16 +55,19 @@ def main():
     b = run(m_z2, e_z2, rank)
     torch.cuda.synchronize()
     K.check_status(dev)
+    DL.check()
     for (la, na), (lb, nb) in zip(a, b):
         assert abs(la - lb) < 5e-2 and abs(na - nb) < 5e-2 * max(1.0, nb), (a, b)
     e_fs.gather_full_params()
     torch.cuda.synchronize()
+    DL.check()
     for (n, p), (_, q) in zip(m_fs.named_parameters(), m_z2.named_parameters()):
         assert torch.isfinite(p.float()).all(), n
         assert torch.allclose(p.float(), q.float(), atol=3e-2, rtol=3e-2), n
     td.barrier()
     if rank == 0:
         print("FULLSHARD_OK", a)
+    DL.check()
     td.destroy_process_group()
 
 

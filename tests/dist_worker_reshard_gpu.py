@@ -16,8 +16,13 @@ from trl_b200.rollout.tp_engine import TPRolloutEngine
 from trl_b200.testing import make_tiny_model
 
 
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from _dist_util import Deadline  # noqa: E402
+
+
 def main():
     D.init_process_group()
+    DL = Deadline()  # the ranks leave on their own, between steps, before the parent's limit
     rank = D.rank()
     dev = torch.device("cuda", D.local_rank())
     model = make_tiny_model("tiny-qwen2", dtype=torch.bfloat16, device=dev, hidden_size=512, num_attention_heads=4,
@@ -26,6 +31,7 @@ def main():
     group = td.new_group([0, 1])
     tp = TPRolloutEngine(model, group, max_num_seqs=4, max_model_len=128)
     eng = FullShardEngine(model, copiers=4)  # from here on, remote slices of the layer buckets are NaN
+    DL.check()
     for w in tp.w:
         for t in w.values():
             if t is not None:
@@ -35,6 +41,7 @@ def main():
     torch.cuda.synchronize()
     K.check_status(dev)
     ref_tp = TPRolloutEngine(full, group, max_num_seqs=4, max_model_len=128)  # sliced from the complete copy
+    DL.check()
     for a, b in zip(tp.w, ref_tp.w):
         for k in a:
             if a[k] is not None:
@@ -44,6 +51,7 @@ def main():
     td.barrier()
     if rank == 0:
         print("RESHARD_OK", rs.n, rs.bytes)
+    DL.check()
     td.destroy_process_group()
 
 

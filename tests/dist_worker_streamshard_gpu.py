@@ -33,13 +33,19 @@ def run(model, engine, rank, steps=3):
     return out
 
 
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from _dist_util import Deadline  # noqa: E402
+
+
 def main():
     D.init_process_group()
+    DL = Deadline()  # the ranks leave on their own, between steps, before the parent's limit
     rank = D.rank()
     dev = torch.device("cuda", D.local_rank())
     base = make_tiny_model("tiny-qwen2", dtype=torch.bfloat16, device=dev, hidden_size=512, num_attention_heads=4,
                            num_key_value_heads=2, head_dim=128, intermediate_size=1024, num_hidden_layers=3, seed=0)
     m_st, m_z2 = copy.deepcopy(base), copy.deepcopy(base)
+    DL.check()
     for m in (m_st, m_z2):
         m.gradient_checkpointing_enable()
         m.train()
@@ -49,10 +55,12 @@ def main():
     b = run(m_z2, e_z2, rank)
     torch.cuda.synchronize()
     K.check_status(dev)
+    DL.check()
     for (la, na), (lb, nb) in zip(a, b):
         assert abs(la - lb) < 5e-2 and abs(na - nb) < 5e-2 * max(1.0, nb), (a, b)
     sd = e_st.streamed_hf_state_dict(to_cpu=True)
     ref = m_z2.state_dict_hf()
+    DL.check()
     for k, v in ref.items():
         assert torch.isfinite(sd[k].float()).all(), k
         assert torch.allclose(sd[k].float().cpu(), v.float().cpu(), atol=3e-2, rtol=3e-2), k
@@ -63,6 +71,7 @@ def main():
     td.barrier()
     if rank == 0:
         print("STREAMSHARD_OK", a, b)
+    DL.check()
     td.destroy_process_group()
 
 

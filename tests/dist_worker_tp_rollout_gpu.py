@@ -14,8 +14,13 @@ from trl_b200.rollout.tp_engine import TPRolloutEngine
 from trl_b200.testing import make_tiny_model
 
 
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from _dist_util import Deadline  # noqa: E402
+
+
 def main():
     D.init_process_group()
+    DL = Deadline()  # the ranks leave on their own, between steps, before the parent's limit
     rank = D.rank()
     dev = torch.device("cuda", D.local_rank())
     model = make_tiny_model("tiny-qwen2", dtype=torch.bfloat16, device=dev, hidden_size=512, num_attention_heads=4,
@@ -27,6 +32,7 @@ def main():
     ref = RolloutEngine(model, max_num_seqs=4, max_model_len=64, poll_every=4).generate(mine, sp)
     group = td.new_group([0, 1])
     eng = TPRolloutEngine(model, group, max_num_seqs=4, max_model_len=64, poll_every=4)
+    assert eng.fused == (os.environ.get("TRL_B200_TP_FUSED", "1") == "1")
     out = eng.generate(mine, sp)
     torch.cuda.synchronize()
     K.check_status(dev)
@@ -49,11 +55,15 @@ def main():
     cfg = model.config
     ql = eng.hq_local * cfg.head_dim
     il = cfg.intermediate_size // 2
-    for l, w in zip(model.layers, eng.w):  # the TP buffers are exact slices of the new weights
-        assert torch.equal(w["qkv"][:ql], l.qkv_proj[rank * ql:(rank + 1) * ql])
-        assert torch.equal(w["o"], l.o_proj[:, rank * ql:(rank + 1) * ql])
-        assert torch.equal(w["gu"][:il], l.gate_up_proj[rank * il:(rank + 1) * il])
-        assert torch.equal(w["down"], l.down_proj[:, rank * il:(rank + 1) * il])
+    # the TP buffers are exact slices of the new weights (tile-major copies of them on the fused path)
+    lay = (lambda t: K.tile_weights(t.contiguous())) if eng.fused else (lambda t: t)
+    for l, w in zip(model.layers, eng.w):
+        q_sl = lay(l.qkv_proj[rank * ql:(rank + 1) * ql])
+        assert torch.equal(w["qkv"][:q_sl.numel()] if eng.fused else w["qkv"][:ql], q_sl)
+        assert torch.equal(w["o"], lay(l.o_proj[:, rank * ql:(rank + 1) * ql]))
+        g_sl = lay(l.gate_up_proj[rank * il:(rank + 1) * il])
+        assert torch.equal(w["gu"][:g_sl.numel()] if eng.fused else w["gu"][:il], g_sl)
+        assert torch.equal(w["down"], lay(l.down_proj[:, rank * il:(rank + 1) * il]))
     ref3 = RolloutEngine(model, max_num_seqs=4, max_model_len=64, poll_every=4).generate(mine, sp)
     out3 = eng.generate(mine, sp)
     # greedy decoding of a tiny random model sits on near-ties, and the two engines round differently: most, not all
@@ -61,6 +71,7 @@ def main():
     td.barrier()
     if rank == 0:
         print("TP_ROLLOUT_OK")
+    DL.check()
     td.destroy_process_group()
 
 

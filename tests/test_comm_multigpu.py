@@ -1,10 +1,12 @@
 """Fused compute+collective kernels on 2 GPUs (child processes; skipped with fewer than 2 devices)."""
 import os
-import subprocess
 import sys
 
 import pytest
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from _dist_util import run_ranks  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
@@ -12,47 +14,39 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_comm_kernels_two_ranks():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29621", os.path.join(HERE, "dist_worker_comm_gpu.py")]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=200)
-    assert r.returncode == 0 and "COMM_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    rc, out, err = run_ranks(os.path.join(HERE, "dist_worker_comm_gpu.py"), 29621, multimem=True)
+    assert rc == 0 and "COMM_OK" in out, out[-3000:] + err[-3000:]
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_tp_rollout_engine_two_ranks():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29622", os.path.join(HERE, "dist_worker_tp_rollout_gpu.py")]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=200)
-    assert r.returncode == 0 and "TP_ROLLOUT_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+@pytest.mark.parametrize("fused", ["1", "0"])
+def test_tp_rollout_engine_two_ranks(fused):
+    """fused=1: decode GEMMs with the all-reduce in their epilogue (peer reductions + arrival counters);
+    fused=0: library GEMMs + the all-reduce kernel."""
+    rc, out, err = run_ranks(os.path.join(HERE, "dist_worker_tp_rollout_gpu.py"), 29622 + 20 * int(fused),
+                             extra_env={"TRL_B200_TP_FUSED": fused})
+    assert rc == 0 and "TP_ROLLOUT_OK" in out, out[-3000:] + err[-3000:]
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_full_shard_engine_two_ranks():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29623", os.path.join(HERE, "dist_worker_fullshard_gpu.py")]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=200)
-    assert r.returncode == 0 and "FULLSHARD_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    rc, out, err = run_ranks(os.path.join(HERE, "dist_worker_fullshard_gpu.py"), 29623)
+    assert rc == 0 and "FULLSHARD_OK" in out, out[-3000:] + err[-3000:]
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_expert_parallel_moe_two_ranks():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29627", os.path.join(HERE, "dist_worker_ep_moe_gpu.py")]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=200)
-    assert r.returncode == 0 and "EP_MOE_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    rc, out, err = run_ranks(os.path.join(HERE, "dist_worker_ep_moe_gpu.py"), 29627)
+    assert rc == 0 and "EP_MOE_OK" in out, out[-3000:] + err[-3000:]
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_weight_reshard_from_full_shard_to_tp_layout():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29629", os.path.join(HERE, "dist_worker_reshard_gpu.py")]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=200)
-    assert r.returncode == 0 and "RESHARD_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    rc, out, err = run_ranks(os.path.join(HERE, "dist_worker_reshard_gpu.py"), 29629)
+    assert rc == 0 and "RESHARD_OK" in out, out[-3000:] + err[-3000:]
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_streamed_full_shard_engine_two_ranks():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29631", os.path.join(HERE, "dist_worker_streamshard_gpu.py")]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=200)
-    assert r.returncode == 0 and "STREAMSHARD_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    rc, out, err = run_ranks(os.path.join(HERE, "dist_worker_streamshard_gpu.py"), 29631)
+    assert rc == 0 and "STREAMSHARD_OK" in out, out[-3000:] + err[-3000:]

@@ -59,8 +59,10 @@ def test_lmhead_backward_matches_autograd():
     assert torch.allclose(w.grad.float(), w2.grad, atol=3e-2, rtol=3e-2), (w.grad.float() - w2.grad).abs().max()
 
 
-@pytest.mark.parametrize("B,N,K", [(64, 3584, 18944), (7, 1000, 520), (33, 4608, 3584)])
-def test_smallm_splitk_gemm_and_fp32_add_rmsnorm(B, N, K):
+@pytest.mark.parametrize("pdl", [False, True])
+@pytest.mark.parametrize("B,N,K", [(64, 3584, 18944), (7, 1000, 520), (33, 4608, 3584), (1, 136, 64), (100, 777 * 8, 264),
+                                   (128, 3584, 3584)])
+def test_decode_gemm_stream_k_and_fp32_add_rmsnorm(B, N, K, pdl):
     from trl_b200.ops import cuda as Kc
 
     torch.manual_seed(0)
@@ -68,19 +70,93 @@ def test_smallm_splitk_gemm_and_fp32_add_rmsnorm(B, N, K):
     w = (torch.randn(N, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
     bias = torch.randn(N, device="cuda").to(torch.bfloat16)
     y = torch.zeros(B, N, device="cuda")
-    Kc.smallm_gemm_accumulate(x, w, y, bias=bias)
-    want = x.float() @ w.float().t() + bias.float()
-    assert (y - want).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item())
-    Kc.smallm_gemm_accumulate(x, w, y)  # accumulates
-    assert (y - (2 * want - bias.float())).abs().max().item() < 4e-2 * max(1.0, want.abs().max().item())
-    if N % 8 == 0:
-        res = torch.randn(B, N, device="cuda").to(torch.bfloat16)
-        gamma = torch.randn(N, device="cuda").to(torch.bfloat16)
-        r0, d0 = res.clone(), y.clone()
-        out = Kc.add_rmsnorm_f32_infer(res, y, gamma, 1e-6)
-        s = (r0.float() + d0).to(torch.bfloat16).float()
-        ref = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.float()
-        assert (out.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
-        assert float(y.abs().max()) == 0.0 and torch.equal(res.float(), s)
+    was = Kc.set_pdl(pdl)
+    try:
+        Kc.decode_gemm(x, w, bias, y32=y)
+        want = x.float() @ w.float().t() + bias.float()
+        assert (y - want).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item())
+        Kc.decode_gemm(x, w, y32=y)  # accumulates
+        assert (y - (2 * want - bias.float())).abs().max().item() < 4e-2 * max(1.0, want.abs().max().item())
+        for ctas in (1, 5, 148):  # any grid gives the same sums
+            y2 = torch.zeros(B, N, device="cuda")
+            Kc.decode_gemm(x, w, bias, y32=y2, max_ctas=ctas)
+            assert (y2 - want).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item()), ctas
+        out = Kc.decode_gemm(x, w, bias)  # bf16 store, whole slab pairs
+        assert (out.float() - want).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item())
+        wt = Kc.tile_weights(w)  # tile-major copy of the weight
+        y3 = torch.zeros(B, N, device="cuda")
+        Kc.decode_gemm(x, wt, bias, y32=y3, tiled_shape=(N, K))
+        assert (y3 - want).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item())
+        ctr = torch.zeros(1, dtype=torch.int32, device="cuda")  # single rank: the arrival counter counts the grid
+        y4 = torch.zeros(B, N, device="cuda")
+        Kc.decode_gemm(x, w, bias, y32=y4, peers=([], [ctr.data_ptr()]))
+        assert int(ctr.item()) == Kc.decode_gemm_ctas(B, N, K) and (y4 - want).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item())
+        if N % 8 == 0:
+            res = torch.randn(B, N, device="cuda").to(torch.bfloat16)
+            gamma = torch.randn(N, device="cuda").to(torch.bfloat16)
+            r0, d0 = res.clone(), y.clone()
+            o = Kc.add_rmsnorm_f32_infer(res, y, gamma, 1e-6)
+            s = (r0.float() + d0).to(torch.bfloat16).float()
+            ref = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.float()
+            assert (o.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
+            assert float(y.abs().max()) == 0.0 and torch.equal(res.float(), s)
+        torch.cuda.synchronize()
+        Kc.check_status(torch.device("cuda"))
+    finally:
+        Kc.set_pdl(was)
+
+
+@pytest.mark.parametrize("B,I,K", [(64, 18944, 3584), (5, 256, 72), (128, 1024, 256), (70, 384, 520)])
+def test_decode_gemm_swiglu_epilogue(B, I, K):
+    from trl_b200.ops import cuda as Kc
+
+    torch.manual_seed(3)
+    x = (torch.randn(B, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    out = Kc.decode_gemm(x, w, swiglu=True)
+    g, u = x.float() @ w[:I].float().t(), x.float() @ w[I:].float().t()
+    want = torch.nn.functional.silu(g) * u
     torch.cuda.synchronize()
     Kc.check_status(torch.device("cuda"))
+    assert (out.float() - want).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item())
+    out2 = Kc.decode_gemm(x, Kc.tile_weights(w), swiglu=True, tiled_shape=(2 * I, K))
+    torch.cuda.synchronize()
+    assert (out2.float() - want).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item())
+
+
+@pytest.mark.parametrize("qk_norm,bias,v_t", [(False, True, True), (True, False, True), (False, False, False)])
+def test_rope_kv_write_from_fp32_sums_matches_bf16_path(qk_norm, bias, v_t):
+    from trl_b200.ops import cuda as Kc
+
+    torch.manual_seed(4)
+    B, Hq, Hk, D, bs, nblk = 9, 8, 2, 128, 64 if v_t else 16, 40
+    qkv32 = torch.randn(B, (Hq + 2 * Hk) * D, device="cuda")
+    b = torch.randn((Hq + 2 * Hk) * D, device="cuda").to(torch.bfloat16) if bias else None
+    qn = (1 + 0.1 * torch.randn(D, device="cuda")).to(torch.bfloat16) if qk_norm else None
+    kn = (1 + 0.1 * torch.randn(D, device="cuda")).to(torch.bfloat16) if qk_norm else None
+    seq_lens = torch.tensor([3, 70, -1, 0, 129, 17, 64, 63, 5], dtype=torch.int32, device="cuda")
+    table = torch.randperm(nblk, device="cuda").to(torch.int32)[: B * 4].reshape(B, 4)
+
+    def caches():
+        kc = torch.zeros(nblk, bs, Hk, D, device="cuda", dtype=torch.bfloat16)
+        vc = torch.zeros((nblk, Hk, D, bs) if v_t else (nblk, bs, Hk, D), device="cuda", dtype=torch.bfloat16)
+        return kc, vc, torch.zeros(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+
+    # reference: the bf16 path (bias add, per-head norm in PyTorch, then the bf16 kernel)
+    ref = qkv32 + (b.float() if bias else 0)
+    ref = ref.to(torch.bfloat16)
+    if qk_norm:
+        r = ref.view(B, Hq + 2 * Hk, D).float()
+        for lo, hi, wt in ((0, Hq, qn), (Hq, Hq + Hk, kn)):
+            h = r[:, lo:hi]
+            r[:, lo:hi] = (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-6) * wt.float()).to(torch.bfloat16).float()
+        ref = r.view(B, -1).to(torch.bfloat16)
+    kc0, vc0, q0 = caches()
+    Kc.rope_kv_write(ref, seq_lens, None, table, bs, q0, kc0, vc0, Hq, Hk, D, 1e6, v_transposed=v_t)
+    kc1, vc1, q1 = caches()
+    acc = qkv32.clone()
+    Kc.rope_kv_write_f32(acc, b, qn, kn, 1e-6, seq_lens, None, table, bs, q1, kc1, vc1, Hq, Hk, D, 1e6, v_transposed=v_t)
+    torch.cuda.synchronize()
+    assert float(acc.abs().max()) == 0.0
+    for a_, b_ in ((q0, q1), (kc0, kc1), (vc0, vc1)):
+        assert (a_.float() - b_.float()).abs().max().item() < 4e-2

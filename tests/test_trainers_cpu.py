@@ -389,3 +389,97 @@ def test_dpo_trajectory_equivalence_classes(tmp_path, tiny_tokenizer):
         got = _dpo_trajectory(tmp_path, name, tiny_tokenizer, **over)
         for a, b in zip(base, got):
             assert all(abs(x - y) < 2e-4 * max(1.0, abs(x)) for x, y in zip(a, b)), (name, base, got)
+
+
+def test_grpo_adaptive_entropy_moves_one_delta_per_optimizer_step(tmp_path, tiny_tokenizer):
+    """The controller sees the whole accumulation window once, at the optimizer-step boundary: with GA=4 the
+    coefficient moves by exactly one delta per step, the first window applies no bonus (nothing measured yet), and
+    the measured entropy is checkpointed with the coefficient."""
+    model = make_tiny_model()
+    args = GRPOConfig(output_dir=str(tmp_path), **dict(COMMON, max_steps=3, save_strategy="steps", save_steps=3),
+                      num_generations=4, max_completion_length=6, gradient_accumulation_steps=4, loss_type="grpo",
+                      entropy_coef=0.02, use_adaptive_entropy=True, entropy_target=1e9, entropy_coef_delta=0.003,
+                      entropy_coef_max=1.0)
+    tr = GRPOTrainer(model, _len_reward, args, train_dataset=make_dataset("standard_prompt_only", 32),
+                     processing_class=tiny_tokenizer)
+    assert tr._last_world_entropy == float("inf")
+    tr.train()
+    # entropy <= target on every step -> +delta three times
+    assert abs(tr.entropy_coef - (0.02 + 3 * 0.003)) < 1e-9
+    assert 0.0 < tr._last_world_entropy < 20.0 and tr._entropy_window_stats is None
+    coefs = [h["entropy_coef"] for h in tr.state.log_history if "entropy_coef" in h]
+    assert [round(c, 6) for c in coefs] == [0.023, 0.026, 0.029]
+    assert any("policy_loss" in h for h in tr.state.log_history)
+    with open(os.path.join(str(tmp_path), "checkpoint-3", "entropy_ctrl_state.json")) as f:
+        st = json.load(f)
+    assert abs(st["entropy_coef"] - tr.entropy_coef) < 1e-12 and st["last_world_entropy"] == tr._last_world_entropy
+    # target below any entropy: the coefficient walks down, and the gate closes the bonus
+    model2 = make_tiny_model()
+    args2 = GRPOConfig(output_dir=str(tmp_path / "b"), **dict(COMMON, max_steps=2), num_generations=4,
+                       max_completion_length=6, gradient_accumulation_steps=2, loss_type="grpo", entropy_coef=0.02,
+                       use_adaptive_entropy=True, entropy_target=-1.0, entropy_coef_delta=0.003)
+    tr2 = GRPOTrainer(model2, _len_reward, args2, train_dataset=make_dataset("standard_prompt_only", 16),
+                      processing_class=tiny_tokenizer)
+    tr2.train()
+    assert abs(tr2.entropy_coef - (0.02 - 2 * 0.003)) < 1e-9 and tr2._last_world_entropy > -1.0
+
+
+def test_grpo_entropy_bonus_is_the_differentiable_mean_entropy():
+    """d(mean entropy)/d(hidden) through the chunked lm_head equals autograd over explicit logits."""
+    from trl_b200.ops import functional as ops
+
+    torch.manual_seed(0)
+    h = torch.randn(6, 16, requires_grad=True)
+    w = torch.randn(40, 16) * 0.3
+    y = torch.randint(0, 40, (6,))
+    _, ent = ops.lm_head_logprobs(h, w, y, 0.7, compute_entropy=True, entropy_grad=True)
+    ent.mean().backward()
+    h2 = h.detach().clone().requires_grad_()
+    z = (h2 @ w.t()) / 0.7
+    p = torch.softmax(z, -1)
+    (-(p * torch.log_softmax(z, -1)).sum(-1)).mean().backward()
+    assert torch.allclose(h.grad, h2.grad, atol=1e-5)
+    _, ent_stat = ops.lm_head_logprobs(h, w, y, 0.7, compute_entropy=True)
+    assert not ent_stat.requires_grad
+
+
+def test_grpo_vespo_weights_and_rollout_ratio_guards():
+    adv = torch.tensor([[1.0], [-1.0]])
+    mask = torch.ones(2, 4)
+    huge = torch.full((2, 4), 50.0)  # exp(200) overflows without the clamps
+    phi = GRPOTrainer.get_gamma_weights(adv, huge, mask, None, 2.0, 3.0, 3.0, 2.0)
+    assert torch.isfinite(phi).all() and (phi >= 0).all()
+    # hand value for a small ratio: log w = 0.1 * 4, phi = exp(k * lw + lam * (1 - exp(lw)))
+    lw = torch.tensor(0.4)
+    want = torch.exp(2.0 * lw + 3.0 * (1 - torch.exp(lw)))
+    got = GRPOTrainer.get_gamma_weights(adv[:1], torch.full((1, 4), 0.1), mask[:1], None, 2.0, 3.0, 3.0, 2.0)
+    assert torch.allclose(got.squeeze(), want, atol=1e-6)
+    # the rollout correction enters unmasked, as one more log factor of the sequence weight
+    isr = torch.full((1, 1), 2.0)
+    got2 = GRPOTrainer.get_gamma_weights(adv[:1], torch.zeros(1, 4), mask[:1], isr, 2.0, 3.0, 3.0, 2.0)
+    lw2 = torch.log(torch.tensor(2.0))
+    assert torch.allclose(got2.squeeze(), torch.exp(2.0 * lw2 + 3.0 * (1 - torch.exp(lw2))), atol=1e-6)
+
+    class _A:
+        vllm_importance_sampling_mode = "token_truncate"
+        vllm_importance_sampling_clip_max = None
+        vllm_importance_sampling_clip_min = None
+
+    class _T:
+        args = _A()
+
+    train, samp = torch.tensor([[0.0, 2.0]]), torch.tensor([[0.0, 0.0]])
+    r = GRPOTrainer._rollout_is_ratio(_T(), train, samp, torch.ones(1, 2))
+    assert torch.allclose(r, torch.exp(torch.tensor([[0.0, 2.0]])))  # no bound on either side
+    _A.vllm_importance_sampling_mode, _A.vllm_importance_sampling_clip_max = "token_mask", 3.0
+    r = GRPOTrainer._rollout_is_ratio(_T(), train, samp, torch.ones(1, 2))
+    assert r.tolist() == [[1.0, 0.0]]
+
+
+def test_deferred_metrics_resolve_to_global_ratios_and_means():
+    from trl_b200.trainer.utils import defer_mean, defer_ratio, resolve_deferred_metrics
+
+    m = {"entropy": [defer_ratio(torch.tensor(6.0), torch.tensor(4.0)), defer_ratio(torch.tensor(1.0), torch.tensor(0.0))],
+         "policy_loss": [defer_mean(torch.tensor(0.25))], "plain": [1.5]}
+    resolve_deferred_metrics(m)
+    assert m == {"entropy": [1.5, 1.0], "policy_loss": [0.25], "plain": [1.5]}

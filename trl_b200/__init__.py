@@ -1,7 +1,5 @@
 """trl_b200: a Blackwell-native post-training framework with TRL's public surface
 (exports of trl/__init__.py:28-73)."""
-import sys
-
 __version__ = "0.1.0.dev0"
 
 _import_structure = {
@@ -39,9 +37,8 @@ _import_structure = {
 }
 
 from . import _compat as _compat_mod  # noqa: E402
-from ._lazy_module import _LazyModule  # noqa: E402
+from ._lazy_module import lazy_exports  # noqa: E402
 
 _compat_mod.apply()
 
-sys.modules[__name__] = _LazyModule(__name__, globals()["__file__"], _import_structure, module_spec=__spec__,
-                                    extra_objects={"__version__": __version__})
+__getattr__, __dir__, __all__ = lazy_exports(__name__, _import_structure, globals())

@@ -1,52 +1,43 @@
-"""Attribute-triggered submodule import (role of trl/_lazy_module.py:22-79): ``import trl_b200`` stays cheap,
-``trl_b200.SFTTrainer`` imports only what that class needs.  Picklable through ``__reduce__``."""
+"""Lazy exports for a package ``__init__`` through the module-level ``__getattr__`` / ``__dir__`` hooks (PEP 562).
+
+``import trl_b200`` stays cheap; ``trl_b200.SFTTrainer`` imports only the submodule that defines the class.  The
+reference gets the same effect by swapping a ``ModuleType`` subclass into ``sys.modules`` (trl/_lazy_module.py:22-79);
+here the package keeps its real module object, so pickling, ``importlib.reload`` and ``__spec__`` need no special care.
+"""
 from __future__ import annotations
 
 import importlib
-import os
-from types import ModuleType
+from typing import Callable
 
 
-class _LazyModule(ModuleType):
-    def __init__(self, name, module_file, import_structure, module_spec=None, extra_objects=None):
-        super().__init__(name)
-        self._modules = set(import_structure.keys())
-        self._class_to_module = {}
-        for key, values in import_structure.items():
-            for v in values:
-                self._class_to_module[v] = key
-        self.__all__ = list(import_structure.keys()) + [v for vs in import_structure.values() for v in vs]
-        self.__file__ = module_file
-        self.__spec__ = module_spec
-        self.__path__ = [os.path.dirname(module_file)]
-        self._objects = extra_objects or {}
-        self._name = name
-        self._import_structure = import_structure
+def lazy_exports(package: str, structure: dict[str, list[str]], namespace: dict) -> tuple[Callable, Callable, list[str]]:
+    """Builds ``(__getattr__, __dir__, __all__)`` for ``package``.
 
-    def __dir__(self):
-        return sorted(set(super().__dir__()) | set(self.__all__))
+    ``structure`` maps a submodule path relative to the package (``"trainer.sft_trainer"``) to the names it exports.
+    A resolved attribute is cached in ``namespace`` (the package's ``globals()``), so the hook runs once per name.
+    """
+    owner = {name: sub for sub, names in structure.items() for name in names}
+    exported = sorted(set(owner) | {sub.split(".")[0] for sub in structure})
 
-    def __getattr__(self, name: str):
-        if name in self._objects:
-            return self._objects[name]
-        if name in self._class_to_module:
-            value = getattr(self._get_module(self._class_to_module[name]), name)
-        elif name in self._modules:
-            value = self._get_module(name)
+    def _load(sub: str):
+        try:
+            return importlib.import_module(f"{package}.{sub}")
+        except ModuleNotFoundError as e:
+            if e.name is not None and e.name.startswith(package):
+                raise AttributeError(f"module {package!r} has no attribute {sub!r}") from None
+            raise
+
+    def __getattr__(name: str):
+        if name in owner:
+            value = getattr(_load(owner[name]), name)
+        elif name.startswith("__"):
+            raise AttributeError(f"module {package!r} has no attribute {name!r}")
         else:
-            try:
-                value = importlib.import_module("." + name, self.__name__)
-            except ModuleNotFoundError:
-                raise AttributeError(f"module {self.__name__} has no attribute {name}") from None
-        setattr(self, name, value)
+            value = _load(name)  # a submodule, listed or not
+        namespace[name] = value
         return value
 
-    def _get_module(self, module_name: str):
-        try:
-            return importlib.import_module("." + module_name, self.__name__)
-        except Exception as e:
-            raise RuntimeError(f"Failed to import {self.__name__}.{module_name} because of the following error "
-                               f"(look up to see its traceback):\n{e}") from e
+    def __dir__():
+        return sorted(set(namespace) | set(exported))
 
-    def __reduce__(self):
-        return (self.__class__, (self._name, self.__file__, self._import_structure))
+    return __getattr__, __dir__, exported

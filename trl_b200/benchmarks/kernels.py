@@ -141,18 +141,54 @@ def main():
             out[f"tcgen05_2groups_splits{sp}_frac_of_copy_bw"] = byt / ms3 / 1e6 / hbm
         K.check_status(dev)
     elif a.kernel == "decode_gemm":
-        # the weight-streaming GEMMs of one Qwen2.5-7B decode step at batch a.batch: cuBLAS vs the split-K kernel
+        # the weight-streaming GEMMs of one Qwen2.5-7B decode step at batch a.batch: cuBLAS vs the stream-K kernel,
+        # each alone with a cold L2, then the four back to back (as in a layer) with and without dependent launch
         rows = []
-        for name, N, Kd in (("qkv", 4608, 3584), ("o_proj", 3584, 3584), ("gate_up", 37888, 3584), ("down", 3584, 18944)):
+        shapes = (("qkv", 4608, 3584, "acc"), ("o_proj", 3584, 3584, "acc"), ("gate_up", 37888, 3584, "swiglu"),
+                  ("down", 3584, 18944, "acc"), ("lm_head", a.v, 3584, "store"))
+        bufs = []
+        for name, N, Kd, kind in shapes:
             x = (torch.randn(a.batch, Kd, device=dev) * 0.5).to(torch.bfloat16)
             w = (torch.randn(N, Kd, device=dev) / Kd ** 0.5).to(torch.bfloat16)
-            y32 = torch.zeros(a.batch, N, device=dev)
-            t_lib = timeit(lambda: torch.nn.functional.linear(x, w), a.iters, a.warmup)
-            t_own = timeit(lambda: K.smallm_gemm_accumulate(x, w, y32), a.iters, a.warmup)
+            if kind == "acc":
+                y32 = torch.zeros(a.batch, N, device=dev)
+                own = lambda x=x, w=w, y32=y32: K.decode_gemm(x, w, y32=y32)
+            elif kind == "swiglu":
+                ob = torch.empty(a.batch, N // 2, device=dev, dtype=torch.bfloat16)
+                own = lambda x=x, w=w, ob=ob: K.decode_gemm(x, w, out=ob, swiglu=True)
+            else:
+                ob = torch.empty(a.batch, N, device=dev, dtype=torch.bfloat16)
+                own = lambda x=x, w=w, ob=ob: K.decode_gemm(x, w, out=ob)
+            lib_fn = lambda x=x, w=w: torch.nn.functional.linear(x, w)
+            t_lib = timeit(lib_fn, a.iters, a.warmup)
+            t_own = timeit(own, a.iters, a.warmup)
             byt = N * Kd * 2.0
             rows.append({"gemm": name, "weight_MB": round(byt / 1e6, 1), "cublas_us": round(t_lib * 1e3, 1),
-                         "splitk_us": round(t_own * 1e3, 1), "floor_us": round(byt / hbm / 1e3, 1)})
-        out.update(batch=a.batch, gemms=rows)
+                         "own_us": round(t_own * 1e3, 1), "floor_us": round(byt / hbm / 1e3, 1),
+                         "own_frac_of_copy_bw": round(byt / t_own / 1e6 / hbm, 3)})
+            if name != "lm_head":
+                bufs.append((own, lib_fn, byt))
+
+        def chain(fns, reps=28):
+            for _ in range(reps):
+                for f in fns:
+                    f()
+
+        total = 28 * sum(b for _, _, b in bufs)
+        res = {}
+        for label, fns, pdl in (("cublas", [b[1] for b in bufs], False), ("own", [b[0] for b in bufs], False),
+                                ("own_pdl", [b[0] for b in bufs], True)):
+            was = K.set_pdl(pdl)
+            g = torch.cuda.CUDAGraph()
+            chain(fns, 1)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g):
+                chain(fns)
+            ms = timeit(g.replay, a.iters, a.warmup)
+            K.set_pdl(was)
+            res[label + "_28_layers_ms"] = round(ms, 3)
+            res[label + "_frac_of_copy_bw"] = round(total / ms / 1e6 / hbm, 3)
+        out.update(batch=a.batch, gemms=rows, chain=res)
     elif a.kernel == "moe":
         # Qwen3-30B-A3B expert shapes: 128 experts, hidden 2048, expert FFN 768, top-8; a.t tokens
         E, H, I, k = 128, 2048, 768, 8

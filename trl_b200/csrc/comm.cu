@@ -422,6 +422,157 @@ allreduce_add_rmsnorm_kernel(Peers P, long long buf_elems, __nv_bfloat16* __rest
   if (grid_last_block(local_gate + 1) && threadIdx.x == 0) *epoch_ctr = epoch;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Consumer of the row-parallel decode GEMM that is fused with its all-reduce (decode_gemm.cu): every rank's GEMM
+// CTAs have added their fp32 partial sums into `delta` of EVERY rank and then bumped `arrive` on every rank.
+// This kernel waits (bounded) until `arrive` has reached `target` = ranks x CTAs per GEMM, then does
+// res += bf16(delta), delta = 0, y = rmsnorm(res) * w.  The last CTA to finish takes `target` off the counter, so
+// the counter never has to be cleared from the host and arrivals for the next use may already be coming in.
+// One CTA per row; `done` is a zero-initialised word that the kernel leaves at zero.
+// ------------------------------------------------------------------------------------------------
+template <int VPT>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_f32_wait_kernel(__nv_bfloat16* __restrict__ res, float* __restrict__ delta,
+                            const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int H, float eps,
+                            uint32_t* arrive, uint32_t target, uint32_t* done, int* status) {
+  __shared__ float red[8];
+  __shared__ int ok_s;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  if (tid == 0) {
+    int ok = 1;
+    const uint64_t t0 = globaltimer_ns();
+    while (ld_acquire_sys(arrive) < target) {
+      if (globaltimer_ns() - t0 > kPeerWaitNs) {
+        report_error(status, ERR_WAIT_TIMEOUT, 610, (int)ld_acquire_sys(arrive));
+        ok = 0;
+        break;
+      }
+      __nanosleep(32);
+    }
+    ok_s = ok;
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  const int nvec = H >> 3;
+  uint4* xr = reinterpret_cast<uint4*>(res + (size_t)row * H);
+  float4* dr = reinterpret_cast<float4*>(delta + (size_t)row * H);
+  float buf[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * 256;
+    if (v < nvec) {
+      uint4 a = xr[v];
+      uint32_t* au = reinterpret_cast<uint32_t*>(&a);
+      const float4 d0 = __ldcg(dr + 2 * v), d1 = __ldcg(dr + 2 * v + 1);  // written by peers: read at L2
+      dr[2 * v] = make_float4(0.f, 0.f, 0.f, 0.f);
+      dr[2 * v + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float dv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16(au[j]);
+        // the block output is rounded to bf16 first (what an unfused GEMM + all-reduce would hand over)
+        const float2 s = unpack_bf16(pack_bf16(dv[2 * j], dv[2 * j + 1]));
+        au[j] = pack_bf16(f.x + s.x, f.y + s.y);
+      }
+      xr[v] = a;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 r = unpack_bf16(au[j]);
+        buf[i][2 * j] = r.x; buf[i][2 * j + 1] = r.y;
+        ss += r.x * r.x + r.y * r.y;
+      }
+    }
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) red[wid] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) tot += red[k];
+  const float rstd = rsqrtf(tot / (float)H + eps);
+  uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * H);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * 256;
+    if (v < nvec) {
+      const uint4 wv = wr[v];
+      const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wv);
+      uint4 o;
+      uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 g = unpack_bf16(wu[j]);
+        ou[j] = pack_bf16(buf[i][2 * j] * rstd * g.x, buf[i][2 * j + 1] * rstd * g.y);
+      }
+      yr[v] = o;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(done, 1u) == gridDim.x - 1) {  // every CTA of this launch is past its wait
+      *done = 0;
+      atomicSub(arrive, target);
+    }
+  }
+}
+
+// Token agreement of a tensor-parallel decode group: rank 0's sampled tokens (and their log-probs) are the group's.
+// Rank 0 stores them into every peer's mailbox and raises the peer's flag to the call's epoch; the other ranks wait
+// (bounded) for their flag and copy the mailbox over their own samples.  With partial sums added in arrival order
+// (atomics) the ranks' logits may differ in the last bit, so sampling on every rank from "identical" logits is not
+// safe any more; one small message per step is.  mail[p] = rank p's mailbox (B ints then B floats), flag[p] its flag.
+struct TokenSync {
+  int* mail[MAX_PEERS];
+  uint32_t* flag[MAX_PEERS];
+  int rank, world;
+};
+
+__global__ void __launch_bounds__(256) tp_token_sync_kernel(TokenSync S, int* __restrict__ tok, float* __restrict__ logp,
+                                                            int B, uint32_t* epoch_ctr, int* status) {
+  __shared__ int ok_s;
+  const uint32_t epoch = *epoch_ctr + 1;
+  if (S.rank == 0) {
+    for (int p = 1; p < S.world; ++p) {
+      for (int i = threadIdx.x; i < B; i += blockDim.x) {
+        S.mail[p][i] = tok[i];
+        reinterpret_cast<float*>(S.mail[p] + B)[i] = logp[i];
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x > 0 && threadIdx.x < S.world) st_release_sys(S.flag[threadIdx.x], epoch);
+  } else {
+    if (threadIdx.x == 0) {
+      int ok = 1;
+      const uint64_t t0 = globaltimer_ns();
+      while ((int32_t)(ld_acquire_sys(S.flag[S.rank]) - epoch) < 0) {
+        if (globaltimer_ns() - t0 > kPeerWaitNs) {
+          report_error(status, ERR_WAIT_TIMEOUT, 620, (int)epoch);
+          ok = 0;
+          break;
+        }
+        __nanosleep(32);
+      }
+      ok_s = ok;
+    }
+    __syncthreads();
+    if (ok_s) {
+      const int* mail = S.mail[S.rank];
+      for (int i = threadIdx.x; i < B; i += blockDim.x) {
+        tok[i] = __ldcg(mail + i);
+        logp[i] = __ldcg(reinterpret_cast<const float*>(mail + B) + i);
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *epoch_ctr = epoch;
+}
+
 // Self-test of the bounded-wait discipline: one thread polls a flag with a time budget, exactly like the peer
 // waits above; when nothing sets the flag the kernel records ERR_WAIT_TIMEOUT and returns, and the context stays
 // usable.  Used by the failure-detection test.
@@ -534,6 +685,36 @@ TRLB_API int trlb_allreduce_add_rmsnorm(const unsigned long long* bufs, const un
   if (vpt <= 1) allreduce_add_rmsnorm_kernel<1><<<T, 256, 0, st>>>(P, buf_elems, R, W, Y, H, eps, epoch_ctr, local_gate, channel, status);
   else if (vpt <= 2) allreduce_add_rmsnorm_kernel<2><<<T, 256, 0, st>>>(P, buf_elems, R, W, Y, H, eps, epoch_ctr, local_gate, channel, status);
   else allreduce_add_rmsnorm_kernel<4><<<T, 256, 0, st>>>(P, buf_elems, R, W, Y, H, eps, epoch_ctr, local_gate, channel, status);
+  return (int)cudaGetLastError();
+}
+
+// res[T,H] += bf16(delta32[T,H]) once `arrive` has reached `target`; delta32 is cleared, y = rmsnorm(res) * w and the
+// last CTA subtracts `target` from `arrive` (see add_rmsnorm_f32_wait_kernel).  `done`: zero-initialised scratch word.
+TRLB_API int trlb_add_rmsnorm_f32_wait(void* res, float* delta, const void* w, void* y, int T, int H, float eps,
+                                       unsigned* arrive, unsigned target, unsigned* done, int* status, cudaStream_t st) {
+  if (T == 0) return 0;
+  if (H % 8 != 0 || H > 8192 || T > 4 * trlb_host::sm_count()) return -1;  // every CTA must become resident
+  auto R = (__nv_bfloat16*)res; auto W = (const __nv_bfloat16*)w; auto Y = (__nv_bfloat16*)y;
+  const int vpt = (H / 8 + 255) / 256;
+  auto kern = vpt <= 1 ? add_rmsnorm_f32_wait_kernel<1>
+                       : (vpt <= 2 ? add_rmsnorm_f32_wait_kernel<2> : add_rmsnorm_f32_wait_kernel<4>);
+  return (int)trlb_host::launch_kernel(kern, dim3(T), dim3(256), 0, st, trlb_host::pdl_enabled(), R, delta, W, Y, H, eps,
+                                       arrive, target, done, status);
+}
+
+// Rank 0's tok / logp (B entries each) become every rank's; mails[p] / flags[p] are rank p's mailbox (2 * B words)
+// and flag word in symmetric memory; epoch_ctr is a local zero-initialised word.
+TRLB_API int trlb_tp_token_sync(const unsigned long long* mails, const unsigned long long* flags, int rank, int world,
+                                int* tok, float* logp, int B, unsigned* epoch_ctr, int* status, cudaStream_t st) {
+  if (world < 2) return 0;
+  if (world > MAX_PEERS) return -1;
+  TokenSync S;
+  for (int p = 0; p < MAX_PEERS; ++p) {
+    S.mail[p] = p < world ? reinterpret_cast<int*>(mails[p]) : nullptr;
+    S.flag[p] = p < world ? reinterpret_cast<uint32_t*>(flags[p]) : nullptr;
+  }
+  S.rank = rank; S.world = world;
+  tp_token_sync_kernel<<<1, 256, 0, st>>>(S, tok, logp, B, epoch_ctr, status);
   return (int)cudaGetLastError();
 }
 

@@ -57,6 +57,18 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+// A kernel launched with the programmatic-serialization attribute may start while its predecessor in the
+// stream still runs.  pdl_wait() returns once the predecessor has completed and its memory is visible; work
+// that does not depend on the predecessor (barrier set-up, TMEM allocation, streaming weights) goes before
+// it.  pdl_launch_dependents() lets the successor start early; a kernel that allocates TMEM calls it only
+// after its allocation, so that a successor resident on the same SM can never hold the TMEM columns an
+// unfinished predecessor CTA still has to allocate.  Both are no-ops in a kernel launched the ordinary way.
+// Every kernel launched with the attribute executes pdl_wait() at least once, which keeps completion
+// transitive along a chain of such kernels.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- mbarrier ---------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
@@ -179,6 +191,17 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32]) {
       : "r"(taddr)
       : "memory");
 }
+// 32 lanes x 16 consecutive fp32 columns.
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, float (&v)[16]) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 // 32 lanes x 8 consecutive fp32 columns.
 __device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, float (&v)[8]) {
   uint32_t* r = reinterpret_cast<uint32_t*>(v);
@@ -227,4 +250,24 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_elems,
                       uint64_t stride2_elems, uint32_t b0, uint32_t b1, uint32_t b2);
 int sm_count();
+// Process-wide switch for programmatic dependent launch of the decode-path kernels (trlb_set_pdl).
+bool pdl_enabled();
+
+// Launches `kernel` on `st`; with `pdl` the launch carries the programmatic stream serialization attribute
+// (the kernel must then call trlb::pdl_wait() before it touches anything its predecessor wrote).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 }  // namespace trlb_host

@@ -57,6 +57,87 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, long
   }
 }
 
+// Variant fed by the stream-K decode GEMM: the fused QKV row arrives as fp32 partial sums, which are consumed
+// (bias added, optional per-head RMSNorm of q and k as in Qwen3, RoPE, cache append) and cleared here, so the next
+// step's GEMM accumulates from zero without a memset.  One warp per (token, head); each lane owns the rotation pairs
+// (f, f + D/2) for f = lane, lane + 32, ...
+__global__ void __launch_bounds__(256)
+rope_kv_write_f32_kernel(float* __restrict__ acc, long long row_stride, const __nv_bfloat16* __restrict__ bias,
+                         const __nv_bfloat16* __restrict__ q_norm, const __nv_bfloat16* __restrict__ k_norm,
+                         float norm_eps, const int* __restrict__ seq_lens, const int* __restrict__ slot_ids,
+                         const int* __restrict__ block_table, int max_blocks, int block_size,
+                         __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc,
+                         int B, int Hq, int Hk, int D, float log2_theta, int v_t) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int half = D >> 1, heads = Hq + 2 * Hk;
+  const int lane = threadIdx.x & 31;
+  const int warps_total = (gridDim.x * blockDim.x) >> 5;
+  for (int item = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; item < B * heads; item += warps_total) {
+    const int b = item / heads, head = item % heads;
+    const int slot = slot_ids ? slot_ids[b] : b;
+    const int pos = seq_lens[slot];
+    float* src = acc + (size_t)b * row_stride + (size_t)head * D;
+    const __nv_bfloat16* bsrc = bias ? bias + (size_t)head * D : nullptr;
+    float lo[2], hi[2];  // D <= 128: at most two pairs per lane
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int f = lane + 32 * j;
+      lo[j] = hi[j] = 0.f;
+      if (f < half) {
+        lo[j] = src[f];
+        hi[j] = src[half + f];
+        src[f] = 0.f;
+        src[half + f] = 0.f;
+        if (bsrc) { lo[j] += __bfloat162float(bsrc[f]); hi[j] += __bfloat162float(bsrc[half + f]); }
+        // from here on the projection has the precision of the unfused path (a bf16 GEMM output)
+        lo[j] = __bfloat162float(__float2bfloat16(lo[j]));
+        hi[j] = __bfloat162float(__float2bfloat16(hi[j]));
+        ss += lo[j] * lo[j] + hi[j] * hi[j];
+      }
+    }
+    if (pos < 0) continue;  // inactive slot: sums are dropped
+    const __nv_bfloat16* nw = head < Hq ? q_norm : (head < Hq + Hk ? k_norm : nullptr);
+    if (nw != nullptr) {
+      const float rstd = rsqrtf(warp_sum(ss) / (float)D + norm_eps);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int f = lane + 32 * j;
+        if (f < half) {
+          // the normalised value is rounded to bf16 before the rotation, as the unfused path does
+          lo[j] = __bfloat162float(__float2bfloat16(lo[j] * rstd * __bfloat162float(nw[f])));
+          hi[j] = __bfloat162float(__float2bfloat16(hi[j] * rstd * __bfloat162float(nw[half + f])));
+        }
+      }
+    }
+    const int blk = block_table[(size_t)slot * max_blocks + pos / block_size];
+    const size_t cache_row = ((size_t)blk * block_size + pos % block_size) * Hk;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int f = lane + 32 * j;
+      if (f >= half) continue;
+      if (head < Hq + Hk) {
+        const float l = lo[j], h = hi[j];
+        const float inv = exp2f(-log2_theta * (float)(2 * f) / (float)D);
+        float sn, cs;
+        sincosf((float)pos * inv, &sn, &cs);
+        __nv_bfloat16* dst = head < Hq ? q_out + ((size_t)b * Hq + head) * D : kc + (cache_row + (head - Hq)) * D;
+        dst[f] = __float2bfloat16(l * cs - h * sn);
+        dst[half + f] = __float2bfloat16(h * cs + l * sn);
+      } else if (v_t) {
+        __nv_bfloat16* dst = vc + (((size_t)blk * Hk + (head - Hq - Hk)) * D) * block_size + pos % block_size;
+        dst[(size_t)f * block_size] = __float2bfloat16(lo[j]);
+        dst[(size_t)(half + f) * block_size] = __float2bfloat16(hi[j]);
+      } else {
+        __nv_bfloat16* dst = vc + (cache_row + (head - Hq - Hk)) * D;
+        dst[f] = __float2bfloat16(lo[j]);
+        dst[half + f] = __float2bfloat16(hi[j]);
+      }
+    }
+  }
+}
+
 // k,v [T,Hk,D] (already rotated) of packed prompts -> cache.  tok_slot[t], tok_pos[t] give the
 // destination sequence slot and position of token t.
 __global__ void kv_write_prefill_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
@@ -338,6 +419,22 @@ TRLB_API int trlb_rope_kv_write(const void* qkv, long long row_stride, const int
   return (int)cudaGetLastError();
 }
 
+// fp32 sums in, cleared on the way (see rope_kv_write_f32_kernel).  bias / q_norm / k_norm may be null.  D <= 128.
+TRLB_API int trlb_rope_kv_write_f32(float* acc, long long row_stride, const void* bias, const void* q_norm,
+                                    const void* k_norm, float norm_eps, const int* seq_lens, const int* slot_ids,
+                                    const int* block_table, int max_blocks, int block_size, void* q_out, void* kc,
+                                    void* vc, int B, int Hq, int Hk, int D, float theta, int v_t, cudaStream_t st) {
+  if (B == 0) return 0;
+  if (D > 128 || (D & 1)) return -1;
+  const int items = B * (Hq + 2 * Hk);
+  const int grid = (items + 7) / 8;
+  return (int)trlb_host::launch_kernel(rope_kv_write_f32_kernel, dim3(grid), dim3(256), 0, st, trlb_host::pdl_enabled(), acc,
+                                       row_stride, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)q_norm,
+                                       (const __nv_bfloat16*)k_norm, norm_eps, seq_lens, slot_ids, block_table, max_blocks,
+                                       block_size, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, B, Hq, Hk,
+                                       D, log2f(theta), v_t);
+}
+
 TRLB_API int trlb_kv_write_prefill(const void* k, const void* v, long long k_stride, long long v_stride,
                                    const int* tok_slot, const int* tok_pos, const int* block_table, int max_blocks,
                                    int block_size, void* kc, void* vc, int T, int Hk, int D, int v_t, cudaStream_t st) {
@@ -473,6 +570,8 @@ TRLB_API int trlb_paged_decode_attn_noalloc(const void* q, const void* kc, const
                                                               (const __nv_bfloat16*)vc, seq_lens, slot_ids, block_table,
                                                               max_blocks, block_size, Hq, Hk, scale, splits, part_o,
                                                               part_ml);
+  const cudaError_t first = cudaGetLastError();
+  if (first != cudaSuccess) return (int)first;  // the combine kernel would read partials that were never written
   paged_attn_combine_kernel<128><<<B * Hq, 128, 0, st>>>(part_o, part_ml, splits, (__nv_bfloat16*)out, B * Hq);
   return (int)cudaGetLastError();
 }

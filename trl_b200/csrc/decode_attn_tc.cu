@@ -127,6 +127,8 @@ paged_decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();  // after the TMEM allocation, see common.cuh
+  pdl_wait();               // q and the newest K/V rows come from the kernel before this one
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -409,6 +411,8 @@ paged_decode_attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_k, const _
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();  // after the TMEM allocation, see common.cuh
+  pdl_wait();               // q and the newest K/V rows come from the kernel before this one
 
   if (warp == 0) {
     // ---------------- TMA producer (same ring as the one-group kernel) ----------------
@@ -680,10 +684,13 @@ static int decode_attn_tc_launch(const void* q, const void* kc, const void* vct,
   p.part_o = part_o; p.part_ml = part_ml; p.status = status; p.out = (__nv_bfloat16*)out;
   const int items = B * Hk * splits;
   const int grid = items < trlb_host::sm_count() ? items : trlb_host::sm_count();
+  const bool pdl = trlb_host::pdl_enabled();
+  cudaError_t le;
   if (groups == 2)
-    paged_decode_attn_tc2_kernel<<<grid, TC2_THREADS, TC2_SMEM, st>>>(tk, tv, p);
+    le = trlb_host::launch_kernel(paged_decode_attn_tc2_kernel, dim3(grid), dim3(TC2_THREADS), TC2_SMEM, st, pdl, tk, tv, p);
   else
-    paged_decode_attn_tc_kernel<<<grid, TC_THREADS, TC_SMEM, st>>>(tk, tv, p);
+    le = trlb_host::launch_kernel(paged_decode_attn_tc_kernel, dim3(grid), dim3(TC_THREADS), TC_SMEM, st, pdl, tk, tv, p);
+  if (le != cudaSuccess) return (int)le;
   if (splits > 1)
     paged_attn_combine_kernel<128><<<B * Hq, 128, 0, st>>>(part_o, part_ml, splits, (__nv_bfloat16*)out, B * Hq);
   return (int)cudaGetLastError();

@@ -194,6 +194,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_f32_row_kernel(__nv_bfloat16*
                                                                  const __nv_bfloat16* __restrict__ w,
                                                                  __nv_bfloat16* __restrict__ y, int H, float eps) {
   __shared__ float red[8];
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   const int nvec = H >> 3;
   uint4* xr = reinterpret_cast<uint4*>(res + (size_t)row * H);
@@ -604,10 +606,9 @@ TRLB_API int trlb_add_rmsnorm_f32(void* res, float* delta, const void* w, void* 
   if (H % 8 != 0 || H > 8192) return -1;
   auto R = (__nv_bfloat16*)res; auto W = (const __nv_bfloat16*)w; auto Y = (__nv_bfloat16*)y;
   const int vpt = (H / 8 + 255) / 256;
-  if (vpt <= 1) add_rmsnorm_f32_row_kernel<1><<<T, 256, 0, st>>>(R, delta, W, Y, H, eps);
-  else if (vpt <= 2) add_rmsnorm_f32_row_kernel<2><<<T, 256, 0, st>>>(R, delta, W, Y, H, eps);
-  else add_rmsnorm_f32_row_kernel<4><<<T, 256, 0, st>>>(R, delta, W, Y, H, eps);
-  return (int)cudaGetLastError();
+  const bool pdl = trlb_host::pdl_enabled();
+  auto kern = vpt <= 1 ? add_rmsnorm_f32_row_kernel<1> : (vpt <= 2 ? add_rmsnorm_f32_row_kernel<2> : add_rmsnorm_f32_row_kernel<4>);
+  return (int)trlb_host::launch_kernel(kern, dim3(T), dim3(256), 0, st, pdl, R, delta, W, Y, H, eps);
 }
 
 // res[T,H] += delta[T,H] in place, y = rmsnorm(res) * w  (H <= 8192)

@@ -42,6 +42,8 @@ struct GemmParams {
   int* part_arg;       // [n_splits, M]: argmax column
   const float* lse;    // [M]  (EPI_DZ)
   const float* grow;   // [M]  dL/dlogp per row (EPI_DZ)
+  const float* ent;    // [M]  entropy per row and
+  const float* gent;   // [M]  dL/dentropy per row (EPI_DZ, both null when the entropy carries no gradient)
   int* status;
   // ---- all-gather fused into the GEMM (EPI_STORE only; ag_world == 0 disables) ----
   // B (the weight) lives at element offset ag_w_off of a bf16 buffer of ag_total elements that every rank
@@ -379,10 +381,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       float run_max = -INFINITY, run_sum = 0.f, run_zsum = 0.f, tgt = 0.f;
       int arg = 0;
       long long label = -1;
-      float lse_row = 0.f, g_row = 0.f;
+      float lse_row = 0.f, g_row = 0.f, ent_row = 0.f, gent_row = 0.f;
       if (EPI != EPI_STORE && row_ok) {
         label = p.labels[row];
-        if (EPI == EPI_DZ) { lse_row = p.lse[row]; g_row = p.grow[row]; }
+        if (EPI == EPI_DZ) {
+          lse_row = p.lse[row];
+          g_row = p.grow[row];
+          if (p.gent != nullptr) { ent_row = p.ent[row]; gent_row = p.gent[row]; }
+        }
       }
       for (int nt = n0; nt < n1 && ok; ++nt) {
         if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, 400 + acc)) { ok = false; break; }
@@ -457,12 +463,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (row_ok && cbase < p.N) {
               __nv_bfloat16* dst = p.C + (long long)row * p.ldc + cbase;
               const float sc = p.inv_temp;
-              const float gs = g_row * sc;
+              const float gs = g_row * sc, ge = gent_row * sc;
               const int rel = (int)(label - cbase);
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
-                const float pr = __expf(fmaf(v[i], sc, -lse_row));
-                v[i] = gs * ((i == rel ? 1.f : 0.f) - pr);
+                // d logp_label / dz_j = (1[j = label] - p_j) / T;  dH / dz_j = -p_j (log p_j + H) / T
+                const float lp = fmaf(v[i], sc, -lse_row);
+                const float pr = __expf(lp);
+                v[i] = gs * ((i == rel ? 1.f : 0.f) - pr) - ge * pr * (lp + ent_row);
               }
               if (cbase + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
@@ -643,12 +651,14 @@ TRLB_API int trlb_lmhead_fwd(const void* H, const void* W, const long long* labe
 }
 
 // Fused lm_head backward, stage 1: dZ[M,V] (bf16, row stride ldz) = grow * (1[label] - softmax(z/T)) / T
+// and, when gent is given, - gent * p * (log p + ent) / T (the gradient of the row's entropy); ent / gent may be null.
 TRLB_API int trlb_lmhead_dz(const void* H, const void* W, const long long* labels, const float* lse, const float* grow,
-                            void* dZ, int M, int V, int K, long long ldh, long long ldw, long long ldz, float inv_temp,
-                            int* status, cudaStream_t stream) {
+                            const float* ent, const float* gent, void* dZ, int M, int V, int K, long long ldh,
+                            long long ldw, long long ldz, float inv_temp, int* status, cudaStream_t stream) {
   GemmParams p = {};
   p.M = M; p.N = V; p.K = K;
   p.labels = labels; p.inv_temp = inv_temp; p.lse = lse; p.grow = grow;
+  p.ent = gent != nullptr ? ent : nullptr; p.gent = ent != nullptr ? gent : nullptr;
   p.C = (__nv_bfloat16*)dZ; p.ldc = ldz;
   p.status = status;
   return launch_gemm<EPI_DZ>(H, W, p, ldh, ldw, stream);

@@ -61,6 +61,17 @@ int sm_count() {
   return n;
 }
 
+static bool g_pdl = false;
+bool pdl_enabled() { return g_pdl; }
+
 }  // namespace trlb_host
+
+// Switches programmatic dependent launch of the decode-path kernels on or off for this process; returns the
+// previous setting.  Set it before a CUDA graph is captured: the choice is baked into the graph's edges.
+TRLB_API int trlb_set_pdl(int on) {
+  const bool was = trlb_host::g_pdl;
+  trlb_host::g_pdl = on != 0;
+  return was ? 1 : 0;
+}
 
 TRLB_API int trlb_sm_count() { return trlb_host::sm_count(); }

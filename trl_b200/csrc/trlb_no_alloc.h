@@ -26,6 +26,13 @@
 //     kernels overwrite every partial they later read, so nothing has to start at zero; but two
 //     calls that overlap on the GPU (different streams, no ordering between them) race on the
 //     array.  Order them on one stream or with events.
+//   * Host threads: the looked-up addresses are cached per device ordinal without a lock.  Two host
+//     threads that make the first call on one device at the same moment both look the addresses up
+//     and store the same values, which is harmless, but it is cleaner to make the first call from
+//     one thread (during set-up) before others use the device.  The cache does not survive
+//     cudaDeviceReset: do not reset a device between calls.
+//   * An error left behind by earlier work on the device (a sticky error) is returned by this call's
+//     launch check like by any other CUDA call; it does not come from this entry point.
 //   * No cudaMalloc, cudaFree or allocating library routine is called on any path.
 #pragma once
 #include <cuda_runtime.h>

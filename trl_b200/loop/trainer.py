@@ -10,6 +10,8 @@ optimizer*.pt, scheduler.pt, rng_state_<rank>.pth, training_args.json}``.
 """
 from __future__ import annotations
 
+import contextlib
+
 import json
 import math
 import os
@@ -380,11 +382,26 @@ class Trainer:
     def training_step(self, model, inputs, num_items_in_batch=None):
         model.train()
         inputs = self._prepare_inputs(inputs)
-        loss = self.compute_loss(model, inputs, num_items_in_batch=num_items_in_batch)
+        with self._activation_offload_context():
+            loss = self.compute_loss(model, inputs, num_items_in_batch=num_items_in_batch)
         if (not self.model_accepts_loss_kwargs or num_items_in_batch is None) and self.compute_loss_func is None:
             loss = loss / self.current_gradient_accumulation_steps
         self.engine.backward(loss)
         return loss.detach()
+
+    def _activation_offload_context(self):
+        """Saved activations of the forward go to pinned host memory when ``args.activation_offloading`` is set
+        (every trainer: trl/trainer/sft_trainer.py:1840-1842 and the same lines of the DPO / KTO / reward trainers).
+        The context is built once; trainers that wrap only part of their forward themselves set
+        ``self._own_offload_scope``."""
+        if not getattr(self.args, "activation_offloading", False) or getattr(self, "_own_offload_scope", False):
+            return contextlib.nullcontext()
+        ctx = getattr(self, "_offload_ctx", None)
+        if ctx is None:
+            from ..models.activation_offloading import get_act_offloading_ctx_manager
+
+            ctx = self._offload_ctx = get_act_offloading_ctx_manager(self.model)
+        return ctx
 
     def _count_items(self, batches) -> Optional[torch.Tensor]:
         """Global number of supervised tokens over the accumulation window (HF ``num_items_in_batch``)."""
@@ -507,6 +524,8 @@ class Trainer:
         self.control = self.callback_handler.call_event("on_step_begin", a, st, self.control)
         total = torch.zeros((), device=a.device)
         for i, b in enumerate(batches):
+            # True while the last micro-batch of the accumulation window runs (accelerate's ``sync_gradients``)
+            self.sync_gradients = i == len(batches) - 1
             loss = self.training_step(self.model, b, n_items)
             keep_nan = not a.logging_nan_inf_filter or "underflow_overflow" in str(a.debug)
             total += loss if keep_nan else torch.nan_to_num(loss.float(), nan=0.0, posinf=0.0, neginf=0.0)
@@ -557,6 +576,9 @@ class Trainer:
         mode = "train" if self.model is None or self.model.training else "eval"
         own = self._metrics[mode]
         if own:
+            from ..trainer.utils import resolve_deferred_metrics
+
+            resolve_deferred_metrics(own)  # one collective for everything the micro-batches recorded
             avg = {k: sum(v) / len(v) for k, v in own.items() if len(v)}
             if D.world_size() > 1 and os.environ.get("TRL_B200_PROFILE_MAX_OVER_RANKS", "0") == "1":
                 # a phase is as slow as its slowest rank: report the maximum of the phase timers (one small object
@@ -670,7 +692,13 @@ class Trainer:
                 torch.save(self.engine.optimizer_state_dict(), os.path.join(folder, name))
             if a.should_save:
                 torch.save(self.lr_scheduler.state_dict(), os.path.join(folder, "scheduler.pt"))
-            rng = {"python": random.getstate(), "numpy": np.random.get_state(), "cpu": torch.get_rng_state()}
+            # plain containers and tensors only, so that every file of a checkpoint loads with weights_only=True
+            py = random.getstate()
+            npst = np.random.get_state()
+            rng = {"python": [py[0], list(py[1]), py[2]],
+                   "numpy": {"name": npst[0], "keys": torch.from_numpy(npst[1].astype(np.int64)), "pos": int(npst[2]),
+                             "has_gauss": int(npst[3]), "cached_gaussian": float(npst[4])},
+                   "cpu": torch.get_rng_state()}
             if torch.cuda.is_available() and a.device.type == "cuda":
                 rng["cuda"] = torch.cuda.get_rng_state()
             torch.save(rng, os.path.join(folder, f"rng_state_{D.rank()}.pth" if D.world_size() > 1 else "rng_state.pth"))
@@ -722,21 +750,23 @@ class Trainer:
         if saved and sorted(expect) != saved and hasattr(self.engine, "load_optimizer_state_resharded"):
             # elastic resume: the checkpoint was written with another world size or shard mode.  Every rank reads all
             # optimizer files and keeps the slices it owns now.
-            shards = [torch.load(os.path.join(folder, f), map_location="cpu", weights_only=False) for f in saved]
+            shards = [torch.load(os.path.join(folder, f), map_location="cpu", weights_only=True) for f in saved]
             self.engine.load_optimizer_state_resharded(shards)
         elif os.path.exists(op):
-            self.engine.load_optimizer_state_dict(torch.load(op, map_location="cpu", weights_only=False))
+            self.engine.load_optimizer_state_dict(torch.load(op, map_location="cpu", weights_only=True))
         elif getattr(m, "_is_native", False):
             self.engine.refresh_master_from_params() if hasattr(self.engine, "refresh_master_from_params") else None
         sc = os.path.join(folder, "scheduler.pt")
         if os.path.exists(sc):
-            self.lr_scheduler.load_state_dict(torch.load(sc, weights_only=False))
+            self.lr_scheduler.load_state_dict(torch.load(sc, weights_only=True))
         for cand in (f"rng_state_{D.rank()}.pth", "rng_state.pth"):
             rp = os.path.join(folder, cand)
             if os.path.exists(rp):
-                rng = torch.load(rp, weights_only=False)
-                random.setstate(rng["python"])
-                np.random.set_state(rng["numpy"])
+                rng = torch.load(rp, weights_only=True)
+                py, npst = rng["python"], rng["numpy"]
+                random.setstate((py[0], tuple(py[1]), py[2]))
+                np.random.set_state((npst["name"], npst["keys"].numpy().astype(np.uint32), npst["pos"], npst["has_gauss"],
+                                     npst["cached_gaussian"]))
                 torch.set_rng_state(rng["cpu"])
                 if "cuda" in rng and torch.cuda.is_available():
                     torch.cuda.set_rng_state(rng["cuda"])

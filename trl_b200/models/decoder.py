@@ -332,9 +332,15 @@ class CausalLM(nn.Module):
         for li, layer in enumerate(self.layers):
             if (self.gradient_checkpointing and self.training and torch.is_grad_enabled()
                     and (n_ckpt is None or li < n_ckpt)):
-                from torch.utils.checkpoint import checkpoint
+                from .activation_offloading import offload_checkpoint, offloading_active
 
-                x = checkpoint(layer, x, ctx, use_reentrant=False)
+                if getattr(self, "offload_checkpoint_inputs", False) and offloading_active():
+                    # the layer input is saved through the saved-tensor hooks, i.e. it goes to pinned host memory
+                    x = offload_checkpoint(lambda h, layer=layer: layer(h, ctx), x)
+                else:
+                    from torch.utils.checkpoint import checkpoint
+
+                    x = checkpoint(layer, x, ctx, use_reentrant=False)
             else:
                 x = layer(x, ctx)
         return self.final_norm(x)

@@ -111,13 +111,14 @@ def lmhead_forward(hidden, weight, labels, inv_temp: float, want_entropy=True, w
     return logp, ent, lse, amax
 
 
-def lmhead_dz(hidden, weight, labels, lse, grow, inv_temp: float, out=None):
-    """dZ[M,V] = grow * (1[label] - softmax(z/T)) / T as bf16 (stage 1 of the lm_head backward)."""
+def lmhead_dz(hidden, weight, labels, lse, grow, inv_temp: float, out=None, ent=None, gent=None):
+    """dZ[M,V] = grow * (1[label] - softmax(z/T)) / T as bf16 (stage 1 of the lm_head backward); with ``ent`` and
+    ``gent`` (entropy and its incoming gradient per row) the entropy's gradient -gent * p (log p + H) / T is added."""
     M, K = hidden.shape
     V = weight.shape[0]
     if out is None:
         out = torch.empty(M, V, dtype=torch.bfloat16, device=hidden.device)
-    rc = lib().trlb_lmhead_dz(_p(hidden), _p(weight), _p(labels), _p(lse), _p(grow), _p(out), c_int(M), c_int(V),
+    rc = lib().trlb_lmhead_dz(_p(hidden), _p(weight), _p(labels), _p(lse), _p(grow), _p(ent), _p(gent), _p(out), c_int(M), c_int(V),
                               c_int(K), c_longlong(hidden.stride(0)), c_longlong(weight.stride(0)),
                               c_longlong(out.stride(0)), c_float(inv_temp), _p(status_buffer(hidden.device)), _s())
     _chk(rc, "trlb_lmhead_dz")
@@ -125,30 +126,33 @@ def lmhead_dz(hidden, weight, labels, lse, grow, inv_temp: float, out=None):
 
 
 class _LmHeadLogprobFn(torch.autograd.Function):
-    """log p(label) (+ entropy, no grad) from hidden @ W^T without materialising fp32 logits.
+    """log p(label) (+ entropy) from hidden @ W^T without materialising fp32 logits.
 
     Backward recomputes the logits tile by tile inside the dZ kernel (bf16 dZ in token chunks),
-    then dH = dZ @ W and dW += dZ^T @ H are plain library GEMMs.
+    then dH = dZ @ W and dW += dZ^T @ H.  The entropy carries a gradient only with ``entropy_grad``
+    (the GRPO entropy bonus); otherwise it is a statistic, as in trl/trainer/utils.py:1291-1424.
     """
 
     CHUNK = 8192
 
     @staticmethod
-    def forward(ctx, hidden, weight, labels, inv_temp, want_entropy, want_argmax):
+    def forward(ctx, hidden, weight, labels, inv_temp, want_entropy, want_argmax, entropy_grad=False):
         hidden = hidden.contiguous()
         labels = labels.to(torch.int64).contiguous()
         logp, ent, lse, amax = lmhead_forward(hidden, weight, labels, inv_temp, want_entropy, want_argmax)
-        ctx.save_for_backward(hidden, weight, labels, lse)
+        ctx.entropy_grad = bool(entropy_grad and ent is not None)
+        ctx.save_for_backward(hidden, weight, labels, lse, ent if ctx.entropy_grad else None)
         ctx.inv_temp = inv_temp
-        ctx.mark_non_differentiable(*[t for t in (ent, amax) if t is not None])
+        ctx.mark_non_differentiable(*[t for t in ((None if ctx.entropy_grad else ent), amax) if t is not None])
         return logp, ent, amax
 
     @staticmethod
-    def backward(ctx, g_logp, _ge, _ga):
-        hidden, weight, labels, lse = ctx.saved_tensors
+    def backward(ctx, g_logp, g_ent, _ga):
+        hidden, weight, labels, lse, ent = ctx.saved_tensors
         M, K = hidden.shape
         V = weight.shape[0]
-        g = g_logp.float().contiguous()
+        g = g_logp.float().contiguous() if g_logp is not None else torch.zeros(M, device=hidden.device)
+        ge = g_ent.float().contiguous() if (ctx.entropy_grad and g_ent is not None) else None
         dH = torch.empty_like(hidden) if ctx.needs_input_grad[0] else None
         dW = torch.zeros(V, K, dtype=torch.float32, device=hidden.device) if ctx.needs_input_grad[1] else None
         ck = _LmHeadLogprobFn.CHUNK
@@ -156,18 +160,18 @@ class _LmHeadLogprobFn(torch.autograd.Function):
         for s in range(0, M, ck):
             e = min(M, s + ck)
             dz = buf[: (e - s) * V * 2].view(torch.bfloat16).view(e - s, V)
-            lmhead_dz(hidden[s:e], weight, labels[s:e], lse[s:e], g[s:e], ctx.inv_temp, out=dz)
+            lmhead_dz(hidden[s:e], weight, labels[s:e], lse[s:e], g[s:e], ctx.inv_temp, out=dz,
+                      ent=None if ge is None else ent[s:e], gent=None if ge is None else ge[s:e])
             if dH is not None:
                 torch.matmul(dz, weight, out=dH[s:e])
             if dW is not None:
                 dW += torch.matmul(dz.t(), hidden[s:e]).float()
-        return dH, (dW.to(weight.dtype) if dW is not None else None), None, None, None, None
+        return dH, (dW.to(weight.dtype) if dW is not None else None), None, None, None, None, None
 
 
-def lm_head_logprobs(hidden, weight, labels, temperature=1.0, compute_entropy=True):
-    valid = labels >= 0
+def lm_head_logprobs(hidden, weight, labels, temperature=1.0, compute_entropy=True, entropy_grad=False):
     logp, ent, _ = _LmHeadLogprobFn.apply(hidden, weight, labels.clamp_min(0), 1.0 / float(temperature),
-                                          compute_entropy, False)
+                                          compute_entropy, False, entropy_grad)
     return logp, ent
 
 
@@ -511,21 +515,103 @@ def add_rmsnorm_f32_infer(res, delta32, w, eps, out=None):
     return out
 
 
+def add_rmsnorm_f32_wait(res, delta32, w, eps, arrive_ptr: int, target: int, done_ptr: int, out=None):
+    """Consumer of a row-parallel :func:`decode_gemm` fused with its all-reduce: waits (bounded) until the arrival
+    counter at ``arrive_ptr`` has reached ``target`` (ranks x GEMM CTAs), then ``res += delta32`` (cleared) and returns
+    ``rmsnorm(res) * w``; the counter is taken back down by ``target`` when the last row is done."""
+    T, H = res.shape
+    assert delta32.dtype == torch.float32 and delta32.is_contiguous()
+    out = torch.empty_like(res) if out is None else out
+    _chk(lib().trlb_add_rmsnorm_f32_wait(_p(res), _p(delta32), _p(w), _p(out), c_int(T), c_int(H), c_float(eps),
+                                         c_void_p(arrive_ptr), ctypes.c_uint(target), c_void_p(done_ptr),
+                                         _p(status_buffer(res.device)), _s()), "add_rmsnorm_f32_wait")
+    return out
+
+
+def tp_token_sync(mail_ptrs, flag_ptrs, rank: int, world: int, tok, logp, epoch_word):
+    """Rank 0's sampled tokens and log-probs replace those of the other ranks of a tensor-parallel decode group
+    (``mail_ptrs`` / ``flag_ptrs``: every rank's mailbox and flag address in symmetric memory)."""
+    B = tok.shape[0]
+    mails = (ctypes.c_ulonglong * world)(*mail_ptrs)
+    flags = (ctypes.c_ulonglong * world)(*flag_ptrs)
+    _chk(lib().trlb_tp_token_sync(mails, flags, c_int(rank), c_int(world), _p(tok), _p(logp), c_int(B), _p(epoch_word),
+                                  _p(status_buffer(tok.device)), _s()), "tp_token_sync")
+
+
 def accum_grad(dst32, src_bf16):
     """dst32 (fp32 main gradient, contiguous) += src (bf16 gradient of one micro-batch)."""
     _chk(lib().trlb_accum_bf16_f32(_p(dst32), _p(src_bf16), c_longlong(dst32.numel()), _s()), "accum_grad")
 
 
-def smallm_gemm_accumulate(x, w, y32, bias=None):
-    """y32[B, N] (fp32) += x[B, K] @ w[N, K]^T for decode batches (B <= 64): split-K weight-streaming tcgen05 kernel."""
+def set_pdl(on: bool) -> bool:
+    """Programmatic dependent launch for the decode-path kernels (their prologues and the first ring of weight tiles
+    overlap the tail of the kernel before them).  Returns the previous setting.  Choose before a CUDA graph is captured."""
+    return bool(lib().trlb_set_pdl(c_int(int(bool(on)))))
+
+
+def decode_gemm(x, w, bias=None, *, y32=None, out=None, swiglu=False, max_ctas: int = 0, tiled_shape=None,
+                peers=None):
+    """Weight-streaming tcgen05 GEMM for decode batches (at most 128 rows of ``x``).
+
+    ``y32`` given: ``y32[B, N] (fp32) += x @ w^T (+ bias)``, work split stream-K style over every SM; the caller passes
+    zeros (the consumer kernels clear the buffer after reading it).  Otherwise bf16 ``out[B, N] = x @ w^T (+ bias)``;
+    with ``swiglu`` ``w`` is ``[2N, K]`` (gate rows, then up rows) and ``out = silu(x Wg^T) * (x Wu^T)``.
+
+    ``tiled_shape=(rows, K)``: ``w`` is the flat tile-major copy made by :func:`tile_weights` of a ``[rows, K]`` weight.
+    ``peers=(peer_y32_ptrs, arrive_ptrs)``: row-parallel GEMM fused with its all-reduce: the sums are also added into
+    the peers' buffers (device addresses) and each CTA bumps every rank's arrival counter (``arrive_ptrs[0]`` is this
+    rank's own); see :func:`decode_gemm_ctas` for the count to wait for."""
     B, Kd = x.shape
-    N = w.shape[0]
-    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and y32.dtype == torch.float32
-    assert x.stride(1) == 1 and w.stride(1) == 1 and y32.stride(1) == 1 and y32.shape == (B, N)
-    _chk(lib().trlb_smallm_gemm_bf16(_p(x), _p(w), _p(bias), _p(y32), c_int(B), c_int(N), c_int(Kd), c_longlong(x.stride(0)),
-                                     c_longlong(w.stride(0)), c_longlong(y32.stride(0)), _p(status_buffer(x.device)), _s()),
-         "smallm_gemm")
-    return y32
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1
+    if tiled_shape is not None:
+        rows, kw = tiled_shape
+        assert kw == Kd and w.is_contiguous()
+        ldw = 0
+    else:
+        assert w.stride(1) == 1 and w.shape[1] == Kd
+        rows, ldw = w.shape[0], w.stride(0)
+    N = rows // 2 if swiglu else rows
+    if y32 is not None:
+        assert y32.dtype == torch.float32 and y32.stride(1) == 1 and tuple(y32.shape) == (B, N) and not swiglu
+        mode, ldy, dst32, dstb, ret = 0, y32.stride(0), y32, None, y32
+    else:
+        if out is None:
+            out = torch.empty(B, N, dtype=torch.bfloat16, device=x.device)
+        assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and tuple(out.shape) == (B, N)
+        mode, ldy, dst32, dstb, ret = (2 if swiglu else 1), out.stride(0), None, out, out
+    n_peers, peer_arr, arrive_arr = 0, None, None
+    if peers is not None:
+        peer_ptrs, arrive_ptrs = peers
+        n_peers = len(peer_ptrs)
+        assert mode == 0 and len(arrive_ptrs) == n_peers + 1
+        peer_arr = (c_void_p * max(1, n_peers))(*peer_ptrs) if n_peers else None
+        arrive_arr = (c_void_p * (n_peers + 1))(*arrive_ptrs)
+    _chk(lib().trlb_decode_gemm(_p(x), _p(w), _p(bias), _p(dst32), _p(dstb), c_int(B), c_int(N), c_int(Kd),
+                                c_longlong(x.stride(0)), c_longlong(ldw), c_longlong(ldy), c_int(mode),
+                                c_int(int(tiled_shape is not None)), c_int(max_ctas), c_int(n_peers), peer_arr, arrive_arr,
+                                _p(status_buffer(x.device)), _s()), "decode_gemm")
+    return ret
+
+
+def decode_gemm_ctas(B: int, N: int, K: int, mode: int = 0, max_ctas: int = 0) -> int:
+    """Grid size :func:`decode_gemm` uses for ``B`` rows and an ``[N, K]`` weight (mode 0: fp32 sums, 1: bf16 store,
+    2: SwiGLU)."""
+    return int(lib().trlb_decode_gemm_ctas(c_int(B), c_int(N), c_int(K), c_int(mode), c_int(max_ctas)))
+
+
+def tile_weights(w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Tile-major copy of a row-major ``[rows, K]`` bf16 weight for :func:`decode_gemm` (``tiled_shape=(rows, K)``):
+    ``[ceil(rows/128)][ceil(K/64)][128][64]``, every 16 KB tile contiguous, zero padded."""
+    rows, Kd = w.shape
+    assert w.dtype == torch.bfloat16 and w.stride(1) == 1
+    L = lib()
+    L.trlb_tiled_elems.restype = c_longlong
+    n = int(L.trlb_tiled_elems(c_int(rows), c_int(Kd)))
+    if out is None:
+        out = torch.empty(n, dtype=torch.bfloat16, device=w.device)
+    assert out.numel() == n and out.is_contiguous() and out.dtype == torch.bfloat16
+    _chk(L.trlb_tile_weights(_p(w), c_longlong(w.stride(0)), _p(out), c_int(rows), c_int(Kd), _s()), "tile_weights")
+    return out
 
 
 def swiglu_infer(gu, out=None):
@@ -544,6 +630,19 @@ def rope_kv_write(qkv, seq_lens, slot_ids, block_table, block_size, q_out, k_cac
                                   c_int(block_table.shape[1]), c_int(block_size), _p(q_out), _p(k_cache), _p(v_cache),
                                   c_int(B), c_int(Hq), c_int(Hk), c_int(D), c_float(theta), c_int(int(v_transposed)), _s()),
          "rope_kv_write")
+
+
+def rope_kv_write_f32(acc, bias, q_norm, k_norm, norm_eps, seq_lens, slot_ids, block_table, block_size, q_out, k_cache,
+                      v_cache, Hq, Hk, D, theta, v_transposed=False):
+    """Like :func:`rope_kv_write` for the fp32 sums of the stream-K QKV GEMM: adds ``bias``, applies the per-head
+    RMSNorm of q / k when ``q_norm`` / ``k_norm`` are given, rotates, appends, and clears ``acc``."""
+    B = acc.shape[0]
+    assert acc.dtype == torch.float32 and acc.stride(1) == 1
+    _chk(lib().trlb_rope_kv_write_f32(_p(acc), c_longlong(acc.stride(0)), _p(bias), _p(q_norm), _p(k_norm),
+                                      c_float(norm_eps), _p(seq_lens), _p(slot_ids), _p(block_table),
+                                      c_int(block_table.shape[1]), c_int(block_size), _p(q_out), _p(k_cache), _p(v_cache),
+                                      c_int(B), c_int(Hq), c_int(Hk), c_int(D), c_float(theta), c_int(int(v_transposed)),
+                                      _s()), "rope_kv_write_f32")
 
 
 def kv_write_prefill(k, v, tok_slot, tok_pos, block_table, block_size, k_cache, v_cache, v_transposed=False):

@@ -67,13 +67,22 @@ def attention_varlen_qk(q, k, v, cu_q, cu_k, max_q, max_k):
 
 
 def lm_head_logprobs(hidden, weight, labels, temperature=1.0, bias=None, softcap=None,
-                     compute_entropy=True, chunk_tokens: int = 4096):
-    """Fused lm_head GEMM + log-softmax gather (+entropy); logits never materialise."""
+                     compute_entropy=True, chunk_tokens: int = 4096, entropy_grad: bool = False):
+    """Fused lm_head GEMM + log-softmax gather (+entropy); logits never materialise.  ``entropy_grad``: the entropy
+    is differentiable too (GRPO entropy bonus); by default it is a statistic without gradient."""
+    from ..models.activation_offloading import no_offload
+
+    with no_offload():  # the head's input is used again at once: it stays on the device
+        return _lm_head_logprobs(hidden, weight, labels, temperature, bias, softcap, compute_entropy, chunk_tokens,
+                                 entropy_grad)
+
+
+def _lm_head_logprobs(hidden, weight, labels, temperature, bias, softcap, compute_entropy, chunk_tokens, entropy_grad):
     if _use_kernel(hidden) and bias is None and not softcap:
-        return _cuda().lm_head_logprobs(hidden, weight, labels, temperature, compute_entropy)
+        return _cuda().lm_head_logprobs(hidden, weight, labels, temperature, compute_entropy, entropy_grad)
     if hidden.shape[0] <= chunk_tokens or not torch.is_grad_enabled():
         outs = [
-            _ref.lm_head_logprobs(h, weight, y, temperature, bias, softcap, compute_entropy)
+            _ref.lm_head_logprobs(h, weight, y, temperature, bias, softcap, compute_entropy, entropy_grad)
             for h, y in zip(hidden.split(chunk_tokens), labels.split(chunk_tokens))
         ] or [(hidden.new_zeros(0, dtype=torch.float32), hidden.new_zeros(0, dtype=torch.float32))]
         lp = torch.cat([o[0] for o in outs])
@@ -85,7 +94,7 @@ def lm_head_logprobs(hidden, weight, labels, temperature=1.0, bias=None, softcap
     lps, ens = [], []
     for h, y in zip(hidden.split(chunk_tokens), labels.split(chunk_tokens)):
         lp, en = checkpoint(_ref.lm_head_logprobs, h, weight, y, temperature, bias, softcap,
-                            compute_entropy, use_reentrant=False)
+                            compute_entropy, entropy_grad, use_reentrant=False)
         lps.append(lp)
         ens.append(en)
     return torch.cat(lps), (torch.cat(ens) if compute_entropy else None)
@@ -93,9 +102,12 @@ def lm_head_logprobs(hidden, weight, labels, temperature=1.0, bias=None, softcap
 
 def lm_head_ce(hidden, weight, labels, ignore_index=-100, bias=None):
     """Sum NLL + (correct, entropy_sum, n_valid) without a full logits tensor."""
-    if _use_kernel(hidden) and bias is None:
-        return _cuda().lm_head_ce(hidden, weight, labels, ignore_index)
-    return _ref.lm_head_ce(hidden, weight, labels, ignore_index, bias)
+    from ..models.activation_offloading import no_offload
+
+    with no_offload():
+        if _use_kernel(hidden) and bias is None:
+            return _cuda().lm_head_ce(hidden, weight, labels, ignore_index)
+        return _ref.lm_head_ce(hidden, weight, labels, ignore_index, bias)
 
 
 def moe_mlp(hidden, router_w, gate_up_w, down_w, top_k, norm_topk_prob):

@@ -96,10 +96,11 @@ def attention_varlen_qk(q, k, v, cu_q, cu_k, scale=None):
 
 
 def lm_head_logprobs(hidden, weight, labels, temperature=1.0, bias=None, softcap=None,
-                     compute_entropy=True):
+                     compute_entropy=True, entropy_grad=False):
     """Per-token log p(label) and entropy from ``hidden[N,H] @ weight[V,H]^T``.
 
-    Entropy carries no gradient (matches trl/trainer/utils.py:1291-1424).
+    Entropy carries no gradient (matches trl/trainer/utils.py:1291-1424) unless ``entropy_grad``
+    (the differentiable entropy of the GRPO bonus, trl/trainer/grpo_trainer.py:3155-3175).
     """
     logits = hidden.float() @ weight.float().t()
     if bias is not None:
@@ -112,9 +113,9 @@ def lm_head_logprobs(hidden, weight, labels, temperature=1.0, bias=None, softcap
     logp = tgt - lse
     ent = None
     if compute_entropy:
-        with torch.no_grad():
+        with torch.set_grad_enabled(bool(entropy_grad) and torch.is_grad_enabled()):
             p = torch.softmax(logits, dim=-1)
-            ent = lse.detach() - (p * logits).sum(-1)
+            ent = (lse if entropy_grad else lse.detach()) - (p * logits).sum(-1)
     return logp, ent
 
 

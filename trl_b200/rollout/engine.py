@@ -191,15 +191,22 @@ class RolloutEngine:
         self.q_buf = torch.empty(max_num_seqs, self.hq_local, D, dtype=dt, device=self.dev)
         self._fused_gate_up = (os.environ.get("TRL_B200_DECODE_FUSED_GATE_UP", "1") == "1" and not cfg.is_moe and tp == 1
                                and cfg.hidden_size % 8 == 0 and cfg.intermediate_size % 8 == 0)
-        # optional (TRL_B200_DECODE_SPLITK=1): o / down projections through the split-K weight-streaming kernel.  Off by
-        # default: at batch 64 on Qwen2.5-7B it measured 4.26 ms per decode step against 3.77 ms with cuBLAS.
-        # It needs the fused gate/up branch (its down projection is the one replaced) and a batch <= 64
-        self._splitk = (os.environ.get("TRL_B200_DECODE_SPLITK", "0") == "1" and self._fused_gate_up and max_num_seqs <= 64
-                        and cfg.hidden_size <= 8192)
-        if self._splitk:  # fp32 accumulators; their consumer (add + RMSNorm) clears them after reading
-            self._acc_o = torch.zeros(max_num_seqs, cfg.hidden_size, dtype=torch.float32, device=self.dev)
-            self._acc_d = torch.zeros(max_num_seqs, cfg.hidden_size, dtype=torch.float32, device=self.dev)
-        if self._fused_gate_up:
+        # decode linears on the weight-streaming tcgen05 kernel (stream-K over every SM, fp32 sums consumed and cleared
+        # by the next kernel, programmatic dependent launch); TRL_B200_DECODE_GEMM=cublas keeps the library GEMMs
+        self._own_gemm = (os.environ.get("TRL_B200_DECODE_GEMM", "own") != "cublas" and tp == 1 and max_num_seqs <= 128
+                          and cfg.hidden_size <= 8192 and cfg.hidden_size % 8 == 0 and cfg.head_dim <= 128
+                          and (cfg.is_moe or cfg.intermediate_size % 8 == 0))
+        self._pdl = os.environ.get("TRL_B200_PDL", "1") == "1"
+        if self._own_gemm:  # fp32 accumulators; their consumers clear them after reading
+            f32 = dict(dtype=torch.float32, device=self.dev)
+            qkv_out = (self.hq_local + 2 * self.hk_local) * cfg.head_dim
+            self._acc_qkv = torch.zeros(max_num_seqs, qkv_out, **f32)
+            self._acc_o = torch.zeros(max_num_seqs, cfg.hidden_size, **f32)
+            self._acc_d = torch.zeros(max_num_seqs, cfg.hidden_size, **f32)
+            self._logits_buf = torch.empty(max_num_seqs, cfg.vocab_size, dtype=dt, device=self.dev)
+            if not cfg.is_moe:
+                self._act_buf = torch.empty(max_num_seqs, cfg.intermediate_size // tp, dtype=dt, device=self.dev)
+        if self._fused_gate_up and not self._own_gemm:
             self._one_group = torch.tensor([0, max_num_seqs], dtype=torch.int32, device=self.dev)
             self._act_buf = torch.empty(max_num_seqs, cfg.intermediate_size, dtype=dt, device=self.dev)
         self.attn_buf = torch.empty(max_num_seqs, self.hq_local, D, dtype=dt, device=self.dev)
@@ -225,19 +232,74 @@ class RolloutEngine:
     def _decode_step(self, sp: SamplingParams, max_total_len: int):
         from ..ops import cuda as K
 
+        if self._own_gemm:
+            was = K.set_pdl(self._pdl)
+            try:
+                logits = self._decode_layers_own()
+            finally:
+                K.set_pdl(was)
+        else:
+            logits = self._decode_layers_lib()
+        self._sample(logits, sp)
+        K.advance(self.tok, self.logp, None, self.seq_lens, self.n_gen, self.finished, self.out_tokens, self.out_logps,
+                  sp.eos_token_id, max_total_len, self.next_input, self.step_counter, 1)
+        if self.seen is not None:
+            self.seen.scatter_(1, self.next_input[:, None], 1)
+
+    def _decode_layers_own(self):
+        """Decoder stack of one decode step on this library's kernels only: every linear is the weight-streaming
+        tcgen05 GEMM; q/k/v, attention output and MLP output travel as fp32 sums that the next kernel consumes."""
+        from ..ops import cuda as K
+
+        cfg, m = self.cfg, self.model
+        eps = cfg.rms_norm_eps
+        x = torch.nn.functional.embedding(self.next_input, m.embed_tokens)
+        scale = 1.0 / math.sqrt(cfg.head_dim)
+        pending = False  # the MLP output of the previous layer still sits in _acc_d
+        for li, l in enumerate(m.layers):
+            if pending:
+                h = K.add_rmsnorm_f32_infer(x, self._acc_d, l.input_layernorm, eps)
+            else:
+                h = K.rmsnorm_infer(x, l.input_layernorm, eps)
+            K.decode_gemm(h, l.qkv_proj, y32=self._acc_qkv)
+            K.rope_kv_write_f32(self._acc_qkv, l.qkv_bias, l.q_norm if cfg.qk_norm else None,
+                                l.k_norm if cfg.qk_norm else None, eps, self.seq_lens, None, self.block_table,
+                                self.block_size, self.q_buf, self.k_cache[li], self.v_cache[li], cfg.num_attention_heads,
+                                cfg.num_key_value_heads, cfg.head_dim, cfg.rope_theta, v_transposed=self.attn_tc)
+            self._decode_attention(li, scale)
+            K.decode_gemm(self.attn_buf.view(self.max_seqs, -1), l.o_proj, y32=self._acc_o)
+            h = K.add_rmsnorm_f32_infer(x, self._acc_o, l.post_attention_layernorm, eps)
+            if cfg.is_moe:
+                from ..ops import functional as F_
+
+                y, _, _ = F_.moe_mlp(h, l.router, l.experts_gate_up, l.experts_down, cfg.num_experts_per_tok,
+                                     cfg.norm_topk_prob)
+                x.add_(y)
+                pending = False
+            else:
+                act = K.decode_gemm(h, l.gate_up_proj, out=self._act_buf, swiglu=True)
+                K.decode_gemm(act, l.down_proj, y32=self._acc_d)
+                pending = True
+        if pending:
+            hN = K.add_rmsnorm_f32_infer(x, self._acc_d, m.norm, eps)
+        else:
+            hN = K.rmsnorm_infer(x, m.norm, eps)
+        return K.decode_gemm(hN, m.lm_head_weight, out=self._logits_buf)
+
+    def _decode_layers_lib(self):
+        """The same stack with library GEMMs for the plain linears (comparison path, and the path of shapes the
+        weight-streaming kernel does not cover)."""
+        from ..ops import cuda as K
+
         cfg, m = self.cfg, self.model
         eps = cfg.rms_norm_eps
         x = torch.nn.functional.embedding(self.next_input, m.embed_tokens)
         scale = 1.0 / math.sqrt(cfg.head_dim)
         fuse = cfg.hidden_size <= 8192  # residual add folded into the following RMSNorm
         pending = None  # block output not yet added to the residual stream
-        splitk = self._splitk and fuse  # o / down projections through the split-K weight-streaming kernel
         for li, l in enumerate(m.layers):
             if pending is None:
                 h = K.rmsnorm_infer(x, l.input_layernorm, eps)
-            elif splitk:
-                h = K.add_rmsnorm_f32_infer(x, pending, l.input_layernorm, eps)
-                pending = None
             else:
                 h = K.add_rmsnorm_infer(x, pending, l.input_layernorm, eps)
                 pending = None
@@ -251,10 +313,7 @@ class RolloutEngine:
                             self.v_cache[li], cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
                             cfg.rope_theta, v_transposed=self.attn_tc)
             self._decode_attention(li, scale)
-            if splitk:
-                K.smallm_gemm_accumulate(self.attn_buf.view(self.max_seqs, -1), l.o_proj, self._acc_o)
-                h = K.add_rmsnorm_f32_infer(x, self._acc_o, l.post_attention_layernorm, eps)
-            elif fuse:
+            if fuse:
                 attn_out = torch.nn.functional.linear(self.attn_buf.view(self.max_seqs, -1), l.o_proj)
                 h = K.add_rmsnorm_infer(x, attn_out, l.post_attention_layernorm, eps)
             else:
@@ -270,10 +329,7 @@ class RolloutEngine:
                 # and one launch per layer disappear
                 act = K.grouped_gemm(h, l.gate_up_proj.unsqueeze(0), self._one_group, cfg.intermediate_size, swiglu=True,
                                      out=self._act_buf)
-                if splitk:
-                    y = K.smallm_gemm_accumulate(act, l.down_proj, self._acc_d)
-                else:
-                    y = torch.nn.functional.linear(act, l.down_proj)
+                y = torch.nn.functional.linear(act, l.down_proj)
             else:
                 gu = torch.nn.functional.linear(h, l.gate_up_proj)
                 y = torch.nn.functional.linear(K.swiglu_infer(gu), l.down_proj)
@@ -283,16 +339,9 @@ class RolloutEngine:
                 x = x + y
         if pending is None:
             hN = K.rmsnorm_infer(x, m.norm, eps)
-        elif splitk:
-            hN = K.add_rmsnorm_f32_infer(x, pending, m.norm, eps)
         else:
             hN = K.add_rmsnorm_infer(x, pending, m.norm, eps)
-        logits = torch.nn.functional.linear(hN, m.lm_head_weight)
-        self._sample(logits, sp)
-        K.advance(self.tok, self.logp, None, self.seq_lens, self.n_gen, self.finished, self.out_tokens, self.out_logps,
-                  sp.eos_token_id, max_total_len, self.next_input, self.step_counter, 1)
-        if self.seen is not None:
-            self.seen.scatter_(1, self.next_input[:, None], 1)
+        return torch.nn.functional.linear(hN, m.lm_head_weight)
 
     def _sample(self, logits, sp: SamplingParams, rows: Optional[torch.Tensor] = None, tok=None, logp=None):
         from ..ops import cuda as K
@@ -372,7 +421,8 @@ class RolloutEngine:
         self.seq_lens.fill_(-1)
         self.finished.zero_()
         self.n_gen.zero_()
-        if getattr(self, "_splitk", False):  # a step that raised half-way may have left partial sums behind
+        if self._own_gemm:  # a step that raised half-way may have left partial sums behind
+            self._acc_qkv.zero_()
             self._acc_o.zero_()
             self._acc_d.zero_()
         bt_np = self.block_table_host.numpy()

@@ -1,24 +1,32 @@
 """Tensor-parallel rollout engine (decode split over the ranks of a TP group).
 
 Layout per rank r of tp: attention heads [r*Hq/tp, (r+1)*Hq/tp) with their KV heads (the paged cache holds
-local heads only), MLP columns [r*I/tp, (r+1)*I/tp); embeddings, norms and the lm_head are replicated so that
-every rank samples from bit-identical logits with the same counter-based RNG and no token exchange is needed.
+local heads only), MLP columns [r*I/tp, (r+1)*I/tp); embeddings, norms and the lm_head are replicated.
 
-Per layer the two row-parallel GEMMs (O-proj, down-proj) write their partial [T, H] outputs into symmetric
-memory; the following norm is ``allreduce_add_rmsnorm``: it sums the ranks' partials over NVLink in rank order,
-adds the residual and normalises in one kernel.  There are 2L+1 such call sites per step, each with its own
-buffer: a buffer is rewritten one full step later, after 2L other cross-rank barriers, so no reader can still
-be on it.  The whole step is one CUDA graph per rank.
+Fused path (default; batches of at most 128 rows, 128-row-aligned slices): every decode linear is the
+weight-streaming tcgen05 GEMM on tile-major weight slices (the repack that tensor parallelism needs anyway writes
+them tile-major, so each 16 KB weight tile is one sequential DRAM burst).  The two row-parallel GEMMs of a layer
+(O-proj, down-proj) are fused with their all-reduce: the epilogue adds the fp32 partial sums into the accumulator
+of EVERY rank over NVLink (red.global on peer pointers) and bumps an arrival counter on every rank; the consumer
+(residual add + RMSNorm) waits on its own counter, reads one local buffer and clears it.  No rank reads a peer's
+memory, no separate all-reduce kernel runs and no barrier has two directions: a rank only ever waits for "all
+partial sums have landed here".  Accumulator reuse needs no extra handshake: a peer can reach the next GEMM on the
+same accumulator only after it has consumed this rank's partial sums of the GEMM in between, which this rank
+launched after clearing the accumulator.  Partial sums arrive in no fixed order, so the ranks' logits may differ
+in the last bit; rank 0's sampled tokens are therefore copied to the other ranks (one small message per step).
+
+Legacy path (``TRL_B200_TP_FUSED=0`` or shapes outside the fused kernels): library GEMMs write bf16 partials into
+symmetric memory and ``allreduce_add_rmsnorm`` sums them over peer loads behind a two-sided barrier.
 
 Weight "sync": under the zero modes every rank already holds the full bf16 parameters, so the TP layout is a
-local repack (row/column slices copied into contiguous TP buffers, ``sync_weights``); under full-shard the
-buckets are first completed with the ``shard_allgather`` kernel.  Prompts of the group's ranks are gathered so
-all ranks run the same batch; each rank keeps its own completions (vllm_generation.py:636-699 does the same
-around vLLM's TP workers).
+local repack (``sync_weights``); under full-shard the buckets are first completed with the ``shard_allgather``
+kernel.  Prompts of the group's ranks are gathered so all ranks run the same batch; each rank keeps its own
+completions (vllm_generation.py:636-699 does the same around vLLM's TP workers).
 """
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 import torch.distributed as td
@@ -40,28 +48,89 @@ class TPRolloutEngine(RolloutEngine):
             raise ValueError("TP decode batch (max_num_seqs * tp) is limited to 148 rows per step")
         H, D, I = cfg.hidden_size, cfg.head_dim, cfg.intermediate_size
         ql, kl, il = self.hq_local * D, self.hk_local * D, I // tp
+        self._dims = (ql, kl, il)
+        self.fused = (os.environ.get("TRL_B200_TP_FUSED", "1") == "1" and self.max_seqs <= 128 and H <= 8192 and H % 8 == 0
+                      and D <= 128 and ql % 128 == 0 and kl % 128 == 0 and il % 128 == 0 and tp <= 8)
+        self._pdl = os.environ.get("TRL_B200_PDL", "1") == "1"
         self.w = []
-        for _ in cfg_layers(cfg):
-            self.w.append({
-                "qkv": torch.empty(ql + 2 * kl, H, dtype=dt, device=dev),
-                "qkv_b": torch.empty(ql + 2 * kl, dtype=dt, device=dev) if cfg.attention_bias else None,
-                "o": torch.empty(H, ql, dtype=dt, device=dev),
-                "gu": torch.empty(2 * il, H, dtype=dt, device=dev),
-                "down": torch.empty(H, il, dtype=dt, device=dev),
-            })
-        self.n_sites = 2 * cfg.num_hidden_layers
-        self.site_elems = self.max_seqs * H
-        self.arena = SymmArena(self.n_sites * self.site_elems * 2 + 4096, dev, tp_group)
-        self.partials, self.partials_off = self.arena.carve(self.n_sites * self.site_elems, dt)
-        self.sync = SyncWords(dev, channel=1)
+        if self.fused:
+            from ..ops import cuda as K
+
+            L_ = K.lib()
+            L_.trlb_tiled_elems.restype = __import__("ctypes").c_longlong
+            n_el = lambda rows, k: int(L_.trlb_tiled_elems(rows, k))
+            for _ in cfg_layers(cfg):
+                self.w.append({
+                    "qkv": torch.empty(n_el(ql + 2 * kl, H), dtype=dt, device=dev),
+                    "qkv_b": torch.empty(ql + 2 * kl, dtype=dt, device=dev) if cfg.attention_bias else None,
+                    "o": torch.empty(n_el(H, ql), dtype=dt, device=dev),
+                    "gu": torch.empty(n_el(2 * il, H), dtype=dt, device=dev),
+                    "down": torch.empty(n_el(H, il), dtype=dt, device=dev),
+                })
+            B = self.max_seqs
+            # symmetric: two fp32 accumulators [B, H], two arrival counters, a token mailbox and its flag
+            acc_bytes = B * H * 4
+            self.arena = SymmArena(2 * acc_bytes + 4096 + 2 * B * 4 + 1024, dev, tp_group)
+            self._acc_o, self._acc_o_off = self.arena.carve(B * H, torch.float32)
+            self._acc_d, self._acc_d_off = self.arena.carve(B * H, torch.float32)
+            self._acc_o, self._acc_d = self._acc_o.view(B, H), self._acc_d.view(B, H)
+            self._ctr, self._ctr_off = self.arena.carve(64, torch.int32)   # [0] O-proj arrivals, [16] down-proj arrivals
+            self._mail, self._mail_off = self.arena.carve(2 * B, torch.int32)
+            self._flag, self._flag_off = self.arena.carve(64, torch.int32)
+            peers = [p for p in range(tp) if p != tp_rank]
+            base = self.arena.peer_ptrs
+            self._peer_acc_o = [base[p] + self._acc_o_off for p in peers]
+            self._peer_acc_d = [base[p] + self._acc_d_off for p in peers]
+            self._arrive_o = [base[tp_rank] + self._ctr_off] + [base[p] + self._ctr_off for p in peers]
+            self._arrive_d = [base[tp_rank] + self._ctr_off + 64] + [base[p] + self._ctr_off + 64 for p in peers]
+            self._mail_ptrs = [base[p] + self._mail_off for p in range(tp)]
+            self._flag_ptrs = [base[p] + self._flag_off for p in range(tp)]
+            self._local = torch.zeros(16, dtype=torch.int32, device=dev)  # [0] done word O, [4] done word down, [8] epoch
+            self._acc_qkv = torch.zeros(B, ql + 2 * kl, dtype=torch.float32, device=dev)
+            self._act_buf = torch.empty(B, il, dtype=dt, device=dev)
+            self._logits_buf = torch.empty(B, cfg.vocab_size, dtype=dt, device=dev)
+            self._target_o = tp * K.decode_gemm_ctas(B, H, ql)
+            self._target_d = tp * K.decode_gemm_ctas(B, H, il)
+        else:
+            for _ in cfg_layers(cfg):
+                self.w.append({
+                    "qkv": torch.empty(ql + 2 * kl, H, dtype=dt, device=dev),
+                    "qkv_b": torch.empty(ql + 2 * kl, dtype=dt, device=dev) if cfg.attention_bias else None,
+                    "o": torch.empty(H, ql, dtype=dt, device=dev),
+                    "gu": torch.empty(2 * il, H, dtype=dt, device=dev),
+                    "down": torch.empty(H, il, dtype=dt, device=dev),
+                })
+            self.n_sites = 2 * cfg.num_hidden_layers
+            self.site_elems = self.max_seqs * H
+            self.arena = SymmArena(self.n_sites * self.site_elems * 2 + 4096, dev, tp_group)
+            self.partials, self.partials_off = self.arena.carve(self.n_sites * self.site_elems, dt)
+            self.sync = SyncWords(dev, channel=1)
         self.sync_weights()
 
     @torch.no_grad()
     def sync_weights(self, model=None):
         cfg, r, tp = self.cfg, self.tp_rank, self.tp
-        D, I = cfg.head_dim, cfg.intermediate_size
+        D, I, H = cfg.head_dim, cfg.intermediate_size, cfg.hidden_size
         qs, ks = cfg.q_size, cfg.kv_size
-        ql, kl, il = self.hq_local * D, self.hk_local * D, I // tp
+        ql, kl, il = self._dims
+        if self.fused:
+            from ..ops import cuda as K
+
+            kb_h = -(-H // 64)
+            tile = 128 * 64
+            for l, w in zip(self.model.layers, self.w):
+                # every piece is a whole number of 128-row slabs, so it lands at a slab boundary of the tiled buffer
+                o = 0
+                for start, n in ((r * ql, ql), (qs + r * kl, kl), (qs + ks + r * kl, kl)):
+                    K.tile_weights(l.qkv_proj[start:start + n], out=w["qkv"][o * kb_h * 64:(o + n) * kb_h * 64])
+                    if w["qkv_b"] is not None:
+                        w["qkv_b"][o:o + n].copy_(l.qkv_bias[start:start + n])
+                    o += n
+                K.tile_weights(l.o_proj[:, r * ql:(r + 1) * ql], out=w["o"])
+                K.tile_weights(l.gate_up_proj[r * il:(r + 1) * il], out=w["gu"][: il * kb_h * 64])
+                K.tile_weights(l.gate_up_proj[I + r * il:I + (r + 1) * il], out=w["gu"][il * kb_h * 64:])
+                K.tile_weights(l.down_proj[:, r * il:(r + 1) * il], out=w["down"])
+            return
         for l, w in zip(self.model.layers, self.w):
             rows = [(0 + r * ql, ql), (qs + r * kl, kl), (qs + ks + r * kl, kl)]
             o = 0
@@ -79,6 +148,53 @@ class TPRolloutEngine(RolloutEngine):
         return self.partials[i * self.site_elems:(i + 1) * self.site_elems].view(self.max_seqs, self.cfg.hidden_size)
 
     def _decode_step(self, sp: SamplingParams, max_total_len: int):
+        from ..ops import cuda as K
+
+        if self.fused:
+            was = K.set_pdl(self._pdl)
+            try:
+                logits = self._decode_layers_fused()
+            finally:
+                K.set_pdl(was)
+            self._sample(logits, sp)
+            # the ranks' logits can differ in the last bit (partial sums arrive in no fixed order): rank 0 decides
+            K.tp_token_sync(self._mail_ptrs, self._flag_ptrs, self.tp_rank, self.tp, self.tok, self.logp, self._local[8:9])
+        else:
+            self._sample(self._decode_layers_legacy(), sp)
+        K.advance(self.tok, self.logp, None, self.seq_lens, self.n_gen, self.finished, self.out_tokens, self.out_logps,
+                  sp.eos_token_id, max_total_len, self.next_input, self.step_counter, 1)
+        if self.seen is not None:
+            self.seen.scatter_(1, self.next_input[:, None], 1)
+
+    def _decode_layers_fused(self):
+        from ..ops import cuda as K
+
+        cfg, m = self.cfg, self.model
+        eps, scale = cfg.rms_norm_eps, 1.0 / math.sqrt(cfg.head_dim)
+        H = cfg.hidden_size
+        ql, kl, il = self._dims
+        x = torch.nn.functional.embedding(self.next_input, m.embed_tokens)
+        loc = self._local.data_ptr()
+        for li, (l, w) in enumerate(zip(m.layers, self.w)):
+            if li == 0:
+                h = K.rmsnorm_infer(x, l.input_layernorm, eps)
+            else:
+                h = K.add_rmsnorm_f32_wait(x, self._acc_d, l.input_layernorm, eps, self._arrive_d[0], self._target_d, loc + 16)
+            K.decode_gemm(h, w["qkv"], y32=self._acc_qkv, tiled_shape=(ql + 2 * kl, H))
+            K.rope_kv_write_f32(self._acc_qkv, w["qkv_b"], l.q_norm if cfg.qk_norm else None,
+                                l.k_norm if cfg.qk_norm else None, eps, self.seq_lens, None, self.block_table,
+                                self.block_size, self.q_buf, self.k_cache[li], self.v_cache[li], self.hq_local,
+                                self.hk_local, cfg.head_dim, cfg.rope_theta, v_transposed=self.attn_tc)
+            self._decode_attention(li, scale)
+            K.decode_gemm(self.attn_buf.view(self.max_seqs, -1), w["o"], y32=self._acc_o, tiled_shape=(H, ql),
+                          peers=(self._peer_acc_o, self._arrive_o))
+            h = K.add_rmsnorm_f32_wait(x, self._acc_o, l.post_attention_layernorm, eps, self._arrive_o[0], self._target_o, loc)
+            act = K.decode_gemm(h, w["gu"], out=self._act_buf, swiglu=True, tiled_shape=(2 * il, H))
+            K.decode_gemm(act, w["down"], y32=self._acc_d, tiled_shape=(H, il), peers=(self._peer_acc_d, self._arrive_d))
+        hN = K.add_rmsnorm_f32_wait(x, self._acc_d, m.norm, eps, self._arrive_d[0], self._target_d, loc + 16)
+        return K.decode_gemm(hN, m.lm_head_weight, out=self._logits_buf)
+
+    def _decode_layers_legacy(self):
         from ..ops import cuda as K
 
         cfg, m, F = self.cfg, self.model, torch.nn.functional
@@ -106,12 +222,7 @@ class TPRolloutEngine(RolloutEngine):
             site += 1
         hN = K.allreduce_add_rmsnorm(self.arena, self.partials_off + (site - 1) * self.site_elems * 2, 0, x, m.norm, eps,
                                      self.sync)
-        logits = F.linear(hN, m.lm_head_weight)
-        self._sample(logits, sp)
-        K.advance(self.tok, self.logp, None, self.seq_lens, self.n_gen, self.finished, self.out_tokens, self.out_logps,
-                  sp.eos_token_id, max_total_len, self.next_input, self.step_counter, 1)
-        if self.seen is not None:
-            self.seen.scatter_(1, self.next_input[:, None], 1)
+        return F.linear(hN, m.lm_head_weight)
 
     @torch.no_grad()
     def generate(self, prompts, sp: SamplingParams, images=None) -> list[Completion]:

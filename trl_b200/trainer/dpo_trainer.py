@@ -25,7 +25,8 @@ from ..models.decoder import SeqCtx
 from ..ops import functional as ops
 from ..parallel import dist as D
 from .dpo_config import DPOConfig
-from .utils import create_model_from_path, disable_dropout_in_model, hash_module, pad, use_adapter
+from .utils import (DeferredMetric, create_model_from_path, defer_mean, defer_ratio, disable_dropout_in_model, hash_module, pad,
+                    resolve_deferred_metrics, use_adapter)
 
 
 @dataclass
@@ -252,7 +253,7 @@ class DPOTrainer(Trainer):
         D.broadcast_object_list(key)
         cache = os.path.join(a.output_dir, f"ref_logps_{name}_{key[0]}.pt")
         if os.path.exists(cache):
-            vals = torch.load(cache)
+            vals = torch.load(cache, weights_only=True)
         else:
             bs = a.precompute_ref_batch_size or a.per_device_train_batch_size
             rows = [dataset[i] for i in range(len(dataset))]
@@ -418,26 +419,24 @@ class DPOTrainer(Trainer):
         if aux is not None:
             loss = loss + self.args.router_aux_loss_coef * aux
             m["aux_loss"].append(aux.detach())
-        # ---- metrics (one stacked reduction per micro-batch) ---------------------------------------------------
+        # ---- metrics: local partial results only; one reduction per logging step resolves them ---------------------
         with torch.no_grad():
             cr, rrw = beta * c_lr.detach(), beta * r_lr.detach()
             ent = ex["entropy"]
-            tok_n = torch.tensor(float(ent.numel()), device=ent.device)
-            vals = torch.stack([cr.mean(), rrw.mean(), (cr > rrw).float().mean(), (cr - rrw).mean(), pc.detach().mean(),
-                                pr.detach().mean()])
-            if D.world_size() > 1:
-                D.all_reduce(vals, "mean")
-            sums = torch.stack([ent.sum(), tok_n, inputs["attention_mask"].sum().float()])
-            if D.world_size() > 1:
-                D.all_reduce(sums, "sum")
+            vals = [cr.mean(), rrw.mean(), (cr > rrw).float().mean(), (cr - rrw).mean(), pc.detach().mean(),
+                    pr.detach().mean()]
             names = ["rewards/chosen", "rewards/rejected", "rewards/accuracies", "rewards/margins", "logps/chosen",
                      "logps/rejected"]
             for n, v in zip(names, vals):
-                m[n].append(v)
-            m["entropy"].append(sums[0] / sums[1].clamp(min=1))
+                m[n].append(defer_mean(v))
+            m["entropy"].append(defer_ratio(ent.sum(), torch.tensor(float(ent.numel()), device=ent.device)))
             if mode == "train":
-                self._num_tokens = getattr(self, "_num_tokens", 0.0) + float(sums[2])
-            m["num_tokens"].append(getattr(self, "_num_tokens", 0.0))
+                seen = inputs["attention_mask"].sum().float()
+                prev = getattr(self, "_num_tokens_local", None)
+                self._num_tokens_local = seen if prev is None else prev + seen
+            if getattr(self, "_num_tokens_local", None) is not None:
+                # running local count; summed over the ranks when the log call resolves it
+                m["num_tokens"].append(DeferredMetric(self._num_tokens_local.reshape(1).clone(), "sum"))
         return (loss, None) if return_outputs else loss
 
     def _wpo_weights(self, model, ex, P):
@@ -466,6 +465,7 @@ class DPOTrainer(Trainer):
 
     def log(self, logs, start_time=None):
         mode = "train" if self.model.training else "eval"
+        resolve_deferred_metrics(self._metrics[mode])
         for k in list(self._metrics[mode].keys()):
             self._metrics[mode][k] = [float(v) for v in self._metrics[mode][k]]
         super().log(logs, start_time)

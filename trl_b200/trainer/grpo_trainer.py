@@ -20,7 +20,7 @@ from ..data_utils import is_conversational
 from ..parallel import dist as D
 from .grpo_config import GRPOConfig
 from .online_base import OnlineTrainer
-from .utils import nanmax, nanmin, nanstd, pad
+from .utils import defer_mean, defer_ratio, nanmax, nanmin, nanstd, pad
 
 
 class GRPOTrainer(OnlineTrainer):
@@ -47,6 +47,9 @@ class GRPOTrainer(OnlineTrainer):
         self.vllm_importance_sampling_correction = a.vllm_importance_sampling_correction
         self.entropy_coef = a.entropy_coef
         self._entropy_bonus_enabled = a.entropy_coef != 0.0 or a.use_adaptive_entropy
+        # entropy measured over the previous optimizer step; with the adaptive controller the bonus stays off until one was measured
+        self._last_world_entropy = float("inf")
+        self._entropy_window_stats = None
         if self.tools and not self.rollout_func:
             from .tool_loop import ToolLoop
 
@@ -226,16 +229,13 @@ class GRPOTrainer(OnlineTrainer):
         else:
             lr = diff
         ratio = torch.exp(lr)
-        cmax, cmin = a.vllm_importance_sampling_clip_max, a.vllm_importance_sampling_clip_min
+        # a missing bound does not clip on that side (grpo_trainer.py:2596-2616)
+        cmax = float("inf") if a.vllm_importance_sampling_clip_max is None else a.vllm_importance_sampling_clip_max
+        cmin = float("-inf") if a.vllm_importance_sampling_clip_min is None else a.vllm_importance_sampling_clip_min
         if mode.endswith("truncate"):
-            ratio = torch.clamp(ratio, max=cmax)
-            if cmin is not None:
-                ratio = torch.clamp(ratio, min=cmin)
+            ratio = torch.clamp(ratio, min=cmin, max=cmax)
         else:
-            bad = ratio > cmax
-            if cmin is not None:
-                bad = bad | (ratio < cmin)
-            ratio = ratio.masked_fill(bad, 0.0)
+            ratio = ratio.masked_fill((ratio > cmax) | (ratio < cmin), 0.0)
         return ratio.expand_as(mask) if ratio.shape != mask.shape else ratio
 
     # ---- loss ----------------------------------------------------------------------------------------------------------
@@ -255,14 +255,19 @@ class GRPOTrainer(OnlineTrainer):
     def get_gamma_weights(advantages, log_ratio_per_token, mask, importance_sampling_ratio, k_pos, lambda_pos, k_neg,
                           lambda_neg):
         """VESPO sequence weights: phi(w) = w^k exp(lambda (1 - w)) on the detached sequence ratio."""
-        lr = log_ratio_per_token.detach()
-        if importance_sampling_ratio is not None:
-            lr = lr + torch.log(importance_sampling_ratio.clamp_min(1e-8))
+        # numeric guards of grpo_trainer.py:2943-2990: token log-ratios are clamped to [-20, 20] before the sequence
+        # sum, the rollout correction enters unmasked, log w is clamped again, lambda has a floor, NaN/inf -> finite
+        lr = torch.clamp(log_ratio_per_token.detach(), -20.0, 20.0)
         seq = (lr * mask).sum(-1, keepdim=True)
+        if importance_sampling_ratio is not None:
+            isr = torch.log(importance_sampling_ratio.clamp_min(1e-8))
+            seq = seq + (isr.sum(-1, keepdim=True) if isr.shape[-1] == mask.shape[-1] else isr)
+        seq = torch.clamp(seq, -20.0, 20.0)
         k = torch.where(advantages >= 0, torch.full_like(advantages, k_pos), torch.full_like(advantages, k_neg))
-        lam = torch.where(advantages >= 0, torch.full_like(advantages, lambda_pos), torch.full_like(advantages, lambda_neg))
+        lam = torch.where(advantages >= 0, torch.full_like(advantages, lambda_pos),
+                          torch.full_like(advantages, lambda_neg)).clamp(min=1e-4)
         logphi = k * seq + lam * (1 - torch.exp(seq))
-        return torch.exp(logphi).detach()
+        return torch.nan_to_num(torch.exp(logphi), nan=0.0, posinf=0.0, neginf=0.0).detach()
 
     def _compute_loss(self, model, inputs):
         a = self.args
@@ -274,7 +279,10 @@ class GRPOTrainer(OnlineTrainer):
         maskf = mask.float()
         logps, entropies = self._get_per_token_logps_and_entropies(model, prompt_ids, completion_ids,
                                                                    compute_entropy=True,
-                                                                   pixel_values_list=inputs.get("pixel_values_list"))
+                                                                   pixel_values_list=inputs.get("pixel_values_list"),
+                                                                   entropy_grad=self._entropy_bonus_enabled
+                                                                   and torch.is_grad_enabled())
+        ent_stat = entropies.detach()
         Tc = logps.shape[1]
         if maskf.shape[1] != Tc:  # the buffered mask is padded to the generation batch's longest completion
             maskf = maskf[:, :Tc] if maskf.shape[1] > Tc else torch.nn.functional.pad(maskf, (0, Tc - maskf.shape[1]))
@@ -285,7 +293,7 @@ class GRPOTrainer(OnlineTrainer):
             return t[:, :Tc] if t.shape[1] > Tc else torch.nn.functional.pad(t, (0, Tc - t.shape[1]))
         entropy_mask = None
         if self.top_entropy_quantile < 1.0:
-            entropy_mask = self.get_high_entropy_mask(entropies, maskf, 1 - self.top_entropy_quantile)
+            entropy_mask = self.get_high_entropy_mask(ent_stat, maskf, 1 - self.top_entropy_quantile)
         advantages = inputs["advantages"]
         adv2 = advantages[:, None] if advantages.ndim == 1 else advantages
         old = fit(inputs.get("old_per_token_logps"))
@@ -309,17 +317,14 @@ class GRPOTrainer(OnlineTrainer):
                 row_scale = (D.world_size() / inputs["num_items_in_batch"].clamp(min=1.0)).expand(B)
             loss, stats = K.grpo_loss(logps, old, ref if self.beta != 0.0 else None, advantages, maskf, row_scale.float(),
                                       entropies, self.epsilon_low, self.epsilon_high, self.beta, a.delta)
-            n = stats[4].clamp(min=1.0)
-            red = torch.stack([stats[1], stats[2], stats[3], stats[6], stats[7], stats[4]]).clone()
-            if D.world_size() > 1:
-                D.all_reduce(red, "sum")
-            tot = red[5].clamp(min=1.0)
+            # local partial sums only: the cross-rank reduction happens once per logging step
+            st = stats.detach().clone()
             if self.beta != 0.0:
-                m["kl"].append(red[0] / tot)
-            m["clip_ratio/low_mean"].append(red[1] / tot)
-            m["clip_ratio/high_mean"].append(red[2] / tot)
-            m["clip_ratio/region_mean"].append(red[3] / tot)
-            m["entropy"].append(red[4] / tot)
+                m["kl"].append(defer_ratio(st[1], st[4]))
+            m["clip_ratio/low_mean"].append(defer_ratio(st[2], st[4]))
+            m["clip_ratio/high_mean"].append(defer_ratio(st[3], st[4]))
+            m["clip_ratio/region_mean"].append(defer_ratio(st[6], st[4]))
+            m["entropy"].append(defer_ratio(st[7], st[4]))
             return self._add_aux(loss, m)
         # ---- general path (autograd over PyTorch ops) -----------------------------------------------------------------
         old = logps.detach() if old is None else old
@@ -377,44 +382,59 @@ class GRPOTrainer(OnlineTrainer):
         if kl is not None:
             per_tok = per_tok + self.beta * kl
         if self.loss_type in ("grpo", "sapo", "gmpo"):
-            loss = ((per_tok * maskf).sum(-1) / maskf.sum(-1).clamp(min=1.0)).mean() / ga
+            loss, normalizer = ((per_tok * maskf).sum(-1) / maskf.sum(-1).clamp(min=1.0)).mean(), ga
         elif self.loss_type == "bnpo":
-            loss = (per_tok * maskf).sum() / maskf.sum().clamp(min=1.0) / ga
+            loss, normalizer = (per_tok * maskf).sum() / maskf.sum().clamp(min=1.0), ga
         elif self.loss_type == "dr_grpo":
-            loss = (per_tok * maskf).sum() / (B * self.max_completion_length) / ga
+            loss, normalizer = (per_tok * maskf).sum() / (B * self.max_completion_length), ga
         elif self.loss_type in ("cispo", "dapo", "vespo"):
-            loss = (per_tok * maskf).sum() / (inputs["num_items_in_batch"].clamp(min=1.0) / D.world_size())
+            normalizer = inputs["num_items_in_batch"].clamp(min=1.0) / D.world_size()
+            loss = (per_tok * maskf).sum()
         else:  # luspo
-            loss = (per_tok * maskf.sum(1, keepdim=True)).mean() / ga
+            loss, normalizer = (per_tok * maskf.sum(1, keepdim=True)).mean(), ga
+        loss = loss / normalizer
         if self._entropy_bonus_enabled:
+            # L = L_policy - coef * H with H the mean per-token entropy of the active tokens, differentiable through
+            # the lm_head (grpo_trainer.py:3155-3215).  The term is scaled so that it accumulates to H over the
+            # optimizer step whatever the loss type's own normaliser is.
             eff = maskf if entropy_mask is None else maskf * entropy_mask
-            sums = torch.stack([(entropies * eff).sum(), eff.sum()])
-            g = D.all_reduce(sums.clone(), "sum") if D.world_size() > 1 else sums
-            mean_ent = g[0] / g[1].clamp(min=1.0)
-            # entropy carries no gradient through the fused head: the bonus acts through the
-            # score-function surrogate -(H_t + log p_t) * log p_t, detached in its first factor
-            surrogate = (-(logps.detach() + entropies) * logps * eff).sum() / g[1].clamp(min=1.0) * D.world_size()
-            loss = loss - self.entropy_coef * surrogate / ga
-            m["entropy_coef"].append(self.entropy_coef)
+            if self.loss_type in ("cispo", "dapo", "vespo"):
+                entropy_loss = (entropies * eff).sum() / normalizer
+            else:
+                entropy_loss = (entropies * eff).sum() / eff.sum().clamp(min=1.0) / normalizer
+            # coefficient and gate are those fixed at the end of the previous optimizer step, so that every
+            # micro-batch of the window applies the same bonus
+            apply_coef = self.entropy_coef
+            if a.use_adaptive_entropy and not (self._last_world_entropy <= a.entropy_target):
+                apply_coef = 0.0
+            m["policy_loss"].append(defer_mean(loss.detach() * (1.0 if self.loss_type in ("cispo", "dapo", "vespo")
+                                                                else normalizer)))
+            loss = loss - apply_coef * entropy_loss
             if a.use_adaptive_entropy and mode == "train":
-                self._pending_entropy = float(mean_ent)
+                # running [entropy sum, token count] of the accumulation window, kept on the device
+                stats_w = torch.stack([(ent_stat * eff).sum(), eff.sum()])
+                self._entropy_window_stats = stats_w if self._entropy_window_stats is None \
+                    else self._entropy_window_stats + stats_w
+                if getattr(self, "sync_gradients", True):
+                    self._update_entropy_controller()
+            if mode == "train" and getattr(self, "sync_gradients", True):
+                m["entropy_coef"].append(self.entropy_coef)
 
         def mmean(x):
-            s = torch.stack([(x * maskf).sum(), maskf.sum()])
-            if D.world_size() > 1:
-                D.all_reduce(s, "sum")
-            return s[0] / s[1].clamp(min=1.0)
-        m["entropy"].append(mmean(entropies))
+            if x.shape[1] == 1 and maskf.shape[1] != 1:  # one value per sequence (sequence-level importance sampling)
+                return defer_ratio(x.sum(), torch.tensor(float(x.shape[0]), device=x.device))
+            return defer_ratio((x * maskf).sum(), maskf.sum())
+        m["entropy"].append(mmean(ent_stat))
         if kl is not None:
             m["kl"].append(mmean(kl.detach()))
         if self.loss_type in ("grpo", "bnpo", "dr_grpo", "dapo", "luspo"):
-            low = ((coef_1 < 1 - self.epsilon_low) & (adv2 < 0)).float().expand_as(maskf)
-            high = ((coef_1 > 1 + self.epsilon_high) & (adv2 > 0)).float().expand_as(maskf)
+            low = ((coef_1 < 1 - self.epsilon_low) & (adv2 < 0)).float()
+            high = ((coef_1 > 1 + self.epsilon_high) & (adv2 > 0)).float()
             m["clip_ratio/low_mean"].append(mmean(low))
             m["clip_ratio/high_mean"].append(mmean(high))
             m["clip_ratio/region_mean"].append(mmean(((low + high) > 0).float()))
         elif self.loss_type == "cispo":
-            m["cispo_clip_ratio"].append(mmean(((coef_1 > self.epsilon_high) & (adv2 > 0)).float().expand_as(maskf)))
+            m["cispo_clip_ratio"].append(mmean(((coef_1 > self.epsilon_high) & (adv2 > 0)).float()))
         return self._add_aux(loss, m)
 
     def _add_aux(self, loss, m):
@@ -441,16 +461,24 @@ class GRPOTrainer(OnlineTrainer):
         return ((entropies >= thr) & mask.bool()).float()
 
     # ---- adaptive entropy controller --------------------------------------------------------------------------------
-    def training_step(self, model, inputs, num_items_in_batch=None):
-        out = super().training_step(model, inputs, num_items_in_batch)
+    def _update_entropy_controller(self):
+        """At the optimizer-step boundary: reduce the window's [entropy sum, token count] over the ranks (one small
+        collective and one host read per optimizer step), move the coefficient by one delta towards the target and
+        remember the measured entropy, which gates the bonus of the next window (grpo_trainer.py:3189-3210)."""
         a = self.args
-        if a.use_adaptive_entropy and getattr(self, "_pending_entropy", None) is not None:
-            if self._pending_entropy < a.entropy_target:
-                self.entropy_coef = min(a.entropy_coef_max, self.entropy_coef + a.entropy_coef_delta)
-            else:
-                self.entropy_coef = max(a.entropy_coef_min, self.entropy_coef - a.entropy_coef_delta)
-            self._pending_entropy = None
-        return out
+        w = self._entropy_window_stats
+        self._entropy_window_stats = None
+        if w is None:
+            return
+        if D.world_size() > 1:
+            w = D.all_reduce(w.clone(), "sum")
+        tot = w.tolist()
+        world_entropy = tot[0] / max(tot[1], 1.0)
+        if world_entropy <= a.entropy_target:
+            self.entropy_coef = min(self.entropy_coef + a.entropy_coef_delta, a.entropy_coef_max)
+        else:
+            self.entropy_coef = max(self.entropy_coef - a.entropy_coef_delta, a.entropy_coef_min)
+        self._last_world_entropy = world_entropy
 
     def prediction_step(self, model, inputs, prediction_loss_only=True, ignore_keys=None):
         inputs = self._prepare_inputs(inputs)
@@ -463,11 +491,13 @@ class GRPOTrainer(OnlineTrainer):
         if self.args.use_adaptive_entropy and self.args.should_save:
             folder = os.path.join(self.args.output_dir, f"checkpoint-{self.state.global_step}")
             with open(os.path.join(folder, "entropy_ctrl_state.json"), "w") as f:
-                json.dump({"entropy_coef": self.entropy_coef}, f)
+                json.dump({"entropy_coef": self.entropy_coef, "last_world_entropy": self._last_world_entropy}, f)
 
     def _on_checkpoint_loaded(self, folder: str):
         p = os.path.join(folder, "entropy_ctrl_state.json")
         if os.path.exists(p):
             with open(p) as f:
-                self.entropy_coef = json.load(f)["entropy_coef"]
+                st = json.load(f)
+            self.entropy_coef = st["entropy_coef"]
+            self._last_world_entropy = st.get("last_world_entropy", float("inf"))
         self._buffered_inputs = None  # a resumed run regenerates (grpo_trainer.py:1572-1574)

@@ -28,7 +28,7 @@ from ..ops import functional as ops
 from ..parallel import dist as D
 from ..rollout.sampling import SamplingParams
 from .utils import (RepeatSampler, create_model_from_path, disable_dropout_in_model, nanmax, nanmin, nanstd, pad,
-                    print_prompt_completions_sample, run_coroutine_sync, shuffle_sequence_dict, split_tensor_dict,
+                    print_prompt_completions_sample, resolve_deferred_metrics, run_coroutine_sync, shuffle_sequence_dict, split_tensor_dict,
                     use_adapter)
 
 RewardFunc = Any
@@ -388,9 +388,11 @@ class OnlineTrainer(Trainer):
 
     # ---- log-probabilities --------------------------------------------------------------------------------------------
     def _get_per_token_logps_and_entropies(self, model, prompt_ids, completion_ids, batch_size=None,
-                                           compute_entropy=False, temperature=None, pixel_values_list=None):
+                                           compute_entropy=False, temperature=None, pixel_values_list=None,
+                                           entropy_grad=False):
         """prompt_ids / completion_ids: lists of id lists.  Returns padded [B, Tc] log-probs (and entropies).
-        ``pixel_values_list``: per sequence the pixel tensor of its images (vision-language models)."""
+        ``pixel_values_list``: per sequence the pixel tensor of its images (vision-language models).
+        ``entropy_grad``: the entropies are differentiable (entropy bonus) instead of detached statistics."""
         temperature = self.temperature if temperature is None else temperature
         dev = self.args.device
         B = len(prompt_ids)
@@ -437,7 +439,8 @@ class OnlineTrainer(Trainer):
             hidden = model.forward_hidden(flat, ctx, **fwd_kw)
             tgt = flat[sel_t + 1]
             lp, en = ops.lm_head_logprobs(hidden[sel_t], model.lm_head_weight, tgt, temperature,
-                                          softcap=model.config.final_logit_softcapping, compute_entropy=compute_entropy)
+                                          softcap=model.config.final_logit_softcapping, compute_entropy=compute_entropy,
+                                          entropy_grad=entropy_grad and compute_entropy)
             if getattr(self, "_keep_selected_hidden", False):  # value heads read the same rows (PPO)
                 self._selected_hidden = (hidden[sel_t], r, c_, flat, ctx, sel_t)
             logps = logps.index_put((r, c_), lp)
@@ -473,6 +476,7 @@ class OnlineTrainer(Trainer):
     def log(self, logs: dict, start_time: float | None = None):
         mode = "train" if self.model.training else "eval"
         m = self._metrics[mode]
+        resolve_deferred_metrics(m)
         for k in list(m.keys()):
             vals = [float(v) for v in m[k]]
             vals = [v for v in vals if v == v]  # drop NaN

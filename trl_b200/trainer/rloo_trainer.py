@@ -16,7 +16,7 @@ from ..data_utils import is_conversational
 from ..parallel import dist as D
 from .grpo_config import RLOOConfig
 from .online_base import OnlineTrainer
-from .utils import nanstd
+from .utils import defer_mean, defer_ratio, nanstd
 
 
 class RLOOTrainer(OnlineTrainer):
@@ -130,19 +130,13 @@ class RLOOTrainer(OnlineTrainer):
         aux = getattr(self, "_last_aux_loss", None)
         if aux is not None:
             loss = loss + self.args.router_aux_loss_coef * aux / ga
-        with torch.no_grad():
-            s = torch.stack([(ents * maskf).sum(), maskf.sum()])
-            if D.world_size() > 1:
-                D.all_reduce(s, "sum")
-            m["entropy"].append(s[0] / s[1].clamp(min=1))
+        with torch.no_grad():  # local partial results; reduced once per logging step
+            m["entropy"].append(defer_ratio((ents * maskf).sum(), maskf.sum()))
             low = ((ratio < 1 - self.epsilon_low) & (adv < 0)).float()
             high = ((ratio > 1 + self.epsilon_high) & (adv > 0)).float()
-            c = torch.stack([low.mean(), high.mean(), ((low + high) > 0).float().mean()])
-            if D.world_size() > 1:
-                D.all_reduce(c, "mean")
-            m["clip_ratio/low_mean"].append(c[0])
-            m["clip_ratio/high_mean"].append(c[1])
-            m["clip_ratio/region_mean"].append(c[2])
+            m["clip_ratio/low_mean"].append(defer_mean(low.mean()))
+            m["clip_ratio/high_mean"].append(defer_mean(high.mean()))
+            m["clip_ratio/region_mean"].append(defer_mean(((low + high) > 0).float().mean()))
         return loss
 
     def prediction_step(self, model, inputs, prediction_loss_only=True, ignore_keys=None):

@@ -272,6 +272,7 @@ class SFTTrainer(Trainer):
             from ..models.activation_offloading import get_act_offloading_ctx_manager
 
             self.maybe_activation_offload_context = get_act_offloading_ctx_manager(self.model)
+            self._own_offload_scope = True  # compute_loss wraps the decoder forward itself
         else:
             import contextlib
 

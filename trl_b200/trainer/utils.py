@@ -147,6 +147,56 @@ def nanmax(t: torch.Tensor) -> torch.Tensor:
     return v.max() if v.numel() else t.new_tensor(float("nan"))
 
 
+class DeferredMetric:
+    """A metric value whose cross-rank reduction waits for the next ``log`` call.
+
+    The reference reduces every metric in the micro-batch that produced it (``accelerator.reduce`` /
+    ``gather`` inside ``compute_loss``, e.g. trl/trainer/grpo_trainer.py:3226-3235), which makes every
+    micro-batch a synchronisation point between ranks with different sequence lengths.  Here a micro-batch only
+    records its local partial sums on the device; :func:`resolve_deferred_metrics` reduces all of them with ONE
+    collective (and one host read) per logging step and yields the same numbers: ``ratio`` entries become
+    ``sum_over_ranks(num) / max(sum_over_ranks(den), 1)``, ``mean`` entries the mean over ranks, ``sum`` entries
+    the sum over ranks.
+    """
+
+    __slots__ = ("local", "kind")
+
+    def __init__(self, local: torch.Tensor, kind: str):
+        self.local, self.kind = local, kind
+
+
+def defer_ratio(num: torch.Tensor, den: torch.Tensor) -> DeferredMetric:
+    return DeferredMetric(torch.stack([num.detach().float().reshape(()), den.detach().float().reshape(())]), "ratio")
+
+
+def defer_mean(value: torch.Tensor) -> DeferredMetric:
+    return DeferredMetric(value.detach().float().reshape(1), "mean")
+
+
+def resolve_deferred_metrics(metrics: dict) -> None:
+    """Replace every :class:`DeferredMetric` in ``metrics`` (name -> list) by its globally reduced float.
+    Every rank must hold the same entries in the same order (they do: the entries follow the code path, not the data)."""
+    from ..parallel import dist as D
+
+    pend = [(k, i) for k in sorted(metrics) for i, e in enumerate(metrics[k]) if isinstance(e, DeferredMetric)]
+    if not pend:
+        return
+    flat = torch.cat([metrics[k][i].local for k, i in pend])
+    world = D.world_size()
+    if world > 1:
+        D.all_reduce(flat, "sum")
+    vals = flat.tolist()
+    o = 0
+    for k, i in pend:
+        e = metrics[k][i]
+        if e.kind == "ratio":
+            metrics[k][i] = vals[o] / max(vals[o + 1], 1.0)
+            o += 2
+        else:
+            metrics[k][i] = vals[o] / (world if e.kind == "mean" else 1)
+            o += 1
+
+
 def split_tensor_dict(d: dict[str, Any], num_chunks: int) -> list[dict[str, Any]]:
     """Equal dim-0 chunks; 0-dim tensors / scalars replicated, ``None`` preserved (utils.py:893-927)."""
     first = next(v for v in d.values() if torch.is_tensor(v) and v.ndim > 0)
