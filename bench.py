@@ -30,6 +30,7 @@ import time
 
 os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 os.environ.setdefault("TOKENIZERS_PARALLELISM", "false")
+os.environ.setdefault("TRL_B200_PROFILE_MAX_OVER_RANKS", "1")  # phases_s: a phase is as slow as its slowest rank
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -49,10 +50,10 @@ def parse():
     ap.add_argument("--rollout-tp", type=int, default=0, help="0 = 2 when more than one GPU, else 1")
     ap.add_argument("--layers", type=int, default=None, help="debug only: truncating the model invalidates the number")
     ap.add_argument("--grad-ckpt", default="on", choices=["on", "off"],
-                    help="activation checkpointing.  Measured: with it off the 8-GPU step is SLOWER (10.6 s against "
-                         "8.0 s): next to the symmetric arenas, both weight copies and the KV cache the kept "
-                         "activations push the caching allocator into free-and-retry cycles; an out-of-memory warm-up "
-                         "step switches it back on")
+                    help="activation checkpointing (an out-of-memory warm-up step switches it back on)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the DPO / SFT Llama-3-8B rows that are measured after the headline and reported under "
+                         "'extras'")
     ap.add_argument("--shard", default=None,
                     help="engine shard mode (default: zero2 with more than one GPU, else ddp); full_shard_stream holds "
                          "1 / N of every layer per GPU for models whose training state does not fit otherwise")
@@ -217,6 +218,7 @@ def main():
             trainer._buffered_inputs = None
             torch.cuda.empty_cache()
     K.check_status(dev)
+    comm_check = trainer.engine.comm_selfcheck() if world > 1 and hasattr(trainer.engine, "comm_selfcheck") else None
     gen0 = trainer._total_generated_tokens
     torch.cuda.synchronize()
     D.barrier()
@@ -285,6 +287,8 @@ def main():
             "gpu_launches": int(launches), "clocks": clk, "peak_mem_gib": round(peak_gb, 1),
             "generated_tokens_per_step": float(gen_local) / a.steps,
         }
+        if comm_check is not None:
+            line["comm_selfcheck"] = comm_check
         if e2e is not None:
             line["e2e"] = e2e
             hist = [h for h in trainer.state.log_history if any(k.startswith("profiling/") for k in h)]
@@ -296,13 +300,70 @@ def main():
         if rs and "t_decode" in rs:  # only with TRL_B200_ROLLOUT_TIMING=1 (diagnostic: it adds host syncs)
             line["rollout_sections_s_total"] = {k: round(v, 3) for k, v in rs.items() if k.startswith("t_")}
             line["rollout_decode_steps_total"] = rs.get("decode_steps")
-        print(json.dumps(line))
+    else:
+        line = None
+    # ---- the DPO / SFT rows: measured after everything of the headline has been released -----------------------------
+    master_port = int(os.environ.get("MASTER_PORT", "29500"))
     D.barrier()
     if D.is_initialized():
         import torch.distributed as td
 
         td.destroy_process_group()
+    extras = None
+    if not a.no_extras and not a.layers:
+        del trainer, model, loader
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        free_gib = torch.cuda.mem_get_info()[0] / 2**30
+        extras = run_extras(world, rank, dev.index, master_port)
+        if extras is not None:
+            extras["free_gib_after_headline"] = round(free_gib, 1)
+    if rank == 0:
+        if extras is not None:
+            line["extras"] = extras
+        print(json.dumps(line))
     return 0
+
+
+def run_extras(world: int, rank: int, local_rank: int, master_port: int) -> dict:
+    """DPO (2 pairs per GPU, lengths U[64,512], frozen reference) and packed SFT (8192 tokens per GPU) on the
+    Llama-3-8B architecture with the full-shard engine, each in child processes of its own (one per rank, on this
+    rank's GPU, with its own rendezvous), so that a failure there cannot take the headline number with it."""
+    out = {}
+    shard = "full_shard" if world > 1 else "ddp"
+    for i, (task, key) in enumerate((("dpo", f"dpo_llama3_8b_{shard}_tok_s"), ("sft", f"sft_llama3_8b_{shard}_tok_s"))):
+        env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(local_rank), WORLD_SIZE=str(world),
+                   MASTER_ADDR=os.environ.get("MASTER_ADDR", "127.0.0.1"), MASTER_PORT=str(master_port + 37 + i))
+        cmd = [sys.executable, "-m", "trl_b200.benchmarks.train_throughput", "--task", task, "--model", "llama-3-8b",
+               "--shard", shard, "--steps", "3", "--warmup", "2"]
+        p = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
+                             cwd=os.path.dirname(os.path.abspath(__file__)))
+        try:
+            so, se = p.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            p.kill()  # this exact child, nothing else
+            so, se = p.communicate()
+            out[key] = None
+            out[key + "_note"] = "child run exceeded 240 s"
+            continue
+        if rank != 0:
+            continue
+        rec = None
+        for ln in so.splitlines():
+            if ln.startswith("{"):
+                try:
+                    rec = json.loads(ln)
+                except ValueError:
+                    pass
+        if p.returncode == 0 and rec is not None:
+            out[key] = rec["value"]
+            out[key + "_detail"] = {k: rec.get(k) for k in ("ms_per_step", "steps", "warmup", "n_gpus", "peak_mem_gib", "config")}
+        else:
+            out[key] = None
+            out[key + "_note"] = (se.strip().splitlines() or ["no output"])[-1][:200]
+    return out
 
 
 if __name__ == "__main__":

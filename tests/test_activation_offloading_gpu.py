@@ -51,5 +51,6 @@ def test_offloaded_run_matches_resident_run_and_lowers_the_peak(ckpt):
     for k in g0:  # the library attention backward accumulates with atomics: equal up to summation order
         assert (g0[k] - g1[k]).abs().max().item() <= 2e-2 * g0[k].abs().max().item() + 1e-6, k
     assert off.stats["offloaded"] > 0 and not off.tracker and not off.fwd_stash
-    # with checkpointing the 12 saved layer inputs (32 MiB each) leave the device; without it nearly everything does
-    assert peak1 < peak0 - (150 << 20), (peak0 >> 20, peak1 >> 20)
+    # with checkpointing the 12 saved layer inputs (32 MiB each) leave the device, except the few that the forward stash
+    # and the backward prefetch keep resident; without it nearly every saved activation does
+    assert peak1 < peak0 - ((100 << 20) if ckpt else (1 << 30)), (peak0 >> 20, peak1 >> 20)

@@ -115,3 +115,37 @@ def test_elastic_resume_with_another_world_size(tmp_path, tmp_path_factory, mode
     got = _run_stream(world2, mode2, "phase2", out, port + 1)
     for k in ref:
         assert torch.allclose(ref[k], got[k], atol=2e-5), (k, (ref[k] - got[k]).abs().max())
+
+
+def test_grpo_completions_are_dealt_to_ranks_by_length(tmp_path):
+    """After scoring, the job's completions are exchanged (token ids only) so that the ranks train on equal work."""
+    out = str(tmp_path / "bal.json")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29641", os.path.join(HERE, "dist_worker_grpo_balance.py"), out, "1"]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    with open(out) as f:
+        res = json.load(f)
+    r0, r1 = res["calls"]
+    assert len(r0) == len(r1) >= 1
+    for a, b in zip(r0, r1):
+        # the job keeps exactly the same (completion, advantage) pairs; each rank keeps its sample count
+        assert sorted(map(tuple, a["before"] + b["before"])) == sorted(map(tuple, a["after"] + b["after"]))
+        assert len(a["after"]) == len(a["before"]) == len(b["after"])
+        # token counts end up at least as even as they started
+        assert abs(a["tok_after"] - b["tok_after"]) <= abs(a["tok_before"] - b["tok_before"])
+        assert a["tok_after"] + b["tok_after"] == a["tok_before"] + b["tok_before"]
+    assert len(res["log"]) == 2 and all(h["loss"] == h["loss"] for h in res["log"])
+
+
+def test_balanced_partition_is_deterministic_and_even():
+    from trl_b200.trainer.utils import balanced_partition
+
+    costs = [1000, 10, 20, 990, 500, 480, 30, 15]
+    parts = balanced_partition(costs, 2, 4)
+    assert sorted(i for p in parts for i in p) == list(range(8)) and all(len(p) == 4 for p in parts)
+    loads = [sum(costs[i] for i in p) for p in parts]
+    assert abs(loads[0] - loads[1]) <= 40 and parts == balanced_partition(costs, 2, 4)
+    with pytest.raises(ValueError):
+        balanced_partition(costs, 3, 3)

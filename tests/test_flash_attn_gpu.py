@@ -1,0 +1,120 @@
+"""Varlen attention on tcgen05 vs the fp32 oracle (dense masked softmax): document boundaries, lengths that are not
+multiples of the tile, length-1 documents, grouped-query heads, sliding window, end-aligned masks."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk(lens, Hq, Hk, seed=0, strided=False):
+    torch.manual_seed(seed)
+    T = sum(lens)
+    if strided:  # views into one fused projection, as the decoder produces them
+        qkv = torch.randn(T, (Hq + 2 * Hk) * 128, device="cuda").to(torch.bfloat16)
+        q = qkv[:, : Hq * 128].view(T, Hq, 128)
+        k = qkv[:, Hq * 128:(Hq + Hk) * 128].view(T, Hk, 128)
+        v = qkv[:, (Hq + Hk) * 128:].view(T, Hk, 128)
+    else:
+        q = torch.randn(T, Hq, 128, device="cuda").to(torch.bfloat16)
+        k = torch.randn(T, Hk, 128, device="cuda").to(torch.bfloat16)
+        v = torch.randn(T, Hk, 128, device="cuda").to(torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    return q, k, v, cu
+
+
+@pytest.mark.parametrize("lens,Hq,Hk,window,strided", [
+    ([128], 2, 2, None, False), ([256, 128], 4, 2, None, False), ([1, 130, 7, 300, 1, 129], 4, 1, None, True),
+    ([700, 45], 14, 2, None, True), ([513, 64, 255], 2, 1, 100, False), ([1000], 2, 2, 257, True),
+])
+def test_fa_forward_matches_oracle(lens, Hq, Hk, window, strided):
+    from trl_b200.ops import cuda as K
+    from trl_b200.oracle import ops as ref
+
+    q, k, v, cu = _mk(lens, Hq, Hk, strided=strided)
+    out, lse = K.fa_varlen_fwd(q, k, v, cu, cu, causal=True, window=window)
+    torch.cuda.synchronize()
+    K.check_status()
+    want = ref.attention_varlen(q.float(), k.float(), v.float(), cu, causal=True, window=window)
+    err = (out.float() - want.float()).abs().max().item()
+    assert err < 2e-2, err
+    # log-sum-exp against the dense computation of one head
+    T = q.shape[0]
+    doc = torch.bucketize(torch.arange(T, device="cuda"), cu[1:].long(), right=True)
+    idx = torch.arange(T, device="cuda")
+    mask = (doc[:, None] == doc[None, :]) & (idx[:, None] >= idx[None, :])
+    if window:
+        mask &= idx[:, None] - idx[None, :] < window
+    s = (q[:, 0].float() @ k[:, 0].float().t()) / 128 ** 0.5
+    want_lse = torch.logsumexp(s.masked_fill(~mask, float("-inf")), -1)
+    assert (lse[0] - want_lse).abs().max().item() < 2e-2
+
+
+def test_fa_forward_noncausal_and_end_aligned_segments():
+    from trl_b200.ops import cuda as K
+    from trl_b200.oracle import ops as ref
+
+    torch.manual_seed(1)
+    lq, lk = [40, 128, 3], [200, 128, 131]
+    Tq, Tk, Hq, Hk = sum(lq), sum(lk), 4, 2
+    q = torch.randn(Tq, Hq, 128, device="cuda").to(torch.bfloat16)
+    k = torch.randn(Tk, Hk, 128, device="cuda").to(torch.bfloat16)
+    v = torch.randn(Tk, Hk, 128, device="cuda").to(torch.bfloat16)
+    cq = torch.tensor([0, 40, 168, 171], dtype=torch.int32, device="cuda")
+    ck = torch.tensor([0, 200, 328, 459], dtype=torch.int32, device="cuda")
+    out, _ = K.fa_varlen_fwd(q, k, v, cq, ck, causal=True)
+    want = ref.attention_varlen_qk(q.float(), k.float(), v.float(), cq, ck)
+    torch.cuda.synchronize()
+    K.check_status()
+    assert (out.float() - want.float()).abs().max().item() < 2e-2
+    cu = torch.tensor([0, 150, 300], dtype=torch.int32, device="cuda")
+    q2 = torch.randn(300, 2, 128, device="cuda").to(torch.bfloat16)
+    k2, v2 = k[:300, :2].contiguous(), v[:300, :2].contiguous()
+    out2, _ = K.fa_varlen_fwd(q2, k2, v2, cu, cu, causal=False)
+    want2 = ref.attention_varlen(q2.float(), k2.float(), v2.float(), cu, causal=False)
+    torch.cuda.synchronize()
+    assert (out2.float() - want2.float()).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("lens,Hq,Hk,window,strided", [
+    ([128], 2, 2, None, False), ([192, 64], 4, 2, None, False), ([1, 130, 7, 300, 1, 129], 4, 1, None, True),
+    ([700, 45], 14, 2, None, True), ([513, 64, 255], 2, 1, 100, False),
+])
+def test_fa_backward_matches_autograd_of_the_oracle(lens, Hq, Hk, window, strided):
+    from trl_b200.ops import cuda as K
+    from trl_b200.oracle import ops as ref
+
+    q, k, v, cu = _mk(lens, Hq, Hk, seed=2, strided=strided)
+    q, k, v = (t.detach().clone().requires_grad_() if not strided else t.detach().requires_grad_() for t in (q, k, v))
+    out = K.attention_varlen(q, k, v, cu, max(lens), True, window)
+    g = torch.randn_like(out)
+    dq, dk, dv = torch.autograd.grad(out, (q, k, v), g)
+    torch.cuda.synchronize()
+    K.check_status()
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    want = ref.attention_varlen(qf, kf, vf, cu, causal=True, window=window)
+    rq, rk, rv = torch.autograd.grad(want, (qf, kf, vf), g.float())
+    for name, a, b in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
+        err = (a.float() - b).abs().max().item()
+        assert err < 3e-2 * max(1.0, b.abs().max().item()), (name, err, b.abs().max().item())
+
+
+def test_fa_backward_end_aligned_segments():
+    from trl_b200.ops import cuda as K
+    from trl_b200.oracle import ops as ref
+
+    torch.manual_seed(5)
+    Hq, Hk = 4, 2
+    cq = torch.tensor([0, 40, 168, 171], dtype=torch.int32, device="cuda")
+    ck = torch.tensor([0, 200, 328, 459], dtype=torch.int32, device="cuda")
+    q = torch.randn(171, Hq, 128, device="cuda").to(torch.bfloat16).requires_grad_()
+    k = torch.randn(459, Hk, 128, device="cuda").to(torch.bfloat16).requires_grad_()
+    v = torch.randn(459, Hk, 128, device="cuda").to(torch.bfloat16).requires_grad_()
+    out = K.attention_varlen_qk(q, k, v, cq, ck, 128, 200)
+    g = torch.randn_like(out)
+    dq, dk, dv = torch.autograd.grad(out, (q, k, v), g)
+    torch.cuda.synchronize()
+    K.check_status()
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    rq, rk, rv = torch.autograd.grad(ref.attention_varlen_qk(qf, kf, vf, cq, ck), (qf, kf, vf), g.float())
+    for a, b in ((dq, rq), (dk, rk), (dv, rv)):
+        assert (a.float() - b).abs().max().item() < 3e-2 * max(1.0, b.abs().max().item())

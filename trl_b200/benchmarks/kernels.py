@@ -58,7 +58,7 @@ def timeit(fn, iters, warmup):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "lmhead", "lmhead_bwd", "decode_attn", "rmsnorm", "adamw", "grpo_loss", "moe", "decode_gemm"])
+    ap.add_argument("kernel", choices=["gemm", "lmhead", "lmhead_bwd", "decode_attn", "rmsnorm", "adamw", "grpo_loss", "moe", "decode_gemm", "fa"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4608)
     ap.add_argument("--k", type=int, default=3584)
@@ -189,6 +189,62 @@ def main():
             res[label + "_28_layers_ms"] = round(ms, 3)
             res[label + "_frac_of_copy_bw"] = round(total / ms / 1e6 / hbm, 3)
         out.update(batch=a.batch, gemms=rows, chain=res)
+    elif a.kernel == "fa":
+        # varlen attention, forward and forward + backward: this library's tcgen05 kernels against flash-attn's
+        # flash_attn_varlen_func (when importable) on two packings: one 8192-token pack of documents with log-uniform
+        # lengths in [128, 8192], and 8 sequences of 1280 tokens (the GRPO micro-batch shape)
+        import random
+
+        rows = []
+        rng = random.Random(0)
+        docs, left = [], 8192
+        while left > 0:
+            L = min(left, int(math.exp(rng.uniform(math.log(128), math.log(8192)))))
+            docs.append(L)
+            left -= L
+        for label, lens, Hq, Hk in (("pack8192_loguniform", docs, 32, 8), ("8x1280", [1280] * 8, 28, 4),
+                                    ("1x8192", [8192], 32, 8)):
+            T = sum(lens)
+            q = torch.randn(T, Hq, 128, device=dev, dtype=torch.bfloat16, requires_grad=True)
+            k = torch.randn(T, Hk, 128, device=dev, dtype=torch.bfloat16, requires_grad=True)
+            v = torch.randn(T, Hk, 128, device=dev, dtype=torch.bfloat16, requires_grad=True)
+            cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+            g = torch.randn(T, Hq, 128, device=dev, dtype=torch.bfloat16)
+            flops = sum(4.0 * Hq * 128 * L * (L + 1) / 2 for L in lens)  # causal: QK^T and PV over the visible half
+
+            def own_fwd():
+                with torch.no_grad():
+                    return K.attention_varlen(q, k, v, cu, max(lens), True, None)
+
+            def own_fb():
+                o = K.attention_varlen(q, k, v, cu, max(lens), True, None)
+                torch.autograd.grad(o, (q, k, v), g)
+
+            rec = {"case": label, "tokens": T, "docs": len(lens), "heads": [Hq, Hk]}
+            t = timeit(own_fwd, a.iters, a.warmup)
+            rec.update(own_fwd_ms=round(t, 4), own_fwd_tflops=round(flops / t / 1e9, 1))
+            t = timeit(own_fb, a.iters, a.warmup)
+            rec.update(own_fwd_bwd_ms=round(t, 4), own_fwd_bwd_tflops=round(3.5 * flops / t / 1e9, 1))
+            if a.baseline:
+                try:
+                    from flash_attn import flash_attn_varlen_func
+
+                    def lib_fwd():
+                        with torch.no_grad():
+                            return flash_attn_varlen_func(q, k, v, cu, cu, max(lens), max(lens), causal=True)
+
+                    def lib_fb():
+                        o = flash_attn_varlen_func(q, k, v, cu, cu, max(lens), max(lens), causal=True)
+                        torch.autograd.grad(o, (q, k, v), g)
+
+                    t = timeit(lib_fwd, a.iters, a.warmup)
+                    rec.update(flash_attn_fwd_ms=round(t, 4), flash_attn_fwd_tflops=round(flops / t / 1e9, 1))
+                    t = timeit(lib_fb, a.iters, a.warmup)
+                    rec.update(flash_attn_fwd_bwd_ms=round(t, 4), flash_attn_fwd_bwd_tflops=round(3.5 * flops / t / 1e9, 1))
+                except Exception as e:  # noqa: BLE001
+                    rec["flash_attn"] = f"unavailable: {type(e).__name__}: {str(e)[:80]}"
+            rows.append(rec)
+        out.update(cases=rows)
     elif a.kernel == "moe":
         # Qwen3-30B-A3B expert shapes: 128 experts, hidden 2048, expert FFN 768, top-8; a.t tokens
         E, H, I, k = 128, 2048, 768, 8

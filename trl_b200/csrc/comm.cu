@@ -205,11 +205,19 @@ __global__ void norm_allreduce_kernel(Peers P, const float* __restrict__ my_sums
 // the flat parameter buffer (P.buf = flat_param on each rank) at [lo, lo+n).  With `mc` the store is
 // one multimem.st that NVSwitch replicates.  A closing barrier tells the peers their replica is whole.
 // ------------------------------------------------------------------------------------------------
+// Element ranges of the bucket (absolute indices, half-open) that are exempt from weight decay: the biases and norm
+// weights that sit between the matrices of a layer bucket.  A handful per bucket, passed by value.
+constexpr int MAX_NODECAY = 16;
+struct NoDecay {
+  long long lo[MAX_NODECAY], hi[MAX_NODECAY];
+  int n;
+};
+
 __global__ void __launch_bounds__(512)
 adamw_bcast_kernel(Peers P, void* mc, long long lo, long long n, float* __restrict__ master,
                    const float* __restrict__ grad, float* __restrict__ m, float* __restrict__ v, float lr, float b1,
                    float b2, float eps, float wd, float bc1, float bc2_sqrt, const float* __restrict__ clip,
-                   uint32_t* epoch_ctr, uint32_t* local_gate, int channel, int* status) {
+                   uint32_t* epoch_ctr, uint32_t* local_gate, int channel, int* status, const NoDecay nd) {
   const uint32_t epoch = *epoch_ctr + 1;
   const float gs = clip ? *clip : 1.f;
   const long long nvec = n / 8;
@@ -225,12 +233,24 @@ adamw_bcast_kernel(Peers P, void* mc, long long lo, long long n, float* __restri
       float* mm = reinterpret_cast<float*>(&m4);
       float* vv = reinterpret_cast<float*>(&v4);
       float* pp = reinterpret_cast<float*>(&p4);
+      // decay applies unless the element lies in an exempt range (checked per element: a range may start mid-vector)
+      float wdj[4] = {wd, wd, wd, wd};
+      if (wd != 0.f) {
+        for (int r = 0; r < nd.n; ++r) {
+          const long long a0 = lo + i;
+          if (a0 + 4 > nd.lo[r] && a0 < nd.hi[r]) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (a0 + j >= nd.lo[r] && a0 + j < nd.hi[r]) wdj[j] = 0.f;
+          }
+        }
+      }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         mm[j] = mm[j] * b1 + (1.f - b1) * g[j];
         vv[j] = vv[j] * b2 + (1.f - b2) * g[j] * g[j];
         float p = pp[j];
-        p -= lr * wd * p;
+        p -= lr * wdj[j] * p;
         p -= (lr / bc1) * mm[j] / (sqrtf(vv[j]) / bc2_sqrt + eps);
         pp[j] = p;
         pv[h * 4 + j] = p;
@@ -654,13 +674,21 @@ TRLB_API int trlb_norm_allreduce(const unsigned long long* bufs, const unsigned 
 TRLB_API int trlb_adamw_bcast(const unsigned long long* bufs, const unsigned long long* pads, int rank, int world, void* mc,
                               long long lo, long long n, float* master, const float* grad, float* m, float* v, int step,
                               float lr, float b1, float b2, float eps, float wd, const float* clip, unsigned* epoch_ctr,
-                              unsigned* local_gate, int channel, int* status, cudaStream_t st) {
-  if (world > MAX_PEERS || n % 8 != 0 || lo % 8 != 0) return -1;
+                              unsigned* local_gate, int channel, int* status, const long long* nodecay, int n_nodecay,
+                              cudaStream_t st) {
+  // nodecay: n_nodecay pairs (lo, hi) of absolute element indices of the bucket that take no weight decay (host array)
+  if (world > MAX_PEERS || n % 8 != 0 || lo % 8 != 0 || n_nodecay < 0 || n_nodecay > MAX_NODECAY) return -1;
   Peers P = make_peers(bufs, pads, rank, world);
+  NoDecay nd = {};
+  for (int r = 0; r < n_nodecay; ++r) {
+    // keep only what intersects this rank's shard [lo, lo + n)
+    const long long a = nodecay[2 * r], b = nodecay[2 * r + 1];
+    if (b > lo && a < lo + n) { nd.lo[nd.n] = a; nd.hi[nd.n] = b; ++nd.n; }
+  }
   const float bc1 = 1.f - powf(b1, (float)step), bc2s = sqrtf(1.f - powf(b2, (float)step));
   const int grid = capped_grid(n / 8, 512);
   adamw_bcast_kernel<<<grid, 512, 0, st>>>(P, mc, lo, n, master, grad, m, v, lr, b1, b2, eps, wd, bc1, bc2s, clip,
-                                           epoch_ctr, local_gate, channel, status);
+                                           epoch_ctr, local_gate, channel, status, nd);
   return (int)cudaGetLastError();
 }
 

@@ -223,6 +223,24 @@ __device__ __forceinline__ uint64_t umma_desc_kmajor_sw128(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
   return d;
 }
+// MN-major operand (the contiguous dimension of the tile is M or N, not K), 128-byte swizzle: what a TMA tile of
+// [K rows][64 elements] is when the rows are the reduction dimension (V in P.V, Q in dS^T.Q, ...).  64-element
+// groups along M/N are `lbo_bytes` apart (one TMA box each), 8-row groups along K are 1024 bytes apart.  A K step of
+// 16 rows advances the start address by 2048 bytes.
+__device__ __forceinline__ uint64_t umma_desc_mnmajor_sw128(uint32_t smem_addr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor for kind::f16 with explicit operand majors (bit 15: A is MN-major, bit 16: B is MN-major).
+__host__ __device__ constexpr uint32_t umma_idesc_bf16_major(int M, int N, bool a_mn, bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
+         ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
 // Instruction descriptor for kind::f16: bf16 x bf16 -> fp32, both operands K-major.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);

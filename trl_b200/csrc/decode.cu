@@ -138,6 +138,57 @@ rope_kv_write_f32_kernel(float* __restrict__ acc, long long row_stride, const __
   }
 }
 
+// Same consumer without the per-head norm: one thread per rotation pair, laid out like rope_kv_write_kernel.
+__global__ void __launch_bounds__(256)
+rope_kv_write_f32_flat_kernel(float* __restrict__ acc, long long row_stride, const __nv_bfloat16* __restrict__ bias,
+                              const int* __restrict__ seq_lens, const int* __restrict__ slot_ids,
+                              const int* __restrict__ block_table, int max_blocks, int block_size,
+                              __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ kc,
+                              __nv_bfloat16* __restrict__ vc, int B, int Hq, int Hk, int D, float log2_theta, int v_t) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int half = D >> 1;
+  const int per_tok = (Hq + 2 * Hk) * half;
+  const long long total = (long long)B * per_tok;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int b = (int)(idx / per_tok);
+    const int r = (int)(idx % per_tok);
+    const int head = r / half, f = r % half;
+    float* src = acc + (size_t)b * row_stride + (size_t)head * D;
+    float lo = src[f], hi = src[half + f];
+    src[f] = 0.f;
+    src[half + f] = 0.f;
+    const int slot = slot_ids ? slot_ids[b] : b;
+    const int pos = seq_lens[slot];
+    if (pos < 0) continue;  // inactive slot: the sums are dropped
+    if (bias != nullptr) {
+      lo += __bfloat162float(bias[(size_t)head * D + f]);
+      hi += __bfloat162float(bias[(size_t)head * D + half + f]);
+    }
+    lo = __bfloat162float(__float2bfloat16(lo));  // the precision of a bf16 GEMM output
+    hi = __bfloat162float(__float2bfloat16(hi));
+    const int blk = block_table[(size_t)slot * max_blocks + pos / block_size];
+    const size_t cache_row = ((size_t)blk * block_size + pos % block_size) * Hk;
+    if (head < Hq + Hk) {
+      const float inv = exp2f(-log2_theta * (float)(2 * f) / (float)D);
+      float sn, cs;
+      sincosf((float)pos * inv, &sn, &cs);
+      __nv_bfloat16* dst = head < Hq ? q_out + ((size_t)b * Hq + head) * D : kc + (cache_row + (head - Hq)) * D;
+      dst[f] = __float2bfloat16(lo * cs - hi * sn);
+      dst[half + f] = __float2bfloat16(hi * cs + lo * sn);
+    } else if (v_t) {
+      __nv_bfloat16* dst = vc + (((size_t)blk * Hk + (head - Hq - Hk)) * D) * block_size + pos % block_size;
+      dst[(size_t)f * block_size] = __float2bfloat16(lo);
+      dst[(size_t)(half + f) * block_size] = __float2bfloat16(hi);
+    } else {
+      __nv_bfloat16* dst = vc + (cache_row + (head - Hq - Hk)) * D;
+      dst[f] = __float2bfloat16(lo);
+      dst[half + f] = __float2bfloat16(hi);
+    }
+  }
+}
+
 // k,v [T,Hk,D] (already rotated) of packed prompts -> cache.  tok_slot[t], tok_pos[t] give the
 // destination sequence slot and position of token t.
 __global__ void kv_write_prefill_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
@@ -426,6 +477,14 @@ TRLB_API int trlb_rope_kv_write_f32(float* acc, long long row_stride, const void
                                     void* vc, int B, int Hq, int Hk, int D, float theta, int v_t, cudaStream_t st) {
   if (B == 0) return 0;
   if (D > 128 || (D & 1)) return -1;
+  if (q_norm == nullptr && k_norm == nullptr) {
+    const long long work = (long long)B * (Hq + 2 * Hk) * (D / 2);
+    const int grid = (int)((work + 255) / 256);
+    return (int)trlb_host::launch_kernel(rope_kv_write_f32_flat_kernel, dim3(grid), dim3(256), 0, st,
+                                         trlb_host::pdl_enabled(), acc, row_stride, (const __nv_bfloat16*)bias, seq_lens,
+                                         slot_ids, block_table, max_blocks, block_size, (__nv_bfloat16*)q_out,
+                                         (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, B, Hq, Hk, D, log2f(theta), v_t);
+  }
   const int items = B * (Hq + 2 * Hk);
   const int grid = (items + 7) / 8;
   return (int)trlb_host::launch_kernel(rope_kv_write_f32_kernel, dim3(grid), dim3(256), 0, st, trlb_host::pdl_enabled(), acc,

@@ -323,7 +323,7 @@ int dg_launch(const CUtensorMap& tw, const CUtensorMap& tx, const DecodeGemmPara
 
 int dg_ctas_per_sm(int B, int mode) {
   if (B > 64) return (mode == DG_SWIGLU || g_ctas_per_sm < 2) ? 1 : 2;  // 128-row tiles: 256 / 512 TMEM columns each
-  if (mode == DG_SWIGLU) return g_ctas_per_sm >= 2 ? 2 : 1;             // 256 TMEM columns each
+  if (mode == DG_SWIGLU) return 1;  // SwiGLU slabs cannot be split along K: one CTA per SM with a deep ring
   return g_ctas_per_sm;
 }
 
@@ -393,7 +393,7 @@ TRLB_API int trlb_decode_gemm(const void* X, const void* W, const void* bias, fl
   for (int i = 0; i < n_peers; ++i) { p.peer_Y32[i] = peer_y32[i]; p.arrive[1 + i] = arrive[1 + i]; }
   const int ctas = trlb_decode_gemm_ctas(B, N, K, mode, max_ctas);
   if (BN == 64) {
-    if (mode == DG_SWIGLU) return dg_launch<64, true, 4, 2>(tw, tx, p, ctas, st);
+    if (mode == DG_SWIGLU) return dg_launch<64, true, 8, 1>(tw, tx, p, ctas, st);
     if (g_ctas_per_sm == 3) return dg_launch<64, false, 3, 3>(tw, tx, p, ctas, st);
     return dg_launch<64, false, 4, 2>(tw, tx, p, ctas, st);
   }

@@ -1,0 +1,988 @@
+// Variable-length (packed, padding-free) causal attention for training on the 5th-generation tensor cores:
+// forward, and a backward made of two kernels (dK/dV per key tile, dQ per query tile) that needs no atomics.
+//
+//   q [Tq, Hq, 128], k / v [Tk, Hk, 128] bf16 (row strides free: views into a fused QKV buffer work), sequences given
+//   by cu_seqlens_q / cu_seqlens_k.  Grouped-query attention reads the KV head hq / (Hq / Hk) directly: K and V are
+//   never expanded.  Masks: causal with the diagonal aligned to the END of the key segment (a query segment may be
+//   the tail of its key segment, which is what context parallelism needs; equal lengths give the usual causal
+//   mask), an optional sliding window, or none.
+//
+// Forward, one CTA per (128-query tile, query head), 192 threads:
+//   warp 0   TMA: the Q tile once, then K and V tiles of 128 keys through a 2-stage ring (separate barriers, so
+//            Q.K^T starts when K has landed);
+//   warp 1   tcgen05.mma: S_j = Q K_j^T into one of two TMEM buffers (issued one tile ahead, so the softmax of
+//            tile j runs under Q.K_{j+1}^T), then O_j = P_j V_j into one of two further TMEM buffers.  V is consumed
+//            as an MN-major operand straight from its TMA tile: no transpose anywhere;
+//   warps 2-5 one thread per query row: scale, mask, running max / sum in base 2, P_j written as a K-major swizzled
+//            bf16 tile for the second MMA, and the output accumulated in registers as acc = acc * alpha + O_j
+//            (O_j read back from TMEM), so nothing in TMEM ever needs rescaling and the MMA warp never waits for a
+//            correction step.
+//   TMEM: S0 S1 O0 O1 = 512 columns.  Output bf16 + log-sum-exp (natural log, fp32 [Hq, Tq]) for the backward.
+//
+// Every wait is bounded (common.cuh); a wait that runs out reports through the status words and the CTA leaves
+// through the normal teardown.
+//
+// Takes the place of the FlashAttention-2/3 kernels the reference reaches through transformers
+// (trl/trainer/sft_trainer.py:384-390,1144-1162: padding-free batches with cu_seqlens from position_ids).
+#include "common.cuh"
+
+namespace trlb {
+
+constexpr int FA_BM = 128, FA_BN = 128, FA_D = 128;
+constexpr int FA_THREADS = 192;
+constexpr uint32_t FA_TILE_BYTES = 128 * 128 * 2;  // a [128 x 128] bf16 tile = two TMA boxes of [128 rows x 64]
+constexpr uint32_t FA_BOX_BYTES = 128 * 64 * 2;
+constexpr int FA_KV_STAGES = 2;
+constexpr size_t FA_FWD_SMEM = FA_TILE_BYTES /*Q*/ + FA_TILE_BYTES /*P*/ + FA_KV_STAGES * 2 * FA_TILE_BYTES + 1024 + 512;
+
+struct FaParams {
+  const int* cu_q;
+  const int* cu_k;
+  int n_seq, Hq, Hk;
+  int causal, window;  // window <= 0: unlimited
+  float scale_log2;    // softmax scale * log2(e)
+  __nv_bfloat16* out;  // [Tq, Hq, 128]
+  long long out_row_stride;
+  float* lse;          // [Hq, Tq] natural log
+  int Tq;
+  int* status;
+};
+
+// Tile slot -> (sequence, query tile); tiles of a sequence are handed out from its LAST tile down, so the CTAs with
+// the most keys start first.  Returns false when the slot is beyond the last tile.
+__device__ __forceinline__ bool fa_find_tile(const int* cu_q, int n_seq, int slot, int& seq, int& tile) {
+  for (int s = 0; s < n_seq; ++s) {
+    const int nt = (cu_q[s + 1] - cu_q[s] + FA_BM - 1) / FA_BM;
+    if (slot < nt) { seq = s; tile = nt - 1 - slot; return true; }
+    slot -= nt;
+  }
+  return false;
+}
+
+// Range of key tiles [lo, hi] a query tile attends to; hi < lo means none.
+__device__ __forceinline__ void fa_kv_range(int tile, int lq, int lk, int causal, int window, int& lo, int& hi) {
+  const int off = lk - lq;  // key position of the diagonal for query position 0
+  const int q_first = tile * FA_BM, q_last = min(lq, q_first + FA_BM) - 1;
+  hi = (lk - 1) / FA_BN;
+  lo = 0;
+  if (causal) {
+    hi = min(hi, (q_last + off) / FA_BN);
+    if (q_last + off < 0) hi = -1;
+    if (window > 0) lo = max(0, q_first + off - window + 1) / FA_BN;
+  }
+}
+
+// byte offset of element (row r, column c) in a [128 x 128] bf16 K-major tile stored as two 128-byte-swizzled boxes
+__device__ __forceinline__ uint32_t fa_kmajor_off(int r, int c) {
+  return (uint32_t)((c >> 6) * FA_BOX_BYTES + (r >> 3) * 1024 + (r & 7) * 128 + ((((c & 63) >> 3) ^ (r & 7)) << 4) +
+                    (c & 7) * 2);
+}
+
+__global__ void __launch_bounds__(FA_THREADS, 1)
+fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+              const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
+  int seq, tile;
+  if (!fa_find_tile(p.cu_q, p.n_seq, (int)blockIdx.x, seq, tile)) return;  // uniform: before any barrier or TMEM use
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = smem;
+  uint8_t* p_s = smem + FA_TILE_BYTES;
+  uint8_t* kv_s = smem + 2 * FA_TILE_BYTES;  // stage s: K at s * 2 tiles, V one tile after it
+  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + FA_KV_STAGES * 2 * FA_TILE_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;     // [2]
+  uint64_t* v_full = bars + 3;     // [2]
+  uint64_t* kv_empty = bars + 5;   // [2]
+  uint64_t* s_full = bars + 7;     // [2]
+  uint64_t* s_empty = bars + 9;    // [2]
+  uint64_t* o_full = bars + 11;    // [2]
+  uint64_t* o_empty = bars + 13;   // [2]
+  uint64_t* p_full = bars + 15;
+  uint64_t* p_empty = bars + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, kvh = h / (p.Hq / p.Hk);
+  const int q_beg = p.cu_q[seq], lq = p.cu_q[seq + 1] - q_beg;
+  const int k_beg = p.cu_k[seq], lk = p.cu_k[seq + 1] - k_beg;
+  int lo, hi;
+  fa_kv_range(tile, lq, lk, p.causal, p.window, lo, hi);
+  const int n_kv = hi - lo + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], 4);
+      mbar_init(&o_full[s], 1);
+      mbar_init(&o_empty[s], 4);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(p_empty, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (n_kv > 0) {
+    if (warp == 0) {
+      // ---------------- TMA producer ----------------
+      if (lane == 0) {
+        mbar_expect_tx(q_full, FA_TILE_BYTES);
+        tma_load_2d(q_s, &tmap_q, q_full, h * FA_D, q_beg + tile * FA_BM);
+        tma_load_2d(q_s + FA_BOX_BYTES, &tmap_q, q_full, h * FA_D + 64, q_beg + tile * FA_BM);
+        for (int j = 0; j < n_kv; ++j) {
+          const int s = j & 1;
+          if (!mbar_wait(&kv_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, p.status, 1000 + s)) break;
+          uint8_t* ks = kv_s + (size_t)s * 2 * FA_TILE_BYTES;
+          uint8_t* vs = ks + FA_TILE_BYTES;
+          const int row = k_beg + (lo + j) * FA_BN;
+          mbar_expect_tx(&k_full[s], FA_TILE_BYTES);
+          tma_load_2d(ks, &tmap_k, &k_full[s], kvh * FA_D, row);
+          tma_load_2d(ks + FA_BOX_BYTES, &tmap_k, &k_full[s], kvh * FA_D + 64, row);
+          mbar_expect_tx(&v_full[s], FA_TILE_BYTES);
+          tma_load_2d(vs, &tmap_v, &v_full[s], kvh * FA_D, row);
+          tma_load_2d(vs + FA_BOX_BYTES, &tmap_v, &v_full[s], kvh * FA_D + 64, row);
+        }
+      }
+      __syncwarp();
+    } else if (warp == 1) {
+      // ---------------- MMA issuer ----------------
+      if (lane == 0) {
+        constexpr uint32_t idesc_s = umma_idesc_bf16_major(FA_BM, FA_BN, false, false);
+        constexpr uint32_t idesc_o = umma_idesc_bf16_major(FA_BM, FA_D, false, true);  // V is MN-major
+        const uint32_t q_u = smem_u32(q_s), p_u = smem_u32(p_s), kv_u = smem_u32(kv_s);
+        bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 1010);
+        auto issue_s = [&](int j) {
+          const int s = j & 1;
+          if (!mbar_wait(&k_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1020 + s)) return false;
+          if (!mbar_wait(&s_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, p.status, 1030 + s)) return false;
+          tc_fence_after();
+          const uint32_t k_u = kv_u + (uint32_t)s * 2 * FA_TILE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < FA_D / 16; ++kk) {
+            const uint32_t off = (uint32_t)(kk >> 2) * FA_BOX_BYTES;
+            umma_bf16_ss(tmem_base + (uint32_t)s * FA_BN, umma_desc_kmajor_sw128(q_u + off) + 2 * (kk & 3),
+                         umma_desc_kmajor_sw128(k_u + off) + 2 * (kk & 3), idesc_s, kk != 0);
+          }
+          umma_commit(&s_full[s]);
+          return true;
+        };
+        if (ok) ok = issue_s(0);
+        for (int j = 0; j < n_kv && ok; ++j) {
+          const int s = j & 1;
+          if (j + 1 < n_kv) ok = issue_s(j + 1);
+          if (!ok) break;
+          if (!mbar_wait(p_full, (uint32_t)(j & 1), abort_flag, p.status, 1040)) { ok = false; break; }
+          if (!mbar_wait(&v_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1050 + s)) { ok = false; break; }
+          if (!mbar_wait(&o_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, p.status, 1060 + s)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t v_u = kv_u + (uint32_t)s * 2 * FA_TILE_BYTES + FA_TILE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < FA_BN / 16; ++kk) {
+            const uint64_t adesc = umma_desc_kmajor_sw128(p_u + (uint32_t)(kk >> 2) * FA_BOX_BYTES) + 2 * (kk & 3);
+            const uint64_t bdesc = umma_desc_mnmajor_sw128(v_u + (uint32_t)kk * 2048, FA_BOX_BYTES);
+            umma_bf16_ss(tmem_base + 256 + (uint32_t)s * FA_D, adesc, bdesc, idesc_o, kk != 0);
+          }
+          umma_commit(&o_full[s]);
+          umma_commit(&kv_empty[s]);
+          umma_commit(p_empty);
+        }
+      }
+      __syncwarp();
+    } else {
+      // ---------------- softmax + output accumulation: one thread per query row ----------------
+      const int quarter = warp & 3;
+      const int r = quarter * 32 + lane;
+      const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+      const int q_pos = tile * FA_BM + r;  // position inside the query segment
+      const bool row_ok = q_pos < lq;
+      const int off = lk - lq;
+      // keys this row may see: [k_min, k_max]
+      const int k_max = p.causal ? min(lk - 1, q_pos + off) : lk - 1;
+      const int k_min = (p.causal && p.window > 0) ? max(0, q_pos + off - p.window + 1) : 0;
+      float acc[FA_D];
+#pragma unroll
+      for (int i = 0; i < FA_D; ++i) acc[i] = 0.f;
+      float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
+      bool ok = true;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j & 1;
+        const int key0 = (lo + j) * FA_BN;
+        ok = __all_sync(0xffffffffu, mbar_wait(&s_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1070 + s));
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t ts = tmem_base + lane_off + (uint32_t)s * FA_BN;
+        // pass 1: row maximum over this tile's visible keys
+        float m_tile = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < FA_BN; c += 32) {
+          float v[32];
+          tmem_ld_32x32(ts + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + c + i;
+            if (row_ok && key >= k_min && key <= k_max) m_tile = fmaxf(m_tile, v[i] * p.scale_log2);
+          }
+        }
+        const float m_new = fmaxf(m_run, m_tile);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        const float alpha = exp2f(m_run - m_use);  // 0 while nothing has been seen
+        // pass 2: probabilities -> P tile (bf16, K-major swizzled), row sum
+        ok = __all_sync(0xffffffffu, mbar_wait(p_empty, (uint32_t)((j & 1) ^ 1), abort_flag, p.status, 1080));
+        if (!ok) break;
+        float sum = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < FA_BN; c += 32) {
+          float v[32];
+          tmem_ld_32x32(ts + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+              const int key = key0 + c + i + e;
+              const bool a0 = row_ok && key >= k_min && key <= k_max;
+              const bool a1 = row_ok && key + 1 >= k_min && key + 1 <= k_max;
+              const float p0 = a0 ? exp2f(v[i + e] * p.scale_log2 - m_use) : 0.f;
+              const float p1 = a1 ? exp2f(v[i + e + 1] * p.scale_log2 - m_use) : 0.f;
+              w[e >> 1] = pack_bf16(p0, p1);
+              // the sum uses the rounded values, i.e. exactly what the second MMA multiplies with V
+              const float2 rr = unpack_bf16(w[e >> 1]);
+              sum += rr.x + rr.y;
+            }
+            *reinterpret_cast<uint4*>(p_s + fa_kmajor_off(r, c + i)) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_empty[s]);
+        fence_proxy_async_smem();
+        mbar_arrive(p_full);
+        l_run = l_run * alpha + sum;
+        m_run = m_new;
+        // fold in the previous tile's P.V while the tensor core works on this one
+        if (j > 0) {
+          const int sp = (j - 1) & 1;
+          ok = __all_sync(0xffffffffu, mbar_wait(&o_full[sp], (uint32_t)(((j - 1) >> 1) & 1), abort_flag, p.status, 1090 + sp));
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t to = tmem_base + lane_off + 256 + (uint32_t)sp * FA_D;
+#pragma unroll
+          for (int c = 0; c < FA_D; c += 32) {
+            float v[32];
+            tmem_ld_32x32(to + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[c + i] = acc[c + i] * alpha_prev + v[i];
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&o_empty[sp]);
+        }
+        alpha_prev = alpha;
+      }
+      if (ok) {
+        const int sp = (n_kv - 1) & 1;
+        ok = __all_sync(0xffffffffu, mbar_wait(&o_full[sp], (uint32_t)(((n_kv - 1) >> 1) & 1), abort_flag, p.status, 1095));
+        if (ok) {
+          tc_fence_after();
+          const uint32_t to = tmem_base + lane_off + 256 + (uint32_t)sp * FA_D;
+          const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+          __nv_bfloat16* dst = p.out + (long long)(q_beg + q_pos) * p.out_row_stride + (long long)h * FA_D;
+#pragma unroll
+          for (int c = 0; c < FA_D; c += 32) {
+            float v[32];
+            tmem_ld_32x32(to + c, v);
+            tmem_ld_wait();
+            if (row_ok) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                uint4 o;
+                o.x = pack_bf16((acc[c + i] * alpha_prev + v[i]) * inv, (acc[c + i + 1] * alpha_prev + v[i + 1]) * inv);
+                o.y = pack_bf16((acc[c + i + 2] * alpha_prev + v[i + 2]) * inv, (acc[c + i + 3] * alpha_prev + v[i + 3]) * inv);
+                o.z = pack_bf16((acc[c + i + 4] * alpha_prev + v[i + 4]) * inv, (acc[c + i + 5] * alpha_prev + v[i + 5]) * inv);
+                o.w = pack_bf16((acc[c + i + 6] * alpha_prev + v[i + 6]) * inv, (acc[c + i + 7] * alpha_prev + v[i + 7]) * inv);
+                *reinterpret_cast<uint4*>(dst + c + i) = o;
+              }
+            }
+          }
+          tc_fence_before();
+          if (row_ok && p.lse != nullptr)
+            p.lse[(long long)h * p.Tq + q_beg + q_pos] =
+                l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+        }
+      }
+    }
+  } else if (warp >= 2) {
+    // no visible key at all (a query segment longer than its key segment): zeros, log-sum-exp -inf
+    const int r = (warp & 3) * 32 + lane;
+    const int q_pos = tile * FA_BM + r;
+    if (q_pos < lq) {
+      __nv_bfloat16* dst = p.out + (long long)(q_beg + q_pos) * p.out_row_stride + (long long)h * FA_D;
+      for (int i = 0; i < FA_D; i += 8) *reinterpret_cast<uint4*>(dst + i) = make_uint4(0, 0, 0, 0);
+      if (p.lse != nullptr) p.lse[(long long)h * p.Tq + q_beg + q_pos] = -INFINITY;
+    }
+  }
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace trlb
+
+using namespace trlb;
+
+// q [Tq, Hq, 128] / k, v [Tk, Hk, 128] bf16 with row strides q_rs / k_rs / v_rs (elements; the head dimension is
+// contiguous and heads are 128 elements apart), cu_q / cu_k [n_seq + 1] int32 on the device.  out [Tq, Hq, 128] bf16
+// (row stride o_rs), lse [Hq, Tq] fp32 or null.  causal: the diagonal is aligned to the end of each key segment;
+// window > 0 limits every query to its last `window` keys.
+TRLB_API int trlb_fa_varlen_fwd(const void* q, const void* k, const void* v, long long q_rs, long long k_rs, long long v_rs,
+                                const int* cu_q, const int* cu_k, int n_seq, int Tq, int Tk, int Hq, int Hk, int D,
+                                float scale, int causal, int window, void* out, long long o_rs, float* lse, int* status,
+                                cudaStream_t st) {
+  if (Tq <= 0 || n_seq <= 0) return 0;
+  if (D != FA_D || Hk <= 0 || Hq % Hk != 0 || (q_rs % 8) || (k_rs % 8) || (v_rs % 8) || (o_rs % 8)) return -160;
+  CUtensorMap tq, tk, tv;
+  if (trlb_host::make_tmap_2d_bf16(&tq, q, (uint64_t)Tq, (uint64_t)Hq * D, (uint64_t)q_rs, FA_BM, 64)) return -161;
+  if (trlb_host::make_tmap_2d_bf16(&tk, k, (uint64_t)Tk, (uint64_t)Hk * D, (uint64_t)k_rs, FA_BN, 64)) return -162;
+  if (trlb_host::make_tmap_2d_bf16(&tv, v, (uint64_t)Tk, (uint64_t)Hk * D, (uint64_t)v_rs, FA_BN, 64)) return -163;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(fa_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FA_FWD_SMEM) != cudaSuccess)
+      return -164;
+    attr_set = true;
+  }
+  FaParams p = {};
+  p.cu_q = cu_q; p.cu_k = cu_k; p.n_seq = n_seq; p.Hq = Hq; p.Hk = Hk; p.causal = causal; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.out = (__nv_bfloat16*)out; p.out_row_stride = o_rs; p.lse = lse; p.Tq = Tq; p.status = status;
+  const int max_tiles = (Tq + FA_BM - 1) / FA_BM + n_seq;  // every sequence adds at most one partial tile
+  fa_fwd_kernel<<<dim3(max_tiles, Hq), FA_THREADS, FA_FWD_SMEM, st>>>(tq, tk, tv, p);
+  return (int)cudaGetLastError();
+}
+
+// =====================================================================================================================
+// Backward.  With P = softmax(S), S = scale * Q K^T, delta_i = sum_d dO_id O_id:
+//     dV = P^T dO        dP = dO V^T        dS = P o (dP - delta) * scale        dQ = dS K        dK = dS^T Q
+// Two kernels share no accumulator, so nothing is added atomically:
+//   fa_bwd_dq_kernel   one CTA per (128-query tile, query head); walks the visible keys in chunks of 64:
+//                      S = Q K_c^T and dP = dO V_c^T into TMEM (double-buffered), the row threads form dS (bf16,
+//                      K-major tile in shared memory), dQ += dS K_c accumulates in TMEM (K_c as an MN-major operand).
+//   fa_bwd_dkv_kernel  one CTA per (128-key tile, KV head); walks the query heads of the group and, for each, the
+//                      queries that see the tile in chunks of 64: S^T = K Q_c^T and dP^T = V dO_c^T into TMEM, the
+//                      row threads (one per key) form P^T and dS^T, dV += P^T dO_c and dK += dS^T Q_c accumulate in
+//                      TMEM over all chunks and all heads of the group (this is where grouped-query gradients are
+//                      summed), dO_c / Q_c as MN-major operands.
+// Probabilities are recomputed from the saved log-sum-exp: P = exp2(S * scale * log2e - lse * log2e).
+// =====================================================================================================================
+namespace trlb {
+
+constexpr int FB_C = 64;                                  // inner chunk (keys for dQ, queries for dK/dV)
+constexpr uint32_t FB_CHUNK_BYTES = FB_C * 128 * 2;       // [64 x 128] bf16 = two boxes of [64 rows x 64]
+constexpr uint32_t FB_CBOX_BYTES = FB_C * 64 * 2;
+constexpr uint32_t FB_T64_BYTES = 128 * 64 * 2;           // [128 x 64] bf16 K-major tile (dS, P^T, dS^T)
+constexpr size_t FA_DQ_SMEM = 2 * FA_TILE_BYTES + 2 * 2 * FB_CHUNK_BYTES + FB_T64_BYTES + 1024 + 512;
+constexpr size_t FA_DKV_SMEM = 2 * FA_TILE_BYTES + 2 * 2 * FB_CHUNK_BYTES + 2 * FB_T64_BYTES + 2 * 2 * FB_C * 4 + 1024 + 512;
+
+struct FaBwdParams {
+  const int* cu_q;
+  const int* cu_k;
+  int n_seq, Hq, Hk, causal, window;
+  float scale, scale_log2;
+  const float* lse;    // [Hq, Tq] natural log
+  const float* delta;  // [Hq, Tq]
+  int Tq, Tk;
+  __nv_bfloat16* dq;   // [Tq, Hq, 128]
+  __nv_bfloat16* dk;   // [Tk, Hk, 128]
+  __nv_bfloat16* dv;
+  long long dq_rs, dk_rs, dv_rs;
+  int* status;
+};
+
+// delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (t, h)
+__global__ void __launch_bounds__(256)
+fa_delta_kernel(const __nv_bfloat16* __restrict__ dout, long long do_rs, const __nv_bfloat16* __restrict__ out,
+                long long o_rs, float* __restrict__ delta, int Tq, int Hq) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < (long long)Tq * Hq; w += warps) {
+    const int t = (int)(w / Hq), h = (int)(w % Hq);
+    const uint2 a = *reinterpret_cast<const uint2*>(dout + (long long)t * do_rs + h * FA_D + lane * 4);
+    const uint2 b = *reinterpret_cast<const uint2*>(out + (long long)t * o_rs + h * FA_D + lane * 4);
+    const float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), b0 = unpack_bf16(b.x), b1 = unpack_bf16(b.y);
+    const float s = warp_sum(a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y);
+    if (lane == 0) delta[(long long)h * Tq + t] = s;
+  }
+}
+
+// byte offset of element (row r, column c < 64) in a [128 x 64] bf16 K-major 128-byte-swizzled tile
+__device__ __forceinline__ uint32_t fb_t64_off(int r, int c) {
+  return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + (((c >> 3) ^ (r & 7)) << 4) + (c & 7) * 2);
+}
+
+__global__ void __launch_bounds__(FA_THREADS, 1)
+fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                 const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                 const FaBwdParams p) {
+  int seq, tile;
+  if (!fa_find_tile(p.cu_q, p.n_seq, (int)blockIdx.x, seq, tile)) return;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = smem;
+  uint8_t* do_s = smem + FA_TILE_BYTES;
+  uint8_t* kv_s = smem + 2 * FA_TILE_BYTES;  // stage s: K chunk then V chunk
+  uint8_t* ds_s = kv_s + 2 * 2 * FB_CHUNK_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_s + FB_T64_BYTES);
+  uint64_t* qdo_full = bars;
+  uint64_t* kv_full = bars + 1;     // [2]
+  uint64_t* kv_empty = bars + 3;    // [2]
+  uint64_t* sp_full = bars + 5;     // [2]  S and dP of a chunk are complete
+  uint64_t* sp_empty = bars + 7;    // [2]
+  uint64_t* ds_full = bars + 9;
+  uint64_t* ds_empty = bars + 10;
+  uint64_t* dq_done = bars + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, kvh = h / (p.Hq / p.Hk);
+  const int q_beg = p.cu_q[seq], lq = p.cu_q[seq + 1] - q_beg;
+  const int k_beg = p.cu_k[seq], lk = p.cu_k[seq + 1] - k_beg;
+  int lo, hi;
+  fa_kv_range(tile, lq, lk, p.causal, p.window, lo, hi);
+  // the forward's range is in 128-key tiles; here chunks of 64
+  const int c_lo = lo * 2, c_hi = min(hi * 2 + 1, (lk - 1) / FB_C);
+  const int n_c = hi < lo ? 0 : c_hi - c_lo + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(qdo_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+      mbar_init(&sp_full[s], 1);
+      mbar_init(&sp_empty[s], 4);
+    }
+    mbar_init(ds_full, 128);
+    mbar_init(ds_empty, 1);
+    mbar_init(dq_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_do);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // TMEM columns: S0 [0,64) dP0 [64,128) S1 [128,192) dP1 [192,256) dQ [256,384)
+
+  if (n_c > 0) {
+    if (warp == 0) {
+      if (lane == 0) {
+        const int qrow = q_beg + tile * FA_BM;
+        mbar_expect_tx(qdo_full, 2 * FA_TILE_BYTES);
+        tma_load_2d(q_s, &tmap_q, qdo_full, h * FA_D, qrow);
+        tma_load_2d(q_s + FA_BOX_BYTES, &tmap_q, qdo_full, h * FA_D + 64, qrow);
+        tma_load_2d(do_s, &tmap_do, qdo_full, h * FA_D, qrow);
+        tma_load_2d(do_s + FA_BOX_BYTES, &tmap_do, qdo_full, h * FA_D + 64, qrow);
+        for (int j = 0; j < n_c; ++j) {
+          const int s = j & 1;
+          if (!mbar_wait(&kv_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, p.status, 1100 + s)) break;
+          uint8_t* ks = kv_s + (size_t)s * 2 * FB_CHUNK_BYTES;
+          uint8_t* vs = ks + FB_CHUNK_BYTES;
+          const int row = k_beg + (c_lo + j) * FB_C;
+          mbar_expect_tx(&kv_full[s], 2 * FB_CHUNK_BYTES);
+          tma_load_2d(ks, &tmap_k, &kv_full[s], kvh * FA_D, row);
+          tma_load_2d(ks + FB_CBOX_BYTES, &tmap_k, &kv_full[s], kvh * FA_D + 64, row);
+          tma_load_2d(vs, &tmap_v, &kv_full[s], kvh * FA_D, row);
+          tma_load_2d(vs + FB_CBOX_BYTES, &tmap_v, &kv_full[s], kvh * FA_D + 64, row);
+        }
+      }
+      __syncwarp();
+    } else if (warp == 1) {
+      if (lane == 0) {
+        constexpr uint32_t idesc_s = umma_idesc_bf16_major(FA_BM, FB_C, false, false);
+        constexpr uint32_t idesc_dq = umma_idesc_bf16_major(FA_BM, FA_D, false, true);  // K chunk as MN-major operand
+        const uint32_t q_u = smem_u32(q_s), do_u = smem_u32(do_s), kv_u = smem_u32(kv_s), ds_u = smem_u32(ds_s);
+        bool ok = mbar_wait(qdo_full, 0, abort_flag, p.status, 1110);
+        auto issue_sp = [&](int j) {
+          const int s = j & 1;
+          if (!mbar_wait(&kv_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1120 + s)) return false;
+          if (!mbar_wait(&sp_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, p.status, 1130 + s)) return false;
+          tc_fence_after();
+          const uint32_t k_u = kv_u + (uint32_t)s * 2 * FB_CHUNK_BYTES, v_u = k_u + FB_CHUNK_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < FA_D / 16; ++kk) {
+            const uint32_t qo = (uint32_t)(kk >> 2) * FA_BOX_BYTES, co = (uint32_t)(kk >> 2) * FB_CBOX_BYTES;
+            umma_bf16_ss(tmem_base + (uint32_t)s * 128, umma_desc_kmajor_sw128(q_u + qo) + 2 * (kk & 3),
+                         umma_desc_kmajor_sw128(k_u + co) + 2 * (kk & 3), idesc_s, kk != 0);
+          }
+#pragma unroll
+          for (int kk = 0; kk < FA_D / 16; ++kk) {
+            const uint32_t qo = (uint32_t)(kk >> 2) * FA_BOX_BYTES, co = (uint32_t)(kk >> 2) * FB_CBOX_BYTES;
+            umma_bf16_ss(tmem_base + (uint32_t)s * 128 + 64, umma_desc_kmajor_sw128(do_u + qo) + 2 * (kk & 3),
+                         umma_desc_kmajor_sw128(v_u + co) + 2 * (kk & 3), idesc_s, kk != 0);
+          }
+          umma_commit(&sp_full[s]);
+          return true;
+        };
+        if (ok) ok = issue_sp(0);
+        for (int j = 0; j < n_c && ok; ++j) {
+          const int s = j & 1;
+          if (j + 1 < n_c) ok = issue_sp(j + 1);
+          if (!ok) break;
+          if (!mbar_wait(ds_full, (uint32_t)(j & 1), abort_flag, p.status, 1140)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t k_u = kv_u + (uint32_t)s * 2 * FB_CHUNK_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < FB_C / 16; ++kk)
+            umma_bf16_ss(tmem_base + 256, umma_desc_kmajor_sw128(ds_u) + 2 * kk,
+                         umma_desc_mnmajor_sw128(k_u + (uint32_t)kk * 2048, FB_CBOX_BYTES), idesc_dq, (j | kk) != 0);
+          umma_commit(&kv_empty[s]);
+          umma_commit(ds_empty);
+        }
+        if (ok) umma_commit(dq_done);
+      }
+      __syncwarp();
+    } else {
+      const int quarter = warp & 3;
+      const int r = quarter * 32 + lane;
+      const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+      const int q_pos = tile * FA_BM + r;
+      const bool row_ok = q_pos < lq;
+      const int off = lk - lq;
+      const int k_max = p.causal ? min(lk - 1, q_pos + off) : lk - 1;
+      const int k_min = (p.causal && p.window > 0) ? max(0, q_pos + off - p.window + 1) : 0;
+      float lse2 = INFINITY, dl = 0.f;
+      if (row_ok) {
+        const float l = p.lse[(long long)h * p.Tq + q_beg + q_pos];
+        lse2 = l == -INFINITY ? INFINITY : l * 1.4426950408889634f;
+        dl = p.delta[(long long)h * p.Tq + q_beg + q_pos];
+      }
+      bool ok = true;
+      for (int j = 0; j < n_c && ok; ++j) {
+        const int s = j & 1;
+        const int key0 = (c_lo + j) * FB_C;
+        ok = __all_sync(0xffffffffu, mbar_wait(&sp_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1150 + s));
+        if (!ok) break;
+        tc_fence_after();
+        ok = __all_sync(0xffffffffu, mbar_wait(ds_empty, (uint32_t)((j & 1) ^ 1), abort_flag, p.status, 1160));
+        if (!ok) break;
+        const uint32_t ts = tmem_base + lane_off + (uint32_t)s * 128;
+#pragma unroll 1
+        for (int c = 0; c < FB_C; c += 32) {
+          float sv[32], dp[32];
+          tmem_ld_32x32(ts + c, sv);
+          tmem_ld_32x32(ts + 64 + c, dp);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+              float d2[2];
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                const int key = key0 + c + i + e + u;
+                const bool a = row_ok && key >= k_min && key <= k_max;
+                const float pr = a ? exp2f(sv[i + e + u] * p.scale_log2 - lse2) : 0.f;
+                d2[u] = pr * (dp[i + e + u] - dl) * p.scale;
+              }
+              w[e >> 1] = pack_bf16(d2[0], d2[1]);
+            }
+            *reinterpret_cast<uint4*>(ds_s + fb_t64_off(r, c + i)) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sp_empty[s]);
+        fence_proxy_async_smem();
+        mbar_arrive(ds_full);
+      }
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(dq_done, 0, abort_flag, p.status, 1170));
+      if (ok) {
+        tc_fence_after();
+        __nv_bfloat16* dst = p.dq + (long long)(q_beg + q_pos) * p.dq_rs + (long long)h * FA_D;
+#pragma unroll 1
+        for (int c = 0; c < FA_D; c += 32) {
+          float v[32];
+          tmem_ld_32x32(tmem_base + lane_off + 256 + c, v);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8)
+              *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(pack_bf16(v[i], v[i + 1]), pack_bf16(v[i + 2], v[i + 3]),
+                                                                  pack_bf16(v[i + 4], v[i + 5]), pack_bf16(v[i + 6], v[i + 7]));
+          }
+        }
+        tc_fence_before();
+      }
+    }
+  } else if (warp >= 2) {
+    const int r = (warp & 3) * 32 + lane;
+    const int q_pos = tile * FA_BM + r;
+    if (q_pos < lq) {
+      __nv_bfloat16* dst = p.dq + (long long)(q_beg + q_pos) * p.dq_rs + (long long)h * FA_D;
+      for (int i = 0; i < FA_D; i += 8) *reinterpret_cast<uint4*>(dst + i) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// Tile slot -> (sequence, key tile); same order as fa_find_tile, on the key segments.
+__device__ __forceinline__ bool fa_find_ktile(const int* cu_k, int n_seq, int slot, int& seq, int& tile) {
+  for (int s = 0; s < n_seq; ++s) {
+    const int nt = (cu_k[s + 1] - cu_k[s] + FA_BN - 1) / FA_BN;
+    if (slot < nt) { seq = s; tile = slot; return true; }
+    slot -= nt;
+  }
+  return false;
+}
+
+__global__ void __launch_bounds__(FA_THREADS, 1)
+fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                  const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                  const FaBwdParams p) {
+  int seq, tile;
+  if (!fa_find_ktile(p.cu_k, p.n_seq, (int)blockIdx.x, seq, tile)) return;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* k_s = smem;
+  uint8_t* v_s = smem + FA_TILE_BYTES;
+  uint8_t* qd_s = smem + 2 * FA_TILE_BYTES;      // stage s: Q chunk then dO chunk
+  uint8_t* pt_s = qd_s + 2 * 2 * FB_CHUNK_BYTES;  // P^T  [128 keys x 64 queries]
+  uint8_t* dst_s = pt_s + FB_T64_BYTES;           // dS^T
+  float* stat_s = reinterpret_cast<float*>(dst_s + FB_T64_BYTES);  // [2 stages][lse2 x 64, delta x 64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stat_s + 2 * 2 * FB_C);
+  uint64_t* kv_full = bars;
+  uint64_t* qd_full = bars + 1;    // [2]
+  uint64_t* qd_empty = bars + 3;   // [2]
+  uint64_t* sp_full = bars + 5;    // [2]
+  uint64_t* sp_empty = bars + 7;   // [2]
+  uint64_t* pd_full = bars + 9;
+  uint64_t* pd_empty = bars + 10;
+  uint64_t* acc_done = bars + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = blockIdx.y, G = p.Hq / p.Hk;
+  const int q_beg = p.cu_q[seq], lq = p.cu_q[seq + 1] - q_beg;
+  const int k_beg = p.cu_k[seq], lk = p.cu_k[seq + 1] - k_beg;
+  const int off = lk - lq;
+  const int key_first = tile * FA_BN, key_last = min(lk, key_first + FA_BN) - 1;
+  // queries that see at least one key of this tile: q + off >= key_first, and with a window q + off - window < key_last
+  int qc_lo = 0, qc_hi = (lq - 1) / FB_C;
+  if (p.causal) {
+    qc_lo = max(0, key_first - off) / FB_C;
+    if (p.window > 0) qc_hi = min(qc_hi, max(0, key_last + p.window - 1 - off) / FB_C);
+  }
+  const int per_head = (lq > 0 && qc_hi >= qc_lo) ? qc_hi - qc_lo + 1 : 0;
+  const int n_it = per_head * G;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&qd_full[s], 33);  // the TMA transaction + 32 lanes that stage lse / delta
+      mbar_init(&qd_empty[s], 1);
+      mbar_init(&sp_full[s], 1);
+      mbar_init(&sp_empty[s], 4);
+    }
+    mbar_init(pd_full, 128);
+    mbar_init(pd_empty, 1);
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_do);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // TMEM columns: S^T0 [0,64) dP^T0 [64,128) S^T1 [128,192) dP^T1 [192,256) dV [256,384) dK [384,512)
+
+  if (n_it > 0) {
+    if (warp == 0) {
+      if (lane == 0) {
+        const int krow = k_beg + tile * FA_BN;
+        mbar_expect_tx(kv_full, 2 * FA_TILE_BYTES);
+        tma_load_2d(k_s, &tmap_k, kv_full, kvh * FA_D, krow);
+        tma_load_2d(k_s + FA_BOX_BYTES, &tmap_k, kv_full, kvh * FA_D + 64, krow);
+        tma_load_2d(v_s, &tmap_v, kv_full, kvh * FA_D, krow);
+        tma_load_2d(v_s + FA_BOX_BYTES, &tmap_v, kv_full, kvh * FA_D + 64, krow);
+      }
+      bool ok = true;
+      for (int j = 0; j < n_it && ok; ++j) {
+        const int s = j & 1;
+        const int h = kvh * G + j / per_head, qc = qc_lo + j % per_head;
+        ok = __all_sync(0xffffffffu, mbar_wait(&qd_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, p.status, 1200 + s));
+        if (!ok) break;
+        float* st = stat_s + s * 2 * FB_C;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int qp = qc * FB_C + lane + 32 * u;
+          float l2 = INFINITY, dl = 0.f;  // a query beyond the segment gets probability 0 everywhere
+          if (qp < lq) {
+            const float l = p.lse[(long long)h * p.Tq + q_beg + qp];
+            l2 = l == -INFINITY ? INFINITY : l * 1.4426950408889634f;
+            dl = p.delta[(long long)h * p.Tq + q_beg + qp];
+          }
+          st[lane + 32 * u] = l2;
+          st[FB_C + lane + 32 * u] = dl;
+        }
+        if (lane == 0) {
+          uint8_t* qs = qd_s + (size_t)s * 2 * FB_CHUNK_BYTES;
+          uint8_t* ds = qs + FB_CHUNK_BYTES;
+          const int row = q_beg + qc * FB_C;
+          mbar_expect_tx(&qd_full[s], 2 * FB_CHUNK_BYTES);
+          tma_load_2d(qs, &tmap_q, &qd_full[s], h * FA_D, row);
+          tma_load_2d(qs + FB_CBOX_BYTES, &tmap_q, &qd_full[s], h * FA_D + 64, row);
+          tma_load_2d(ds, &tmap_do, &qd_full[s], h * FA_D, row);
+          tma_load_2d(ds + FB_CBOX_BYTES, &tmap_do, &qd_full[s], h * FA_D + 64, row);
+        }
+        mbar_arrive(&qd_full[s]);  // this lane's lse / delta are in shared memory (release)
+      }
+    } else if (warp == 1) {
+      if (lane == 0) {
+        constexpr uint32_t idesc_st = umma_idesc_bf16_major(FA_BN, FB_C, false, false);
+        constexpr uint32_t idesc_acc = umma_idesc_bf16_major(FA_BN, FA_D, false, true);  // dO / Q chunks MN-major
+        const uint32_t k_u = smem_u32(k_s), v_u = smem_u32(v_s), qd_u = smem_u32(qd_s);
+        const uint32_t pt_u = smem_u32(pt_s), dst_u = smem_u32(dst_s);
+        bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, 1210);
+        auto issue_sp = [&](int j) {
+          const int s = j & 1;
+          if (!mbar_wait(&qd_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1220 + s)) return false;
+          if (!mbar_wait(&sp_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, p.status, 1230 + s)) return false;
+          tc_fence_after();
+          const uint32_t q_u = qd_u + (uint32_t)s * 2 * FB_CHUNK_BYTES, do_u = q_u + FB_CHUNK_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < FA_D / 16; ++kk) {
+            const uint32_t to = (uint32_t)(kk >> 2) * FA_BOX_BYTES, co = (uint32_t)(kk >> 2) * FB_CBOX_BYTES;
+            umma_bf16_ss(tmem_base + (uint32_t)s * 128, umma_desc_kmajor_sw128(k_u + to) + 2 * (kk & 3),
+                         umma_desc_kmajor_sw128(q_u + co) + 2 * (kk & 3), idesc_st, kk != 0);
+          }
+#pragma unroll
+          for (int kk = 0; kk < FA_D / 16; ++kk) {
+            const uint32_t to = (uint32_t)(kk >> 2) * FA_BOX_BYTES, co = (uint32_t)(kk >> 2) * FB_CBOX_BYTES;
+            umma_bf16_ss(tmem_base + (uint32_t)s * 128 + 64, umma_desc_kmajor_sw128(v_u + to) + 2 * (kk & 3),
+                         umma_desc_kmajor_sw128(do_u + co) + 2 * (kk & 3), idesc_st, kk != 0);
+          }
+          umma_commit(&sp_full[s]);
+          return true;
+        };
+        if (ok) ok = issue_sp(0);
+        for (int j = 0; j < n_it && ok; ++j) {
+          const int s = j & 1;
+          if (j + 1 < n_it) ok = issue_sp(j + 1);
+          if (!ok) break;
+          if (!mbar_wait(pd_full, (uint32_t)(j & 1), abort_flag, p.status, 1240)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t q_u = qd_u + (uint32_t)s * 2 * FB_CHUNK_BYTES, do_u = q_u + FB_CHUNK_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < FB_C / 16; ++kk)
+            umma_bf16_ss(tmem_base + 256, umma_desc_kmajor_sw128(pt_u) + 2 * kk,
+                         umma_desc_mnmajor_sw128(do_u + (uint32_t)kk * 2048, FB_CBOX_BYTES), idesc_acc, (j | kk) != 0);
+#pragma unroll
+          for (int kk = 0; kk < FB_C / 16; ++kk)
+            umma_bf16_ss(tmem_base + 384, umma_desc_kmajor_sw128(dst_u) + 2 * kk,
+                         umma_desc_mnmajor_sw128(q_u + (uint32_t)kk * 2048, FB_CBOX_BYTES), idesc_acc, (j | kk) != 0);
+          umma_commit(&qd_empty[s]);
+          umma_commit(pd_empty);
+        }
+        if (ok) umma_commit(acc_done);
+      }
+      __syncwarp();
+    } else {
+      const int quarter = warp & 3;
+      const int r = quarter * 32 + lane;
+      const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+      const int key = key_first + r;  // position inside the key segment
+      const bool key_ok = key < lk;
+      bool ok = true;
+      for (int j = 0; j < n_it && ok; ++j) {
+        const int s = j & 1;
+        const int q0 = (qc_lo + j % per_head) * FB_C;
+        ok = __all_sync(0xffffffffu, mbar_wait(&sp_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1250 + s));
+        if (!ok) break;
+        tc_fence_after();
+        ok = __all_sync(0xffffffffu, mbar_wait(pd_empty, (uint32_t)((j & 1) ^ 1), abort_flag, p.status, 1260));
+        if (!ok) break;
+        const float* st = stat_s + s * 2 * FB_C;  // visible: sp_full follows the MMA that waited on qd_full
+        const uint32_t ts = tmem_base + lane_off + (uint32_t)s * 128;
+#pragma unroll 1
+        for (int c = 0; c < FB_C; c += 32) {
+          float sv[32], dp[32];
+          tmem_ld_32x32(ts + c, sv);
+          tmem_ld_32x32(ts + 64 + c, dp);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint32_t wp[4], wd[4];
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+              float pp[2], dd[2];
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                const int qi = c + i + e + u, qp = q0 + qi;
+                bool a = key_ok;
+                if (p.causal) {
+                  a = a && key <= qp + off;
+                  if (p.window > 0) a = a && key > qp + off - p.window;
+                }
+                const float pr = a ? exp2f(sv[i + e + u] * p.scale_log2 - st[qi]) : 0.f;
+                pp[u] = pr;
+                dd[u] = pr * (dp[i + e + u] - st[FB_C + qi]) * p.scale;
+              }
+              wp[e >> 1] = pack_bf16(pp[0], pp[1]);
+              wd[e >> 1] = pack_bf16(dd[0], dd[1]);
+            }
+            *reinterpret_cast<uint4*>(pt_s + fb_t64_off(r, c + i)) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
+            *reinterpret_cast<uint4*>(dst_s + fb_t64_off(r, c + i)) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sp_empty[s]);
+        fence_proxy_async_smem();
+        mbar_arrive(pd_full);
+      }
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_done, 0, abort_flag, p.status, 1270));
+      if (ok) {
+        tc_fence_after();
+        __nv_bfloat16* dv = p.dv + (long long)(k_beg + key) * p.dv_rs + (long long)kvh * FA_D;
+        __nv_bfloat16* dk = p.dk + (long long)(k_beg + key) * p.dk_rs + (long long)kvh * FA_D;
+#pragma unroll 1
+        for (int c = 0; c < FA_D; c += 32) {
+          float a[32], b[32];
+          tmem_ld_32x32(tmem_base + lane_off + 256 + c, a);
+          tmem_ld_32x32(tmem_base + lane_off + 384 + c, b);
+          tmem_ld_wait();
+          if (key_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              *reinterpret_cast<uint4*>(dv + c + i) = make_uint4(pack_bf16(a[i], a[i + 1]), pack_bf16(a[i + 2], a[i + 3]),
+                                                                 pack_bf16(a[i + 4], a[i + 5]), pack_bf16(a[i + 6], a[i + 7]));
+              *reinterpret_cast<uint4*>(dk + c + i) = make_uint4(pack_bf16(b[i], b[i + 1]), pack_bf16(b[i + 2], b[i + 3]),
+                                                                 pack_bf16(b[i + 4], b[i + 5]), pack_bf16(b[i + 6], b[i + 7]));
+            }
+          }
+        }
+        tc_fence_before();
+      }
+    }
+  } else if (warp >= 2) {
+    const int r = (warp & 3) * 32 + lane;
+    const int key = key_first + r;
+    if (key < lk) {
+      __nv_bfloat16* dv = p.dv + (long long)(k_beg + key) * p.dv_rs + (long long)kvh * FA_D;
+      __nv_bfloat16* dk = p.dk + (long long)(k_beg + key) * p.dk_rs + (long long)kvh * FA_D;
+      for (int i = 0; i < FA_D; i += 8) {
+        *reinterpret_cast<uint4*>(dv + i) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(dk + i) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace trlb
+
+// Backward of trlb_fa_varlen_fwd.  dout / out [Tq, Hq, 128], lse [Hq, Tq] from the forward; delta [Hq, Tq] fp32 is
+// scratch (written here).  dq [Tq, Hq, 128], dk / dv [Tk, Hk, 128] bf16 with their own row strides.
+TRLB_API int trlb_fa_varlen_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                long long q_rs, long long k_rs, long long v_rs, long long o_rs, long long do_rs,
+                                const int* cu_q, const int* cu_k, int n_seq, int Tq, int Tk, int Hq, int Hk, int D,
+                                float scale, int causal, int window, const float* lse, float* delta, void* dq, void* dk,
+                                void* dv, long long dq_rs, long long dk_rs, long long dv_rs, int* status, cudaStream_t st) {
+  if (Tq <= 0 || n_seq <= 0) return 0;
+  if (D != FA_D || Hk <= 0 || Hq % Hk != 0 || (q_rs % 8) || (k_rs % 8) || (v_rs % 8) || (o_rs % 8) || (do_rs % 8) ||
+      (dq_rs % 8) || (dk_rs % 8) || (dv_rs % 8))
+    return -170;
+  {
+    const long long warps = (long long)Tq * Hq;
+    const int grid = (int)((warps + 7) / 8 < 148 * 8 ? (warps + 7) / 8 : 148 * 8);
+    fa_delta_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)dout, do_rs, (const __nv_bfloat16*)out, o_rs, delta, Tq, Hq);
+  }
+  CUtensorMap tq128, tdo128, tk64, tv64, tq64, tdo64, tk128, tv128;
+  using trlb_host::make_tmap_2d_bf16;
+  if (make_tmap_2d_bf16(&tq128, q, (uint64_t)Tq, (uint64_t)Hq * D, (uint64_t)q_rs, 128, 64)) return -171;
+  if (make_tmap_2d_bf16(&tdo128, dout, (uint64_t)Tq, (uint64_t)Hq * D, (uint64_t)do_rs, 128, 64)) return -172;
+  if (make_tmap_2d_bf16(&tk64, k, (uint64_t)Tk, (uint64_t)Hk * D, (uint64_t)k_rs, 64, 64)) return -173;
+  if (make_tmap_2d_bf16(&tv64, v, (uint64_t)Tk, (uint64_t)Hk * D, (uint64_t)v_rs, 64, 64)) return -174;
+  if (make_tmap_2d_bf16(&tq64, q, (uint64_t)Tq, (uint64_t)Hq * D, (uint64_t)q_rs, 64, 64)) return -175;
+  if (make_tmap_2d_bf16(&tdo64, dout, (uint64_t)Tq, (uint64_t)Hq * D, (uint64_t)do_rs, 64, 64)) return -176;
+  if (make_tmap_2d_bf16(&tk128, k, (uint64_t)Tk, (uint64_t)Hk * D, (uint64_t)k_rs, 128, 64)) return -177;
+  if (make_tmap_2d_bf16(&tv128, v, (uint64_t)Tk, (uint64_t)Hk * D, (uint64_t)v_rs, 128, 64)) return -178;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(fa_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FA_DQ_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(fa_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FA_DKV_SMEM) != cudaSuccess)
+      return -179;
+    attr_set = true;
+  }
+  FaBwdParams p = {};
+  p.cu_q = cu_q; p.cu_k = cu_k; p.n_seq = n_seq; p.Hq = Hq; p.Hk = Hk; p.causal = causal; p.window = window;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse = lse; p.delta = delta; p.Tq = Tq; p.Tk = Tk;
+  p.dq = (__nv_bfloat16*)dq; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
+  p.dq_rs = dq_rs; p.dk_rs = dk_rs; p.dv_rs = dv_rs; p.status = status;
+  const int q_tiles = (Tq + FA_BM - 1) / FA_BM + n_seq, k_tiles = (Tk + FA_BN - 1) / FA_BN + n_seq;
+  fa_bwd_dkv_kernel<<<dim3(k_tiles, Hk), FA_THREADS, FA_DKV_SMEM, st>>>(tq64, tdo64, tk128, tv128, p);
+  fa_bwd_dq_kernel<<<dim3(q_tiles, Hq), FA_THREADS, FA_DQ_SMEM, st>>>(tq128, tdo128, tk64, tv64, p);
+  return (int)cudaGetLastError();
+}

@@ -301,8 +301,80 @@ def sumsq(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
 # -------------------------------------------------------------------------------------------
 # attention
 # -------------------------------------------------------------------------------------------
+def fa_varlen_fwd(q, k, v, cu_q, cu_k, causal=True, window=None, scale=None):
+    """Forward of the tcgen05 varlen attention.  q [Tq, Hq, 128], k / v [Tk, Hk, 128] bf16 (any row stride; the last
+    two dimensions dense), cu_q / cu_k int32 device tensors.  Returns (out [Tq, Hq, 128] bf16, lse [Hq, Tq] fp32)."""
+    Tq, Hq, Dh = q.shape
+    Tk, Hk, _ = k.shape
+    for t in (q, k, v):
+        assert t.dtype == torch.bfloat16 and t.stride(2) == 1 and t.stride(1) == Dh
+    out = torch.empty(Tq, Hq, Dh, dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty(Hq, Tq, dtype=torch.float32, device=q.device)
+    sc = float(scale) if scale is not None else 1.0 / Dh ** 0.5
+    _chk(lib().trlb_fa_varlen_fwd(_p(q), _p(k), _p(v), c_longlong(q.stride(0)), c_longlong(k.stride(0)),
+                                  c_longlong(v.stride(0)), _p(cu_q), _p(cu_k), c_int(cu_q.numel() - 1), c_int(Tq), c_int(Tk),
+                                  c_int(Hq), c_int(Hk), c_int(Dh), c_float(sc), c_int(int(bool(causal))),
+                                  c_int(int(window or 0)), _p(out), c_longlong(out.stride(0)), _p(lse),
+                                  _p(status_buffer(q.device)), _s()), "fa_varlen_fwd")
+    return out, lse
+
+
+def fa_varlen_bwd(q, k, v, out, dout, lse, cu_q, cu_k, causal=True, window=None, scale=None):
+    """Backward of :func:`fa_varlen_fwd`: returns (dq, dk, dv) bf16, shaped like q / k / v (contiguous)."""
+    Tq, Hq, Dh = q.shape
+    Tk, Hk, _ = k.shape
+    dout = dout if (dout.stride(2) == 1 and dout.stride(1) == Dh) else dout.contiguous()
+    dq = torch.empty(Tq, Hq, Dh, dtype=torch.bfloat16, device=q.device)
+    dk = torch.empty(Tk, Hk, Dh, dtype=torch.bfloat16, device=q.device)
+    dv = torch.empty(Tk, Hk, Dh, dtype=torch.bfloat16, device=q.device)
+    delta = torch.empty(Hq, Tq, dtype=torch.float32, device=q.device)
+    sc = float(scale) if scale is not None else 1.0 / Dh ** 0.5
+    _chk(lib().trlb_fa_varlen_bwd(_p(q), _p(k), _p(v), _p(out), _p(dout), c_longlong(q.stride(0)), c_longlong(k.stride(0)),
+                                  c_longlong(v.stride(0)), c_longlong(out.stride(0)), c_longlong(dout.stride(0)), _p(cu_q),
+                                  _p(cu_k), c_int(cu_q.numel() - 1), c_int(Tq), c_int(Tk), c_int(Hq), c_int(Hk), c_int(Dh),
+                                  c_float(sc), c_int(int(bool(causal))), c_int(int(window or 0)), _p(lse), _p(delta), _p(dq),
+                                  _p(dk), _p(dv), c_longlong(dq.stride(0)), c_longlong(dk.stride(0)), c_longlong(dv.stride(0)),
+                                  _p(status_buffer(q.device)), _s()), "fa_varlen_bwd")
+    LAUNCHES[0] += 2  # delta + two gradient kernels behind one entry point
+    return dq, dk, dv
+
+
+class _FaVarlenFn(torch.autograd.Function):
+    """Varlen attention on the tcgen05 kernels (csrc/fa_varlen_tcgen05.cu): grouped-query heads are indexed, never
+    expanded; the backward recomputes the probabilities from the saved log-sum-exp."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_q, cu_k, causal, window):
+        out, lse = fa_varlen_fwd(q, k, v, cu_q, cu_k, causal, window)
+        ctx.save_for_backward(q, k, v, out, lse, cu_q, cu_k)
+        ctx.causal, ctx.window = causal, window
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse, cu_q, cu_k = ctx.saved_tensors
+        dq, dk, dv = fa_varlen_bwd(q, k, v, out, dout, lse, cu_q, cu_k, ctx.causal, ctx.window)
+        return dq, dk, dv, None, None, None, None
+
+
+def _fa_ok(q, k, v) -> bool:
+    def dense_heads(t):
+        return t.stride(2) == 1 and t.stride(1) == t.shape[2] and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
+
+    return (q.dtype == torch.bfloat16 and q.shape[2] == 128 and k.shape[2] == 128 and q.shape[1] % k.shape[1] == 0
+            and all(dense_heads(t) for t in (q, k, v)))
+
+
+def _i32(cu, device):
+    return cu if (cu.dtype == torch.int32 and cu.device == device) else cu.to(device=device, dtype=torch.int32)
+
+
 def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True, window=None):
-    """Causal GQA attention over packed documents [T, H, D]; ``window`` = sliding-window size or None."""
+    """Causal GQA attention over packed documents [T, H, D]; ``window`` = sliding-window size or None.  head_dim 128
+    in bf16 runs on this library's tcgen05 kernels (forward and backward); other shapes use the library kernel."""
+    if _fa_ok(q, k, v) and (causal or not window):
+        cu = _i32(cu_seqlens, q.device)
+        return _FaVarlenFn.apply(q, k, v, cu, cu, bool(causal), int(window) if window else None)
     from torch.nn.attention.varlen import varlen_attn
 
     cu = cu_seqlens.to(torch.int32)
@@ -317,8 +389,10 @@ def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True, window=None):
 
 
 def attention_varlen_qk(q, k, v, cu_q, cu_k, max_q, max_k):
-    """Causal GQA attention with separate query / key segments [Tq, H, D] x [Tk, Hk, D]; the library kernel aligns the
-    causal mask to the end of each key segment (query i sees keys up to i + len_k - len_q)."""
+    """Causal GQA attention with separate query / key segments [Tq, H, D] x [Tk, Hk, D]; the causal mask is aligned to
+    the end of each key segment (query i sees keys up to i + len_k - len_q)."""
+    if _fa_ok(q, k, v):
+        return _FaVarlenFn.apply(q, k, v, _i32(cu_q, q.device), _i32(cu_k, q.device), True, None)
     from torch.nn.attention.varlen import varlen_attn
 
     Hq, Hk = q.shape[1], k.shape[1]
@@ -734,13 +808,18 @@ def norm_allreduce(arena, byte_offset, my_sumsq, max_norm, norm_out, clip_out, s
          "norm_allreduce")
 
 
-def adamw_bcast(arena, byte_offset, lo, n, master, grad, m, v, step, lr, b1, b2, eps, wd, clip, sync, use_multimem=False):
-    """AdamW on the shard; refreshed bf16 parameters are stored into every rank's replica at [lo, lo+n)."""
+def adamw_bcast(arena, byte_offset, lo, n, master, grad, m, v, step, lr, b1, b2, eps, wd, clip, sync, use_multimem=False,
+                no_decay_ranges=()):
+    """AdamW on the shard; refreshed bf16 parameters are stored into every rank's replica at [lo, lo+n).
+    ``no_decay_ranges``: up to 16 ``(lo, hi)`` element ranges of the bucket (biases, norm weights) exempt from decay."""
     mc = arena.mc(byte_offset) if use_multimem else None
+    flat = [int(x) for r in no_decay_ranges for x in r]
+    nd = (c_longlong * max(1, len(flat)))(*flat) if flat else None
     _chk(lib().trlb_adamw_bcast(arena.peers(byte_offset), arena.pads(), c_int(arena.rank), c_int(arena.world), mc,
                                 c_longlong(lo), c_longlong(n), _p(master), _p(grad), _p(m), _p(v), c_int(step), c_float(lr),
                                 c_float(b1), c_float(b2), c_float(eps), c_float(wd), _p(clip), sync.epoch_ptr, sync.gate_ptr,
-                                c_int(sync.channel), _p(status_buffer(master.device)), _s()), "adamw_bcast")
+                                c_int(sync.channel), _p(status_buffer(master.device)), nd, c_int(len(flat) // 2), _s()),
+         "adamw_bcast")
 
 
 def shard_allgather(arena, byte_offset, per, sync, use_multimem=False):

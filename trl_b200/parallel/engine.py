@@ -62,6 +62,20 @@ class Bucket:
         return t[self.lo:self.hi]
 
 
+def _merge_ranges(ranges, limit: int = 16):
+    """Adjacent exempt ranges (a layer's norm weights and biases often touch) merged; the fused kernel takes up to
+    ``limit``."""
+    out = []
+    for lo, hi in sorted(ranges):
+        if out and lo <= out[-1][1]:
+            out[-1] = (out[-1][0], max(out[-1][1], hi))
+        else:
+            out.append((lo, hi))
+    if len(out) > limit:
+        raise ValueError(f"{len(out)} separate no-decay ranges in one bucket; the fused optimizer kernel takes {limit}")
+    return out
+
+
 def default_bucket_of(name: str) -> str:
     parts = name.split(".")
     if parts[0] == "layers":
@@ -89,7 +103,7 @@ class TrainEngine:
             import os
 
             use_symm_kernels = (self.sharded and on_gpu and first.dtype == torch.bfloat16 and symmetric_available()
-                                and weight_decay == 0.0 and os.environ.get("TRL_B200_NCCL_OPTIMIZER", "0") != "1")
+                                and os.environ.get("TRL_B200_NCCL_OPTIMIZER", "0") != "1")
         self.use_symm = bool(use_symm_kernels)
         self.use_multimem = False
         self._arenas = {}
@@ -276,8 +290,51 @@ class TrainEngine:
             key = (b.name, str(b.params[0].dtype))
             K.adamw_bcast(pa, self._offsets[("param",) + key], b.lo, b.hi - b.lo, b.master, red, b.exp_avg, b.exp_avg_sq,
                           self.step_count, lr, b1, b2, self.eps, self.weight_decay, self._clip, self._sync,
-                          use_multimem=self.use_multimem)
+                          use_multimem=self.use_multimem,
+                          no_decay_ranges=_merge_ranges(b.no_decay_ranges) if self.weight_decay else ())
         return self._norm[0].clone()
+
+    @torch.no_grad()
+    def comm_selfcheck(self) -> str:
+        """Checks the fused collectives against the library ones on live buffers; returns "ok" or what differed.
+
+        (1) the gradient reduce-scatter kernel (peer loads, or multimem.ld_reduce) of the first bucket against an
+        NCCL all-reduce of the same rank-dependent values; (2) after the last optimizer step every rank's bf16
+        parameter replica must be the same (the AdamW kernel stores its shard into all replicas): compared through
+        min / max reductions of per-bucket checksums.  Gradients are zeroed afterwards; call it between steps."""
+        if not self.use_symm:
+            return "skipped: fused collectives not in use"
+        from ..ops import cuda as K
+
+        b = self.buckets[0]
+        key = (b.name, str(b.params[0].dtype))
+        n = b.flat_grad.numel()
+        idx = torch.arange(n, device=b.flat_grad.device, dtype=torch.float32)
+        b.flat_grad.copy_((torch.sin(idx * 0.37 + self.rank) * (1.0 + 0.1 * self.rank)).to(b.flat_grad.dtype))
+        want = b.flat_grad.float().clone()
+        torch.cuda.synchronize()
+        td.barrier(group=self.group)
+        td.all_reduce(want, group=self.group)
+        want = want[b.lo:b.hi] / self.world
+        got = torch.empty(b.hi - b.lo, dtype=torch.float32, device=want.device)
+        self._sumsq.zero_()
+        K.rs_reduce(self._arenas["grad"], self._offsets[("grad",) + key], b.flat_grad.dtype == torch.bfloat16, b.lo,
+                    b.hi - b.lo, got, self._sumsq, self._sync, use_multimem=self.use_multimem)
+        torch.cuda.synchronize()
+        err = (got - want).abs().max()
+        sums = torch.stack([bk.flat_param.float().sum() for bk in self.buckets])
+        hi_, lo_ = sums.clone(), sums.clone()
+        td.all_reduce(hi_, op=td.ReduceOp.MAX, group=self.group)
+        td.all_reduce(lo_, op=td.ReduceOp.MIN, group=self.group)
+        bad = torch.stack([err > 1e-5, (hi_ != lo_).any()]).float()
+        td.all_reduce(bad, op=td.ReduceOp.MAX, group=self.group)
+        td.barrier(group=self.group)
+        self.zero_grad()
+        if bad[0] > 0:
+            return f"reduce-scatter differs from the library all-reduce (max abs error {float(err):.3e} on this rank)"
+        if bad[1] > 0:
+            return "parameter replicas differ between ranks after the fused AdamW"
+        return "ok"
 
     def _masked_adamw(self, b: Bucket, g, lr, gs, shadow):
         b1, b2 = self.betas

@@ -37,6 +37,9 @@ class _OnlineConfig(_BaseConfig):
     max_completion_length: Optional[int] = 512
     ds3_gather_for_generation: bool = True
     shuffle_dataset: Optional[bool] = True
+    # after scoring, deal the job's completions to the ranks by length so that every rank trains on equal work
+    # (token ids are exchanged; no counterpart in the reference's synchronous trainer)
+    balance_completions: bool = True
     pad_to_multiple_of: Optional[int] = None
     generation_batch_size: Optional[int] = None
     steps_per_generation: Optional[int] = None

@@ -20,7 +20,7 @@ from ..data_utils import is_conversational
 from ..parallel import dist as D
 from .grpo_config import GRPOConfig
 from .online_base import OnlineTrainer
-from .utils import defer_mean, defer_ratio, nanmax, nanmin, nanstd, pad
+from .utils import balanced_partition, defer_mean, defer_ratio, nanmax, nanmin, nanstd, pad
 
 
 class GRPOTrainer(OnlineTrainer):
@@ -76,10 +76,36 @@ class GRPOTrainer(OnlineTrainer):
         tool_mask = extras.pop("env_mask", extras.pop("tool_mask", None))
         B = len(prompts)
         comp_lens = torch.tensor([len(c) for c in completion_ids], device=dev)
-        Tc = max(1, int(comp_lens.max()))
-        completion_mask = (torch.arange(Tc, device=dev)[None] < comp_lens[:, None]).int()
         eos_or_pad = {self.eos_token_id, self.pad_token_id}
         is_trunc = torch.tensor([len(c) == 0 or c[-1] not in eos_or_pad for c in completion_ids], device=dev)
+        # ---- rewards and advantages (on the completions this rank generated) -----------------------------------------
+        tok = self.processing_class
+        completions_text = tok.batch_decode(completion_ids, skip_special_tokens=True)
+        if prompts and is_conversational(inputs[0]):
+            completions = [[{"role": "assistant", "content": c}] for c in completions_text]
+        else:
+            completions = completions_text
+        for k, v in extras.items():
+            if isinstance(v, list) and len(v) == B:
+                for ex, val in zip(inputs, v):
+                    ex[k] = val
+        rewards_per_func = self._calculate_rewards(inputs, prompts, completions, completion_ids)
+        ng = self.num_generations if mode == "train" else self.num_generations_eval
+        advantages, rewards, std_rewards, is_std_zero = self._advantages(rewards_per_func, ng)
+        sl = slice(D.rank() * B, (D.rank() + 1) * B)
+        all_adv = advantages.clone()
+        advantages = advantages[sl]
+        self._last_group_std = std_rewards[sl] if std_rewards.ndim and std_rewards.shape[0] == all_adv.shape[0] else None
+        gen_comp_lens, gen_is_trunc, gen_prompt_ids = comp_lens, is_trunc, prompt_ids  # for the metrics below
+        # ---- even out the training work: completions change ranks, token ids travel, activations never do ------------
+        if (mode == "train" and D.world_size() > 1 and getattr(a, "balance_completions", True) and pixel_list is None):
+            (prompt_ids, completion_ids, sampling_logps, tool_mask, advantages, self._last_group_std) = \
+                self._rebalance_across_ranks(prompt_ids, completion_ids, sampling_logps, tool_mask, advantages,
+                                             self._last_group_std)
+            comp_lens = torch.tensor([len(c) for c in completion_ids], device=dev)
+            is_trunc = torch.tensor([len(c) == 0 or c[-1] not in eos_or_pad for c in completion_ids], device=dev)
+        Tc = max(1, int(comp_lens.max()))
+        completion_mask = (torch.arange(Tc, device=dev)[None] < comp_lens[:, None]).int()
         if self.mask_truncated_completions:
             completion_mask = completion_mask * (~is_trunc)[:, None].int()
         if tool_mask is not None:
@@ -110,37 +136,19 @@ class GRPOTrainer(OnlineTrainer):
                     out["ref_per_token_logps"] = self._ref_logps(prompt_ids, completion_ids, bs, pixel_list)
             if old_logps is not None:
                 out["old_per_token_logps"] = old_logps
-        # ---- rewards and advantages -------------------------------------------------------------------------------
-        tok = self.processing_class
-        completions_text = tok.batch_decode(completion_ids, skip_special_tokens=True)
-        if prompts and is_conversational(inputs[0]):
-            completions = [[{"role": "assistant", "content": c}] for c in completions_text]
-        else:
-            completions = completions_text
-        for k, v in extras.items():
-            if isinstance(v, list) and len(v) == B:
-                for ex, val in zip(inputs, v):
-                    ex[k] = val
-        rewards_per_func = self._calculate_rewards(inputs, prompts, completions, completion_ids)
-        ng = self.num_generations if mode == "train" else self.num_generations_eval
-        advantages, rewards, std_rewards, is_std_zero = self._advantages(rewards_per_func, ng)
-        sl = slice(D.rank() * B, (D.rank() + 1) * B)
-        all_adv = advantages.clone()
-        advantages = advantages[sl]
-        self._last_group_std = std_rewards[sl] if std_rewards.ndim and std_rewards.shape[0] == all_adv.shape[0] else None
         # ---- metrics ----------------------------------------------------------------------------------------------
         m = self._metrics[mode]
         if mode == "train":
-            self._total_train_tokens += int(D.gather((torch.tensor([len(p) for p in prompt_ids], device=dev).sum()
-                                                      + comp_lens.sum()).reshape(1)).sum())
+            self._total_train_tokens += int(D.gather((torch.tensor([len(p) for p in gen_prompt_ids], device=dev).sum()
+                                                      + gen_comp_lens.sum()).reshape(1)).sum())
         m["num_tokens"].append(float(self._total_train_tokens))
-        agg_len = D.gather(comp_lens.float())
+        agg_len = D.gather(gen_comp_lens.float())
         if mode == "train":  # completion tokens produced by the whole job (each completion counted once)
             self._total_generated_tokens = getattr(self, "_total_generated_tokens", 0) + int(agg_len.sum())
         m["completions/mean_length"].append(agg_len.mean())
         m["completions/min_length"].append(agg_len.min())
         m["completions/max_length"].append(agg_len.max())
-        agg_trunc = D.gather(is_trunc.float())
+        agg_trunc = D.gather(gen_is_trunc.float())
         term = agg_len[agg_trunc == 0]
         m["completions/clipped_ratio"].append(agg_trunc.mean())
         if term.numel() == 0:
@@ -188,6 +196,36 @@ class GRPOTrainer(OnlineTrainer):
         if tm is not None:
             out["tool_mask"] = tm
         return out
+
+    def _rebalance_across_ranks(self, prompt_ids, completion_ids, sampling_logps, tool_mask, advantages, group_std):
+        """Deals the job's completions to the ranks so that every rank trains on the same amount of work.
+
+        Completion lengths differ a lot (an EOS can come at any step), and every rank trains on what it generated, so
+        the rank with the longest completions sets the step time of all.  After scoring (advantages are final: a
+        completion no longer needs its group), all ranks exchange the token ids and per-sample scalars, run the same
+        deterministic partition and keep their share: equal counts per rank, costs ``L + L^2 / s`` (linear layers +
+        attention) balanced by longest-first assignment to the least loaded rank.  Only token ids travel; log-probs
+        and activations are computed after the exchange, on the owner.  The reference balances ``sum L^2`` the same
+        way for its asynchronous trainer (trl/experimental/async_grpo/async_grpo_trainer.py:303-406).
+        """
+        B, W, r = len(prompt_ids), D.world_size(), D.rank()
+        adv = advantages.tolist()
+        std = group_std.tolist() if group_std is not None else [None] * B
+        recs = D.gather_object([(prompt_ids[i], completion_ids[i], None if sampling_logps is None else sampling_logps[i],
+                                 None if tool_mask is None else tool_mask[i], adv[i], std[i]) for i in range(B)])
+        cfg = getattr(self.model, "config", None)
+        try:  # sequence length at which attention costs as much as the linear layers
+            s = float(cfg.num_parameters()) / (2.0 * cfg.hidden_size * cfg.num_hidden_layers)
+        except Exception:
+            s = 32768.0
+        lens = [len(x[0]) + len(x[1]) for x in recs]
+        mine = balanced_partition([l + l * l / s for l in lens], W, B)[r]
+        pick = [recs[i] for i in mine]
+        dev = advantages.device
+        new_adv = torch.tensor([x[4] for x in pick], dtype=advantages.dtype, device=dev)
+        new_std = None if group_std is None else torch.tensor([x[5] for x in pick], dtype=group_std.dtype, device=dev)
+        return ([x[0] for x in pick], [x[1] for x in pick], None if sampling_logps is None else [x[2] for x in pick],
+                None if tool_mask is None else [x[3] for x in pick], new_adv, new_std)
 
     def _advantages(self, rewards_per_func, ng):
         dev = rewards_per_func.device

@@ -147,6 +147,21 @@ def nanmax(t: torch.Tensor) -> torch.Tensor:
     return v.max() if v.numel() else t.new_tensor(float("nan"))
 
 
+def balanced_partition(costs: Sequence[float], parts: int, per_part: int) -> list[list[int]]:
+    """Indices of ``costs`` dealt into ``parts`` lists of exactly ``per_part`` entries with near-equal cost sums:
+    longest first, each to the least loaded part that still has room (ties: lowest part, then lowest index), so every
+    rank that runs it on the same costs gets the same answer.  Each list comes back in ascending index order."""
+    if len(costs) != parts * per_part:
+        raise ValueError(f"{len(costs)} items cannot fill {parts} parts of {per_part}")
+    order = sorted(range(len(costs)), key=lambda i: (-costs[i], i))
+    load, out = [0.0] * parts, [[] for _ in range(parts)]
+    for i in order:
+        p = min((q for q in range(parts) if len(out[q]) < per_part), key=lambda q: (load[q], q))
+        out[p].append(i)
+        load[p] += costs[i]
+    return [sorted(x) for x in out]
+
+
 class DeferredMetric:
     """A metric value whose cross-rank reduction waits for the next ``log`` call.
 
