@@ -50,3 +50,24 @@ def test_grouped_gemm_and_moe_forward_backward(E, I, H, T, k):
     for got_g, ref_t in zip(grads, (h32, g32, d32, w32)):
         denom = ref_t.grad.abs().max().item() + 1e-6
         assert (got_g - ref_t.grad).abs().max().item() / denom < 0.08
+
+
+@pytest.mark.parametrize("N,E,K,masked,dtype", [(1000, 128, 8, False, torch.float32), (77, 8, 2, True, torch.float32),
+                                                (5000, 60, 4, True, torch.bfloat16), (3, 512, 8, False, torch.float32)])
+def test_moe_aux_loss_kernel_matches_oracle_and_its_gradient(N, E, K, masked, dtype):
+    from trl_b200.ops import functional as ops
+    from trl_b200.oracle import ops as ref
+
+    torch.manual_seed(0)
+    logits = torch.randn(N, E, device="cuda")
+    probs = torch.softmax(logits, -1).to(dtype).requires_grad_()
+    idx = probs.detach().float().topk(K, -1).indices
+    mask = (torch.rand(N, device="cuda") > 0.3).float() if masked else None
+    for _ in range(2):  # the scratch accumulator must come back zeroed
+        loss = ops.load_balancing_loss(probs, idx, E, K, mask)
+        (g,) = torch.autograd.grad(loss, probs)
+        p2 = probs.detach().float().requires_grad_()
+        want = ref.load_balancing_loss(p2, idx, E, K, mask)
+        (g2,) = torch.autograd.grad(want, p2)
+        assert abs(float(loss) - float(want)) < 2e-3 * max(1.0, abs(float(want))), (float(loss), float(want))
+        assert (g.float() - g2).abs().max().item() < 2e-3 * max(1e-3, g2.abs().max().item()) + 1e-6

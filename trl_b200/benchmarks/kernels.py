@@ -83,9 +83,19 @@ def main():
         ms = timeit(lambda: K.gemm_bf16_tn(A, B, out=C), a.iters, a.warmup)
         fl = 2.0 * a.m * a.n * a.k
         out.update(shape=[a.m, a.n, a.k], ms=ms, tflops=fl / ms / 1e9, frac_of_cublas_peak=fl / ms / 1e9 / tfl)
+        # the two gradient products of the same linear layer: dX = dY W (W read MN-major), dW = dY^T x (both MN-major)
+        dY = torch.randn(a.m, a.n, device=dev, dtype=torch.bfloat16)
+        dX = torch.empty(a.m, a.k, device=dev, dtype=torch.bfloat16)
+        dW = torch.empty(a.n, a.k, device=dev, dtype=torch.bfloat16)
+        ms_dx = timeit(lambda: K.gemm_bf16(dY, B, b_mn=True, out=dX), a.iters, a.warmup)
+        ms_dw = timeit(lambda: K.gemm_bf16(dY, A, a_mn=True, b_mn=True, out=dW), a.iters, a.warmup)
+        out.update(dgrad_ms=ms_dx, dgrad_tflops=fl / ms_dx / 1e9, wgrad_ms=ms_dw, wgrad_tflops=fl / ms_dw / 1e9)
         if a.baseline:
             ms2 = timeit(lambda: torch.matmul(A, B.t(), out=C), a.iters, a.warmup)
-            out.update(cublas_ms=ms2, cublas_tflops=fl / ms2 / 1e9)
+            ms3 = timeit(lambda: torch.matmul(dY, B, out=dX), a.iters, a.warmup)
+            ms4 = timeit(lambda: torch.matmul(dY.t(), A, out=dW), a.iters, a.warmup)
+            out.update(cublas_ms=ms2, cublas_tflops=fl / ms2 / 1e9, cublas_dgrad_ms=ms3, cublas_wgrad_ms=ms4,
+                       fwd_vs_cublas=ms2 / ms, dgrad_vs_cublas=ms3 / ms_dx, wgrad_vs_cublas=ms4 / ms_dw)
     elif a.kernel in ("lmhead", "lmhead_bwd"):
         H = torch.randn(a.m, a.k, device=dev, dtype=torch.bfloat16)
         W = (torch.randn(a.v, a.k, device=dev) * 0.02).to(torch.bfloat16)

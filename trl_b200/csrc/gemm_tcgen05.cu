@@ -29,6 +29,9 @@ enum { EPI_STORE = 0, EPI_LSE = 1, EPI_DZ = 2 };
 
 struct GemmParams {
   int M, N, K;
+  // operand layouts: 0 = K-major (row-major [rows, K]: y = x W^T), 1 = MN-major (row-major [K, rows]: the operand
+  // is given transposed, as dY and X are for the weight gradient and W is for the input gradient)
+  int a_mn, b_mn;
   int m_tiles, n_tiles, k_blocks;
   int n_splits, tiles_per_split;  // work item = (m_tile, split); a split covers tiles_per_split N tiles
   // EPI_STORE
@@ -319,8 +322,20 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             uint8_t* sa = tiles + stage * STAGE_BYTES;
             uint8_t* sb = sa + A_BYTES;
             mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
-            tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m_tile * BM);
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, nta * BN);
+            if (p.a_mn) {  // [64 k-rows x 64] boxes, one per 64 rows of the tile
+#pragma unroll
+              for (int b = 0; b < BM / 64; ++b)
+                tma_load_2d(sa + b * 8192, &tmap_a, &full_bar[stage], m_tile * BM + b * 64, kb * BK);
+            } else {
+              tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m_tile * BM);
+            }
+            if (p.b_mn) {
+#pragma unroll
+              for (int b = 0; b < BN / 64; ++b)
+                tma_load_2d(sb + b * 8192, &tmap_b, &full_bar[stage], nta * BN + b * 64, kb * BK);
+            } else {
+              tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, nta * BN);
+            }
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
         }
@@ -330,7 +345,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      const uint32_t idesc = umma_idesc_bf16_major(BM, BN, p.a_mn != 0, p.b_mn != 0);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -347,13 +362,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 300 + stage)) { ok = false; break; }
             tc_fence_after();
             const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
-            const uint64_t adesc = umma_desc_kmajor_sw128(sa);
-            const uint64_t bdesc = umma_desc_kmajor_sw128(sa + A_BYTES);
+            // K-major: a K step of 16 bf16 is 32 bytes inside the swizzle atom (2 address units);
+            // MN-major: 16 k-rows of 128 bytes (2048 bytes = 128 address units), 64-element groups 8 KB apart
+            const uint64_t adesc = p.a_mn ? umma_desc_mnmajor_sw128(sa, 8192) : umma_desc_kmajor_sw128(sa);
+            const uint64_t bdesc = p.b_mn ? umma_desc_mnmajor_sw128(sa + A_BYTES, 8192) : umma_desc_kmajor_sw128(sa + A_BYTES);
+            const uint32_t astep = p.a_mn ? 128u : 2u, bstep = p.b_mn ? 128u : 2u;
 #pragma unroll
-            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-              // advancing K by 16 bf16 = 32 bytes = 2 descriptor address units inside the swizzle atom
-              umma_bf16_ss(tacc, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) != 0);
-            }
+            for (int kk = 0; kk < BK / UMMA_K; ++kk)
+              umma_bf16_ss(tacc, adesc + astep * kk, bdesc + bstep * kk, idesc, (kb | kk) != 0);
             umma_commit(&empty_bar[stage]);  // smem stage reusable once these MMAs retire
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
@@ -572,11 +588,16 @@ using namespace trlb;
 template <int EPI>
 static int launch_gemm(const void* A, const void* B, GemmParams p, long long lda, long long ldb, cudaStream_t stream) {
   if (p.M <= 0 || p.N <= 0 || p.K <= 0) return 0;
-  if ((p.K % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0) return -100;  // 16-byte TMA stride rule
+  if ((lda % 8) != 0 || (ldb % 8) != 0) return -100;  // 16-byte TMA stride rule
+  if ((!p.a_mn || !p.b_mn) && (p.K % 8) != 0) return -100;
   CUtensorMap ta, tb;
-  int r = trlb_host::make_tmap_2d_bf16(&ta, A, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)lda, BM, BK);
+  // a K-major operand is a [rows, K] matrix read in [tile rows x 64] boxes; an MN-major one is a [K, rows] matrix read
+  // in [64 x 64] boxes (64 k-rows of 64 contiguous operand rows)
+  int r = p.a_mn ? trlb_host::make_tmap_2d_bf16(&ta, A, (uint64_t)p.K, (uint64_t)p.M, (uint64_t)lda, BK, 64)
+                 : trlb_host::make_tmap_2d_bf16(&ta, A, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)lda, BM, BK);
   if (r) return -101;
-  r = trlb_host::make_tmap_2d_bf16(&tb, B, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)ldb, BN, BK);
+  r = p.b_mn ? trlb_host::make_tmap_2d_bf16(&tb, B, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)ldb, BK, 64)
+             : trlb_host::make_tmap_2d_bf16(&tb, B, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)ldb, BN, BK);
   if (r) return -102;
   p.m_tiles = (p.M + BM - 1) / BM;
   p.n_tiles = (p.N + BN - 1) / BN;
@@ -613,6 +634,22 @@ TRLB_API int trlb_gemm_bf16_tn(const void* A, const void* B, void* C, const void
                                long long lda, long long ldb, long long ldc, int* status, cudaStream_t stream) {
   GemmParams p = {};
   p.M = M; p.N = N; p.K = K;
+  p.C = (__nv_bfloat16*)C; p.ldc = ldc; p.bias = (const __nv_bfloat16*)bias;
+  p.status = status;
+  return launch_gemm<EPI_STORE>(A, B, p, lda, ldb, stream);
+}
+
+// General form: C[M,N] (bf16) = op(A) . op(B)^T (+ bias[N]) with each operand either K-major ([rows, K] row-major,
+// a_mn / b_mn = 0) or MN-major ([K, rows] row-major, = 1).  With x [T, K], W [N, K], dY [T, N]:
+//   forward   Y  = x W^T      A = x  (K-major),  B = W  (K-major)
+//   dgrad     dX = dY W       A = dY (K-major),  B = W  (MN-major: [N = contraction, K = output columns])
+//   wgrad     dW = dY^T x     A = dY (MN-major: [T = contraction, N = output rows]),  B = x (MN-major)
+// No operand is ever transposed in memory.  MN-major operands need their row count (M or N) to be a multiple of 8.
+TRLB_API int trlb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
+                            long long ldb, long long ldc, int a_mn, int b_mn, int* status, cudaStream_t stream) {
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K; p.a_mn = a_mn ? 1 : 0; p.b_mn = b_mn ? 1 : 0;
+  if ((p.a_mn && (M % 8)) || (p.b_mn && (N % 8))) return -100;
   p.C = (__nv_bfloat16*)C; p.ldc = ldc; p.bias = (const __nv_bfloat16*)bias;
   p.status = status;
   return launch_gemm<EPI_STORE>(A, B, p, lda, ldb, stream);

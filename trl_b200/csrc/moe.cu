@@ -81,3 +81,121 @@ TRLB_API int trlb_moe_combine(const void* y, const int* inv, const float* w, voi
   moe_combine_kernel<<<T, threads, 0, st>>>((const __nv_bfloat16*)y, inv, w, (__nv_bfloat16*)out, T, k, H);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------------------
+// Router load-balancing loss  E * sum_e f_e * P_e  in one pass (the reference computes it from one-hot tensors of
+// shape [tokens, k, experts], transformers' load_balancing_loss_func reached through trl/trainer/sft_trainer.py:357-378):
+// f_e = routed choices to expert e / valid tokens, P_e = mean router probability of expert e over valid tokens.
+// Every block reduces its slice of tokens into shared memory (probability columns in registers, counts with
+// shared-memory atomics), adds the slice to a small global accumulator, and the last block to arrive forms the loss,
+// writes f (needed by the backward: dL/dP[n, e] = E * f_e * mask_n / valid) and leaves the accumulator zeroed.
+// ------------------------------------------------------------------------------------------------
+namespace trlb {
+
+constexpr int AUX_THREADS = 256;
+constexpr int AUX_MAX_E = 1024;
+
+template <typename PT>
+__global__ void __launch_bounds__(AUX_THREADS)
+moe_aux_loss_kernel(const PT* __restrict__ probs, const long long* __restrict__ idx, const float* __restrict__ mask,
+                    int N, int E, int K, int rows_per_block, float* __restrict__ acc /* [2E + 2] */,
+                    float* __restrict__ loss, float* __restrict__ f_out /* [E] */, float* __restrict__ valid_out) {
+  __shared__ float ps[AUX_MAX_E], cnt[AUX_MAX_E];
+  __shared__ float msum_s;
+  __shared__ unsigned ticket_s;
+  const int t = threadIdx.x;
+  for (int e = t; e < E; e += AUX_THREADS) { ps[e] = 0.f; cnt[e] = 0.f; }
+  if (t == 0) msum_s = 0.f;
+  __syncthreads();
+  const int r0 = blockIdx.x * rows_per_block, r1 = min(N, r0 + rows_per_block);
+  // probability columns: thread (row group, column) walks its rows; up to 4 columns per thread
+  const int cols = E < AUX_THREADS ? E : AUX_THREADS, rgroups = AUX_THREADS / cols;
+  const int my_col = t % cols, my_rg = t / cols;
+  float part[4] = {0.f, 0.f, 0.f, 0.f};
+  if (my_rg < rgroups) {
+    for (int r = r0 + my_rg; r < r1; r += rgroups) {
+      const float m = mask ? mask[r] : 1.f;
+      if (m == 0.f) continue;
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const int e = my_col + s * cols;
+        if (e < E) part[s] += m * (float)probs[(size_t)r * E + e];
+      }
+    }
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const int e = my_col + s * cols;
+      if (e < E && part[s] != 0.f) atomicAdd(&ps[e], part[s]);
+    }
+  }
+  // routed choices
+  float ml = 0.f;
+  for (int i = r0 * K + t; i < r1 * K; i += AUX_THREADS) {
+    const int r = i / K;
+    const float m = mask ? mask[r] : 1.f;
+    const long long e = idx[i];
+    if (m != 0.f && e >= 0 && e < E) atomicAdd(&cnt[(int)e], m);
+  }
+  for (int r = r0 + t; r < r1; r += AUX_THREADS) ml += mask ? mask[r] : 1.f;
+  ml = warp_sum(ml);
+  if ((t & 31) == 0 && ml != 0.f) atomicAdd(&msum_s, ml);
+  __syncthreads();
+  for (int e = t; e < E; e += AUX_THREADS) {
+    if (ps[e] != 0.f) atomicAdd(&acc[e], ps[e]);
+    if (cnt[e] != 0.f) atomicAdd(&acc[E + e], cnt[e]);
+  }
+  if (t == 0 && msum_s != 0.f) atomicAdd(&acc[2 * E], msum_s);
+  __threadfence();
+  __syncthreads();
+  if (t == 0) ticket_s = atomicAdd(reinterpret_cast<unsigned*>(&acc[2 * E + 1]), 1u);
+  __syncthreads();
+  if (ticket_s != gridDim.x - 1) return;
+  // last block: everything has been added
+  __threadfence();
+  const float valid = fmaxf(__ldcg(&acc[2 * E]), 1.f);
+  float l = 0.f;
+  for (int e = t; e < E; e += AUX_THREADS) {
+    const float p = __ldcg(&acc[e]) / valid, f = __ldcg(&acc[E + e]) / valid;
+    f_out[e] = f;
+    l += f * p;
+    acc[e] = 0.f;
+    acc[E + e] = 0.f;
+  }
+  l = warp_sum(l);
+  __syncthreads();
+  if (t == 0) msum_s = 0.f;
+  __syncthreads();
+  if ((t & 31) == 0) atomicAdd(&msum_s, l);
+  __syncthreads();
+  if (t == 0) {
+    *loss = msum_s * (float)E;
+    *valid_out = valid;
+    acc[2 * E] = 0.f;
+    *reinterpret_cast<unsigned*>(&acc[2 * E + 1]) = 0u;
+  }
+}
+
+}  // namespace trlb
+
+// probs [N, E] (fp32 or bf16), idx [N, K] int64, mask [N] fp32 or null.  acc: 2E + 2 zero-initialised floats of scratch
+// (left zeroed).  Outputs: loss (scalar), f_out [E] (routed fraction per expert), valid_out (number of valid tokens).
+TRLB_API int trlb_moe_aux_loss(const void* probs, int probs_bf16, const long long* idx, const float* mask, int N, int E,
+                               int K, float* acc, float* loss, float* f_out, float* valid_out, cudaStream_t st) {
+  if (E <= 0 || E > trlb::AUX_MAX_E || K <= 0) return -1;
+  if (N <= 0) {
+    cudaMemsetAsync(loss, 0, sizeof(float), st);
+    return (int)cudaGetLastError();
+  }
+  int blocks = (N + 63) / 64;
+  const int cap = 2 * trlb_host::sm_count();
+  if (blocks > cap) blocks = cap;
+  const int rows_per_block = (N + blocks - 1) / blocks;
+  blocks = (N + rows_per_block - 1) / rows_per_block;
+  if (probs_bf16)
+    trlb::moe_aux_loss_kernel<__nv_bfloat16><<<blocks, trlb::AUX_THREADS, 0, st>>>(
+        (const __nv_bfloat16*)probs, idx, mask, N, E, K, rows_per_block, acc, loss, f_out, valid_out);
+  else
+    trlb::moe_aux_loss_kernel<float><<<blocks, trlb::AUX_THREADS, 0, st>>>((const float*)probs, idx, mask, N, E, K,
+                                                                           rows_per_block, acc, loss, f_out, valid_out);
+  return (int)cudaGetLastError();
+}

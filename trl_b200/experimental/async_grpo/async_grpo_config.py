@@ -36,6 +36,10 @@ class AsyncGRPOConfig(_BaseConfig):
     log_completions: bool = False
     num_completions_to_print: Optional[int] = None
     scale_rewards: bool = True
+    # "thread": rollouts on a background thread of the training process; "process": a spawned child with its own event
+    # loop that talks to the generation server (reward functions must be picklable); "auto": process when a server is
+    # configured and training runs on a GPU, else thread
+    rollout_worker: str = "auto"
 
     def __post_init__(self):
         super().__post_init__()

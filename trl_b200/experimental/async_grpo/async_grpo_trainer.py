@@ -20,7 +20,26 @@ from ...ops import functional as ops
 from ...parallel import dist as D
 from ...trainer.utils import create_model_from_path
 from .async_grpo_config import AsyncGRPOConfig
-from .async_rollout_worker import AsyncRolloutWorker, RolloutSample
+from .async_rollout_worker import AsyncRolloutWorker, ProcessRolloutWorker, RolloutSample
+
+
+class _ServerSideReward:
+    """Picklable reward call for the spawned rollout process: decodes completions with the tokenizer it carries and
+    sums the (picklable) reward functions, exactly like ``AsyncGRPOTrainer._reward``."""
+
+    def __init__(self, reward_funcs, tokenizer):
+        self.reward_funcs, self.tok = list(reward_funcs), tokenizer
+
+    def __call__(self, examples, prompt_ids, completion_ids):
+        texts = self.tok.batch_decode(completion_ids, skip_special_tokens=True)
+        total = [0.0] * len(texts)
+        keys = [k for k in examples[0] if k not in ("prompt", "prompt_text", "completion")]
+        kw = {k: [ex[k] for ex in examples] for k in keys}
+        for rf in self.reward_funcs:
+            vals = rf(prompts=[ex.get("prompt_text", ex["prompt"]) for ex in examples], completions=texts,
+                      completion_ids=completion_ids, **kw)
+            total = [t + (float(v) if v is not None else 0.0) for t, v in zip(total, vals)]
+        return total
 
 
 class TokenBudgetBatcher:
@@ -128,7 +147,31 @@ class AsyncGRPOTrainer(Trainer):
         import threading
 
         self._model_lock = threading.RLock()
-        if D.rank() == 0:
+        a = self.args
+        mode = getattr(a, "rollout_worker", "auto")
+        use_process = mode == "process" or (mode == "auto" and a.vllm_server_base_url and self._generate_fn is None
+                                            and a.device.type == "cuda")
+        if D.rank() == 0 and use_process:
+            # a spawned child keeps the generation server busy and scores its answers; the trainer only pushes weights
+            from .vllm_client import VLLMClient
+
+            if not a.vllm_server_base_url:
+                raise ValueError("rollout_worker='process' needs vllm_server_base_url (the child talks to a generation server)")
+            self._client = VLLMClient(base_url=a.vllm_server_base_url, connection_timeout=a.vllm_server_timeout)
+            rows = []
+            for i in range(len(self._prompt_rows)):
+                row = dict(self._prompt_rows[i])
+                row["prompt_text"] = row["prompt"]
+                row["prompt"] = self._tokenize([row["prompt"]])[0]
+                rows.append(row)
+            inflight = a.max_inflight_tasks if a.max_inflight_tasks and a.max_inflight_tasks > 0 else 4
+            self.worker = ProcessRolloutWorker(rows, a.vllm_server_base_url, _ServerSideReward(self.reward_funcs, self.processing_class),
+                                               a.num_generations, max_tokens=a.max_completion_length,
+                                               queue_maxsize=a.queue_maxsize, scale_rewards=a.scale_rewards, seed=a.seed,
+                                               temperature=a.temperature, max_inflight=inflight,
+                                               server_timeout=a.vllm_server_timeout)
+            self.worker.start()
+        elif D.rank() == 0:
             fn = self._generate_fn or self._default_generate_fn()
             self.worker = AsyncRolloutWorker(self._prompt_rows, fn, self._reward, self.args.num_generations,
                                              self.args.queue_maxsize, self.args.scale_rewards, self.args.seed)

@@ -1,10 +1,18 @@
 """Asynchronous rollout worker (trl/experimental/async_grpo/async_rollout_worker.py: RolloutSample :188-230,
 _AsyncRolloutLoop :276-760, AsyncRolloutWorker :914-1053).
 
-A background thread keeps sampling groups of completions (through a generation server, or in-process on its own CUDA
-stream next to training), scores them, turns group rewards into advantages and pushes ``RolloutSample`` objects,
-tagged with the weight version they were sampled under, into a bounded queue.  The trainer drops samples that are
-more than ``max_staleness`` versions old.  A heartbeat lets the trainer notice a dead worker."""
+Two workers with one interface (``start / get / update_model_version / check_health / stop``):
+
+* :class:`AsyncRolloutWorker`: a background thread next to training (in-process engine on its own CUDA stream, or any
+  ``generate_fn``);
+* :class:`ProcessRolloutWorker`: a spawned child process, like the reference's: an asyncio loop keeps several
+  ``/generate`` requests to the generation server in flight, a second task scores finished groups (reward functions
+  must be picklable), turns group rewards into advantages and puts ``RolloutSample`` objects on a
+  ``multiprocessing.Queue``.  The weight version travels through a shared integer, the heartbeat through a shared
+  double, a failure through an error queue; the parent notices a dead, silent or failed child in ``check_health``.
+
+Samples are tagged with the weight version they were sampled under; the trainer drops samples that are more than
+``max_staleness`` versions old."""
 from __future__ import annotations
 
 import queue
@@ -105,3 +113,150 @@ class AsyncRolloutWorker:
         self._stop.set()
         if self._thread is not None:
             self._thread.join(timeout=10)
+
+
+# ---- child-process worker ---------------------------------------------------------------------------------------------
+def _advantages(rewards: list, ng: int, scale: bool) -> list:
+    r = torch.tensor(rewards, dtype=torch.float32).view(-1, ng)
+    a = r - r.mean(1, keepdim=True)
+    if scale:
+        a = a / (r.std(1, keepdim=True) + 1e-4)
+    return a.flatten().tolist()
+
+
+def _process_main(cfg: dict, rows: list, reward_fn, out_q, version, heartbeat, stop, err_q):
+    """Entry point of the spawned rollout process."""
+    import asyncio
+    import traceback
+
+    async def run():
+        from .vllm_client import AsyncGenerationClient
+
+        client = AsyncGenerationClient(cfg["server_url"], request_timeout=cfg.get("request_timeout", 600.0))
+        await client.wait_healthy(cfg.get("server_timeout", 60.0))
+        g = torch.Generator().manual_seed(cfg.get("seed", 0))
+        ng, ppc = cfg["num_generations"], cfg.get("prompts_per_call", 4)
+        done_groups = asyncio.Queue(maxsize=cfg.get("max_inflight", 4) * 2)
+        state = {"groups": 0}
+
+        async def generate_loop():
+            sem = asyncio.Semaphore(cfg.get("max_inflight", 4))
+
+            async def one(examples, v):
+                try:
+                    res = await client.generate([ex["prompt"] for ex in examples], n=ng, max_tokens=cfg["max_tokens"],
+                                                temperature=cfg.get("temperature", 1.0),
+                                                generation_kwargs=cfg.get("generation_kwargs") or {})
+                    await done_groups.put((examples, v, res))
+                finally:
+                    sem.release()
+
+            tasks = set()
+            while not stop.is_set():
+                await sem.acquire()
+                idx = torch.randint(0, len(rows), (ppc,), generator=g).tolist()
+                t = asyncio.ensure_future(one([rows[i] for i in idx], version.value))
+                tasks.add(t)
+                t.add_done_callback(lambda f: (tasks.discard(f), f.exception() and err_q.put(repr(f.exception()))))
+                heartbeat.value = time.monotonic()
+            for t in tasks:
+                t.cancel()
+
+        async def score_loop():
+            loop = asyncio.get_running_loop()
+            while not stop.is_set():
+                try:
+                    examples, v, res = await asyncio.wait_for(done_groups.get(), timeout=0.2)
+                except asyncio.TimeoutError:
+                    continue
+                prompts = [p for p in res["prompt_ids"] for _ in range(ng)]
+                comps = res["completion_ids"]
+                lps = [[x[0] for x in seq] for seq in res["logprobs"]]
+                rep = [ex for ex in examples for _ in range(ng)]
+                rewards = await loop.run_in_executor(None, reward_fn, rep, prompts, comps)
+                adv = _advantages(list(rewards), ng, cfg.get("scale_rewards", True))
+                for j, (p, c, lp) in enumerate(zip(prompts, comps, lps)):
+                    smp = RolloutSample(list(p), list(c), list(lp), float(rewards[j]), float(adv[j]), int(v),
+                                        state["groups"] + j // ng)
+                    while not stop.is_set():
+                        try:
+                            out_q.put(smp, timeout=0.2)
+                            break
+                        except queue.Full:
+                            heartbeat.value = time.monotonic()
+                state["groups"] += len(examples)
+                heartbeat.value = time.monotonic()
+
+        try:
+            await asyncio.gather(generate_loop(), score_loop())
+        finally:
+            await client.close()
+
+    try:
+        asyncio.run(run())
+    except BaseException as e:  # noqa: BLE001  (reported to the parent)
+        err_q.put("".join(traceback.format_exception_only(type(e), e)).strip())
+
+
+class ProcessRolloutWorker:
+    """Rollout generation and scoring in a spawned child process that talks to a generation server
+    (trl/experimental/async_grpo/async_rollout_worker.py:914-1053).  ``reward_fn(examples, prompt_ids, completion_ids)``
+    and the dataset rows must be picklable."""
+
+    def __init__(self, dataset, server_url: str, reward_fn: Callable, num_generations: int, max_tokens: int = 64,
+                 queue_maxsize: int = 1024, scale_rewards: bool = True, seed: int = 0, temperature: float = 1.0,
+                 prompts_per_call: int = 4, max_inflight: int = 4, server_timeout: float = 60.0, generation_kwargs=None):
+        import multiprocessing as mp
+
+        self._ctx = mp.get_context("spawn")
+        self.rows = [dict(dataset[i]) for i in range(len(dataset))]
+        self.reward_fn = reward_fn
+        self.cfg = dict(server_url=server_url, num_generations=num_generations, max_tokens=max_tokens,
+                        scale_rewards=scale_rewards, seed=seed, temperature=temperature, prompts_per_call=prompts_per_call,
+                        max_inflight=max_inflight, server_timeout=server_timeout, generation_kwargs=generation_kwargs or {})
+        self.queue = self._ctx.Queue(maxsize=queue_maxsize)
+        self._version = self._ctx.Value("i", 0)
+        self._heartbeat = self._ctx.Value("d", time.monotonic())
+        self._stop = self._ctx.Event()
+        self._errors = self._ctx.Queue()
+        self._proc = None
+        self._failure: Optional[str] = None
+
+    @property
+    def model_version(self) -> int:
+        return self._version.value
+
+    def update_model_version(self, v: int) -> None:
+        self._version.value = int(v)
+
+    def start(self) -> None:
+        if self._proc is None:
+            self._heartbeat.value = time.monotonic()
+            self._proc = self._ctx.Process(target=_process_main, name="trl-b200-rollout", daemon=True,
+                                           args=(self.cfg, self.rows, self.reward_fn, self.queue, self._version,
+                                                 self._heartbeat, self._stop, self._errors))
+            self._proc.start()
+
+    def check_health(self, stale_after_s: float) -> None:
+        try:
+            while True:
+                self._failure = self._errors.get_nowait()
+        except queue.Empty:
+            pass
+        if self._failure is not None:
+            raise RuntimeError(f"rollout worker failed: {self._failure}")
+        if self._proc is not None and not self._proc.is_alive() and not self._stop.is_set():
+            raise RuntimeError(f"rollout worker exited (exit code {self._proc.exitcode})")
+        if time.monotonic() - self._heartbeat.value > stale_after_s:
+            raise RuntimeError(f"rollout worker produced nothing for {stale_after_s:.0f} s")
+
+    def get(self, timeout: float) -> RolloutSample:
+        return self.queue.get(timeout=timeout)
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self._proc is not None:
+            self._proc.join(timeout=10)
+            if self._proc.is_alive():
+                self._proc.terminate()  # this exact child
+                self._proc.join(timeout=5)

@@ -70,7 +70,12 @@ class RolloutClient:
         return out
 
     def init_communicator(self, device=0):
-        return self._post("init_communicator", {"device": str(device)})
+        """Asks the server which weight transports it takes (``ipc``: CUDA IPC, device to device on one box;
+        ``packed``: one binary body for many tensors; ``named``: one tensor per request) and remembers them."""
+        info = self._post("init_communicator", {"device": str(device)})
+        self.transports = info.get("transports", ["named"])
+        self.server_device = info.get("device", "cpu")
+        return info
 
     def update_named_param(self, name: str, weights):
         import torch
@@ -82,10 +87,90 @@ class RolloutClient:
         return self._post("update_named_param", dict(name=name, dtype=str(weights.dtype), shape=list(weights.shape),
                                                      data=base64.b64encode(buf.getvalue()).decode()))
 
-    def update_model_params(self, model):
+    def update_packed(self, named: list, chunk_bytes: int = 256 << 20) -> int:
+        """Pushes ``[(name, tensor)]`` in binary bodies of at most ``chunk_bytes``: no base64, no JSON around the
+        payload, one request per chunk instead of one per tensor."""
+        import json
+
+        import torch
+
+        from ..scripts.rollout_serve import pack_tensors
+
+        sent, group, size = 0, [], 0
+
+        def flush():
+            nonlocal group, size, sent
+            if not group:
+                return
+            meta, parts = pack_tensors(group)
+            blob = bytearray(meta["total"])
+            for m, part in zip(meta["tensors"], parts):
+                blob[m["offset"]:m["offset"] + m["nbytes"]] = part.cpu().numpy().tobytes()
+            head = json.dumps(meta).encode()
+            r = self.session.post(f"{self.base_url}/update_packed/", data=len(head).to_bytes(8, "little") + head + bytes(blob),
+                                  headers={"Content-Type": "application/octet-stream"})
+            if r.status_code != 200:
+                raise Exception(f"Request failed: {r.status_code}, {r.text}")
+            sent += len(group)
+            group, size = [], 0
+
+        for name, t in named:
+            nb = t.numel() * t.element_size()
+            if group and size + nb > chunk_bytes:
+                flush()
+            group.append((name, t))
+            size += nb
+        flush()
+        return sent
+
+    def update_ipc(self, named: list) -> int:
+        """Device-to-device push on one box: the tensors are packed into one CUDA buffer whose IPC handle travels in
+        the request (plain fields); the server opens it and copies into its parameters without touching host memory.
+        The buffer is kept until the server has answered."""
+        import torch
+        from torch.multiprocessing.reductions import reduce_tensor
+
+        from ..scripts.rollout_serve import pack_tensors
+
+        meta, parts = pack_tensors(named)
+        dev = parts[0].device
+        flat = torch.empty(meta["total"], dtype=torch.uint8, device=dev)
+        for m, part in zip(meta["tensors"], parts):
+            flat[m["offset"]:m["offset"] + m["nbytes"]].copy_(part)
+        torch.cuda.synchronize(dev)
+        _, args = reduce_tensor(flat)
+        (_, _, _, _, _, _, device, handle, storage_size, storage_offset, _, ref_handle, ref_offset, event_handle,
+         event_sync) = args
+        b64 = lambda b: base64.b64encode(bytes(b)).decode()  # noqa: E731
+        ipc = {"nbytes": meta["total"], "device": int(device), "handle": b64(handle), "storage_size_bytes": int(storage_size),
+               "storage_offset_bytes": int(storage_offset), "ref_counter_handle": b64(ref_handle),
+               "ref_counter_offset": int(ref_offset), "event_handle": b64(event_handle), "event_sync_required": bool(event_sync)}
+        self._post("update_ipc", {"meta": meta, "ipc": ipc})
+        del flat
+        return len(named)
+
+    def update_model_params(self, model, transport: str | None = None) -> int:
+        """Pushes every parameter (HF names).  ``transport``: ``"ipc"`` | ``"packed"`` | ``"named"``; by default the
+        fastest one the server and the tensors allow (CUDA tensors + a CUDA server on this box -> IPC)."""
         sd = model.state_dict_hf() if hasattr(model, "state_dict_hf") else dict(model.named_parameters())
-        for name, p in sd.items():
+        named = [(k, v.detach()) for k, v in sd.items()]
+        if transport is None:
+            if not hasattr(self, "transports"):
+                try:
+                    self.init_communicator()
+                except Exception:  # noqa: BLE001  (an older server: one tensor per request)
+                    self.transports = ["named"]
+            local = self.base_url.split("//")[-1].split(":")[0] in ("127.0.0.1", "localhost")
+            cuda = bool(named) and named[0][1].is_cuda
+            transport = "ipc" if ("ipc" in self.transports and cuda and local) else (
+                "packed" if "packed" in self.transports else "named")
+        if transport == "ipc":
+            return self.update_ipc(named)
+        if transport == "packed":
+            return self.update_packed(named)
+        for name, p in named:
             self.update_named_param(name, p)
+        return len(named)
 
     def reset_prefix_cache(self):
         return self._post("reset_prefix_cache", {})

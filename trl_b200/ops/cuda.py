@@ -78,6 +78,56 @@ def gemm_bf16_tn(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = N
     return out
 
 
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias=None, *, a_mn: bool = False, b_mn: bool = False, out=None):
+    """``out[M, N] = op(a) @ op(b)^T (+ bias)`` on the tcgen05 kernel with either operand given transposed:
+    ``a`` is ``[M, K]`` (``a_mn=False``) or ``[K, M]`` (``a_mn=True``), ``b`` is ``[N, K]`` or ``[K, N]``.  The
+    transposed forms are read as MN-major tensor-core operands straight from their TMA tiles: nothing is transposed
+    in memory.  This is what makes ``dX = dY @ W`` and ``dW = dY^T @ x`` run on the same kernel as ``y = x @ W^T``."""
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.is_cuda and a.stride(-1) == 1 and b.stride(-1) == 1
+    K_, M = (a.shape if a_mn else a.shape[::-1])
+    Kb, N = (b.shape if b_mn else b.shape[::-1])
+    assert K_ == Kb, (a.shape, b.shape, a_mn, b_mn)
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    rc = lib().trlb_gemm_bf16(_p(a), _p(b), _p(out), _p(bias), c_int(M), c_int(N), c_int(K_), c_longlong(a.stride(0)),
+                              c_longlong(b.stride(0)), c_longlong(out.stride(0)), c_int(int(a_mn)), c_int(int(b_mn)),
+                              _p(status_buffer(a.device)), _s())
+    _chk(rc, "trlb_gemm_bf16")
+    return out
+
+
+class LinearFn(torch.autograd.Function):
+    """``y = x W^T (+ b)`` with forward, input gradient and weight gradient all on the tcgen05 GEMM (no operand is
+    transposed in memory; the bias gradient is a column sum)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(-1) != 1 or x2.stride(0) % 8:
+            x2 = x2.contiguous()
+        ctx.save_for_backward(x2, weight)
+        ctx.has_bias, ctx.shape = bias is not None, x.shape
+        return gemm_bf16(x2, weight, bias).view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, weight = ctx.saved_tensors
+        g2 = gy.reshape(-1, gy.shape[-1])
+        if g2.stride(-1) != 1 or g2.stride(0) % 8:
+            g2 = g2.contiguous()
+        dx = gemm_bf16(g2, weight, b_mn=True).view(ctx.shape) if ctx.needs_input_grad[0] else None
+        dw = gemm_bf16(g2, x2, a_mn=True, b_mn=True) if ctx.needs_input_grad[1] else None
+        db = g2.sum(0).to(gy.dtype) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
+        return dx, dw, db
+
+
+def linear_own_ok(x, weight) -> bool:
+    """Shapes the tcgen05 GEMM takes for all three products of a linear layer (16-byte TMA stride rule)."""
+    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.stride(-1) == 1
+            and x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0 and weight.stride(0) % 8 == 0 and x.numel() > 0
+            and (x.numel() // x.shape[-1]) % 8 == 0)
+
+
 _scratch: dict = {}
 
 
@@ -505,6 +555,46 @@ def moe_experts(hidden, gate_up_w, down_w, topk_w, topk_idx):
 # -------------------------------------------------------------------------------------------
 # fused losses
 # -------------------------------------------------------------------------------------------
+_AUX_SCRATCH: dict = {}
+
+
+class _MoeAuxLossFn(torch.autograd.Function):
+    """Router load-balancing loss ``E * sum_e f_e P_e`` in one reduction kernel (csrc/moe.cu); the gradient reaches the
+    router probabilities only (f counts hard assignments): ``dL/dP[n, e] = E f_e mask_n / valid``."""
+
+    @staticmethod
+    def forward(ctx, probs, idx, num_experts, mask):
+        N, E = probs.shape
+        K = idx.shape[1]
+        dev = probs.device
+        key = (dev, E)
+        acc = _AUX_SCRATCH.get(key)
+        if acc is None:
+            acc = _AUX_SCRATCH[key] = torch.zeros(2 * E + 2, dtype=torch.float32, device=dev)
+        out = torch.empty(E + 2, dtype=torch.float32, device=dev)  # [loss, valid, f_0 .. f_{E-1}]
+        p = probs if probs.dtype in (torch.float32, torch.bfloat16) else probs.float()
+        p = p.contiguous()
+        m = None if mask is None else mask.reshape(-1).float().contiguous()
+        _chk(lib().trlb_moe_aux_loss(_p(p), c_int(int(p.dtype == torch.bfloat16)), _p(idx.to(torch.int64).contiguous()),
+                                     _p(m), c_int(N), c_int(E), c_int(K), _p(acc), _p(out[0:1]), _p(out[2:]), _p(out[1:2]),
+                                     _s()), "moe_aux_loss")
+        ctx.save_for_backward(out, m)
+        ctx.E, ctx.dtype = E, probs.dtype
+        return out[0].clone()
+
+    @staticmethod
+    def backward(ctx, g):
+        out, m = ctx.saved_tensors
+        row = (g * ctx.E / out[1]) * out[2:]
+        return (m[:, None] * row[None, :]).to(ctx.dtype), None, None, None
+
+
+def moe_aux_loss(probs, idx, num_experts, mask=None):
+    if mask is None:  # the backward needs the row count: give it an explicit all-ones mask
+        mask = torch.ones(probs.shape[0], dtype=torch.float32, device=probs.device)
+    return _MoeAuxLossFn.apply(probs, idx, num_experts, mask)
+
+
 class GrpoLossFn(torch.autograd.Function):
     """Clipped-ratio + KL token loss, reduced with per-row scales; returns (loss, stats[8])."""
 

@@ -27,8 +27,30 @@ def _use_kernel(x: torch.Tensor) -> bool:
     return x.is_cuda and x.dtype in (torch.bfloat16,)
 
 
+import os as _os
+
+# which GEMM the decoder's plain linears run on: "own" = this library's tcgen05 kernel for the forward, the input
+# gradient and the weight gradient (operands read transposed in place), "cublas" = the library GEMM through torch.
+# The default follows the measurements in benchmarks/kernels.py gemm: the library where it is faster.
+_LINEAR_IMPL = _os.environ.get("TRL_B200_LINEAR", "cublas")
+
+
+def set_linear_impl(name: str) -> str:
+    """Selects the GEMM of :func:`linear` ("own" or "cublas"); returns the previous choice."""
+    global _LINEAR_IMPL
+    if name not in ("own", "cublas"):
+        raise ValueError(name)
+    was, _LINEAR_IMPL = _LINEAR_IMPL, name
+    return was
+
+
 def linear(x, weight, bias=None):
-    """Plain library GEMM (cuBLAS through torch).  Fused variants live in ops.cuda."""
+    """``x @ weight^T (+ bias)``.  With ``TRL_B200_LINEAR=own`` (or :func:`set_linear_impl`) bf16 CUDA inputs run
+    forward, dgrad and wgrad on the tcgen05 GEMM under autograd; otherwise the library GEMM."""
+    if _LINEAR_IMPL == "own" and x.is_cuda:
+        c = _cuda()
+        if c.linear_own_ok(x, weight):
+            return c.LinearFn.apply(x, weight, bias)
     return F.linear(x, weight, bias)
 
 
@@ -122,4 +144,10 @@ def moe_mlp(hidden, router_w, gate_up_w, down_w, top_k, norm_topk_prob):
 
 selective_log_softmax = _ref.selective_log_softmax
 entropy_from_logits = _ref.entropy_from_logits
-load_balancing_loss = _ref.load_balancing_loss
+
+
+def load_balancing_loss(router_probs, topk_idx, num_experts, top_k, token_mask=None):
+    """Router aux loss ``E * sum_e f_e P_e``: one reduction kernel on CUDA tensors, the dense oracle on CPU."""
+    if router_probs.is_cuda and num_experts <= 1024:
+        return _cuda().moe_aux_loss(router_probs, topk_idx, num_experts, token_mask)
+    return _ref.load_balancing_loss(router_probs, topk_idx, num_experts, top_k, token_mask)
