@@ -334,19 +334,27 @@ def run_extras(world: int, rank: int, local_rank: int, master_port: int) -> dict
     out = {}
     shard = "full_shard" if world > 1 else "ddp"
     for i, (task, key) in enumerate((("dpo", f"dpo_llama3_8b_{shard}_tok_s"), ("sft", f"sft_llama3_8b_{shard}_tok_s"))):
-        env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(local_rank), WORLD_SIZE=str(world),
+        # the launcher's agent-store variables must not reach the children: with them rank 0 would not open the
+        # rendezvous store on the new port and every rank would wait for it
+        env = {k: v for k, v in os.environ.items() if not k.startswith("TORCHELASTIC_")}
+        env.update(RANK=str(rank), LOCAL_RANK=str(local_rank), WORLD_SIZE=str(world),
                    MASTER_ADDR=os.environ.get("MASTER_ADDR", "127.0.0.1"), MASTER_PORT=str(master_port + 37 + i))
+        if out.get("_timed_out"):
+            out[key] = None
+            out[key + "_note"] = "skipped: the previous child run exceeded its time limit"
+            continue
         cmd = [sys.executable, "-m", "trl_b200.benchmarks.train_throughput", "--task", task, "--model", "llama-3-8b",
                "--shard", shard, "--steps", "3", "--warmup", "2"]
         p = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
                              cwd=os.path.dirname(os.path.abspath(__file__)))
         try:
-            so, se = p.communicate(timeout=240)
+            so, se = p.communicate(timeout=200)
         except subprocess.TimeoutExpired:
             p.kill()  # this exact child, nothing else
             so, se = p.communicate()
             out[key] = None
-            out[key + "_note"] = "child run exceeded 240 s"
+            out[key + "_note"] = "child run exceeded 200 s"
+            out["_timed_out"] = True
             continue
         if rank != 0:
             continue
@@ -363,6 +371,7 @@ def run_extras(world: int, rank: int, local_rank: int, master_port: int) -> dict
         else:
             out[key] = None
             out[key + "_note"] = (se.strip().splitlines() or ["no output"])[-1][:200]
+    out.pop("_timed_out", None)
     return out
 
 

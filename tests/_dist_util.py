@@ -57,3 +57,20 @@ class Deadline:
                     td.destroy_process_group()
             finally:
                 raise SystemExit(3)
+
+
+def greedy_gaps(model, prompt, tokens):
+    """For a greedy completion ``tokens`` of ``prompt``: at every step, how far (in logit units, fp32 oracle forward of
+    the same weights) the chosen token lies below the best one.  Greedy decoding of a tiny random model sits on
+    near-ties, so two correct engines may pick different tokens; both must stay within rounding of the maximum."""
+    import copy
+
+    import torch
+
+    m32 = copy.deepcopy(model).float()
+    ids = torch.tensor([list(prompt) + list(tokens)], device=model.device)
+    with torch.no_grad():
+        logits = m32(input_ids=ids).logits[0].float()
+    steps = logits[len(prompt) - 1:len(prompt) - 1 + len(tokens)]
+    chosen = steps.gather(1, torch.tensor(list(tokens), device=steps.device)[:, None])[:, 0]
+    return (steps.max(dim=1).values - chosen).tolist()

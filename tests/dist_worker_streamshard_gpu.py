@@ -1,4 +1,4 @@
-"""2-GPU worker: streamed full-shard engine (bf16, NCCL all-gather / reduce-scatter per layer) vs zero2."""
+"""2-GPU worker: streamed full-shard engine (bf16; own peer-memory kernels or the backend's collectives) vs zero2."""
 import copy
 import os
 import sys
@@ -50,6 +50,7 @@ def main():
         m.gradient_checkpointing_enable()
         m.train()
     e_st = StreamShardEngine(m_st)
+    assert e_st.fused == (os.environ.get("TRL_B200_STREAM_FUSED", "1") != "0")
     e_z2 = TrainEngine(m_z2, mode="zero2", use_symm_kernels=False)
     a = run(m_st, e_st, rank)
     b = run(m_z2, e_z2, rank)

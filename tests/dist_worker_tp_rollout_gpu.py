@@ -15,7 +15,7 @@ from trl_b200.testing import make_tiny_model
 
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
-from _dist_util import Deadline  # noqa: E402
+from _dist_util import Deadline, greedy_gaps  # noqa: E402
 
 
 def main():
@@ -37,8 +37,13 @@ def main():
     torch.cuda.synchronize()
     K.check_status(dev)
     assert len(out) == len(ref) == 4
-    agree = sum(o.token_ids[:3] == r.token_ids[:3] for o, r in zip(out, ref))
-    assert agree >= 3, [(o.token_ids, r.token_ids) for o, r in zip(out, ref)]
+    # greedy decoding of a tiny random model sits on near-ties and the engines round differently (bf16 partial sums,
+    # fp32 accumulators, summation order), so tokens may differ: every chosen token must be within rounding of the
+    # fp32 oracle's best logit, for both engines
+    for o, r, p in zip(out, ref, [mine[0], mine[0], mine[1], mine[1]]):
+        for name, c in (("tp", o), ("single", r)):
+            gaps = greedy_gaps(model, p, c.token_ids)
+            assert max(gaps) < 0.1, (name, c.token_ids, gaps)
     # sampled decoding: both ranks of the group must produce identical tokens for the shared batch
     sp2 = SamplingParams(n=2, max_tokens=12, temperature=1.0, eos_token_id=2, eos_prob_floor=0.05, seed=11)
     out2 = eng.generate(mine, sp2)
@@ -66,8 +71,10 @@ def main():
         assert torch.equal(w["down"], lay(l.down_proj[:, rank * il:(rank + 1) * il]))
     ref3 = RolloutEngine(model, max_num_seqs=4, max_model_len=64, poll_every=4).generate(mine, sp)
     out3 = eng.generate(mine, sp)
-    # greedy decoding of a tiny random model sits on near-ties, and the two engines round differently: most, not all
-    assert sum(o.token_ids[:2] == r.token_ids[:2] for o, r in zip(out3, ref3)) >= 2, [(o.token_ids, r.token_ids) for o, r in zip(out3, ref3)]
+    for o, r, p in zip(out3, ref3, [mine[0], mine[0], mine[1], mine[1]]):
+        for name, c in (("tp", o), ("single", r)):
+            gaps = greedy_gaps(model, p, c.token_ids)
+            assert max(gaps) < 0.1, (name, c.token_ids, gaps)
     td.barrier()
     if rank == 0:
         print("TP_ROLLOUT_OK")

@@ -47,6 +47,10 @@ def test_weight_reshard_from_full_shard_to_tp_layout():
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_streamed_full_shard_engine_two_ranks():
-    rc, out, err = run_ranks(os.path.join(HERE, "dist_worker_streamshard_gpu.py"), 29631)
+@pytest.mark.parametrize("fused", [1, 0])
+def test_streamed_full_shard_engine_two_ranks(fused):
+    """fused=1: slices pulled over peer loads on a side stream and per-layer gradient reduction by the own kernel;
+    fused=0: the backend's all-gather / reduce-scatter."""
+    rc, out, err = run_ranks(os.path.join(HERE, "dist_worker_streamshard_gpu.py"), 29631 + 20 * fused,
+                             extra_env={"TRL_B200_STREAM_FUSED": str(fused)})
     assert rc == 0 and "STREAMSHARD_OK" in out, out[-3000:] + err[-3000:]

@@ -89,8 +89,21 @@ def test_decode_gemm_stream_k_and_fp32_add_rmsnorm(B, N, K, pdl):
         assert (y3 - want).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item())
         ctr = torch.zeros(1, dtype=torch.int32, device="cuda")  # single rank: the arrival counter counts the grid
         y4 = torch.zeros(B, N, device="cuda")
-        Kc.decode_gemm(x, w, bias, y32=y4, peers=([], [ctr.data_ptr()]))
+        Kc.decode_gemm(x, w, bias, y32=y4, peers=([], [ctr.data_ptr()], None, None))
         assert int(ctr.item()) == Kc.decode_gemm_ctas(B, N, K) and (y4 - want).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item())
+        if N % 4 == 0:
+            # the fused all-reduce path with a second local buffer standing in for a peer's accumulator: partial sums
+            # meet in the staging buffer, every finished quarter is handed to both buffers once, two launches add up
+            y5, y6 = torch.zeros(B, N, device="cuda"), torch.zeros(B, N, device="cuda")
+            stage = torch.zeros(B, N, device="cuda")
+            slab_ctr = torch.zeros(4 * ((N + 127) // 128), dtype=torch.int32, device="cuda")
+            ctrs = torch.zeros(32, dtype=torch.int32, device="cuda")
+            for _ in range(2):
+                Kc.decode_gemm(x, w, bias, y32=y5, peers=([y6.data_ptr()], [ctrs.data_ptr(), ctrs[16:].data_ptr()], stage, slab_ctr))
+            assert ctrs[0].item() == ctrs[16].item() == 2 * Kc.decode_gemm_arrivals(N)
+            assert float(stage.abs().max()) == 0.0 and int(slab_ctr.abs().max()) == 0
+            for got in (y5, y6):
+                assert (got - 2 * want).abs().max().item() < 4e-2 * max(1.0, want.abs().max().item())
         if N % 8 == 0:
             res = torch.randn(B, N, device="cuda").to(torch.bfloat16)
             gamma = torch.randn(N, device="cuda").to(torch.bfloat16)

@@ -8,6 +8,8 @@
 //   adamw_bcast      sharded AdamW on the reduced shard, writing the updated bf16 parameters straight
 //                    into every rank's replica (the parameter all-gather happens in the store)
 //   shard_allgather  parameter all-gather by pull (peer loads) or push (multimem.st)
+//   shard_pull       a layer's parameter slices pulled from every owner into a local full-size slot (streamed
+//                    full shard: no barrier, the slices only change at the optimizer step)
 //   allreduce_add_rmsnorm   TP decode: sum of the ranks' partial GEMM outputs + residual add + RMSNorm
 //   norm_allreduce   grad-norm partials of all ranks -> clip coefficient on every rank, no host sync
 //
@@ -116,7 +118,7 @@ __device__ bool grid_last_block(uint32_t* counter) {
 template <typename GradT>
 __global__ void __launch_bounds__(512)
 rs_reduce_kernel(Peers P, const void* mc, long long lo, long long n, float* __restrict__ out, float* __restrict__ sumsq,
-                 uint32_t* epoch_ctr, uint32_t* local_gate, int channel, int* status) {
+                 uint32_t* epoch_ctr, uint32_t* local_gate, int channel, int* status, int accumulate) {
   const uint32_t epoch = *epoch_ctr + 1;
   if (!peers_barrier(P, channel, epoch, local_gate, status, 500)) return;
   const float inv = 1.f / (float)P.world;
@@ -163,6 +165,14 @@ rs_reduce_kernel(Peers P, const void* mc, long long lo, long long n, float* __re
       ss += acc[j] * acc[j];
     }
     float4* dst = reinterpret_cast<float4*>(out + v * VEC);
+    if (accumulate) {  // out += mean (the accumulator of several micro-batches)
+      const float4 o0 = dst[0];
+      acc[0] += o0.x; acc[1] += o0.y; acc[2] += o0.z; acc[3] += o0.w;
+      if constexpr (VEC == 8) {
+        const float4 o1 = dst[1];
+        acc[4] += o1.x; acc[5] += o1.y; acc[6] += o1.z; acc[7] += o1.w;
+      }
+    }
     dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
     if constexpr (VEC == 8) dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
   }
@@ -608,6 +618,34 @@ __global__ void bounded_wait_selftest_kernel(const uint32_t* flag, uint32_t expe
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// shard_pull: dst[owner * per + i] = src_owner[i] for every owner (16-byte vectors, four in flight per thread); the
+// owners are visited starting after this rank so that the ranks do not all read one owner at once.  No flags: the
+// caller orders the launch after the point where the owners' slices became final.
+// ------------------------------------------------------------------------------------------------
+struct PullSrc {
+  const uint4* src[MAX_PEERS];
+};
+
+__global__ void __launch_bounds__(512) shard_pull_kernel(PullSrc S, uint4* __restrict__ dst, long long nvec, int world,
+                                                         int rank) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (int s = 1; s <= world; ++s) {
+    const int owner = (rank + s) % world;  // the own slice comes last
+    const uint4* __restrict__ src = nullptr;
+#pragma unroll
+    for (int p = 0; p < MAX_PEERS; ++p)
+      if (p == owner) src = S.src[p];  // static indices: the parameter struct stays in constant memory
+    uint4* d = dst + owner * nvec;
+    long long q = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    for (; q + 3 * stride < nvec; q += 4 * stride) {
+      const uint4 a = src[q], b = src[q + stride], c = src[q + 2 * stride], e = src[q + 3 * stride];
+      d[q] = a; d[q + stride] = b; d[q + 2 * stride] = c; d[q + 3 * stride] = e;
+    }
+    for (; q < nvec; q += stride) d[q] = src[q];
+  }
+}
+
 // Trainer -> generator weight sync from sharded parameters: a list of contiguous ranges, each read from the rank that
 // owns it (a peer mapping of the symmetric parameter arena, or local memory) and written into this rank's
 // tensor-parallel weight buffers.  One CTA per range at a time, 16 bytes per thread and iteration.  The list is built
@@ -656,9 +694,27 @@ TRLB_API int trlb_rs_reduce(const unsigned long long* bufs, const unsigned long 
   Peers P = make_peers(bufs, pads, rank, world);
   const int grid = capped_grid(n / 4, 512);
   if (grad_is_bf16)
-    rs_reduce_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(P, nullptr, lo, n, out, sumsq, epoch_ctr, local_gate, channel, status);
+    rs_reduce_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(P, nullptr, lo, n, out, sumsq, epoch_ctr, local_gate, channel, status, 0);
   else
-    rs_reduce_kernel<float><<<grid, 512, 0, st>>>(P, mc, lo, n, out, sumsq, epoch_ctr, local_gate, channel, status);
+    rs_reduce_kernel<float><<<grid, 512, 0, st>>>(P, mc, lo, n, out, sumsq, epoch_ctr, local_gate, channel, status, 0);
+  return (int)cudaGetLastError();
+}
+
+// out[n] (fp32) += mean over ranks of grad[lo:lo+n] (bf16 or fp32 buffers read in place over peer loads).  The
+// squared norm of the means of this call (not of the accumulator) is added to sumsq.  max_ctas bounds the grid so
+// that the kernel can run beside a backward pass (0 = one CTA per SM).
+TRLB_API int trlb_rs_reduce_accum(const unsigned long long* bufs, const unsigned long long* pads, int rank, int world,
+                                  int grad_is_bf16, long long lo, long long n, float* out, float* sumsq,
+                                  unsigned* epoch_ctr, unsigned* local_gate, int channel, int max_ctas, int* status,
+                                  cudaStream_t st) {
+  if (world > MAX_PEERS || n % 8 != 0 || lo % 8 != 0) return -1;
+  Peers P = make_peers(bufs, pads, rank, world);
+  int grid = capped_grid(n / 4, 512);
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  if (grad_is_bf16)
+    rs_reduce_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(P, nullptr, lo, n, out, sumsq, epoch_ctr, local_gate, channel, status, 1);
+  else
+    rs_reduce_kernel<float><<<grid, 512, 0, st>>>(P, nullptr, lo, n, out, sumsq, epoch_ctr, local_gate, channel, status, 1);
   return (int)cudaGetLastError();
 }
 
@@ -749,6 +805,22 @@ TRLB_API int trlb_tp_token_sync(const unsigned long long* mails, const unsigned 
 TRLB_API int trlb_bounded_wait_selftest(const void* flag, unsigned expect, int budget_ms, int* status, cudaStream_t st) {
   if (budget_ms < 1 || budget_ms > 1000) return -160;  // the budget is what keeps this from being a hang
   bounded_wait_selftest_kernel<<<1, 32, 0, st>>>((const uint32_t*)flag, expect, (uint64_t)budget_ms * 1000000ull, status);
+  return (int)cudaGetLastError();
+}
+
+// srcs[p]: rank p's slice (per elements of 2 bytes, 16-byte aligned, per a multiple of 8) as mapped by this rank;
+// dst: local buffer of world * per elements.  ctas: grid size (it shares the GPU with the compute stream).
+TRLB_API int trlb_shard_pull(const unsigned long long* srcs, int rank, int world, void* dst, long long per, int ctas,
+                             cudaStream_t st) {
+  if (world < 1 || world > MAX_PEERS || per % 8 != 0 || (reinterpret_cast<uintptr_t>(dst) & 15)) return -1;
+  PullSrc S;
+  for (int p = 0; p < MAX_PEERS; ++p) {
+    S.src[p] = p < world ? reinterpret_cast<const uint4*>(srcs[p]) : nullptr;
+    if (p < world && (srcs[p] & 15)) return -1;
+  }
+  if (ctas < 1) ctas = 32;
+  if (ctas > 4 * trlb_host::sm_count()) ctas = 4 * trlb_host::sm_count();
+  shard_pull_kernel<<<ctas, 512, 0, st>>>(S, (uint4*)dst, per / 8, world, rank);
   return (int)cudaGetLastError();
 }
 

@@ -13,10 +13,15 @@
 //     equal contiguous runs, so every SM streams the same number of bytes whatever N is (a 28-slab projection
 //     still keeps 148 SMs busy, and there is no ragged last wave);
 //   * a run that does not cover a slab's whole K range adds its partial sums to an fp32 output with red.global
-//     (lanes = consecutive features, one 128-byte line per warp instruction), optionally also into the same buffer
-//     of tensor-parallel peers over NVLink, followed by an arrival count that the consumer waits on: this is the
-//     row-parallel GEMM fused with its all-reduce.  The consumer of that output (residual add + RMSNorm, or RoPE +
-//     KV append) reads the sums and clears them, so no memset or conversion kernel runs between two GEMMs;
+//     (lanes = consecutive features, one 128-byte line per warp instruction).  The consumer of that output
+//     (residual add + RMSNorm, or RoPE + KV append) reads the sums and clears them, so no memset or conversion
+//     kernel runs between two GEMMs;
+//   * row-parallel GEMM fused with its all-reduce: with tensor-parallel peers the runs add into a LOCAL fp32
+//     staging buffer and count their K blocks per (slab, 32-feature quarter); the warp whose count completes a
+//     quarter reads the finished sums back from L2, clears them and adds them ONCE into the accumulator of every
+//     rank (its own and, over NVLink, the peers') with 16-byte vector reductions, then bumps every rank's arrival
+//     counter.  So each sum crosses NVLink once per peer whatever the stream-K split is, finished quarters go out
+//     while other SMs still stream weights, and the consumer waits only on its own counter;
 //   * whole-slab schedules store bf16 directly (+ bias), or apply SwiGLU: gate and up slabs of the same features go
 //     to two accumulators through alternate pipeline stages and the epilogue writes silu(gate) * up;
 //   * W may be stored tile-major ([slab][K block][128][64], each 16 KB tile contiguous), which turns the weight
@@ -50,9 +55,13 @@ struct DecodeGemmParams {
   long long ldy;
   const __nv_bfloat16* bias;  // [N] or null (not with SwiGLU)
   int* status;
-  // row-parallel all-reduce (DG_ACCUM_F32 only): the same sums are added into the peers' buffers, then every CTA
-  // bumps the arrival counter of each rank (its own included) after a system-scope fence
+  // row-parallel all-reduce (DG_ACCUM_F32 only).  n_peers > 0: partial sums go to `stage` ([B, ldy] fp32, local,
+  // zero between launches), K blocks are counted in slab_ctr[slab * 4 + quarter] (local, zero between launches) and
+  // the finisher of a quarter adds the sums into Y32 and every peer_Y32 and bumps every arrive[] once.
+  // n_peers == 0 with arrive[0] set: sums go straight to Y32 and every CTA bumps arrive[0] once.
   int n_peers;
+  float* stage;
+  uint32_t* slab_ctr;
   float* peer_Y32[DG_MAX_PEERS];
   uint32_t* arrive[DG_MAX_PEERS + 1];  // [0] = this rank's counter, then the peers'
 };
@@ -78,8 +87,49 @@ __device__ __forceinline__ void dg_range(const DecodeGemmParams& p, int g, int G
   }
 }
 
-__device__ __forceinline__ void red_add_sys(float* addr, float v) {
-  asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
+__device__ __forceinline__ void red_add_v4_sys(float* addr, const float4& v) {
+  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z),
+               "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void red_add_v4_gpu(float* addr, const float4& v) {
+  asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z),
+               "f"(v.w) : "memory");
+}
+
+// One warp hands the finished sums of features [f0, f0 + 32) of all B rows from the staging buffer to every rank.
+// Lane l covers the float4 (l & 7) of row (l >> 3) + 4 j; four rows' loads are in flight per lane at a time.
+__device__ __forceinline__ void dg_finish_quarter(const DecodeGemmParams& p, int f0, int lane) {
+  const int f = f0 + 4 * (lane & 7);
+  if (f < p.N) {  // N is a multiple of 4 on this path
+#pragma unroll 1
+    for (int rb = lane >> 3; rb < p.B; rb += 16) {
+      float4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int row = rb + 4 * j;
+        if (row < p.B) {
+          float4* src = reinterpret_cast<float4*>(p.stage + (long long)row * p.ldy + f);
+          v[j] = __ldcg(src);
+          __stcg(src, make_float4(0.f, 0.f, 0.f, 0.f));
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int row = rb + 4 * j;
+        if (row < p.B) {
+          const long long off = (long long)row * p.ldy + f;
+          red_add_v4_gpu(p.Y32 + off, v[j]);
+          for (int q = 0; q < p.n_peers; ++q) red_add_v4_sys(p.peer_Y32[q] + off, v[j]);
+        }
+      }
+    }
+  }
+  __threadfence_system();  // this lane's sums, before the warp's arrival below
+  __syncwarp();
+  if (lane == 0) {
+    for (int q = 0; q <= p.n_peers; ++q)
+      asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.arrive[q]) : "memory");
+  }
 }
 
 template <int BN, bool SWIGLU, int STAGES, int MIN_CTAS>
@@ -236,19 +286,11 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         const int rows = min(16, p.B - c);
         const long long off = (long long)c * p.ldy + n;
         if (p.mode == DG_ACCUM_F32) {
-          float* dst = p.Y32 + off;
+          float* dst = (p.n_peers > 0 ? p.stage : p.Y32) + off;
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             if (i < rows) atomicAdd(dst, v[i] + bias);
             dst += p.ldy;
-          }
-          for (int q = 0; q < p.n_peers; ++q) {
-            float* pd = p.peer_Y32[q] + off;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              if (i < rows) red_add_sys(pd, v[i] + bias);
-              pd += p.ldy;
-            }
           }
         } else {
           __nv_bfloat16* dst = p.Yb + off;
@@ -263,12 +305,29 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      if (p.n_peers > 0) {
+        // count this run's K blocks for (slab, quarter); whoever completes the count owns the hand-over
+        __threadfence();
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) {
+          uint32_t* ctr = p.slab_ctr + slab * 4 + quarter;
+          const uint32_t before = atomicAdd(ctr, (uint32_t)(s1 - s0));
+          last = before + (uint32_t)(s1 - s0) == (uint32_t)sps;
+          if (last) *ctr = 0;  // nobody else touches this word until the next launch
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+          __threadfence();
+          dg_finish_quarter(p, slab * DG_BM + quarter * 32, lane);
+        }
+      }
       t += s1 - s0;
     }
-    if (p.arrive[0] != nullptr) __threadfence_system();  // this thread's sums, before the CTA's arrival below
+    if (p.n_peers == 0 && p.arrive[0] != nullptr) __threadfence_system();  // before the CTA's arrival below
   }
   __syncthreads();
-  if (p.arrive[0] != nullptr && threadIdx.x == 64) {
+  if (p.n_peers == 0 && p.arrive[0] != nullptr && threadIdx.x == 64) {
     __threadfence_system();
     for (int q = 0; q <= p.n_peers; ++q)
       asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.arrive[q]) : "memory");
@@ -354,23 +413,32 @@ TRLB_API int trlb_decode_gemm_ctas(int B, int N, int K, int mode, int max_ctas) 
   return ctas;
 }
 
+// Arrivals per rank of one fused all-reduce GEMM with N output features (one per slab and 32-feature quarter).
+TRLB_API int trlb_decode_gemm_arrivals(int N) { return 4 * ((N + DG_BM - 1) / DG_BM); }
+
 // X [B, K] bf16 (row stride ldx), B <= 128.  W bf16: row-major with row stride ldw, or (tiled != 0) tile-major
 // [ceil(rows/128)][ceil(K/64)][128][64] as written by trlb_tile_weights.
 //   mode 0  W [N, K];  Y32 [B, N] fp32 (row stride ldy) is added to (+ bias once): the caller provides zeros
 //   mode 1  W [N, K];  Yb  [B, N] bf16 = X W^T (+ bias)
 //   mode 2  W [2N, K] (gate rows, then up rows; N a multiple of 128);  Yb [B, N] bf16 = silu(X Wg^T) * (X Wu^T)
 // max_ctas: 0 = every SM with its resident CTAs, else an upper bound on the grid.
-// Fused all-reduce (mode 0): peer_y32[i] is the same buffer on peer i (n_peers of them); arrive[0] is this rank's
-// arrival counter and arrive[1 + i] peer i's; each CTA adds 1 to every counter once its sums are visible
-// system-wide.  arrive may be given with n_peers == 0 (a single rank still counts its own CTAs), or be null.
+// Fused all-reduce (mode 0, n_peers > 0): peer_y32[i] is the same buffer on peer i; arrive[0] is this rank's arrival
+// counter and arrive[1 + i] peer i's; stage is a local zeroed fp32 buffer shaped like Y32 and slab_ctr a local zeroed
+// array of 4 * ceil(N / 128) words (both are left zeroed); N and ldy multiples of 4.  Every (slab, quarter) adds 1
+// to every counter once its sums are visible system-wide: a consumer waits for ranks * trlb_decode_gemm_arrivals(N).
+// arrive may also be given with n_peers == 0: then each CTA adds 1 to arrive[0] (trlb_decode_gemm_ctas of them).
 TRLB_API int trlb_decode_gemm(const void* X, const void* W, const void* bias, float* Y32, void* Yb, int B, int N, int K,
                               long long ldx, long long ldw, long long ldy, int mode, int tiled, int max_ctas, int n_peers,
-                              float* const* peer_y32, uint32_t* const* arrive, int* status, cudaStream_t st) {
+                              float* const* peer_y32, uint32_t* const* arrive, float* stage, uint32_t* slab_ctr,
+                              int* status, cudaStream_t st) {
   if (B <= 0 || N <= 0 || K <= 0) return 0;
   if (B > 128 || (K % 8) != 0 || (ldx % 8) != 0 || mode < 0 || mode > 2) return -150;
   if (!tiled && (ldw % 8) != 0) return -150;
   if (mode == DG_SWIGLU && (bias != nullptr || (N % DG_BM) != 0)) return -150;
   if (n_peers < 0 || n_peers > DG_MAX_PEERS || (n_peers > 0 && (mode != DG_ACCUM_F32 || !peer_y32 || !arrive))) return -150;
+  if (n_peers > 0 && (!stage || !slab_ctr || (N % 4) != 0 || (ldy % 4) != 0 || (reinterpret_cast<uintptr_t>(Y32) & 15) ||
+                      (reinterpret_cast<uintptr_t>(stage) & 15)))
+    return -150;
   const int BN = B <= 64 ? 64 : 128;
   const long long w_rows = mode == DG_SWIGLU ? 2LL * N : N;
   DecodeGemmParams p = {};
@@ -388,7 +456,7 @@ TRLB_API int trlb_decode_gemm(const void* X, const void* W, const void* bias, fl
   }
   if (trlb_host::make_tmap_2d_bf16(&tx, X, (uint64_t)B, (uint64_t)K, (uint64_t)ldx, (uint32_t)BN, DG_BK)) return -152;
   p.Y32 = Y32; p.Yb = (__nv_bfloat16*)Yb; p.ldy = ldy; p.bias = (const __nv_bfloat16*)bias; p.status = status;
-  p.n_peers = n_peers;
+  p.n_peers = n_peers; p.stage = stage; p.slab_ctr = slab_ctr;
   if (arrive != nullptr && mode == DG_ACCUM_F32) p.arrive[0] = arrive[0];
   for (int i = 0; i < n_peers; ++i) { p.peer_Y32[i] = peer_y32[i]; p.arrive[1 + i] = arrive[1 + i]; }
   const int ctas = trlb_decode_gemm_ctas(B, N, K, mode, max_ctas);

@@ -722,9 +722,11 @@ def decode_gemm(x, w, bias=None, *, y32=None, out=None, swiglu=False, max_ctas: 
     with ``swiglu`` ``w`` is ``[2N, K]`` (gate rows, then up rows) and ``out = silu(x Wg^T) * (x Wu^T)``.
 
     ``tiled_shape=(rows, K)``: ``w`` is the flat tile-major copy made by :func:`tile_weights` of a ``[rows, K]`` weight.
-    ``peers=(peer_y32_ptrs, arrive_ptrs)``: row-parallel GEMM fused with its all-reduce: the sums are also added into
-    the peers' buffers (device addresses) and each CTA bumps every rank's arrival counter (``arrive_ptrs[0]`` is this
-    rank's own); see :func:`decode_gemm_ctas` for the count to wait for."""
+    ``peers=(peer_y32_ptrs, arrive_ptrs, stage, slab_ctr)``: row-parallel GEMM fused with its all-reduce: partial sums
+    are collected in the local fp32 ``stage`` (shaped like ``y32``, zeros; left zeroed) and every finished 32-feature
+    quarter of a slab is added once into ``y32`` and the peers' buffers (device addresses), bumping every rank's
+    arrival counter (``arrive_ptrs[0]`` is this rank's own); ``slab_ctr``: zeroed int32 words, four per 128 features.
+    A consumer waits for ``ranks * decode_gemm_arrivals(N)``."""
     B, Kd = x.shape
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1
     if tiled_shape is not None:
@@ -743,17 +745,19 @@ def decode_gemm(x, w, bias=None, *, y32=None, out=None, swiglu=False, max_ctas: 
             out = torch.empty(B, N, dtype=torch.bfloat16, device=x.device)
         assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and tuple(out.shape) == (B, N)
         mode, ldy, dst32, dstb, ret = (2 if swiglu else 1), out.stride(0), None, out, out
-    n_peers, peer_arr, arrive_arr = 0, None, None
+    n_peers, peer_arr, arrive_arr, stage, slab_ctr = 0, None, None, None, None
     if peers is not None:
-        peer_ptrs, arrive_ptrs = peers
+        peer_ptrs, arrive_ptrs, stage, slab_ctr = peers
         n_peers = len(peer_ptrs)
         assert mode == 0 and len(arrive_ptrs) == n_peers + 1
+        if n_peers:
+            assert stage.dtype == torch.float32 and stage.stride() == y32.stride() and slab_ctr.numel() * 32 >= N
         peer_arr = (c_void_p * max(1, n_peers))(*peer_ptrs) if n_peers else None
         arrive_arr = (c_void_p * (n_peers + 1))(*arrive_ptrs)
     _chk(lib().trlb_decode_gemm(_p(x), _p(w), _p(bias), _p(dst32), _p(dstb), c_int(B), c_int(N), c_int(Kd),
                                 c_longlong(x.stride(0)), c_longlong(ldw), c_longlong(ldy), c_int(mode),
                                 c_int(int(tiled_shape is not None)), c_int(max_ctas), c_int(n_peers), peer_arr, arrive_arr,
-                                _p(status_buffer(x.device)), _s()), "decode_gemm")
+                                _p(stage), _p(slab_ctr), _p(status_buffer(x.device)), _s()), "decode_gemm")
     return ret
 
 
@@ -761,6 +765,11 @@ def decode_gemm_ctas(B: int, N: int, K: int, mode: int = 0, max_ctas: int = 0) -
     """Grid size :func:`decode_gemm` uses for ``B`` rows and an ``[N, K]`` weight (mode 0: fp32 sums, 1: bf16 store,
     2: SwiGLU)."""
     return int(lib().trlb_decode_gemm_ctas(c_int(B), c_int(N), c_int(K), c_int(mode), c_int(max_ctas)))
+
+
+def decode_gemm_arrivals(N: int) -> int:
+    """Arrival-counter increments per rank of one fused all-reduce :func:`decode_gemm` with ``N`` output features."""
+    return int(lib().trlb_decode_gemm_arrivals(c_int(N)))
 
 
 def tile_weights(w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -889,6 +898,23 @@ def rs_reduce(arena, byte_offset, grad_is_bf16, lo, n, out, sumsq, sync, use_mul
                               c_int(int(grad_is_bf16)), c_longlong(lo), c_longlong(n), _p(out), _p(sumsq),
                               sync.epoch_ptr, sync.gate_ptr, c_int(sync.channel), _p(status_buffer(out.device)), _s()),
          "rs_reduce")
+
+
+def rs_reduce_accum(arena, byte_offset, grad_is_bf16, lo, n, out, sumsq, sync, max_ctas: int = 0):
+    """out[n] (fp32) += mean over ranks of grad[lo:lo+n], read in place from every rank's buffer at ``byte_offset`` of
+    the arena; ``max_ctas`` bounds the grid so that the kernel can run beside other work."""
+    _chk(lib().trlb_rs_reduce_accum(arena.peers(byte_offset), arena.pads(), c_int(arena.rank), c_int(arena.world),
+                                    c_int(int(grad_is_bf16)), c_longlong(lo), c_longlong(n), _p(out), _p(sumsq),
+                                    sync.epoch_ptr, sync.gate_ptr, c_int(sync.channel), c_int(max_ctas),
+                                    _p(status_buffer(out.device)), _s()), "rs_reduce_accum")
+
+
+def shard_pull(arena, byte_offset, per, dst, ctas: int = 32):
+    """``dst[p * per:(p + 1) * per] = `` rank p's ``per`` bf16 elements at ``byte_offset`` of the arena, for every p
+    (peer loads; no barrier: the caller orders the launch after the slices became final)."""
+    assert dst.dtype == torch.bfloat16 and dst.numel() >= per * arena.world
+    _chk(lib().trlb_shard_pull(arena.peers(byte_offset), c_int(arena.rank), c_int(arena.world), _p(dst), c_longlong(per),
+                               c_int(ctas), _s()), "shard_pull")
 
 
 def norm_allreduce(arena, byte_offset, my_sumsq, max_norm, norm_out, clip_out, sync):

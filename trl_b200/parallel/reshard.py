@@ -7,6 +7,10 @@ once, the list of contiguous ranges each TP weight buffer is made of, resolves e
 and its address in that rank's mapping of the symmetric parameter arena, and a single kernel (``trlb_copy_list``)
 pulls exactly the bytes this rank needs: 1/tp of the model instead of all of it.
 
+When the rollout engine keeps its slices tile-major (the fused tensor-parallel decode path) the pull goes layer by
+layer into one layer-sized row-major staging set, and each matrix is re-tiled from there into the engine's buffer:
+a 128-byte tile row is too small a unit for a copy list (60 M entries for a 7 B model).
+
 The reference moves weights to its generator with per-parameter ``full_tensor()`` gathers and NCCL broadcasts
 (trl/generation/vllm_generation.py:400-470, trl/generation/vllm_client.py:481-512)."""
 from __future__ import annotations
@@ -28,6 +32,12 @@ class WeightResharder:
         ql, kl, il = tp_engine.hq_local * D, tp_engine.hk_local * D, I // tp
         by_name = {b.name: b for b in engine.buckets}
         entries: list[tuple[int, int, int]] = []
+        self.tiled = bool(getattr(tp_engine, "fused", False))
+        dt, dev = torch.bfloat16, tp_engine.dev
+        self.stage = ({"qkv": torch.empty(ql + 2 * kl, H, dtype=dt, device=dev), "o": torch.empty(H, ql, dtype=dt, device=dev),
+                       "gu": torch.empty(2 * il, H, dtype=dt, device=dev), "down": torch.empty(H, il, dtype=dt, device=dev)}
+                      if self.tiled else None)
+        self.layer_ranges: list[tuple[int, int]] = []
 
         def add(bucket, elem_off, n_elems, dst_ptr):
             """[elem_off, elem_off + n) of the bucket -> dst; split at ownership boundaries."""
@@ -44,6 +54,9 @@ class WeightResharder:
                 elem_off, n_elems, dst_ptr = elem_off + n, n_elems - n, dst_ptr + n * 2
 
         for i, w in enumerate(tp_engine.w):
+            first = len(entries)
+            if self.tiled:
+                w = self.stage
             b = by_name[f"layers.{i}"]
             off = {n.split(".")[-1]: o for n, o in zip(b.names, b.offsets)}
             # row slices: contiguous
@@ -57,6 +70,7 @@ class WeightResharder:
             for row in range(H):
                 add(b, off["o_proj"] + row * qs + r * ql, ql, w["o"].data_ptr() + row * ql * 2)
                 add(b, off["down_proj"] + row * I + r * il, il, w["down"].data_ptr() + row * il * 2)
+            self.layer_ranges.append((first, len(entries)))
         self.n = len(entries)
         self.bytes = sum(e[2] for e in entries)
         self.table = torch.from_numpy(np.asarray(entries, dtype=np.uint64).reshape(-1, 3).view(np.int64).copy()).to(tp_engine.dev)
@@ -70,7 +84,25 @@ class WeightResharder:
 
         from ..ops.cuda import _chk, _p, _s, lib
 
-        _chk(lib().trlb_copy_list(_p(self.table), c_int(self.n), _s()), "copy_list")
+        if self.tiled:
+            from ..ops import cuda as K
+
+            ql, kl, il = self.tp._dims
+            H = self.tp.cfg.hidden_size
+            kb_h = -(-H // 64)
+            for (a, b), w in zip(self.layer_ranges, self.tp.w):
+                _chk(lib().trlb_copy_list(_p(self.table[a:]), c_int(b - a), _s()), "copy_list")
+                # pieces are whole 128-row slabs (the fused path requires it), so they tile independently
+                o = 0
+                for n in (ql, kl, kl):
+                    K.tile_weights(self.stage["qkv"][o:o + n], out=w["qkv"][o * kb_h * 64:(o + n) * kb_h * 64])
+                    o += n
+                K.tile_weights(self.stage["o"], out=w["o"])
+                K.tile_weights(self.stage["gu"][:il], out=w["gu"][: il * kb_h * 64])
+                K.tile_weights(self.stage["gu"][il:], out=w["gu"][il * kb_h * 64:])
+                K.tile_weights(self.stage["down"], out=w["down"])
+        else:
+            _chk(lib().trlb_copy_list(_p(self.table), c_int(self.n), _s()), "copy_list")
         if self._bias:  # biases live in the replicated vector bucket: slice locally
             tp = self.tp
             D = tp.cfg.head_dim

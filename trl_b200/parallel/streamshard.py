@@ -17,10 +17,27 @@ profiles, trl/accelerate_configs/fsdp2.yaml and zero3.yaml):
 * embeddings, final norm and lm_head stay whole on every rank (gradient + optimizer state sharded, zero-2 style).
 
 Activation checkpointing is required: with it autograd keeps no references to a layer's weights between forward and
-backward, which is what makes overwriting the slot legal.  Collectives are the backend's (NCCL on GPUs, gloo on
-CPU), issued asynchronously: while a layer computes, the gather of the layer expected next already fills the other
-slot (2 L - 2 gathers per forward + backward of L layers, none wasted).  Gathering *inside* the consuming GEMM is the
-job of the fused kernels in ``fullshard.py`` and is not repeated here.
+backward, which is what makes overwriting the slot legal.  While a layer computes, the gather of the layer expected
+next already fills the other slot (2 L - 2 gathers per forward + backward of L layers, none wasted).
+
+On GPUs of one NVLink domain (bf16, symmetric memory available) the data movement is the framework's own kernels
+over peer memory, not the backend's collectives:
+
+* every rank keeps its bf16 slices in one symmetric arena.  A gather is ``shard_pull``: one kernel on a side stream
+  that reads each owner's slice through its peer mapping straight into the local slot.  It needs no flag and no
+  barrier, because slices change only inside the optimizer step, which is fenced by the gradient-norm all-reduce
+  before it (every rank's gathers are joined first) and by the collective that republishes the replicated
+  parameters after it;
+* a layer's gradients are collected in one of three symmetric gradient buffers, and ``rs_reduce`` (accumulating
+  form) runs on a second side stream as soon as the layer's last gradient has arrived: each rank reads its slice of
+  every peer's buffer in place, averages in fp32 and adds to its accumulator, while the main stream goes on with the
+  backward pass of the next layer.  The kernel's entry barrier is what makes reuse safe: a buffer is written again
+  three layers later, after this rank's reduction of the layer in between has passed its barrier, which no rank
+  passes before every rank has finished reading the earlier buffer.
+
+Elsewhere (CPU / gloo, fp32, a single rank, ``TRL_B200_STREAM_FUSED=0``) the backend's all-gather / reduce-scatter are
+used, issued asynchronously in the same order.  Gathering *inside* the consuming GEMM is the job of the fused
+kernels in ``fullshard.py`` and is not repeated here.
 
 Per rank and per parameter of a streamed layer: 4 + 8 (fp32 master, moments; the bf16 copy exists only inside the
 slots) + 4 (gradient accumulator; 2 with ``grad_dtype=torch.bfloat16``) = 16 (14) bytes / world, plus 2 slots + 1
@@ -29,11 +46,23 @@ against 140 GB for the bf16 weights alone under ``FullShardEngine``.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as td
 import torch.nn as nn
 
 from .engine import _ALIGN, adamw_flat
+
+
+class _EventWork:
+    """Stands where an async collective's work handle would: ``wait()`` orders the current stream after the event."""
+
+    def __init__(self, event):
+        self.event = event
+
+    def wait(self):
+        torch.cuda.current_stream().wait_event(self.event)
 
 
 class _LayerShard:
@@ -118,7 +147,33 @@ class StreamShardEngine:
         slot_numel = max(l.numel for l in self.layers)
         # separate allocations: autograd tracks in-place writes per base tensor
         self.slots = [torch.zeros(slot_numel, dtype=self.dtype, device=self.dev) for _ in range(2)]
-        self.gbuf = None if frozen else torch.zeros(slot_numel, dtype=self.dtype, device=self.dev)
+        self.fused = False
+        if (self.dev.type == "cuda" and self.world > 1 and self.dtype == torch.bfloat16
+                and os.environ.get("TRL_B200_STREAM_FUSED", "1") != "0"):
+            from .symm import SymmArena, SyncWords, symmetric_available
+
+            if symmetric_available():
+                nbytes = sum(l.numel // self.world * 2 + 256 for l in self.layers) + 4096
+                nbytes += 0 if frozen else 3 * (slot_numel * 2 + 256)
+                self.arena = SymmArena(nbytes, self.dev, group)
+                self.fused = True
+                self._gstream, self._rstream = torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev)
+                self._pull_ctas = int(os.environ.get("TRL_B200_STREAM_PULL_CTAS", "32"))
+                self._reduce_ctas = int(os.environ.get("TRL_B200_STREAM_REDUCE_CTAS", "32"))
+                for l in self.layers:
+                    l.shard16, l.shard16_off = self.arena.carve(l.numel // self.world, torch.bfloat16)
+                if not frozen:
+                    self._gbufs = [self.arena.carve(slot_numel, torch.bfloat16) for _ in range(3)]
+                    self._gbuf_done = [None, None, None]
+                    self._n_flush, self._cur = 0, 0
+                    self._rs_sync = SyncWords(self.dev, channel=2)
+                    self._sq_scratch = torch.zeros(1, dtype=torch.float32, device=self.dev)
+        if frozen:
+            self.gbuf = None
+        elif self.fused:
+            self.gbuf = self._gbufs[0][0]
+        else:
+            self.gbuf = torch.zeros(slot_numel, dtype=self.dtype, device=self.dev)
         self._resident = [None, None]  # layer index whose gathered weights a slot holds (or is receiving), or None
         self._inflight = [None, None]  # per slot: (layer, async work handle, send buffer) of a gather not yet waited for
         self._last_idx = None
@@ -137,13 +192,19 @@ class StreamShardEngine:
                 for p, v in zip(ls.params, views):
                     v.copy_(p.data)   # layers two apart share the slot: the slice is taken right below
                     p.data = v        # the original storage is released here
+            if self.fused:
+                ls.shard16.copy_(slot[lo:lo + per])
             if frozen:
-                ls.master = slot[lo:lo + per].clone()  # the slice in the model's dtype is all a frozen model needs
+                # the slice in the model's dtype is all a frozen model needs
+                ls.master = ls.shard16 if self.fused else slot[lo:lo + per].clone()
                 continue
             ls.master = slot[lo:lo + per].to(torch.float32, copy=True)  # fp32 owned slice; the compute-dtype copy is made when gathering
             ls.exp_avg = torch.zeros(per, dtype=torch.float32, device=self.dev)
             ls.exp_avg_sq = torch.zeros(per, dtype=torch.float32, device=self.dev)
             ls.grad_acc = torch.zeros(per, dtype=self.grad_dtype, device=self.dev)
+        if self.fused:  # every owner's slices are in place before anybody pulls
+            torch.cuda.synchronize(self.dev)
+            td.barrier(group=self.group)
         # ---- everything outside the layers: whole on every rank, zero-2 style state ----
         if frozen:  # embeddings / norm / lm_head of a frozen model stay as they are (whole, own storage)
             if meta:  # same generator and order as the trainable path below: a frozen copy starts equal to the policy
@@ -220,6 +281,17 @@ class StreamShardEngine:
     def _start_gather(self, idx: int):
         ls = self.layers[idx]
         self._wait_slot(ls.slot)
+        if self.fused:
+            from ..ops import cuda as K
+
+            # the slot is free once everything queued so far on this stream (its previous tenant's kernels) has run
+            self._gstream.wait_event(torch.cuda.current_stream().record_event())
+            with torch.cuda.stream(self._gstream):
+                K.shard_pull(self.arena, ls.shard16_off, ls.numel // self.world, self.slots[ls.slot], ctas=self._pull_ctas)
+                done = self._gstream.record_event()
+            self._inflight[ls.slot] = (idx, _EventWork(done), None)
+            self._resident[ls.slot] = idx
+            return
         src = ls.master.to(self.dtype)
         work = td.all_gather_into_tensor(self.slots[ls.slot][:ls.numel], src, group=self.group, async_op=True)
         self._inflight[ls.slot] = (idx, work, src)  # src must outlive the collective
@@ -259,9 +331,30 @@ class StreamShardEngine:
         return buf[self.rank * per:(self.rank + 1) * per] / self.world
 
     def _flush_layer(self, ls: _LayerShard):
-        ls.grad_acc.add_(self._reduce_to_shard(self.gbuf, ls.numel).to(ls.grad_acc.dtype))
+        if self.fused and ls.grad_acc.dtype == torch.float32:
+            from ..ops import cuda as K
+
+            k, per = self._cur, ls.numel // self.world
+            self._rstream.wait_event(torch.cuda.current_stream().record_event())  # the layer's gradients are in the buffer
+            with torch.cuda.stream(self._rstream):
+                K.rs_reduce_accum(self.arena, self._gbufs[k][1], True, self.rank * per, per, ls.grad_acc, self._sq_scratch,
+                                  self._rs_sync, max_ctas=self._reduce_ctas)
+                self._gbuf_done[k] = self._rstream.record_event()
+            self._n_flush += 1
+        else:
+            ls.grad_acc.add_(self._reduce_to_shard(self.gbuf, ls.numel).to(ls.grad_acc.dtype))
         ls.arrived = 0
         self._pending = None
+
+    def _next_gbuf(self):
+        """Fused path: the gradient buffer of the layer whose first gradient has just arrived.  Its previous contents
+        (three reductions ago) may be overwritten once this rank's reduction of two layers ago has run: that kernel's
+        entry barrier is passed only after every rank has finished the reduction before it."""
+        k = self._n_flush % 3
+        ev = self._gbuf_done[(k + 1) % 3]
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+        self._cur, self.gbuf = k, self._gbufs[k][0]
 
     def _install_hooks(self):
         for ls in self.layers:
@@ -273,6 +366,8 @@ class StreamShardEngine:
                     if pend is not None and pend is not ls:
                         self._flush_layer(pend)  # the previous layer had parameters without a gradient
                     if ls.arrived == 0:
+                        if self.fused:
+                            self._next_gbuf()
                         self.gbuf[:ls.numel].zero_()  # padding and parameters without a gradient contribute zero
                         self._pending = ls
                     self.gbuf[o:o + param.numel()].copy_(param.grad.reshape(-1))
@@ -325,8 +420,17 @@ class StreamShardEngine:
             adamw_flat(master, grad, m, v, self.step_count, lr, b1, b2, self.eps,
                        self.weight_decay if not no_decay else 0.0, scale, shadow)
 
+    def _join_side_streams(self):
+        for slot in (0, 1):
+            self._wait_slot(slot)
+        if self.fused and not self.frozen:
+            torch.cuda.current_stream().wait_stream(self._rstream)
+
     def step(self, lr: float, max_grad_norm: float | None = None) -> torch.Tensor:
         self.step_count += 1
+        # fused path: nothing of this rank still reads a peer's slices or adds into an accumulator when the norm
+        # all-reduce below runs, and no rank updates its slices before every rank has passed that all-reduce
+        self._join_side_streams()
         rest_g = self._reduce_to_shard(self.rest_grad, self.rest_numel) if self.rest_numel else None
         sq = torch.zeros((), dtype=torch.float32, device=self.dev)
         for ls in self.layers:
@@ -342,13 +446,16 @@ class StreamShardEngine:
         for ls in self.layers:
             per = ls.numel // self.world
             g = ls.grad_acc if ls.grad_acc.dtype == torch.float32 else ls.grad_acc.float()
-            self._adamw(ls.master, g, ls.exp_avg, ls.exp_avg_sq, None, lr, scale, ls.no_decay, self.rank * per)
+            self._adamw(ls.master, g, ls.exp_avg, ls.exp_avg_sq, ls.shard16 if self.fused else None, lr, scale,
+                        ls.no_decay, self.rank * per)
         if rest_g is not None:
             sh = self.rest_flat[self.rest_lo:self.rest_hi]
             shadow = None if self.dtype == torch.float32 else sh
             self._adamw(self.rest_master, rest_g, self.rest_exp_avg, self.rest_exp_avg_sq, shadow, lr, scale,
                         self.rest_no_decay, self.rest_lo)
             self._gather_into(self.rest_flat, sh.clone())
+        elif self.fused:
+            td.all_reduce(sq, group=self.group)  # closing fence: every rank's new slices are written before anyone pulls
         self._invalidate()
         return norm
 
@@ -372,6 +479,7 @@ class StreamShardEngine:
         self.rest_exp_avg.copy_(sd["rest"]["exp_avg"])
         self.rest_exp_avg_sq.copy_(sd["rest"]["exp_avg_sq"])
         self._publish_rest()
+        self._publish_shards()
         self._invalidate()
 
     @torch.no_grad()
@@ -397,7 +505,20 @@ class StreamShardEngine:
         for k, dst in (("master", self.rest_master), ("exp_avg", self.rest_exp_avg), ("exp_avg_sq", self.rest_exp_avg_sq)):
             recut([s["rest"][k] for s in shards], self.rest_numel, self.rest_lo, self.rest_hi, dst)
         self._publish_rest()
+        self._publish_shards()
         self._invalidate()
+
+    def _publish_shards(self):
+        """Fused path: the fp32 slices were replaced outside the optimizer step (checkpoint load): refresh the bf16
+        slices the peers pull from, and make sure nobody pulls before every rank has done so."""
+        if not self.fused:
+            return
+        self._join_side_streams()
+        if not self.frozen:
+            for ls in self.layers:
+                ls.shard16.copy_(ls.master)
+        torch.cuda.synchronize(self.dev)
+        td.barrier(group=self.group)
 
     def _publish_rest(self):
         sh = self.rest_flat[self.rest_lo:self.rest_hi]
@@ -427,7 +548,9 @@ class StreamShardEngine:
 
         lm = getattr(self.model, "language_model", self.model)
         load_hf_state_dict(lm, hf_state, strict=strict, after_layer=reslice)
-        self.refresh_master_from_params()
+        if not self.frozen:
+            self.refresh_master_from_params()
+        self._publish_shards()
 
     @torch.no_grad()
     def export_weights(self, target: nn.Module):

@@ -6,8 +6,9 @@ local heads only), MLP columns [r*I/tp, (r+1)*I/tp); embeddings, norms and the l
 Fused path (default; batches of at most 128 rows, 128-row-aligned slices): every decode linear is the
 weight-streaming tcgen05 GEMM on tile-major weight slices (the repack that tensor parallelism needs anyway writes
 them tile-major, so each 16 KB weight tile is one sequential DRAM burst).  The two row-parallel GEMMs of a layer
-(O-proj, down-proj) are fused with their all-reduce: the epilogue adds the fp32 partial sums into the accumulator
-of EVERY rank over NVLink (red.global on peer pointers) and bumps an arrival counter on every rank; the consumer
+(O-proj, down-proj) are fused with their all-reduce: the stream-K partial sums meet in a local staging buffer and
+the warp that completes a 32-feature quarter of a slab adds it once into the accumulator of EVERY rank over NVLink
+(16-byte vector red.global on peer pointers) and bumps an arrival counter on every rank; the consumer
 (residual add + RMSNorm) waits on its own counter, reads one local buffer and clears it.  No rank reads a peer's
 memory, no separate all-reduce kernel runs and no barrier has two directions: a rank only ever waits for "all
 partial sums have landed here".  Accumulator reuse needs no extra handshake: a peer can reach the next GEMM on the
@@ -89,8 +90,9 @@ class TPRolloutEngine(RolloutEngine):
             self._acc_qkv = torch.zeros(B, ql + 2 * kl, dtype=torch.float32, device=dev)
             self._act_buf = torch.empty(B, il, dtype=dt, device=dev)
             self._logits_buf = torch.empty(B, cfg.vocab_size, dtype=dt, device=dev)
-            self._target_o = tp * K.decode_gemm_ctas(B, H, ql)
-            self._target_d = tp * K.decode_gemm_ctas(B, H, il)
+            self._stage = torch.zeros(B, H, dtype=torch.float32, device=dev)  # both GEMMs: they never overlap
+            self._slab_ctr = torch.zeros(4 * (-(-H // 128)), dtype=torch.int32, device=dev)
+            self._target_o = self._target_d = tp * K.decode_gemm_arrivals(H)
         else:
             for _ in cfg_layers(cfg):
                 self.w.append({
@@ -187,10 +189,10 @@ class TPRolloutEngine(RolloutEngine):
                                 self.hk_local, cfg.head_dim, cfg.rope_theta, v_transposed=self.attn_tc)
             self._decode_attention(li, scale)
             K.decode_gemm(self.attn_buf.view(self.max_seqs, -1), w["o"], y32=self._acc_o, tiled_shape=(H, ql),
-                          peers=(self._peer_acc_o, self._arrive_o))
+                          peers=(self._peer_acc_o, self._arrive_o, self._stage, self._slab_ctr))
             h = K.add_rmsnorm_f32_wait(x, self._acc_o, l.post_attention_layernorm, eps, self._arrive_o[0], self._target_o, loc)
             act = K.decode_gemm(h, w["gu"], out=self._act_buf, swiglu=True, tiled_shape=(2 * il, H))
-            K.decode_gemm(act, w["down"], y32=self._acc_d, tiled_shape=(H, il), peers=(self._peer_acc_d, self._arrive_d))
+            K.decode_gemm(act, w["down"], y32=self._acc_d, tiled_shape=(H, il), peers=(self._peer_acc_d, self._arrive_d, self._stage, self._slab_ctr))
         hN = K.add_rmsnorm_f32_wait(x, self._acc_d, m.norm, eps, self._arrive_d[0], self._target_d, loc + 16)
         return K.decode_gemm(hN, m.lm_head_weight, out=self._logits_buf)
 
