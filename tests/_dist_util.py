@@ -67,10 +67,10 @@ def greedy_gaps(model, prompt, tokens):
 
     import torch
 
-    m32 = copy.deepcopy(model).float()
-    ids = torch.tensor([list(prompt) + list(tokens)], device=model.device)
+    m32 = copy.deepcopy(model).float().cpu()  # the plain fp32 path of the model
+    ids = torch.tensor([list(prompt) + list(tokens)])
     with torch.no_grad():
         logits = m32(input_ids=ids).logits[0].float()
     steps = logits[len(prompt) - 1:len(prompt) - 1 + len(tokens)]
-    chosen = steps.gather(1, torch.tensor(list(tokens), device=steps.device)[:, None])[:, 0]
+    chosen = steps.gather(1, torch.tensor(list(tokens))[:, None])[:, 0]
     return (steps.max(dim=1).values - chosen).tolist()

@@ -70,6 +70,9 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--baseline", action="store_true", help="also time the library (cuBLAS / eager) path")
+    ap.add_argument("--tp", type=int, default=1, help="decode_gemm: the shapes of one rank of a tensor-parallel group of "
+                    "this size; the row-parallel GEMMs then run their fused all-reduce form against a local stand-in "
+                    "for the peer's accumulator")
     a = ap.parse_args()
     from ..ops import cuda as K
 
@@ -154,13 +157,23 @@ def main():
         # the weight-streaming GEMMs of one Qwen2.5-7B decode step at batch a.batch: cuBLAS vs the stream-K kernel,
         # each alone with a cold L2, then the four back to back (as in a layer) with and without dependent launch
         rows = []
-        shapes = (("qkv", 4608, 3584, "acc"), ("o_proj", 3584, 3584, "acc"), ("gate_up", 37888, 3584, "swiglu"),
-                  ("down", 3584, 18944, "acc"), ("lm_head", a.v, 3584, "store"))
+        tp = a.tp
+        shapes = (("qkv", 4608 // tp, 3584, "acc"), ("o_proj", 3584, 3584 // tp, "acc" if tp == 1 else "allreduce"),
+                  ("gate_up", 37888 // tp, 3584, "swiglu"), ("down", 3584, 18944 // tp, "acc" if tp == 1 else "allreduce"),
+                  ("lm_head", a.v, 3584, "store"))
         bufs = []
         for name, N, Kd, kind in shapes:
             x = (torch.randn(a.batch, Kd, device=dev) * 0.5).to(torch.bfloat16)
             w = (torch.randn(N, Kd, device=dev) / Kd ** 0.5).to(torch.bfloat16)
-            if kind == "acc":
+            if kind == "allreduce":
+                y32, peer = torch.zeros(a.batch, N, device=dev), torch.zeros(a.batch, N, device=dev)
+                stage = torch.zeros(a.batch, N, device=dev)
+                ctr = torch.zeros(4 * ((N + 127) // 128), dtype=torch.int32, device=dev)
+                arr = torch.zeros(32, dtype=torch.int32, device=dev)
+                own = lambda x=x, w=w, y32=y32, peer=peer, stage=stage, ctr=ctr, arr=arr: K.decode_gemm(
+                    x, w, y32=y32, peers=([peer.data_ptr()] * (tp - 1), [arr.data_ptr()] + [arr[16:].data_ptr()] * (tp - 1),
+                                          stage, ctr))
+            elif kind == "acc":
                 y32 = torch.zeros(a.batch, N, device=dev)
                 own = lambda x=x, w=w, y32=y32: K.decode_gemm(x, w, y32=y32)
             elif kind == "swiglu":
@@ -198,7 +211,7 @@ def main():
             K.set_pdl(was)
             res[label + "_28_layers_ms"] = round(ms, 3)
             res[label + "_frac_of_copy_bw"] = round(total / ms / 1e6 / hbm, 3)
-        out.update(batch=a.batch, gemms=rows, chain=res)
+        out.update(batch=a.batch, tp=tp, gemms=rows, chain=res)
     elif a.kernel == "fa":
         # varlen attention, forward and forward + backward: this library's tcgen05 kernels against flash-attn's
         # flash_attn_varlen_func (when importable) on two packings: one 8192-token pack of documents with log-uniform

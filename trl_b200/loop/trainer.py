@@ -345,6 +345,17 @@ class Trainer:
     def _create_engine(self) -> TrainEngine:
         a = self.args
         mode = a.shard_mode
+        if getattr(a, "ep_size", 1) > 1:
+            if a.ep_size != D.world_size():
+                raise ValueError(f"ep_size={a.ep_size} must equal the number of processes ({D.world_size()})")
+            if mode in ("full_shard", "full_shard_stream"):
+                raise ValueError("expert parallelism goes with shard_mode ddp, zero1 or zero2: the experts are already "
+                                 "split over the ranks, the rest of the model is small")
+            lm = getattr(self.model, "language_model", self.model)
+            if getattr(lm, "ep_world", 1) == 1:
+                from ..parallel.expert_parallel import shard_experts
+
+                shard_experts(self.model, max_tokens=int(os.environ.get("TRL_B200_EP_MAX_TOKENS", "16384")))
         if mode == "full_shard" and D.world_size() > 1:
             from ..parallel.symm import symmetric_available
 
@@ -652,6 +663,12 @@ class Trainer:
         if self.engine is not None and hasattr(self.engine, "streamed_hf_state_dict"):
             sd = self.engine.streamed_hf_state_dict(to_cpu=self.args.should_save)
             return sd if self.args.should_save else None
+        lm = getattr(self.model, "language_model", self.model)
+        if getattr(lm, "ep_world", 1) > 1:  # expert-parallel model: the experts are gathered layer by layer
+            from ..parallel.expert_parallel import ep_hf_state_dict
+
+            sd = ep_hf_state_dict(self.model, to_cpu=self.args.should_save)
+            return sd if self.args.should_save else None
         return None
 
     def save_model(self, output_dir: str | None = None, _internal_call: bool = False):
@@ -686,7 +703,7 @@ class Trainer:
             except Exception:  # a missing template engine must not lose the checkpoint
                 pass
         if not a.save_only_model:
-            sharded = self.engine.sharded
+            sharded = getattr(self.engine, "per_rank_state", self.engine.sharded)
             if sharded or a.should_save:
                 name = f"optimizer_rank{D.rank()}.pt" if sharded else "optimizer.pt"
                 torch.save(self.engine.optimizer_state_dict(), os.path.join(folder, name))
@@ -744,9 +761,10 @@ class Trainer:
             old = TrainerState.load_from_json(sp)
             old.is_world_process_zero, old.is_local_process_zero = self.state.is_world_process_zero, self.state.is_local_process_zero
             self.state = old
-        op = os.path.join(folder, f"optimizer_rank{D.rank()}.pt" if self.engine.sharded else "optimizer.pt")
+        per_rank = getattr(self.engine, "per_rank_state", self.engine.sharded)
+        op = os.path.join(folder, f"optimizer_rank{D.rank()}.pt" if per_rank else "optimizer.pt")
         saved = sorted(f for f in os.listdir(folder) if re.fullmatch(r"optimizer(_rank\d+)?\.pt", f))
-        expect = [f"optimizer_rank{r}.pt" for r in range(D.world_size())] if self.engine.sharded else ["optimizer.pt"]
+        expect = [f"optimizer_rank{r}.pt" for r in range(D.world_size())] if per_rank else ["optimizer.pt"]
         if saved and sorted(expect) != saved and hasattr(self.engine, "load_optimizer_state_resharded"):
             # elastic resume: the checkpoint was written with another world size or shard mode.  Every rank reads all
             # optimizer files and keeps the slices it owns now.

@@ -148,6 +148,10 @@ class TrainingArguments:
                 "(multi_gpu, zero1/2/3, fsdp1/2) map onto these.  full_shard keeps a full-size buffer per layer and "
                 "gathers once per optimizer step (fast, the model must fit one GPU in bf16); full_shard_stream holds "
                 "1 / world of every layer and gathers layer by layer (needs gradient_checkpointing)."})
+    ep_size: int = field(default=1, metadata={
+        "help": "Expert parallelism for mixture-of-experts models: 1 keeps every expert on every rank; a value equal to "
+                "the number of processes gives each rank num_experts / ep_size experts (tokens travel to the experts; "
+                "data parallelism for everything else).  Works with shard_mode ddp, zero1 and zero2."})
     activation_offloading: bool = False
 
     def __post_init__(self):

@@ -179,8 +179,13 @@ class DecoderLayer(nn.Module):
     def mlp_block(self, x, ctx: SeqCtx):
         c = self.cfg
         if c.is_moe:
-            out, probs, idx = ops.moe_mlp(x, self.router, self.experts_gate_up, self.experts_down,
-                                          c.num_experts_per_tok, c.norm_topk_prob)
+            ep = getattr(self, "ep", None)
+            if ep is not None:  # expert parallel (parallel/expert_parallel.py:shard_experts): this rank holds a slice
+                w, idx, probs = ops.moe_router(x, self.router, c.num_experts_per_tok, c.norm_topk_prob)
+                out = ep(x, self.experts_gate_up, self.experts_down, w, idx)
+            else:
+                out, probs, idx = ops.moe_mlp(x, self.router, self.experts_gate_up, self.experts_down,
+                                              c.num_experts_per_tok, c.norm_topk_prob)
             ctx.router_records.append((probs, idx))
             return out
         gu = ops.linear(x, self.gate_up_proj)

@@ -60,10 +60,16 @@ def to_hf_state_dict(model, include_lora: bool = False, before_layer=None, copy_
         if c.is_moe:
             I = c.moe_intermediate_size
             sd[p + "mlp.gate.weight"] = l.router.detach()
+            # an expert-parallel layer holds a slice of the experts; ``_ep_full`` is set (by the gather that runs in
+            # ``before_layer``) to the complete tensors while the layer is exported
+            gu_all, dn_all = getattr(l, "_ep_full", None) or (l.experts_gate_up.detach(), l.experts_down.detach())
+            if gu_all.shape[0] != c.num_experts:
+                raise RuntimeError("expert-parallel model: export through parallel.expert_parallel.ep_hf_state_dict "
+                                   "(a collective that gathers the experts layer by layer)")
             for e in range(c.num_experts):
-                sd[p + f"mlp.experts.{e}.gate_proj.weight"] = l.experts_gate_up.detach()[e, :I]
-                sd[p + f"mlp.experts.{e}.up_proj.weight"] = l.experts_gate_up.detach()[e, I:]
-                sd[p + f"mlp.experts.{e}.down_proj.weight"] = l.experts_down.detach()[e]
+                sd[p + f"mlp.experts.{e}.gate_proj.weight"] = gu_all[e, :I]
+                sd[p + f"mlp.experts.{e}.up_proj.weight"] = gu_all[e, I:]
+                sd[p + f"mlp.experts.{e}.down_proj.weight"] = dn_all[e]
         else:
             I = c.intermediate_size
             if fused_on_disk:
@@ -126,14 +132,20 @@ def load_hf_state_dict(model, sd: dict[str, torch.Tensor], strict: bool = True, 
             I = c.moe_intermediate_size
             put(l.router, take(p + "mlp.gate.weight"))
             fused_gu = take(p + "mlp.experts.gate_up_proj", required=False)
+            # expert-parallel layers keep experts [e0, e0 + n_loc) only; the other experts' tensors are skipped
+            e0, n_loc = getattr(l, "ep_first_expert", 0), l.experts_gate_up.shape[0]
             if fused_gu is not None:  # transformers>=5 in-memory fused layout
-                put(l.experts_gate_up, fused_gu)
-                put(l.experts_down, take(p + "mlp.experts.down_proj"))
+                put(l.experts_gate_up, fused_gu[e0:e0 + n_loc])
+                put(l.experts_down, take(p + "mlp.experts.down_proj")[e0:e0 + n_loc])
             else:
                 for e in range(c.num_experts):
-                    put(l.experts_gate_up[e, :I], take(p + f"mlp.experts.{e}.gate_proj.weight"))
-                    put(l.experts_gate_up[e, I:], take(p + f"mlp.experts.{e}.up_proj.weight"))
-                    put(l.experts_down[e], take(p + f"mlp.experts.{e}.down_proj.weight"))
+                    if e0 <= e < e0 + n_loc:
+                        put(l.experts_gate_up[e - e0, :I], take(p + f"mlp.experts.{e}.gate_proj.weight"))
+                        put(l.experts_gate_up[e - e0, I:], take(p + f"mlp.experts.{e}.up_proj.weight"))
+                        put(l.experts_down[e - e0], take(p + f"mlp.experts.{e}.down_proj.weight"))
+                    else:
+                        for leaf in ("gate_proj", "up_proj", "down_proj"):
+                            take(p + f"mlp.experts.{e}.{leaf}.weight", required=False)
         else:
             I = c.intermediate_size
             fused_gate_up = take(p + "mlp.gate_up_proj.weight", required=False)

@@ -142,6 +142,7 @@ def moe_mlp(hidden, router_w, gate_up_w, down_w, top_k, norm_topk_prob):
     return out, probs, idx
 
 
+moe_router = _ref.moe_router
 selective_log_softmax = _ref.selective_log_softmax
 entropy_from_logits = _ref.entropy_from_logits
 

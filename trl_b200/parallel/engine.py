@@ -16,6 +16,11 @@ Modes (they replace the reference's accelerate profiles, trl/accelerate_configs/
 ``full_shard`` parameters live as 1/world shards between uses; see
                :mod:`trl_b200.parallel.fullshard`, which reuses the buckets below.
 
+Expert-parallel parameters (flagged ``_ep_local`` by ``parallel.expert_parallel.shard_experts``) differ between the
+ranks by construction: they go to *local* buckets whose gradients are not reduced (the dispatch already brought every
+rank's tokens to the expert; the gradient is scaled by 1 / world like the averaged ones), whose optimizer state is
+whole on the owner, and whose squared norm enters the global gradient norm once.
+
 On GPUs the reduce-scatter, the fp32 cast/scale, the norm partials and the
 AdamW update are the ``rs_adamw`` kernels over symmetric memory
 (:mod:`trl_b200.parallel.symm`); the NCCL calls below are the measured baseline
@@ -57,6 +62,7 @@ class Bucket:
     exp_avg: torch.Tensor = None
     exp_avg_sq: torch.Tensor = None
     no_decay_ranges: list = field(default_factory=list)
+    local: bool = False  # expert-parallel parameters: owned whole by this rank, never reduced or gathered
 
     def shard(self, t: torch.Tensor) -> torch.Tensor:
         return t[self.lo:self.hi]
@@ -131,7 +137,9 @@ class TrainEngine:
             if not p.requires_grad or id(p) in seen:
                 continue
             seen.add(id(p))
-            groups.setdefault((bucket_of(n), p.dtype), []).append((n, p))
+            bname = bucket_of(n) + (".ep" if getattr(p, "_ep_local", False) else "")
+            groups.setdefault((bname, p.dtype), []).append((n, p))
+        is_local = {key: all(getattr(p, "_ep_local", False) for _, p in items) for key, items in groups.items()}
         self.buckets: list[Bucket] = []
         unit = self.world * _ALIGN
         if self.use_symm:
@@ -141,7 +149,9 @@ class TrainEngine:
 
             gd0 = grad_dtype or torch.float32
             tot_p = tot_g = 0
-            for (_, dtype), items in groups.items():
+            for (bn, dtype), items in groups.items():
+                if is_local[(bn, dtype)]:
+                    continue
                 cur = sum((p.numel() + 15) // 16 * 16 for _, p in items)
                 numel = (cur + unit - 1) // unit * unit
                 tot_p += numel * torch.empty(0, dtype=dtype).element_size() + 256
@@ -158,7 +168,7 @@ class TrainEngine:
                 cur += (p.numel() + 15) // 16 * 16
             numel = (cur + unit - 1) // unit * unit
             dev = items[0][1].device
-            b = Bucket(bname, [n for n, _ in items], [p for _, p in items], offs, numel)
+            b = Bucket(bname, [n for n, _ in items], [p for _, p in items], offs, numel, local=is_local[(bname, dtype)])
             b.flat_param = self._alloc("param", b, numel, dtype, dev)
             for (n, p), o in zip(items, offs):
                 b.flat_param[o:o + p.numel()].view_as(p).copy_(p.data)
@@ -167,7 +177,7 @@ class TrainEngine:
                     b.no_decay_ranges.append((o, o + p.numel()))
             gd = grad_dtype or torch.float32
             b.flat_grad = self._alloc("grad", b, numel, gd, dev)
-            if self.sharded:
+            if self.sharded and not b.local:
                 per = numel // self.world
                 b.lo, b.hi = self.rank * per, (self.rank + 1) * per
             else:
@@ -187,7 +197,7 @@ class TrainEngine:
             self.buckets.append(b)
 
     def _alloc(self, kind, bucket, numel, dtype, dev):
-        if not self.use_symm:
+        if not self.use_symm or bucket.local:
             return torch.zeros(numel, dtype=dtype, device=dev)
         t, off = self._arenas[kind].carve(numel, dtype)
         self._offsets[(kind, bucket.name, str(bucket.params[0].dtype))] = off
@@ -232,6 +242,9 @@ class TrainEngine:
         """Average gradients over ranks; returns this rank's (shard of the) reduced gradient."""
         if self.world == 1:
             return b.flat_grad
+        if b.local:  # every rank's tokens already reached the expert: only the 1 / world of the averaged objective
+            b.flat_grad /= self.world
+            return b.flat_grad
         if self.sharded:
             out = torch.empty(b.hi - b.lo, dtype=b.flat_grad.dtype, device=b.flat_grad.device)
             if b.flat_grad.is_cuda:
@@ -251,10 +264,16 @@ class TrainEngine:
             return self._step_fused(lr, max_grad_norm)
         reduced = [self._reduce(b) for b in self.buckets]
         sq = torch.zeros((), dtype=torch.float32, device=reduced[0].device)
-        for g in reduced:
-            sq += g.float().pow(2).sum()
-        if self.sharded:
-            D.all_reduce(sq, "sum", group=self.group)
+        sq_local = torch.zeros_like(sq)  # parts every rank holds a different piece of: shards, expert-parallel buckets
+        for b, g in zip(self.buckets, reduced):
+            part = g.float().pow(2).sum()
+            if self.sharded or (b.local and self.world > 1):
+                sq_local += part
+            else:
+                sq += part
+        if self.sharded or any(b.local for b in self.buckets) and self.world > 1:
+            D.all_reduce(sq_local, "sum", group=self.group)
+        sq = sq + sq_local
         norm = sq.sqrt()
         scale = 1.0
         if max_grad_norm is not None and max_grad_norm > 0:
@@ -268,25 +287,49 @@ class TrainEngine:
                            self.weight_decay, gs, shadow)
             else:  # biases / norm weights inside the bucket are exempt from decay
                 self._masked_adamw(b, g, lr, gs, shadow)
-            if self.sharded:
+            if self.sharded and not b.local:
                 td.all_gather_into_tensor(b.flat_param, b.flat_param[b.lo:b.hi].clone(), group=self.group)
         return norm
+
+    def align_ranks(self):
+        """Stream-ordered meeting of the ranks through the backend (one element).  The cross-rank waits inside the comm
+        kernels give up after a second, which is right for a peer that is gone but not for one that is merely late:
+        ranks reach an optimizer step seconds apart when their micro-batches differ in length.  After this call they
+        are within a launch of each other."""
+        if self.world > 1 and self.use_symm:
+            if not hasattr(self, "_tick"):
+                self._tick = torch.zeros(1, dtype=torch.float32, device=self.buckets[0].flat_param.device)
+            td.all_reduce(self._tick, group=self.group)
 
     def _step_fused(self, lr: float, max_grad_norm: float | None) -> torch.Tensor:
         """Optimizer step on the comm kernels: per bucket a reduce-scatter that reads the peers' gradient
         buffers in place (fp32 cast, 1/world, norm partial), one exchange of the norm partials, then AdamW
-        whose bf16 output is stored into every rank's parameter replica.  No NCCL call, no host sync."""
+        whose bf16 output is stored into every rank's parameter replica.  No host sync; the only library
+        collective is the one-element meeting in front (see ``align_ranks``)."""
         from ..ops import cuda as K
 
+        self.align_ranks()
         ga, pa = self._arenas["grad"], self._arenas["param"]
         self._sumsq.zero_()
         for b, red in zip(self.buckets, self._reduced):
+            if b.local:  # expert-parallel bucket: scale, add its squared norm to this rank's partial
+                red.copy_(b.flat_grad).div_(self.world)
+                self._sumsq += red.pow(2).sum()
+                continue
             key = (b.name, str(b.params[0].dtype))
             K.rs_reduce(ga, self._offsets[("grad",) + key], b.flat_grad.dtype == torch.bfloat16, b.lo, b.hi - b.lo, red,
                         self._sumsq, self._sync, use_multimem=self.use_multimem)
         K.norm_allreduce(ga, self._norm_off, self._sumsq, max_grad_norm or 0.0, self._norm, self._clip, self._sync)
         b1, b2 = self.betas
         for b, red in zip(self.buckets, self._reduced):
+            if b.local:
+                shadow = None if b.flat_param.dtype == torch.float32 else b.flat_param
+                if b.decay_mask is None:
+                    adamw_flat(b.master, red, b.exp_avg, b.exp_avg_sq, self.step_count, lr, b1, b2, self.eps,
+                               self.weight_decay, self._clip[0], shadow)
+                else:
+                    self._masked_adamw(b, red, lr, self._clip[0], shadow)
+                continue
             key = (b.name, str(b.params[0].dtype))
             K.adamw_bcast(pa, self._offsets[("param",) + key], b.lo, b.hi - b.lo, b.master, red, b.exp_avg, b.exp_avg_sq,
                           self.step_count, lr, b1, b2, self.eps, self.weight_decay, self._clip, self._sync,
@@ -306,7 +349,7 @@ class TrainEngine:
             return "skipped: fused collectives not in use"
         from ..ops import cuda as K
 
-        b = self.buckets[0]
+        b = next(bk for bk in self.buckets if not bk.local)
         key = (b.name, str(b.params[0].dtype))
         n = b.flat_grad.numel()
         idx = torch.arange(n, device=b.flat_grad.device, dtype=torch.float32)
@@ -322,7 +365,7 @@ class TrainEngine:
                     b.hi - b.lo, got, self._sumsq, self._sync, use_multimem=self.use_multimem)
         torch.cuda.synchronize()
         err = (got - want).abs().max()
-        sums = torch.stack([bk.flat_param.float().sum() for bk in self.buckets])
+        sums = torch.stack([bk.flat_param.float().sum() for bk in self.buckets if not bk.local])
         hi_, lo_ = sums.clone(), sums.clone()
         td.all_reduce(hi_, op=td.ReduceOp.MAX, group=self.group)
         td.all_reduce(lo_, op=td.ReduceOp.MIN, group=self.group)
@@ -344,12 +387,17 @@ class TrainEngine:
         if shadow is not None:
             shadow.copy_(b.master)
 
+    @property
+    def per_rank_state(self) -> bool:
+        """Whether every rank has optimizer state of its own to save (shards, or expert-parallel buckets)."""
+        return self.sharded or (self.world > 1 and any(b.local for b in self.buckets))
+
     # ---- (de)serialisation of optimizer state -------------------------------------
     def optimizer_state_dict(self) -> dict:
         return {
             "step": self.step_count, "mode": self.mode, "world": self.world, "rank": self.rank,
             "buckets": {b.name + "|" + str(b.flat_param.dtype): {
-                "names": b.names, "lo": b.lo, "hi": b.hi,
+                "names": b.names, "lo": b.lo, "hi": b.hi, "local": b.local,
                 "master": b.master.detach().cpu().clone(), "exp_avg": b.exp_avg.cpu(), "exp_avg_sq": b.exp_avg_sq.cpu()}
                 for b in self.buckets},
         }
@@ -375,6 +423,16 @@ class TrainEngine:
             if any(key not in s["buckets"] for s in shards):
                 raise ValueError(f"the checkpoint's optimizer state has no bucket {key!r}: it was written by an engine with "
                                  f"another bucket layout (mode {shards[0].get('mode')!r}, this run {self.mode!r})")
+            if b.local:
+                # expert-parallel buckets are whole on their owner: they survive a change of shard mode, not of world size
+                mine = [s for s in shards if s.get("rank") == self.rank and s.get("world") == self.world]
+                if len(mine) != 1:
+                    raise ValueError("expert-parallel optimizer state can only be resumed with the same number of ranks")
+                for k, dst in (("master", b.master), ("exp_avg", b.exp_avg), ("exp_avg_sq", b.exp_avg_sq)):
+                    dst.copy_(mine[0]["buckets"][key][k].to(dst.dtype))
+                if b.master.data_ptr() != b.flat_param.data_ptr():
+                    b.flat_param.copy_(b.master.to(b.flat_param.dtype))
+                continue
             parts = sorted((s["buckets"][key] for s in shards), key=lambda x: x["lo"])
             if parts[0]["names"] != b.names:
                 raise ValueError(f"bucket {b.name}: the checkpoint holds other parameters ({parts[0]['names'][:3]}...)")

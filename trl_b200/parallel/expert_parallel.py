@@ -16,7 +16,11 @@ The reference reaches expert parallelism through DeepSpeed / accelerate sharding
 (trl/accelerate_configs/*.yaml); it has no fused path.
 
 Backward (training) moves rows with ``all_to_all_single`` and uses library GEMMs per expert; the gate/up
-pre-activations are recomputed with the fused kernel."""
+pre-activations are recomputed with the fused kernel.
+
+``shard_experts(model, group)`` wires the block into a model (expert slices as parameters flagged ``_ep_local``,
+``layer.ep`` called by ``DecoderLayer.mlp_block``); ``HostExpertParallelMoE`` is the same block over the backend's
+all-to-all for CPU / gloo runs and shapes outside the kernels; ``ep_hf_state_dict`` gathers the experts for saving."""
 from __future__ import annotations
 
 import ctypes
@@ -185,3 +189,139 @@ class _EpMoeFn(torch.autograd.Function):
         d_x = exchange(d_x_in, recv, send)
         d_hidden = torch.zeros(hidden.shape, dtype=torch.float32, device=d_out.device).index_add_(0, tok, d_x.float())
         return d_hidden.to(hidden.dtype), d_gu_w, d_dn_w, d_topk.view_as(topk_w).to(topk_w.dtype), None, None
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Host path: the same block through the backend's all-to-all (gloo on CPU, NCCL where the symmetric kernels do not
+# apply: fp32, tiny hidden sizes).  Everything is ordinary autograd, so it is also the oracle of the fused path.
+# ---------------------------------------------------------------------------------------------------------------------
+class _AllToAllRows(torch.autograd.Function):
+    """Rows exchanged with per-rank counts; the backward pass sends the gradients the other way."""
+
+    @staticmethod
+    def forward(ctx, x, send, recv, group):
+        ctx.send, ctx.recv, ctx.group = send, recv, group
+        out = torch.empty((sum(recv),) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        td.all_to_all_single(out, x.contiguous(), list(recv), list(send), group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        d = torch.empty((sum(ctx.send),) + tuple(g.shape[1:]), dtype=g.dtype, device=g.device)
+        td.all_to_all_single(d, g.contiguous(), list(ctx.send), list(ctx.recv), group=ctx.group)
+        return d, None, None, None
+
+
+class HostExpertParallelMoE:
+    """Expert parallelism over ``all_to_all_single``: tokens sorted by expert, sent to the expert's owner, run through
+    the local experts, sent back and combined with the routing weights."""
+
+    def __init__(self, group, num_experts: int, top_k: int):
+        self.group = group if group is not None else td.group.WORLD
+        self.world, self.rank = td.get_world_size(self.group), td.get_rank(self.group)
+        if num_experts % self.world:
+            raise ValueError("the number of experts must be divisible by the expert-parallel size")
+        self.E, self.E_loc, self.k = num_experts, num_experts // self.world, top_k
+
+    def __call__(self, hidden, gate_up_local, down_local, topk_w, topk_idx):
+        W, E_loc = self.world, self.E_loc
+        T, k = topk_idx.shape
+        flat = topk_idx.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        tok = order // k
+        counts = torch.bincount(flat, minlength=self.E)
+        all_cnt = torch.empty(W * self.E, dtype=counts.dtype, device=counts.device)
+        td.all_gather_into_tensor(all_cnt, counts, group=self.group)
+        all_cnt = all_cnt.view(W, self.E).cpu()
+        e0 = self.rank * E_loc
+        send = [int(all_cnt[self.rank, r * E_loc:(r + 1) * E_loc].sum()) for r in range(W)]
+        recv = [int(all_cnt[s, e0:e0 + E_loc].sum()) for s in range(W)]
+        x_in = _AllToAllRows.apply(hidden.index_select(0, tok), send, recv, self.group)  # source-major, expert-minor
+        # rows of local expert e: one run per source
+        base = [sum(recv[:s]) for s in range(W)]
+        within = all_cnt[:, e0:e0 + E_loc].cumsum(1) - all_cnt[:, e0:e0 + E_loc]
+        y_in = torch.zeros_like(x_in)
+        I = gate_up_local.shape[1] // 2
+        for e in range(E_loc):
+            idx = torch.cat([torch.arange(base[s] + int(within[s, e]), base[s] + int(within[s, e]) + int(all_cnt[s, e0 + e]),
+                                          device=hidden.device) for s in range(W)])
+            if idx.numel() == 0:
+                continue
+            xe = x_in.index_select(0, idx)
+            gu = xe @ gate_up_local[e].t()
+            act = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+            y_in = y_in.index_copy(0, idx, (act @ down_local[e].t()).to(y_in.dtype))
+        y_perm = _AllToAllRows.apply(y_in, recv, send, self.group)
+        w_perm = topk_w.reshape(-1).index_select(0, order)
+        out = torch.zeros(T, hidden.shape[1], dtype=torch.float32, device=hidden.device)
+        out = out.index_add(0, tok, y_perm.float() * w_perm.float()[:, None])
+        return out.to(hidden.dtype)
+
+
+def shard_experts(model, group=None, max_tokens: int = 16384, fused: bool | None = None):
+    """Turns a replicated MoE model into an expert-parallel one, in place (collective over ``group``).
+
+    Every MoE layer keeps experts ``[rank * E / world, (rank + 1) * E / world)`` of ``experts_gate_up`` /
+    ``experts_down``; the new parameters carry ``_ep_local = True`` so that the training engines leave their gradients
+    unreduced (each expert receives the tokens of every rank through the dispatch; the gradients are scaled by 1 / world
+    like an averaged data-parallel gradient) and keep their optimizer state whole on the owner.  ``layer.ep`` runs
+    the block: the fused kernels over symmetric memory on bf16 CUDA models (pull dispatch, grouped tcgen05 GEMMs,
+    peer-store combine), the backend's all-to-all elsewhere.  ``max_tokens``: most tokens of one forward call on a
+    rank (sizes the symmetric buffers of the fused path)."""
+    import torch.nn as nn
+
+    lm = getattr(model, "language_model", model)
+    cfg = lm.config
+    if not cfg.is_moe:
+        raise ValueError("shard_experts needs a mixture-of-experts model")
+    group = group if group is not None else td.group.WORLD
+    world, rank = td.get_world_size(group), td.get_rank(group)
+    if cfg.num_experts % world:
+        raise ValueError(f"{cfg.num_experts} experts cannot be split over {world} ranks")
+    e_loc = cfg.num_experts // world
+    first = lm.layers[0].experts_gate_up
+    if fused is None:
+        from .symm import symmetric_available
+
+        fused = (first.is_cuda and first.dtype == torch.bfloat16 and world > 1 and symmetric_available()
+                 and cfg.hidden_size % 64 == 0 and cfg.moe_intermediate_size % 64 == 0)
+    ep = (ExpertParallelMoE(group, cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size, cfg.num_experts_per_tok,
+                            max_tokens, first.device) if fused
+          else HostExpertParallelMoE(group, cfg.num_experts, cfg.num_experts_per_tok))
+    for l in lm.layers:
+        for name in ("experts_gate_up", "experts_down"):
+            full = getattr(l, name)
+            p = nn.Parameter(full.detach()[rank * e_loc:(rank + 1) * e_loc].clone(), requires_grad=full.requires_grad)
+            p._ep_local = True
+            setattr(l, name, p)
+        l.ep, l.ep_first_expert = ep, rank * e_loc
+    lm.ep_group, lm.ep_world, lm.ep_rank = group, world, rank
+    return model
+
+
+@torch.no_grad()
+def ep_hf_state_dict(model, to_cpu: bool = True) -> dict:
+    """Complete checkpoint tensors of an expert-parallel model (collective): the experts of one layer at a time are
+    all-gathered, exported and (with ``to_cpu``) copied to host memory before the next layer's are gathered; ranks
+    that do not save pass False and get an empty dict."""
+    from ..models.hf_io import to_hf_state_dict
+
+    lm = getattr(model, "language_model", model)
+    group, world = lm.ep_group, lm.ep_world
+    state = {"prev": None}
+
+    def gather(i):
+        if state["prev"] is not None:
+            state["prev"]._ep_full = None
+        l = lm.layers[i]
+        full = []
+        for t in (l.experts_gate_up.detach(), l.experts_down.detach()):
+            out = torch.empty(world * t.numel(), dtype=t.dtype, device=t.device)
+            td.all_gather_into_tensor(out, t.contiguous().view(-1), group=group)
+            full.append(out.view((world * t.shape[0],) + tuple(t.shape[1:])))
+        l._ep_full, state["prev"] = tuple(full), l
+
+    sd = to_hf_state_dict(lm, before_layer=gather, copy_to="cpu" if to_cpu else None)
+    if state["prev"] is not None:
+        state["prev"]._ep_full = None
+    return sd

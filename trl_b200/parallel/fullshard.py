@@ -47,6 +47,8 @@ class _AgLinearFn(torch.autograd.Function):
         if gather.fresh:  # later micro-batches and the recompute in backward: the buffer is still complete
             y = x2 @ weight.t()
         else:
+            if gather.align is not None:  # ranks may come out of a generation phase seconds apart
+                gather.align()
             y = ag_gemm(x2, gather.arena, gather.byte_offset, gather.per, gather.total, gather.w_off, weight.shape[0],
                         gather.state, bias=None)
             gather.fresh = True
@@ -68,9 +70,10 @@ class _AgLinearFn(torch.autograd.Function):
 class LayerGather:
     """What a decoder layer needs to run its QKV GEMM as an all-gather-fused GEMM."""
 
-    def __init__(self, arena, byte_offset, per, total, w_off, device, copiers):
+    def __init__(self, arena, byte_offset, per, total, w_off, device, copiers, align=None):
         from ..ops.cuda_comm import AgGemmState
 
+        self.align = align  # called before the first gather after an optimizer step (only layer 0 has one)
         self.arena, self.byte_offset, self.per, self.total, self.w_off = arena, byte_offset, per, total, w_off
         self.state = AgGemmState(device, copiers=copiers)
         self.fresh = False  # True from the first gather after an optimizer step until the next step
@@ -104,7 +107,7 @@ class FullShardEngine(TrainEngine):
             w_off = b.offsets[b.names.index(qname)]
             key = ("param", b.name, str(b.params[0].dtype))
             layer._shard_gather = LayerGather(self._arenas["param"], self._offsets[key], b.hi - b.lo, b.numel, w_off,
-                                              b.flat_param.device, copiers)
+                                              b.flat_param.device, copiers, align=self.align_ranks if i == 0 else None)
             self._layer_buckets.append(b)
         self._other_buckets = [b for b in self.buckets if b not in self._layer_buckets]
         model._trl_b200_engine = self
@@ -144,6 +147,7 @@ class FullShardEngine(TrainEngine):
     def _step_fused(self, lr, max_grad_norm):
         from ..ops import cuda as K
 
+        self.align_ranks()
         ga = self._arenas["grad"]
         self._sumsq.zero_()
         for b, red in zip(self.buckets, self._reduced):

@@ -168,6 +168,7 @@ class StreamShardEngine:
                     self._n_flush, self._cur = 0, 0
                     self._rs_sync = SyncWords(self.dev, channel=2)
                     self._sq_scratch = torch.zeros(1, dtype=torch.float32, device=self.dev)
+                    self._tick = torch.zeros(1, dtype=torch.float32, device=self.dev)
         if frozen:
             self.gbuf = None
         elif self.fused:
@@ -395,6 +396,7 @@ class StreamShardEngine:
         if not getattr(self.model, "gradient_checkpointing", False) or getattr(self.model, "checkpoint_num_layers", None):
             raise RuntimeError("the streamed full-shard engine overwrites layer weights between forward and backward: "
                                "enable activation checkpointing for all layers (gradient_checkpointing=True)")
+        self.align_ranks()
         loss.backward()
         for ls in self.layers:  # a layer some of whose parameters got no gradient never reached its count
             if ls.arrived:
@@ -419,6 +421,12 @@ class StreamShardEngine:
         else:
             adamw_flat(master, grad, m, v, self.step_count, lr, b1, b2, self.eps,
                        self.weight_decay if not no_decay else 0.0, scale, shadow)
+
+    def align_ranks(self):
+        """Fused path: the per-layer reductions wait at most a second for a peer; ranks that start a step seconds apart
+        (an online trainer whose completions differ in length) meet here first, through the backend."""
+        if self.fused and not self.frozen:
+            td.all_reduce(self._tick, group=self.group)
 
     def _join_side_streams(self):
         for slot in (0, 1):
