@@ -41,8 +41,11 @@ def test_expert_parallel_moe_two_ranks():
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_weight_reshard_from_full_shard_to_tp_layout():
-    rc, out, err = run_ranks(os.path.join(HERE, "dist_worker_reshard_gpu.py"), 29629)
+@pytest.mark.parametrize("tiled", ["0", "1"])
+def test_weight_reshard_from_full_shard_to_tp_layout(tiled):
+    """tiled=1: the rollout engine keeps its slices tile-major (fused TP decode), the reshard re-tiles per layer."""
+    rc, out, err = run_ranks(os.path.join(HERE, "dist_worker_reshard_gpu.py"), 29629 + 40 * int(tiled),
+                             extra_env={"TRL_B200_TP_FUSED": tiled})
     assert rc == 0 and "RESHARD_OK" in out, out[-3000:] + err[-3000:]
 
 

@@ -91,9 +91,8 @@ class FullShardEngine(TrainEngine):
                          grad_dtype=grad_dtype, use_symm_kernels=True, group=group, bucket_of=fullshard_bucket_of)
         self.poison = os.environ.get("TRL_B200_FULLSHARD_POISON", "0") == "1"
         if copiers is None:
-            # CTAs of the QKV GEMM that only pull peers' shards.  One copier sustains roughly 26 GB/s.  Measured on the
-            # Llama-3-8B layer bucket: 2 ranks 0.507 / 0.462 / 0.425 / 0.409 ms with 8 / 16 / 24 / 32 copiers (NCCL
-            # all-gather + cuBLAS: 0.677 ms); 8 ranks 1.92 ms with 8 copiers, where 7/8 of the bucket is remote.
+            # CTAs of the QKV GEMM that only pull peers' shards: enough of them to keep NVLink busy, growing with the
+            # remote fraction of the bucket (7/8 at 8 ranks)
             copiers = int(os.environ.get("TRL_B200_AG_COPIERS", "0")) or min(64, max(32, 6 * self.world))
         self._layer_buckets, self._other_buckets = [], []
         by_name = {b.name: b for b in self.buckets}
