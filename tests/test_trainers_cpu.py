@@ -483,3 +483,33 @@ def test_deferred_metrics_resolve_to_global_ratios_and_means():
          "policy_loss": [defer_mean(torch.tensor(0.25))], "plain": [1.5]}
     resolve_deferred_metrics(m)
     assert m == {"entropy": [1.5, 1.0], "policy_loss": [0.25], "plain": [1.5]}
+
+
+def test_grpo_trains_from_a_streaming_dataset_with_functools_partial_reward(tmp_path, tiny_tokenizer):
+    """A dataset without ``__len__`` goes through ``repeat_iterable_dataset``: every prompt of a generation batch
+    appears ``num_generations`` times in a row, as with the index sampler; the reward's display name is the wrapped
+    function's."""
+    import functools
+
+    class Stream:
+        def __init__(self, rows):
+            self.rows = rows
+
+        def __iter__(self):
+            return iter(self.rows)
+
+    rows = [dict(r) for r in make_dataset("standard_prompt_only", 16)]
+    seen = []
+
+    def reward(completions, prompts=None, bonus=0.0, **kw):
+        seen.append(list(prompts))
+        return [len(c) * 0.1 + bonus for c in completions]
+
+    args = GRPOConfig(output_dir=str(tmp_path), **dict(COMMON, max_steps=2), num_generations=4, max_completion_length=4)
+    tr = GRPOTrainer(make_tiny_model(), functools.partial(reward, bonus=1.0), args, train_dataset=Stream(rows),
+                     processing_class=tiny_tokenizer)
+    assert tr.reward_func_names == ["reward"]
+    tr.train()
+    assert tr.state.global_step == 2 and seen
+    first = seen[0]
+    assert len(first) % 4 == 0 and all(len(set(first[i:i + 4])) == 1 for i in range(0, len(first), 4))

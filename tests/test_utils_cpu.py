@@ -166,3 +166,137 @@ def test_plumbing_modules(tmp_path):
     assert float(_ForwardRedirection()(w, inner, inner.other, torch.tensor(2.0))) == 20.0 and w.calls == 1
     assert float(inner(torch.tensor(2.0))) == 3.0
     assert trl_b200.__version__
+
+
+# ---- streaming repetition, callable names, sampler variants -----------------------------------------------------------
+@pytest.mark.parametrize("mini,bs,rep", [(1, 1, 1), (2, 3, 4), (3, 2, 2), (2, 2, 3)])
+def test_repeat_iterable_dataset_follows_the_unshuffled_sampler(mini, bs, rep):
+    from trl_b200.trainer.utils import RepeatSampler, repeat_iterable_dataset
+
+    n = 12
+    want = list(RepeatSampler(list(range(n)), mini_repeat_count=mini, batch_size=bs, repeat_count=rep, shuffle=False))
+    got = [r["x"] for r in repeat_iterable_dataset(({"x": i} for i in range(n)), mini, bs, rep)]
+    assert got == want
+
+
+def test_repeat_iterable_dataset_defaults_tail_columns_and_independent_copies():
+    from trl_b200.trainer.utils import repeat_iterable_dataset
+
+    assert [r["x"] for r in repeat_iterable_dataset([{"x": i} for i in range(4)], mini_repeat_count=2)] == [0, 0, 1, 1, 2, 2, 3, 3]
+    # seven rows in chunks of two: the seventh cannot fill a chunk and is dropped
+    assert [r["x"] for r in repeat_iterable_dataset([{"x": i} for i in range(7)], 1, batch_size=2)] == [0, 1, 2, 3, 4, 5]
+    rows = list(repeat_iterable_dataset([{"x": 0, "answer": "0"}, {"x": 1, "answer": "1"}], 2))
+    assert rows == [{"x": 0, "answer": "0"}, {"x": 0, "answer": "0"}, {"x": 1, "answer": "1"}, {"x": 1, "answer": "1"}]
+    a, b = list(repeat_iterable_dataset([{"prompt": [{"content": "hi"}]}], 2))
+    a["prompt"][-1]["content"] += " there"  # editing one repeat must not leak into the other
+    assert a is not b and b["prompt"][-1]["content"] == "hi"
+
+
+def test_repeat_iterable_dataset_forwards_set_epoch_to_the_source():
+    from trl_b200.trainer.utils import repeat_iterable_dataset
+
+    class Shuffled:
+        def __init__(self):
+            self.epoch = 0
+
+        def set_epoch(self, e):
+            self.epoch = e
+
+        def __iter__(self):
+            g = torch.Generator().manual_seed(42 + self.epoch)
+            return iter({"x": int(i)} for i in torch.randperm(8, generator=g))
+
+    rep = repeat_iterable_dataset(Shuffled(), 1, batch_size=8)
+    rep.set_epoch(0)
+    e0 = [r["x"] for r in rep]
+    rep.set_epoch(1)
+    e1 = [r["x"] for r in rep]
+    assert sorted(e0) == sorted(e1) == list(range(8)) and e0 != e1
+
+
+def test_get_callable_name_for_functions_partials_instances_and_lambdas():
+    import functools
+
+    from trl_b200.trainer.utils import get_callable_name
+
+    def reward(x, scale=1.0):
+        return x
+
+    class Scorer:
+        def __call__(self, x):
+            return x
+
+    assert get_callable_name(reward) == "reward"
+    assert get_callable_name(functools.partial(reward, scale=2.0)) == "reward"
+    assert get_callable_name(functools.partial(functools.partial(reward, scale=2.0), 1)) == "reward"
+    assert get_callable_name(Scorer()) == "Scorer"
+    assert get_callable_name(lambda x: x) == "<lambda>"
+
+
+def test_repeat_sampler_shapes_of_the_schedule():
+    from trl_b200.trainer.utils import RepeatSampler
+
+    data = ["a", "b", "c", "d", "e", "f", "g"]
+    # every index exactly `mini_repeat_count` times when nothing is dropped
+    out = list(RepeatSampler(data, mini_repeat_count=2, seed=0))
+    assert len(out) == 14 and all(out[i] == out[i + 1] for i in range(0, 14, 2)) and sorted(set(out)) == list(range(7))
+    assert list(RepeatSampler(data, mini_repeat_count=2, shuffle=False)) == [0, 0, 1, 1, 2, 2, 3, 3, 4, 4, 5, 5, 6, 6]
+    # chunks of three, the seventh item has no chunk
+    out = list(RepeatSampler(data, mini_repeat_count=1, batch_size=3, shuffle=False))
+    assert out == [0, 1, 2, 3, 4, 5]
+    # 7 items, pairs of repeats, chunks of 3, every chunk 4 times: 2 chunks x 4 x 3 x 2
+    out = list(RepeatSampler(data, mini_repeat_count=2, batch_size=3, repeat_count=4, shuffle=False))
+    assert len(out) == 48 and out[:6] == [0, 0, 1, 1, 2, 2] and out[6:12] == out[:6] and out[24:30] == [3, 3, 4, 4, 5, 5]
+    assert len(RepeatSampler(data, mini_repeat_count=2, batch_size=3, repeat_count=4)) == 48
+    # the same seed gives the same permutation, and each epoch draws a new one
+    s1, s2 = RepeatSampler(data, 1, seed=5), RepeatSampler(data, 1, seed=5)
+    assert list(s1) == list(s2) and list(s1) != list(RepeatSampler(data, 1, seed=5))
+
+
+def test_pad_variants():
+    from trl_b200.trainer.utils import pad
+
+    x, y = torch.tensor([1, 2, 3]), torch.tensor([4, 5])
+    assert pad([x, y], padding_value=0, padding_side="left").tolist() == [[1, 2, 3], [0, 4, 5]]
+    assert pad([x, y], padding_value=0, padding_side="right").tolist() == [[1, 2, 3], [4, 5, 0]]
+    a, b = torch.tensor([[1, 2], [3, 4]]), torch.tensor([[5, 6]])
+    assert pad([a, b], padding_value=0, padding_side="left").tolist() == [[[1, 2], [3, 4]], [[0, 0], [5, 6]]]
+    assert pad([a, b], padding_value=0, padding_side="right").tolist() == [[[1, 2], [3, 4]], [[5, 6], [0, 0]]]
+    assert pad([x, y], padding_value=0, pad_to_multiple_of=4).tolist() == [[1, 2, 3, 0], [4, 5, 0, 0]]
+    assert pad([x, y], padding_value=0, padding_side="left", pad_to_multiple_of=4).tolist() == [[0, 1, 2, 3], [0, 0, 4, 5]]
+    assert pad([torch.tensor([1, 2, 3, 4]), y], padding_value=0, pad_to_multiple_of=4).shape == (2, 4)  # already a multiple
+
+
+def test_nanstd_and_hash_module_details():
+    from trl_b200.trainer.utils import hash_module, nanstd
+
+    t = torch.tensor([1.0, 2.0, 3.0, float("nan")])
+    assert abs(float(nanstd(t)) - 1.0) < 1e-6
+    m = torch.tensor([[1.0, 3.0], [float("nan"), 4.0], [5.0, float("nan")]])
+    assert nanstd(m, dim=0, keepdim=True).shape == (1, 2)
+    assert torch.isnan(nanstd(torch.tensor([float("nan"), float("nan")])))
+    a, b = torch.nn.Linear(4, 3), torch.nn.Linear(4, 3)
+    b.load_state_dict(a.state_dict())
+    assert hash_module(a) == hash_module(b)
+    with torch.no_grad():
+        b.weight[0, 0] += 1e-3
+    assert hash_module(a) != hash_module(b)
+    assert hash_module(torch.nn.Linear(4, 3).half()) != hash_module(a)
+
+
+def test_entropy_and_selective_log_softmax_in_chunks_and_dtypes():
+    from trl_b200.oracle.ops import entropy_from_logits, selective_log_softmax
+
+    g = torch.Generator().manual_seed(0)
+    for shape in [(7, 33), (2, 5, 33)]:
+        logits = torch.randn(*shape, generator=g)
+        lp = torch.log_softmax(logits, -1)
+        want = -(lp.exp() * lp).sum(-1)
+        for chunk in (1, 3, 128):
+            assert torch.allclose(entropy_from_logits(logits, chunk_size=chunk), want, atol=1e-5)
+        idx = torch.randint(0, 33, shape[:-1], generator=g)
+        assert torch.allclose(selective_log_softmax(logits, idx), lp.gather(-1, idx[..., None])[..., 0], atol=1e-5)
+        multi = torch.randint(0, 33, shape[:-1] + (4,), generator=g)
+        assert torch.allclose(selective_log_softmax(logits, multi), lp.gather(-1, multi), atol=1e-5)
+        got16 = selective_log_softmax(logits.to(torch.bfloat16), idx)
+        assert got16.dtype == torch.bfloat16 and (got16.float() - lp.gather(-1, idx[..., None])[..., 0]).abs().max() < 0.1

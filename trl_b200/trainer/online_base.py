@@ -27,7 +27,7 @@ from ..models.decoder import CausalLM, SeqCtx
 from ..ops import functional as ops
 from ..parallel import dist as D
 from ..rollout.sampling import SamplingParams
-from .utils import (RepeatSampler, create_model_from_path, disable_dropout_in_model, nanmax, nanmin, nanstd, pad,
+from .utils import (RepeatSampler, get_callable_name, create_model_from_path, disable_dropout_in_model, nanmax, nanmin, nanstd, pad,
                     print_prompt_completions_sample, resolve_deferred_metrics, run_coroutine_sync, shuffle_sequence_dict, split_tensor_dict,
                     use_adapter)
 
@@ -73,7 +73,7 @@ class OnlineTrainer(Trainer):
             if isinstance(reward_funcs[i], nn.Module):
                 self.reward_func_names.append(os.path.basename(str(getattr(reward_funcs[i], "name_or_path", f"reward_model_{i}"))) or f"reward_model_{i}")
             else:
-                self.reward_func_names.append(getattr(reward_funcs[i], "__name__", type(reward_funcs[i]).__name__))
+                self.reward_func_names.append(get_callable_name(reward_funcs[i]))
         self.reward_funcs = reward_funcs
         if args.reward_weights is not None:
             if len(args.reward_weights) != len(reward_funcs):
@@ -151,6 +151,19 @@ class OnlineTrainer(Trainer):
 
     def get_train_dataloader(self):
         self._train_batch_size = self.args.per_device_train_batch_size * self.args.steps_per_generation
+        ds = self.train_dataset
+        if ds is not None and (not hasattr(ds, "__len__") or not hasattr(ds, "__getitem__")):
+            # streaming dataset: the same repetition pattern as RepeatSampler, applied to the stream (needs max_steps)
+            from .utils import repeat_iterable_dataset
+
+            a = self.args
+            held, self.train_dataset = ds, repeat_iterable_dataset(
+                ds, self.num_generations, a.generation_batch_size // self.num_generations,
+                self.num_iterations * a.steps_per_generation)
+            try:
+                return super().get_train_dataloader()
+            finally:
+                self.train_dataset = held
         return super().get_train_dataloader()
 
     def _count_items(self, batches):

@@ -105,19 +105,46 @@ class RepeatSampler:
 RepeatRandomSampler = RepeatSampler
 
 
-def repeat_iterable_dataset(rows: Iterable, mini_repeat_count: int, batch_size: int, repeat_count: int):
-    """Streaming counterpart of :class:`RepeatSampler` (utils.py:791-853): a generator over rows."""
-    import copy
+class _RepeatedIterable:
+    """Re-iterable view produced by :func:`repeat_iterable_dataset`; stays chained to its source so that ``set_epoch``
+    reaches an upstream shuffle."""
 
-    buf = []
-    for r in rows:
-        buf.append(r)
-        if len(buf) == batch_size:
-            for _ in range(repeat_count):
-                for x in buf:
-                    for _ in range(mini_repeat_count):
-                        yield copy.deepcopy(x)
-            buf = []
+    def __init__(self, rows, mini_repeat_count, batch_size, repeat_count):
+        self.rows, self.mini_repeat_count, self.batch_size, self.repeat_count = rows, mini_repeat_count, batch_size, repeat_count
+
+    def set_epoch(self, epoch: int):
+        if hasattr(self.rows, "set_epoch"):
+            self.rows.set_epoch(epoch)
+
+    def __iter__(self):
+        import copy
+
+        buf = []
+        for r in self.rows:
+            buf.append(r)
+            if len(buf) == self.batch_size:
+                for _ in range(self.repeat_count):
+                    for x in buf:
+                        for _ in range(self.mini_repeat_count):
+                            yield copy.deepcopy(x)  # every repeat is its own object, like a fresh dataset access
+                buf = []
+        # an incomplete last chunk is dropped, like RepeatSampler does
+
+
+def repeat_iterable_dataset(rows: Iterable, mini_repeat_count: int, batch_size: int = 1, repeat_count: int = 1):
+    """Streaming counterpart of :class:`RepeatSampler` (trl/trainer/utils.py:791-853): rows come out in the order in
+    which the unshuffled sampler would emit their indices."""
+    return _RepeatedIterable(rows, mini_repeat_count, batch_size, repeat_count)
+
+
+def get_callable_name(func) -> str:
+    """Display name of a reward callable: functions by ``__name__``, ``functools.partial`` objects by the function
+    they wrap (however deeply nested), callable instances by their class (trl/trainer/utils.py:224-232)."""
+    import functools
+
+    while isinstance(func, functools.partial):
+        func = func.func
+    return getattr(func, "__name__", type(func).__name__)
 
 
 def nanstd(t: torch.Tensor, dim=None, keepdim: bool = False) -> torch.Tensor:
