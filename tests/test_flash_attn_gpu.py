@@ -49,6 +49,42 @@ def test_fa_forward_matches_oracle(lens, Hq, Hk, window, strided):
     assert (lse[0] - want_lse).abs().max().item() < 2e-2
 
 
+@pytest.mark.parametrize("causal", [True, False])
+def test_fa_forward_when_the_reference_maximum_moves(causal):
+    """Scores that keep growing along the keys (by far more than 2^8 from tile to tile) force the rows to move their
+    reference maximum and rescale the output accumulated in TMEM many times; the result and the log-sum-exp must
+    still match the dense fp32 computation."""
+    from trl_b200.ops import cuda as K
+    from trl_b200.oracle import ops as ref
+
+    torch.manual_seed(3)
+    lens, Hq, Hk = [640, 385], 4, 2
+    T = sum(lens)
+    q = torch.randn(T, Hq, 128, device="cuda")
+    k = torch.randn(T, Hk, 128, device="cuda")
+    ramp = torch.linspace(0.0, 8.0, T, device="cuda")  # later keys score higher for every query
+    k = k + ramp[:, None, None]  # along the all-ones direction ...
+    q = q + 1.0                  # ... which every query has a component of: score += ramp * (128 + noise) / sqrt(128)
+    q, k = q.to(torch.bfloat16), k.to(torch.bfloat16)
+    v = torch.randn(T, Hk, 128, device="cuda").to(torch.bfloat16)
+    cu = torch.tensor([0, 640, 1025], dtype=torch.int32, device="cuda")
+    out, lse = K.fa_varlen_fwd(q, k, v, cu, cu, causal=causal)
+    torch.cuda.synchronize()
+    K.check_status()
+    want = ref.attention_varlen(q.float(), k.float(), v.float(), cu, causal=causal)
+    assert (out.float() - want.float()).abs().max().item() < 3e-2
+    idx = torch.arange(T, device="cuda")
+    doc = torch.bucketize(idx, cu[1:].long(), right=True)
+    mask = doc[:, None] == doc[None, :]
+    if causal:
+        mask &= idx[:, None] >= idx[None, :]
+    sc = (q[:, 1].float() @ k[:, 0].float().t()) / 128 ** 0.5
+    want_lse = torch.logsumexp(sc.masked_fill(~mask, float("-inf")), -1)
+    spread = (sc.masked_fill(~mask, float("-inf")).max(-1).values - sc.masked_fill(~mask, float("inf")).min(-1).values)
+    assert spread.max().item() > 40  # the ramp really spans many factors of 2^8
+    assert (lse[1] - want_lse).abs().max().item() < 5e-2 * max(1.0, want_lse.abs().max().item() / 20)
+
+
 def test_fa_forward_noncausal_and_end_aligned_segments():
     from trl_b200.ops import cuda as K
     from trl_b200.oracle import ops as ref

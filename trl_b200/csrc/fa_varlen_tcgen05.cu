@@ -11,13 +11,13 @@
 //   warp 0   TMA: the Q tile once, then K and V tiles of 128 keys through a 2-stage ring (separate barriers, so
 //            Q.K^T starts when K has landed);
 //   warp 1   tcgen05.mma: S_j = Q K_j^T into one of two TMEM buffers (issued one tile ahead, so the softmax of
-//            tile j runs under Q.K_{j+1}^T), then O_j = P_j V_j into one of two further TMEM buffers.  V is consumed
-//            as an MN-major operand straight from its TMA tile: no transpose anywhere;
-//   warps 2-5 one thread per query row: scale, mask, running max / sum in base 2, P_j written as a K-major swizzled
-//            bf16 tile for the second MMA, and the output accumulated in registers as acc = acc * alpha + O_j
-//            (O_j read back from TMEM), so nothing in TMEM ever needs rescaling and the MMA warp never waits for a
-//            correction step.
-//   TMEM: S0 S1 O0 O1 = 512 columns.  Output bf16 + log-sum-exp (natural log, fp32 [Hq, Tq]) for the backward.
+//            tile j runs under Q.K_{j+1}^T), then O += P_j V_j accumulating in TMEM over all key tiles.  V is
+//            consumed as an MN-major operand straight from its TMA tile: no transpose anywhere;
+//   warps 2-5 one thread per query row: maximum, exponentials in base 2 against a reference maximum that moves only
+//            when a tile exceeds it by 2^8 (then, and only then, the warp rescales its rows of O in TMEM), P_j
+//            written as a K-major swizzled bf16 tile for the second MMA.  Tiles that every row sees completely skip
+//            the per-element mask tests.
+//   TMEM: S0 S1 O = 384 columns.  Output bf16 + log-sum-exp (natural log, fp32 [Hq, Tq]) for the backward.
 //
 // Every wait is bounded (common.cuh); a wait that runs out reports through the status words and the CTA leaves
 // through the normal teardown.
@@ -95,8 +95,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   uint64_t* kv_empty = bars + 5;   // [2]
   uint64_t* s_full = bars + 7;     // [2]
   uint64_t* s_empty = bars + 9;    // [2]
-  uint64_t* o_full = bars + 11;    // [2]
-  uint64_t* o_empty = bars + 13;   // [2]
+  uint64_t* o_full = bars + 11;    // one phase per P.V product
   uint64_t* p_full = bars + 15;
   uint64_t* p_empty = bars + 16;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
@@ -118,9 +117,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       mbar_init(&kv_empty[s], 1);
       mbar_init(&s_full[s], 1);
       mbar_init(&s_empty[s], 4);
-      mbar_init(&o_full[s], 1);
-      mbar_init(&o_empty[s], 4);
     }
+    mbar_init(o_full, 1);
     mbar_init(p_full, 128);
     mbar_init(p_empty, 1);
     *abort_flag = 0;
@@ -189,60 +187,103 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           if (!ok) break;
           if (!mbar_wait(p_full, (uint32_t)(j & 1), abort_flag, p.status, 1040)) { ok = false; break; }
           if (!mbar_wait(&v_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1050 + s)) { ok = false; break; }
-          if (!mbar_wait(&o_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, p.status, 1060 + s)) { ok = false; break; }
           tc_fence_after();
           const uint32_t v_u = kv_u + (uint32_t)s * 2 * FA_TILE_BYTES + FA_TILE_BYTES;
 #pragma unroll
           for (int kk = 0; kk < FA_BN / 16; ++kk) {
             const uint64_t adesc = umma_desc_kmajor_sw128(p_u + (uint32_t)(kk >> 2) * FA_BOX_BYTES) + 2 * (kk & 3);
             const uint64_t bdesc = umma_desc_mnmajor_sw128(v_u + (uint32_t)kk * 2048, FA_BOX_BYTES);
-            umma_bf16_ss(tmem_base + 256 + (uint32_t)s * FA_D, adesc, bdesc, idesc_o, kk != 0);
+            // O accumulates in TMEM over all key tiles; the row threads rescale it in place when a row's reference
+            // maximum moves (see below), always between two P.V products
+            umma_bf16_ss(tmem_base + 256, adesc, bdesc, idesc_o, (j != 0) || (kk != 0));
           }
-          umma_commit(&o_full[s]);
+          umma_commit(o_full);
           umma_commit(&kv_empty[s]);
           umma_commit(p_empty);
         }
       }
       __syncwarp();
     } else {
-      // ---------------- softmax + output accumulation: one thread per query row ----------------
+      // ---------------- softmax: one thread per query row ----------------
+      // The output accumulates in TMEM.  A row keeps a *reference* maximum m_ref for its exponents and moves it only
+      // when a tile's maximum exceeds it by more than 8 (in log2 units): until then probabilities are at most 2^8,
+      // which bf16 and the fp32 sums hold without loss, and nothing has to be rescaled.  When it does move, the
+      // warp rescales its 32 rows of O in TMEM (after the previous P.V product has finished, before the next one is
+      // released) and the running sum; with ordinary scores that happens in the first tile or two of a row only.
       const int quarter = warp & 3;
       const int r = quarter * 32 + lane;
       const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-      const int q_pos = tile * FA_BM + r;  // position inside the query segment
+      const int q_first = tile * FA_BM;
+      const int q_pos = q_first + r;  // position inside the query segment
       const bool row_ok = q_pos < lq;
       const int off = lk - lq;
       // keys this row may see: [k_min, k_max]
       const int k_max = p.causal ? min(lk - 1, q_pos + off) : lk - 1;
       const int k_min = (p.causal && p.window > 0) ? max(0, q_pos + off - p.window + 1) : 0;
-      float acc[FA_D];
-#pragma unroll
-      for (int i = 0; i < FA_D; ++i) acc[i] = 0.f;
-      float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
+      const uint32_t to = tmem_base + lane_off + 256;
+      float m_ref = -INFINITY, l_run = 0.f;
       bool ok = true;
       for (int j = 0; j < n_kv && ok; ++j) {
         const int s = j & 1;
         const int key0 = (lo + j) * FA_BN;
+        // every row of the tile sees every key of this tile: no per-element tests (all but the diagonal / edge tiles)
+        bool full = (q_first + FA_BM <= lq) && (key0 + FA_BN <= lk);
+        if (p.causal) {
+          full = full && (key0 + FA_BN - 1 <= q_first + off);
+          if (p.window > 0) full = full && (key0 >= q_first + FA_BM - 1 + off - p.window + 1);
+        }
         ok = __all_sync(0xffffffffu, mbar_wait(&s_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1070 + s));
         if (!ok) break;
         tc_fence_after();
         const uint32_t ts = tmem_base + lane_off + (uint32_t)s * FA_BN;
-        // pass 1: row maximum over this tile's visible keys
-        float m_tile = -INFINITY;
+        // pass 1: row maximum over this tile's visible keys (raw scores; the scale is positive)
+        float mx = -INFINITY;
 #pragma unroll 1
-        for (int c = 0; c < FA_BN; c += 32) {
-          float v[32];
-          tmem_ld_32x32(ts + c, v);
+        for (int c = 0; c < FA_BN; c += 64) {
+          float v0[32], v1[32];
+          tmem_ld_32x32(ts + c, v0);
+          tmem_ld_32x32(ts + c + 32, v1);
           tmem_ld_wait();
+          if (full) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = key0 + c + i;
-            if (row_ok && key >= k_min && key <= k_max) m_tile = fmaxf(m_tile, v[i] * p.scale_log2);
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(v0[i], v1[i]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int key = key0 + c + i;
+              if (row_ok && key >= k_min && key <= k_max) mx = fmaxf(mx, v0[i]);
+              if (row_ok && key + 32 >= k_min && key + 32 <= k_max) mx = fmaxf(mx, v1[i]);
+            }
           }
         }
-        const float m_new = fmaxf(m_run, m_tile);
-        const float m_use = m_new == -INFINITY ? 0.f : m_new;
-        const float alpha = exp2f(m_run - m_use);  // 0 while nothing has been seen
+        const float m_tile = mx * p.scale_log2;
+        float alpha = 1.f;
+        bool moved = false;
+        if (m_ref == -INFINITY) {
+          m_ref = m_tile;  // nothing seen so far: the row of O is still zero, nothing to rescale
+        } else if (m_tile > m_ref + 8.f) {
+          alpha = fast_exp2(m_ref - m_tile);
+          m_ref = m_tile;
+          moved = true;
+        }
+        if (j > 0 && __any_sync(0xffffffffu, moved)) {
+          // P.V of tile j-1 must have landed; the tile before it has (S of this tile was issued after it)
+          ok = __all_sync(0xffffffffu, mbar_wait(o_full, (uint32_t)((j - 1) & 1), abort_flag, p.status, 1090));
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < FA_D; c += 32) {
+            float v[32];
+            tmem_ld_32x32(to + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= alpha;
+            tmem_st_32x32(to + c, v);
+          }
+          tmem_st_wait();
+        }
+        l_run *= alpha;
+        const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
         // pass 2: probabilities -> P tile (bf16, K-major swizzled), row sum
         ok = __all_sync(0xffffffffu, mbar_wait(p_empty, (uint32_t)((j & 1) ^ 1), abort_flag, p.status, 1080));
         if (!ok) break;
@@ -252,81 +293,61 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           float v[32];
           tmem_ld_32x32(ts + c, v);
           tmem_ld_wait();
+          if (full) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint32_t w[4];
-#pragma unroll
-            for (int e = 0; e < 8; e += 2) {
-              const int key = key0 + c + i + e;
-              const bool a0 = row_ok && key >= k_min && key <= k_max;
-              const bool a1 = row_ok && key + 1 >= k_min && key + 1 <= k_max;
-              const float p0 = a0 ? exp2f(v[i + e] * p.scale_log2 - m_use) : 0.f;
-              const float p1 = a1 ? exp2f(v[i + e + 1] * p.scale_log2 - m_use) : 0.f;
-              w[e >> 1] = pack_bf16(p0, p1);
-              // the sum uses the rounded values, i.e. exactly what the second MMA multiplies with V
-              const float2 rr = unpack_bf16(w[e >> 1]);
-              sum += rr.x + rr.y;
+            for (int i = 0; i < 32; ++i) {
+              v[i] = fast_exp2(fmaf(v[i], p.scale_log2, neg_m));
+              sum += v[i];
             }
-            *reinterpret_cast<uint4*>(p_s + fa_kmajor_off(r, c + i)) = make_uint4(w[0], w[1], w[2], w[3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int key = key0 + c + i;
+              const bool vis = row_ok && key >= k_min && key <= k_max;
+              v[i] = vis ? fast_exp2(fmaf(v[i], p.scale_log2, neg_m)) : 0.f;
+              sum += v[i];
+            }
           }
+#pragma unroll
+          for (int i = 0; i < 32; i += 8)
+            *reinterpret_cast<uint4*>(p_s + fa_kmajor_off(r, c + i)) =
+                make_uint4(pack_bf16(v[i], v[i + 1]), pack_bf16(v[i + 2], v[i + 3]), pack_bf16(v[i + 4], v[i + 5]),
+                           pack_bf16(v[i + 6], v[i + 7]));
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_empty[s]);
         fence_proxy_async_smem();
         mbar_arrive(p_full);
-        l_run = l_run * alpha + sum;
-        m_run = m_new;
-        // fold in the previous tile's P.V while the tensor core works on this one
-        if (j > 0) {
-          const int sp = (j - 1) & 1;
-          ok = __all_sync(0xffffffffu, mbar_wait(&o_full[sp], (uint32_t)(((j - 1) >> 1) & 1), abort_flag, p.status, 1090 + sp));
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t to = tmem_base + lane_off + 256 + (uint32_t)sp * FA_D;
-#pragma unroll
-          for (int c = 0; c < FA_D; c += 32) {
-            float v[32];
-            tmem_ld_32x32(to + c, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc[c + i] = acc[c + i] * alpha_prev + v[i];
-          }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&o_empty[sp]);
-        }
-        alpha_prev = alpha;
+        l_run += sum;
       }
       if (ok) {
-        const int sp = (n_kv - 1) & 1;
-        ok = __all_sync(0xffffffffu, mbar_wait(&o_full[sp], (uint32_t)(((n_kv - 1) >> 1) & 1), abort_flag, p.status, 1095));
+        // the last P.V product: wait for the one before it first, so that the parity of the last wait is unambiguous
+        const int last = n_kv - 1;
+        if (last >= 1)
+          ok = __all_sync(0xffffffffu, mbar_wait(o_full, (uint32_t)((last - 1) & 1), abort_flag, p.status, 1094));
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_full, (uint32_t)(last & 1), abort_flag, p.status, 1095));
         if (ok) {
           tc_fence_after();
-          const uint32_t to = tmem_base + lane_off + 256 + (uint32_t)sp * FA_D;
           const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
           __nv_bfloat16* dst = p.out + (long long)(q_beg + q_pos) * p.out_row_stride + (long long)h * FA_D;
-#pragma unroll
+#pragma unroll 1
           for (int c = 0; c < FA_D; c += 32) {
             float v[32];
             tmem_ld_32x32(to + c, v);
             tmem_ld_wait();
             if (row_ok) {
 #pragma unroll
-              for (int i = 0; i < 32; i += 8) {
-                uint4 o;
-                o.x = pack_bf16((acc[c + i] * alpha_prev + v[i]) * inv, (acc[c + i + 1] * alpha_prev + v[i + 1]) * inv);
-                o.y = pack_bf16((acc[c + i + 2] * alpha_prev + v[i + 2]) * inv, (acc[c + i + 3] * alpha_prev + v[i + 3]) * inv);
-                o.z = pack_bf16((acc[c + i + 4] * alpha_prev + v[i + 4]) * inv, (acc[c + i + 5] * alpha_prev + v[i + 5]) * inv);
-                o.w = pack_bf16((acc[c + i + 6] * alpha_prev + v[i + 6]) * inv, (acc[c + i + 7] * alpha_prev + v[i + 7]) * inv);
-                *reinterpret_cast<uint4*>(dst + c + i) = o;
-              }
+              for (int i = 0; i < 32; i += 8)
+                *reinterpret_cast<uint4*>(dst + c + i) =
+                    make_uint4(pack_bf16(v[i] * inv, v[i + 1] * inv), pack_bf16(v[i + 2] * inv, v[i + 3] * inv),
+                               pack_bf16(v[i + 4] * inv, v[i + 5] * inv), pack_bf16(v[i + 6] * inv, v[i + 7] * inv));
             }
           }
           tc_fence_before();
           if (row_ok && p.lse != nullptr)
             p.lse[(long long)h * p.Tq + q_beg + q_pos] =
-                l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+                l_run > 0.f ? (m_ref + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
         }
       }
     }
