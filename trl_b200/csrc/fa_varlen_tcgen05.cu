@@ -426,8 +426,13 @@ constexpr int FB_C = 64;                                  // inner chunk (keys f
 constexpr uint32_t FB_CHUNK_BYTES = FB_C * 128 * 2;       // [64 x 128] bf16 = two boxes of [64 rows x 64]
 constexpr uint32_t FB_CBOX_BYTES = FB_C * 64 * 2;
 constexpr uint32_t FB_T64_BYTES = 128 * 64 * 2;           // [128 x 64] bf16 K-major tile (dS, P^T, dS^T)
-constexpr size_t FA_DQ_SMEM = 2 * FA_TILE_BYTES + 2 * 2 * FB_CHUNK_BYTES + FB_T64_BYTES + 1024 + 512;
-constexpr size_t FA_DKV_SMEM = 2 * FA_TILE_BYTES + 2 * 2 * FB_CHUNK_BYTES + 2 * FB_T64_BYTES + 2 * 2 * FB_C * 4 + 1024 + 512;
+// The chunk rings are deeper than the two TMEM buffers they feed: a stage is refilled only when the second MMA of
+// its chunk has finished, and a TMA round trip (L2 or HBM to shared memory) is longer than the work on one chunk.
+constexpr int FB_QD_STAGES = 3;  // dK/dV kernel: ring of (Q chunk, dO chunk) pairs
+constexpr int FB_KV_STAGES = 4;  // dQ kernel: ring of (K chunk, V chunk) pairs
+constexpr size_t FA_DQ_SMEM = 2 * FA_TILE_BYTES + FB_KV_STAGES * 2 * FB_CHUNK_BYTES + FB_T64_BYTES + 1024 + 512;
+constexpr size_t FA_DKV_SMEM = 2 * FA_TILE_BYTES + FB_QD_STAGES * 2 * FB_CHUNK_BYTES + 2 * FB_T64_BYTES +
+                               FB_QD_STAGES * 2 * FB_C * 4 + 1024 + 512;
 
 struct FaBwdParams {
   const int* cu_q;
@@ -476,17 +481,17 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint8_t* q_s = smem;
   uint8_t* do_s = smem + FA_TILE_BYTES;
   uint8_t* kv_s = smem + 2 * FA_TILE_BYTES;  // stage s: K chunk then V chunk
-  uint8_t* ds_s = kv_s + 2 * 2 * FB_CHUNK_BYTES;
+  uint8_t* ds_s = kv_s + FB_KV_STAGES * 2 * FB_CHUNK_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ds_s + FB_T64_BYTES);
   uint64_t* qdo_full = bars;
-  uint64_t* kv_full = bars + 1;     // [2]
-  uint64_t* kv_empty = bars + 3;    // [2]
-  uint64_t* sp_full = bars + 5;     // [2]  S and dP of a chunk are complete
-  uint64_t* sp_empty = bars + 7;    // [2]
-  uint64_t* ds_full = bars + 9;
-  uint64_t* ds_empty = bars + 10;
-  uint64_t* dq_done = bars + 11;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* kv_full = bars + 1;                      // [FB_KV_STAGES]
+  uint64_t* kv_empty = kv_full + FB_KV_STAGES;       // [FB_KV_STAGES]
+  uint64_t* sp_full = kv_empty + FB_KV_STAGES;       // [2]  S and dP of a chunk are complete
+  uint64_t* sp_empty = sp_full + 2;                  // [2]
+  uint64_t* ds_full = sp_empty + 2;
+  uint64_t* ds_empty = ds_full + 1;
+  uint64_t* dq_done = ds_empty + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -501,9 +506,11 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < FB_KV_STAGES; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&sp_full[s], 1);
       mbar_init(&sp_empty[s], 4);
     }
@@ -537,8 +544,8 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tma_load_2d(do_s, &tmap_do, qdo_full, h * FA_D, qrow);
         tma_load_2d(do_s + FA_BOX_BYTES, &tmap_do, qdo_full, h * FA_D + 64, qrow);
         for (int j = 0; j < n_c; ++j) {
-          const int s = j & 1;
-          if (!mbar_wait(&kv_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, p.status, 1100 + s)) break;
+          const int s = j % FB_KV_STAGES;
+          if (!mbar_wait(&kv_empty[s], (uint32_t)(((j / FB_KV_STAGES) & 1) ^ 1), abort_flag, p.status, 1100 + s)) break;
           uint8_t* ks = kv_s + (size_t)s * 2 * FB_CHUNK_BYTES;
           uint8_t* vs = ks + FB_CHUNK_BYTES;
           const int row = k_beg + (c_lo + j) * FB_C;
@@ -557,11 +564,11 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const uint32_t q_u = smem_u32(q_s), do_u = smem_u32(do_s), kv_u = smem_u32(kv_s), ds_u = smem_u32(ds_s);
         bool ok = mbar_wait(qdo_full, 0, abort_flag, p.status, 1110);
         auto issue_sp = [&](int j) {
-          const int s = j & 1;
-          if (!mbar_wait(&kv_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1120 + s)) return false;
+          const int s = j & 1, ks = j % FB_KV_STAGES;  // TMEM buffer, ring stage
+          if (!mbar_wait(&kv_full[ks], (uint32_t)((j / FB_KV_STAGES) & 1), abort_flag, p.status, 1120 + ks)) return false;
           if (!mbar_wait(&sp_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, p.status, 1130 + s)) return false;
           tc_fence_after();
-          const uint32_t k_u = kv_u + (uint32_t)s * 2 * FB_CHUNK_BYTES, v_u = k_u + FB_CHUNK_BYTES;
+          const uint32_t k_u = kv_u + (uint32_t)ks * 2 * FB_CHUNK_BYTES, v_u = k_u + FB_CHUNK_BYTES;
 #pragma unroll
           for (int kk = 0; kk < FA_D / 16; ++kk) {
             const uint32_t qo = (uint32_t)(kk >> 2) * FA_BOX_BYTES, co = (uint32_t)(kk >> 2) * FB_CBOX_BYTES;
@@ -579,7 +586,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         };
         if (ok) ok = issue_sp(0);
         for (int j = 0; j < n_c && ok; ++j) {
-          const int s = j & 1;
+          const int s = j % FB_KV_STAGES;
           if (j + 1 < n_c) ok = issue_sp(j + 1);
           if (!ok) break;
           if (!mbar_wait(ds_full, (uint32_t)(j & 1), abort_flag, p.status, 1140)) { ok = false; break; }
@@ -610,10 +617,17 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         lse2 = l == -INFINITY ? INFINITY : l * 1.4426950408889634f;
         dl = p.delta[(long long)h * p.Tq + q_beg + q_pos];
       }
+      const float neg_lse = -lse2;
+      const int q_first = tile * FA_BM;
       bool ok = true;
       for (int j = 0; j < n_c && ok; ++j) {
         const int s = j & 1;
         const int key0 = (c_lo + j) * FB_C;
+        bool full = (q_first + FA_BM <= lq) && (key0 + FB_C <= lk);
+        if (p.causal) {
+          full = full && (key0 + FB_C - 1 <= q_first + off);
+          if (p.window > 0) full = full && (key0 >= q_first + FA_BM - 1 + off - p.window + 1);
+        }
         ok = __all_sync(0xffffffffu, mbar_wait(&sp_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1150 + s));
         if (!ok) break;
         tc_fence_after();
@@ -626,23 +640,23 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           tmem_ld_32x32(ts + c, sv);
           tmem_ld_32x32(ts + 64 + c, dp);
           tmem_ld_wait();
+          if (full) {  // every row sees every key of the chunk
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint32_t w[4];
+            for (int i = 0; i < 32; ++i)
+              sv[i] = fast_exp2(fmaf(sv[i], p.scale_log2, neg_lse)) * ((dp[i] - dl) * p.scale);
+          } else {
 #pragma unroll
-            for (int e = 0; e < 8; e += 2) {
-              float d2[2];
-#pragma unroll
-              for (int u = 0; u < 2; ++u) {
-                const int key = key0 + c + i + e + u;
-                const bool a = row_ok && key >= k_min && key <= k_max;
-                const float pr = a ? exp2f(sv[i + e + u] * p.scale_log2 - lse2) : 0.f;
-                d2[u] = pr * (dp[i + e + u] - dl) * p.scale;
-              }
-              w[e >> 1] = pack_bf16(d2[0], d2[1]);
+            for (int i = 0; i < 32; ++i) {
+              const int key = key0 + c + i;
+              const bool a = row_ok && key >= k_min && key <= k_max;
+              sv[i] = a ? fast_exp2(fmaf(sv[i], p.scale_log2, neg_lse)) * ((dp[i] - dl) * p.scale) : 0.f;
             }
-            *reinterpret_cast<uint4*>(ds_s + fb_t64_off(r, c + i)) = make_uint4(w[0], w[1], w[2], w[3]);
           }
+#pragma unroll
+          for (int i = 0; i < 32; i += 8)
+            *reinterpret_cast<uint4*>(ds_s + fb_t64_off(r, c + i)) =
+                make_uint4(pack_bf16(sv[i], sv[i + 1]), pack_bf16(sv[i + 2], sv[i + 3]), pack_bf16(sv[i + 4], sv[i + 5]),
+                           pack_bf16(sv[i + 6], sv[i + 7]));
         }
         tc_fence_before();
         __syncwarp();
@@ -710,19 +724,19 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   uint8_t* k_s = smem;
   uint8_t* v_s = smem + FA_TILE_BYTES;
   uint8_t* qd_s = smem + 2 * FA_TILE_BYTES;      // stage s: Q chunk then dO chunk
-  uint8_t* pt_s = qd_s + 2 * 2 * FB_CHUNK_BYTES;  // P^T  [128 keys x 64 queries]
-  uint8_t* dst_s = pt_s + FB_T64_BYTES;           // dS^T
-  float* stat_s = reinterpret_cast<float*>(dst_s + FB_T64_BYTES);  // [2 stages][lse2 x 64, delta x 64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stat_s + 2 * 2 * FB_C);
+  uint8_t* pt_s = qd_s + FB_QD_STAGES * 2 * FB_CHUNK_BYTES;  // P^T  [128 keys x 64 queries]
+  uint8_t* dst_s = pt_s + FB_T64_BYTES;                      // dS^T
+  float* stat_s = reinterpret_cast<float*>(dst_s + FB_T64_BYTES);  // [stage][lse2 x 64, delta x 64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stat_s + FB_QD_STAGES * 2 * FB_C);
   uint64_t* kv_full = bars;
-  uint64_t* qd_full = bars + 1;    // [2]
-  uint64_t* qd_empty = bars + 3;   // [2]
-  uint64_t* sp_full = bars + 5;    // [2]
-  uint64_t* sp_empty = bars + 7;   // [2]
-  uint64_t* pd_full = bars + 9;
-  uint64_t* pd_empty = bars + 10;
-  uint64_t* acc_done = bars + 11;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* qd_full = bars + 1;                  // [FB_QD_STAGES]
+  uint64_t* qd_empty = qd_full + FB_QD_STAGES;   // [FB_QD_STAGES]
+  uint64_t* sp_full = qd_empty + FB_QD_STAGES;   // [2]
+  uint64_t* sp_empty = sp_full + 2;              // [2]
+  uint64_t* pd_full = sp_empty + 2;
+  uint64_t* pd_empty = pd_full + 1;
+  uint64_t* acc_done = pd_empty + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -742,9 +756,11 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < FB_QD_STAGES; ++s) {
       mbar_init(&qd_full[s], 33);  // the TMA transaction + 32 lanes that stage lse / delta
       mbar_init(&qd_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&sp_full[s], 1);
       mbar_init(&sp_empty[s], 4);
     }
@@ -780,10 +796,21 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
       bool ok = true;
       for (int j = 0; j < n_it && ok; ++j) {
-        const int s = j & 1;
+        const int s = j % FB_QD_STAGES;
         const int h = kvh * G + j / per_head, qc = qc_lo + j % per_head;
-        ok = __all_sync(0xffffffffu, mbar_wait(&qd_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, p.status, 1200 + s));
+        ok = __all_sync(0xffffffffu, mbar_wait(&qd_empty[s], (uint32_t)(((j / FB_QD_STAGES) & 1) ^ 1), abort_flag, p.status, 1200 + s));
         if (!ok) break;
+        if (lane == 0) {  // the bulk copies first: the scalar loads below then run under their latency
+          uint8_t* qs = qd_s + (size_t)s * 2 * FB_CHUNK_BYTES;
+          uint8_t* ds = qs + FB_CHUNK_BYTES;
+          const int row = q_beg + qc * FB_C;
+          mbar_expect_tx(&qd_full[s], 2 * FB_CHUNK_BYTES);
+          tma_load_2d(qs, &tmap_q, &qd_full[s], h * FA_D, row);
+          tma_load_2d(qs + FB_CBOX_BYTES, &tmap_q, &qd_full[s], h * FA_D + 64, row);
+          tma_load_2d(ds, &tmap_do, &qd_full[s], h * FA_D, row);
+          tma_load_2d(ds + FB_CBOX_BYTES, &tmap_do, &qd_full[s], h * FA_D + 64, row);
+        }
+        __syncwarp();
         float* st = stat_s + s * 2 * FB_C;
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
@@ -797,16 +824,6 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           st[lane + 32 * u] = l2;
           st[FB_C + lane + 32 * u] = dl;
         }
-        if (lane == 0) {
-          uint8_t* qs = qd_s + (size_t)s * 2 * FB_CHUNK_BYTES;
-          uint8_t* ds = qs + FB_CHUNK_BYTES;
-          const int row = q_beg + qc * FB_C;
-          mbar_expect_tx(&qd_full[s], 2 * FB_CHUNK_BYTES);
-          tma_load_2d(qs, &tmap_q, &qd_full[s], h * FA_D, row);
-          tma_load_2d(qs + FB_CBOX_BYTES, &tmap_q, &qd_full[s], h * FA_D + 64, row);
-          tma_load_2d(ds, &tmap_do, &qd_full[s], h * FA_D, row);
-          tma_load_2d(ds + FB_CBOX_BYTES, &tmap_do, &qd_full[s], h * FA_D + 64, row);
-        }
         mbar_arrive(&qd_full[s]);  // this lane's lse / delta are in shared memory (release)
       }
     } else if (warp == 1) {
@@ -817,11 +834,11 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         const uint32_t pt_u = smem_u32(pt_s), dst_u = smem_u32(dst_s);
         bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, 1210);
         auto issue_sp = [&](int j) {
-          const int s = j & 1;
-          if (!mbar_wait(&qd_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1220 + s)) return false;
+          const int s = j & 1, qs = j % FB_QD_STAGES;  // TMEM buffer, ring stage
+          if (!mbar_wait(&qd_full[qs], (uint32_t)((j / FB_QD_STAGES) & 1), abort_flag, p.status, 1220 + qs)) return false;
           if (!mbar_wait(&sp_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, p.status, 1230 + s)) return false;
           tc_fence_after();
-          const uint32_t q_u = qd_u + (uint32_t)s * 2 * FB_CHUNK_BYTES, do_u = q_u + FB_CHUNK_BYTES;
+          const uint32_t q_u = qd_u + (uint32_t)qs * 2 * FB_CHUNK_BYTES, do_u = q_u + FB_CHUNK_BYTES;
 #pragma unroll
           for (int kk = 0; kk < FA_D / 16; ++kk) {
             const uint32_t to = (uint32_t)(kk >> 2) * FA_BOX_BYTES, co = (uint32_t)(kk >> 2) * FB_CBOX_BYTES;
@@ -839,7 +856,7 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         };
         if (ok) ok = issue_sp(0);
         for (int j = 0; j < n_it && ok; ++j) {
-          const int s = j & 1;
+          const int s = j % FB_QD_STAGES;
           if (j + 1 < n_it) ok = issue_sp(j + 1);
           if (!ok) break;
           if (!mbar_wait(pd_full, (uint32_t)(j & 1), abort_flag, p.status, 1240)) { ok = false; break; }
@@ -869,12 +886,17 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       for (int j = 0; j < n_it && ok; ++j) {
         const int s = j & 1;
         const int q0 = (qc_lo + j % per_head) * FB_C;
+        bool full = (key_first + FA_BN <= lk) && (q0 + FB_C <= lq);
+        if (p.causal) {
+          full = full && (key_first + FA_BN - 1 <= q0 + off);
+          if (p.window > 0) full = full && (key_first > q0 + FB_C - 1 + off - p.window);
+        }
         ok = __all_sync(0xffffffffu, mbar_wait(&sp_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1250 + s));
         if (!ok) break;
         tc_fence_after();
         ok = __all_sync(0xffffffffu, mbar_wait(pd_empty, (uint32_t)((j & 1) ^ 1), abort_flag, p.status, 1260));
         if (!ok) break;
-        const float* st = stat_s + s * 2 * FB_C;  // visible: sp_full follows the MMA that waited on qd_full
+        const float* st = stat_s + (j % FB_QD_STAGES) * 2 * FB_C;  // visible: sp_full follows the MMA that waited on qd_full
         const uint32_t ts = tmem_base + lane_off + (uint32_t)s * 128;
 #pragma unroll 1
         for (int c = 0; c < FB_C; c += 32) {
@@ -882,29 +904,33 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           tmem_ld_32x32(ts + c, sv);
           tmem_ld_32x32(ts + 64 + c, dp);
           tmem_ld_wait();
+          if (full) {  // every key of the tile is seen by every query of the chunk
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              sv[i] = fast_exp2(fmaf(sv[i], p.scale_log2, -st[c + i]));
+              dp[i] = sv[i] * ((dp[i] - st[FB_C + c + i]) * p.scale);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int qp = q0 + c + i;
+              bool a = key_ok;
+              if (p.causal) {
+                a = a && key <= qp + off;
+                if (p.window > 0) a = a && key > qp + off - p.window;
+              }
+              sv[i] = a ? fast_exp2(fmaf(sv[i], p.scale_log2, -st[c + i])) : 0.f;
+              dp[i] = sv[i] * ((dp[i] - st[FB_C + c + i]) * p.scale);
+            }
+          }
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
-            uint32_t wp[4], wd[4];
-#pragma unroll
-            for (int e = 0; e < 8; e += 2) {
-              float pp[2], dd[2];
-#pragma unroll
-              for (int u = 0; u < 2; ++u) {
-                const int qi = c + i + e + u, qp = q0 + qi;
-                bool a = key_ok;
-                if (p.causal) {
-                  a = a && key <= qp + off;
-                  if (p.window > 0) a = a && key > qp + off - p.window;
-                }
-                const float pr = a ? exp2f(sv[i + e + u] * p.scale_log2 - st[qi]) : 0.f;
-                pp[u] = pr;
-                dd[u] = pr * (dp[i + e + u] - st[FB_C + qi]) * p.scale;
-              }
-              wp[e >> 1] = pack_bf16(pp[0], pp[1]);
-              wd[e >> 1] = pack_bf16(dd[0], dd[1]);
-            }
-            *reinterpret_cast<uint4*>(pt_s + fb_t64_off(r, c + i)) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
-            *reinterpret_cast<uint4*>(dst_s + fb_t64_off(r, c + i)) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+            *reinterpret_cast<uint4*>(pt_s + fb_t64_off(r, c + i)) =
+                make_uint4(pack_bf16(sv[i], sv[i + 1]), pack_bf16(sv[i + 2], sv[i + 3]), pack_bf16(sv[i + 4], sv[i + 5]),
+                           pack_bf16(sv[i + 6], sv[i + 7]));
+            *reinterpret_cast<uint4*>(dst_s + fb_t64_off(r, c + i)) =
+                make_uint4(pack_bf16(dp[i], dp[i + 1]), pack_bf16(dp[i + 2], dp[i + 3]), pack_bf16(dp[i + 4], dp[i + 5]),
+                           pack_bf16(dp[i + 6], dp[i + 7]));
           }
         }
         tc_fence_before();
