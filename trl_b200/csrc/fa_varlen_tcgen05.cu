@@ -8,16 +8,17 @@
 //   mask), an optional sliding window, or none.
 //
 // Forward, one CTA per (128-query tile, query head), 192 threads:
-//   warp 0   TMA: the Q tile once, then K and V tiles of 128 keys through a 2-stage ring (separate barriers, so
-//            Q.K^T starts when K has landed);
+//   warp 0   TMA: the Q tile once, then K tiles of 128 keys through a 3-stage ring and V tiles through a 2-stage
+//            ring (a K stage is released by Q.K^T, a V stage by P.V);
 //   warp 1   tcgen05.mma: S_j = Q K_j^T into one of two TMEM buffers (issued one tile ahead, so the softmax of
 //            tile j runs under Q.K_{j+1}^T), then O += P_j V_j accumulating in TMEM over all key tiles.  V is
 //            consumed as an MN-major operand straight from its TMA tile: no transpose anywhere;
 //   warps 2-5 one thread per query row: maximum, exponentials in base 2 against a reference maximum that moves only
-//            when a tile exceeds it by 2^8 (then, and only then, the warp rescales its rows of O in TMEM), P_j
-//            written as a K-major swizzled bf16 tile for the second MMA.  Tiles that every row sees completely skip
-//            the per-element mask tests.
-//   TMEM: S0 S1 O = 384 columns.  Output bf16 + log-sum-exp (natural log, fp32 [Hq, Tq]) for the backward.
+//            when a tile exceeds it by 2^8 (then, and only then, the warp rescales its rows of O in TMEM).  P_j goes
+//            back into tensor memory as bf16 pairs over the first half of S_j's own columns and is the A operand
+//            of the second MMA from there: no shared-memory tile, no proxy fence, and it is double-buffered for
+//            free.  Tiles that every row sees completely skip the per-element mask tests.
+//   TMEM: S0/P0 S1/P1 O = 384 columns.  Output bf16 + log-sum-exp (natural log, fp32 [Hq, Tq]) for the backward.
 //
 // Every wait is bounded (common.cuh); a wait that runs out reports through the status words and the CTA leaves
 // through the normal teardown.
@@ -32,8 +33,11 @@ constexpr int FA_BM = 128, FA_BN = 128, FA_D = 128;
 constexpr int FA_THREADS = 192;
 constexpr uint32_t FA_TILE_BYTES = 128 * 128 * 2;  // a [128 x 128] bf16 tile = two TMA boxes of [128 rows x 64]
 constexpr uint32_t FA_BOX_BYTES = 128 * 64 * 2;
-constexpr int FA_KV_STAGES = 2;
-constexpr size_t FA_FWD_SMEM = FA_TILE_BYTES /*Q*/ + FA_TILE_BYTES /*P*/ + FA_KV_STAGES * 2 * FA_TILE_BYTES + 1024 + 512;
+// K and V tiles travel through rings of their own: a K stage is free again as soon as Q.K^T of its tile has run
+// (one tile ahead of the softmax), a V stage only after P.V, so K gets the third stage and its loads start a full
+// tile earlier than they could in a shared ring.
+constexpr int FA_K_STAGES = 3, FA_V_STAGES = 3;
+constexpr size_t FA_FWD_SMEM = FA_TILE_BYTES /*Q*/ + (FA_K_STAGES + FA_V_STAGES) * FA_TILE_BYTES + 1024 + 512;
 
 struct FaParams {
   const int* cu_q;
@@ -86,19 +90,18 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_s = smem;
-  uint8_t* p_s = smem + FA_TILE_BYTES;
-  uint8_t* kv_s = smem + 2 * FA_TILE_BYTES;  // stage s: K at s * 2 tiles, V one tile after it
-  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + FA_KV_STAGES * 2 * FA_TILE_BYTES);
+  uint8_t* k_s = smem + FA_TILE_BYTES;                 // [FA_K_STAGES] K tiles
+  uint8_t* v_s = k_s + FA_K_STAGES * FA_TILE_BYTES;    // [FA_V_STAGES] V tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + FA_V_STAGES * FA_TILE_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;     // [2]
-  uint64_t* v_full = bars + 3;     // [2]
-  uint64_t* kv_empty = bars + 5;   // [2]
-  uint64_t* s_full = bars + 7;     // [2]
-  uint64_t* s_empty = bars + 9;    // [2]
-  uint64_t* o_full = bars + 11;    // one phase per P.V product
-  uint64_t* p_full = bars + 15;
-  uint64_t* p_empty = bars + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  uint64_t* k_full = bars + 1;                  // [FA_K_STAGES]
+  uint64_t* k_empty = k_full + FA_K_STAGES;     // [FA_K_STAGES]
+  uint64_t* v_full = k_empty + FA_K_STAGES;     // [FA_V_STAGES]
+  uint64_t* v_empty = v_full + FA_V_STAGES;     // [FA_V_STAGES]
+  uint64_t* s_full = v_empty + FA_V_STAGES;     // [2]
+  uint64_t* o_full = s_full + 2;                // one phase per P.V product
+  uint64_t* p_full = o_full + 1;                // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_full + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -111,16 +114,19 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < FA_K_STAGES; ++s) {
       mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+    }
+    for (int s = 0; s < FA_V_STAGES; ++s) {
       mbar_init(&v_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 4);
+      mbar_init(&p_full[s], 128);
     }
     mbar_init(o_full, 1);
-    mbar_init(p_full, 128);
-    mbar_init(p_empty, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_q);
@@ -143,15 +149,25 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         mbar_expect_tx(q_full, FA_TILE_BYTES);
         tma_load_2d(q_s, &tmap_q, q_full, h * FA_D, q_beg + tile * FA_BM);
         tma_load_2d(q_s + FA_BOX_BYTES, &tmap_q, q_full, h * FA_D + 64, q_beg + tile * FA_BM);
-        for (int j = 0; j < n_kv; ++j) {
-          const int s = j & 1;
-          if (!mbar_wait(&kv_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, p.status, 1000 + s)) break;
-          uint8_t* ks = kv_s + (size_t)s * 2 * FA_TILE_BYTES;
-          uint8_t* vs = ks + FA_TILE_BYTES;
+        auto load_k = [&](int j) {
+          const int s = j % FA_K_STAGES;
+          if (!mbar_wait(&k_empty[s], (uint32_t)(((j / FA_K_STAGES) & 1) ^ 1), abort_flag, p.status, 1000 + s)) return false;
+          uint8_t* ks = k_s + (size_t)s * FA_TILE_BYTES;
           const int row = k_beg + (lo + j) * FA_BN;
           mbar_expect_tx(&k_full[s], FA_TILE_BYTES);
           tma_load_2d(ks, &tmap_k, &k_full[s], kvh * FA_D, row);
           tma_load_2d(ks + FA_BOX_BYTES, &tmap_k, &k_full[s], kvh * FA_D + 64, row);
+          return true;
+        };
+        // order K(0) K(1) V(0) K(2) V(1) ...: a V stage frees later than the K stage asked for after it
+        bool ok = load_k(0);
+        for (int j = 0; j < n_kv && ok; ++j) {
+          if (j + 1 < n_kv) ok = load_k(j + 1);
+          if (!ok) break;
+          const int s = j % FA_V_STAGES;
+          if (!mbar_wait(&v_empty[s], (uint32_t)(((j / FA_V_STAGES) & 1) ^ 1), abort_flag, p.status, 1005 + s)) break;
+          uint8_t* vs = v_s + (size_t)s * FA_TILE_BYTES;
+          const int row = k_beg + (lo + j) * FA_BN;
           mbar_expect_tx(&v_full[s], FA_TILE_BYTES);
           tma_load_2d(vs, &tmap_v, &v_full[s], kvh * FA_D, row);
           tma_load_2d(vs + FA_BOX_BYTES, &tmap_v, &v_full[s], kvh * FA_D + 64, row);
@@ -163,14 +179,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       if (lane == 0) {
         constexpr uint32_t idesc_s = umma_idesc_bf16_major(FA_BM, FA_BN, false, false);
         constexpr uint32_t idesc_o = umma_idesc_bf16_major(FA_BM, FA_D, false, true);  // V is MN-major
-        const uint32_t q_u = smem_u32(q_s), p_u = smem_u32(p_s), kv_u = smem_u32(kv_s);
+        const uint32_t q_u = smem_u32(q_s), ks_u = smem_u32(k_s), vs_u = smem_u32(v_s);
         bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 1010);
         auto issue_s = [&](int j) {
-          const int s = j & 1;
-          if (!mbar_wait(&k_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1020 + s)) return false;
-          if (!mbar_wait(&s_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, p.status, 1030 + s)) return false;
+          const int s = j & 1, kst = j % FA_K_STAGES;  // TMEM buffer, K ring stage
+          // buffer s is free: it held S and then P of tile j - 2, whose P.V product was issued before this call
+          if (!mbar_wait(&k_full[kst], (uint32_t)((j / FA_K_STAGES) & 1), abort_flag, p.status, 1020 + kst)) return false;
           tc_fence_after();
-          const uint32_t k_u = kv_u + (uint32_t)s * 2 * FA_TILE_BYTES;
+          const uint32_t k_u = ks_u + (uint32_t)kst * FA_TILE_BYTES;
 #pragma unroll
           for (int kk = 0; kk < FA_D / 16; ++kk) {
             const uint32_t off = (uint32_t)(kk >> 2) * FA_BOX_BYTES;
@@ -178,28 +194,30 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                          umma_desc_kmajor_sw128(k_u + off) + 2 * (kk & 3), idesc_s, kk != 0);
           }
           umma_commit(&s_full[s]);
+          umma_commit(&k_empty[kst]);
           return true;
         };
         if (ok) ok = issue_s(0);
         for (int j = 0; j < n_kv && ok; ++j) {
-          const int s = j & 1;
+          const int s = j % FA_V_STAGES;
           if (j + 1 < n_kv) ok = issue_s(j + 1);
           if (!ok) break;
-          if (!mbar_wait(p_full, (uint32_t)(j & 1), abort_flag, p.status, 1040)) { ok = false; break; }
-          if (!mbar_wait(&v_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1050 + s)) { ok = false; break; }
+          const int sb = j & 1;  // the TMEM buffer that held S_j now holds P_j (bf16 pairs in its first 64 columns)
+          if (!mbar_wait(&p_full[sb], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1040 + sb)) { ok = false; break; }
+          if (!mbar_wait(&v_full[s], (uint32_t)((j / FA_V_STAGES) & 1), abort_flag, p.status, 1050 + s)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t v_u = kv_u + (uint32_t)s * 2 * FA_TILE_BYTES + FA_TILE_BYTES;
+          const uint32_t v_u = vs_u + (uint32_t)s * FA_TILE_BYTES;
 #pragma unroll
           for (int kk = 0; kk < FA_BN / 16; ++kk) {
-            const uint64_t adesc = umma_desc_kmajor_sw128(p_u + (uint32_t)(kk >> 2) * FA_BOX_BYTES) + 2 * (kk & 3);
             const uint64_t bdesc = umma_desc_mnmajor_sw128(v_u + (uint32_t)kk * 2048, FA_BOX_BYTES);
-            // O accumulates in TMEM over all key tiles; the row threads rescale it in place when a row's reference
-            // maximum moves (see below), always between two P.V products
-            umma_bf16_ss(tmem_base + 256, adesc, bdesc, idesc_o, (j != 0) || (kk != 0));
+            // P is the A operand straight from tensor memory (16 keys = 8 columns per step).  O accumulates in TMEM
+            // over all key tiles; the row threads rescale it in place when a row's reference maximum moves (see
+            // below), always between two P.V products
+            umma_bf16_ts(tmem_base + 256, tmem_base + (uint32_t)sb * FA_BN + (uint32_t)kk * 8, bdesc, idesc_o,
+                         (j != 0) || (kk != 0));
           }
           umma_commit(o_full);
-          umma_commit(&kv_empty[s]);
-          umma_commit(p_empty);
+          umma_commit(&v_empty[s]);
         }
       }
       __syncwarp();
@@ -284,9 +302,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         }
         l_run *= alpha;
         const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-        // pass 2: probabilities -> P tile (bf16, K-major swizzled), row sum
-        ok = __all_sync(0xffffffffu, mbar_wait(p_empty, (uint32_t)((j & 1) ^ 1), abort_flag, p.status, 1080));
-        if (!ok) break;
+        // pass 2: probabilities, row sum; P_j (bf16 pairs) overwrites the columns of S_j this thread has already read
         float sum = 0.f;
 #pragma unroll 1
         for (int c = 0; c < FA_BN; c += 32) {
@@ -308,17 +324,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
               sum += v[i];
             }
           }
+          uint32_t w[16];
 #pragma unroll
-          for (int i = 0; i < 32; i += 8)
-            *reinterpret_cast<uint4*>(p_s + fa_kmajor_off(r, c + i)) =
-                make_uint4(pack_bf16(v[i], v[i + 1]), pack_bf16(v[i + 2], v[i + 3]), pack_bf16(v[i + 4], v[i + 5]),
-                           pack_bf16(v[i + 6], v[i + 7]));
+          for (int i = 0; i < 16; ++i) w[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+          tmem_st_32x16(ts + (c >> 1), w);
         }
+        tmem_st_wait();
         tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s_empty[s]);
-        fence_proxy_async_smem();
-        mbar_arrive(p_full);
+        mbar_arrive(&p_full[s]);
         l_run += sum;
       }
       if (ok) {
