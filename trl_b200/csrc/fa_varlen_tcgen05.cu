@@ -77,11 +77,6 @@ __device__ __forceinline__ void fa_kv_range(int tile, int lq, int lk, int causal
 }
 
 // byte offset of element (row r, column c) in a [128 x 128] bf16 K-major tile stored as two 128-byte-swizzled boxes
-__device__ __forceinline__ uint32_t fa_kmajor_off(int r, int c) {
-  return (uint32_t)((c >> 6) * FA_BOX_BYTES + (r >> 3) * 1024 + (r & 7) * 128 + ((((c & 63) >> 3) ^ (r & 7)) << 4) +
-                    (c & 7) * 2);
-}
-
 __global__ void __launch_bounds__(FA_THREADS, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
               const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
@@ -424,8 +419,9 @@ TRLB_API int trlb_fa_varlen_fwd(const void* q, const void* k, const void* v, lon
 //     dV = P^T dO        dP = dO V^T        dS = P o (dP - delta) * scale        dQ = dS K        dK = dS^T Q
 // Two kernels share no accumulator, so nothing is added atomically:
 //   fa_bwd_dq_kernel   one CTA per (128-query tile, query head); walks the visible keys in chunks of 64:
-//                      S = Q K_c^T and dP = dO V_c^T into TMEM (double-buffered), the row threads form dS (bf16,
-//                      K-major tile in shared memory), dQ += dS K_c accumulates in TMEM (K_c as an MN-major operand).
+//                      S = Q K_c^T and dP = dO V_c^T into TMEM (double-buffered), the row threads form dS (bf16
+//                      pairs written back over S in TMEM), dQ += dS K_c accumulates in TMEM (dS as the A operand
+//                      from tensor memory, K_c as an MN-major operand).
 //   fa_bwd_dkv_kernel  one CTA per (128-key tile, KV head); walks the query heads of the group and, for each, the
 //                      queries that see the tile in chunks of 64: S^T = K Q_c^T and dP^T = V dO_c^T into TMEM, the
 //                      row threads (one per key) form P^T and dS^T, dV += P^T dO_c and dK += dS^T Q_c accumulate in
@@ -438,14 +434,14 @@ namespace trlb {
 constexpr int FB_C = 64;                                  // inner chunk (keys for dQ, queries for dK/dV)
 constexpr uint32_t FB_CHUNK_BYTES = FB_C * 128 * 2;       // [64 x 128] bf16 = two boxes of [64 rows x 64]
 constexpr uint32_t FB_CBOX_BYTES = FB_C * 64 * 2;
-constexpr uint32_t FB_T64_BYTES = 128 * 64 * 2;           // [128 x 64] bf16 K-major tile (dS, P^T, dS^T)
 // The chunk rings are deeper than the two TMEM buffers they feed: a stage is refilled only when the second MMA of
 // its chunk has finished, and a TMA round trip (L2 or HBM to shared memory) is longer than the work on one chunk.
-constexpr int FB_QD_STAGES = 3;  // dK/dV kernel: ring of (Q chunk, dO chunk) pairs
-constexpr int FB_KV_STAGES = 4;  // dQ kernel: ring of (K chunk, V chunk) pairs
-constexpr size_t FA_DQ_SMEM = 2 * FA_TILE_BYTES + FB_KV_STAGES * 2 * FB_CHUNK_BYTES + FB_T64_BYTES + 1024 + 512;
-constexpr size_t FA_DKV_SMEM = 2 * FA_TILE_BYTES + FB_QD_STAGES * 2 * FB_CHUNK_BYTES + 2 * FB_T64_BYTES +
-                               FB_QD_STAGES * 2 * FB_C * 4 + 1024 + 512;
+// dS (and P^T, dS^T in the other kernel) never visit shared memory: the row threads write them as bf16 pairs over the
+// tensor-memory columns of S / dP they have just read, and the second MMA takes them as its A operand from there.
+constexpr int FB_QD_STAGES = 4;  // dK/dV kernel: ring of (Q chunk, dO chunk) pairs
+constexpr int FB_KV_STAGES = 5;  // dQ kernel: ring of (K chunk, V chunk) pairs
+constexpr size_t FA_DQ_SMEM = 2 * FA_TILE_BYTES + FB_KV_STAGES * 2 * FB_CHUNK_BYTES + 1024 + 512;
+constexpr size_t FA_DKV_SMEM = 2 * FA_TILE_BYTES + FB_QD_STAGES * 2 * FB_CHUNK_BYTES + FB_QD_STAGES * 2 * FB_C * 4 + 1024 + 512;
 
 struct FaBwdParams {
   const int* cu_q;
@@ -478,11 +474,6 @@ fa_delta_kernel(const __nv_bfloat16* __restrict__ dout, long long do_rs, const _
   }
 }
 
-// byte offset of element (row r, column c < 64) in a [128 x 64] bf16 K-major 128-byte-swizzled tile
-__device__ __forceinline__ uint32_t fb_t64_off(int r, int c) {
-  return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + (((c >> 3) ^ (r & 7)) << 4) + (c & 7) * 2);
-}
-
 __global__ void __launch_bounds__(FA_THREADS, 1)
 fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                  const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
@@ -494,16 +485,13 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint8_t* q_s = smem;
   uint8_t* do_s = smem + FA_TILE_BYTES;
   uint8_t* kv_s = smem + 2 * FA_TILE_BYTES;  // stage s: K chunk then V chunk
-  uint8_t* ds_s = kv_s + FB_KV_STAGES * 2 * FB_CHUNK_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_s + FB_T64_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + FB_KV_STAGES * 2 * FB_CHUNK_BYTES);
   uint64_t* qdo_full = bars;
   uint64_t* kv_full = bars + 1;                      // [FB_KV_STAGES]
   uint64_t* kv_empty = kv_full + FB_KV_STAGES;       // [FB_KV_STAGES]
   uint64_t* sp_full = kv_empty + FB_KV_STAGES;       // [2]  S and dP of a chunk are complete
-  uint64_t* sp_empty = sp_full + 2;                  // [2]
-  uint64_t* ds_full = sp_empty + 2;
-  uint64_t* ds_empty = ds_full + 1;
-  uint64_t* dq_done = ds_empty + 1;
+  uint64_t* ds_full = sp_full + 2;                   // [2]  dS of a chunk is in tensor memory
+  uint64_t* dq_done = ds_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -525,10 +513,8 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sp_full[s], 1);
-      mbar_init(&sp_empty[s], 4);
+      mbar_init(&ds_full[s], 128);
     }
-    mbar_init(ds_full, 128);
-    mbar_init(ds_empty, 1);
     mbar_init(dq_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -574,12 +560,12 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       if (lane == 0) {
         constexpr uint32_t idesc_s = umma_idesc_bf16_major(FA_BM, FB_C, false, false);
         constexpr uint32_t idesc_dq = umma_idesc_bf16_major(FA_BM, FA_D, false, true);  // K chunk as MN-major operand
-        const uint32_t q_u = smem_u32(q_s), do_u = smem_u32(do_s), kv_u = smem_u32(kv_s), ds_u = smem_u32(ds_s);
+        const uint32_t q_u = smem_u32(q_s), do_u = smem_u32(do_s), kv_u = smem_u32(kv_s);
         bool ok = mbar_wait(qdo_full, 0, abort_flag, p.status, 1110);
         auto issue_sp = [&](int j) {
           const int s = j & 1, ks = j % FB_KV_STAGES;  // TMEM buffer, ring stage
+          // TMEM buffer s is free: the dQ product of chunk j - 2, which read dS from it, was issued before this call
           if (!mbar_wait(&kv_full[ks], (uint32_t)((j / FB_KV_STAGES) & 1), abort_flag, p.status, 1120 + ks)) return false;
-          if (!mbar_wait(&sp_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, p.status, 1130 + s)) return false;
           tc_fence_after();
           const uint32_t k_u = kv_u + (uint32_t)ks * 2 * FB_CHUNK_BYTES, v_u = k_u + FB_CHUNK_BYTES;
 #pragma unroll
@@ -602,15 +588,15 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           const int s = j % FB_KV_STAGES;
           if (j + 1 < n_c) ok = issue_sp(j + 1);
           if (!ok) break;
-          if (!mbar_wait(ds_full, (uint32_t)(j & 1), abort_flag, p.status, 1140)) { ok = false; break; }
+          const int sb = j & 1;
+          if (!mbar_wait(&ds_full[sb], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1140 + sb)) { ok = false; break; }
           tc_fence_after();
           const uint32_t k_u = kv_u + (uint32_t)s * 2 * FB_CHUNK_BYTES;
 #pragma unroll
           for (int kk = 0; kk < FB_C / 16; ++kk)
-            umma_bf16_ss(tmem_base + 256, umma_desc_kmajor_sw128(ds_u) + 2 * kk,
+            umma_bf16_ts(tmem_base + 256, tmem_base + (uint32_t)sb * 128 + (uint32_t)kk * 8,
                          umma_desc_mnmajor_sw128(k_u + (uint32_t)kk * 2048, FB_CBOX_BYTES), idesc_dq, (j | kk) != 0);
           umma_commit(&kv_empty[s]);
-          umma_commit(ds_empty);
         }
         if (ok) umma_commit(dq_done);
       }
@@ -644,8 +630,6 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         ok = __all_sync(0xffffffffu, mbar_wait(&sp_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1150 + s));
         if (!ok) break;
         tc_fence_after();
-        ok = __all_sync(0xffffffffu, mbar_wait(ds_empty, (uint32_t)((j & 1) ^ 1), abort_flag, p.status, 1160));
-        if (!ok) break;
         const uint32_t ts = tmem_base + lane_off + (uint32_t)s * 128;
 #pragma unroll 1
         for (int c = 0; c < FB_C; c += 32) {
@@ -665,17 +649,14 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
               sv[i] = a ? fast_exp2(fmaf(sv[i], p.scale_log2, neg_lse)) * ((dp[i] - dl) * p.scale) : 0.f;
             }
           }
+          uint32_t w[16];  // dS as bf16 pairs over the columns of S already read
 #pragma unroll
-          for (int i = 0; i < 32; i += 8)
-            *reinterpret_cast<uint4*>(ds_s + fb_t64_off(r, c + i)) =
-                make_uint4(pack_bf16(sv[i], sv[i + 1]), pack_bf16(sv[i + 2], sv[i + 3]), pack_bf16(sv[i + 4], sv[i + 5]),
-                           pack_bf16(sv[i + 6], sv[i + 7]));
+          for (int i = 0; i < 16; ++i) w[i] = pack_bf16(sv[2 * i], sv[2 * i + 1]);
+          tmem_st_32x16(ts + (c >> 1), w);
         }
+        tmem_st_wait();
         tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sp_empty[s]);
-        fence_proxy_async_smem();
-        mbar_arrive(ds_full);
+        mbar_arrive(&ds_full[s]);
       }
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(dq_done, 0, abort_flag, p.status, 1170));
       if (ok) {
@@ -737,18 +718,14 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   uint8_t* k_s = smem;
   uint8_t* v_s = smem + FA_TILE_BYTES;
   uint8_t* qd_s = smem + 2 * FA_TILE_BYTES;      // stage s: Q chunk then dO chunk
-  uint8_t* pt_s = qd_s + FB_QD_STAGES * 2 * FB_CHUNK_BYTES;  // P^T  [128 keys x 64 queries]
-  uint8_t* dst_s = pt_s + FB_T64_BYTES;                      // dS^T
-  float* stat_s = reinterpret_cast<float*>(dst_s + FB_T64_BYTES);  // [stage][lse2 x 64, delta x 64]
+  float* stat_s = reinterpret_cast<float*>(qd_s + FB_QD_STAGES * 2 * FB_CHUNK_BYTES);  // [stage][lse2 x 64, delta x 64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(stat_s + FB_QD_STAGES * 2 * FB_C);
   uint64_t* kv_full = bars;
   uint64_t* qd_full = bars + 1;                  // [FB_QD_STAGES]
   uint64_t* qd_empty = qd_full + FB_QD_STAGES;   // [FB_QD_STAGES]
   uint64_t* sp_full = qd_empty + FB_QD_STAGES;   // [2]
-  uint64_t* sp_empty = sp_full + 2;              // [2]
-  uint64_t* pd_full = sp_empty + 2;
-  uint64_t* pd_empty = pd_full + 1;
-  uint64_t* acc_done = pd_empty + 1;
+  uint64_t* pd_full = sp_full + 2;               // [2]  P^T and dS^T of a chunk are in tensor memory
+  uint64_t* acc_done = pd_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -775,10 +752,8 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sp_full[s], 1);
-      mbar_init(&sp_empty[s], 4);
+      mbar_init(&pd_full[s], 128);
     }
-    mbar_init(pd_full, 128);
-    mbar_init(pd_empty, 1);
     mbar_init(acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -844,12 +819,12 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         constexpr uint32_t idesc_st = umma_idesc_bf16_major(FA_BN, FB_C, false, false);
         constexpr uint32_t idesc_acc = umma_idesc_bf16_major(FA_BN, FA_D, false, true);  // dO / Q chunks MN-major
         const uint32_t k_u = smem_u32(k_s), v_u = smem_u32(v_s), qd_u = smem_u32(qd_s);
-        const uint32_t pt_u = smem_u32(pt_s), dst_u = smem_u32(dst_s);
         bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, 1210);
         auto issue_sp = [&](int j) {
           const int s = j & 1, qs = j % FB_QD_STAGES;  // TMEM buffer, ring stage
+          // TMEM buffer s is free: the dV / dK products of chunk j - 2, which read P^T / dS^T from it, were issued
+          // before this call
           if (!mbar_wait(&qd_full[qs], (uint32_t)((j / FB_QD_STAGES) & 1), abort_flag, p.status, 1220 + qs)) return false;
-          if (!mbar_wait(&sp_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, p.status, 1230 + s)) return false;
           tc_fence_after();
           const uint32_t q_u = qd_u + (uint32_t)qs * 2 * FB_CHUNK_BYTES, do_u = q_u + FB_CHUNK_BYTES;
 #pragma unroll
@@ -872,19 +847,20 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           const int s = j % FB_QD_STAGES;
           if (j + 1 < n_it) ok = issue_sp(j + 1);
           if (!ok) break;
-          if (!mbar_wait(pd_full, (uint32_t)(j & 1), abort_flag, p.status, 1240)) { ok = false; break; }
+          const int sb = j & 1;
+          if (!mbar_wait(&pd_full[sb], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1240 + sb)) { ok = false; break; }
           tc_fence_after();
           const uint32_t q_u = qd_u + (uint32_t)s * 2 * FB_CHUNK_BYTES, do_u = q_u + FB_CHUNK_BYTES;
+          const uint32_t pt_t = tmem_base + (uint32_t)sb * 128, dst_t = pt_t + 64;  // A operands in tensor memory
 #pragma unroll
           for (int kk = 0; kk < FB_C / 16; ++kk)
-            umma_bf16_ss(tmem_base + 256, umma_desc_kmajor_sw128(pt_u) + 2 * kk,
+            umma_bf16_ts(tmem_base + 256, pt_t + (uint32_t)kk * 8,
                          umma_desc_mnmajor_sw128(do_u + (uint32_t)kk * 2048, FB_CBOX_BYTES), idesc_acc, (j | kk) != 0);
 #pragma unroll
           for (int kk = 0; kk < FB_C / 16; ++kk)
-            umma_bf16_ss(tmem_base + 384, umma_desc_kmajor_sw128(dst_u) + 2 * kk,
+            umma_bf16_ts(tmem_base + 384, dst_t + (uint32_t)kk * 8,
                          umma_desc_mnmajor_sw128(q_u + (uint32_t)kk * 2048, FB_CBOX_BYTES), idesc_acc, (j | kk) != 0);
           umma_commit(&qd_empty[s]);
-          umma_commit(pd_empty);
         }
         if (ok) umma_commit(acc_done);
       }
@@ -907,8 +883,6 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         ok = __all_sync(0xffffffffu, mbar_wait(&sp_full[s], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 1250 + s));
         if (!ok) break;
         tc_fence_after();
-        ok = __all_sync(0xffffffffu, mbar_wait(pd_empty, (uint32_t)((j & 1) ^ 1), abort_flag, p.status, 1260));
-        if (!ok) break;
         const float* st = stat_s + (j % FB_QD_STAGES) * 2 * FB_C;  // visible: sp_full follows the MMA that waited on qd_full
         const uint32_t ts = tmem_base + lane_off + (uint32_t)s * 128;
 #pragma unroll 1
@@ -936,21 +910,18 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
               dp[i] = sv[i] * ((dp[i] - st[FB_C + c + i]) * p.scale);
             }
           }
+          uint32_t wp[16], wd[16];  // P^T and dS^T as bf16 pairs over the columns of S^T / dP^T already read
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            *reinterpret_cast<uint4*>(pt_s + fb_t64_off(r, c + i)) =
-                make_uint4(pack_bf16(sv[i], sv[i + 1]), pack_bf16(sv[i + 2], sv[i + 3]), pack_bf16(sv[i + 4], sv[i + 5]),
-                           pack_bf16(sv[i + 6], sv[i + 7]));
-            *reinterpret_cast<uint4*>(dst_s + fb_t64_off(r, c + i)) =
-                make_uint4(pack_bf16(dp[i], dp[i + 1]), pack_bf16(dp[i + 2], dp[i + 3]), pack_bf16(dp[i + 4], dp[i + 5]),
-                           pack_bf16(dp[i + 6], dp[i + 7]));
+          for (int i = 0; i < 16; ++i) {
+            wp[i] = pack_bf16(sv[2 * i], sv[2 * i + 1]);
+            wd[i] = pack_bf16(dp[2 * i], dp[2 * i + 1]);
           }
+          tmem_st_32x16(ts + (c >> 1), wp);
+          tmem_st_32x16(ts + 64 + (c >> 1), wd);
         }
+        tmem_st_wait();
         tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sp_empty[s]);
-        fence_proxy_async_smem();
-        mbar_arrive(pd_full);
+        mbar_arrive(&pd_full[s]);
       }
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_done, 0, abort_flag, p.status, 1270));
       if (ok) {
