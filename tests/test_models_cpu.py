@@ -215,3 +215,33 @@ def test_eager_generator_greedy_matches_transformers_generate(tmp_path):
         full = torch.tensor([prompt[0].tolist() + ref])
         lp = torch.log_softmax(hf(full).logits[0, 8:-1].float(), -1).gather(1, torch.tensor(ref)[:, None])[:, 0]
     assert torch.allclose(torch.tensor(out[0].logprobs), lp, atol=1e-4)
+
+
+def test_export_merged_weights_gives_a_plain_model_equal_to_the_adapted_one():
+    """The generation replica of an adapted policy: adapters folded in, the policy itself untouched."""
+    import copy
+
+    from trl_b200.models.decoder import CausalLM
+    from trl_b200.models.lora import LoraConfig, export_merged_weights, get_peft_model
+    from trl_b200.testing import make_tiny_model
+
+    model = make_tiny_model("tiny-qwen2", seed=0)
+    get_peft_model(model, LoraConfig(r=4, lora_alpha=8, target_modules=["q_proj", "v_proj", "gate_proj", "down_proj"]))
+    model.eval()  # no adapter dropout
+    g = torch.Generator().manual_seed(1)
+    for l in model.layers:
+        for slot in l.lora.values():
+            slot.lora_B.data.normal_(0, 0.05, generator=g)  # a fresh adapter has B = 0: make it matter
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    replica = CausalLM(model.config, dtype=model.dtype, init=False)
+    export_merged_weights(model, replica)
+    assert all(torch.equal(before[n], p) for n, p in model.named_parameters())  # the policy is not merged into
+    assert not any(len(l.lora) for l in replica.layers)
+    ids = torch.randint(0, 1024, (2, 17), generator=g)
+    with torch.no_grad():
+        want = model(input_ids=ids).logits
+        got = replica(input_ids=ids).logits
+        model.set_adapter_enabled(False)
+        base = model(input_ids=ids).logits
+        model.set_adapter_enabled(True)
+    assert torch.allclose(got, want, atol=2e-5) and (want - base).abs().max() > 1e-3

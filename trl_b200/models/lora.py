@@ -153,3 +153,24 @@ def load_adapter(model, path: str):
         if k in sd:
             v.copy_(sd[k].to(v.dtype))
     return model
+
+
+@torch.no_grad()
+def export_merged_weights(model, target) -> None:
+    """Writes ``model``'s weights with every adapter folded in (``W + scaling * B @ A`` on the adapted slices, in fp32,
+    rounded once) into ``target``, a plain copy of the same architecture without adapters.  The generation engines
+    read ``target``; the trained model is never touched, so nothing drifts the way a merge / unmerge round trip in
+    bf16 would (the reference merges into the model itself before each weight sync and unmerges afterwards:
+    trl/generation/vllm_generation.py:459-486)."""
+    src = dict(model.named_parameters())
+    for n, p in target.named_parameters():
+        if n in src and src[n].shape == p.shape:
+            p.copy_(src[n])
+    for l_src, l_dst in zip(model.layers, target.layers):
+        if not getattr(l_src, "lora_enabled", True):
+            continue
+        slices = l_src.proj_slices()
+        for name, slot in l_src.lora.items():
+            pname, sl = slices[name]
+            w_src, w_dst = getattr(l_src, pname), getattr(l_dst, pname)
+            w_dst[sl] = (w_src[sl].float() + slot.delta_weight().to(w_src.device)).to(w_dst.dtype)

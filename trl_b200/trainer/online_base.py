@@ -213,6 +213,18 @@ class OnlineTrainer(Trainer):
                 self._gen_model = CausalLM(self.model.config, dtype=self.model.dtype, device=self.args.device, init=False)
                 self._gen_model.eval().requires_grad_(False)
             gen_model = self._gen_model
+        elif (getattr(self.model, "peft_config", None) is not None and self.args.device.type == "cuda"
+              and any(len(l.lora) for l in self.model.layers)):
+            # adapters: the decode kernels read plain weight matrices, so generation gets a replica with the adapters
+            # folded in, refreshed before every generation batch (`export_merged_weights`); the eager generator on
+            # CPU runs the adapted model itself
+            if getattr(self.model, "is_vlm", False):
+                raise NotImplementedError("adapters with a vision-language generation replica")
+            if getattr(self, "_gen_model", None) is None:
+                self._gen_model = CausalLM(self.model.config, dtype=self.model.dtype, device=self.args.device, init=False)
+                self._gen_model.eval().requires_grad_(False)
+                self._gen_merged = True
+            gen_model = self._gen_model
         if self._rollout is None:
             if self.args.device.type == "cuda":
                 from ..rollout.engine import RolloutEngine
@@ -323,7 +335,12 @@ class OnlineTrainer(Trainer):
         eng = self._get_rollout()
         if self.state.global_step != self._last_loaded_step and getattr(self, "_gen_model", None) is not None:
             with self._profile("sync_weights"):  # slices of the streamed engine -> the whole generation replica
-                self.engine.export_weights(self._gen_model)
+                if getattr(self, "_gen_merged", False):  # adapters folded into the replica, the policy left as it is
+                    from ..models.lora import export_merged_weights
+
+                    export_merged_weights(self.model, self._gen_model)
+                else:
+                    self.engine.export_weights(self._gen_model)
                 if hasattr(eng, "sync_weights"):
                     eng.sync_weights()
             self._last_loaded_step = self.state.global_step
