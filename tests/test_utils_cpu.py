@@ -300,3 +300,27 @@ def test_entropy_and_selective_log_softmax_in_chunks_and_dtypes():
         assert torch.allclose(selective_log_softmax(logits, multi), lp.gather(-1, multi), atol=1e-5)
         got16 = selective_log_softmax(logits.to(torch.bfloat16), idx)
         assert got16.dtype == torch.bfloat16 and (got16.float() - lp.gather(-1, idx[..., None])[..., 0]).abs().max() < 0.1
+
+
+def test_small_compat_helpers():
+    import asyncio
+
+    from trl_b200.trainer import utils as U
+
+    rows = [{"a": {"aa": None, "ab": 1}, "b": "my_string", "c": [{"x": None, "y": 2}, 3]}]
+    assert U.remove_none_values(rows) == [{"a": {"ab": 1}, "b": "my_string", "c": [{"y": 2}, 3]}]
+    with pytest.raises(TypeError):
+        U.remove_none_values("text")
+    assert U.identity(5) == 5 and U.get_config_model_id(object()) == ""
+    t, loop, ready = U.start_event_loop_in_daemon("helper-loop")
+    assert ready.wait(5) and t.daemon and t.name == "helper-loop"
+
+    async def twice(x):
+        return 2 * x
+
+    assert asyncio.run_coroutine_threadsafe(twice(21), loop).result(5) == 42
+    U.shutdown_event_loop_in_daemon(t, loop)
+    assert not t.is_alive()
+    U.shutdown_event_loop_in_daemon(None, None)  # no-op
+    assert U.get_comet_experiment_url() is None and U.get_trackio_space_url() is None
+    assert callable(U.selective_log_softmax) and callable(U.patch_chunked_lm_head) and callable(U.ensure_master_addr_port)

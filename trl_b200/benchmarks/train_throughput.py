@@ -56,6 +56,9 @@ def main():
     ap.add_argument("--pairs-per-gpu", type=int, default=2)
     ap.add_argument("--tokens-per-gpu", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=None, help="debug only: a truncated model is not the named config")
+    ap.add_argument("--kernel-table", type=int, default=0, metavar="N",
+                    help="after the timed steps, run one more step under the PyTorch profiler and add the N kernels with "
+                         "the most device time to the JSON line (`top_kernels`: name, calls, total ms, share)")
     a = ap.parse_args()
 
     from trl_b200.models.configuration import preset
@@ -150,6 +153,20 @@ def main():
         for _ in range(a.steps):
             tokens += one_step()
         ms = torch.tensor([(time.perf_counter() - t0) * 1e3])
+    top = None
+    if a.kernel_table and on_gpu:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            one_step()
+            torch.cuda.synchronize()
+        ev = [e for e in prof.key_averages() if getattr(e, "device_time_total", 0) > 0]
+        total = sum(e.device_time_total for e in ev) or 1.0
+        ev.sort(key=lambda e: -e.device_time_total)
+        top = [{"kernel": e.key[:90], "calls": int(e.count), "ms": round(e.device_time_total / 1e3, 3),
+                "share": round(e.device_time_total / total, 4)} for e in ev[: a.kernel_table]]
+        top.append({"kernel": "(all kernels of the profiled step)", "calls": int(sum(e.count for e in ev)),
+                    "ms": round(total / 1e3, 3), "share": 1.0})
     D.all_reduce(ms, "max")
     tok_t = torch.tensor([float(tokens)], device=dev)
     D.all_reduce(tok_t, "sum")
@@ -164,6 +181,7 @@ def main():
                        "per_gpu": f"{a.pairs_per_gpu} pairs, lengths U[64,512]" if a.task == "dpo"
                        else f"{a.tokens_per_gpu} packed tokens, doc lengths log-uniform [128,{a.tokens_per_gpu}]",
                        "l2_policy": "inputs larger than L2 (all weights streamed every step)"},
+            **({"top_kernels": top} if top else {}),
             "gpu_launches": int(K.LAUNCHES[0] - l0), "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2**30, 1) if on_gpu else None}))
     D.barrier()
     if D.is_initialized():

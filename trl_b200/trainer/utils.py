@@ -491,3 +491,96 @@ def generate_model_card(base_model=None, model_name="model", hub_model_id=None, 
                            hub_model_id=hub_model_id or model_name, dataset_name=dataset_name, trainer_name=trainer_name,
                            trainer_citation=trainer_citation, paper_title=paper_title, paper_id=paper_id,
                            versions=versions, wandb_url=wandb_url, comet_url=comet_url)
+
+
+# ---- small helpers kept for API compatibility (trl/trainer/utils.py) ----------------------------------------------------
+def identity(x):
+    return x
+
+
+def remove_none_values(example):
+    """``None`` entries removed from nested lists / mappings (a dataset transform: Arrow fills missing keys of
+    heterogeneous rows with ``None``; trl/trainer/utils.py:1088-1131)."""
+    from collections.abc import Mapping
+
+    if isinstance(example, list):
+        return [remove_none_values(v) if isinstance(v, (Mapping, list)) else v for v in example]
+    if isinstance(example, Mapping):
+        return {k: (remove_none_values(v) if isinstance(v, (Mapping, list)) else v) for k, v in example.items()
+                if v is not None}
+    raise TypeError("Input must be a list or a dictionary.")
+
+
+def get_config_model_id(config) -> str:
+    return getattr(config, "_name_or_path", "")
+
+
+def start_event_loop_in_daemon(name: str | None = None):
+    """New asyncio loop running forever in a daemon thread; returns (thread, loop, ready event)."""
+    import threading
+
+    loop = asyncio.new_event_loop()
+    ready = threading.Event()
+
+    def run():
+        asyncio.set_event_loop(loop)
+        loop.call_soon(ready.set)
+        loop.run_forever()
+
+    t = threading.Thread(target=run, name=name, daemon=True)
+    t.start()
+    return t, loop, ready
+
+
+def shutdown_event_loop_in_daemon(thread, loop) -> None:
+    if loop is None or thread is None:
+        return
+    loop.call_soon_threadsafe(loop.stop)
+    thread.join(timeout=5)
+
+
+def get_comet_experiment_url():
+    """URL of the running Comet experiment, or None (comet_ml is optional and absent from offline images)."""
+    try:
+        import comet_ml
+    except ImportError:
+        return None
+    exp = comet_ml.get_running_experiment()
+    return exp.url if exp is not None else None
+
+
+def get_trackio_space_url():
+    try:
+        from trackio import context_vars
+    except ImportError:
+        return None
+    run = context_vars.current_run.get()
+    if run is None or getattr(run, "_space_id", None) is None:
+        return None
+    return f"https://{run._space_id.replace('/', '-')}.hf.space?project={run.project}&runs={run.name}&sidebar=collapsed"
+
+
+def log_table_to_comet_experiment(name: str, table) -> None:
+    try:
+        import comet_ml
+    except ImportError as e:
+        raise ModuleNotFoundError("The comet-ml is not installed. Please install it first: pip install comet-ml") from e
+    exp = comet_ml.get_running_experiment()
+    if exp is not None:
+        exp.log_table(tabular_data=table, filename=name)
+
+
+def __getattr__(name):  # names that live in the ops / parallel packages here, under the reference's module path
+    if name in ("selective_log_softmax", "entropy_from_logits"):
+        from ..oracle import ops as _o
+
+        return getattr(_o, name)
+    if name == "patch_chunked_lm_head":
+        from ..ops.chunked_lm_head import patch_chunked_lm_head
+
+        return patch_chunked_lm_head
+    if name == "ensure_master_addr_port":
+        from ..parallel.dist import ensure_master_addr_port
+
+        return ensure_master_addr_port
+    raise AttributeError(name)
