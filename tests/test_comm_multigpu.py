@@ -63,3 +63,9 @@ def test_streamed_full_shard_engine_two_ranks(fused):
 def test_expert_parallel_model_trains_like_replicated_experts():
     rc, out, err = run_ranks(os.path.join(HERE, "dist_worker_ep_model_gpu.py"), 29671)
     assert rc == 0 and "EP_MODEL_OK" in out, out[-3000:] + err[-3000:]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_sequence_and_context_parallel_match_one_rank_on_gpus():
+    rc, out, err = run_ranks(os.path.join(HERE, "dist_worker_spcp_gpu.py"), 29681)
+    assert rc == 0 and "SPCP_OK" in out, out[-3000:] + err[-3000:]

@@ -8,8 +8,10 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-COMMON = dict(per_device_train_batch_size=4, max_steps=2, logging_steps=1, learning_rate=1e-3, save_strategy="no",
+COMMON = dict(per_device_train_batch_size=4, max_steps=2, logging_steps=1, learning_rate=5e-3, save_strategy="no",
               report_to="none", bf16=True)
+# the learning rate is large on purpose: norm weights start at 1.0, where one bf16 step is 2^-8, and the check below
+# looks at the bf16 parameters (the fp32 master copies move with any rate)
 SHAPE = dict(hidden_size=256, num_attention_heads=2, num_key_value_heads=1, head_dim=128, intermediate_size=512,
              num_hidden_layers=2)
 

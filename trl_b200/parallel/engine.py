@@ -46,6 +46,16 @@ def adamw_flat(*a, **k):  # imported on use: loop/ imports this module
 _ALIGN = 256  # elements; keeps every shard 16-byte aligned for TMA / vector access
 
 
+def _sumsq(g: torch.Tensor) -> torch.Tensor:
+    """Sum of squares of a flat gradient as a 0-dim fp32 tensor: one read of the buffer on GPUs (the eager
+    ``float().pow(2).sum()`` writes and re-reads an fp32 temporary of the same size)."""
+    if g.is_cuda and g.dtype in (torch.float32, torch.bfloat16) and g.is_contiguous():
+        from ..ops.cuda import sumsq
+
+        return sumsq(g)[0]
+    return g.float().pow(2).sum()
+
+
 @dataclass
 class Bucket:
     name: str
@@ -266,7 +276,7 @@ class TrainEngine:
         sq = torch.zeros((), dtype=torch.float32, device=reduced[0].device)
         sq_local = torch.zeros_like(sq)  # parts every rank holds a different piece of: shards, expert-parallel buckets
         for b, g in zip(self.buckets, reduced):
-            part = g.float().pow(2).sum()
+            part = _sumsq(g)
             if self.sharded or (b.local and self.world > 1):
                 sq_local += part
             else:
@@ -314,7 +324,7 @@ class TrainEngine:
         for b, red in zip(self.buckets, self._reduced):
             if b.local:  # expert-parallel bucket: scale, add its squared norm to this rank's partial
                 red.copy_(b.flat_grad).div_(self.world)
-                self._sumsq += red.pow(2).sum()
+                self._sumsq += _sumsq(red)
                 continue
             key = (b.name, str(b.params[0].dtype))
             K.rs_reduce(ga, self._offsets[("grad",) + key], b.flat_grad.dtype == torch.bfloat16, b.lo, b.hi - b.lo, red,

@@ -441,10 +441,12 @@ class StreamShardEngine:
         self._join_side_streams()
         rest_g = self._reduce_to_shard(self.rest_grad, self.rest_numel) if self.rest_numel else None
         sq = torch.zeros((), dtype=torch.float32, device=self.dev)
+        from .engine import _sumsq
+
         for ls in self.layers:
-            sq += ls.grad_acc.float().pow(2).sum()
+            sq += _sumsq(ls.grad_acc)
         if rest_g is not None:
-            sq += rest_g.pow(2).sum()
+            sq += _sumsq(rest_g)
         if self.world > 1:
             td.all_reduce(sq, group=self.group)
         norm = sq.sqrt()
