@@ -59,8 +59,10 @@ def parse():
                          "1 / N of every layer per GPU for models whose training state does not fit otherwise")
     ap.add_argument("--meta-init", action="store_true",
                     help="with --shard full_shard_stream: build the policy on the meta device (initialised slice by slice)")
-    ap.add_argument("--ckpt-layers", type=int, default=None,
-                    help="with checkpointing on: recompute only the first n layers, keep the activations of the rest")
+    ap.add_argument("--ckpt-layers", default="auto",
+                    help="with checkpointing on: recompute only the first n layers and keep the activations of the rest; "
+                         "'auto' (default) lets the trainer measure in the first two warm-up steps how many layers fit "
+                         "(gradient_checkpointing_kwargs={'num_layers': 'auto'}); 'all' recomputes every layer")
     return ap.parse_args()
 
 
@@ -176,7 +178,15 @@ def main():
     out_dir = tempfile.mkdtemp(prefix="bench_grpo_")
     rollout_tp = a.rollout_tp or (2 if world > 1 else 1)
     grad_ckpt = a.grad_ckpt == "on"
-    ckpt_kwargs = {"num_layers": a.ckpt_layers} if a.ckpt_layers is not None else None
+    shard_mode = a.shard or ("zero2" if world > 1 else "ddp")
+    if a.ckpt_layers in ("all", None) or shard_mode == "full_shard_stream":
+        ckpt_kwargs = None
+    elif a.ckpt_layers == "auto":
+        if a.warmup < 3:
+            raise SystemExit("--ckpt-layers auto settles in the first two steps: use --warmup >= 3 or --ckpt-layers all")
+        ckpt_kwargs = {"num_layers": "auto"}
+    else:
+        ckpt_kwargs = {"num_layers": int(a.ckpt_layers)}
     args = GRPOConfig(output_dir=out_dir, per_device_train_batch_size=a.micro_batch, gradient_accumulation_steps=ga,
                       num_generations=a.num_generations, max_completion_length=a.max_new, temperature=1.0, beta=0.04,
                       epsilon=0.2, learning_rate=1e-6, max_steps=a.steps, logging_steps=1, save_strategy="no",

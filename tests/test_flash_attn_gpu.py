@@ -154,3 +154,44 @@ def test_fa_backward_end_aligned_segments():
     rq, rk, rv = torch.autograd.grad(ref.attention_varlen_qk(qf, kf, vf, cq, ck), (qf, kf, vf), g.float())
     for a, b in ((dq, rq), (dk, rk), (dv, rv)):
         assert (a.float() - b).abs().max().item() < 3e-2 * max(1.0, b.abs().max().item())
+
+
+def test_checkpointed_layers_reuse_the_attention_output_in_their_recompute():
+    """With activation checkpointing the recompute of a layer takes the attention output of the first pass instead of
+    launching the forward kernel again: same gradients, one attention forward per layer instead of two."""
+    from trl_b200.models.decoder import SeqCtx
+    from trl_b200.ops import cuda as K
+    from trl_b200.ops import functional as ops
+    from trl_b200.testing import make_tiny_model
+
+    model = make_tiny_model("tiny-qwen2", dtype=torch.bfloat16, device="cuda", hidden_size=256, num_attention_heads=2,
+                            num_key_value_heads=1, head_dim=128, intermediate_size=512, num_hidden_layers=3, seed=0)
+    model.gradient_checkpointing_enable()
+    model.train()
+    g = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, 1024, (400,), generator=g).cuda()
+    lens = [150, 250]
+
+    def run():
+        for p in model.parameters():
+            p.grad = None
+        before = K.LAUNCHES[0]
+        h = model.forward_hidden(ids, SeqCtx.from_lengths(lens, ids.device))
+        loss_sum, _, _, n = ops.lm_head_ce(h, model.lm_head_weight, torch.roll(ids, -1))
+        (loss_sum / n).backward()
+        torch.cuda.synchronize()
+        return K.LAUNCHES[0] - before, {k: p.grad.clone() for k, p in model.named_parameters()}
+
+    was = K.AttnKeep.enabled
+    try:
+        K.AttnKeep.enabled = True
+        n_keep, g_keep = run()
+        assert not K.AttnKeep.store  # every kept output was taken back by its recompute
+        K.AttnKeep.enabled = False
+        n_plain, g_plain = run()
+    finally:
+        K.AttnKeep.enabled = was
+    assert n_plain - n_keep == 3, (n_plain, n_keep)  # one forward attention launch less per layer
+    for k in g_keep:
+        assert torch.equal(g_keep[k], g_plain[k]), k
+    K.check_status()

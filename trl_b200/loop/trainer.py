@@ -231,7 +231,13 @@ class Trainer:
             dt = torch.bfloat16 if self.args.bf16 else (torch.float16 if self.args.fp16 else None)
             self.model.to(device=dev, dtype=dt) if dt is not None else self.model.to(dev)
         if self.args.gradient_checkpointing and hasattr(self.model, "gradient_checkpointing_enable"):
-            self.model.gradient_checkpointing_enable(self.args.gradient_checkpointing_kwargs)
+            kw = self.args.gradient_checkpointing_kwargs
+            # {"num_layers": "auto"}: start with every layer recomputed and let the first optimizer steps measure how
+            # many layers can keep their activations (see _autotune_checkpointing)
+            self._ckpt_auto = 0 if isinstance(kw, dict) and kw.get("num_layers") == "auto" else None
+            if self._ckpt_auto is not None:
+                kw = {k: v for k, v in kw.items() if k != "num_layers"} or None
+            self.model.gradient_checkpointing_enable(kw)
 
     @property
     def accelerator(self):
@@ -555,7 +561,52 @@ class Trainer:
         self.control = self.callback_handler.call_event("on_optimizer_step", a, st, self.control)
         self.lr_scheduler.step()
         self.engine.zero_grad()
+        if getattr(self, "_ckpt_auto", None) is not None:
+            self._autotune_checkpointing()
         return total, grad_norm, lr
+
+    def _autotune_checkpointing(self, probe: int = 4):
+        """``gradient_checkpointing_kwargs={"num_layers": "auto"}``: how many layers may keep their activations.
+
+        Optimizer step 1 runs with every layer recomputed and gives the peak memory of the whole step (generation and
+        reference passes of the online trainers included).  Step 2 keeps the activations of the last ``probe`` layers;
+        the growth of the peak is what one layer costs.  From step 3 on as many layers keep theirs as fit into the
+        memory that was free at the first peak, less a reserve of a tenth of the device (allocator slack,
+        variation between batches), the minimum over all ranks.  Engines that need every layer recomputed (streamed
+        shards) and CPU runs leave the setting alone."""
+        m, dev = self.model, self.args.device
+        lm = getattr(m, "language_model", m)
+        L = len(getattr(lm, "layers", []))
+        if dev.type != "cuda" or L == 0 or getattr(self.engine, "mode", "") == "full_shard_stream":
+            self._ckpt_auto = None
+            return
+        stage = self._ckpt_auto
+        peak = torch.cuda.max_memory_allocated(dev)
+        if stage == 0:
+            self._ckpt_peak0 = peak
+            lm.checkpoint_num_layers = max(0, L - min(probe, L))
+            torch.cuda.reset_peak_memory_stats(dev)
+            self._ckpt_auto = 1
+            return
+        total_mem = torch.cuda.get_device_properties(dev).total_memory
+        kept = L - lm.checkpoint_num_layers
+        per_layer = max((peak - self._ckpt_peak0) / max(kept, 1), 1.0)
+        # a step whose peak lies outside the training pass hides the cost of the probe: fall back to an estimate of
+        # what a layer saves for backward (about 34 values of hidden size per token for a SwiGLU decoder, in bf16)
+        c = lm.config
+        tokens = getattr(self, "_last_micro_batch_tokens", None) or 8192
+        floor = tokens * (10 * c.hidden_size + 4 * (getattr(c, "moe_intermediate_size", None) or c.intermediate_size)) * 2
+        per_layer = max(per_layer, floor / 2)
+        headroom = total_mem - self._ckpt_peak0 - int(0.10 * total_mem)
+        k = int(max(0, min(L, headroom // per_layer)))
+        t = torch.tensor([k], device=dev)
+        if D.world_size() > 1:
+            D.all_reduce(t, "min")
+        k = int(t)
+        lm.checkpoint_num_layers = L - k
+        self._ckpt_auto = None
+        self._ckpt_auto_result = {"layers_keeping_activations": k, "layers": L, "bytes_per_layer": int(per_layer),
+                                  "peak_all_recomputed": int(self._ckpt_peak0)}
 
     def _maybe_log_save_evaluate(self, tr_loss, grad_norm, lr, t_start):
         st, a = self.state, self.args

@@ -334,18 +334,32 @@ class CausalLM(nn.Module):
         language models splice image features into it)."""
         x = self.embed(input_ids) if inputs_embeds is None else inputs_embeds
         n_ckpt = getattr(self, "checkpoint_num_layers", None)
+        keep = None
         for li, layer in enumerate(self.layers):
             if (self.gradient_checkpointing and self.training and torch.is_grad_enabled()
                     and (n_ckpt is None or li < n_ckpt)):
                 from .activation_offloading import offload_checkpoint, offloading_active
 
+                if keep is None and x.is_cuda:
+                    from ..ops.cuda import AttnKeep as keep
+
+                    fwd_id = keep.new_forward()
+
+                def run(h, c=ctx, layer=layer, li=li):
+                    # both the forward pass and its recompute go through here under the same name, so the attention
+                    # output of the first is handed to the second (ops/cuda.py: AttnKeep)
+                    if keep is None:
+                        return layer(h, c)
+                    with keep.scope((fwd_id, li)):
+                        return layer(h, c)
+
                 if getattr(self, "offload_checkpoint_inputs", False) and offloading_active():
                     # the layer input is saved through the saved-tensor hooks, i.e. it goes to pinned host memory
-                    x = offload_checkpoint(lambda h, layer=layer: layer(h, ctx), x)
+                    x = offload_checkpoint(run, x)
                 else:
                     from torch.utils.checkpoint import checkpoint
 
-                    x = checkpoint(layer, x, ctx, use_reentrant=False)
+                    x = checkpoint(run, x, use_reentrant=False)
             else:
                 x = layer(x, ctx)
         return self.final_norm(x)

@@ -6,6 +6,8 @@ buffer; :func:`check_status` reads it (one host sync) and raises if a bounded wa
 """
 from __future__ import annotations
 
+import os
+
 import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
@@ -389,13 +391,52 @@ def fa_varlen_bwd(q, k, v, out, dout, lse, cu_q, cu_k, causal=True, window=None,
     return dq, dk, dv
 
 
+class AttnKeep:
+    """Attention outputs kept across the recompute of activation checkpointing.
+
+    A checkpointed layer runs its forward twice: once when the model is evaluated and once more, inside backward, to
+    rebuild what autograd needs.  Everything in the layer is cheap to rebuild except attention, whose cost grows
+    with the square of the sequence length, while its output is one [tokens, hidden] tensor.  The decoder therefore
+    names every checkpointed layer call (``with AttnKeep.scope((forward_id, layer)):``): the first attention call
+    under a name stores its output and log-sum-exp, the second one (the recompute) takes them back instead of
+    launching the kernel.  A new forward pass drops whatever an abandoned one left behind."""
+
+    store: dict = {}
+    current = None
+    forward_id = 0
+    enabled = os.environ.get("TRL_B200_KEEP_ATTN", "1") != "0"
+
+    @classmethod
+    def new_forward(cls) -> int:
+        cls.forward_id += 1
+        cls.store.clear()  # whatever a forward pass without a backward pass left behind
+        return cls.forward_id
+
+    class scope:
+        def __init__(self, key):
+            self.key = key
+
+        def __enter__(self):
+            self.prev, AttnKeep.current = AttnKeep.current, (self.key if AttnKeep.enabled else None)
+
+        def __exit__(self, *exc):
+            AttnKeep.current = self.prev
+
+
 class _FaVarlenFn(torch.autograd.Function):
     """Varlen attention on the tcgen05 kernels (csrc/fa_varlen_tcgen05.cu): grouped-query heads are indexed, never
     expanded; the backward recomputes the probabilities from the saved log-sum-exp."""
 
     @staticmethod
     def forward(ctx, q, k, v, cu_q, cu_k, causal, window):
-        out, lse = fa_varlen_fwd(q, k, v, cu_q, cu_k, causal, window)
+        key = AttnKeep.current
+        kept = AttnKeep.store.pop(key, None) if key is not None else None
+        if kept is not None and kept[0].shape == q.shape:
+            out, lse = kept  # the recompute of a checkpointed layer: same inputs, same result
+        else:
+            out, lse = fa_varlen_fwd(q, k, v, cu_q, cu_k, causal, window)
+            if key is not None:
+                AttnKeep.store[key] = (out.detach(), lse)
         ctx.save_for_backward(q, k, v, out, lse, cu_q, cu_k)
         ctx.causal, ctx.window = causal, window
         return out
