@@ -397,13 +397,16 @@ class Trainer:
         return (loss, outputs) if return_outputs else loss
 
     def training_step(self, model, inputs, num_items_in_batch=None):
+        from ..extras.profiling import profiling_context
+
         model.train()
         inputs = self._prepare_inputs(inputs)
-        with self._activation_offload_context():
-            loss = self.compute_loss(model, inputs, num_items_in_batch=num_items_in_batch)
-        if (not self.model_accepts_loss_kwargs or num_items_in_batch is None) and self.compute_loss_func is None:
-            loss = loss / self.current_gradient_accumulation_steps
-        self.engine.backward(loss)
+        with profiling_context(self, "forward_backward"):  # the micro-batch itself: loss forward + backward
+            with self._activation_offload_context():
+                loss = self.compute_loss(model, inputs, num_items_in_batch=num_items_in_batch)
+            if (not self.model_accepts_loss_kwargs or num_items_in_batch is None) and self.compute_loss_func is None:
+                loss = loss / self.current_gradient_accumulation_steps
+            self.engine.backward(loss)
         return loss.detach()
 
     def _activation_offload_context(self):
@@ -571,8 +574,9 @@ class Trainer:
         Optimizer step 1 runs with every layer recomputed and gives the peak memory of the whole step (generation and
         reference passes of the online trainers included).  Step 2 keeps the activations of the last ``probe`` layers;
         the growth of the peak is what one layer costs.  From step 3 on as many layers keep theirs as fit into the
-        memory that was free at the first peak, less a reserve of a tenth of the device (allocator slack,
-        variation between batches), the minimum over all ranks.  Engines that need every layer recomputed (streamed
+        memory that was free at the first peak, less a reserve of 12 % of the device + 4 GiB (allocator slack,
+        variation between batches: a step that runs close to the limit loses more in allocator retries than it saves
+        in recomputation), the minimum over all ranks.  Engines that need every layer recomputed (streamed
         shards) and CPU runs leave the setting alone."""
         m, dev = self.model, self.args.device
         lm = getattr(m, "language_model", m)
@@ -597,7 +601,7 @@ class Trainer:
         tokens = getattr(self, "_last_micro_batch_tokens", None) or 8192
         floor = tokens * (10 * c.hidden_size + 4 * (getattr(c, "moe_intermediate_size", None) or c.intermediate_size)) * 2
         per_layer = max(per_layer, floor / 2)
-        headroom = total_mem - self._ckpt_peak0 - int(0.10 * total_mem)
+        headroom = total_mem - self._ckpt_peak0 - int(0.12 * total_mem) - (4 << 30)
         k = int(max(0, min(L, headroom // per_layer)))
         t = torch.tensor([k], device=dev)
         if D.world_size() > 1:
