@@ -59,10 +59,12 @@ def parse():
                          "1 / N of every layer per GPU for models whose training state does not fit otherwise")
     ap.add_argument("--meta-init", action="store_true",
                     help="with --shard full_shard_stream: build the policy on the meta device (initialised slice by slice)")
-    ap.add_argument("--ckpt-layers", default="auto",
-                    help="with checkpointing on: recompute only the first n layers and keep the activations of the rest; "
-                         "'auto' (default) lets the trainer measure in the first two warm-up steps how many layers fit "
-                         "(gradient_checkpointing_kwargs={'num_layers': 'auto'}); 'all' recomputes every layer")
+    ap.add_argument("--ckpt-layers", default="all",
+                    help="with checkpointing on: 'all' (default) recomputes every layer; n recomputes only the first n "
+                         "layers and keeps the activations of the rest; 'auto' lets the trainer measure in the first two "
+                         "warm-up steps how many layers fit (gradient_checkpointing_kwargs={'num_layers': 'auto'}).  With "
+                         "micro-batches of varying length keeping activations did not pay here: the allocator's "
+                         "remapping cost what the recomputation saved")
     return ap.parse_args()
 
 
