@@ -2,6 +2,9 @@
 
     python -m trl_b200.benchmarks.rollout_vs_vllm --engine ours
     python -m trl_b200.benchmarks.rollout_vs_vllm --engine vllm        # needs the installed vllm package to start here
+    # tensor parallel over 2 GPUs, 128 sequences (64 per GPU, as in the GRPO benchmark):
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m trl_b200.benchmarks.rollout_vs_vllm --engine ours
+    python -m trl_b200.benchmarks.rollout_vs_vllm --engine vllm --tp 2 --prompts 16
 
 Work: random-init Qwen2.5-7B architecture in bf16, 8 prompts of 256 uniform-random token ids, 8 completions each
 (64 sequences), at most 1024 new tokens, temperature 1.  Completion lengths follow the benchmark's end-of-sequence
@@ -44,10 +47,24 @@ def run_ours(a) -> dict:
     from trl_b200.rollout.sampling import SamplingParams
 
     cfg = preset(a.model, eos_token_id=1, pad_token_id=0)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = 0
+    if world > 1:  # launched through torch.distributed.run: one tensor-parallel group over all ranks
+        import torch.distributed as td
+
+        from trl_b200.parallel import dist as D
+        from trl_b200.rollout.tp_engine import TPRolloutEngine
+
+        D.init_process_group()
+        rank = D.rank()
+        torch.cuda.set_device(D.local_rank())
     torch.manual_seed(0)
     model = CausalLM(cfg, dtype=torch.bfloat16, device="cuda").eval()
-    eng = RolloutEngine(model, max_num_seqs=a.prompts * a.n, max_model_len=a.prompt_len + a.max_new + 16)
-    g = torch.Generator().manual_seed(1)
+    if world > 1:
+        eng = TPRolloutEngine(model, td.group.WORLD, max_num_seqs=a.prompts * a.n, max_model_len=a.prompt_len + a.max_new + 16)
+    else:
+        eng = RolloutEngine(model, max_num_seqs=a.prompts * a.n, max_model_len=a.prompt_len + a.max_new + 16)
+    g = torch.Generator().manual_seed(1 + rank)  # every rank brings its own prompts; the group decodes the union
     prompts = [torch.randint(2, cfg.vocab_size, (a.prompt_len,), generator=g).tolist() for _ in range(a.prompts)]
     sp = SamplingParams(n=a.n, max_tokens=a.max_new, temperature=1.0, eos_token_id=1, eos_prob_floor=a.eos_floor, seed=3)
     eng.generate(prompts, sp)  # warm-up: graph capture
@@ -61,8 +78,19 @@ def run_ours(a) -> dict:
         times.append(time.perf_counter() - t0)
         toks.append(sum(len(o.token_ids) for o in outs))
     i = sorted(range(len(times)), key=lambda k: times[k])[len(times) // 2]
-    return {"engine": "trl_b200 RolloutEngine", "generate_s": round(times[i], 3), "generated_tokens": toks[i],
-            "tokens_per_s": round(toks[i] / times[i], 1), "decode_steps": eng.stats.get("decode_steps")}
+    n_tok = toks[i]
+    if world > 1:  # tokens of all ranks' completions in the median iteration
+        t = torch.tensor([float(x) for x in toks], device="cuda")
+        td.all_reduce(t)
+        n_tok = int(t[i])
+        td.barrier()
+        if rank != 0:
+            td.destroy_process_group()
+            return {}
+        td.destroy_process_group()
+    return {"engine": "trl_b200 " + (f"TPRolloutEngine (TP{world})" if world > 1 else "RolloutEngine"),
+            "generate_s": round(times[i], 3), "generated_tokens": n_tok, "tokens_per_s": round(n_tok / times[i], 1),
+            "decode_steps": eng.stats.get("decode_steps")}
 
 
 def run_vllm(a) -> dict:
@@ -123,7 +151,10 @@ def main():
         rec = run_ours(a) if a.engine == "ours" else run_vllm(a)
     except Exception as e:  # noqa: BLE001  (an engine that cannot start here is a result too)
         rec = {"engine": a.engine, "unavailable": f"{type(e).__name__}: {str(e)[:300]}"}
-    rec["config"] = {"model": f"{a.model} (random init)", "sequences": a.prompts * a.n, "prompt_len": a.prompt_len,
+    if not rec:
+        return 0
+    seqs = a.prompts * a.n * (int(os.environ.get("WORLD_SIZE", "1")) if a.engine == "ours" else 1)
+    rec["config"] = {"model": f"{a.model} (random init)", "sequences": seqs, "prompt_len": a.prompt_len,
                      "max_new_tokens": a.max_new, "eos_prob_floor": a.eos_floor, "dtype": "bf16"}
     print(json.dumps(rec))
     return 0
