@@ -183,3 +183,44 @@ def test_engine_generates_from_image_prompts_like_the_eager_generator():
     other = [None if x is None else torch.randn_like(x) * 3 for x in images]
     outs2 = eng.generate(prompts, sp, images=other)
     assert any(a.token_ids != b.token_ids for a, b in zip(outs[:4], outs2[:4]))
+
+
+def test_engine_generates_with_multimodal_rope_like_the_eager_generator():
+    """Qwen2-VL layout: images of different sizes as flat patches, three rotary position rows in the prefill, and a
+    per-slot rotary lead in the decode kernels (an image advances the position by less than its token count)."""
+    from trl_b200.models.configuration import preset
+    from trl_b200.models.vision_qwen import Qwen2VLArch, Qwen2VLModel, QwenVisionArch, patchify
+    from trl_b200.rollout.engine import EagerGenerator, RolloutEngine
+    from trl_b200.rollout.sampling import SamplingParams
+
+    torch.manual_seed(0)
+    text = preset("tiny-qwen2", hidden_size=256, num_attention_heads=2, num_key_value_heads=1, head_dim=128,
+                  intermediate_size=512)
+    text.extra["mrope_section"] = [16, 24, 24]
+    vis = QwenVisionArch(depth=2, embed_dim=64, hidden_size=256, num_heads=2, mlp_ratio=2)
+    cfg = Qwen2VLArch(text, vis, image_token_id=7)
+    model = Qwen2VLModel(cfg, dtype=torch.bfloat16, device="cuda")
+    prompts, images = [], []
+    for sizes, tail in (((56, 112),), 9), (((28, 28), (84, 56)), 40), ((), 12):
+        p, pv, grids = [11, 12], [], []
+        for h, w in sizes:
+            a, g = patchify(torch.randn(1, 3, h, w), vis)
+            pv.append(a)
+            grids.append(g)
+            p += [7] * (a.shape[0] // 4) + [13]
+        p += torch.randint(20, 1000, (tail,)).tolist()
+        prompts.append(p)
+        images.append((torch.cat(pv), torch.cat(grids)) if sizes else None)
+    sp = SamplingParams(n=2, max_tokens=8, greedy=True, temperature=1.0, eos_token_id=2)
+    eng = RolloutEngine(model, max_num_seqs=6, max_model_len=128, poll_every=4)
+    assert eng.rope_delta is not None
+    outs = eng.generate(prompts, sp, images=images)
+    # 56 x 112 -> 2 x 4 merged tokens that advance the position by 4 (lead -4); 28 x 28 -> one token (0) and
+    # 84 x 56 -> 3 x 2 tokens that advance it by 3 (-3); no lead for the text prompt
+    assert sorted(eng.rope_delta.tolist()) == [-4, -4, -3, -3, 0, 0]
+    ref = EagerGenerator(model).generate(prompts, sp, images=images)
+    agree = sum(o.token_ids[:3] == r.token_ids[:3] for o, r in zip(outs, ref))
+    assert agree >= 4, [(o.token_ids, r.token_ids) for o, r in zip(outs, ref)]
+    outs_text = eng.generate(prompts[2:], sp)  # the slots are reused: the lead of a text prompt is zero again
+    assert sorted(eng.rope_delta.tolist())[-2:] == [0, 0] and len(outs_text) == 2
+    assert [o.token_ids[:3] for o in outs_text] == [o.token_ids[:3] for o in outs[4:]]

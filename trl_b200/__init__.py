@@ -12,7 +12,8 @@ _import_structure = {
     "models.utils": ["create_reference_model", "unwrap_model_for_generation"],
     "models.decoder": ["CausalLM"],
     "models.vision": ["VisionLanguageModel", "VlmArch", "VisionArch"],
-    "models.vision_processing": ["VisionProcessor"],
+    "models.vision_processing": ["VisionProcessor", "DynamicResolutionProcessor"],
+    "models.vision_qwen": ["Qwen2VLModel", "Qwen2VLArch", "QwenVisionArch"],
     "models.configuration": ["ModelArch", "preset"],
     "models.lora": ["LoraConfig", "get_peft_model"],
     "scripts.utils": ["DatasetMixtureConfig", "ScriptArguments", "TrlParser", "get_dataset", "init_zero_verbose"],

@@ -20,7 +20,7 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, long
                                      const int* __restrict__ block_table, int max_blocks, int block_size,
                                      __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ kc,
                                      __nv_bfloat16* __restrict__ vc, int B, int Hq, int Hk, int D, float log2_theta,
-                                     int v_t) {
+                                     int v_t, const int* __restrict__ pos_delta) {
   const int half = D >> 1;
   const int per_tok = (Hq + 2 * Hk) * half;
   const long long total = (long long)B * per_tok;
@@ -38,7 +38,7 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, long
     if (head < Hq + Hk) {
       const float inv = exp2f(-log2_theta * (float)(2 * f) / (float)D);
       float s, c;
-      sincosf((float)pos * inv, &s, &c);
+      sincosf((float)(pos + (pos_delta ? pos_delta[slot] : 0)) * inv, &s, &c);  // rotary position may lead the cache slot
       const float lo = __bfloat162float(src[f]), hi = __bfloat162float(src[half + f]);
       const float o0 = lo * c - hi * s, o1 = hi * c + lo * s;
       __nv_bfloat16* dst = head < Hq ? q_out + ((size_t)b * Hq + head) * D : kc + (cache_row + (head - Hq)) * D;
@@ -67,7 +67,7 @@ rope_kv_write_f32_kernel(float* __restrict__ acc, long long row_stride, const __
                          float norm_eps, const int* __restrict__ seq_lens, const int* __restrict__ slot_ids,
                          const int* __restrict__ block_table, int max_blocks, int block_size,
                          __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc,
-                         int B, int Hq, int Hk, int D, float log2_theta, int v_t) {
+                         int B, int Hq, int Hk, int D, float log2_theta, int v_t, const int* __restrict__ pos_delta) {
   pdl_launch_dependents();
   pdl_wait();
   const int half = D >> 1, heads = Hq + 2 * Hk;
@@ -121,7 +121,7 @@ rope_kv_write_f32_kernel(float* __restrict__ acc, long long row_stride, const __
         const float l = lo[j], h = hi[j];
         const float inv = exp2f(-log2_theta * (float)(2 * f) / (float)D);
         float sn, cs;
-        sincosf((float)pos * inv, &sn, &cs);
+        sincosf((float)(pos + (pos_delta ? pos_delta[slot] : 0)) * inv, &sn, &cs);
         __nv_bfloat16* dst = head < Hq ? q_out + ((size_t)b * Hq + head) * D : kc + (cache_row + (head - Hq)) * D;
         dst[f] = __float2bfloat16(l * cs - h * sn);
         dst[half + f] = __float2bfloat16(h * cs + l * sn);
@@ -144,7 +144,8 @@ rope_kv_write_f32_flat_kernel(float* __restrict__ acc, long long row_stride, con
                               const int* __restrict__ seq_lens, const int* __restrict__ slot_ids,
                               const int* __restrict__ block_table, int max_blocks, int block_size,
                               __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ kc,
-                              __nv_bfloat16* __restrict__ vc, int B, int Hq, int Hk, int D, float log2_theta, int v_t) {
+                              __nv_bfloat16* __restrict__ vc, int B, int Hq, int Hk, int D, float log2_theta, int v_t,
+                              const int* __restrict__ pos_delta) {
   pdl_launch_dependents();
   pdl_wait();
   const int half = D >> 1;
@@ -173,7 +174,7 @@ rope_kv_write_f32_flat_kernel(float* __restrict__ acc, long long row_stride, con
     if (head < Hq + Hk) {
       const float inv = exp2f(-log2_theta * (float)(2 * f) / (float)D);
       float sn, cs;
-      sincosf((float)pos * inv, &sn, &cs);
+      sincosf((float)(pos + (pos_delta ? pos_delta[slot] : 0)) * inv, &sn, &cs);
       __nv_bfloat16* dst = head < Hq ? q_out + ((size_t)b * Hq + head) * D : kc + (cache_row + (head - Hq)) * D;
       dst[f] = __float2bfloat16(lo * cs - hi * sn);
       dst[half + f] = __float2bfloat16(hi * cs + lo * sn);
@@ -460,13 +461,14 @@ using namespace trlb;
 
 TRLB_API int trlb_rope_kv_write(const void* qkv, long long row_stride, const int* seq_lens, const int* slot_ids,
                                 const int* block_table, int max_blocks, int block_size, void* q_out, void* kc, void* vc,
-                                int B, int Hq, int Hk, int D, float theta, int v_t, cudaStream_t st) {
+                                int B, int Hq, int Hk, int D, float theta, int v_t, const int* pos_delta,
+                                cudaStream_t st) {
   if (B == 0) return 0;
   const long long work = (long long)B * (Hq + 2 * Hk) * (D / 2);
   int grid = (int)((work + 255) / 256);
   rope_kv_write_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)qkv, row_stride, seq_lens, slot_ids, block_table,
                                              max_blocks, block_size, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kc,
-                                             (__nv_bfloat16*)vc, B, Hq, Hk, D, log2f(theta), v_t);
+                                             (__nv_bfloat16*)vc, B, Hq, Hk, D, log2f(theta), v_t, pos_delta);
   return (int)cudaGetLastError();
 }
 
@@ -474,7 +476,8 @@ TRLB_API int trlb_rope_kv_write(const void* qkv, long long row_stride, const int
 TRLB_API int trlb_rope_kv_write_f32(float* acc, long long row_stride, const void* bias, const void* q_norm,
                                     const void* k_norm, float norm_eps, const int* seq_lens, const int* slot_ids,
                                     const int* block_table, int max_blocks, int block_size, void* q_out, void* kc,
-                                    void* vc, int B, int Hq, int Hk, int D, float theta, int v_t, cudaStream_t st) {
+                                    void* vc, int B, int Hq, int Hk, int D, float theta, int v_t,
+                                    const int* pos_delta, cudaStream_t st) {
   if (B == 0) return 0;
   if (D > 128 || (D & 1)) return -1;
   if (q_norm == nullptr && k_norm == nullptr) {
@@ -483,7 +486,7 @@ TRLB_API int trlb_rope_kv_write_f32(float* acc, long long row_stride, const void
     return (int)trlb_host::launch_kernel(rope_kv_write_f32_flat_kernel, dim3(grid), dim3(256), 0, st,
                                          trlb_host::pdl_enabled(), acc, row_stride, (const __nv_bfloat16*)bias, seq_lens,
                                          slot_ids, block_table, max_blocks, block_size, (__nv_bfloat16*)q_out,
-                                         (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, B, Hq, Hk, D, log2f(theta), v_t);
+                                         (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, B, Hq, Hk, D, log2f(theta), v_t, pos_delta);
   }
   const int items = B * (Hq + 2 * Hk);
   const int grid = (items + 7) / 8;
@@ -491,7 +494,7 @@ TRLB_API int trlb_rope_kv_write_f32(float* acc, long long row_stride, const void
                                        row_stride, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)q_norm,
                                        (const __nv_bfloat16*)k_norm, norm_eps, seq_lens, slot_ids, block_table, max_blocks,
                                        block_size, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, B, Hq, Hk,
-                                       D, log2f(theta), v_t);
+                                       D, log2f(theta), v_t, pos_delta);
 }
 
 TRLB_API int trlb_kv_write_prefill(const void* k, const void* v, long long k_stride, long long v_stride,

@@ -35,6 +35,8 @@ class SeqCtx:
     router_records: list = field(default_factory=list)
     # sequence parallelism (parallel/ulysses.py): positions are this rank's chunk, cu_seqlens / max_seqlen are global
     sp: Any = None
+    # multimodal rotary positions [3, T] (temporal, height, width; models/vision_qwen.py); None = ordinary RoPE
+    mrope_positions: Any = None
 
     @staticmethod
     def from_lengths(lengths, device) -> "SeqCtx":
@@ -156,7 +158,10 @@ class DecoderLayer(nn.Module):
         if c.qk_norm:
             q = ops.rms_norm(q.contiguous(), self.q_norm, c.rms_norm_eps)
             k = ops.rms_norm(k.contiguous(), self.k_norm, c.rms_norm_eps)
-        q, k = ops.apply_rope_qk(q, k, ctx.positions, c.rope_theta)
+        if ctx.mrope_positions is not None and c.extra.get("mrope_section"):
+            q, k = ops.apply_mrope_qk(q, k, ctx.mrope_positions, c.rope_theta, c.extra["mrope_section"])
+        else:
+            q, k = ops.apply_rope_qk(q, k, ctx.positions, c.rope_theta)
         if ctx.kv is not None:
             o = ctx.kv.attend(self.layer_idx, q, k, v, ctx)
         elif ctx.sp is not None and ctx.sp.mode == "allgather_kv":

@@ -238,10 +238,15 @@ def load_model(path_or_name, dtype=None, device=None, num_labels: int | None = N
     is_dir = os.path.isdir(name)
     if is_dir and config is None and os.path.exists(os.path.join(name, "config.json")):
         with open(os.path.join(name, "config.json")) as f:
-            if json.load(f).get("model_type") == "llava":  # vision tower + projector + decoder
-                from .vision import VisionLanguageModel
+            mt = json.load(f).get("model_type")
+        if mt == "llava":  # vision tower + projector + decoder
+            from .vision import VisionLanguageModel
 
-                return VisionLanguageModel.from_pretrained(name, dtype=dtype, device=device)
+            return VisionLanguageModel.from_pretrained(name, dtype=dtype, device=device)
+        if mt == "qwen2_vl":  # dynamic-resolution tower + decoder with multimodal RoPE
+            from .vision_qwen import Qwen2VLModel
+
+            return Qwen2VLModel.from_pretrained(name, dtype=dtype, device=device)
     if config is None:
         if is_dir:
             config = ModelArch.from_pretrained(name)

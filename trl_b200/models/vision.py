@@ -423,3 +423,55 @@ def tiny_vlm_arch(text_preset: str = "tiny-llama", image_token_index: int = 5) -
     vis = VisionArch(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, image_size=28,
                      patch_size=14)
     return VlmArch(text=preset(text_preset), vision=vis, image_token_index=image_token_index)
+
+
+# ---- per-sequence image inputs ------------------------------------------------------------------------------------------
+# The online trainers and the rollout engines carry the images of every sequence as one "entry": a tensor
+# [n_images, C, S, S] for fixed-resolution towers, or a pair (patches [N, D], grid [n_images, 3]) for towers that take
+# images of any size as a flat list of patches.  These helpers are the only code that looks inside an entry.
+def vision_entry_numel(e) -> int:
+    if e is None:
+        return 0
+    return int((e[0] if isinstance(e, tuple) else e).numel())
+
+
+def same_vision_entry(a, b) -> bool:
+    if a is None or b is None:
+        return a is None and b is None
+    if isinstance(a, tuple) != isinstance(b, tuple):
+        return False
+    xs, ys = (a, b) if isinstance(a, tuple) else ((a,), (b,))
+    return all(x.shape == y.shape and torch.equal(x, y) for x, y in zip(xs, ys))
+
+
+def merge_vision_entries(entries, device, dtype=None) -> dict:
+    """Entries of the sequences of one packed batch, in order -> keyword arguments of ``forward_hidden``."""
+    live = [e for e in entries if vision_entry_numel(e)]
+    if not live:
+        return {"pixel_values": None}
+    if isinstance(live[0], tuple):
+        return {"pixel_values": torch.cat([e[0] for e in live]).to(device, dtype),
+                "image_grid_thw": torch.cat([e[1] for e in live]).to(device)}
+    return {"pixel_values": torch.cat(live).to(device, dtype)}
+
+
+def split_vision_batch(enc: dict, counts: list[int]) -> list:
+    """Output of a processor for a batch whose example i has ``counts[i]`` images -> one entry per example."""
+    pv, grid = enc.get("pixel_values"), enc.get("image_grid_thw")
+    if pv is None:
+        return [None] * len(counts)
+    pv = torch.as_tensor(pv)
+    out, o = [], 0
+    if grid is None:
+        for n in counts:
+            out.append(pv[o:o + n])
+            o += n
+        return out
+    grid = torch.as_tensor(grid)
+    per_image = grid.prod(-1).tolist()
+    po = 0
+    for n in counts:
+        k = sum(per_image[o:o + n])
+        out.append((pv[po:po + k], grid[o:o + n]) if n else None)
+        o, po = o + n, po + k
+    return out

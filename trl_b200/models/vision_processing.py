@@ -56,7 +56,8 @@ class VisionProcessor:
         return self.tokenizer.chat_template
 
     # ---- images -----------------------------------------------------------------------------------------------------
-    def _one_image(self, img: Any) -> torch.Tensor:
+    def _load(self, img: Any) -> torch.Tensor:
+        """Any accepted image form -> float tensor [3, H, W] in [0, 1]."""
         # file paths and the {"path": ..., "bytes": ...} records of an undecoded datasets.Image column are opened here
         if isinstance(img, dict) and ("bytes" in img or "path" in img):
             import io
@@ -84,6 +85,10 @@ class VisionProcessor:
                 t = t / 255.0
         if t.shape[0] == 1:
             t = t.expand(3, -1, -1)
+        return t
+
+    def _one_image(self, img: Any) -> torch.Tensor:
+        t = self._load(img)
         S = self.image_size
         if t.shape[1:] != (S, S):
             t = torch.nn.functional.interpolate(t[None], size=(S, S), mode="bilinear", align_corners=False,
@@ -120,19 +125,26 @@ class VisionProcessor:
     def __call__(self, images=None, text=None, padding=False, padding_side=None, pad_to_multiple_of=None,
                  truncation=False, max_length=None, return_tensors=None, add_special_tokens=True, **kw):
         texts = [text] if isinstance(text, str) else list(text)
-        expanded = [t.replace(self.image_token, self.image_token * self.image_seq_length) for t in texts]
+        vis = self._convert(images, texts) if images is not None else {}
+        expanded = self._expand(texts, vis)
         tk = dict(padding=padding, truncation=truncation, max_length=max_length, return_tensors=return_tensors,
                   add_special_tokens=add_special_tokens, pad_to_multiple_of=pad_to_multiple_of)
         if padding_side is not None:
             tk["padding_side"] = padding_side
         out = dict(self.tokenizer(expanded, **tk))
-        if images is not None:
-            pv = self.preprocess_images(images)
-            n_slots = sum(t.count(self.image_token) for t in texts)
-            if n_slots != pv.shape[0]:
-                raise ValueError(f"{pv.shape[0]} images for {n_slots} image placeholders in the text")
-            out["pixel_values"] = pv
+        out.update(vis)
         return out
+
+    def _convert(self, images, texts) -> dict:
+        pv = self.preprocess_images(images)
+        n_slots = sum(t.count(self.image_token) for t in texts)
+        if n_slots != pv.shape[0]:
+            raise ValueError(f"{pv.shape[0]} images for {n_slots} image placeholders in the text")
+        return {"pixel_values": pv}
+
+    def _expand(self, texts, pv):
+        """Image placeholders of the texts -> the run of image tokens the model replaces."""
+        return [t.replace(self.image_token, self.image_token * self.image_seq_length) for t in texts]
 
     def batch_decode(self, *a, **kw):
         return self.tokenizer.batch_decode(*a, **kw)
@@ -156,3 +168,104 @@ class VisionProcessor:
             d = json.load(f)
         return cls(AutoTokenizer.from_pretrained(path), d["image_size"], d["image_seq_length"], d["image_token"],
                    d["image_mean"], d["image_std"])
+
+
+class DynamicResolutionProcessor(VisionProcessor):
+    """Processor of towers that take images of any size as a flat list of patches (Qwen2-VL layout): every image keeps
+    its aspect ratio, its sides are rounded to multiples of ``patch_size * merge_size`` with the pixel count kept inside
+    ``[min_pixels, max_pixels]``, and it contributes ``(h / patch / merge) * (w / patch / merge)`` image tokens.
+    Returns ``pixel_values`` [sum patches, C * temporal * patch * patch] and ``image_grid_thw`` [n_images, 3]."""
+
+    def __init__(self, tokenizer, patch_size: int = 14, merge_size: int = 2, temporal_patch_size: int = 2,
+                 min_pixels: int = 56 * 56, max_pixels: int = 28 * 28 * 1280, image_token: str = "<image>",
+                 image_mean=CLIP_MEAN, image_std=CLIP_STD):
+        super().__init__(tokenizer, image_size=0, image_seq_length=0, image_token=image_token, image_mean=image_mean,
+                         image_std=image_std)
+        self.patch_size, self.merge_size, self.temporal_patch_size = int(patch_size), int(merge_size), int(temporal_patch_size)
+        self.min_pixels, self.max_pixels = int(min_pixels), int(max_pixels)
+
+    @classmethod
+    def for_model(cls, tokenizer, model, **kw) -> "DynamicResolutionProcessor":
+        v = model.config.vision
+        p = cls(tokenizer, v.patch_size, v.spatial_merge_size, v.temporal_patch_size, **kw)
+        if p.image_token_id != model.config.image_token_id:
+            raise ValueError(f"tokenizer maps {p.image_token!r} to {p.image_token_id}, the model expects "
+                             f"image_token_id={model.config.image_token_id}")
+        return p
+
+    def target_size(self, h: int, w: int) -> tuple[int, int]:
+        """Sides rounded to the merge window, scaled (aspect kept) into the pixel budget."""
+        f = self.patch_size * self.merge_size
+        if max(h, w) / max(1, min(h, w)) > 200:
+            raise ValueError("aspect ratio above 200")
+        H, W = max(f, round(h / f) * f), max(f, round(w / f) * f)
+        if H * W > self.max_pixels:
+            s = (h * w / self.max_pixels) ** 0.5
+            H, W = max(f, int(h / s / f) * f), max(f, int(w / s / f) * f)
+        elif H * W < self.min_pixels:
+            s = (self.min_pixels / (h * w)) ** 0.5
+            H, W = -int(-h * s // f) * f, -int(-w * s // f) * f
+        return H, W
+
+    def _one_image(self, img: Any) -> torch.Tensor:
+        t = self._load(img)
+        H, W = self.target_size(t.shape[1], t.shape[2])
+        if t.shape[1:] != (H, W):
+            t = torch.nn.functional.interpolate(t[None], size=(H, W), mode="bicubic", align_corners=False,
+                                                antialias=True)[0].clamp(0.0, 1.0)
+        mean = torch.tensor(self.image_mean)[:, None, None]
+        std = torch.tensor(self.image_std)[:, None, None]
+        return (t - mean) / std
+
+    def preprocess_images(self, images):
+        """-> (patches [N, C * T * P * P], grid [n, 3])."""
+        from .vision_qwen import QwenVisionArch, patchify
+
+        flat = []
+        for x in images:
+            flat.extend(x) if isinstance(x, (list, tuple)) else flat.append(x)
+        arch = QwenVisionArch(patch_size=self.patch_size, spatial_merge_size=self.merge_size,
+                              temporal_patch_size=self.temporal_patch_size)
+        if not flat:
+            return torch.zeros(0, arch.patch_dim), torch.zeros(0, 3, dtype=torch.long)
+        parts = [patchify(self._one_image(i)[None], arch) for i in flat]
+        return torch.cat([p for p, _ in parts]), torch.cat([g for _, g in parts])
+
+    def _convert(self, images, texts) -> dict:
+        pv, grid = self.preprocess_images(images)
+        n_slots = sum(t.count(self.image_token) for t in texts)
+        if n_slots != grid.shape[0]:
+            raise ValueError(f"{grid.shape[0]} images for {n_slots} image placeholders in the text")
+        return {"pixel_values": pv, "image_grid_thw": grid}
+
+    def _expand(self, texts, vis):
+        if not vis:
+            return list(texts)
+        counts = (vis["image_grid_thw"].prod(-1) // (self.merge_size ** 2)).tolist()
+        out, k = [], 0
+        for t in texts:
+            parts = t.split(self.image_token)
+            s = parts[0]
+            for p in parts[1:]:
+                s += self.image_token * int(counts[k]) + p
+                k += 1
+            out.append(s)
+        return out
+
+    def save_pretrained(self, path: str, **kw):
+        os.makedirs(path, exist_ok=True)
+        self.tokenizer.save_pretrained(path)
+        with open(os.path.join(path, "preprocessor_config.json"), "w") as f:
+            json.dump({"processor_class": "DynamicResolutionProcessor", "patch_size": self.patch_size,
+                       "merge_size": self.merge_size, "temporal_patch_size": self.temporal_patch_size,
+                       "min_pixels": self.min_pixels, "max_pixels": self.max_pixels, "image_token": self.image_token,
+                       "image_mean": list(self.image_mean), "image_std": list(self.image_std)}, f, indent=2)
+
+    @classmethod
+    def from_pretrained(cls, path: str, **kw) -> "DynamicResolutionProcessor":
+        from transformers import AutoTokenizer
+
+        with open(os.path.join(path, "preprocessor_config.json")) as f:
+            d = json.load(f)
+        d.pop("processor_class", None)
+        return cls(AutoTokenizer.from_pretrained(path), **d)

@@ -836,18 +836,21 @@ def swiglu_infer(gu, out=None):
 
 
 def rope_kv_write(qkv, seq_lens, slot_ids, block_table, block_size, q_out, k_cache, v_cache, Hq, Hk, D, theta,
-                  v_transposed=False):
+                  v_transposed=False, pos_delta=None):
     """RoPE on q/k of the new tokens, q -> q_out, k/v appended to the paged cache.  ``v_transposed``: the V cache is
-    [block, head, dim, token] (layout of the tensor-core decode attention) instead of [block, token, head, dim]."""
+    [block, head, dim, token] (layout of the tensor-core decode attention) instead of [block, token, head, dim].
+    ``pos_delta`` (int32 per slot, optional): rotary position = cache position + delta (multimodal RoPE, where an
+    image of many tokens advances the position by less than its token count)."""
     B = qkv.shape[0]
     _chk(lib().trlb_rope_kv_write(_p(qkv), c_longlong(qkv.stride(0)), _p(seq_lens), _p(slot_ids), _p(block_table),
                                   c_int(block_table.shape[1]), c_int(block_size), _p(q_out), _p(k_cache), _p(v_cache),
-                                  c_int(B), c_int(Hq), c_int(Hk), c_int(D), c_float(theta), c_int(int(v_transposed)), _s()),
+                                  c_int(B), c_int(Hq), c_int(Hk), c_int(D), c_float(theta), c_int(int(v_transposed)),
+                                  _p(pos_delta), _s()),
          "rope_kv_write")
 
 
 def rope_kv_write_f32(acc, bias, q_norm, k_norm, norm_eps, seq_lens, slot_ids, block_table, block_size, q_out, k_cache,
-                      v_cache, Hq, Hk, D, theta, v_transposed=False):
+                      v_cache, Hq, Hk, D, theta, v_transposed=False, pos_delta=None):
     """Like :func:`rope_kv_write` for the fp32 sums of the stream-K QKV GEMM: adds ``bias``, applies the per-head
     RMSNorm of q / k when ``q_norm`` / ``k_norm`` are given, rotates, appends, and clears ``acc``."""
     B = acc.shape[0]
@@ -856,7 +859,7 @@ def rope_kv_write_f32(acc, bias, q_norm, k_norm, norm_eps, seq_lens, slot_ids, b
                                       c_float(norm_eps), _p(seq_lens), _p(slot_ids), _p(block_table),
                                       c_int(block_table.shape[1]), c_int(block_size), _p(q_out), _p(k_cache), _p(v_cache),
                                       c_int(B), c_int(Hq), c_int(Hk), c_int(D), c_float(theta), c_int(int(v_transposed)),
-                                      _s()), "rope_kv_write_f32")
+                                      _p(pos_delta), _s()), "rope_kv_write_f32")
 
 
 def kv_write_prefill(k, v, tok_slot, tok_pos, block_table, block_size, k_cache, v_cache, v_transposed=False):

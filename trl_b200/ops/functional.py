@@ -142,6 +142,12 @@ def moe_mlp(hidden, router_w, gate_up_w, down_w, top_k, norm_topk_prob):
     return out, probs, idx
 
 
+def apply_mrope_qk(q, k, positions3, theta, sections):
+    """Multimodal rotary embedding of q and k (PyTorch math on every device: vision-language models are a small part
+    of the step and the rotation is elementwise)."""
+    return _ref.apply_mrope(q, positions3, theta, sections), _ref.apply_mrope(k, positions3, theta, sections)
+
+
 moe_router = _ref.moe_router
 selective_log_softmax = _ref.selective_log_softmax
 entropy_from_logits = _ref.entropy_from_logits

@@ -35,6 +35,25 @@ def apply_rope(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.
     return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
 
 
+def apply_mrope(x: torch.Tensor, positions3: torch.Tensor, theta: float, sections) -> torch.Tensor:
+    """Multimodal rotary embedding on ``x`` [T, H, D]: ``positions3`` [3, T] holds a temporal, a height and a width
+    position per token; the D/2 rotary frequencies are cut into ``sections`` (their sizes sum to D/2) and section i
+    turns with position set i mod 3.  With three equal position rows this is ordinary RoPE
+    (Qwen2-VL; transformers modeling_qwen2_vl.py ``apply_multimodal_rotary_pos_emb`` is the behaviour matched)."""
+    d = x.shape[-1]
+    half = d // 2
+    if sum(sections) != half:
+        raise ValueError(f"mrope_section {list(sections)} must sum to head_dim / 2 = {half}")
+    inv = 1.0 / (theta ** (torch.arange(0, d, 2, device=x.device, dtype=torch.float32) / d))  # [half]
+    ang = positions3.float()[:, :, None] * inv[None, None, :]                                  # [3, T, half]
+    which = torch.cat([torch.full((n,), i % 3, dtype=torch.long) for i, n in enumerate(sections)]).to(x.device)
+    ang = ang.gather(0, which[None, None, :].expand(1, ang.shape[1], half))[0]                 # [T, half]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    xf = x.float()
+    x1, x2 = xf[..., :half], xf[..., half:]
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
+
+
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     """``silu(gate) * up`` for ``gate_up = [gate | up]`` along the last dim."""
     g, u = gate_up.float().chunk(2, dim=-1)

@@ -30,6 +30,7 @@ import numpy as np
 import torch
 
 from ..models.decoder import CausalLM, SeqCtx
+from ..models.vision import merge_vision_entries, vision_entry_numel
 from .sampling import SamplingParams, apply_repetition_penalty, filter_top_k_top_p, sample_reference
 
 
@@ -71,8 +72,7 @@ class EagerGenerator:
             ctx = SeqCtx.from_lengths(lens, dev)
             kw = {}
             if pix is not None:
-                px = [pix[i] for i in alive if pix[i] is not None and pix[i].numel()]
-                kw["pixel_values"] = torch.cat(px).to(dev) if px else None
+                kw = merge_vision_entries([pix[i] for i in alive], dev)
             hidden = self.model.forward_hidden(flat, ctx, **kw)
             last = (ctx.cu_seqlens[1:] - 1).long()
             logits = (hidden[last].float() @ self.model.lm_head_weight.float().t()).cpu()
@@ -175,6 +175,9 @@ class RolloutEngine:
         self.block_table = torch.zeros(max_num_seqs, self.max_blocks, **i32)
         self.block_table_host = torch.zeros(max_num_seqs, self.max_blocks, dtype=torch.int32).pin_memory()
         self.seq_lens = torch.full((max_num_seqs,), -1, **i32)
+        # multimodal RoPE: rotary position of a slot's next token = its length + rope_delta[slot]
+        self.rope_delta = (torch.zeros(max_num_seqs, dtype=torch.int32, device=self.dev)
+                           if self.vlm is not None and cfg.extra.get("mrope_section") else None)
         self.n_gen = torch.zeros(max_num_seqs, **i32)
         self.finished = torch.zeros(max_num_seqs, **i32)
         self.next_input = torch.zeros(max_num_seqs, dtype=torch.int64, device=self.dev)
@@ -265,7 +268,7 @@ class RolloutEngine:
             K.rope_kv_write_f32(self._acc_qkv, l.qkv_bias, l.q_norm if cfg.qk_norm else None,
                                 l.k_norm if cfg.qk_norm else None, eps, self.seq_lens, None, self.block_table,
                                 self.block_size, self.q_buf, self.k_cache[li], self.v_cache[li], cfg.num_attention_heads,
-                                cfg.num_key_value_heads, cfg.head_dim, cfg.rope_theta, v_transposed=self.attn_tc)
+                                cfg.num_key_value_heads, cfg.head_dim, cfg.rope_theta, v_transposed=self.attn_tc, pos_delta=self.rope_delta)
             self._decode_attention(li, scale)
             K.decode_gemm(self.attn_buf.view(self.max_seqs, -1), l.o_proj, y32=self._acc_o)
             h = K.add_rmsnorm_f32_infer(x, self._acc_o, l.post_attention_layernorm, eps)
@@ -311,7 +314,7 @@ class RolloutEngine:
                 qkv = torch.cat([qn.view(-1, qs), kn.view(-1, ks), qkv[:, qs + ks:]], dim=1)
             K.rope_kv_write(qkv, self.seq_lens, None, self.block_table, self.block_size, self.q_buf, self.k_cache[li],
                             self.v_cache[li], cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
-                            cfg.rope_theta, v_transposed=self.attn_tc)
+                            cfg.rope_theta, v_transposed=self.attn_tc, pos_delta=self.rope_delta)
             self._decode_attention(li, scale)
             if fuse:
                 attn_out = torch.nn.functional.linear(self.attn_buf.view(self.max_seqs, -1), l.o_proj)
@@ -373,16 +376,7 @@ class RolloutEngine:
         self.stats["prefill_tokens"] += int(flat.numel())
         was = self.model.training
         self.model.eval()
-        embeds = None
-        if self.vlm is not None and pixels is not None:
-            px = [x for x in pixels if x is not None and x.numel()]
-            if px:
-                embeds = self.model.embed(flat)
-                feats = self.vlm.image_features(torch.cat(px).to(self.dev, embeds.dtype)).to(embeds.dtype)
-                slots = (flat == self.vlm.config.image_token_index).nonzero().flatten()
-                if slots.numel() != feats.shape[0]:
-                    raise ValueError(f"{slots.numel()} image placeholder tokens for {feats.shape[0]} image features")
-                embeds.index_copy_(0, slots, feats)
+        embeds = self._vision_prefill(flat, ctx, pixels)
         hidden = self.model.forward_hidden(flat, ctx, inputs_embeds=embeds)
         if was:
             self.model.train()
@@ -418,6 +412,7 @@ class RolloutEngine:
                 self.sched.add(rid, len(p), min(max_new, self.max_len - len(p)), pi)
         results: list[Optional[Completion]] = [None] * n_req
         slot_req = [-1] * self.max_seqs
+        delta_of_prompt: dict[int, int] = {}  # multimodal RoPE: rotary lead of every prefilled prompt
         self.seq_lens.fill_(-1)
         self.finished.zero_()
         self.n_gen.zero_()
@@ -447,6 +442,12 @@ class RolloutEngine:
                 group_row = {reqs[rid][1]: i for i, (rid, slot, pre, _) in enumerate([a for a in admitted if a[2]])}
                 own_px = None if images is None else [images[reqs[rid][1]] for rid, slot, pre, _ in admitted if pre]
                 last_h = self._prefill(owners, own_px) if owners else None
+                if self.rope_delta is not None:
+                    if owners:
+                        for (rid, _, _, _), d in zip([a for a in admitted if a[2]], self._prefill_delta):
+                            delta_of_prompt[reqs[rid][1]] = d
+                    self.rope_delta[torch.tensor([a[1] for a in admitted], device=dev)] = torch.tensor(
+                        [delta_of_prompt[reqs[a[0]][1]] for a in admitted], dtype=torch.int32, device=dev)
                 # sharers: copy the partial tail block of the prompt from the group's owner
                 # (all sharers of the batch at once: two gathers + scatters per layer instead of two copies per sharer)
                 pairs = [(int(bt_np[slot, len(reqs[rid][0]) // self.block_size]), copy_blk)
@@ -474,7 +475,8 @@ class RolloutEngine:
                     need = {}
                     for a in admitted:
                         need.setdefault(reqs[a[0]][1], a)
-                    tmp = self._prefill_hidden_only([reqs[a[0]][0] for a in need.values()])
+                    tmp = self._prefill_hidden_only([reqs[a[0]][0] for a in need.values()],
+                                                    None if images is None else [images[g] for g in need])
                     gi = {g: i for i, g in enumerate(need)}
                     h_rows = tmp[torch.tensor([gi[reqs[a[0]][1]] for a in admitted], device=dev)]
                 logits = torch.nn.functional.linear(h_rows, self.model.lm_head_weight)
@@ -535,12 +537,39 @@ class RolloutEngine:
         self._tmp_next = torch.zeros(self.max_seqs, dtype=torch.int64, device=self.dev)
         return self._tmp_next
 
-    def _prefill_hidden_only(self, prompts):
+    def _prefill_hidden_only(self, prompts, pixels: list | None = None):
         lens = [len(p) for p in prompts]
         flat = torch.tensor([t for p in prompts for t in p], dtype=torch.long, device=self.dev)
         ctx = SeqCtx.from_lengths(lens, self.dev)
-        hidden = self.model.forward_hidden(flat, ctx)
+        hidden = self.model.forward_hidden(flat, ctx, inputs_embeds=self._vision_prefill(flat, ctx, pixels))
         return hidden[(ctx.cu_seqlens[1:] - 1).long()]
+
+    def _vision_prefill(self, flat, ctx, pixels):
+        """Vision-language models: input embeddings with the image features spliced in (None for text-only batches).
+        With multimodal RoPE the three position rows go into ``ctx`` and ``self._prefill_delta`` gets, per sequence,
+        how far the next rotary position leads (or trails) the sequence length."""
+        self._prefill_delta = None
+        if self.vlm is None:
+            return None
+        embeds, kw = None, {}
+        if pixels is not None and any(vision_entry_numel(x) for x in pixels):
+            embeds = self.model.embed(flat)
+            kw = merge_vision_entries(pixels, self.dev, embeds.dtype)
+            feats = self.vlm.image_features(**kw).to(embeds.dtype)
+            tid = getattr(self.vlm.config, "image_token_index", None)
+            slots = (flat == tid).nonzero().flatten()
+            if slots.numel() != feats.shape[0]:
+                raise ValueError(f"{slots.numel()} image placeholder tokens for {feats.shape[0]} image features")
+            embeds.index_copy_(0, slots, feats)
+        if self.rope_delta is not None:
+            from ..models.vision_qwen import rope_index
+
+            pos3 = rope_index(flat, ctx.cu_seqlens, kw.get("image_grid_thw"), self.vlm.config)
+            ctx.mrope_positions = pos3
+            cu = ctx.cu_seqlens.tolist()
+            top = pos3.max(0).values
+            self._prefill_delta = [int(top[a:b].max()) + 1 - (b - a) for a, b in zip(cu[:-1], cu[1:])]
+        return embeds
 
     def _capture(self, sp, max_total, key):
         # one eager step on a side stream warms every allocation and scratch buffer, but it also

@@ -193,7 +193,7 @@ class TPRolloutEngine(RolloutEngine):
             K.rope_kv_write_f32(self._acc_qkv, w["qkv_b"], l.q_norm if cfg.qk_norm else None,
                                 l.k_norm if cfg.qk_norm else None, eps, self.seq_lens, None, self.block_table,
                                 self.block_size, self.q_buf, self.k_cache[li], self.v_cache[li], self.hq_local,
-                                self.hk_local, cfg.head_dim, cfg.rope_theta, v_transposed=self.attn_tc)
+                                self.hk_local, cfg.head_dim, cfg.rope_theta, v_transposed=self.attn_tc, pos_delta=self.rope_delta)
             self._decode_attention(li, scale)
             K.decode_gemm(self.attn_buf.view(self.max_seqs, -1), w["o"], y32=self._acc_o, tiled_shape=(H, ql),
                           peers=(self._peer_acc_o, self._arrive_o, self._stage, self._slab_ctr))
@@ -220,7 +220,7 @@ class TPRolloutEngine(RolloutEngine):
             qkv = F.linear(h, w["qkv"], w["qkv_b"])
             K.rope_kv_write(qkv, self.seq_lens, None, self.block_table, self.block_size, self.q_buf, self.k_cache[li],
                             self.v_cache[li], self.hq_local, self.hk_local, cfg.head_dim, cfg.rope_theta,
-                            v_transposed=self.attn_tc)
+                            v_transposed=self.attn_tc, pos_delta=self.rope_delta)
             self._decode_attention(li, scale)
             torch.matmul(self.attn_buf.view(self.max_seqs, -1), w["o"].t(), out=self._site(site))
             h = K.allreduce_add_rmsnorm(self.arena, self.partials_off + site * self.site_elems * 2, 0, x,

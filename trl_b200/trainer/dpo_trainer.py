@@ -291,6 +291,8 @@ class DPOTrainer(Trainer):
         tgt_f, pred_f = tgt.reshape(-1)[mask_flat], pred.reshape(-1)[mask_flat].bool()
         cmgr = use_adapter(model, None) if adapter_off else _null()
         extra = {"pixel_values": inputs.get("pixel_values")} if getattr(model, "is_vlm", False) else {}
+        if extra and inputs.get("image_grid_thw") is not None:
+            extra["image_grid_thw"] = inputs["image_grid_thw"]
         with cmgr:
             hidden = model.forward_hidden(flat, ctx, **extra)
         sel = pred_f.nonzero().flatten()

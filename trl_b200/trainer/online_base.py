@@ -24,6 +24,7 @@ import torch.nn as nn
 from ..data_utils import apply_chat_template, is_conversational, maybe_apply_chat_template
 from ..loop.trainer import Trainer
 from ..models.decoder import CausalLM, SeqCtx
+from ..models.vision import merge_vision_entries, same_vision_entry
 from ..ops import functional as ops
 from ..parallel import dist as D
 from ..rollout.sampling import SamplingParams
@@ -263,7 +264,8 @@ class OnlineTrainer(Trainer):
 
     def _tokenize_prompts_with_images(self, prompts: list, images: list):
         """Vision-language prompts: the processor expands every image placeholder and converts the images.
-        Returns (prompt ids, per-prompt pixel tensors [n_images_i, C, S, S])."""
+        Returns (prompt ids, per-prompt image entries: pixel tensors [n_images_i, C, S, S], or (patches, grid) pairs
+        for towers that take images of any size)."""
         from ..data_utils import prepare_multimodal_messages
 
         proc = self.processing_class
@@ -278,12 +280,9 @@ class OnlineTrainer(Trainer):
             texts = list(prompts)
         enc = proc(images=imgs if any(imgs) else None, text=texts, add_special_tokens=False, return_tensors=None)
         ids = [list(x) for x in enc["input_ids"]]
-        pv = enc.get("pixel_values")
-        per, o = [], 0
-        for i in imgs:
-            per.append(pv[o:o + len(i)] if pv is not None else None)
-            o += len(i)
-        return ids, per
+        from ..models.vision import split_vision_batch
+
+        return ids, split_vision_batch(enc, [len(i) for i in imgs])
 
     def _tokenize_prompts(self, prompts: list):
         tok = self.processing_class
@@ -323,8 +322,7 @@ class OnlineTrainer(Trainer):
         uniq, counts, uniq_px = [], [], []
         for j, p in enumerate(prompt_ids):
             px = pixels[j] if pixels is not None else None
-            same_px = px is None or (uniq_px and uniq_px[-1] is not None and uniq_px[-1].shape == px.shape
-                                     and torch.equal(uniq_px[-1], px))
+            same_px = px is None or (bool(uniq_px) and same_vision_entry(uniq_px[-1], px))
             if uniq and uniq[-1] == p and same_px and counts[-1] < self.num_generations:
                 counts[-1] += 1
             else:
@@ -464,8 +462,7 @@ class OnlineTrainer(Trainer):
             ctx = SeqCtx(buf[o_pos:o_cu].to(torch.int32), buf[o_cu:o_sel].to(torch.int32), int(lens.max()))
             fwd_kw = {}
             if pixel_values_list is not None and getattr(model, "is_vlm", False):
-                px = [x for x in pixel_values_list[s:s + bs] if x is not None and x.numel()]
-                fwd_kw["pixel_values"] = torch.cat(px).to(dev) if px else None
+                fwd_kw = merge_vision_entries(pixel_values_list[s:s + bs], dev)
             hidden = model.forward_hidden(flat, ctx, **fwd_kw)
             tgt = flat[sel_t + 1]
             lp, en = ops.lm_head_logprobs(hidden[sel_t], model.lm_head_weight, tgt, temperature,

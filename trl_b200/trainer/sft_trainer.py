@@ -427,6 +427,8 @@ class SFTTrainer(Trainer):
         extra = {}
         if getattr(model, "is_vlm", False):
             extra["pixel_values"] = inputs.get("pixel_values")
+            if inputs.get("image_grid_thw") is not None:  # towers that take flat patches of images of any size
+                extra["image_grid_thw"] = inputs["image_grid_thw"]
             tgt = tgt.masked_fill(tgt == model.config.image_token_index, -100)  # placeholders carry no target
         with self.maybe_activation_offload_context:
             hidden = model.forward_hidden(flat, ctx, **extra)
