@@ -35,6 +35,19 @@ def test_grouped_gemm_and_moe_forward_backward(E, I, H, T, k):
     want_act = torch.nn.functional.silu(want[:, :I]) * want[:, I:]
     assert (fused.float() - want_act).abs().max().item() < 0.06 * max(1.0, want_act.abs().max().item())
 
+    # input gradient form: the forward weight [E, 2I, H] read transposed, rows [R, 2I] -> [R, H]
+    d_gu = (torch.randn(x_perm.shape[0], 2 * I, device=dev) * 0.5).to(torch.bfloat16)
+    got_dx = K.grouped_gemm(d_gu, gu.detach(), offsets, H, w_transposed=True)
+    want_dx = torch.cat([d_gu[offs[e]:offs[e + 1]].float() @ gu.detach()[e].float() for e in range(E)])
+    assert (got_dx.float() - want_dx).abs().max().item() < 0.03 * max(1.0, want_dx.abs().max().item())
+    # weight gradient: per expert d_gu^T @ x over the expert's rows (any row count, also none)
+    got_dw = K.grouped_wgrad(d_gu, x_perm, offsets, E)
+    want_dw = torch.stack([d_gu[offs[e]:offs[e + 1]].float().t() @ x_perm[offs[e]:offs[e + 1]].float() for e in range(E)])
+    assert (got_dw.float() - want_dw).abs().max().item() < 0.03 * max(1.0, want_dw.abs().max().item())
+    if E > 2:
+        assert got_dw[1].abs().max().item() == 0.0
+    K.check_status(torch.device(dev))
+
     out = K.moe_experts(hidden, gu, dw, topw, topi)
     out.float().square().sum().backward()
     grads = [t.grad.float().clone() for t in (hidden, gu, dw, topw)]

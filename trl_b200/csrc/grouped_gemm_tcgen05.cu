@@ -35,6 +35,7 @@ struct TmapArray {
 struct GroupedParams {
   int E, N, K, n_tiles, k_blocks;
   int swiglu;          // 1: W is [E, 2*N, K] (gate rows then up rows), C gets N columns
+  int b_mn;            // 1: W is [E, K, N] (the weight of the forward pass read transposed: input gradient)
   const int* offsets;  // [E + 1] row offsets into A / C (plain mode)
   __nv_bfloat16* C;
   long long ldc;
@@ -141,7 +142,11 @@ grouped_gemm_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_cons
           uint8_t* sb = sa + GA_BYTES;
           mbar_expect_tx(&full_bar[stage], GSTAGE_BYTES);
           tma_load_2d(sa, ta, &full_bar[stage], kb * GBK, row0);
-          if (p.swiglu) {  // 128 gate rows, then the 128 up rows of the same output columns
+          if (p.b_mn) {  // [64 k-rows x 64 columns] boxes, one per 64 output columns
+#pragma unroll
+            for (int b = 0; b < GBN / 64; ++b)
+              tma_load_3d(sb + b * 8192, &tmap_b, &full_bar[stage], nt * GBN + b * 64, kb * GBK, we);
+          } else if (p.swiglu) {  // 128 gate rows, then the 128 up rows of the same output columns
             tma_load_3d(sb, &tmap_b, &full_bar[stage], kb * GBK, nt * 128, we);
             tma_load_3d(sb + GB_BYTES / 2, &tmap_b, &full_bar[stage], kb * GBK, p.N + nt * 128, we);
           } else {
@@ -155,7 +160,8 @@ grouped_gemm_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_cons
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(GBM, GBN);
+      const uint32_t idesc = umma_idesc_bf16_major(GBM, GBN, false, p.b_mn != 0);
+      const uint32_t bstep = p.b_mn ? 128u : 2u;  // K step of 16: 32 bytes in a K-major atom, 16 rows of 128 bytes MN-major
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
@@ -168,9 +174,10 @@ grouped_gemm_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_cons
           tc_fence_after();
           const uint32_t sa = smem_u32(tiles + stage * GSTAGE_BYTES);
           const uint64_t adesc = umma_desc_kmajor_sw128(sa);
-          const uint64_t bdesc = umma_desc_kmajor_sw128(sa + GA_BYTES);
+          const uint64_t bdesc = p.b_mn ? umma_desc_mnmajor_sw128(sa + GA_BYTES, 8192) : umma_desc_kmajor_sw128(sa + GA_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < GBK / 16; ++kk) umma_bf16_ss(tacc, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) != 0);
+          for (int kk = 0; kk < GBK / 16; ++kk)
+            umma_bf16_ss(tacc, adesc + 2 * kk, bdesc + bstep * kk, idesc, (kb | kk) != 0);
           umma_commit(&empty_bar[stage]);
           if (++stage == GSTAGES) { stage = 0; phase ^= 1; }
         }
@@ -265,6 +272,199 @@ grouped_gemm_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_cons
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Grouped weight gradient:  dW[e] = G[rows of e]^T . X[rows of e]     (dW[e] is [Nw, Kw], G [rows, Nw], X [rows, Kw])
+//
+// The contraction runs over the rows of expert e, so both operands are MN-major (a TMA box is [64 rows x 64 columns],
+// rows = reduction dimension) and nothing is transposed in memory.  One item = (expert, 128 x 256 tile of dW[e]); its
+// K loop walks the expert's rows in blocks of 64, starting at the expert's first row wherever that is.  The last block
+// of an expert runs into the rows of the next one: the MMA warp clears those rows of the G tile in shared memory
+// before it issues (a zero row of either operand removes the term), which costs a few hundred 16-byte stores per item.
+// An expert without rows gets zeros.
+// ---------------------------------------------------------------------------------------------------------------------
+struct GroupedWgradParams {
+  int E, Nw, Kw, m_tiles, n_tiles;
+  const int* offsets;
+  __nv_bfloat16* dW;
+  int* status;
+};
+
+__global__ void __launch_bounds__(G_THREADS, 1)
+grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmap_g, const __grid_constant__ CUtensorMap tmap_x,
+                     const GroupedWgradParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GSTAGES * GSTAGE_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + GSTAGES;
+  uint64_t* tfull_bar = bars + 2 * GSTAGES;
+  uint64_t* tempty_bar = bars + 2 * GSTAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * GSTAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < GSTAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_g);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int per_e = p.m_tiles * p.n_tiles;
+  const int total_items = p.E * per_e;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        const int e = item / per_e, mt = (item % per_e) / p.n_tiles, nt = item % p.n_tiles;
+        const int r0 = p.offsets[e], cnt = p.offsets[e + 1] - r0;
+        const int k_blocks = (cnt + GBK - 1) / GBK;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 840 + stage)) { ok = false; break; }
+          uint8_t* sa = tiles + stage * GSTAGE_BYTES;
+          uint8_t* sb = sa + GA_BYTES;
+          mbar_expect_tx(&full_bar[stage], GSTAGE_BYTES);
+#pragma unroll
+          for (int b = 0; b < GBM / 64; ++b)
+            tma_load_2d(sa + b * 8192, &tmap_g, &full_bar[stage], mt * GBM + b * 64, r0 + kb * GBK);
+#pragma unroll
+          for (int b = 0; b < GBN / 64; ++b)
+            tma_load_2d(sb + b * 8192, &tmap_x, &full_bar[stage], nt * GBN + b * 64, r0 + kb * GBK);
+          if (++stage == GSTAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // every lane follows the loop: lane 0 waits on the barriers and issues the MMAs, the whole warp clears the rows
+    // past the expert's end (lane 0's wait, then the warp shuffle, orders the TMA writes before those stores)
+    constexpr uint32_t idesc = umma_idesc_bf16_major(GBM, GBN, true, true);
+    int stage = 0, acc = 0;
+    uint32_t phase = 0, acc_phase = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      const int e = item / per_e;
+      const int cnt = p.offsets[e + 1] - p.offsets[e];
+      const int k_blocks = (cnt + GBK - 1) / GBK;
+      if (lane == 0) ok = mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, 850 + acc);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tacc = tmem_base + (uint32_t)acc * GBN;
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        if (lane == 0) ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 860 + stage);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        uint8_t* sa_p = tiles + stage * GSTAGE_BYTES;
+        const int valid = cnt - kb * GBK;  // rows of this block that belong to the expert
+        if (valid < GBK) {
+          // a k-row is 128 contiguous bytes of each 64-column box (the swizzle permutes 16-byte chunks inside it)
+          const int chunks = (GBK - valid) * 8;
+          for (int b = 0; b < GBM / 64; ++b) {
+            uint4* base = reinterpret_cast<uint4*>(sa_p + b * 8192 + valid * 128);
+            for (int i = lane; i < chunks; i += 32) base[i] = make_uint4(0u, 0u, 0u, 0u);
+          }
+          fence_proxy_async_smem();  // generic-proxy stores -> tensor-core reads
+        }
+        __syncwarp();
+        if (lane == 0) {
+          tc_fence_after();
+          const uint32_t sa = smem_u32(sa_p);
+          const uint64_t adesc = umma_desc_mnmajor_sw128(sa, 8192);
+          const uint64_t bdesc = umma_desc_mnmajor_sw128(sa + GA_BYTES, 8192);
+#pragma unroll
+          for (int kk = 0; kk < GBK / 16; ++kk)
+            umma_bf16_ss(tacc, adesc + 128u * kk, bdesc + 128u * kk, idesc, (kb | kk) != 0);
+          umma_commit(&empty_bar[stage]);
+        }
+        __syncwarp();
+        if (++stage == GSTAGES) { stage = 0; phase ^= 1; }
+      }
+      if (!ok) break;
+      if (lane == 0) umma_commit(&tfull_bar[acc]);  // with no block issued this arrives at once; the epilogue writes zeros
+      __syncwarp();
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      const int e = item / per_e, mt = (item % per_e) / p.n_tiles, nt = item % p.n_tiles;
+      const bool empty = p.offsets[e + 1] - p.offsets[e] <= 0;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, 870 + acc)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t tacc = tmem_base + (uint32_t)acc * GBN + ((uint32_t)(quarter * 32) << 16);
+      const int row = mt * GBM + r, col0 = nt * GBN;
+      __nv_bfloat16* out_row = p.dW + ((long long)e * p.Nw + row) * p.Kw;
+#pragma unroll 1
+      for (int c = 0; c < GBN; c += 32) {
+        float v[32];
+        tmem_ld_32x32(tacc + c, v);
+        tmem_ld_wait();
+        if (empty) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0.f;
+        }
+        if (row < p.Nw && col0 + c < p.Kw) {
+          __nv_bfloat16* dst = out_row + col0 + c;
+          if (col0 + c + 32 <= p.Kw && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 o;
+              o.x = pack_bf16(v[i], v[i + 1]);
+              o.y = pack_bf16(v[i + 2], v[i + 3]);
+              o.z = pack_bf16(v[i + 4], v[i + 5]);
+              o.w = pack_bf16(v[i + 6], v[i + 7]);
+              *reinterpret_cast<uint4*>(dst + i) = o;
+            }
+          } else {
+            for (int i = 0; i < 32; ++i)
+              if (col0 + c + i < p.Kw) dst[i] = __float2bfloat16(v[i]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 }  // namespace trlb
 
 using namespace trlb;
@@ -272,17 +472,24 @@ using namespace trlb;
 // A [rows, K] bf16 (row stride lda), rows sorted by expert; W [E, Nw, K] bf16 contiguous with Nw = N (plain) or
 // 2 * N (swiglu: gate rows then up rows); offsets [E + 1] int32 on the device; C [rows, N] bf16 (row stride ldc).
 // `rows` is the allocated row count of A and C (an upper bound of offsets[E]).
+// `w_transposed` = 1: W is [E, K, N] and C[r, :] = A[r, :] . W[e] (the forward weight read transposed, for the
+// input gradient); N must then be a multiple of 8 and swiglu 0.
 TRLB_API int trlb_grouped_gemm_bf16(const void* A, const void* W, const int* offsets, void* C, long long rows, int E, int N,
-                                    int K, long long lda, long long ldc, int swiglu, int* status, cudaStream_t st) {
+                                    int K, long long lda, long long ldc, int swiglu, int w_transposed, int* status,
+                                    cudaStream_t st) {
   if (rows <= 0 || E <= 0) return 0;
   if (E > G_MAX_EXPERTS || (K % 8) != 0 || (lda % 8) != 0) return -130;
+  if (w_transposed && (swiglu || (N % 8) != 0)) return -130;
   const long long Nw = swiglu ? 2LL * N : N;
   TmapArray ta;
   CUtensorMap tb;
   int r = trlb_host::make_tmap_2d_bf16(&ta.m[0], A, (uint64_t)rows, (uint64_t)K, (uint64_t)lda, GBM, GBK);
   if (r) return -131;
   for (int i = 1; i < 8; ++i) ta.m[i] = ta.m[0];
-  r = trlb_host::make_tmap_3d_bf16(&tb, W, (uint64_t)K, (uint64_t)Nw, (uint64_t)E, (uint64_t)K, (uint64_t)Nw * K, GBK, 128, 1);
+  r = w_transposed
+          ? trlb_host::make_tmap_3d_bf16(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)E, (uint64_t)N, (uint64_t)N * K, 64, GBK, 1)
+          : trlb_host::make_tmap_3d_bf16(&tb, W, (uint64_t)K, (uint64_t)Nw, (uint64_t)E, (uint64_t)K, (uint64_t)Nw * K, GBK,
+                                         128, 1);
   if (r) return -132;
   static bool attr_set = false;
   if (!attr_set) {
@@ -290,7 +497,7 @@ TRLB_API int trlb_grouped_gemm_bf16(const void* A, const void* W, const int* off
     attr_set = true;
   }
   GroupedParams p = {};
-  p.E = E; p.N = N; p.K = K; p.swiglu = swiglu;
+  p.E = E; p.N = N; p.K = K; p.swiglu = swiglu; p.b_mn = w_transposed ? 1 : 0;
   p.n_tiles = swiglu ? (N + 127) / 128 : (N + GBN - 1) / GBN;
   p.k_blocks = (K + GBK - 1) / GBK;
   p.offsets = offsets; p.C = (__nv_bfloat16*)C; p.ldc = ldc; p.status = status;
@@ -340,5 +547,33 @@ TRLB_API int trlb_grouped_gemm_seg_bf16(const unsigned long long* a_bases, const
   int grid = trlb_host::sm_count();
   if (max_items < grid) grid = (int)max_items;
   grouped_gemm_kernel<<<grid, G_THREADS, G_SMEM, st>>>(ta, tb, p);
+  return (int)cudaGetLastError();
+}
+
+// dW[e] = G[offsets[e] : offsets[e+1]]^T . X[offsets[e] : offsets[e+1]] for every expert.  G [rows, Nw] (row stride ldg),
+// X [rows, Kw] (row stride ldx), dW [E, Nw, Kw] contiguous bf16.  Nw, Kw, ldg, ldx multiples of 8.
+TRLB_API int trlb_grouped_wgrad_bf16(const void* G, const void* X, const int* offsets, void* dW, long long rows, int E,
+                                     int Nw, int Kw, long long ldg, long long ldx, int* status, cudaStream_t st) {
+  if (E <= 0 || Nw <= 0 || Kw <= 0) return 0;
+  if ((Nw % 8) != 0 || (Kw % 8) != 0 || (ldg % 8) != 0 || (ldx % 8) != 0) return -136;
+  if (rows <= 0) return (int)cudaMemsetAsync(dW, 0, (size_t)E * Nw * Kw * 2, st);
+  CUtensorMap tg, tx;
+  // a [rows, cols] matrix read in [64 rows x 64 columns] boxes: rows are the reduction dimension
+  if (trlb_host::make_tmap_2d_bf16(&tg, G, (uint64_t)rows, (uint64_t)Nw, (uint64_t)ldg, GBK, 64)) return -137;
+  if (trlb_host::make_tmap_2d_bf16(&tx, X, (uint64_t)rows, (uint64_t)Kw, (uint64_t)ldx, GBK, 64)) return -138;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(grouped_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G_SMEM);
+    attr_set = true;
+  }
+  GroupedWgradParams p = {};
+  p.E = E; p.Nw = Nw; p.Kw = Kw;
+  p.m_tiles = (Nw + GBM - 1) / GBM;
+  p.n_tiles = (Kw + GBN - 1) / GBN;
+  p.offsets = offsets; p.dW = (__nv_bfloat16*)dW; p.status = status;
+  const long long items = (long long)E * p.m_tiles * p.n_tiles;
+  int grid = trlb_host::sm_count();
+  if (items < grid) grid = (int)items;
+  grouped_wgrad_kernel<<<grid, G_THREADS, G_SMEM, st>>>(tg, tx, p);
   return (int)cudaGetLastError();
 }

@@ -495,35 +495,47 @@ def attention_varlen_qk(q, k, v, cu_q, cu_k, max_q, max_k):
                        int(max_q), int(max_k), window_size=(-1, 0))
 
 
-def grouped_gemm(a, w, offsets, n_out, swiglu=False, out=None):
+def grouped_gemm(a, w, offsets, n_out, swiglu=False, out=None, w_transposed=False):
     """Per-expert GEMM on tcgen05: rows of ``a`` [R, K] are sorted by expert, ``offsets`` [E + 1] int32 on the device,
     ``w`` [E, n_out (or 2 * n_out with swiglu), K].  Returns [R, n_out]; with ``swiglu`` the gate / up halves are
-    combined in the epilogue."""
+    combined in the epilogue.  ``w_transposed``: ``w`` is [E, K, n_out] and is read as it lies (the input gradient of
+    a layer whose forward weight is ``w``)."""
     R, Kd = a.shape
     E = w.shape[0]
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and a.stride(1) == 1
-    assert w.shape[1] == (2 * n_out if swiglu else n_out) and w.shape[2] == Kd
+    if w_transposed:
+        assert not swiglu and w.shape[1] == Kd and w.shape[2] == n_out
+    else:
+        assert w.shape[1] == (2 * n_out if swiglu else n_out) and w.shape[2] == Kd
     if out is None:
         out = torch.empty(R, n_out, dtype=torch.bfloat16, device=a.device)
     _chk(lib().trlb_grouped_gemm_bf16(_p(a), _p(w), _p(offsets), _p(out), c_longlong(R), c_int(E), c_int(n_out), c_int(Kd),
                                       c_longlong(a.stride(0)), c_longlong(out.stride(0)), c_int(int(swiglu)),
-                                      _p(status_buffer(a.device)), _s()), "grouped_gemm")
+                                      c_int(int(w_transposed)), _p(status_buffer(a.device)), _s()), "grouped_gemm")
     return out
 
 
-def _grouped_mm_ref(a, b, offsets_host, transpose_b):
-    """Library fallback for the backward products: per-expert cuBLAS on row slices."""
-    outs = []
-    for e in range(len(offsets_host) - 1):
-        s, t = offsets_host[e], offsets_host[e + 1]
-        outs.append(a[s:t] @ (b[e].t() if transpose_b else b[e]))
-    return torch.cat(outs) if outs else a.new_zeros(0, b.shape[1 if transpose_b else 2])
+def grouped_wgrad(g, x, offsets, num_experts, out=None):
+    """Per-expert weight gradient on tcgen05: ``out[e] = g[rows of e]^T @ x[rows of e]`` with ``g`` [R, N], ``x``
+    [R, K] sorted by expert and ``offsets`` [E + 1] int32 on the device; returns [E, N, K] bf16 (zeros for an expert
+    without rows).  Neither operand is transposed in memory and nothing is read back to the host."""
+    R, N = g.shape
+    Kd = x.shape[1]
+    assert g.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and g.stride(1) == 1 and x.stride(1) == 1
+    assert x.shape[0] == R
+    if out is None:
+        out = torch.empty(num_experts, N, Kd, dtype=torch.bfloat16, device=g.device)
+    _chk(lib().trlb_grouped_wgrad_bf16(_p(g), _p(x), _p(offsets), _p(out), c_longlong(R), c_int(num_experts), c_int(N),
+                                       c_int(Kd), c_longlong(g.stride(0)), c_longlong(x.stride(0)),
+                                       _p(status_buffer(g.device)), _s()), "grouped_wgrad")
+    return out
 
 
 class _MoeExpertsFn(torch.autograd.Function):
     """Sort tokens by expert, gate/up grouped GEMM with SwiGLU epilogue, down grouped GEMM, weighted combine.
-    Backward recomputes the gate/up pre-activations with the same kernel and uses library GEMMs per expert for the
-    transposed products."""
+    Backward recomputes the gate/up pre-activations with the same kernel; input gradients read the forward weights
+    transposed through the grouped kernel and weight gradients come from the grouped weight-gradient kernel, so the
+    backward has no per-expert loop and never reads the token counts back to the host."""
 
     @staticmethod
     def forward(ctx, hidden, gate_up_w, down_w, topk_w, topk_idx):
@@ -557,30 +569,25 @@ class _MoeExpertsFn(torch.autograd.Function):
         E, I2, H = gate_up_w.shape
         I = I2 // 2
         tok = order // k
-        offs = offsets.tolist()  # host copy for the per-expert library GEMMs
         w_perm = topk_w.reshape(-1).index_select(0, order).float()
         d_rows = d_out.index_select(0, tok)
         d_w_perm = (d_rows.float() * y_perm.float()).sum(-1)
         d_topk_w = torch.zeros(topk_w.numel(), dtype=torch.float32, device=d_out.device)
         d_topk_w[order] = d_w_perm
         d_y = (d_rows.float() * w_perm[:, None]).to(hidden.dtype)
-        # down projection: y = act @ Wd[e]^T, Wd[e] is [H, I]
-        d_act = _grouped_mm_ref(d_y, down_w, offs, transpose_b=False)
-        d_down = torch.zeros_like(down_w)
+        # down projection: y = act @ Wd[e]^T with Wd[e] [H, I]  ->  d_act = d_y @ Wd[e],  dWd[e] = d_y^T @ act
+        d_act = grouped_gemm(d_y, down_w, offsets, I, w_transposed=True)
+        d_down = grouped_wgrad(d_y, act, offsets, E)
         x_perm = hidden.index_select(0, tok)
         gu = grouped_gemm(x_perm, gate_up_w, offsets, I2, swiglu=False)  # recompute the pre-activations
         g, u = gu[:, :I].float(), gu[:, I:].float()
         sg = torch.sigmoid(g)
-        d_g = d_act.float() * u * sg * (1 + g * (1 - sg))
-        d_u = d_act.float() * g * sg
-        d_gu = torch.cat([d_g, d_u], 1).to(hidden.dtype)
-        d_x = _grouped_mm_ref(d_gu, gate_up_w, offs, transpose_b=False)
-        d_gate_up = torch.zeros_like(gate_up_w)
-        for e in range(E):
-            s, t = offs[e], offs[e + 1]
-            if t > s:
-                d_down[e] = d_y[s:t].t() @ act[s:t]
-                d_gate_up[e] = d_gu[s:t].t() @ x_perm[s:t]
+        d_gu = torch.empty_like(gu)
+        d_gu[:, :I] = d_act.float() * u * sg * (1 + g * (1 - sg))
+        d_gu[:, I:] = d_act.float() * g * sg
+        # gate/up projection: gu = x @ Wgu[e]^T with Wgu[e] [2I, H]  ->  d_x = d_gu @ Wgu[e],  dWgu[e] = d_gu^T @ x
+        d_x = grouped_gemm(d_gu, gate_up_w, offsets, H, w_transposed=True)
+        d_gate_up = grouped_wgrad(d_gu, x_perm, offsets, E)
         d_hidden = torch.zeros(hidden.shape, dtype=torch.float32, device=d_out.device).index_add_(0, tok, d_x.float())
         return d_hidden.to(hidden.dtype), d_gate_up, d_down, d_topk_w.view_as(topk_w).to(topk_w.dtype), None
 
