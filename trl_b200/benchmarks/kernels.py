@@ -287,8 +287,32 @@ def main():
         xp = x[order // k]
         ms1 = timeit(lambda: K.grouped_gemm(xp, gu, offsets, I, swiglu=True), a.iters, a.warmup)
         out.update(gate_up_swiglu_ms=ms1, gate_up_tflops=2.0 * a.t * k * H * 2 * I / ms1 / 1e9)
+        # backward: the block's forward + backward, and the two grouped gradient kernels on the gate/up shapes
+        xg, gug, dwg = (t.clone().requires_grad_(True) for t in (x, gu, dw))
+
+        def fwd_bwd():
+            K.moe_experts(xg, gug, dwg, tw, ti).backward(x)
+            xg.grad = gug.grad = dwg.grad = None
+        ms_fb = timeit(fwd_bwd, a.iters, a.warmup)
+        d_gu = (torch.randn(xp.shape[0], 2 * I, device=dev) * 0.1).to(torch.bfloat16)
+        ms_dx = timeit(lambda: K.grouped_gemm(d_gu, gu, offsets, H, w_transposed=True), a.iters, a.warmup)
+        dwo = torch.empty_like(gu)
+        ms_dw = timeit(lambda: K.grouped_wgrad(d_gu, xp, offsets, E, out=dwo), a.iters, a.warmup)
+        f_gu = 2.0 * a.t * k * H * 2 * I
+        out.update(moe_block_fwd_bwd_ms=ms_fb, gate_up_dgrad_ms=ms_dx, gate_up_dgrad_tflops=f_gu / ms_dx / 1e9,
+                   gate_up_wgrad_ms=ms_dw, gate_up_wgrad_tflops=f_gu / ms_dw / 1e9)
         if a.baseline:
             from trl_b200.oracle.ops import moe_experts as loop
+
+            offs_h = offsets.tolist()
+
+            def lib_grads():  # what the backward did before: one library GEMM per expert and product
+                for e in range(E):
+                    s0, s1 = offs_h[e], offs_h[e + 1]
+                    if s1 > s0:
+                        torch.matmul(d_gu[s0:s1], gu[e])
+                        torch.matmul(d_gu[s0:s1].t(), xp[s0:s1])
+            out["gate_up_dgrad_wgrad_library_loop_ms"] = timeit(lib_grads, max(2, a.iters // 3), 1)
 
             with torch.no_grad():
                 out["expert_loop_ms"] = timeit(lambda: loop(x, gu, dw, tw, ti), max(2, a.iters // 3), 1)

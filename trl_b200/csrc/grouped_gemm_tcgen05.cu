@@ -512,14 +512,17 @@ TRLB_API int trlb_grouped_gemm_bf16(const void* A, const void* W, const int* off
 // Segment mode for expert parallelism.  a_bases[i] / c_bases[i] (i < n_bufs <= 8): buffers that the segment tables index
 // (this rank's own and its peers' mappings of the same symmetric buffers); every A buffer is [a_rows, K] with row stride
 // lda, every C buffer has row stride ldc.  seg_* are int32 device arrays of length n_seg; W [E_local, Nw, K].
-// max_rows bounds the total number of rows over all segments (sizes the grid only).
+// max_rows bounds the total number of rows over all segments (sizes the grid only).  `w_transposed`: W is
+// [E_local, K, N], read as it lies (input gradient of a layer whose forward weight is W).
 TRLB_API int trlb_grouped_gemm_seg_bf16(const unsigned long long* a_bases, const unsigned long long* c_bases, int n_bufs,
                                         long long a_rows, const void* W, int E_local, int n_seg, const int* seg_rows,
                                         const int* seg_a_src, const int* seg_a_row, const int* seg_c_dst,
                                         const int* seg_c_row, const int* seg_w, long long max_rows, int N, int K,
-                                        long long lda, long long ldc, int swiglu, int* status, cudaStream_t st) {
+                                        long long lda, long long ldc, int swiglu, int w_transposed, int* status,
+                                        cudaStream_t st) {
   if (n_seg <= 0 || max_rows <= 0) return 0;
   if (n_seg > G_MAX_EXPERTS || n_bufs < 1 || n_bufs > 8 || (K % 8) != 0 || (lda % 8) != 0) return -133;
+  if (w_transposed && (swiglu || (N % 8) != 0)) return -133;
   const long long Nw = swiglu ? 2LL * N : N;
   TmapArray ta;
   CUtensorMap tb;
@@ -527,8 +530,10 @@ TRLB_API int trlb_grouped_gemm_seg_bf16(const unsigned long long* a_bases, const
     const void* base = reinterpret_cast<const void*>(a_bases[i < n_bufs ? i : 0]);
     if (trlb_host::make_tmap_2d_bf16(&ta.m[i], base, (uint64_t)a_rows, (uint64_t)K, (uint64_t)lda, GBM, GBK)) return -134;
   }
-  if (trlb_host::make_tmap_3d_bf16(&tb, W, (uint64_t)K, (uint64_t)Nw, (uint64_t)E_local, (uint64_t)K, (uint64_t)Nw * K, GBK,
-                                   128, 1))
+  if (w_transposed ? trlb_host::make_tmap_3d_bf16(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)E_local, (uint64_t)N,
+                                                  (uint64_t)N * K, 64, GBK, 1)
+                   : trlb_host::make_tmap_3d_bf16(&tb, W, (uint64_t)K, (uint64_t)Nw, (uint64_t)E_local, (uint64_t)K,
+                                                  (uint64_t)Nw * K, GBK, 128, 1))
     return -135;
   static bool attr_set = false;
   if (!attr_set) {
@@ -536,7 +541,7 @@ TRLB_API int trlb_grouped_gemm_seg_bf16(const unsigned long long* a_bases, const
     attr_set = true;
   }
   GroupedParams p = {};
-  p.E = n_seg; p.n_seg = n_seg; p.N = N; p.K = K; p.swiglu = swiglu;
+  p.E = n_seg; p.n_seg = n_seg; p.N = N; p.K = K; p.swiglu = swiglu; p.b_mn = w_transposed ? 1 : 0;
   p.n_tiles = swiglu ? (N + 127) / 128 : (N + GBN - 1) / GBN;
   p.k_blocks = (K + GBK - 1) / GBK;
   p.ldc = ldc; p.status = status;

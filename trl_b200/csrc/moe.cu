@@ -57,6 +57,47 @@ moe_pull_rows_kernel(const PullParams pp, const int* __restrict__ seg_rows, cons
   }
 }
 
+// Backward of the weighted combine, one permuted row per CTA iteration: with (t, j) = the (token, choice) that row r
+// holds (order[r] = t * k + j),
+//     d_y[r, :] = w[t, j] * d_out[t, :]          (gradient of the expert output row)
+//     d_w[t, j] = <d_out[t, :], y[r, :]>         (gradient of the routing weight)
+// d_out is read once per choice (k rows share a token; the repeats hit L2), y once, d_y written once.
+__global__ void __launch_bounds__(256)
+moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ d_out, const __nv_bfloat16* __restrict__ y,
+                       const long long* __restrict__ order, const float* __restrict__ w,
+                       __nv_bfloat16* __restrict__ d_y, float* __restrict__ d_w, long long rows, int k, int H) {
+  const int nvec = H >> 3;
+  __shared__ float part[8];
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const long long flat = order[r];
+    const long long t = flat / k;
+    const float wj = w[flat];
+    float dot = 0.f;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      const uint4 g = reinterpret_cast<const uint4*>(d_out + (size_t)t * H)[v];
+      const uint4 yy = reinterpret_cast<const uint4*>(y + (size_t)r * H)[v];
+      const uint32_t gq[4] = {g.x, g.y, g.z, g.w}, yq[4] = {yy.x, yy.y, yy.z, yy.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 a = unpack_bf16(gq[i]), b = unpack_bf16(yq[i]);
+        dot = fmaf(a.x, b.x, fmaf(a.y, b.y, dot));
+        o[i] = pack_bf16(wj * a.x, wj * a.y);
+      }
+      reinterpret_cast<uint4*>(d_y + (size_t)r * H)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    dot = warp_sum(dot);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = dot;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float s = 0.f;
+      for (int i = 0; i < (int)(blockDim.x >> 5); ++i) s += part[i];
+      d_w[flat] = s;
+    }
+    __syncthreads();
+  }
+}
+
 }  // namespace trlb
 
 using namespace trlb;
@@ -197,5 +238,17 @@ TRLB_API int trlb_moe_aux_loss(const void* probs, int probs_bf16, const long lon
   else
     trlb::moe_aux_loss_kernel<float><<<blocks, trlb::AUX_THREADS, 0, st>>>((const float*)probs, idx, mask, N, E, K,
                                                                            rows_per_block, acc, loss, f_out, valid_out);
+  return (int)cudaGetLastError();
+}
+
+// d_out [T, H] bf16, y [rows, H] bf16 (expert-sorted), order [rows] int64 (flat (token, choice) index of every row),
+// w [T * k] fp32 -> d_y [rows, H] bf16, d_w [T * k] fp32 (every entry written: order is a permutation).
+TRLB_API int trlb_moe_combine_bwd(const void* d_out, const void* y, const long long* order, const float* w, void* d_y,
+                                  float* d_w, long long rows, int k, int H, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (H % 8) return -142;
+  const long long grid = rows < 148LL * 16 ? rows : 148LL * 16;
+  moe_combine_bwd_kernel<<<(int)grid, 256, 0, st>>>((const __nv_bfloat16*)d_out, (const __nv_bfloat16*)y, order, w,
+                                                    (__nv_bfloat16*)d_y, d_w, rows, k, H);
   return (int)cudaGetLastError();
 }

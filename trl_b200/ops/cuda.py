@@ -531,6 +531,29 @@ def grouped_wgrad(g, x, offsets, num_experts, out=None):
     return out
 
 
+def moe_combine_bwd(d_out, y_perm, order, topk_w, d_y=None):
+    """Backward of the weighted combine in one pass: ``d_y[r] = w[order[r]] * d_out[order[r] // k]`` (bf16, written to
+    ``d_y`` when given) and ``d_w[order[r]] = <d_out[order[r] // k], y_perm[r]>`` (fp32, shaped like ``topk_w``)."""
+    rows, H = y_perm.shape
+    k = topk_w.shape[1]
+    d_y = torch.empty(rows, H, dtype=torch.bfloat16, device=d_out.device) if d_y is None else d_y
+    d_w = torch.empty(topk_w.numel(), dtype=torch.float32, device=d_out.device)
+    assert d_out.dtype == torch.bfloat16 and y_perm.dtype == torch.bfloat16 and order.dtype == torch.int64
+    assert d_y.is_contiguous() and y_perm.is_contiguous()
+    _chk(lib().trlb_moe_combine_bwd(_p(d_out.contiguous()), _p(y_perm), _p(order), _p(topk_w.float().contiguous()),
+                                    _p(d_y), _p(d_w), c_longlong(rows), c_int(k), c_int(H), _s()), "moe_combine_bwd")
+    return d_y, d_w.view_as(topk_w)
+
+
+def moe_gather_sum(rows, inv, T, k):
+    """``out[t] = sum_j rows[inv[t, j]]`` (bf16): the scatter-add of permuted rows back to tokens, as a gather."""
+    H = rows.shape[1]
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=rows.device)
+    ones = torch.ones(T * k, dtype=torch.float32, device=rows.device)
+    _chk(lib().trlb_moe_combine(_p(rows), _p(inv), _p(ones), _p(out), c_int(T), c_int(k), c_int(H), _s()), "moe_combine")
+    return out
+
+
 class _MoeExpertsFn(torch.autograd.Function):
     """Sort tokens by expert, gate/up grouped GEMM with SwiGLU epilogue, down grouped GEMM, weighted combine.
     Backward recomputes the gate/up pre-activations with the same kernel; input gradients read the forward weights
@@ -558,38 +581,30 @@ class _MoeExpertsFn(torch.autograd.Function):
         out = torch.empty(T, H, dtype=torch.bfloat16, device=hidden.device)
         _chk(lib().trlb_moe_combine(_p(y_perm), _p(inv), _p(topk_w.float().contiguous()), _p(out), c_int(T), c_int(k),
                                     c_int(H), _s()), "moe_combine")
-        ctx.save_for_backward(hidden, gate_up_w, down_w, topk_w, order, offsets, act, y_perm)
+        ctx.save_for_backward(hidden, gate_up_w, down_w, topk_w, order, offsets, act, y_perm, inv)
         ctx.k = k
         return out
 
     @staticmethod
     def backward(ctx, d_out):
-        hidden, gate_up_w, down_w, topk_w, order, offsets, act, y_perm = ctx.saved_tensors
+        hidden, gate_up_w, down_w, topk_w, order, offsets, act, y_perm, inv = ctx.saved_tensors
         k = ctx.k
         E, I2, H = gate_up_w.shape
         I = I2 // 2
-        tok = order // k
-        w_perm = topk_w.reshape(-1).index_select(0, order).float()
-        d_rows = d_out.index_select(0, tok)
-        d_w_perm = (d_rows.float() * y_perm.float()).sum(-1)
-        d_topk_w = torch.zeros(topk_w.numel(), dtype=torch.float32, device=d_out.device)
-        d_topk_w[order] = d_w_perm
-        d_y = (d_rows.float() * w_perm[:, None]).to(hidden.dtype)
+        T = hidden.shape[0]
+        d_y, d_topk_w = moe_combine_bwd(d_out, y_perm, order, topk_w)
         # down projection: y = act @ Wd[e]^T with Wd[e] [H, I]  ->  d_act = d_y @ Wd[e],  dWd[e] = d_y^T @ act
         d_act = grouped_gemm(d_y, down_w, offsets, I, w_transposed=True)
         d_down = grouped_wgrad(d_y, act, offsets, E)
-        x_perm = hidden.index_select(0, tok)
+        x_perm = hidden.index_select(0, order // k)
         gu = grouped_gemm(x_perm, gate_up_w, offsets, I2, swiglu=False)  # recompute the pre-activations
-        g, u = gu[:, :I].float(), gu[:, I:].float()
-        sg = torch.sigmoid(g)
         d_gu = torch.empty_like(gu)
-        d_gu[:, :I] = d_act.float() * u * sg * (1 + g * (1 - sg))
-        d_gu[:, I:] = d_act.float() * g * sg
+        _chk(lib().trlb_swiglu_bwd(_p(d_act), _p(gu), _p(d_gu), c_longlong(gu.shape[0]), c_int(I), _s()), "swiglu_bwd")
         # gate/up projection: gu = x @ Wgu[e]^T with Wgu[e] [2I, H]  ->  d_x = d_gu @ Wgu[e],  dWgu[e] = d_gu^T @ x
         d_x = grouped_gemm(d_gu, gate_up_w, offsets, H, w_transposed=True)
         d_gate_up = grouped_wgrad(d_gu, x_perm, offsets, E)
-        d_hidden = torch.zeros(hidden.shape, dtype=torch.float32, device=d_out.device).index_add_(0, tok, d_x.float())
-        return d_hidden.to(hidden.dtype), d_gate_up, d_down, d_topk_w.view_as(topk_w).to(topk_w.dtype), None
+        d_hidden = moe_gather_sum(d_x, inv, T, k)
+        return d_hidden, d_gate_up, d_down, d_topk_w.to(topk_w.dtype), None
 
 
 def moe_experts(hidden, gate_up_w, down_w, topk_w, topk_idx):

@@ -15,8 +15,10 @@ kernel and runs the first GEMM on the local copy.  Only the per-expert row offse
 The reference reaches expert parallelism through DeepSpeed / accelerate sharding of transformers MoE blocks
 (trl/accelerate_configs/*.yaml); it has no fused path.
 
-Backward (training) moves rows with ``all_to_all_single`` and uses library GEMMs per expert; the gate/up
-pre-activations are recomputed with the fused kernel.
+Backward (training) moves rows the same way: x and d_y rows are pulled from the source ranks, the local experts'
+input and weight gradients run on the grouped kernels (forward weights read transposed; ``grouped_wgrad``), and the
+stores of the last grouped GEMM return the d_x rows to their source ranks.  The gate/up pre-activations are
+recomputed.
 
 ``shard_experts(model, group)`` wires the block into a model (expert slices as parameters flagged ``_ep_local``,
 ``layer.ep`` called by ``DecoderLayer.mlp_block``); ``HostExpertParallelMoE`` is the same block over the backend's
@@ -82,14 +84,31 @@ class ExpertParallelMoE:
         return order, offsets, all_off, dict(rows=seg_rows.contiguous(), act_row=seg_act_row, src=seg_src,
                                              src_row=seg_src_row, w=seg_w, zeros=zeros, loc_off=loc_off)
 
-    def _seg_gemm(self, a_bases, c_bases, n_bufs, a_rows, w, seg, a_src, a_row, c_dst, c_row, n_out, k_dim, lda, ldc, swiglu):
+    def _seg_gemm(self, a_bases, c_bases, n_bufs, a_rows, w, seg, a_src, a_row, c_dst, c_row, n_out, k_dim, lda, ldc, swiglu,
+                  w_transposed=False):
         from ..ops.cuda import _chk, _p, _s, lib, status_buffer
 
         _chk(lib().trlb_grouped_gemm_seg_bf16(a_bases, c_bases, c_int(n_bufs), c_longlong(a_rows), _p(w), c_int(w.shape[0]),
                                               c_int(seg["rows"].numel()), _p(seg["rows"]), _p(a_src), _p(a_row), _p(c_dst),
                                               _p(c_row), _p(seg["w"]), c_longlong(self.world * self.max_rows), c_int(n_out),
                                               c_int(k_dim), c_longlong(lda), c_longlong(ldc), c_int(int(swiglu)),
-                                              _p(status_buffer(self.dev)), _s()), "grouped_gemm_seg")
+                                              c_int(int(w_transposed)), _p(status_buffer(self.dev)), _s()),
+             "grouped_gemm_seg")
+
+    def _pull_rows(self, bases, seg, dst):
+        """dst[segment rows] = rows of the source ranks' symmetric buffer (each row crosses NVLink once)."""
+        from ..ops.cuda import _chk, _p, _s, lib
+
+        _chk(lib().trlb_moe_pull_rows(bases, c_int(self.world), _p(seg["rows"]), _p(seg["src"]), _p(seg["src_row"]),
+                                      _p(seg["act_row"]), c_int(seg["rows"].numel()), _p(dst), c_int(self.H), _s()),
+             "moe_pull_rows")
+
+    def _bwd_buffer(self, name):
+        buf = getattr(self, name, None)
+        if buf is None:
+            buf = torch.empty(self.world * self.max_rows, self.H, dtype=torch.bfloat16, device=self.dev)
+            setattr(self, name, buf)
+        return buf
 
     def _device_barrier(self):
         td.all_reduce(self._sync, group=self.group)  # stream-ordered: completes when every rank has reached it
@@ -112,9 +131,7 @@ class ExpertParallelMoE:
         else:
             from ..ops.cuda import grouped_gemm
 
-            _chk(lib().trlb_moe_pull_rows(self._a_x, c_int(self.world), _p(seg["rows"]), _p(seg["src"]), _p(seg["src_row"]),
-                                          _p(seg["act_row"]), c_int(seg["rows"].numel()), _p(self.x_in), c_int(H), _s()),
-                 "moe_pull_rows")
+            self._pull_rows(self._a_x, seg, self.x_in)
             grouped_gemm(self.x_in, gate_up_local, seg["loc_off"], self.I, swiglu=True, out=self.act)
         self._seg_gemm(self._self_act, self._c_y, self.world, self.world * self.max_rows, down_local, seg, seg["zeros"],
                        seg["act_row"], seg["src"], seg["src_row"], H, self.I, self.I, H, False)
@@ -145,50 +162,48 @@ class _EpMoeFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, d_out):
+        """Rows travel as in the forward pass: x and d_y rows are pulled from the source ranks' symmetric buffers into
+        the expert-sorted local layout, the local experts' gradients run on the grouped kernels, and the stores of the
+        last grouped GEMM put every d_x row back into its source rank's buffer.  One scalar (the number of rows this
+        rank's experts received) is read back to size the element-wise work."""
+        from ..ops.cuda import _chk, _p, _s, grouped_gemm, grouped_wgrad, lib, moe_combine_bwd, moe_gather_sum
+
         ep, keep, k = ctx.ep, ctx.keep, ctx.k
         hidden, gu_w, dn_w, topk_w = ctx.saved_tensors
         W, E_loc, I, H = ep.world, ep.E_loc, ep.I, ep.H
-        order, all_off = keep["order"], keep["all_off"].cpu()
+        order, seg = keep["order"], keep["seg"]
         tok = order // k
-        w_perm = topk_w.reshape(-1).index_select(0, order).float()
-        d_rows = d_out.index_select(0, tok)
-        d_topk = torch.zeros(topk_w.numel(), dtype=torch.float32, device=d_out.device)
-        d_topk[order] = (d_rows.float() * keep["y_perm"].float()).sum(-1)
-        d_y = (d_rows.float() * w_perm[:, None]).to(hidden.dtype)
-        x_perm = hidden.index_select(0, tok)
-        # rows this rank sends to rank r: its tokens for r's experts (contiguous in expert-sorted order)
-        mine = all_off[ep.rank]
-        send = [int(mine[(r + 1) * E_loc] - mine[r * E_loc]) for r in range(W)]
-        e0 = ep.rank * E_loc
-        recv = [int(all_off[s, e0 + E_loc] - all_off[s, e0]) for s in range(W)]
-
-        def exchange(t, send_counts, recv_counts):
-            out = torch.empty(sum(recv_counts), t.shape[1], dtype=t.dtype, device=t.device)
-            td.all_to_all_single(out, t.contiguous(), recv_counts, send_counts, group=ep.group)
-            return out
-        d_y_in, x_in = exchange(d_y, send, recv), exchange(x_perm, send, recv)  # layout: source-major, expert-minor
-        d_x_in = torch.empty_like(x_in)
-        d_gu_w, d_dn_w = torch.zeros_like(gu_w), torch.zeros_like(dn_w)
-        base = [sum(recv[:s]) for s in range(W)]
-        for e in range(E_loc):
-            idx = torch.cat([torch.arange(base[s] + int(all_off[s, e0 + e] - all_off[s, e0]),
-                                          base[s] + int(all_off[s, e0 + e + 1] - all_off[s, e0]), device=d_out.device)
-                             for s in range(W)])
-            if idx.numel() == 0:
-                continue
-            xe, dye = x_in[idx], d_y_in[idx]
-            gu = xe @ gu_w[e].t()
-            g, u = gu[:, :I].float(), gu[:, I:].float()
-            sg = torch.sigmoid(g)
-            act = (g * sg * u).to(xe.dtype)
-            d_dn_w[e] = dye.t() @ act
-            d_act = (dye @ dn_w[e]).float()
-            d_gu = torch.cat([d_act * u * sg * (1 + g * (1 - sg)), d_act * g * sg], 1).to(xe.dtype)
-            d_gu_w[e] = d_gu.t() @ xe
-            d_x_in[idx] = d_gu @ gu_w[e]
-        d_x = exchange(d_x_in, recv, send)
-        d_hidden = torch.zeros(hidden.shape, dtype=torch.float32, device=d_out.device).index_add_(0, tok, d_x.float())
-        return d_hidden.to(hidden.dtype), d_gu_w, d_dn_w, d_topk.view_as(topk_w).to(topk_w.dtype), None, None
+        Tk = order.numel()
+        torch.index_select(hidden, 0, tok, out=ep.x_buf[:Tk])
+        _, d_topk = moe_combine_bwd(d_out, keep["y_perm"], order, topk_w, d_y=ep.y_buf[:Tk])
+        ep._device_barrier()  # every rank's x and d_y rows are in place
+        x_full = ep.x_in if ep.x_in is not None else ep._bwd_buffer("_x_in_bwd")
+        dy_full = ep._bwd_buffer("_dy_in_bwd")
+        ep._pull_rows(ep._a_x, seg, x_full)
+        ep._pull_rows(ep._c_y, seg, dy_full)
+        ep._device_barrier()  # every rank has pulled: x_buf is free to receive the d_x rows
+        off = seg["loc_off"]
+        n = int(off[-1])
+        if n > 0:
+            x_in, dy_in = x_full[:n], dy_full[:n]
+            gu = grouped_gemm(x_in, gu_w, off, 2 * I)  # recompute the pre-activations
+            act = torch.empty(n, I, dtype=gu.dtype, device=gu.device)
+            _chk(lib().trlb_swiglu_fwd(_p(gu), _p(act), c_longlong(n), c_int(I), _s()), "swiglu_fwd")
+            d_dn_w = grouped_wgrad(dy_in, act, off, E_loc)
+            d_act = grouped_gemm(dy_in, dn_w, off, I, w_transposed=True)
+            d_gu = torch.empty_like(gu)
+            _chk(lib().trlb_swiglu_bwd(_p(d_act), _p(gu), _p(d_gu), c_longlong(n), c_int(I), _s()), "swiglu_bwd")
+            d_gu_w = grouped_wgrad(d_gu, x_in, off, E_loc)
+            bases = (ctypes.c_ulonglong * W)(*([d_gu.data_ptr()] * W))
+            ep._seg_gemm(bases, ep._a_x, W, n, gu_w, seg, seg["zeros"], seg["act_row"], seg["src"], seg["src_row"], H,
+                         2 * I, 2 * I, H, False, w_transposed=True)
+        else:
+            d_gu_w, d_dn_w = torch.zeros_like(gu_w), torch.zeros_like(dn_w)
+        ep._device_barrier()  # all peers have stored my d_x rows
+        inv = torch.empty(Tk, dtype=torch.int32, device=d_out.device)
+        inv[order] = torch.arange(Tk, dtype=torch.int32, device=d_out.device)
+        d_hidden = moe_gather_sum(ep.x_buf, inv, hidden.shape[0], k)
+        return d_hidden, d_gu_w, d_dn_w, d_topk.to(topk_w.dtype), None, None
 
 
 # ---------------------------------------------------------------------------------------------------------------------
