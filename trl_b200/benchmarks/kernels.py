@@ -93,12 +93,18 @@ def main():
         ms_dx = timeit(lambda: K.gemm_bf16(dY, B, b_mn=True, out=dX), a.iters, a.warmup)
         ms_dw = timeit(lambda: K.gemm_bf16(dY, A, a_mn=True, b_mn=True, out=dW), a.iters, a.warmup)
         out.update(dgrad_ms=ms_dx, dgrad_tflops=fl / ms_dx / 1e9, wgrad_ms=ms_dw, wgrad_tflops=fl / ms_dw / 1e9)
+        # the same three products on the CTA-pair kernel (cta_group::2, 256 x 256 tile per pair of SMs)
+        ms_p = timeit(lambda: K.gemm_pair_bf16(A, B, out=C), a.iters, a.warmup)
+        ms_pdx = timeit(lambda: K.gemm_pair_bf16(dY, B, b_mn=True, out=dX), a.iters, a.warmup)
+        ms_pdw = timeit(lambda: K.gemm_pair_bf16(dY, A, a_mn=True, b_mn=True, out=dW), a.iters, a.warmup)
+        out.update(pair_ms=ms_p, pair_tflops=fl / ms_p / 1e9, pair_dgrad_ms=ms_pdx, pair_wgrad_ms=ms_pdw)
         if a.baseline:
             ms2 = timeit(lambda: torch.matmul(A, B.t(), out=C), a.iters, a.warmup)
             ms3 = timeit(lambda: torch.matmul(dY, B, out=dX), a.iters, a.warmup)
             ms4 = timeit(lambda: torch.matmul(dY.t(), A, out=dW), a.iters, a.warmup)
             out.update(cublas_ms=ms2, cublas_tflops=fl / ms2 / 1e9, cublas_dgrad_ms=ms3, cublas_wgrad_ms=ms4,
-                       fwd_vs_cublas=ms2 / ms, dgrad_vs_cublas=ms3 / ms_dx, wgrad_vs_cublas=ms4 / ms_dw)
+                       fwd_vs_cublas=ms2 / ms, dgrad_vs_cublas=ms3 / ms_dx, wgrad_vs_cublas=ms4 / ms_dw,
+                       pair_fwd_vs_cublas=ms2 / ms_p, pair_dgrad_vs_cublas=ms3 / ms_pdx, pair_wgrad_vs_cublas=ms4 / ms_pdw)
     elif a.kernel in ("lmhead", "lmhead_bwd"):
         H = torch.randn(a.m, a.k, device=dev, dtype=torch.bfloat16)
         W = (torch.randn(a.v, a.k, device=dev) * 0.02).to(torch.bfloat16)

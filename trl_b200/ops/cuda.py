@@ -98,6 +98,22 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias=None, *, a_mn: bool = False
     return out
 
 
+def gemm_pair_bf16(a: torch.Tensor, b: torch.Tensor, bias=None, *, a_mn: bool = False, b_mn: bool = False, out=None):
+    """Same contract as :func:`gemm_bf16` on the CTA-pair kernel (``tcgen05`` ``cta_group::2``: two SMs per 256 x 256
+    tile, each staging its own rows of ``a`` and half of the ``b`` tile).  Plain store epilogue (+ bias)."""
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.is_cuda and a.stride(-1) == 1 and b.stride(-1) == 1
+    K_, M = (a.shape if a_mn else a.shape[::-1])
+    Kb, N = (b.shape if b_mn else b.shape[::-1])
+    assert K_ == Kb, (a.shape, b.shape, a_mn, b_mn)
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    rc = lib().trlb_gemm_pair_bf16(_p(a), _p(b), _p(out), _p(bias), c_int(M), c_int(N), c_int(K_), c_longlong(a.stride(0)),
+                                   c_longlong(b.stride(0)), c_longlong(out.stride(0)), c_int(int(a_mn)), c_int(int(b_mn)),
+                                   _p(status_buffer(a.device)), _s())
+    _chk(rc, "trlb_gemm_pair_bf16")
+    return out
+
+
 class LinearFn(torch.autograd.Function):
     """``y = x W^T (+ b)`` with forward, input gradient and weight gradient all on the tcgen05 GEMM (no operand is
     transposed in memory; the bias gradient is a column sum)."""
