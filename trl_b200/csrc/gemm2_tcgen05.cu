@@ -23,7 +23,7 @@ namespace trlb {
 
 constexpr int P_BM = 128;   // rows of A per CTA (256 per pair)
 constexpr int P_BN = 256;   // columns of the pair's tile; each CTA stages P_BN / 2 of them
-constexpr int P_BK = 64, P_STAGES = 6;
+constexpr int P_BK = 64, P_STAGES = 7;
 constexpr uint32_t P_A_BYTES = P_BM * P_BK * 2, P_B_BYTES = (P_BN / 2) * P_BK * 2, P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
 constexpr int P_THREADS = 192;
 constexpr size_t P_SMEM = P_STAGES * P_STAGE_BYTES + 1024 + 256;

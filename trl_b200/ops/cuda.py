@@ -114,6 +114,12 @@ def gemm_pair_bf16(a: torch.Tensor, b: torch.Tensor, bias=None, *, a_mn: bool = 
     return out
 
 
+def _linear_gemm(*a, **kw):
+    """The GEMM of :class:`LinearFn`: the CTA-pair kernel (faster of the two own kernels); ``TRL_B200_GEMM_PAIR=0``
+    selects the one-CTA kernel."""
+    return (gemm_pair_bf16 if os.environ.get("TRL_B200_GEMM_PAIR", "1") != "0" else gemm_bf16)(*a, **kw)
+
+
 class LinearFn(torch.autograd.Function):
     """``y = x W^T (+ b)`` with forward, input gradient and weight gradient all on the tcgen05 GEMM (no operand is
     transposed in memory; the bias gradient is a column sum)."""
@@ -125,7 +131,7 @@ class LinearFn(torch.autograd.Function):
             x2 = x2.contiguous()
         ctx.save_for_backward(x2, weight)
         ctx.has_bias, ctx.shape = bias is not None, x.shape
-        return gemm_bf16(x2, weight, bias).view(*x.shape[:-1], weight.shape[0])
+        return _linear_gemm(x2, weight, bias).view(*x.shape[:-1], weight.shape[0])
 
     @staticmethod
     def backward(ctx, gy):
@@ -133,8 +139,8 @@ class LinearFn(torch.autograd.Function):
         g2 = gy.reshape(-1, gy.shape[-1])
         if g2.stride(-1) != 1 or g2.stride(0) % 8:
             g2 = g2.contiguous()
-        dx = gemm_bf16(g2, weight, b_mn=True).view(ctx.shape) if ctx.needs_input_grad[0] else None
-        dw = gemm_bf16(g2, x2, a_mn=True, b_mn=True) if ctx.needs_input_grad[1] else None
+        dx = _linear_gemm(g2, weight, b_mn=True).view(ctx.shape) if ctx.needs_input_grad[0] else None
+        dw = _linear_gemm(g2, x2, a_mn=True, b_mn=True) if ctx.needs_input_grad[1] else None
         db = g2.sum(0).to(gy.dtype) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
         return dx, dw, db
 

@@ -31,7 +31,7 @@ import os as _os
 
 # which GEMM the decoder's plain linears run on: "own" = this library's tcgen05 kernel for the forward, the input
 # gradient and the weight gradient (operands read transposed in place), "cublas" = the library GEMM through torch.
-# The default follows the measurements in benchmarks/kernels.py gemm (see DESIGN.md): the library where it is faster.
+# The default follows the measurements in benchmarks/kernels.py gemm: the library where it is faster.
 _LINEAR_IMPL = _os.environ.get("TRL_B200_LINEAR", "cublas")
 
 
