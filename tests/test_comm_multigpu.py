@@ -29,6 +29,14 @@ def test_tp_rollout_engine_two_ranks(fused):
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp_rollout_engine_with_expert_layers():
+    """Mixture-of-experts model under tensor parallelism: every expert sliced along its intermediate dimension."""
+    rc, out, err = run_ranks(os.path.join(HERE, "dist_worker_tp_rollout_gpu.py"), 29682,
+                             extra_env={"TRL_B200_TP_FUSED": "0", "TP_TEST_MOE": "1"})
+    assert rc == 0 and "TP_ROLLOUT_OK" in out, out[-3000:] + err[-3000:]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_full_shard_engine_two_ranks():
     rc, out, err = run_ranks(os.path.join(HERE, "dist_worker_fullshard_gpu.py"), 29623)
     assert rc == 0 and "FULLSHARD_OK" in out, out[-3000:] + err[-3000:]

@@ -27,6 +27,9 @@ class WeightResharder:
         self.engine, self.tp = engine, tp_engine
         arena = engine._arenas["param"]
         cfg, r, tp = tp_engine.cfg, tp_engine.tp_rank, tp_engine.tp
+        if cfg.is_moe:
+            raise NotImplementedError("full shard -> tensor-parallel copy lists for expert weights (gather the "
+                                      "parameters and call the engine's sync_weights instead)")
         D, I, H = cfg.head_dim, cfg.intermediate_size, cfg.hidden_size
         qs, ks = cfg.q_size, cfg.kv_size
         ql, kl, il = tp_engine.hq_local * D, tp_engine.hk_local * D, I // tp

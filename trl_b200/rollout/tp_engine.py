@@ -50,14 +50,16 @@ class TPRolloutEngine(RolloutEngine):
         tp, tp_rank = td.get_world_size(tp_group), td.get_rank(tp_group)
         super().__init__(model, max_num_seqs=max_num_seqs * tp, max_model_len=max_model_len, tp=tp, tp_rank=tp_rank, **kw)
         cfg, dev, dt = self.cfg, self.dev, torch.bfloat16
-        if cfg.is_moe:
-            raise NotImplementedError("TP decode of MoE layers")
         if self.max_seqs > 148:
             raise ValueError("TP decode batch (max_num_seqs * tp) is limited to 148 rows per step")
-        H, D, I = cfg.hidden_size, cfg.head_dim, cfg.intermediate_size
+        # mixture-of-experts layers: every rank keeps 1 / tp of every expert's intermediate dimension (router replicated),
+        # so the block's output is a partial sum like a dense MLP's and rides on the same all-reduce
+        H, D, I = cfg.hidden_size, cfg.head_dim, (cfg.moe_intermediate_size if cfg.is_moe else cfg.intermediate_size)
+        if I % tp or (cfg.is_moe and (I // tp) % 8):
+            raise ValueError(f"tensor parallel size {tp} must divide the MLP width {I} (in multiples of 8 for experts)")
         ql, kl, il = self.hq_local * D, self.hk_local * D, I // tp
         self._dims = (ql, kl, il)
-        self.fused = (os.environ.get("TRL_B200_TP_FUSED", "0") == "1" and self.max_seqs <= 128 and H <= 8192 and H % 8 == 0
+        self.fused = (os.environ.get("TRL_B200_TP_FUSED", "0") == "1" and not cfg.is_moe and self.max_seqs <= 128 and H <= 8192 and H % 8 == 0
                       and D <= 128 and ql % 128 == 0 and kl % 128 == 0 and il % 128 == 0 and tp <= 8)
         self._pdl = os.environ.get("TRL_B200_PDL", "1") == "1"
         self.w = []
@@ -106,8 +108,8 @@ class TPRolloutEngine(RolloutEngine):
                     "qkv": torch.empty(ql + 2 * kl, H, dtype=dt, device=dev),
                     "qkv_b": torch.empty(ql + 2 * kl, dtype=dt, device=dev) if cfg.attention_bias else None,
                     "o": torch.empty(H, ql, dtype=dt, device=dev),
-                    "gu": torch.empty(2 * il, H, dtype=dt, device=dev),
-                    "down": torch.empty(H, il, dtype=dt, device=dev),
+                    "gu": torch.empty(*((cfg.num_experts,) if cfg.is_moe else ()), 2 * il, H, dtype=dt, device=dev),
+                    "down": torch.empty(*((cfg.num_experts,) if cfg.is_moe else ()), H, il, dtype=dt, device=dev),
                 })
             self.n_sites = 2 * cfg.num_hidden_layers
             self.site_elems = self.max_seqs * H
@@ -149,6 +151,12 @@ class TPRolloutEngine(RolloutEngine):
                     w["qkv_b"][o:o + n].copy_(l.qkv_bias[start:start + n])
                 o += n
             w["o"].copy_(l.o_proj[:, r * ql:(r + 1) * ql])
+            if cfg.is_moe:
+                Im = cfg.moe_intermediate_size
+                w["gu"][:, :il].copy_(l.experts_gate_up[:, r * il:(r + 1) * il])
+                w["gu"][:, il:].copy_(l.experts_gate_up[:, Im + r * il:Im + (r + 1) * il])
+                w["down"].copy_(l.experts_down[:, :, r * il:(r + 1) * il])
+                continue
             w["gu"][:il].copy_(l.gate_up_proj[r * il:(r + 1) * il])
             w["gu"][il:].copy_(l.gate_up_proj[I + r * il:I + (r + 1) * il])
             w["down"].copy_(l.down_proj[:, r * il:(r + 1) * il])
@@ -218,6 +226,11 @@ class TPRolloutEngine(RolloutEngine):
                 h = K.allreduce_add_rmsnorm(self.arena, self.partials_off + (site - 1) * self.site_elems * 2, 0, x,
                                             l.input_layernorm, eps, self.sync)
             qkv = F.linear(h, w["qkv"], w["qkv_b"])
+            if cfg.qk_norm:  # per-head RMSNorm of this rank's q and k heads (Qwen3 families)
+                ql, kl, _ = self._dims
+                qn = K.rmsnorm_infer(qkv[:, :ql].reshape(-1, cfg.head_dim).contiguous(), l.q_norm, eps)
+                kn = K.rmsnorm_infer(qkv[:, ql:ql + kl].reshape(-1, cfg.head_dim).contiguous(), l.k_norm, eps)
+                qkv = torch.cat([qn.view(-1, ql), kn.view(-1, kl), qkv[:, ql + kl:]], dim=1)
             K.rope_kv_write(qkv, self.seq_lens, None, self.block_table, self.block_size, self.q_buf, self.k_cache[li],
                             self.v_cache[li], self.hq_local, self.hk_local, cfg.head_dim, cfg.rope_theta,
                             v_transposed=self.attn_tc, pos_delta=self.rope_delta)
@@ -226,8 +239,14 @@ class TPRolloutEngine(RolloutEngine):
             h = K.allreduce_add_rmsnorm(self.arena, self.partials_off + site * self.site_elems * 2, 0, x,
                                         l.post_attention_layernorm, eps, self.sync)
             site += 1
-            gu = F.linear(h, w["gu"])
-            torch.matmul(K.swiglu_infer(gu), w["down"].t(), out=self._site(site))
+            if cfg.is_moe:
+                from ..ops import functional as F_
+
+                y, _, _ = F_.moe_mlp(h, l.router, w["gu"], w["down"], cfg.num_experts_per_tok, cfg.norm_topk_prob)
+                self._site(site).copy_(y)
+            else:
+                gu = F.linear(h, w["gu"])
+                torch.matmul(K.swiglu_infer(gu), w["down"].t(), out=self._site(site))
             site += 1
         hN = K.allreduce_add_rmsnorm(self.arena, self.partials_off + (site - 1) * self.site_elems * 2, 0, x, m.norm, eps,
                                      self.sync)
