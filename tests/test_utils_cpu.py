@@ -324,3 +324,35 @@ def test_small_compat_helpers():
     U.shutdown_event_loop_in_daemon(None, None)  # no-op
     assert U.get_comet_experiment_url() is None and U.get_trackio_space_url() is None
     assert callable(U.selective_log_softmax) and callable(U.patch_chunked_lm_head) and callable(U.ensure_master_addr_port)
+
+
+def test_split_and_unsplit_pixel_values_for_the_three_vision_layouts():
+    from trl_b200.trainer.utils import split_pixel_values_by_grid, unsplit_pixel_values_by_grid
+
+    # patches + grids: samples with 1, 0 and 2 images
+    grid = torch.tensor([[1, 2, 2], [1, 2, 4], [1, 4, 2]])
+    pv = torch.arange(20 * 3, dtype=torch.float32).view(20, 3)
+    batch = {"pixel_values": pv, "image_grid_thw": grid, "num_images": [1, 0, 2], "input_ids": torch.zeros(3, 4)}
+    sp = split_pixel_values_by_grid(batch)
+    assert [t.shape[0] for t in sp["pixel_values"]] == [4, 0, 16]
+    assert [t.tolist() for t in sp["image_grid_thw"]] == [[[1, 2, 2]], [], [[1, 2, 4], [1, 4, 2]]]
+    assert sp["input_ids"] is batch["input_ids"]
+    back = unsplit_pixel_values_by_grid(sp)
+    assert torch.equal(back["pixel_values"], pv) and torch.equal(back["image_grid_thw"], grid)
+    with pytest.raises(ValueError):
+        split_pixel_values_by_grid({**batch, "pixel_values": pv[:-1]})
+    # one row per image, positions travel with it
+    b2 = {"pixel_values": torch.randn(3, 5, 7), "image_position_ids": torch.arange(3 * 4).view(3, 4), "num_images": [2, 1]}
+    s2 = split_pixel_values_by_grid(b2)
+    assert [t.shape[0] for t in s2["pixel_values"]] == [2, 1] and s2["image_position_ids"][1].tolist() == [[8, 9, 10, 11]]
+    assert torch.equal(unsplit_pixel_values_by_grid(s2)["image_position_ids"], b2["image_position_ids"])
+    # tiles: split by num_tiles, mask and shapes alongside
+    b3 = {"pixel_values": torch.randn(5, 6), "pixel_attention_mask": torch.ones(5, 6), "spatial_shapes": torch.ones(5, 2),
+          "num_tiles": [3, 2], "num_images": [1, 1]}
+    s3 = split_pixel_values_by_grid(b3)
+    assert [t.shape[0] for t in s3["pixel_values"]] == [3, 2] and [t.shape[0] for t in s3["spatial_shapes"]] == [3, 2]
+    assert unsplit_pixel_values_by_grid(s3)["pixel_attention_mask"].shape == (5, 6)
+    # nothing to split
+    assert split_pixel_values_by_grid({"input_ids": 1}) == {"input_ids": 1}
+    plain = {"pixel_values": torch.zeros(2, 3), "num_images": [1, 1]}
+    assert split_pixel_values_by_grid(plain) is plain

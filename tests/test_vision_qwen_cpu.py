@@ -213,3 +213,48 @@ def test_grpo_trains_qwen2_vl(tmp_path):
     logs = [h for h in tr.state.log_history if "reward" in h]
     assert logs and all(np.isfinite(h["loss"]) for h in logs) and "kl" in logs[-1]
     assert not torch.equal(w0, model.visual.merge2_w)
+
+
+def test_vision_entries_split_merge_and_compare():
+    from trl_b200.models.vision import (merge_vision_entries, same_vision_entry, split_vision_batch,
+                                        vision_entry_numel)
+
+    # fixed-resolution towers: one tensor [n_images, C, S, S] per example
+    pv = torch.arange(3 * 2 * 2 * 2, dtype=torch.float32).view(3, 2, 2, 2)
+    per = split_vision_batch({"pixel_values": pv}, [2, 0, 1])
+    assert [vision_entry_numel(e) for e in per] == [16, 0, 8]
+    kw = merge_vision_entries(per, "cpu")
+    assert set(kw) == {"pixel_values"} and torch.equal(kw["pixel_values"], pv)
+    assert same_vision_entry(per[0], per[0].clone()) and not same_vision_entry(per[0], per[2])
+    assert merge_vision_entries([None, per[1]], "cpu") == {"pixel_values": None}
+    # flat patches + grids: example 0 owns images of 4 and 8 patches, example 1 none, example 2 one of 4
+    grid = torch.tensor([[1, 2, 2], [1, 2, 4], [1, 2, 2]])
+    patches = torch.arange(16 * 3, dtype=torch.float32).view(16, 3)
+    per = split_vision_batch({"pixel_values": patches, "image_grid_thw": grid}, [2, 0, 1])
+    assert per[1] is None and per[0][0].shape == (12, 3) and per[2][0].shape == (4, 3)
+    assert per[0][1].tolist() == [[1, 2, 2], [1, 2, 4]]
+    kw = merge_vision_entries([per[2], None, per[0]], "cpu")   # any order of sequences inside a packed batch
+    assert torch.equal(kw["pixel_values"], torch.cat([patches[12:], patches[:12]]))
+    assert kw["image_grid_thw"].tolist() == [[1, 2, 2], [1, 2, 2], [1, 2, 4]]
+    assert same_vision_entry(per[0], (per[0][0].clone(), per[0][1].clone()))
+    assert not same_vision_entry(per[0], per[2]) and not same_vision_entry(per[0], pv) and not same_vision_entry(None, per[0])
+    assert split_vision_batch({}, [1, 1]) == [None, None]
+
+
+def test_mrope_with_equal_rows_is_plain_rope_and_sections_pick_their_row():
+    from trl_b200.oracle import ops as ref
+
+    torch.manual_seed(0)
+    x = torch.randn(7, 3, 16)
+    pos = torch.arange(7)
+    same = ref.apply_mrope(x, pos[None].expand(3, 7), 10000.0, [2, 3, 3])
+    assert torch.equal(same, ref.apply_rope(x, pos, 10000.0))
+    # only the height row differs: the frequencies of the temporal and width sections do not move
+    pos3 = torch.stack([pos, pos + 5, pos])
+    out = ref.apply_mrope(x, pos3, 10000.0, [2, 3, 3])
+    half = 8
+    keep = [0, 1, 5, 6, 7]        # temporal (2) and width (last 3) frequency slots
+    moved = [2, 3, 4]             # height section
+    for f in keep:
+        assert torch.equal(out[..., f], same[..., f]) and torch.equal(out[..., half + f], same[..., half + f])
+    assert any(not torch.equal(out[..., f], same[..., f]) for f in moved)

@@ -276,26 +276,50 @@ def shuffle_sequence_dict(d: dict[str, Any], generator: torch.Generator | None =
     return {k: p(v) for k, v in d.items()}
 
 
+# keys of a vision batch that travel with ``pixel_values`` and are split / merged with it, per layout
+_VISION_COMPANIONS = ("image_grid_thw", "image_position_ids", "pixel_attention_mask", "spatial_shapes")
+
+
 def split_pixel_values_by_grid(batch: dict) -> dict:
-    """Split flattened ``pixel_values`` into per-sample tensors using ``image_grid_thw`` (utils.py:995-1040)."""
-    if "image_grid_thw" not in batch or "pixel_values" not in batch or "num_images" not in batch:
+    """One ``pixel_values`` entry per sample instead of one flat tensor (``batch["num_images"]`` images per sample), so
+    that samples can be shuffled or re-dealt between ranks (trl/trainer/utils.py:995-1043).  Three layouts:
+
+    * ``image_grid_thw`` (Qwen2-VL family): ``pixel_values`` holds patches, image i owns ``prod(grid[i])`` rows;
+    * ``image_position_ids`` (Gemma family): one ``pixel_values`` row per image;
+    * ``spatial_shapes`` (LFM2-VL family): rows are tiles, ``batch["num_tiles"]`` of them per sample, with
+      ``pixel_attention_mask`` and ``spatial_shapes`` split the same way.
+    """
+    if "pixel_values" not in batch or "num_images" not in batch:
         return batch
-    lens = batch["image_grid_thw"].prod(-1).tolist()
-    pv = list(torch.split(batch["pixel_values"], lens, 0))
-    grids = list(torch.split(batch["image_grid_thw"], 1, 0))
-    out_pv, out_g, i = [], [], 0
-    for n in batch["num_images"]:
-        out_pv.append(torch.cat(pv[i:i + n], 0) if n else batch["pixel_values"].new_zeros((0,) + batch["pixel_values"].shape[1:]))
-        out_g.append(torch.cat(grids[i:i + n], 0) if n else batch["image_grid_thw"].new_zeros((0, 3)))
-        i += n
-    return {**batch, "pixel_values": out_pv, "image_grid_thw": out_g}
+    pv, counts = batch["pixel_values"], [int(n) for n in batch["num_images"]]
+    if "image_grid_thw" in batch:
+        grid = batch["image_grid_thw"]
+        per_image = grid.prod(-1).tolist()
+        if sum(per_image) != pv.shape[0]:
+            raise ValueError(f"image_grid_thw describes {sum(per_image)} patches, pixel_values has {pv.shape[0]} rows")
+        rows, o = [], 0
+        for n in counts:
+            rows.append(sum(per_image[o:o + n]))
+            o += n
+        return {**batch, "pixel_values": list(torch.split(pv, rows, 0)), "image_grid_thw": list(torch.split(grid, counts, 0))}
+    if "image_position_ids" in batch:
+        return {**batch, "pixel_values": list(torch.split(pv, counts, 0)),
+                "image_position_ids": list(torch.split(batch["image_position_ids"], counts, 0))}
+    if "spatial_shapes" in batch:
+        tiles = [int(n) for n in batch["num_tiles"]]
+        return {**batch, "pixel_values": list(torch.split(pv, tiles, 0)),
+                "pixel_attention_mask": list(torch.split(batch["pixel_attention_mask"], tiles, 0)),
+                "spatial_shapes": list(torch.split(batch["spatial_shapes"], tiles, 0))}
+    return batch
 
 
 def unsplit_pixel_values_by_grid(batch: dict) -> dict:
-    pv, g = batch.get("pixel_values"), batch.get("image_grid_thw")
-    if isinstance(pv, list) and isinstance(g, list):
-        return {**batch, "pixel_values": torch.cat(pv, 0), "image_grid_thw": torch.cat(g, 0)}
-    return batch
+    """Inverse of :func:`split_pixel_values_by_grid`: per-sample lists back to flat tensors."""
+    out = dict(batch)
+    for k in ("pixel_values",) + _VISION_COMPANIONS:
+        if isinstance(out.get(k), list):
+            out[k] = torch.cat(out[k], 0)
+    return out
 
 
 def hash_module(module: nn.Module) -> str:
