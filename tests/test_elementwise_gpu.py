@@ -47,6 +47,35 @@ def test_rope_fwd_bwd():
     assert torch.allclose(qkv.grad.float(), qkv2.grad, atol=6e-2, rtol=3e-2)
 
 
+def test_multimodal_rope_fwd_bwd():
+    """Three position rows, frequency sections pick their row (Qwen2-VL); also equal rows = plain RoPE."""
+    from trl_b200.ops import functional as F_
+    from trl_b200.oracle import ops as ref
+
+    torch.manual_seed(0)
+    T, Hq, Hk, D = 70, 4, 2, 128
+    sections = [16, 24, 24]
+    qkv = torch.randn(T, (Hq + 2 * Hk) * D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    pos3 = torch.randint(0, 3000, (3, T), device="cuda")
+
+    def split(t):
+        return t[:, :Hq * D].reshape(T, Hq, D), t[:, Hq * D:(Hq + Hk) * D].reshape(T, Hk, D)
+    q, k = split(qkv)
+    qo, ko = F_.apply_mrope_qk(q, k, pos3, 1e6, sections)
+    (qo.float().sum() * 2 + (ko.float() ** 2).sum()).backward()
+    qkv2 = qkv.detach().float().requires_grad_()
+    q2, k2 = split(qkv2)
+    qr, kr = ref.apply_mrope(q2, pos3, 1e6, sections), ref.apply_mrope(k2, pos3, 1e6, sections)
+    (qr.sum() * 2 + (kr ** 2).sum()).backward()
+    assert torch.allclose(qo.float(), qr, atol=3e-2, rtol=2e-2)
+    assert torch.allclose(ko.float(), kr, atol=3e-2, rtol=2e-2)
+    assert torch.allclose(qkv.grad.float(), qkv2.grad, atol=6e-2, rtol=3e-2)
+    same = pos3[:1].expand(3, T).contiguous()
+    a, b = F_.apply_mrope_qk(q.detach(), k.detach(), same, 1e6, sections)
+    c, d = F_.apply_rope_qk(q.detach(), k.detach(), same[0], 1e6)
+    assert torch.equal(a, c) and torch.equal(b, d)
+
+
 def test_swiglu_fwd_bwd():
     from trl_b200.ops import functional as F_
     from trl_b200.oracle import ops as ref

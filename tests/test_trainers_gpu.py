@@ -116,3 +116,46 @@ def test_grpo_with_adapters_generates_from_a_merged_replica(tmp_path, tiny_token
     assert any(float(s.lora_B.abs().max()) > 0 for s in l_src.lora.values())  # the adapters were trained
     torch.cuda.synchronize()
     K.check_status(torch.device("cuda"))
+
+
+def test_qwen2_vl_sft_and_grpo_on_the_gpu(tmp_path):
+    """Dynamic-resolution tower + multimodal RoPE in bf16 on the GPU: SFT with images of two sizes, then GRPO whose
+    rollouts run on the paged engine with the per-slot rotary lead."""
+    import numpy as np
+
+    from trl_b200 import GRPOConfig, GRPOTrainer, SFTConfig, SFTTrainer
+    from trl_b200.models.configuration import preset
+    from trl_b200.models.vision_processing import DynamicResolutionProcessor
+    from trl_b200.models.vision_qwen import Qwen2VLArch, Qwen2VLModel, QwenVisionArch
+    from trl_b200.rollout.engine import RolloutEngine
+    from trl_b200.testing import make_tiny_tokenizer
+
+    tok = make_tiny_tokenizer()  # its own copy: the processor adds the image token
+    proc = DynamicResolutionProcessor(tok, min_pixels=28 * 28, max_pixels=56 * 56)
+    text = preset("tiny-qwen2", vocab_size=max(1024, len(tok)), **SHAPE)
+    text.extra["mrope_section"] = [16, 24, 24]
+    arch = Qwen2VLArch(text, QwenVisionArch(depth=2, embed_dim=64, hidden_size=SHAPE["hidden_size"], num_heads=2, mlp_ratio=2),
+                       image_token_id=proc.image_token_id)
+    torch.manual_seed(0)
+    model = Qwen2VLModel(arch, dtype=torch.bfloat16, device="cuda")
+    rs = np.random.RandomState(0)
+    imgs = [(rs.rand(28 * (1 + i % 2), 56, 3) * 255).astype("uint8") for i in range(8)]
+    rows = [{"images": [im], "messages": [{"role": "user", "content": "what is this"},
+                                          {"role": "assistant", "content": "a picture " + "ab"[i % 2]}]}
+            for i, im in enumerate(imgs)]
+    before = _snap(model)
+    tr = SFTTrainer(model, SFTConfig(output_dir=str(tmp_path / "sft"), max_length=None, **COMMON), train_dataset=rows,
+                    processing_class=proc)
+    tr.train()
+    _finite_losses(tr)
+    still = _unchanged(model, before)
+    assert not [n for n in still if "visual" in n and n.endswith("_w")], still
+    prompts = [{"image": im, "prompt": [{"role": "user", "content": "describe"}]} for im in imgs]
+    args = GRPOConfig(output_dir=str(tmp_path / "grpo"), num_generations=4, max_completion_length=8, beta=0.04,
+                      temperature=1.0, **COMMON)
+    tr2 = GRPOTrainer(model, lambda completion_ids, **kw: [float(sum(c) % 7) for c in completion_ids], args,
+                      train_dataset=prompts, processing_class=proc)
+    tr2.train()
+    assert isinstance(tr2._rollout, RolloutEngine) and tr2._rollout.rope_delta is not None
+    logs = [h for h in tr2.state.log_history if "reward" in h]
+    assert logs and all(math.isfinite(h["loss"]) for h in logs)

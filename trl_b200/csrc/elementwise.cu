@@ -353,10 +353,11 @@ __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ part, int npa
 // RoPE (rotate-half) on q [T,Hq,D] and k [T,Hk,D] read through a row stride (views of the fused
 // QKV output) and written densely.  sign = +1 forward, -1 backward (inverse rotation).
 // ------------------------------------------------------------------------------------------
+template <bool MULTI>
 __global__ void rope_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                             long long q_row_stride, long long k_row_stride, const int* __restrict__ pos,
                             __nv_bfloat16* __restrict__ qo, __nv_bfloat16* __restrict__ ko, int T, int Hq, int Hk, int D,
-                            float log2_theta, float sign) {
+                            float log2_theta, float sign, const int* __restrict__ row_of_freq) {
   const int half = D >> 1;
   const int pairs_per_tok = (Hq + Hk) * (half >> 1);  // two frequencies per thread
   const long long total = (long long)T * pairs_per_tok;
@@ -366,12 +367,14 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     int r = (int)(idx % pairs_per_tok);
     const int head = r / (half >> 1);
     const int f = (r % (half >> 1)) * 2;
-    const float p = (float)pos[t];
+    // MULTI: pos is [rows, T] and frequency f turns with the position row row_of_freq[f] (multimodal RoPE)
+    const float p0 = MULTI ? (float)pos[(size_t)row_of_freq[f] * T + t] : (float)pos[t];
+    const float p1 = MULTI ? (float)pos[(size_t)row_of_freq[f + 1] * T + t] : p0;
     const float inv0 = exp2f(-log2_theta * (float)(2 * f) / (float)D);
     const float inv1 = exp2f(-log2_theta * (float)(2 * f + 2) / (float)D);
     float s0, c0, s1, c1;
-    sincosf(p * inv0, &s0, &c0);
-    sincosf(p * inv1, &s1, &c1);
+    sincosf(p0 * inv0, &s0, &c0);
+    sincosf(p1 * inv1, &s1, &c1);
     s0 *= sign; s1 *= sign;
     const __nv_bfloat16* src;
     __nv_bfloat16* dst;
@@ -663,9 +666,23 @@ TRLB_API int trlb_rope(const void* q, const void* k, long long q_row_stride, lon
   if (T == 0) return 0;
   if (D % 4 != 0) return -1;
   const long long work = (long long)T * (Hq + Hk) * (D / 4);
-  rope_kernel<<<grid_for(work, 256), 256, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, q_row_stride,
-                                                   k_row_stride, pos, (__nv_bfloat16*)qo, (__nv_bfloat16*)ko, T, Hq, Hk,
-                                                   D, log2f(theta), sign);
+  rope_kernel<false><<<grid_for(work, 256), 256, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, q_row_stride,
+                                                          k_row_stride, pos, (__nv_bfloat16*)qo, (__nv_bfloat16*)ko, T, Hq,
+                                                          Hk, D, log2f(theta), sign, nullptr);
+  return (int)cudaGetLastError();
+}
+
+// Multimodal RoPE: pos3 [rows, T] int32 (temporal / height / width positions), row_of_freq [D / 2] int32 says which
+// row turns each rotary frequency.
+TRLB_API int trlb_rope_multi(const void* q, const void* k, long long q_row_stride, long long k_row_stride, const int* pos3,
+                             const int* row_of_freq, void* qo, void* ko, int T, int Hq, int Hk, int D, float theta,
+                             float sign, cudaStream_t st) {
+  if (T == 0) return 0;
+  if (D % 4 != 0) return -1;
+  const long long work = (long long)T * (Hq + Hk) * (D / 4);
+  rope_kernel<true><<<grid_for(work, 256), 256, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, q_row_stride,
+                                                         k_row_stride, pos3, (__nv_bfloat16*)qo, (__nv_bfloat16*)ko, T, Hq,
+                                                         Hk, D, log2f(theta), sign, row_of_freq);
   return (int)cudaGetLastError();
 }
 

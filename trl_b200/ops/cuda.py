@@ -325,6 +325,48 @@ class RopeFn(torch.autograd.Function):
         return gq, gk, None, None
 
 
+_ROW_OF_FREQ: dict = {}
+
+
+class MRopeFn(torch.autograd.Function):
+    """Multimodal RoPE on q and k in one kernel: ``positions3`` [3, T] and the frequency sections pick, per rotary
+    frequency, which position row turns it; the backward pass is the inverse rotation."""
+
+    @staticmethod
+    def forward(ctx, q, k, positions3, theta, sections):
+        T, Hq, D = q.shape
+        Hk = k.shape[1]
+        assert q.stride(2) == 1 and q.stride(1) == D and k.stride(2) == 1 and k.stride(1) == D
+        if sum(sections) != D // 2:
+            raise ValueError(f"mrope_section {list(sections)} must sum to head_dim / 2 = {D // 2}")
+        key = (q.device, tuple(sections))
+        rof = _ROW_OF_FREQ.get(key)
+        if rof is None:
+            rof = _ROW_OF_FREQ[key] = torch.tensor([i % 3 for i, n in enumerate(sections) for _ in range(n)],
+                                                   dtype=torch.int32, device=q.device)
+        pos = positions3.to(torch.int32).contiguous()
+        qo = torch.empty(T, Hq, D, dtype=q.dtype, device=q.device)
+        ko = torch.empty(T, Hk, D, dtype=k.dtype, device=k.device)
+        _chk(lib().trlb_rope_multi(_p(q), _p(k), c_longlong(q.stride(0)), c_longlong(k.stride(0)), _p(pos), _p(rof), _p(qo),
+                                   _p(ko), c_int(T), c_int(Hq), c_int(Hk), c_int(D), c_float(theta), c_float(1.0), _s()),
+             "rope_multi")
+        ctx.save_for_backward(pos, rof)
+        ctx.theta = theta
+        return qo, ko
+
+    @staticmethod
+    def backward(ctx, dq, dk):
+        pos, rof = ctx.saved_tensors
+        dq, dk = dq.contiguous(), dk.contiguous()
+        T, Hq, D = dq.shape
+        Hk = dk.shape[1]
+        gq, gk = torch.empty_like(dq), torch.empty_like(dk)
+        _chk(lib().trlb_rope_multi(_p(dq), _p(dk), c_longlong(dq.stride(0)), c_longlong(dk.stride(0)), _p(pos), _p(rof),
+                                   _p(gq), _p(gk), c_int(T), c_int(Hq), c_int(Hk), c_int(D), c_float(ctx.theta),
+                                   c_float(-1.0), _s()), "rope_multi_bwd")
+        return gq, gk, None, None, None
+
+
 class SwigluFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, gate_up):

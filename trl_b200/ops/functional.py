@@ -143,8 +143,9 @@ def moe_mlp(hidden, router_w, gate_up_w, down_w, top_k, norm_topk_prob):
 
 
 def apply_mrope_qk(q, k, positions3, theta, sections):
-    """Multimodal rotary embedding of q and k (PyTorch math on every device: vision-language models are a small part
-    of the step and the rotation is elementwise)."""
+    """Multimodal rotary embedding of q and k: one kernel on bf16 CUDA tensors, the PyTorch oracle elsewhere."""
+    if _use_kernel(q) and q.shape[-1] % 4 == 0:
+        return _cuda().MRopeFn.apply(q, k, positions3, theta, tuple(sections))
     return _ref.apply_mrope(q, positions3, theta, sections), _ref.apply_mrope(k, positions3, theta, sections)
 
 

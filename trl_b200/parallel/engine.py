@@ -137,7 +137,25 @@ class TrainEngine:
 
             self.use_multimem = bool(self._arenas["param"].multicast_ptr) and os.environ.get("TRL_B200_MULTIMEM", "1") == "1"
         self._hooks = []
+        # a model that an earlier engine has wrapped (one trainer after another on the same object): that engine's
+        # gradient hooks would fire next to this one's and hand it an already consumed gradient
+        prev = getattr(model, "_trlb_engine_ref", None)
+        prev = prev() if prev is not None else None
+        if prev is not None and prev is not self and hasattr(prev, "release_hooks"):
+            prev.release_hooks()
+        import weakref
+
+        try:
+            model._trlb_engine_ref = weakref.ref(self)
+        except Exception:  # noqa: BLE001  (objects without attribute storage)
+            pass
         self._install_grad_views()
+
+    def release_hooks(self):
+        """Detaches this engine's gradient hooks from the parameters (the buffers stay valid)."""
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
 
     # ---- construction ---------------------------------------------------------
     def _build_buckets(self, bucket_of, grad_dtype):
