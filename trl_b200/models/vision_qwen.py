@@ -188,35 +188,43 @@ class QwenVisionTower(nn.Module):
 def rope_index(input_ids: torch.Tensor, cu_seqlens: torch.Tensor, grid_thw: Optional[torch.Tensor], cfg: Qwen2VLArch):
     """Multimodal rotary positions [3, T] of a packed stream.  Per sequence: text tokens count up with the same value
     in the three rows; the ``t * (h / m) * (w / m)`` placeholder tokens of an image take (frame, row, column) offsets
-    from the position where the image starts; the text after it continues at the largest value used so far + 1."""
-    ids = input_ids.tolist()
-    cu = cu_seqlens.tolist()
-    m = cfg.vision.spatial_merge_size
-    grids = grid_thw.tolist() if grid_thw is not None else []
-    out = torch.zeros(3, len(ids), dtype=torch.long)
-    gi = 0
-    for s in range(len(cu) - 1):
-        lo, hi = cu[s], cu[s + 1]
-        nxt, i = 0, lo
-        while i < hi:
-            if ids[i] == cfg.image_token_id and gi < len(grids):
-                t, h, w = grids[gi]
-                gi += 1
-                gh, gw = h // m, w // m
-                n = t * gh * gw
-                if i + n > hi:
-                    raise ValueError("an image's placeholder tokens run past the end of their sequence")
-                tt = torch.arange(t).repeat_interleave(gh * gw)
-                hh = torch.arange(gh).repeat_interleave(gw).repeat(t)
-                ww = torch.arange(gw).repeat(gh).repeat(t)
-                out[:, i:i + n] = torch.stack([tt, hh, ww]) + nxt
-                nxt += max(t, gh, gw)
-                i += n
-            else:
-                out[:, i] = nxt
-                nxt += 1
-                i += 1
-    return out.to(input_ids.device)
+    from the position where the image starts; the text after it continues at the largest value used so far + 1.
+    Tensor operations only (no loop over tokens): the stream may be a whole packed batch."""
+    dev = input_ids.device
+    T = input_ids.numel()
+    cu = cu_seqlens.to(dev).long()
+    lens = cu[1:] - cu[:-1]
+    seq_of = torch.repeat_interleave(torch.arange(lens.numel(), device=dev), lens, output_size=T)
+    adv = torch.ones(T, dtype=torch.long, device=dev)          # how far every token moves the text position
+    img_pos = None
+    if grid_thw is not None and grid_thw.numel():
+        m = cfg.vision.spatial_merge_size
+        g = grid_thw.to(dev).long()
+        t, gh, gw = g[:, 0], g[:, 1] // m, g[:, 2] // m
+        n = t * gh * gw                                         # placeholder tokens per image
+        total = int(n.sum())
+        slots = (input_ids == cfg.image_token_id).nonzero().flatten()
+        if slots.numel() < total:
+            raise ValueError("an image's placeholder tokens run past the end of their sequence")
+        slots = slots[:total]                                   # placeholders beyond the images count as text
+        first = torch.cumsum(n, 0) - n                          # index into `slots` of every image's first token
+        start, last = slots[first], slots[first + n - 1]
+        if bool(((last - start) != n - 1).any()) or bool((seq_of[start] != seq_of[last]).any()):
+            raise ValueError("an image's placeholder tokens run past the end of their sequence")
+        adv[slots] = 0
+        adv[start] = torch.maximum(t, torch.maximum(gh, gw))
+        img_of = torch.repeat_interleave(torch.arange(n.numel(), device=dev), n, output_size=total)
+        r = torch.arange(total, device=dev) - first[img_of]     # index of the token inside its image
+        hw = (gh * gw)[img_of]
+        img_pos = (slots, img_of, torch.stack([r // hw, (r // gw[img_of]) % gh[img_of], r % gw[img_of]]))
+    before = torch.cumsum(adv, 0) - adv                         # text position if the stream were one sequence
+    pos = before - before[cu[:-1]][seq_of]                      # ... restarted at every sequence
+    out = pos[None].repeat(3, 1)
+    if img_pos is not None:
+        slots, img_of, offs = img_pos
+        base = pos[slots[(torch.cumsum(n, 0) - n)]]             # position at which every image starts
+        out[:, slots] = base[img_of][None] + offs
+    return out
 
 
 class Qwen2VLModel(nn.Module):
