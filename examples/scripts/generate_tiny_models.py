@@ -43,6 +43,18 @@ def main():
         VisionLanguageModel(tiny_vlm_arch("tiny-llama", image_token_index=proc.image_token_id)).save_pretrained(path)
         proc.save_pretrained(path)
         print("wrote", path)
+        from trl_b200.models.vision_processing import DynamicResolutionProcessor
+        from trl_b200.models.vision_qwen import Qwen2VLModel, tiny_qwen2_vl_arch
+
+        tok = make_tiny_tokenizer()
+        proc = DynamicResolutionProcessor(tok, min_pixels=28 * 28, max_pixels=112 * 112)
+        arch = tiny_qwen2_vl_arch()
+        arch.image_token_id = proc.image_token_id
+        arch.text.vocab_size = max(arch.text.vocab_size, len(tok))
+        path = os.path.join(a.out, "tiny-qwen2-vl")
+        Qwen2VLModel(arch).save_pretrained(path)
+        proc.save_pretrained(path)
+        print("wrote", path)
 
 
 if __name__ == "__main__":

@@ -11,6 +11,7 @@ _import_structure = {
                    "prepare_multimodal_messages_vllm", "unpair_preference_dataset", "truncate_dataset"],
     "models.utils": ["create_reference_model", "unwrap_model_for_generation"],
     "models.decoder": ["CausalLM"],
+    "models.hf_io": ["load_model"],
     "models.vision": ["VisionLanguageModel", "VlmArch", "VisionArch"],
     "models.vision_processing": ["VisionProcessor", "DynamicResolutionProcessor"],
     "models.vision_qwen": ["Qwen2VLModel", "Qwen2VLArch", "QwenVisionArch"],

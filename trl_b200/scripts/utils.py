@@ -124,8 +124,9 @@ def load_script_dataset(script_args: ScriptArguments, dataset_args: DatasetMixtu
 # dataclass -> argparse
 # ---------------------------------------------------------------------------------------------------
 def load_processing_class(path, **tokenizer_kwargs):
-    """Tokenizer for a text checkpoint directory; for a vision-language checkpoint (``model_type: llava``) a processor:
-    the framework's ``VisionProcessor`` when it was saved next to the model, else ``transformers.AutoProcessor``.
+    """Tokenizer for a text checkpoint directory; for a vision-language checkpoint (``model_type: llava`` or
+    ``qwen2_vl``) a processor: the framework's ``VisionProcessor`` / ``DynamicResolutionProcessor`` when one was saved
+    next to the model, else ``transformers.AutoProcessor``.
     Presets (no files on disk) get the offline ChatML fixture tokenizer."""
     import json
     import os
@@ -141,15 +142,16 @@ def load_processing_class(path, **tokenizer_kwargs):
     is_vlm = False
     if os.path.exists(cfg):
         with open(cfg) as f:
-            is_vlm = json.load(f).get("model_type") == "llava"
+            is_vlm = json.load(f).get("model_type") in ("llava", "qwen2_vl")
     if is_vlm:
         pre = os.path.join(path, "preprocessor_config.json")
         if os.path.exists(pre):
             with open(pre) as f:
-                if json.load(f).get("processor_class") == "VisionProcessor":
-                    from ..models.vision_processing import VisionProcessor
+                kind = json.load(f).get("processor_class")
+            if kind in ("VisionProcessor", "DynamicResolutionProcessor"):
+                from ..models import vision_processing
 
-                    return VisionProcessor.from_pretrained(path)
+                return getattr(vision_processing, kind).from_pretrained(path)
         from transformers import AutoProcessor
 
         return AutoProcessor.from_pretrained(path)
