@@ -31,11 +31,14 @@ def main():
     model = make_tiny_model("tiny-qwen2", seed=0)
     rows = synthetic_token_batches(1024, 4 * steps, 128, seed=3)
     # "sp2": Ulysses sequence parallelism over both ranks; "cp2": context parallel (gathered K/V); plain DP engine
+    optim = "adamw_torch_fused"
+    if mode.endswith("+sgd"):  # another update rule on the engine's master slices (sharded under zero2)
+        mode, optim = mode[:-4], "sgd"
     sp = 2 if mode in ("sp2", "cp2") else 1
     pc = {"sp_size" if mode == "sp2" else "cp_size": sp} if sp > 1 else None
     mode = "ddp" if sp > 1 else mode
     args = SFTConfig(output_dir=out + "_o", per_device_train_batch_size=4 // (world // sp), max_steps=steps, logging_steps=1,
-                     learning_rate=1e-4, use_cpu=True, save_strategy="no", padding_free=True, shard_mode=mode,
+                     learning_rate=1e-4 if optim != "sgd" else 0.05, optim=optim, optim_args="momentum=0.9", use_cpu=True, save_strategy="no", padding_free=True, shard_mode=mode,
                      parallelism_config=pc,
                      lr_scheduler_type="constant", train_sampling_strategy="sequential", completion_only_loss=True,
                      dataset_kwargs={"skip_prepare_dataset": True}, gradient_checkpointing=mode == "full_shard_stream",

@@ -40,6 +40,18 @@ def test_sft_world1_vs_world2(tmp_path, tmp_path_factory, mode, port):
     assert ref[-1]["loss"] < ref[0]["loss"] + 0.05
 
 
+def test_custom_optimizer_sharded_over_two_ranks_matches_one_rank(tmp_path):
+    """SGD with momentum through `optim`: zero2 over two ranks (every rank updates its half of the master copy, the
+    momentum buffers are sharded with it) follows the single-process trajectory."""
+    ref = _run(1, "ddp+sgd", str(tmp_path / "w1.json"))
+    two = _run(2, "zero2+sgd", str(tmp_path / "w2.json"), port=29616)
+    assert len(ref) == len(two) == 4
+    for a, b in zip(ref, two):
+        assert abs(a["loss"] - b["loss"]) < 2e-4, (ref, two)
+        assert abs(a["grad_norm"] - b["grad_norm"]) < 1e-3 * max(1.0, a["grad_norm"]), (ref, two)
+    assert ref[-1]["loss"] < ref[0]["loss"] + 0.05 and ref[-1]["loss"] != ref[0]["loss"]
+
+
 def _run_stream(world, mode, variant, out, port, load=True):
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
     worker = os.path.join(HERE, "dist_worker_stream.py")

@@ -16,7 +16,8 @@ def _run(args, tmp_path, timeout=600):
     return r.stdout
 
 
-EXAMPLES = ["kto", "reward_modeling", "rloo", "sft_lora", "gkd", "dpo_vlm", "grpo_vlm", "cpo_simpo", "orpo", "prm"]
+EXAMPLES = ["kto", "reward_modeling", "rloo", "sft_lora", "gkd", "dpo_vlm", "grpo_vlm", "cpo_simpo", "orpo", "prm", "ppo", "bco",
+            "xpo_nash_md", "gold_distillation", "sft_expert_parallel", "online_dpo"]
 
 _RUNNER = """
 import runpy, sys, os
@@ -42,6 +43,12 @@ def test_examples_smoke(tmp_path):
 def test_sft_vlm_example_smoke(tmp_path):
     out = _run(["sft_vlm.py", "--steps", "2", "--out", str(tmp_path / "v")], tmp_path)
     assert "train_runtime" in out and os.path.exists(tmp_path / "v" / "preprocessor_config.json")
+    out = _run(["sft_vlm.py", "--steps", "2", "--family", "qwen2_vl", "--out", str(tmp_path / "q")], tmp_path)
+    assert "train_runtime" in out
+    import json
+
+    assert json.load(open(tmp_path / "q" / "config.json"))["model_type"] == "qwen2_vl"
+    assert json.load(open(tmp_path / "q" / "preprocessor_config.json"))["processor_class"] == "DynamicResolutionProcessor"
 
 
 def test_generate_tiny_models_are_loadable(tmp_path):

@@ -513,3 +513,75 @@ def test_grpo_trains_from_a_streaming_dataset_with_functools_partial_reward(tmp_
     assert tr.state.global_step == 2 and seen
     first = seen[0]
     assert len(first) % 4 == 0 and all(len(set(first[i:i + 4])) == 1 for i in range(0, len(first), 4))
+
+
+def test_other_optimizers_through_optim_and_optimizer_cls(tmp_path, tiny_tokenizer):
+    """`optim="sgd"` and `optimizer_cls_and_kwargs` put the caller's update rule on the engine's fp32 master slices:
+    one SGD step equals p - lr * clipped gradient, decay-exempt parameters get no weight decay, and the optimizer state
+    survives a checkpoint."""
+    from trl_b200 import SFTConfig, SFTTrainer
+
+    rows = make_dataset("standard_language_modeling", 16)
+    one_batch = make_dataset("standard_language_modeling", 4)  # whatever the order, the step sees these four rows
+    base = dict(COMMON, max_steps=1, max_grad_norm=0.0, lr_scheduler_type="constant", learning_rate=0.5, weight_decay=0.0)
+    model = make_tiny_model(seed=0)
+    before = _snap(model)
+    tr = SFTTrainer(model, SFTConfig(output_dir=str(tmp_path / "sgd"), optim="sgd", **base), train_dataset=one_batch,
+                    processing_class=tiny_tokenizer)
+    tr.train()
+    assert isinstance(tr.engine.custom_opt, torch.optim.SGD)
+    # the same gradient through autograd on a copy of the model and the same batch
+    ref = make_tiny_model(seed=0)
+    tr2 = SFTTrainer(ref, SFTConfig(output_dir=str(tmp_path / "ref"), **dict(base, max_steps=1, learning_rate=0.0)),
+                     train_dataset=one_batch, processing_class=tiny_tokenizer)
+    batch = next(iter(tr2.get_train_dataloader()))
+    loss = tr2.compute_loss(ref, tr2._prepare_inputs(batch))
+    loss.backward()
+    g = {n: p.grad for n, p in ref.named_parameters()}  # no engine yet: plain autograd gradients
+    # the loop divides the summed loss by the number of labelled tokens of the batch (first tokens included, as
+    # transformers counts num_items_in_batch), compute_loss alone by the number of targets: one common factor
+    d0, g0 = (before["lm_head"] - dict(model.named_parameters())["lm_head"]) / 0.5, g["lm_head"]
+    c = float((d0 * g0).sum() / (g0 * g0).sum())
+    assert 0.85 < c <= 1.0 + 1e-6
+    for n, p in model.named_parameters():
+        assert torch.allclose(p, before[n] - 0.5 * c * g[n], atol=1e-5), n
+
+    # a class of the caller's, with weight decay: norm weights and biases are exempt
+    class SignSGD(torch.optim.Optimizer):
+        def __init__(self, params, lr=1e-3, weight_decay=0.0):
+            super().__init__(params, dict(lr=lr, weight_decay=weight_decay))
+
+        @torch.no_grad()
+        def step(self):
+            for grp in self.param_groups:
+                for p in grp["params"]:
+                    if p.grad is not None:
+                        p.mul_(1 - grp["lr"] * grp["weight_decay"]).add_(p.grad.sign(), alpha=-grp["lr"])
+                        self.state[p]["steps"] = self.state[p].get("steps", 0) + 1
+
+    model = make_tiny_model(seed=0)
+    before = _snap(model)
+    cfg = SFTConfig(output_dir=str(tmp_path / "sign"), save_steps=2,
+                    **dict(base, max_steps=2, learning_rate=0.01, weight_decay=0.5, save_strategy="steps"))
+    tr = SFTTrainer(model, cfg, train_dataset=rows, processing_class=tiny_tokenizer, optimizer_cls_and_kwargs=(SignSGD, {}))
+    tr.train()
+    groups = tr.engine.custom_opt.param_groups
+    assert groups[0]["weight_decay"] == 0.5 and groups[1]["weight_decay"] == 0.0 and groups[1]["params"]
+    norm_name = next(n for n, _ in model.named_parameters() if "layernorm" in n)
+    moved = (dict(model.named_parameters())[norm_name] - before[norm_name]).abs()
+    assert float(moved.max()) <= 2 * 0.01 + 1e-6            # two sign steps, no decay on a norm weight (value 1.0)
+    w_name = next(n for n, p in model.named_parameters() if p.ndim == 2 and "embed" not in n)
+    assert float((dict(model.named_parameters())[w_name] - before[w_name]).abs().max()) > 0
+    # resume: the custom state comes back
+    model2 = make_tiny_model(seed=0)
+    cfg2 = SFTConfig(output_dir=str(tmp_path / "sign"), **dict(base, max_steps=3, learning_rate=0.01, weight_decay=0.5))
+    tr3 = SFTTrainer(model2, cfg2, train_dataset=rows, processing_class=tiny_tokenizer, optimizer_cls_and_kwargs=(SignSGD, {}))
+    tr3.train(resume_from_checkpoint=True)
+    assert tr3.state.global_step == 3
+    assert max(st["steps"] for st in tr3.engine.custom_opt.state.values()) == 3
+    with pytest.raises(NotImplementedError):
+        SFTTrainer(make_tiny_model(), SFTConfig(output_dir=str(tmp_path / "x"), **COMMON), train_dataset=rows,
+                   processing_class=tiny_tokenizer, optimizers=(torch.optim.SGD([torch.zeros(1, requires_grad=True)], lr=0.1), None))
+    with pytest.raises(ValueError):
+        SFTTrainer(make_tiny_model(), SFTConfig(output_dir=str(tmp_path / "y"), optim="lion_8bit", **COMMON),
+                   train_dataset=rows, processing_class=tiny_tokenizer).train()

@@ -194,6 +194,12 @@ class Trainer:
         self.engine: TrainEngine | None = None
         self.lr_scheduler: LRScheduler | None = None
         self.optimizer = None
+        if optimizers is not None and (optimizers[0] is not None or optimizers[1] is not None):
+            # parameters live in the engine's flat buffers (bf16 compute copy + fp32 master slices), which do not exist
+            # yet when a caller builds an optimizer over model.parameters()
+            raise NotImplementedError("a ready-made (optimizer, scheduler) pair is not supported: pass "
+                                      "optimizer_cls_and_kwargs=(cls, kwargs) or set args.optim / args.lr_scheduler_type")
+        self._optimizer_cls_and_kwargs = optimizer_cls_and_kwargs
         self._metrics = {"train": defaultdict(list), "eval": defaultdict(list)}
         self._watchdog_dir = os.environ.get("TRL_B200_WATCHDOG_DIR")
         self._train_batch_size = self.args.per_device_train_batch_size
@@ -348,9 +354,36 @@ class Trainer:
                                                                        **(a.lr_scheduler_kwargs or {})))
         self.callback_handler.optimizer, self.callback_handler.lr_scheduler = self.engine, self.lr_scheduler
 
+    def _optimizer_factory(self):
+        """None for the built-in AdamW (every ``adamw_*`` name of ``optim``); else a function building the optimizer
+        from parameter groups: ``optimizer_cls_and_kwargs`` (trainer argument, as in transformers), or ``optim`` in
+        ``sgd`` / ``adagrad`` / ``rmsprop`` / ``adafactor`` with ``optim_args`` ("key=value,..." or a dict)."""
+        a = self.args
+        if self._optimizer_cls_and_kwargs is not None:
+            cls, kw = self._optimizer_cls_and_kwargs
+            return lambda groups: cls(groups, **{"lr": a.learning_rate, **(kw or {})})
+        name = (a.optim or "adamw_torch_fused").lower()
+        if name.startswith("adamw"):
+            return None
+        extra = a.optim_args if isinstance(getattr(a, "optim_args", None), dict) else dict(
+            kv.split("=") for kv in (getattr(a, "optim_args", None) or "").replace(" ", "").split(",") if kv)
+        extra = {k: (float(v) if isinstance(v, str) else v) for k, v in extra.items()}
+        table = {"sgd": torch.optim.SGD, "adagrad": torch.optim.Adagrad, "rmsprop": torch.optim.RMSprop}
+        if name in table:
+            return lambda groups: table[name](groups, lr=a.learning_rate, **extra)
+        if name == "adafactor":
+            from transformers.optimization import Adafactor
+
+            return lambda groups: Adafactor(groups, lr=a.learning_rate, scale_parameter=False, relative_step=False, **extra)
+        raise ValueError(f"optim={a.optim!r} is not available; use an adamw_* name, sgd, adagrad, rmsprop, adafactor, or "
+                         "pass optimizer_cls_and_kwargs=(cls, kwargs)")
+
     def _create_engine(self) -> TrainEngine:
         a = self.args
         mode = a.shard_mode
+        factory = self._optimizer_factory()
+        if factory is not None and mode in ("full_shard", "full_shard_stream") and D.world_size() > 1:
+            raise NotImplementedError("a custom optimizer runs with shard_mode ddp, zero1 or zero2")
         if getattr(a, "ep_size", 1) > 1:
             if a.ep_size != D.world_size():
                 raise ValueError(f"ep_size={a.ep_size} must equal the number of processes ({D.world_size()})")
@@ -381,7 +414,7 @@ class Trainer:
             return StreamShardEngine(self.model, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
                                      weight_decay=a.weight_decay, device=a.device, init_seed=a.seed, grad_dtype=gd)
         return TrainEngine(self.model, mode=mode, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
-                           weight_decay=a.weight_decay)
+                           weight_decay=a.weight_decay, optimizer_factory=factory)
 
     def _get_learning_rate(self) -> float:
         return self.lr_scheduler.get_last_lr()[0]

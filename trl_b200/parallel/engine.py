@@ -102,8 +102,14 @@ def default_bucket_of(name: str) -> str:
 class TrainEngine:
     def __init__(self, model: nn.Module, *, mode: str = "ddp", betas=(0.9, 0.999), eps=1e-8,
                  weight_decay: float = 0.0, grad_dtype: torch.dtype | None = None, bucket_of=default_bucket_of,
-                 use_symm_kernels: bool | None = None, group=None):
+                 use_symm_kernels: bool | None = None, group=None, optimizer_factory=None):
+        """``optimizer_factory(param_groups) -> torch.optim.Optimizer``: another update rule than the built-in AdamW.
+        It is given two groups of fp32 tensors (decayed / exempt from decay: slices of this rank's master copy) and
+        runs on the backend path (no fused comm kernels); the engine still does reduction, clipping, the bf16 refresh
+        and the gathers."""
         self.model = model
+        self.optimizer_factory = optimizer_factory
+        self.custom_opt = None
         self.world, self.rank = D.world_size(), D.rank()
         self.group = group
         self.mode = "ddp" if (mode in ("auto", None) or self.world == 1 and mode != "full_shard") else mode
@@ -120,6 +126,8 @@ class TrainEngine:
 
             use_symm_kernels = (self.sharded and on_gpu and first.dtype == torch.bfloat16 and symmetric_available()
                                 and os.environ.get("TRL_B200_NCCL_OPTIMIZER", "0") != "1")
+        if optimizer_factory is not None:
+            use_symm_kernels = False
         self.use_symm = bool(use_symm_kernels)
         self.use_multimem = False
         self._arenas = {}
@@ -306,6 +314,9 @@ class TrainEngine:
         scale = 1.0
         if max_grad_norm is not None and max_grad_norm > 0:
             scale = torch.clamp(max_grad_norm / (norm + 1e-6), max=1.0)
+        if self.optimizer_factory is not None:
+            self._custom_step(reduced, lr, scale)
+            return norm
         b1, b2 = self.betas
         for b, g in zip(self.buckets, reduced):
             shadow = None if b.flat_param.dtype == torch.float32 else b.flat_param[b.lo:b.hi]
@@ -318,6 +329,37 @@ class TrainEngine:
             if self.sharded and not b.local:
                 td.all_gather_into_tensor(b.flat_param, b.flat_param[b.lo:b.hi].clone(), group=self.group)
         return norm
+
+    # ---- an update rule of the caller's ----------------------------------------------------------------------------
+    def _custom_params(self):
+        """Leaf tensors over this rank's master slices, one per (parameter, slice) piece, split by decay exemption."""
+        decay, exempt, self._custom_views = [], [], []
+        for b in self.buckets:
+            cuts = sorted({b.lo, b.hi, *[x for r in b.no_decay_ranges for x in r if b.lo < x < b.hi]})
+            for lo, hi in zip(cuts[:-1], cuts[1:]):
+                is_exempt = any(r0 <= lo and hi <= r1 for r0, r1 in b.no_decay_ranges)
+                t = torch.nn.Parameter(b.master[lo - b.lo:hi - b.lo], requires_grad=False)
+                (exempt if is_exempt else decay).append(t)
+                self._custom_views.append((b, lo - b.lo, hi - b.lo, t))
+        return [{"params": decay, "weight_decay": self.weight_decay}, {"params": exempt, "weight_decay": 0.0}]
+
+    @torch.no_grad()
+    def _custom_step(self, reduced, lr, scale):
+        if self.custom_opt is None:
+            self.custom_opt = self.optimizer_factory(self._custom_params())
+        for g in self.custom_opt.param_groups:
+            g["lr"] = lr
+        by_bucket = {id(b): g for b, g in zip(self.buckets, reduced)}
+        for b, lo, hi, t in self._custom_views:
+            t.grad = by_bucket[id(b)][lo:hi] * scale
+        self.custom_opt.step()
+        for _, _, _, t in self._custom_views:
+            t.grad = None
+        for b in self.buckets:
+            if b.master.data_ptr() != b.flat_param[b.lo:b.hi].data_ptr():
+                b.flat_param[b.lo:b.hi].copy_(b.master)
+            if self.sharded and not b.local:
+                td.all_gather_into_tensor(b.flat_param, b.flat_param[b.lo:b.hi].clone(), group=self.group)
 
     def align_ranks(self):
         """Stream-ordered meeting of the ranks through the backend (one element).  The cross-rank waits inside the comm
@@ -422,6 +464,10 @@ class TrainEngine:
 
     # ---- (de)serialisation of optimizer state -------------------------------------
     def optimizer_state_dict(self) -> dict:
+        if self.custom_opt is not None:  # the caller's rule: its own state, keyed by the order of the master pieces
+            return {"step": self.step_count, "mode": self.mode, "world": self.world, "rank": self.rank,
+                    "custom": self.custom_opt.state_dict(),
+                    "masters": {b.name + "|" + str(b.flat_param.dtype): b.master.detach().cpu().clone() for b in self.buckets}}
         return {
             "step": self.step_count, "mode": self.mode, "world": self.world, "rank": self.rank,
             "buckets": {b.name + "|" + str(b.flat_param.dtype): {
@@ -432,6 +478,15 @@ class TrainEngine:
 
     def load_optimizer_state_dict(self, sd: dict):
         self.step_count = sd["step"]
+        if "custom" in sd:
+            if self.optimizer_factory is None:
+                raise ValueError("the checkpoint holds the state of a custom optimizer; pass the same optimizer again")
+            for b in self.buckets:
+                b.master.copy_(sd["masters"][b.name + "|" + str(b.flat_param.dtype)])
+            if self.custom_opt is None:
+                self.custom_opt = self.optimizer_factory(self._custom_params())
+            self.custom_opt.load_state_dict(sd["custom"])
+            return
         for b in self.buckets:
             s = sd["buckets"][b.name + "|" + str(b.flat_param.dtype)]
             if (s["lo"], s["hi"]) != (b.lo, b.hi):

@@ -185,7 +185,7 @@ class DPOTrainer(Trainer):
                     eval_dataset = {k: self._prepare_dataset(v, tok, args, k) for k, v in eval_dataset.items()}
                 else:
                     eval_dataset = self._prepare_dataset(eval_dataset, tok, args, "eval")
-        super().__init__(model=model, args=args, data_collator=data_collator, train_dataset=train_dataset,
+        super().__init__(optimizers=optimizers, model=model, args=args, data_collator=data_collator, train_dataset=train_dataset,
                          eval_dataset=eval_dataset, processing_class=processing_class if self._is_vlm else tok,
                          compute_metrics=compute_metrics, callbacks=callbacks)
         self.model_accepts_loss_kwargs = False  # loss is divided by the accumulation steps by the loop

@@ -144,7 +144,7 @@ class KTOTrainer(Trainer):
                 train_dataset = self._prepare_dataset(train_dataset, tok, args, args.per_device_train_batch_size, True)
             if eval_dataset is not None:
                 eval_dataset = self._prepare_dataset(eval_dataset, tok, args, args.per_device_eval_batch_size, False)
-        super().__init__(model=model, args=args, data_collator=data_collator, train_dataset=train_dataset,
+        super().__init__(optimizers=optimizers, model=model, args=args, data_collator=data_collator, train_dataset=train_dataset,
                          eval_dataset=eval_dataset, processing_class=tok, callbacks=callbacks,
                          compute_metrics=compute_metrics)
         self.model_accepts_loss_kwargs = False

@@ -117,7 +117,7 @@ class OnlineTrainer(Trainer):
         self._total_train_tokens = 0
         if args.disable_dropout:
             disable_dropout_in_model(model)
-        super().__init__(model=model, args=args, data_collator=_identity, train_dataset=train_dataset,
+        super().__init__(optimizers=optimizers, model=model, args=args, data_collator=_identity, train_dataset=train_dataset,
                          eval_dataset=eval_dataset, processing_class=tok, callbacks=callbacks)
         self.model_accepts_loss_kwargs = False
         self.compute_loss_func = "non-None: the trainer divides by the accumulation steps itself"

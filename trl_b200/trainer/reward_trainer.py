@@ -106,7 +106,7 @@ class RewardTrainer(Trainer):
                     eval_dataset = {k: self._prepare_dataset(v, tok, args) for k, v in eval_dataset.items()}
                 else:
                     eval_dataset = self._prepare_dataset(eval_dataset, tok, args)
-        super().__init__(model=model, args=args, data_collator=data_collator, train_dataset=train_dataset,
+        super().__init__(optimizers=optimizers, model=model, args=args, data_collator=data_collator, train_dataset=train_dataset,
                          eval_dataset=eval_dataset, processing_class=tok, compute_metrics=compute_metrics,
                          callbacks=callbacks)
         self.model_accepts_loss_kwargs = False

@@ -262,7 +262,7 @@ class SFTTrainer(Trainer):
                         eval_dataset = self._prepare_dataset(eval_dataset, tok, args, ep, formatting_func, "eval")
         self._total_train_tokens = 0
         self.aux_loss_enabled = getattr(getattr(model, "config", None), "is_moe", False)
-        super().__init__(model=model, args=args, data_collator=data_collator, train_dataset=train_dataset,
+        super().__init__(optimizers=optimizers, optimizer_cls_and_kwargs=optimizer_cls_and_kwargs, model=model, args=args, data_collator=data_collator, train_dataset=train_dataset,
                          eval_dataset=eval_dataset, processing_class=processing_class if self._is_vlm else tok,
                          compute_loss_func=compute_loss_func,
                          compute_metrics=compute_metrics, callbacks=callbacks,
