@@ -102,6 +102,29 @@ def test_engine_sampling_with_shared_prefix_and_continuous_batching(block_size):
     assert len({tuple(o.token_ids) for o in outs[:4]}) > 1  # samples of one prompt differ
 
 
+def test_a_new_seed_changes_the_samples_but_not_the_captured_graph():
+    """The seed reaches the sampler through the device-side step counter: same seed, same completions; another seed,
+    other completions, with the decode graph of the first call replayed."""
+    from trl_b200.rollout.engine import RolloutEngine
+    from trl_b200.rollout.sampling import SamplingParams
+    from trl_b200.testing import make_tiny_model
+
+    model = make_tiny_model("tiny-qwen2", dtype=torch.bfloat16, device="cuda", hidden_size=256, num_attention_heads=2,
+                            num_key_value_heads=1, head_dim=128, intermediate_size=512)
+    prompts = [list(range(10, 10 + n)) for n in (7, 16)]
+    eng = RolloutEngine(model, max_num_seqs=4, max_model_len=64, poll_every=4)
+
+    def run(seed):
+        sp = SamplingParams(n=2, max_tokens=12, temperature=1.0, eos_token_id=2, seed=seed)
+        return [tuple(o.token_ids) for o in eng.generate(prompts, sp)]
+    a = run(5)
+    graph = eng._graph
+    assert graph is not None
+    b, c = run(6), run(5)
+    assert eng._graph is graph          # no new capture for a new seed
+    assert a == c and a != b
+
+
 @pytest.mark.parametrize("B", [64, 16])  # 2 and 8 CTAs per row
 def test_split_sampler_matches_distribution_and_logprob(B):
     from trl_b200.ops import cuda as K

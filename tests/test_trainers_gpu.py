@@ -159,3 +159,20 @@ def test_qwen2_vl_sft_and_grpo_on_the_gpu(tmp_path):
     assert isinstance(tr2._rollout, RolloutEngine) and tr2._rollout.rope_delta is not None
     logs = [h for h in tr2.state.log_history if "reward" in h]
     assert logs and all(math.isfinite(h["loss"]) for h in logs)
+
+
+def test_sft_with_another_optimizer_on_the_gpu(tmp_path, tiny_tokenizer):
+    """`optim="sgd"` on a bf16 model: the update runs on the fp32 master slices and the bf16 copy follows it."""
+    from trl_b200 import SFTConfig, SFTTrainer
+    from trl_b200.testing import make_dataset
+
+    model = _model()
+    before = _snap(model)
+    args = SFTConfig(output_dir=str(tmp_path), optim="sgd", optim_args="momentum=0.9", **dict(COMMON, learning_rate=0.5))
+    tr = SFTTrainer(model, args, train_dataset=make_dataset("standard_language_modeling", 16), processing_class=tiny_tokenizer)
+    tr.train()
+    _finite_losses(tr)
+    assert isinstance(tr.engine.custom_opt, torch.optim.SGD) and not _unchanged(model, before)
+    b = tr.engine.buckets[0]
+    assert b.master.dtype == torch.float32 and b.flat_param.dtype == torch.bfloat16
+    assert torch.equal(b.flat_param[b.lo:b.hi], b.master.to(torch.bfloat16))

@@ -42,6 +42,9 @@ class Completion:
     finish_reason: str = "length"
 
 
+_KERNEL_SEED = 0x5EED1234
+
+
 class EagerGenerator:
     """Reference generator: recomputes the full forward every step (fine for tiny CPU models)."""
 
@@ -360,7 +363,9 @@ class RolloutEngine:
             inv_t = 1.0
         else:
             inv_t = 1.0 / max(sp.temperature, 1e-6)
-        K.sample_tokens(z, inv_t, sp.min_p, sp.eos_token_id, sp.eos_prob_floor, sp.seed, self.step_counter,
+        # the seed argument is a constant (it is baked into the captured graph); the call's seed enters through the
+        # start value of the device-side step counter, so a new seed needs no new capture
+        K.sample_tokens(z, inv_t, sp.min_p, sp.eos_token_id, sp.eos_prob_floor, _KERNEL_SEED, self.step_counter,
                         sp.greedy or sp.temperature == 0, tok, logp)
 
     # ---- prefill -------------------------------------------------------------------------------------
@@ -423,7 +428,9 @@ class RolloutEngine:
         bt_np = self.block_table_host.numpy()
         timing = os.environ.get("TRL_B200_ROLLOUT_TIMING", "0") == "1"  # wall-clock sections in self.stats (adds syncs)
         graph_key = (sp.temperature, sp.top_p, sp.top_k, sp.min_p, sp.repetition_penalty, sp.eos_token_id,
-                     sp.eos_prob_floor, sp.seed, sp.greedy, max_total, max_new)
+                     sp.eos_prob_floor, sp.greedy, max_total, max_new)
+        # random stream of this call: the sampler hashes (step counter, row); the counter starts at a mix of the seed
+        self.step_counter.fill_((int(sp.seed) * 0x9E3779B1 + 0x7F4A7C15) & 0x3FFFFFFF)
         # every request retires after at most max_new decode steps; a generous bound on the number of
         # polls turns a scheduling or kernel fault into an error instead of an endless host loop
         max_polls = (n_req // max(1, self.max_seqs) + 2) * (max_new // self.poll_every + 2) + 8
