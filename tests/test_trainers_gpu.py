@@ -172,7 +172,9 @@ def test_sft_with_another_optimizer_on_the_gpu(tmp_path, tiny_tokenizer):
     tr = SFTTrainer(model, args, train_dataset=make_dataset("standard_language_modeling", 16), processing_class=tiny_tokenizer)
     tr.train()
     _finite_losses(tr)
-    assert isinstance(tr.engine.custom_opt, torch.optim.SGD) and not _unchanged(model, before)
+    assert isinstance(tr.engine.custom_opt, torch.optim.SGD)
+    # norm weights sit at 1.0, where one bf16 step is 2^-7: their fp32 master copies move, the bf16 values may not
+    assert all("norm" in n for n in _unchanged(model, before)), _unchanged(model, before)
     b = tr.engine.buckets[0]
     assert b.master.dtype == torch.float32 and b.flat_param.dtype == torch.bfloat16
     assert torch.equal(b.flat_param[b.lo:b.hi], b.master.to(torch.bfloat16))
