@@ -585,3 +585,54 @@ def test_other_optimizers_through_optim_and_optimizer_cls(tmp_path, tiny_tokeniz
     with pytest.raises(ValueError):
         SFTTrainer(make_tiny_model(), SFTConfig(output_dir=str(tmp_path / "y"), optim="lion_8bit", **COMMON),
                    train_dataset=rows, processing_class=tiny_tokenizer).train()
+
+
+def test_sft_loss_matches_cross_entropy_and_its_corner_cases(tmp_path, tiny_tokenizer):
+    """The fused lm_head loss of the SFT trainer against ``F.cross_entropy`` on explicit logits: ignore_index,
+    ``num_items_in_batch`` as an int and as a tensor, a batch with no target at all (zero loss, connected graph),
+    and ``shift_labels`` taking precedence over ``labels``."""
+    import torch.nn.functional as F
+
+    from trl_b200 import SFTConfig, SFTTrainer
+
+    model = make_tiny_model(seed=0)
+    tr = SFTTrainer(model, SFTConfig(output_dir=str(tmp_path), **COMMON), train_dataset=make_dataset("standard_language_modeling", 4),
+                    processing_class=tiny_tokenizer)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(5, 1000, (3, 9), generator=g)
+    labels = ids.clone()
+    labels[0, :4] = -100      # a masked prompt
+    labels[2, 5:] = -100      # a masked tail
+    batch = {"input_ids": ids, "attention_mask": torch.ones_like(ids), "labels": labels}
+
+    def reference(lab_shifted, denom=None):
+        logits = model(input_ids=ids).logits.float()
+        flat = F.cross_entropy(logits.reshape(-1, logits.shape[-1]), lab_shifted.reshape(-1), ignore_index=-100, reduction="sum")
+        n = (lab_shifted != -100).sum()
+        return flat / (denom if denom is not None else n)
+    shifted = torch.full_like(labels, -100)
+    shifted[:, :-1] = labels[:, 1:]
+    loss = tr.compute_loss(model, dict(batch))
+    assert torch.allclose(loss, reference(shifted), atol=1e-5)
+    # gradients agree too
+    model.zero_grad()
+    loss.backward()
+    got = {n: p.grad.clone() for n, p in model.named_parameters()}
+    model.zero_grad()
+    reference(shifted).backward()
+    for n, p in model.named_parameters():
+        assert torch.allclose(got[n], p.grad, atol=2e-5), n
+    model.zero_grad()
+    # the denominator handed over by the loop: an int or a tensor
+    for denom in (7, torch.tensor(7)):
+        assert torch.allclose(tr.compute_loss(model, dict(batch), num_items_in_batch=denom), reference(shifted, 7), atol=1e-5)
+    # shift_labels (already shifted, e.g. by a sequence-parallel loader) win over labels
+    other = torch.full_like(labels, -100)
+    other[:, 2:5] = ids[:, 3:6]
+    loss_s = tr.compute_loss(model, {**batch, "shift_labels": other})
+    assert torch.allclose(loss_s, reference(other), atol=1e-5) and not torch.allclose(loss_s, loss)
+    # nothing to predict: zero loss whose backward still reaches every parameter the forward used
+    empty = tr.compute_loss(model, {**batch, "labels": torch.full_like(labels, -100)})
+    assert float(empty) == 0.0 and empty.requires_grad
+    empty.backward()
+    assert all(p.grad is not None and float(p.grad.abs().sum()) == 0.0 for n, p in model.named_parameters())

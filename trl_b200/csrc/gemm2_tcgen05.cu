@@ -5,7 +5,7 @@
 // Why pairs: with one CTA per 128 x 256 tile every MMA of 16 k-columns reads 4 KB of A and 8 KB of B from shared
 // memory; in a pair each CTA stages its own 128 rows of A and only HALF of the B tile (128 of the 256 columns), and the
 // tensor cores of both SMs read both halves.  Shared-memory traffic and TMA traffic per SM drop by a third, and a
-// stage is 32 KB instead of 48 KB, so the ring is six stages deep instead of four.
+// stage is 32 KB instead of 48 KB, so the ring is seven stages deep instead of four.
 //
 // Roles per CTA (192 threads): warp 0 = TMA producer (its own A rows and its half of B; completion is counted on the
 // LEADER's barrier, CTA rank 0 of the pair), warp 1 = TMEM allocation in both CTAs and, in the leader only, the MMA
