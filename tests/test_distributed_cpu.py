@@ -127,8 +127,8 @@ def test_elastic_resume_with_another_world_size(tmp_path, tmp_path_factory, mode
     out = str(tmp_path / "el")
     _run_stream(world1, mode1, "phase1", out, port, load=False)
     got = _run_stream(world2, mode2, "phase2", out, port + 1)
-    for k in ref:
-        assert torch.allclose(ref[k], got[k], atol=2e-5), (k, (ref[k] - got[k]).abs().max())
+    for k in ref:  # AdamW at lr 1e-3 turns summation-order noise into up to a few 1e-5; a wrong slice shows as 1e-3
+        assert torch.allclose(ref[k], got[k], atol=1e-4), (k, (ref[k] - got[k]).abs().max())
 
 
 def test_grpo_completions_are_dealt_to_ranks_by_length(tmp_path):
