@@ -636,3 +636,54 @@ def test_sft_loss_matches_cross_entropy_and_its_corner_cases(tmp_path, tiny_toke
     assert float(empty) == 0.0 and empty.requires_grad
     empty.backward()
     assert all(p.grad is not None and float(p.grad.abs().sum()) == 0.0 for n, p in model.named_parameters())
+
+
+def test_load_best_model_at_end_neftune_and_ignored_arguments(tmp_path, tiny_tokenizer):
+    from safetensors.torch import load_file
+
+    from trl_b200 import SFTConfig, SFTTrainer
+
+    rows = make_dataset("standard_language_modeling", 16)
+    model = make_tiny_model(seed=0)
+    # a learning rate that makes the evaluation loss rise after the first checkpoint: the best one is the first
+    args = SFTConfig(output_dir=str(tmp_path / "o"), eval_strategy="steps", eval_steps=1, save_steps=1, load_best_model_at_end=True,
+                     metric_for_best_model="loss", **dict(COMMON, max_steps=3, learning_rate=0.3, save_strategy="steps",
+                                                          lr_scheduler_type="constant"))
+    with pytest.warns(UserWarning, match="torch_compile"):
+        args.torch_compile = True
+        tr = SFTTrainer(model, args, train_dataset=rows, eval_dataset=rows[:4] if isinstance(rows, list) else rows.select(range(4)),
+                        processing_class=tiny_tokenizer)
+        tr.train()
+    evals = [(h["step"], h["eval_loss"]) for h in tr.state.log_history if "eval_loss" in h]
+    best_step = min(evals, key=lambda t: t[1])[0]
+    assert tr.state.best_model_checkpoint.endswith(f"checkpoint-{best_step}")
+    saved = load_file(os.path.join(tr.state.best_model_checkpoint, "model.safetensors"))
+    from trl_b200.models.hf_io import to_hf_state_dict
+
+    now = to_hf_state_dict(model)
+    assert all(torch.equal(now[k].float(), saved[k].float()) for k in saved)
+    if best_step != 3:  # the final weights were replaced
+        last = load_file(os.path.join(str(tmp_path / "o"), "checkpoint-3", "model.safetensors"))
+        assert any(not torch.equal(last[k], saved[k]) for k in saved)
+    # NEFTune: noise on the embeddings in training mode only, scaled by alpha / sqrt(L * H), removed after train()
+    m2 = make_tiny_model(seed=0)
+    ids = torch.randint(5, 1000, (2, 12))
+    m2.train()
+    clean = m2(input_ids=ids).logits
+    m2.neftune_noise_alpha = 5.0
+    noisy = m2(input_ids=ids).logits
+    assert not torch.allclose(clean, noisy)
+    m2.eval()
+    assert torch.allclose(m2(input_ids=ids).logits, clean, atol=1e-6)
+    tr2 = SFTTrainer(m2, SFTConfig(output_dir=str(tmp_path / "n"), neftune_noise_alpha=5.0, **COMMON), train_dataset=rows,
+                     processing_class=tiny_tokenizer)
+    m2.neftune_noise_alpha = None
+    seen = {}
+    orig = m2.forward_hidden
+
+    def spy(*a, **kw):
+        seen["alpha"] = m2.neftune_noise_alpha
+        return orig(*a, **kw)
+    m2.forward_hidden = spy
+    tr2.train()
+    assert seen["alpha"] == 5.0 and m2.neftune_noise_alpha is None

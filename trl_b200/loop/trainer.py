@@ -19,6 +19,7 @@ import random
 import re
 import shutil
 import time
+import warnings
 from collections import defaultdict
 from typing import Any, Callable, Optional
 
@@ -480,6 +481,7 @@ class Trainer:
                 raise ValueError(f"No valid checkpoint found in output directory ({a.output_dir})")
         loader = self.get_train_dataloader()
         self.callback_handler.train_dataloader = loader
+        self._apply_runtime_arguments()
         ga = a.gradient_accumulation_steps
         try:
             n_batches = len(loader)
@@ -560,6 +562,12 @@ class Trainer:
         metrics = {"train_runtime": round(runtime, 4), "train_steps_per_second": round(st.global_step / max(runtime, 1e-9), 3),
                    "train_loss": train_loss, "epoch": st.epoch}
         self.log(metrics)
+        lm = getattr(self.model, "language_model", self.model)
+        if getattr(lm, "neftune_noise_alpha", None) is not None:
+            lm.neftune_noise_alpha = None
+        if a.load_best_model_at_end and st.best_model_checkpoint and os.path.isdir(st.best_model_checkpoint):
+            # weights of the checkpoint that scored best on `metric_for_best_model` (optimizer state is left as it is)
+            self._load_weights_only(st.best_model_checkpoint)
         self.control = self.callback_handler.call_event("on_train_end", a, st, self.control)
         from ..extras import profiling
 
@@ -567,6 +575,49 @@ class Trainer:
             profiling.dump_trace(rank=D.rank())
         self.is_in_train = False
         return TrainOutput(st.global_step, train_loss, metrics)
+
+    _IGNORED_WHEN_SET = {
+        "torch_compile": "kernels are hand-written; nothing is traced or compiled",
+        "group_by_length": "batches are not grouped by length (use packing / padding_free instead)",
+        "label_smoothing_factor": "the fused lm_head losses have no label smoothing",
+        "optim_target_modules": "layer-wise optimizers are not available",
+        "hub_model_id": "there is no network: nothing is pushed to the Hub",
+        "fsdp_config": "sharding is chosen with shard_mode", "accelerator_config": "there is no accelerate layer",
+        "liger_kernel_config": "the fused kernels are always on",
+    }
+
+    def _apply_runtime_arguments(self):
+        """Arguments that act on the process or the model rather than on the loop: ``tf32``, ``neftune_noise_alpha``;
+        and one warning for arguments that were set but have no effect here."""
+        a = self.args
+        if a.tf32 is not None and torch.cuda.is_available():
+            torch.backends.cuda.matmul.allow_tf32 = bool(a.tf32)
+            torch.backends.cudnn.allow_tf32 = bool(a.tf32)
+        if a.neftune_noise_alpha:
+            lm = getattr(self.model, "language_model", self.model)
+            lm.neftune_noise_alpha = float(a.neftune_noise_alpha)
+        if not getattr(self, "_warned_ignored", False):
+            self._warned_ignored = True
+            base = TrainingArguments()
+            hit = [f"{k} ({why})" for k, why in self._IGNORED_WHEN_SET.items()
+                   if getattr(a, k, None) not in (None, False, 0, 0.0, "") and getattr(a, k, None) != getattr(base, k, None)]
+            if hit:
+                warnings.warn("training arguments without effect in this framework: " + "; ".join(hit))
+
+    def _load_weights_only(self, folder: str):
+        from ..models.hf_io import load_hf_state_dict, load_state_dict_dir
+
+        m = self.model
+        if hasattr(m, "load_adapter") and os.path.exists(os.path.join(folder, "adapter_model.safetensors")):
+            m.load_adapter(folder)
+        elif getattr(m, "_is_native", False) and hasattr(self.engine, "load_weights"):
+            self.engine.load_weights(load_state_dict_dir(folder))
+        elif hasattr(m, "load_hf_state_dict"):  # composite models (vision-language) map their own key layout
+            m.load_hf_state_dict(load_state_dict_dir(folder))
+        elif getattr(m, "_is_native", False):
+            load_hf_state_dict(m, load_state_dict_dir(folder), strict=True)
+        if self.engine is not None and hasattr(self.engine, "sync_master_from_params"):
+            self.engine.sync_master_from_params()
 
     def optimizer_step(self, batches: list):
         """One optimizer step over ``batches`` (the accumulation window): forward/backward of every

@@ -338,6 +338,14 @@ class CausalLM(nn.Module):
         """Flat ids [T] -> final-norm hidden [T, H].  ``inputs_embeds`` [T, H] replaces the embedding lookup (vision-
         language models splice image features into it)."""
         x = self.embed(input_ids) if inputs_embeds is None else inputs_embeds
+        alpha = getattr(self, "neftune_noise_alpha", None)
+        if alpha and self.training:
+            # NEFTune: uniform noise of magnitude alpha / sqrt(sequence length * hidden size) on the input embeddings
+            # while training (the loop sets the attribute from `neftune_noise_alpha` and removes it afterwards)
+            lens = (ctx.cu_seqlens[1:] - ctx.cu_seqlens[:-1]).to(x.device)
+            per_tok = torch.repeat_interleave(lens, lens.long(), output_size=x.shape[0]).to(torch.float32)
+            mag = float(alpha) / torch.sqrt(per_tok * x.shape[-1])
+            x = x + ((torch.rand_like(x, dtype=torch.float32) * 2 - 1) * mag[:, None]).to(x.dtype)
         n_ckpt = getattr(self, "checkpoint_num_layers", None)
         keep = None
         for li, layer in enumerate(self.layers):

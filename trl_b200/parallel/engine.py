@@ -159,6 +159,14 @@ class TrainEngine:
             pass
         self._install_grad_views()
 
+    @torch.no_grad()
+    def sync_master_from_params(self):
+        """After weights were written into the parameters from outside (a checkpoint loaded in place): refresh this
+        rank's fp32 master slices so that the next optimizer step starts from them."""
+        for b in self.buckets:
+            if b.master.data_ptr() != b.flat_param[b.lo:b.hi].data_ptr():
+                b.master.copy_(b.flat_param[b.lo:b.hi])
+
     def release_hooks(self):
         """Detaches this engine's gradient hooks from the parameters (the buffers stay valid)."""
         for h in self._hooks:
