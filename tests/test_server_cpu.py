@@ -137,3 +137,38 @@ def test_process_rollout_worker_feeds_samples_and_reports_failures(tiny_tokenize
             raise AssertionError("no failure reported")
     finally:
         nowhere.stop()
+
+
+def test_grpo_trains_against_the_rollout_server(tmp_path, tiny_tokenizer):
+    """`vllm_mode="server"`: completions come from the server over HTTP, the policy's weights are pushed to it before
+    every generation batch (after the push the server's log-probs follow the trained policy)."""
+    from trl_b200 import GRPOConfig, GRPOTrainer
+    from trl_b200.generation.server_rollout import ServerRollout
+    from trl_b200.scripts.rollout_serve import ServeArguments, WorkerPool
+    from trl_b200.testing import make_dataset, make_tiny_model
+
+    pool = WorkerPool(ServeArguments(model="preset:tiny-qwen2", data_parallel_size=1, max_model_len=96))
+    with _Server(pool) as srv:
+        model = make_tiny_model("tiny-qwen2", seed=0)
+        args = GRPOConfig(output_dir=str(tmp_path), per_device_train_batch_size=4, num_generations=4, max_completion_length=6,
+                          max_steps=2, logging_steps=1, learning_rate=5e-3, use_cpu=True, save_strategy="no", report_to="none",
+                          beta=0.0, use_vllm=True, vllm_mode="server", vllm_server_host="127.0.0.1",
+                          vllm_server_port=srv.port, vllm_server_timeout=30)
+        seen = []
+
+        def reward(completion_ids, **kw):
+            seen.append(len(completion_ids))
+            return [float(sum(c) % 5) for c in completion_ids]
+        tr = GRPOTrainer(model, reward, args, train_dataset=make_dataset("standard_prompt_only", 8), processing_class=tiny_tokenizer)
+        tr.train()
+        assert isinstance(tr._rollout, ServerRollout) and tr._rollout.stats["requests"] >= 2 and sum(seen) >= 8
+        logs = [h for h in tr.state.log_history if "reward" in h]
+        assert len(logs) == 2 and all(np.isfinite(h["loss"]) for h in logs)
+        # the server holds the weights of the last push: after one more push its log-probs equal the trained policy's
+        tr._rollout.sync_weights()
+        seq = [5, 6, 7, 8, 9, 10, 11]
+        got = tr._rollout.client.get_sequence_logprobs([seq], [3])[0]
+        with torch.no_grad():
+            lp = torch.log_softmax(model(input_ids=torch.tensor([seq])).logits[0].float(), -1)
+        want = lp[torch.arange(2, 6), torch.tensor(seq[3:])]
+        assert np.allclose(got, want.numpy(), atol=1e-4), (got, want)

@@ -204,6 +204,15 @@ class OnlineTrainer(Trainer):
                               **(a.generation_kwargs or {}))
 
     def _get_rollout(self):
+        a0 = self.args
+        if a0.use_vllm and a0.vllm_mode == "server":  # generation lives in another process: `trl vllm-serve`
+            if self._rollout is None:
+                from ..generation.server_rollout import ServerRollout
+
+                self._rollout = ServerRollout(self.model, base_url=a0.vllm_server_base_url, host=a0.vllm_server_host,
+                                              port=a0.vllm_server_port, timeout=a0.vllm_server_timeout,
+                                              client=getattr(self, "_rollout_client", None))
+            return self._rollout
         gen_model = self.model
         if getattr(getattr(self, "engine", None), "mode", "") == "full_shard_stream":
             # the training side holds one layer at a time: generation gets its own whole replica, refreshed from the
