@@ -160,6 +160,10 @@ class GRPOConfig(_OnlineConfig):
             self.scale_rewards = "group" if self.scale_rewards else "none"
         if self.scale_rewards not in ("group", "batch", "none"):
             raise ValueError("scale_rewards must be one of 'group', 'batch', 'none'")
+        if getattr(self, "vllm_structured_outputs_regex", None):
+            raise NotImplementedError("vllm_structured_outputs_regex: the rollout engine has no regex-constrained sampler")
+        if self.use_vllm and self.vllm_mode not in ("colocate", "server"):
+            raise ValueError("vllm_mode must be 'colocate' (the in-process engine) or 'server'")
         if self.loss_type not in self._LOSS_TYPES:
             raise ValueError(f"Unknown loss type: {self.loss_type}")
         if self.importance_sampling_level not in ("token", "sequence", "sequence_token"):

@@ -537,7 +537,10 @@ class OnlineTrainer(Trainer):
                          "completion": [str(c) for c in self._logs["completion"]],
                          **{k: list(v) for k, v in self._logs["rewards"].items()},
                          "advantage": list(self._logs["advantages"])}
-                pd.DataFrame(table).to_parquet(os.path.join(d, f"completions_{self.state.global_step:05d}.parquet"))
+                df = pd.DataFrame(table)
+                if getattr(self.args, "log_unique_prompts", False):  # one row per prompt: the first completion seen
+                    df = df.drop_duplicates(subset=["prompt"])
+                df.to_parquet(os.path.join(d, f"completions_{self.state.global_step:05d}.parquet"))
             except Exception:
                 pass
             for v in (self._logs["prompt"], self._logs["completion"], self._logs["advantages"]):
