@@ -687,3 +687,25 @@ def test_load_best_model_at_end_neftune_and_ignored_arguments(tmp_path, tiny_tok
     m2.forward_hidden = spy
     tr2.train()
     assert seen["alpha"] == 5.0 and m2.neftune_noise_alpha is None
+
+
+def test_group_by_length_batches_hold_similar_lengths(tmp_path, tiny_tokenizer):
+    from trl_b200 import SFTConfig, SFTTrainer
+    from trl_b200.loop.trainer import LengthGroupedSampler
+
+    lengths = [3, 50, 4, 48, 5, 47, 6, 46, 7, 45, 8, 44]
+    order = list(LengthGroupedSampler(lengths, batch_size=4, seed=0))
+    assert sorted(order) == list(range(12)) and lengths[order[0]] == 50          # the longest sample comes first
+    spans = [max(lengths[j] for j in order[i:i + 4]) - min(lengths[j] for j in order[i:i + 4]) for i in range(0, 12, 4)]
+    assert sum(s < 10 for s in spans) >= 2, spans                                # batches are homogeneous in length
+    assert list(LengthGroupedSampler(lengths, 4, seed=0)) == order               # reproducible
+    s2 = LengthGroupedSampler(lengths, 4, seed=0)
+    s2.set_epoch(1)
+    assert sorted(s2) == list(range(12))
+    rows = [{"text": " ".join(["word"] * n)} for n in (2, 30, 3, 28, 2, 31, 4, 29)]
+    tr = SFTTrainer(make_tiny_model(), SFTConfig(output_dir=str(tmp_path), group_by_length=True, **COMMON), train_dataset=rows,
+                    processing_class=tiny_tokenizer)
+    batches = list(tr.get_train_dataloader())
+    widths = [b["input_ids"].shape[1] for b in batches]
+    assert max(widths) > 2 * min(widths)        # short samples sit together, long ones together
+    tr.train()

@@ -102,6 +102,27 @@ class SeededRandomSampler:
         return self.n
 
 
+class LengthGroupedSampler(SeededRandomSampler):
+    """``group_by_length``: a random order in which every global batch holds samples of similar length, so that padded
+    batches waste little.  As in transformers: shuffle, cut into mega-batches of 50 global batches, sort each by
+    length (longest first), and put the mega-batch with the longest sample first (an out-of-memory shows at step 1)."""
+
+    def __init__(self, lengths, batch_size: int, seed: int, mega: int = 50):
+        super().__init__(len(lengths), seed)
+        self.lengths, self.batch = [int(x) for x in lengths], max(1, int(batch_size))
+        self.mega = self.batch * mega
+
+    def __iter__(self):
+        g = torch.Generator()
+        g.manual_seed(self.seed + self.epoch)
+        order = torch.randperm(self.n, generator=g).tolist()
+        chunks = [sorted(order[i:i + self.mega], key=lambda j: -self.lengths[j]) for i in range(0, self.n, self.mega)]
+        if chunks:
+            k = max(range(len(chunks)), key=lambda c: self.lengths[chunks[c][0]])
+            chunks[0], chunks[k] = chunks[k], chunks[0]
+        return iter([j for c in chunks for j in c])
+
+
 class DataLoaderLite:
     """Minimal map-style / iterable loader (single process; collate on the host)."""
 
@@ -276,6 +297,16 @@ class Trainer:
         if getattr(self.args, "train_sampling_strategy", "random") == "sequential":
             return range(len(ds))
         seed = self.args.data_seed if self.args.data_seed is not None else self.args.seed
+        if getattr(self.args, "group_by_length", False):
+            col = self.args.length_column_name or "length"
+            names = getattr(ds, "column_names", None) or (list(ds[0].keys()) if len(ds) and isinstance(ds[0], dict) else [])
+            if col in names:
+                lengths = ds[col] if hasattr(ds, "column_names") else [r[col] for r in ds]
+            elif "input_ids" in names:
+                lengths = [len(r["input_ids"]) for r in ds]
+            else:
+                raise ValueError(f"group_by_length needs a {col!r} or an 'input_ids' column in the (prepared) dataset")
+            return LengthGroupedSampler(lengths, self._train_batch_size * max(1, D.world_size() // self.sp_size), seed)
         return SeededRandomSampler(len(ds), seed)
 
     def _get_eval_sampler(self, dataset):
@@ -578,7 +609,6 @@ class Trainer:
 
     _IGNORED_WHEN_SET = {
         "torch_compile": "kernels are hand-written; nothing is traced or compiled",
-        "group_by_length": "batches are not grouped by length (use packing / padding_free instead)",
         "label_smoothing_factor": "the fused lm_head losses have no label smoothing",
         "optim_target_modules": "layer-wise optimizers are not available",
         "hub_model_id": "there is no network: nothing is pushed to the Hub",
