@@ -218,6 +218,9 @@ def test_ppo(tmp_path, tiny_tokenizer, separate_value_model):
     assert [n for n in _unchanged(model, before) if not n.startswith("value_model.")] == []
     assert any("loss/policy_avg" in x for x in tr.state.log_history)
     assert any("objective/rlhf_reward" in x for x in tr.state.log_history)
+    # sample generations: default 10 over the run -> at least one table of near-greedy completions with scores
+    tab = tr.sample_generations
+    assert set(tab) == {"query", "model response", "score"} and len(tab["score"]) == len(tab["query"]) > 0
     wrapped = AutoModelForCausalLMWithValueHead(make_tiny_model())
     ids = torch.randint(5, 100, (2, 7))
     logits, _, values = wrapped(input_ids=ids, attention_mask=torch.ones_like(ids))

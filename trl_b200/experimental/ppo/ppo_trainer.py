@@ -161,6 +161,44 @@ class PPOTrainer(OnlineTrainer):
                 m[k].append(v)
         return (loss, None) if return_outputs else loss
 
+    # ---- sample generations ------------------------------------------------------------------------------------------
+    def generate_completions(self, sampling: bool = False, max_prompts: int = 8) -> dict:
+        """Near-greedy completions for a few evaluation prompts with their scores, printed as a table and kept in
+        ``self.sample_generations`` (trl/experimental/ppo/ppo_trainer.py:951-1029).  ``sampling=True``: one batch only."""
+        ds = self.eval_dataset if self.eval_dataset is not None else self.train_dataset
+        rows = [dict(ds[i]) for i in range(min(len(ds), max_prompts))]
+        prompts = [r["prompt"] for r in rows]
+        was_t, was_training = self.temperature, self.model.training
+        self.temperature = 0.01 + 1e-7
+        self.model.eval()
+        try:
+            with torch.no_grad():
+                _, completion_ids, _, _ = self._generate(prompts)
+                texts = self.processing_class.batch_decode(completion_ids, skip_special_tokens=True)
+                rw = self._calculate_rewards(rows, prompts, texts, completion_ids)
+        finally:
+            self.temperature = was_t
+            self.model.train(was_training)
+        B, r = len(prompts), D.rank()
+        scores = (rw[r * B:(r + 1) * B] * self.reward_weights.to(rw.device)[None]).nansum(1).tolist()
+        table = {"query": [p if isinstance(p, str) else str(p) for p in prompts], "model response": texts, "score": scores}
+        self.sample_generations = table
+        if D.is_main():
+            from ...trainer.utils import print_prompt_completions_sample
+
+            print_prompt_completions_sample(table["query"], texts, {"score": scores}, [0.0] * B, self.state.global_step, B)
+        return table
+
+    def _maybe_log_save_evaluate(self, tr_loss, grad_norm, lr, t_start):
+        out = super()._maybe_log_save_evaluate(tr_loss, grad_norm, lr, t_start)
+        n, st = self.args.num_sample_generations, self.state
+        if n and n > 0 and st.max_steps and st.global_step > getattr(self, "_sampled_at", -1):
+            every = max(1, st.max_steps // n)
+            if st.global_step % every == 0:
+                self._sampled_at = st.global_step
+                self.generate_completions(sampling=True)
+        return out
+
     def _save(self, output_dir: str, state_dict=None):
         """The checkpoint is the policy; the value parts are stored next to it."""
         import os
