@@ -709,3 +709,24 @@ def test_group_by_length_batches_hold_similar_lengths(tmp_path, tiny_tokenizer):
     widths = [b["input_ids"].shape[1] for b in batches]
     assert max(widths) > 2 * min(widths)        # short samples sit together, long ones together
     tr.train()
+
+
+def test_sft_evaluation_with_compute_metrics(tmp_path, tiny_tokenizer):
+    """`compute_metrics` receives predictions and labels of the whole evaluation set (batches of different width are
+    padded with -100); `preprocess_logits_for_metrics` turns logits into token ids before they are collected."""
+    from trl_b200 import SFTConfig, SFTTrainer
+
+    rows = [{"text": " ".join(["word"] * n)} for n in (3, 9, 4, 12, 5, 7)]
+    seen = {}
+
+    def metrics(ep):
+        seen["pred"], seen["lab"] = ep.predictions.shape, ep.label_ids.shape
+        valid = ep.label_ids[:, 1:] != -100
+        acc = ((ep.predictions[:, :-1] == ep.label_ids[:, 1:]) & valid).sum() / max(1, valid.sum())
+        return {"token_accuracy": float(acc)}
+    tr = SFTTrainer(make_tiny_model(), SFTConfig(output_dir=str(tmp_path), per_device_eval_batch_size=2, **COMMON),
+                    train_dataset=rows, eval_dataset=rows, processing_class=tiny_tokenizer, compute_metrics=metrics,
+                    preprocess_logits_for_metrics=lambda logits, labels: logits.argmax(-1))
+    out = tr.evaluate()
+    assert "eval_token_accuracy" in out and 0.0 <= out["eval_token_accuracy"] <= 1.0 and "eval_loss" in out
+    assert seen["pred"] == seen["lab"] and seen["pred"][0] == 6 and seen["pred"][1] >= 12

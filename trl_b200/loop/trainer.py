@@ -801,6 +801,8 @@ class Trainer:
             loss, logits, labels = self.prediction_step(self.model, batch, prediction_loss_only=self.compute_metrics is None)
             losses.append(loss.float().reshape(1))
             if logits is not None and self.compute_metrics is not None:
+                if self.preprocess_logits_for_metrics is not None:
+                    logits = self.preprocess_logits_for_metrics(logits, labels)
                 preds.append(logits.cpu())
                 labels_all.append(labels.cpu() if labels is not None else None)
             self.control = self.callback_handler.call_event("on_prediction_step", self.args, self.state, self.control)
@@ -812,8 +814,15 @@ class Trainer:
         if self.compute_metrics is not None and preds:
             from types import SimpleNamespace
 
-            ep = SimpleNamespace(predictions=torch.cat(preds).numpy(),
-                                 label_ids=torch.cat(labels_all).numpy() if labels_all[0] is not None else None)
+            def pad_cat(ts):  # batches of different width: pad the sequence dimension with -100, as transformers does
+                if ts[0].ndim < 2:
+                    return torch.cat(ts)
+                w = max(t.shape[1] for t in ts)
+                return torch.cat([t if t.shape[1] == w else torch.nn.functional.pad(
+                    t, (0, 0) * (t.ndim - 2) + (0, w - t.shape[1]), value=-100) for t in ts])
+
+            ep = SimpleNamespace(predictions=pad_cat(preds).float().numpy(),
+                                 label_ids=pad_cat(labels_all).numpy() if labels_all[0] is not None else None)
             for k, v in self.compute_metrics(ep).items():
                 metrics[k if k.startswith(metric_key_prefix) else f"{metric_key_prefix}_{k}"] = v
         metrics[f"{metric_key_prefix}_runtime"] = round(time.time() - t0, 4)

@@ -439,7 +439,13 @@ class SFTTrainer(Trainer):
         inputs = self._prepare_inputs(inputs)
         with torch.no_grad():
             loss = self.compute_loss(model, inputs)
-        return loss.detach(), None, None
+            if prediction_loss_only or getattr(model, "is_vlm", False):
+                return loss.detach(), None, None
+            # metrics on predictions (``compute_metrics``): this is the one place where [batch, length, vocab] logits
+            # are materialised, as the reference does in evaluation; training never does
+            kw = {k: inputs[k] for k in ("attention_mask", "position_ids") if inputs.get(k) is not None}
+            logits = model(input_ids=inputs["input_ids"], **kw).logits
+        return loss.detach(), logits, inputs.get("labels")
 
     def log(self, logs: dict, start_time: float | None = None):
         mode = "train" if self.model.training else "eval"
