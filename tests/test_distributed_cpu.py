@@ -196,3 +196,13 @@ def test_expert_parallel_sft_matches_replicated_experts(tmp_path, tmp_path_facto
     # (Adam normalises them), so the sums agree to a fraction of the total movement (4096+ elements x 4e-4), not bit-wise
     for k, v in ref["digest"].items():
         assert abs(v - two["digest"][k]) < 2e-3, k
+
+
+def test_server_rollout_with_two_training_ranks():
+    """`vllm_mode="server"` with two training processes: prompts gathered, one request by the main process, every rank
+    gets its own completions back; one weight push for the job."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29631", os.path.join(HERE, "dist_worker_server_rollout.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "SERVER_ROLLOUT_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
