@@ -356,3 +356,77 @@ def test_split_and_unsplit_pixel_values_for_the_three_vision_layouts():
     assert split_pixel_values_by_grid({"input_ids": 1}) == {"input_ids": 1}
     plain = {"pixel_values": torch.zeros(2, 3), "num_images": [1, 1]}
     assert split_pixel_values_by_grid(plain) is plain
+
+
+def test_flops_per_token_and_mfu_properties():
+    """Properties the reference tests for its MFU helpers (tests/test_utils.py:1462-1541), on native configurations."""
+    import copy
+
+    from trl_b200.models.configuration import preset
+    from trl_b200.trainer.utils import adjusted_mfu, compute_mfu
+
+    cfg = preset("tiny-qwen3")
+    f8, f16, f32 = (compute_flops_per_token(cfg, n) for n in (8192, 16384, 32768))
+    assert f32 - f16 == 2 * (f16 - f8)                      # only the attention scores depend on the length
+    tied, untied = copy.deepcopy(cfg), copy.deepcopy(cfg)
+    tied.tie_word_embeddings, untied.tie_word_embeddings = True, False
+    assert compute_flops_per_token(untied, 16384) - compute_flops_per_token(tied, 16384) == 3 * 2 * cfg.vocab_size * cfg.hidden_size
+    moe = preset("tiny-qwen3-moe")
+    lo, hi = copy.deepcopy(moe), copy.deepcopy(moe)
+    lo.num_experts_per_tok, hi.num_experts_per_tok = 1, 2
+    per_expert = 2 * 3 * moe.hidden_size * moe.moe_intermediate_size
+    assert compute_flops_per_token(hi, 16384) - compute_flops_per_token(lo, 16384) == 3 * moe.num_hidden_layers * per_expert
+    # utilisation: 100 % when the job's tokens per second are exactly peak * devices / flops per token
+    flops, peak, world = 100e9, 989.5e12, 8
+    assert compute_mfu(flops, peak * world / flops, world, peak_flops_per_device=peak) == pytest.approx(100.0)
+    # causal correction: multiplicative, consistent with the two formulas, stronger for longer sequences
+    full = compute_flops_per_token(moe, 16384)
+    hd = moe.head_dim or moe.hidden_size // moe.num_attention_heads
+    half = moe.num_hidden_layers * 3 * 2 * moe.num_attention_heads * hd * 16384
+    assert adjusted_mfu(100.0, moe, 16384) == pytest.approx(100.0 * (full - half) / full)
+    assert adjusted_mfu(100.0, moe, 16384) == pytest.approx(2 * adjusted_mfu(50.0, moe, 16384))
+    assert adjusted_mfu(100.0, moe, 4096) > adjusted_mfu(100.0, moe, 16384) > adjusted_mfu(100.0, moe, 65536)
+
+
+@pytest.mark.parametrize("temperature", [1.0, 0.7])
+def test_patched_chunked_lm_head_with_and_without_completion_mask(temperature):
+    """With a completion mask the patched forward equals the unmasked one on completion positions and is zero on prompt
+    positions; the lm_head gradient of a masked sum is the same either way; values equal a plain log-softmax
+    (tests/test_utils.py:1321-1460 on the native decoder)."""
+    from trl_b200.ops.chunked_lm_head import patch_chunked_lm_head
+    from trl_b200.testing import make_tiny_model
+
+    torch.manual_seed(42)
+    B, S = 4, 16
+    plain = make_tiny_model(seed=0)
+    model = patch_chunked_lm_head(make_tiny_model(seed=0), chunk_size=32, temperature=temperature)
+    ids = torch.randint(5, 1000, (B, S))
+    am = torch.ones(B, S, dtype=torch.long)
+    cm = torch.zeros(B, S)
+    cm[:, S // 2:] = 1.0
+    full = model(input_ids=ids, attention_mask=am)
+    masked = model(input_ids=ids, attention_mask=am, completion_mask=cm)
+    sm = cm[:, 1:].bool()
+    assert torch.allclose(masked["log_probs"][sm], full["log_probs"][sm], atol=1e-5)
+    assert torch.allclose(masked["entropy"][sm], full["entropy"][sm], atol=1e-5)
+    assert (masked["log_probs"][~sm] == 0).all() and (masked["entropy"][~sm] == 0).all()
+    # against explicit logits
+    with torch.no_grad():
+        logits = plain(input_ids=ids, attention_mask=am).logits[:, :-1].float() / temperature
+    lsm = torch.log_softmax(logits, -1)
+    want_lp = lsm.gather(-1, ids[:, 1:, None])[..., 0]
+    want_ent = -(lsm.exp() * lsm).sum(-1)
+    assert torch.allclose(full["log_probs"], want_lp, atol=1e-4) and torch.allclose(full["entropy"], want_ent, atol=1e-4)
+    # gradients of a masked sum agree
+    head = "lm_head"
+    (full["log_probs"] * cm[:, 1:]).sum().backward()
+    g_full = dict(model.named_parameters())[head].grad.clone()
+    model.zero_grad()
+    out2 = model(input_ids=ids, attention_mask=am, completion_mask=cm)
+    (out2["log_probs"] * cm[:, 1:]).sum().backward()
+    assert torch.allclose(dict(model.named_parameters())[head].grad, g_full, atol=1e-5)
+    # padding on the right is excluded like a prompt position
+    am2 = am.clone()
+    am2[0, -3:] = 0
+    out3 = model(input_ids=ids, attention_mask=am2, completion_mask=cm)
+    assert (out3["log_probs"][0, -3:] == 0).all() and torch.allclose(out3["log_probs"][1:], masked["log_probs"][1:], atol=1e-5)

@@ -380,34 +380,47 @@ B200_PEAK_BF16_FLOPS = 2.25e15
 H100_PEAK_BF16_FLOPS = 989.5e12
 
 
-def compute_flops_per_token(config, seq_len: int) -> float:
-    """Training FLOPs per token = 3 x forward (2 FLOPs per MAC); MoE counts router + top-k experts."""
+def compute_flops_per_token(config, seq_len: int) -> int:
+    """Training FLOPs per token of a causal decoder: 3 x the forward pass (backward counted as twice the forward), two
+    FLOPs per multiply-add.  Attention scores are counted against the whole ``seq_len`` (the non-causal convention of
+    PaLM / Megatron; :func:`adjusted_mfu` removes the masked half).  Mixture-of-experts layers count the router and
+    the ``num_experts_per_tok`` active experts; the embedding lookup is counted like a ``V x h`` product and the
+    lm_head only when it is not tied to it (trl/trainer/utils.py:1520-1574)."""
     c = config
-    h, L = c.hidden_size, c.num_hidden_layers
+    h, L, V = c.hidden_size, c.num_hidden_layers, c.vocab_size
     hd = getattr(c, "head_dim", None) or h // c.num_attention_heads
     q, kv = c.num_attention_heads * hd, c.num_key_value_heads * hd
-    attn_proj = 2 * h * (q + 2 * kv) + 2 * q * h
-    attn_score = 2 * 2 * q * seq_len / 2  # causal: half the square
-    n_exp = getattr(c, "num_experts", 0) or 0
-    if n_exp:
-        k = c.num_experts_per_tok
-        mlp = 2 * 3 * h * c.moe_intermediate_size * k + 2 * h * n_exp
+    attn = 2 * h * (q + 2 * kv) + 2 * q * h + 2 * 2 * q * seq_len
+    dense_mlp = 2 * 3 * h * c.intermediate_size
+    k = getattr(c, "num_experts_per_tok", None) or 0
+    n_exp = getattr(c, "num_experts", None) or getattr(c, "num_local_experts", None) or 0
+    if k and n_exp:
+        sparse = k * 2 * 3 * h * c.moe_intermediate_size + 2 * h * n_exp
+        step = getattr(c, "decoder_sparse_step", 1) or 1
+        layers = sum(attn + (sparse if li % step == 0 else dense_mlp) for li in range(L))
     else:
-        mlp = 2 * 3 * h * c.intermediate_size
-    head = 2 * h * c.vocab_size
-    return 3.0 * (L * (attn_proj + attn_score + mlp) + head)
+        layers = L * (attn + dense_mlp)
+    head = 0 if getattr(c, "tie_word_embeddings", False) else 2 * V * h
+    return int(3 * (layers + 2 * V * h + head))
 
 
-def compute_mfu(config, tokens_per_second: float, seq_len: int, num_devices: int = 1,
+def compute_mfu(flops_per_token, tokens_per_second: float, world_size: int = 1,
                 peak_flops_per_device: float = B200_PEAK_BF16_FLOPS) -> float:
-    return compute_flops_per_token(config, seq_len) * tokens_per_second / (num_devices * peak_flops_per_device)
+    """Model FLOPs utilisation in percent: ``flops_per_token`` (from :func:`compute_flops_per_token`) times the job's
+    tokens per second over the peak of ``world_size`` devices (default peak: B200 dense bf16; the reference defaults to
+    an H100's 989.5e12).  Tokens that several ranks see together (sequence / context / tensor parallel groups) are to
+    be counted once by the caller."""
+    return 100.0 * float(flops_per_token) * tokens_per_second / (peak_flops_per_device * world_size)
 
 
-def adjusted_mfu(config, tokens_per_second: float, seq_len: int, num_devices: int = 1, gradient_checkpointing=True,
-                 peak_flops_per_device: float = B200_PEAK_BF16_FLOPS) -> float:
-    """With full recomputation the hardware does 4x forward, not 3x."""
-    m = compute_mfu(config, tokens_per_second, seq_len, num_devices, peak_flops_per_device)
-    return m * (4.0 / 3.0) if gradient_checkpointing else m
+def adjusted_mfu(mfu: float, config, seq_len: int) -> float:
+    """``mfu`` corrected for causal masking: half of the attention-score FLOPs (``Q K^T`` and ``P V``) that
+    :func:`compute_flops_per_token` counts are never done."""
+    c = config
+    hd = getattr(c, "head_dim", None) or c.hidden_size // c.num_attention_heads
+    full = compute_flops_per_token(c, seq_len)
+    half_scores = c.num_hidden_layers * 3 * 2 * c.num_attention_heads * hd * seq_len
+    return mfu * (full - half_scores) / full
 
 
 def print_prompt_completions_sample(prompts: list, completions: list, rewards: dict[str, list[float]],
