@@ -430,3 +430,62 @@ def test_patched_chunked_lm_head_with_and_without_completion_mask(temperature):
     am2[0, -3:] = 0
     out3 = model(input_ids=ids, attention_mask=am2, completion_mask=cm)
     assert (out3["log_probs"][0, -3:] == 0).all() and torch.allclose(out3["log_probs"][1:], masked["log_probs"][1:], atol=1e-5)
+
+
+def test_print_prompt_completions_sample_tables(capsys):
+    """Literal tables of the reference's tests (tests/test_utils.py:632-866): plain strings, extra columns after the
+    advantage, chat messages with the role on its own line and reasoning before the answer, a random sub-sample."""
+    import textwrap
+
+    from trl_b200.trainer.utils import print_prompt_completions_sample
+
+    rewards = {"Correctness": [0.123, 0.456], "Format": [0.789, 0.101]}
+    print_prompt_completions_sample(["The sky is", "The sun is"], [" blue.", " in the sky."], rewards, [0.987, 0.654], 42)
+    assert capsys.readouterr().out == textwrap.dedent("""\
+        ╭──────────────────────────── Step 42 ─────────────────────────────╮
+        │ ┏━━━━━━━━━━━━┳━━━━━━━━━━━━━━┳━━━━━━━━━━━━━┳━━━━━━━━┳━━━━━━━━━━━┓ │
+        │ ┃ Prompt     ┃ Completion   ┃ Correctness ┃ Format ┃ Advantage ┃ │
+        │ ┡━━━━━━━━━━━━╇━━━━━━━━━━━━━━╇━━━━━━━━━━━━━╇━━━━━━━━╇━━━━━━━━━━━┩ │
+        │ │ The sky is │  blue.       │        0.12 │   0.79 │      0.99 │ │
+        │ ├────────────┼──────────────┼─────────────┼────────┼───────────┤ │
+        │ │ The sun is │  in the sky. │        0.46 │   0.10 │      0.65 │ │
+        │ └────────────┴──────────────┴─────────────┴────────┴───────────┘ │
+        ╰──────────────────────────────────────────────────────────────────╯
+        """)
+    print_prompt_completions_sample(["The sky is", "The sun is"], [" blue.", " in the sky."], rewards, [0.987, 0.654], 42,
+                                    extra={"source": ["dataset_A", "dataset_B"]})
+    assert capsys.readouterr().out == textwrap.dedent("""\
+        ╭────────────────────────────────── Step 42 ───────────────────────────────────╮
+        │ ┏━━━━━━━━━━━━┳━━━━━━━━━━━━━━┳━━━━━━━━━━━━━┳━━━━━━━━┳━━━━━━━━━━━┳━━━━━━━━━━━┓ │
+        │ ┃ Prompt     ┃ Completion   ┃ Correctness ┃ Format ┃ Advantage ┃ source    ┃ │
+        │ ┡━━━━━━━━━━━━╇━━━━━━━━━━━━━━╇━━━━━━━━━━━━━╇━━━━━━━━╇━━━━━━━━━━━╇━━━━━━━━━━━┩ │
+        │ │ The sky is │  blue.       │        0.12 │   0.79 │      0.99 │ dataset_A │ │
+        │ ├────────────┼──────────────┼─────────────┼────────┼───────────┼───────────┤ │
+        │ │ The sun is │  in the sky. │        0.46 │   0.10 │      0.65 │ dataset_B │ │
+        │ └────────────┴──────────────┴─────────────┴────────┴───────────┴───────────┘ │
+        ╰──────────────────────────────────────────────────────────────────────────────╯
+        """)
+    prompts = [[{"role": "user", "content": "What color is the sky?"}]]
+    for key in ("reasoning_content", "thinking"):
+        completions = [[{"role": "assistant", key: "I think it is blue.", "content": "It is blue."}]]
+        print_prompt_completions_sample(prompts, completions, {"Score": [0.5]}, [0.9], 1)
+        assert capsys.readouterr().out == textwrap.dedent("""\
+            ╭─────────────────────────────── Step 1 ───────────────────────────────╮
+            │ ┏━━━━━━━━━━━━━━━━━━━━━━━━┳━━━━━━━━━━━━━━━━━━━━━┳━━━━━━━┳━━━━━━━━━━━┓ │
+            │ ┃ Prompt                 ┃ Completion          ┃ Score ┃ Advantage ┃ │
+            │ ┡━━━━━━━━━━━━━━━━━━━━━━━━╇━━━━━━━━━━━━━━━━━━━━━╇━━━━━━━╇━━━━━━━━━━━┩ │
+            │ │ USER                   │ ASSISTANT           │  0.50 │      0.90 │ │
+            │ │ What color is the sky? │ I think it is blue. │       │           │ │
+            │ │                        │ It is blue.         │       │           │ │
+            │ └────────────────────────┴─────────────────────┴───────┴───────────┘ │
+            ╰──────────────────────────────────────────────────────────────────────╯
+            """)
+    # tool messages show as name(args); a sub-sample shows one of the rows
+    print_prompt_completions_sample([[{"role": "user", "content": "Paris?"}]],
+                                    [[{"role": "tool", "name": "get_temperature", "args": {"location": "Paris"}}]],
+                                    {"Score": [0.5]}, [0.9], 1)
+    out = capsys.readouterr().out
+    assert "TOOL" in out and "get_temperature(" in out
+    print_prompt_completions_sample(["A", "B"], ["1", "2"], {"Score": [0.1, 0.2]}, [0.3, 0.4], 10, num_samples=1)
+    out = capsys.readouterr().out
+    assert ("│ A      │ 1 " in out) != ("│ B      │ 2 " in out)

@@ -435,9 +435,17 @@ def print_prompt_completions_sample(prompts: list, completions: list, rewards: d
         idx = random.sample(idx, num_samples)
 
     def text(x):
-        if isinstance(x, list):
-            return "\n".join(f"{m.get('role', '?').upper()}: {m.get('content', '')}" for m in x)
-        return str(x)
+        if not isinstance(x, list):
+            return str(x)
+        parts = []
+        for m in x:  # one block per message: the role on a line of its own, reasoning before the answer
+            if m.get("role") == "tool" and "name" in m:
+                body = f"{m['name']}({m.get('args')})"
+            else:
+                think = m.get("reasoning_content") or m.get("thinking")
+                body = (str(think) + "\n" if think else "") + str(m.get("content", ""))
+            parts.append(f"{str(m.get('role', '?')).upper()}\n{body}")
+        return "\n\n".join(parts)
     try:
         from rich.console import Console
         from rich.panel import Panel
@@ -449,12 +457,12 @@ def print_prompt_completions_sample(prompts: list, completions: list, rewards: d
         table.add_column("Completion", style="bright_green")
         for k in rewards:
             table.add_column(k, style="bold cyan", justify="right")
-        for k in (extra or {}):
-            table.add_column(k, style="magenta")
         table.add_column("Advantage", style="bold magenta", justify="right")
+        for k in (extra or {}):  # columns logged by reward functions come last
+            table.add_column(k, style="magenta")
         for i in idx:
             table.add_row(Text(text(prompts[i])), Text(text(completions[i])), *[f"{rewards[k][i]:.2f}" for k in rewards],
-                          *[str(v[i]) for v in (extra or {}).values()], f"{advantages[i]:.2f}")
+                          f"{advantages[i]:.2f}", *[str(v[i]) for v in (extra or {}).values()])
             table.add_section()
         Console().print(Panel(table, expand=False, title=f"Step {step}", border_style="bold white"))
     except Exception:
