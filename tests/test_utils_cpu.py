@@ -489,3 +489,27 @@ def test_print_prompt_completions_sample_tables(capsys):
     print_prompt_completions_sample(["A", "B"], ["1", "2"], {"Score": [0.1, 0.2]}, [0.3, 0.4], 10, num_samples=1)
     out = capsys.readouterr().out
     assert ("│ A      │ 1 " in out) != ("│ B      │ 2 " in out)
+
+
+def test_model_card_fields_and_missing_values():
+    """The assertions of the reference's model-card tests (tests/test_utils.py:334-381)."""
+    from trl_b200.trainer.utils import generate_model_card
+
+    text = str(generate_model_card(
+        base_model="username/my_base_model", model_name="my_model", hub_model_id="username/my_hub_model",
+        dataset_name="username/my_dataset", tags=["trl", "trainer-tag"], wandb_url="https://wandb.ai/username/project_id/runs/abcd1234",
+        trackio_url="https://huggingface.co/spaces/username/space_id",
+        comet_url="https://www.comet.com/username/project_id/experiment_id", trainer_name="My Trainer",
+        trainer_citation="@article{my_trainer, ...}", paper_title="My Paper", paper_id="1234.56789"))
+    for piece in ("[username/my_base_model](https://huggingface.co/username/my_base_model)", "my_model",
+                  'pipeline("text-generation", model="username/my_hub_model", device="cuda")', "datasets: username/my_dataset",
+                  "](https://wandb.ai/username/project_id/runs/abcd1234)", "](https://huggingface.co/spaces/username/space_id)",
+                  "](https://www.comet.com/username/project_id/experiment_id", "My Trainer",
+                  "```bibtex\n@article{my_trainer, ...}\n```", "[My Paper](https://huggingface.co/papers/1234.56789)",
+                  "- trainer-tag"):
+        assert piece in text, piece
+    bare = str(generate_model_card(base_model=None, model_name="my_model", hub_model_id="username/my_hub_model", dataset_name=None,
+                                   tags=[], wandb_url=None, trackio_url=None, comet_url=None, trainer_name="My Trainer",
+                                   trainer_citation=None, paper_title=None, paper_id=None))
+    assert "my_model" in bare and "My Trainer" in bare and "wandb" not in bare and "None" not in bare
+    assert 'pipeline("text-generation", model="username/my_hub_model", device="cuda")' in bare

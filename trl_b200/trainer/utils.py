@@ -513,7 +513,7 @@ def maybe_gather_lm_head_ctx(model, engine=None):
 
 def generate_model_card(base_model=None, model_name="model", hub_model_id=None, dataset_name=None, tags=None,
                         trainer_name="Trainer", trainer_citation=None, template_file="lm_model_card.md", paper_title=None,
-                        paper_id=None, wandb_url=None, comet_url=None, **_):
+                        paper_id=None, wandb_url=None, comet_url=None, trackio_url=None, **_):
     """Renders ``trl_b200/templates/<template_file>`` (counterpart of trl/trainer/utils.py:280-411); returns the text."""
     import os
     import sys
@@ -535,7 +535,7 @@ def generate_model_card(base_model=None, model_name="model", hub_model_id=None, 
     return template.render(card_data="\n".join(c for c in card if c), model_name=model_name, base_model=base_model,
                            hub_model_id=hub_model_id or model_name, dataset_name=dataset_name, trainer_name=trainer_name,
                            trainer_citation=trainer_citation, paper_title=paper_title, paper_id=paper_id,
-                           versions=versions, wandb_url=wandb_url, comet_url=comet_url)
+                           versions=versions, wandb_url=wandb_url, comet_url=comet_url, trackio_url=trackio_url)
 
 
 # ---- small helpers kept for API compatibility (trl/trainer/utils.py) ----------------------------------------------------
