@@ -245,3 +245,38 @@ def test_export_merged_weights_gives_a_plain_model_equal_to_the_adapted_one():
         base = model(input_ids=ids).logits
         model.set_adapter_enabled(True)
     assert torch.allclose(got, want, atol=2e-5) and (want - base).abs().max() > 1e-3
+
+
+def test_use_adapter_disables_and_restores():
+    """`use_adapter(model, None)` runs the base model and puts the adapter back; naming the active adapter is a no-op
+    (the checks of tests/test_utils.py:66-95 on the native LoRA model)."""
+    import pytest
+
+    from trl_b200.models.lora import LoraConfig, get_peft_model
+    from trl_b200.testing import make_tiny_model
+    from trl_b200.trainer.utils import use_adapter
+
+    torch.manual_seed(0)
+    base = make_tiny_model(seed=0).eval()
+    model = get_peft_model(make_tiny_model(seed=0), LoraConfig(r=4, lora_alpha=8, target_modules=["q_proj", "v_proj"]),
+                           adapter_name="my_adapter").eval()
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if "lora" in n and n.endswith("B"):
+                p.normal_(0, 0.05)  # a fresh adapter is the identity: make it matter
+    ids = torch.tensor([[1, 2, 3], [4, 5, 6]])
+    with torch.no_grad():
+        adapted = model(input_ids=ids).logits
+        plain = base(input_ids=ids).logits
+        assert not torch.allclose(adapted, plain)
+        with use_adapter(model, None):
+            assert torch.equal(model(input_ids=ids).logits, plain)
+        assert torch.equal(model(input_ids=ids).logits, adapted)
+        with use_adapter(model, "my_adapter"):
+            assert torch.equal(model(input_ids=ids).logits, adapted)
+        assert torch.equal(model(input_ids=ids).logits, adapted)
+    with pytest.raises(NotImplementedError):
+        with use_adapter(model, "another"):
+            pass
+    with use_adapter(base, None):  # a model without adapters passes through
+        pass

@@ -350,6 +350,12 @@ def use_adapter(model, adapter_name: str | None):
             model.set_adapter_enabled(True)
     else:
         prev = getattr(model, "active_adapter", "default")
+        if adapter_name == prev and not hasattr(model, "set_adapter"):
+            yield  # the model's one adapter is the active one already
+            return
+        if not hasattr(model, "set_adapter"):
+            raise NotImplementedError(f"adapter {adapter_name!r}: native models carry one adapter ({prev!r}); a second set "
+                                      "of adapter weights (for example a separate reference adapter) is not supported")
         model.set_adapter(adapter_name)
         try:
             yield
