@@ -280,3 +280,18 @@ def test_use_adapter_disables_and_restores():
             pass
     with use_adapter(base, None):  # a model without adapters passes through
         pass
+
+
+def test_get_peft_config_from_model_config():
+    """tests/test_utils.py:253-283: nothing without `use_peft`; otherwise every `lora_*` field arrives in the LoraConfig."""
+    from trl_b200 import ModelConfig
+    from trl_b200.models.lora import LoraConfig
+    from trl_b200.trainer.utils import get_peft_config
+
+    assert get_peft_config(ModelConfig(use_peft=False)) is None
+    kw = {"lora_r": 8, "lora_alpha": 16, "lora_dropout": 0.1, "lora_task_type": "SEQ_CLS", "use_rslora": True,
+          "lora_target_modules": ["up_proj", "down_proj"], "lora_modules_to_save": ["up_proj"]}
+    cfg = get_peft_config(ModelConfig(use_peft=True, **kw))
+    assert isinstance(cfg, LoraConfig)
+    assert (cfg.r, cfg.lora_alpha, cfg.lora_dropout, cfg.task_type, cfg.use_rslora) == (8, 16, 0.1, "SEQ_CLS", True)
+    assert set(cfg.target_modules) == {"up_proj", "down_proj"} and list(cfg.modules_to_save) == ["up_proj"]
