@@ -111,3 +111,66 @@ def test_apply_chat_template_variants(tiny_tokenizer):
     assert pref["chosen"].startswith("is good") and pref["rejected"].startswith("no")
     with pytest.raises(KeyError):
         apply_chat_template({"prompt": p, "messages": p}, tok)
+
+
+def test_prepare_multimodal_messages_cases():
+    """The cases of tests/test_data_utils.py:48-270: images go to the first user turn, strings become text blocks,
+    prepared turns keep their blocks (placeholders are filled), tool-call turns pass through."""
+    from PIL import Image
+
+    from trl_b200.data_utils import prepare_multimodal_messages
+
+    img = Image.new("RGB", (10, 10), color="blue")
+    user = lambda *blocks: {"role": "user", "content": list(blocks)}                 # noqa: E731
+    txt = lambda s: {"type": "text", "text": s}                                      # noqa: E731
+    out = prepare_multimodal_messages([{"role": "user", "content": "What color is the sky?"},
+                                       {"role": "assistant", "content": "It is blue."},
+                                       {"role": "user", "content": "How about the grass?"}], images=[img])
+    assert out == [user({"type": "image", "image": img}, txt("What color is the sky?")),
+                   {"role": "assistant", "content": [txt("It is blue.")]}, user(txt("How about the grass?"))]
+    imgs = [Image.new("RGB", (10, 10), color=c) for c in ("red", "green", "blue")]
+    out = prepare_multimodal_messages([{"role": "user", "content": "q"}, {"role": "assistant", "content": "a"}], images=imgs)
+    assert out[0] == user(*[{"type": "image", "image": i} for i in imgs], txt("q"))
+    out = prepare_multimodal_messages([{"role": "system", "content": "You are a helpful assistant"},
+                                       {"role": "user", "content": "q"}], images=[img])
+    assert out == [{"role": "system", "content": [txt("You are a helpful assistant")]}, user({"type": "image", "image": img}, txt("q"))]
+    # already prepared: the image placeholder is filled, nothing else changes
+    prepared = [{"role": "system", "content": [txt("s")]}, user({"type": "image"}, txt("q")),
+                {"role": "assistant", "content": [txt("a")]}]
+    assert prepare_multimodal_messages(prepared, images=[img]) == [
+        {"role": "system", "content": [txt("s")]}, user({"type": "image", "image": img}, txt("q")),
+        {"role": "assistant", "content": [txt("a")]}]
+    mixed = [{"role": "user", "content": "q1"}, {"role": "assistant", "content": [txt("a")]}, {"role": "user", "content": "q2"}]
+    assert prepare_multimodal_messages(mixed, images=[img]) == [user({"type": "image", "image": img}, txt("q1")),
+                                                                {"role": "assistant", "content": [txt("a")]}, user(txt("q2"))]
+    call = {"role": "assistant", "tool_calls": [{"type": "tool", "function": {"name": "get_current_weather",
+                                                                               "arguments": {"location": "New York"}}}]}
+    out = prepare_multimodal_messages([{"role": "user", "content": "weather?"}, call,
+                                       {"role": "tool", "name": "get_current_weather", "content": "22.0"},
+                                       {"role": "assistant", "content": "22 degrees."}])
+    assert out == [user(txt("weather?")), call, {"role": "tool", "name": "get_current_weather", "content": [txt("22.0")]},
+                   {"role": "assistant", "content": [txt("22 degrees.")]}]
+    keep = [user({"type": "image", "image": img}, txt("q")), {"role": "assistant", "content": "a"}]
+    assert prepare_multimodal_messages(keep) == [user({"type": "image", "image": img}, txt("q")),
+                                                 {"role": "assistant", "content": [txt("a")]}]
+
+
+def test_prepare_multimodal_messages_vllm_cases():
+    import copy
+
+    from PIL import Image
+
+    from trl_b200.data_utils import prepare_multimodal_messages_vllm
+
+    img = Image.new("RGB", (10, 10), color="blue")
+    msgs = [{"role": "user", "content": [{"type": "text", "text": "q"}, {"type": "image", "image": img}]},
+            {"role": "assistant", "content": [{"type": "text", "text": "It is blue."}]}]
+    original = copy.deepcopy(msgs)
+    out = prepare_multimodal_messages_vllm(msgs)
+    assert msgs == original                                                  # the input is not touched
+    assert out[0]["content"][0]["type"] == "text" and out[0]["content"][1]["type"] == "image_pil"
+    assert "image" not in out[0]["content"][1] and isinstance(out[0]["content"][1]["image_pil"], Image.Image)
+    assert out[1]["content"][0] == {"type": "text", "text": "It is blue."}
+    plain = [{"role": "user", "content": [{"type": "text", "text": "q"}]}]
+    res = prepare_multimodal_messages_vllm(plain)
+    assert res == plain and res is not plain and res[0] is not plain[0]

@@ -42,9 +42,10 @@ def prepare_multimodal_messages(messages: list[dict], images: list | None = None
                 placed = True
             else:
                 m["content"] = [{"type": "text", "text": c}]
-        elif c is None:
-            m["content"] = []
-    slots = [b for m in out for b in (m["content"] or []) if b.get("type") == "image"]
+    # placeholders still to fill: image blocks that carry no payload yet (turns without content, such as an assistant
+    # turn that only holds tool calls, stay as they are)
+    slots = [b for m in out for b in (m.get("content") or []) if isinstance(b, dict) and b.get("type") == "image"
+             and b.get("image") is None]
     if len(slots) != len(images):
         raise ValueError(f"Number of images provided ({len(images)}) does not match number of image placeholders ({len(slots)}).")
     for b, img in zip(slots, images):
