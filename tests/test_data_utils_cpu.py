@@ -174,3 +174,59 @@ def test_prepare_multimodal_messages_vllm_cases():
     plain = [{"role": "user", "content": [{"type": "text", "text": "q"}]}]
     res = prepare_multimodal_messages_vllm(plain)
     assert res == plain and res is not plain and res[0] is not plain[0]
+
+
+def test_unpair_preference_dataset_cases():
+    """tests/test_data_utils.py:1008-1107: map-style, iterable, dataset dict, extra columns, already unpaired."""
+    from datasets import Dataset, DatasetDict
+
+    from trl_b200.data_utils import maybe_unpair_preference_dataset, unpair_preference_dataset
+
+    paired = Dataset.from_dict({"prompt": ["The sky is", "The sun is"], "chosen": [" blue.", " in the sky."],
+                                "rejected": [" green.", " in the sea."]})
+    want = {"prompt": ["The sky is", "The sun is", "The sky is", "The sun is"],
+            "completion": [" blue.", " in the sky.", " green.", " in the sea."], "label": [True, True, False, False]}
+    assert unpair_preference_dataset(paired).to_dict() == want
+    extra = Dataset.from_dict({**paired.to_dict(), "extra": [1, 2]})
+    assert unpair_preference_dataset(extra).to_dict() == {**want, "extra": [1, 2, 1, 2]}
+    rows = list(unpair_preference_dataset(paired.to_iterable_dataset()))
+    assert rows == [dict(zip(want, vals)) for vals in zip(*want.values())]
+    rows = list(unpair_preference_dataset(extra.to_iterable_dataset()))
+    want_x = {**want, "extra": [1, 2, 1, 2]}
+    assert rows == [dict(zip(want_x, vals)) for vals in zip(*want_x.values())]
+    assert unpair_preference_dataset(DatasetDict({"abc": paired}))["abc"].to_dict() == want
+    assert maybe_unpair_preference_dataset(paired).to_dict() == want
+    assert maybe_unpair_preference_dataset(DatasetDict({"abc": paired}))["abc"].to_dict() == want
+    unpaired = Dataset.from_dict(want)
+    assert maybe_unpair_preference_dataset(unpaired).to_dict() == want
+    assert maybe_unpair_preference_dataset(DatasetDict({"abc": unpaired}))["abc"].to_dict() == want
+
+
+def test_extract_prompt_cases_and_is_conversational():
+    from trl_b200.data_utils import (extract_prompt, is_conversational, is_conversational_from_value, maybe_extract_prompt)
+
+    implicit = {"chosen": [{"role": "user", "content": "What color is the sky?"}, {"role": "assistant", "content": "It is blue."}],
+                "rejected": [{"role": "user", "content": "What color is the sky?"}, {"role": "assistant", "content": "It is green."}]}
+    explicit = {"prompt": [{"role": "user", "content": "What color is the sky?"}],
+                "chosen": [{"role": "assistant", "content": "It is blue."}],
+                "rejected": [{"role": "assistant", "content": "It is green."}]}
+    assert extract_prompt(implicit) == explicit and maybe_extract_prompt(implicit) == explicit
+    assert maybe_extract_prompt(explicit) == explicit
+    std_implicit, std_explicit = {"chosen": "The sky is blue.", "rejected": "The sky is green."}, \
+        {"prompt": "The sky is", "chosen": " blue.", "rejected": " green."}
+    assert extract_prompt(std_implicit) == std_explicit and maybe_extract_prompt(std_implicit) == std_explicit
+    assert maybe_extract_prompt(std_explicit) == std_explicit
+    sky = [{"role": "user", "content": "What color is the sky?"}]
+    think = {"role": "assistant", "thinking": "The user asks the color of the sky...", "content": "It is blue."}
+    call = {"role": "assistant", "tool_calls": [{"type": "function", "function": {"name": "get_color", "arguments": {"what": "sky"}}}]}
+    for ex in ({"messages": sky + [{"role": "assistant", "content": "It is blue."}]}, {"prompt": sky},
+               {"prompt": sky, "completion": [{"role": "assistant", "content": "It is blue."}]}, explicit, implicit,
+               {"prompt": sky, "chosen": [call, {"role": "tool", "name": "get_color", "content": "blue"}], "rejected": [call]},
+               {"prompt": sky, "completion": [think], "label": True},
+               {"messages": [{"role": "system", "content": "Respond in a friendly manner."}] + sky + [think]}):
+        assert is_conversational(ex), ex
+    for ex in ({"prompt": "The sky is", "completion": " blue."}, {"text": "The sky is blue."}, {"prompt": "The sky is"},
+               std_explicit, {"prompt": "The sky is", "completion": " blue.", "label": True}):
+        assert not is_conversational(ex), ex
+    assert is_conversational_from_value({"conversations": [{"from": "user", "value": "q"}, {"from": "assistant", "value": "a"}]})
+    assert not is_conversational_from_value({"messages": sky}) and not is_conversational_from_value({"text": "x"})

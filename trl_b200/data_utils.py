@@ -197,8 +197,9 @@ def _map(dataset, fn, batched=False, remove_columns=None, **kw):
 def _unpair_batch(batch: dict[str, list]) -> dict[str, list]:
     n = len(batch["chosen"])
     res = {"completion": list(batch["chosen"]) + list(batch["rejected"]), "label": [True] * n + [False] * n}
-    if "prompt" in batch:
-        res["prompt"] = list(batch["prompt"]) * 2
+    for name, col in batch.items():  # the prompt and every extra column ride along with both halves
+        if name not in ("chosen", "rejected"):
+            res[name] = list(col) * 2
     return res
 
 
