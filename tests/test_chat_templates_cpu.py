@@ -104,3 +104,59 @@ def test_malformed_calls_fall_back_to_plain_text():
     add_response_schema(tok2, family="lfm2")
     bad2 = "<|tool_call_start|>[multiply(a=3,]<|tool_call_end|>"
     assert parse_response(tok2, bad2)["content"] == bad2
+
+
+_TURNS = ("{%- for m in messages %}{%- if m.role == 'user' %}{{- '<|im_start|>user\\n' + m.content + '<|im_end|>\\n' }}"
+          "{%- elif m.role == 'tool' %}{{- '<|im_start|>tool\\n' + m.content + '<|im_end|>\\n' }}"
+          "{%- elif m.role == 'assistant' %}ASSISTANT{%- endif %}{%- endfor %}"
+          "{%- if add_generation_prompt %}{{- '<|im_start|>assistant\\n' }}{%- endif %}")
+_CALLS = ("{%- if m.tool_calls %}{%- for c in m.tool_calls %}{%- if c.function %}{%- set c = c.function %}{%- endif %}"
+          "{{- '<tool_call>' + c.name + '</tool_call>' }}{%- endfor %}{%- endif %}")
+
+
+def test_prefix_preservation_and_stop_token_probes_on_handwritten_templates():
+    """The behaviours of tests/test_chat_template_utils.py:394-596: a template whose earlier turns never change when a
+    tool turn is appended is prefix-preserving, one that renders a think block only for the last assistant turn is not;
+    the end-of-turn token counts as trained only when it lies inside the generation span; a template that raises reads
+    as not trained."""
+    from trl_b200.chat_template_utils import is_chat_template_prefix_preserving, is_chat_template_stop_token_trained
+    from trl_b200.testing import make_tiny_tokenizer
+
+    tok = make_tiny_tokenizer()
+    plain = "{{- '<|im_start|>assistant\\n' + (m.content or '') }}" + _CALLS + "{{- '<|im_end|>\\n' }}"
+    tok.chat_template = _TURNS.replace("ASSISTANT", plain)
+    assert is_chat_template_prefix_preserving(tok) is True
+    last_only = ("{%- if loop.last %}{{- '<|im_start|>assistant\\n<think>\\n\\n</think>\\n\\n' + (m.content or '') }}"
+                 "{%- else %}{{- '<|im_start|>assistant\\n' + (m.content or '') }}{%- endif %}" + _CALLS + "{{- '<|im_end|>\\n' }}")
+    tok.chat_template = _TURNS.replace("ASSISTANT", last_only)
+    assert is_chat_template_prefix_preserving(tok) is False
+
+    inside = "{{- '<|im_start|>assistant\\n' }}{%- generation %}{{- m.content + '<|im_end|>' }}{%- endgeneration %}{{- '\\n' }}"
+    tok.chat_template = _TURNS.replace("ASSISTANT", inside)
+    assert is_chat_template_stop_token_trained(tok) is True
+    outside = "{{- '<|im_start|>assistant\\n' }}{%- generation %}{{- m.content }}{%- endgeneration %}{{- '<|im_end|>\\n' }}"
+    tok.chat_template = _TURNS.replace("ASSISTANT", outside)
+    assert is_chat_template_stop_token_trained(tok) is False
+    tok.chat_template = "{{ raise_exception('probe rejected') }}"
+    assert is_chat_template_stop_token_trained(tok) is False
+
+
+@pytest.mark.parametrize("family", [f[0] for f in _FAMILIES if f[0] not in NO_TOOL_SYNTAX])
+def test_parse_response_never_raises_on_a_truncated_tool_call_turn(family):
+    """tests/test_chat_template_utils.py:1301-1330: a completion cut anywhere inside a tool call still parses to a
+    message (as text when the call is incomplete)."""
+    tok = _tok(family)
+    before = tok.apply_chat_template(CONV[:4], tokenize=False, tools=TOOLS)
+    upto = tok.apply_chat_template(CONV[:5], tokenize=False, tools=TOOLS)
+    completion = upto[len(before):]
+    add_response_schema(tok, family=family)
+    for end in range(1, len(completion)):
+        msg = parse_response(tok, completion[:end])
+        assert msg["role"] == "assistant" and ("content" in msg or "tool_calls" in msg)
+
+
+def test_json_tool_call_with_a_missing_brace_stays_text():
+    tok = _tok("qwen3")
+    add_response_schema(tok, family="qwen3")
+    bad = '<tool_call>\n{"name": "multiply", "arguments": {"a": 3, "b": 4}\n</tool_call>'
+    assert parse_response(tok, bad + "<|im_end|>") == {"role": "assistant", "content": bad}

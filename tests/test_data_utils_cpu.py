@@ -230,3 +230,82 @@ def test_extract_prompt_cases_and_is_conversational():
         assert not is_conversational(ex), ex
     assert is_conversational_from_value({"conversations": [{"from": "user", "value": "q"}, {"from": "assistant", "value": "a"}]})
     assert not is_conversational_from_value({"messages": sky}) and not is_conversational_from_value({"text": "x"})
+
+
+def test_pack_dataset_reference_vectors():
+    """tests/test_data_utils.py:1184-1325: wrapped / bfd / bfd_split on map-style and iterable datasets; the dataset's
+    format survives, seq_lengths is added to the formatted columns."""
+    from datasets import Dataset
+
+    from trl_b200.data_utils import pack_dataset
+
+    ex = {"input_ids": [[1, 2, 3], [4, 5, 6, 7], [8]], "attention_mask": [[0, 1, 1], [0, 0, 1, 1], [1]]}
+    want = {"input_ids": [[1, 2, 3], [4, 5, 6], [7, 8]], "attention_mask": [[0, 1, 1], [0, 0, 1], [1, 1]]}
+    ds = Dataset.from_dict(ex).with_format("numpy", dtype="float32")
+    fmt = ds.format
+    out = pack_dataset(ds, 3, strategy="wrapped")
+    assert out.to_dict() == want and out.format == fmt
+    it = Dataset.from_dict(ex).to_iterable_dataset().with_format("numpy")
+    out = pack_dataset(it, 3, strategy="wrapped")
+    assert next(iter(out.with_format(None).batch(batch_size=3))) == want
+    assert out._formatting == it._formatting
+
+    ex = {"input_ids": [[1, 2, 3], [4, 5, 6, 7], [8]]}
+    want = {"input_ids": [[4, 5, 6, 7], [1, 2, 3, 8]], "seq_lengths": [[4], [3, 1]]}
+    ds = Dataset.from_dict(ex).with_format("numpy", dtype="float32")
+    fmt = ds.format
+    out = pack_dataset(ds, 4, strategy="bfd")
+    got_fmt = out.format
+    assert out.to_dict() == want and "seq_lengths" in got_fmt["columns"]
+    got_fmt["columns"].remove("seq_lengths")
+    assert got_fmt == fmt
+    it = Dataset.from_dict(ex).to_iterable_dataset().with_format("numpy")
+    out = pack_dataset(it, 4, strategy="bfd")
+    assert next(iter(out.with_format(None).batch(batch_size=3))) == want
+
+    cases = [
+        ({"input_ids": [[1, 2, 3, 4, 5], [6, 7], [8, 9, 10, 11], [12]]}, 4, "bfd_split",
+         {"input_ids": [[1, 2, 3, 4], [8, 9, 10, 11], [6, 7, 5, 12]], "seq_lengths": [[4], [4], [2, 1, 1]]}),
+        ({"col1": [[1, -2, 3, -4, 5, -6], [7, -8, 9], [-10, 11, -12], [13, -14, 15, -16]],
+          "col2": [[-1, 2, -3, 4, -5, 6], [-7, 8, -9], [10, -11, 12], [-13, 14, -15, 16]]}, 4, "bfd_split",
+         {"col1": [[1, -2, 3, -4], [13, -14, 15, -16], [7, -8, 9], [-10, 11, -12], [5, -6]],
+          "col2": [[-1, 2, -3, 4], [-13, 14, -15, 16], [-7, 8, -9], [10, -11, 12], [-5, 6]],
+          "seq_lengths": [[4], [4], [3], [3], [2]]}),
+        ({"input_ids": [[1, 2, 3, 4, 5], [6], [7, 8, 9, 10], [11, 12, 13]]}, 5, "bfd_split",
+         {"input_ids": [[1, 2, 3, 4, 5], [7, 8, 9, 10, 6], [11, 12, 13]], "seq_lengths": [[5], [4, 1], [3]]}),
+        ({"input_ids": [[1, 2, 3, 4, 5], [6, 7], [8, 9, 10, 11], [12]]}, 4, "bfd",
+         {"input_ids": [[1, 2, 3, 4], [8, 9, 10, 11], [6, 7, 12]], "seq_lengths": [[4], [4], [2, 1]]}),
+        ({"input_ids": [[1, 2], [], [3, 4, 5], [], [6]]}, 4, "bfd_split",
+         {"input_ids": [[3, 4, 5, 6], [1, 2]], "seq_lengths": [[3, 1], [2]]}),
+    ]
+    for ex, L, strat, want in cases:
+        assert pack_dataset(Dataset.from_dict(ex), L, strategy=strat).to_dict() == want, (ex, strat)
+
+
+def test_maybe_convert_to_chatml_cases():
+    from trl_b200.data_utils import maybe_convert_to_chatml
+
+    msgs = [{"role": "user", "content": "What color is the sky?"}, {"role": "assistant", "content": "It is blue."}]
+    raw = [{"from": "user", "value": "What color is the sky?"}, {"from": "assistant", "value": "It is blue."}]
+    assert maybe_convert_to_chatml({"conversations": raw}) == {"messages": msgs}
+    assert maybe_convert_to_chatml({"prompt": raw[:1], "completion": raw[1:]}) == {"prompt": msgs[:1], "completion": msgs[1:]}
+    assert maybe_convert_to_chatml({"text": "The sky is blue."}) == {"text": "The sky is blue."}
+    assert maybe_convert_to_chatml({"messages": msgs}) == {"messages": msgs}
+
+
+def test_apply_chat_template_generation_prompt_that_inserts_text_round_trips():
+    """tests/test_data_utils.py:723-748: the completions are cut against the final (shortest) prompt, so a tag opened by
+    the generation prompt stays with the completion that keeps it."""
+    from trl_b200.data_utils import apply_chat_template
+    from trl_b200.testing import make_tiny_tokenizer
+
+    tok = make_tiny_tokenizer()
+    tok.chat_template = ("{% for message in messages %}{{ message['role'] + ': ' + message['content'] + '\n' }}{% endfor %}"
+                         "{% if add_generation_prompt %}{{ 'assistant: <think>' }}{% endif %}")
+    ex = {"prompt": [{"role": "user", "content": "What is 2+2?"}],
+          "chosen": [{"role": "assistant", "content": "<think>2+2=4</think>It is 4."}],
+          "rejected": [{"role": "assistant", "content": "It is 4."}]}
+    out = apply_chat_template(ex, tok)
+    assert out["prompt"] + out["chosen"] == tok.apply_chat_template(ex["prompt"] + ex["chosen"], tokenize=False)
+    assert out["prompt"] + out["rejected"] == tok.apply_chat_template(ex["prompt"] + ex["rejected"], tokenize=False)
+    assert out["chosen"].startswith("<think>")
