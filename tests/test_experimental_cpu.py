@@ -509,3 +509,30 @@ def test_experimental_utils(tiny_tokenizer):
     assert per_tok.shape == (2, 6) and lens.tolist() == [5, 3] and torch.allclose(score[1], per_tok[1, 3])
     ref = U.create_reference_model(make_tiny_model(), num_shared_layers=1)
     assert not any(p.requires_grad for p in ref.parameters())
+
+
+def test_bema_refreshes_the_dpo_reference_model(tmp_path, tiny_tokenizer):
+    """trl/experimental/bema_for_ref_model: the reference model receives the running BEMA weights every
+    ``ref_model_update_freq`` steps after ``ref_model_update_after``; without ``update_ref_model`` it stays frozen."""
+    from trl_b200 import DPOConfig
+    from trl_b200.experimental.bema_for_ref_model import BEMACallback, DPOTrainer
+
+    def run(sub, **kw):
+        cb = BEMACallback(update_freq=2, **kw)
+        model = make_tiny_model("tiny-qwen2", seed=0)
+        cfg = DPOConfig(output_dir=str(tmp_path / sub), per_device_train_batch_size=4, max_steps=6, learning_rate=1e-3,
+                        save_strategy="no", report_to="none", use_cpu=True, bf16=False, logging_steps=100)
+        tr = DPOTrainer(model, None, cfg, train_dataset=make_dataset("standard_preference", 24),
+                        processing_class=tiny_tokenizer, callbacks=[cb])
+        ref0 = {n: p.detach().clone() for n, p in tr.ref_model.named_parameters()}
+        tr.train()
+        return cb, tr, ref0
+
+    cb, tr, ref0 = run("on", update_ref_model=True, ref_model_update_freq=3, ref_model_update_after=0)
+    ref = dict(tr.ref_model.named_parameters())
+    name = cb.names[len(cb.names) // 2]
+    assert not torch.equal(ref[name], ref0[name])
+    # steps 3 and 6 copied the running weights; the last BEMA update (step 6) came first in the same callback
+    assert torch.allclose(ref[name].detach().float(), cb.running[cb.names.index(name)], atol=1e-6)
+    cb, tr, ref0 = run("off")
+    assert all(torch.equal(p, ref0[n]) for n, p in tr.ref_model.named_parameters())

@@ -730,3 +730,47 @@ def test_sft_evaluation_with_compute_metrics(tmp_path, tiny_tokenizer):
     out = tr.evaluate()
     assert "eval_token_accuracy" in out and 0.0 <= out["eval_token_accuracy"] <= 1.0 and "eval_loss" in out
     assert seen["pred"] == seen["lab"] and seen["pred"][0] == 6 and seen["pred"][1] >= 12
+
+
+def test_bema_callback_schedule_weights_and_saved_model(tmp_path, tiny_tokenizer):
+    """tests/test_callbacks.py:120-240: theta_0 restarts at ``update_after``, updates run every ``update_freq`` steps
+    after it with the global step in beta/alpha, and ``output_dir/bema`` holds the running weights."""
+    from unittest.mock import call, patch
+
+    from trl_b200 import BEMACallback, load_model
+
+    def run(cb, sub, patched=True):
+        model = make_tiny_model("tiny-qwen2", seed=0)
+        cfg = SFTConfig(output_dir=str(tmp_path / sub), per_device_train_batch_size=8, max_steps=9, learning_rate=1e-3,
+                        save_strategy="no", report_to="none", use_cpu=True, bf16=False, logging_steps=100)
+        tr = SFTTrainer(model, cfg, train_dataset=make_dataset("standard_language_modeling", 24), processing_class=tiny_tokenizer,
+                        callbacks=[cb])
+        if patched:
+            with patch.object(cb, "_update_bema_weights") as m:
+                tr.train()
+            return m.call_args_list
+        tr.train()
+        return model
+
+    assert run(BEMACallback(update_freq=2), "a") == [call(2), call(4), call(6), call(8)]
+    assert run(BEMACallback(update_freq=3), "b") == [call(3), call(6), call(9)]
+    assert run(BEMACallback(update_freq=2, update_after=3), "c") == [call(5), call(7), call(9)]
+
+    cb = BEMACallback(update_freq=2, lag=10, multiplier=1.0)
+    assert cb._ema_beta(6) == pytest.approx(16 ** -0.5) and cb._bema_alpha(6) == pytest.approx(16 ** -0.2)
+    assert BEMACallback(min_ema_multiplier=0.9)._ema_beta(100) == 0.9
+    theta0 = _snap(make_tiny_model("tiny-qwen2", seed=0))
+    model = run(cb, "d", patched=False)
+    saved = load_model(str(tmp_path / "d" / "bema"), dtype="float32")
+    trained, bema = dict(model.named_parameters()), dict(saved.named_parameters())
+    name = "layers.0.mlp.gate_proj.weight" if "layers.0.mlp.gate_proj.weight" in trained else next(iter(trained))
+    assert not torch.equal(bema[name], trained[name].detach()) and not torch.equal(bema[name], theta0[name])
+    # last update was at step 8, so the saved weights follow e_8 + alpha_8 (theta_8 - theta_0), not theta_9
+    assert torch.allclose(cb.running[cb.names.index(name)], bema[name].detach().float(), atol=1e-6)
+    for kw in (dict(bias_power=0.0), dict(ema_power=0.0)):
+        run(BEMACallback(update_freq=2, **kw), "e" + str(len(kw)) + next(iter(kw)), patched=False)
+    # a run too short for any update still writes the (initial) weights
+    cb = BEMACallback(update_freq=400)
+    run(cb, "f", patched=False)
+    first = load_model(str(tmp_path / "f" / "bema"), dtype="float32")
+    assert torch.allclose(dict(first.named_parameters())[name].detach(), theta0[name], atol=1e-6)

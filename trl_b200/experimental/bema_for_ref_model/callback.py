@@ -13,7 +13,8 @@ class BEMACallback(_BEMA):
     def __init__(self, *a, update_ref_model: bool = False, ref_model_update_freq: int = 400,
                  ref_model_update_after: int = 0, **kw):
         super().__init__(*a, **kw)
-        self.update_ref_model, self.ref_freq, self.ref_after = update_ref_model, ref_model_update_freq, ref_model_update_after
+        self.update_ref_model = update_ref_model
+        self.ref_model_update_freq, self.ref_model_update_after = ref_model_update_freq, ref_model_update_after
         self.ref_model = None
 
     def attach(self, ref_model):
@@ -22,8 +23,10 @@ class BEMACallback(_BEMA):
     @torch.no_grad()
     def on_step_end(self, args, state, control, model=None, **kw):
         super().on_step_end(args, state, control, model=model, **kw)
+        step = state.global_step
         if (self.update_ref_model and self.ref_model is not None and self.running is not None
-                and state.global_step >= self.ref_after and state.global_step % self.ref_freq == 0):
+                and step >= self.ref_model_update_after
+                and (step - self.ref_model_update_after) % self.ref_model_update_freq == 0):
             named = dict(self.ref_model.named_parameters())
             for n, w in zip(self.names, self.running):
                 if n in named:

@@ -126,35 +126,45 @@ class BEMACallback(TrainerCallback):
         self.update_freq, self.ema_power, self.bias_power = update_freq, ema_power, bias_power
         self.lag, self.update_after, self.multiplier, self.min_ema_multiplier = lag, update_after, multiplier, min_ema_multiplier
         self.device = device
-        self.theta0, self.ema, self.running = None, None, None
+        self.theta0, self.ema, self.running, self._model = None, None, None, None
 
     @torch.no_grad()
     def on_train_begin(self, args, state, control, model=None, **kw):
         self.names = [n for n, p in model.named_parameters() if p.requires_grad]
+        self.theta0 = self._snapshot(model)  # theta_0 and the EMA start at the initial weights
+        self.ema = [t.clone() for t in self.theta0]
+        self.running = [t.clone() for t in self.theta0]
 
     @torch.no_grad()
     def _snapshot(self, model):
         return [p.detach().to(self.device, torch.float32).clone() for n, p in model.named_parameters() if n in self.names]
+
+    def _ema_beta(self, step: int) -> float:
+        """beta_t = (lag + multiplier * t)^(-ema_power), floored at ``min_ema_multiplier``."""
+        return max((self.lag + self.multiplier * step) ** (-self.ema_power), self.min_ema_multiplier)
+
+    def _bema_alpha(self, step: int) -> float:
+        """alpha_t = (lag + multiplier * t)^(-bias_power)."""
+        return (self.lag + self.multiplier * step) ** (-self.bias_power)
+
+    @torch.no_grad()
+    def _update_bema_weights(self, step: int):
+        beta, alpha = self._ema_beta(step), self._bema_alpha(step)
+        for e, r, c, z in zip(self.ema, self.running, self._snapshot(self._model), self.theta0):
+            e.mul_(1 - beta).add_(c, alpha=beta)
+            r.copy_(e + alpha * (c - z))
 
     @torch.no_grad()
     def on_step_end(self, args, state, control, model=None, **kw):
         step = state.global_step
         if step < self.update_after:
             return
-        if self.theta0 is None:
+        self._model = model
+        if step == self.update_after:  # restart theta_0 and the EMA from the weights of this step
             self.theta0 = self._snapshot(model)
             self.ema = [t.clone() for t in self.theta0]
-            self.running = [t.clone() for t in self.theta0]
-            return
-        if (step - self.update_after) % self.update_freq != 0:
-            return
-        t = step - self.update_after
-        beta = max((1 + self.multiplier * t / max(self.lag, 1)) ** (-self.ema_power), self.min_ema_multiplier)
-        alpha = (1 + self.multiplier * t / max(self.lag, 1)) ** (-self.bias_power)
-        cur = self._snapshot(model)
-        for e, r, c, z in zip(self.ema, self.running, cur, self.theta0):
-            e.mul_(1 - beta).add_(c, alpha=beta)
-            r.copy_(alpha * (c - z) + e)
+        elif (step - self.update_after) % self.update_freq == 0:
+            self._update_bema_weights(step)
 
     @torch.no_grad()
     def on_train_end(self, args, state, control, model=None, **kw):
