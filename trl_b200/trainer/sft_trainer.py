@@ -38,10 +38,11 @@ class DataCollatorForLanguageModeling:
     def __call__(self, examples: list[dict[str, Any]]) -> dict[str, Any]:
         ids = [torch.as_tensor(e["input_ids"], dtype=torch.long) for e in examples]
         labels = [torch.as_tensor(e.get("labels", e["input_ids"]), dtype=torch.long).clone() for e in examples]
-        if self.completion_only_loss and "completion_mask" in examples[0]:
+        given = "labels" in examples[0]  # labels that come with the rows are final: mask columns beside them are ignored
+        if not given and self.completion_only_loss and "completion_mask" in examples[0]:
             for l, e in zip(labels, examples):
                 l[torch.as_tensor(e["completion_mask"]) == 0] = -100
-        if "assistant_masks" in examples[0]:
+        if not given and "assistant_masks" in examples[0]:
             for l, e in zip(labels, examples):
                 l[torch.as_tensor(e["assistant_masks"]) == 0] = -100
         out = {}
