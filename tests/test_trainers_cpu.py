@@ -774,3 +774,17 @@ def test_bema_callback_schedule_weights_and_saved_model(tmp_path, tiny_tokenizer
     run(cb, "f", patched=False)
     first = load_model(str(tmp_path / "f" / "bema"), dtype="float32")
     assert torch.allclose(dict(first.named_parameters())[name].detach(), theta0[name], atol=1e-6)
+
+
+def test_sft_rejects_a_dataset_with_transform_unless_preparation_is_skipped(tmp_path, tiny_tokenizer):
+    """tests/test_sft_trainer.py:1004-1020."""
+    from datasets import Dataset
+
+    def add_suffix(batch):
+        batch["text"] = [t + " more" for t in batch["text"]]
+        return batch
+
+    ds = Dataset.from_dict({"text": ["hello world"] * 4}).with_transform(add_suffix)
+    cfg = SFTConfig(output_dir=str(tmp_path), report_to="none", use_cpu=True, bf16=False)
+    with pytest.raises(ValueError, match=r"Dataset\.with_transform\(\).*skip_prepare_dataset.*trainer-ready"):
+        SFTTrainer(make_tiny_model(), cfg, train_dataset=ds, processing_class=tiny_tokenizer)

@@ -281,6 +281,12 @@ class SFTTrainer(Trainer):
 
     # ---- dataset ---------------------------------------------------------------------------------
     def _prepare_dataset(self, dataset, tok, args: SFTConfig, packing: bool, formatting_func, name: str):
+        fmt = getattr(dataset, "format", None)
+        if isinstance(fmt, dict) and fmt.get("type") == "custom":
+            # map() would read through the transform and freeze a random or stateful transform into the token columns
+            raise ValueError("SFTTrainer cannot prepare a dataset that uses `Dataset.with_transform()`. Pass "
+                             "`dataset_kwargs={'skip_prepare_dataset': True}` and make the transform return trainer-ready "
+                             "examples (tokenized fields included), or materialize the transform with `Dataset.map()`.")
         cols = get_dataset_column_names(dataset)
         first = next(iter(dataset))
         if "input_ids" in cols:  # already tokenised
