@@ -788,3 +788,35 @@ def test_sft_rejects_a_dataset_with_transform_unless_preparation_is_skipped(tmp_
     cfg = SFTConfig(output_dir=str(tmp_path), report_to="none", use_cpu=True, bf16=False)
     with pytest.raises(ValueError, match=r"Dataset\.with_transform\(\).*skip_prepare_dataset.*trainer-ready"):
         SFTTrainer(make_tiny_model(), cfg, train_dataset=ds, processing_class=tiny_tokenizer)
+
+
+def test_dpo_drops_fully_truncated_rows_and_prepares_datasets_given_to_evaluate(tmp_path, tiny_tokenizer):
+    """tests/test_dpo_trainer.py:1126-1149 and :278-330."""
+    from datasets import Dataset
+
+    ds = Dataset.from_dict({"prompt": ["Hi", "This is a very long prompt that fills up the whole max_length budget on its own"],
+                            "chosen": [" there", " yes"], "rejected": [" bye", " no"]})
+    short = len(tiny_tokenizer("Hi")["input_ids"])
+    cfg = DPOConfig(output_dir=str(tmp_path / "a"), max_length=short + 3, truncation_mode="keep_start", report_to="none",
+                    use_cpu=True, bf16=False)
+    tr = DPOTrainer(make_tiny_model(), None, cfg, train_dataset=ds, processing_class=tiny_tokenizer)
+    assert len(tr.train_dataset) == 1 and tr.train_dataset[0]["prompt_ids"] == tiny_tokenizer("Hi")["input_ids"]
+
+    train, held_out = make_dataset("standard_preference", 16), make_dataset("standard_preference", 8)
+    cfg = DPOConfig(output_dir=str(tmp_path / "b"), max_steps=1, precompute_ref_log_probs=True, report_to="none",
+                    use_cpu=True, bf16=False, per_device_train_batch_size=4, save_strategy="no")
+    tr = DPOTrainer(make_tiny_model(), None, cfg, train_dataset=train, processing_class=tiny_tokenizer)
+    assert tr.evaluate(eval_dataset=held_out)["eval_loss"] is not None  # raw rows: tokenised and given reference log-probs
+    both = tr.evaluate(eval_dataset={"x": held_out, "y": held_out})
+    assert both["eval_x_loss"] == pytest.approx(both["eval_y_loss"])
+    tr.train()
+    with pytest.raises(ValueError, match="Cannot compute reference log-probs for a dataset passed to"):
+        tr.evaluate(eval_dataset=held_out)
+    # with an explicit reference model the same call stays legal after training
+    cfg = DPOConfig(output_dir=str(tmp_path / "c"), max_steps=1, precompute_ref_log_probs=True, report_to="none",
+                    use_cpu=True, bf16=False, per_device_train_batch_size=4, save_strategy="no")
+    tr = DPOTrainer(make_tiny_model(), make_tiny_model(), cfg, train_dataset=train, eval_dataset={"x": held_out},
+                    processing_class=tiny_tokenizer)
+    tr.train()
+    assert tr.evaluate(eval_dataset=held_out)["eval_loss"] is not None
+    assert "eval_x_loss" in tr.evaluate()

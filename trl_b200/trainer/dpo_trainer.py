@@ -209,8 +209,38 @@ class DPOTrainer(Trainer):
         self._precomputed = {"train": False, "eval": False}
         if self.precompute_ref_log_probs:
             self.train_dataset = self._precompute_ref_logps(self.train_dataset, "train")
-            if self.eval_dataset is not None and not isinstance(self.eval_dataset, dict):
+            if isinstance(self.eval_dataset, dict):
+                self.eval_dataset = {k: self._precompute_ref_logps(v, k) for k, v in self.eval_dataset.items()}
+            elif self.eval_dataset is not None:
                 self.eval_dataset = self._precompute_ref_logps(self.eval_dataset, "eval")
+
+    def evaluate(self, eval_dataset=None, ignore_keys=None, metric_key_prefix: str = "eval"):
+        """A dataset handed to ``evaluate`` gets the preparation of ``__init__`` (tokenisation, reference log-probs when
+        they are precomputed), dpo_trainer.py:1657-1713."""
+        if eval_dataset is not None and not isinstance(eval_dataset, str) and not self._is_vlm:
+            if (self.precompute_ref_log_probs and self.ref_model is None and not self._ref_adapter_off
+                    and self.state.global_step > 0):
+                raise ValueError(
+                    "Cannot compute reference log-probs for a dataset passed to `evaluate()` after training has started, "
+                    "because `precompute_ref_log_probs=True` and no `ref_model` was provided (full fine-tuning): the "
+                    "reference is the policy before training and is not kept in memory. Provide this dataset as "
+                    "`eval_dataset` at initialization, pass an explicit `ref_model`, or set "
+                    "`precompute_ref_log_probs=False`.")
+            tok = getattr(self.processing_class, "tokenizer", self.processing_class)
+            parts = eval_dataset if isinstance(eval_dataset, dict) else {"eval": eval_dataset}
+            done = {}
+            for name, ds in parts.items():
+                ds = self._prepare_dataset(ds, tok, self.args, name)
+                if self.precompute_ref_log_probs and "ref_chosen_logps" not in next(iter(ds)):
+                    ds = self._precompute_ref_logps(ds, name)
+                done[name] = ds
+            if isinstance(eval_dataset, dict):
+                out = {}
+                for name, ds in done.items():
+                    out.update(super().evaluate(ds, ignore_keys, f"{metric_key_prefix}_{name}"))
+                return out
+            eval_dataset = done["eval"]
+        return super().evaluate(eval_dataset, ignore_keys, metric_key_prefix)
 
     # ---- dataset ------------------------------------------------------------------------------------
     def _prepare_dataset(self, dataset, tok, args, name):
@@ -236,6 +266,12 @@ class DPOTrainer(Trainer):
             r = tok(text=rejected, add_special_tokens=False)["input_ids"]
             return {"prompt_ids": p, "chosen_ids": c, "rejected_ids": r}
         ds = _map(ds, tokenize)
+        if args.max_length is not None and args.truncation_mode == "keep_start":
+            # a prompt that fills max_length alone leaves no completion token after truncation: such rows are dropped
+            if hasattr(ds, "filter"):
+                ds = ds.filter(lambda ex: len(ex["prompt_ids"]) < args.max_length)
+            else:
+                ds = [r for r in ds if len(r["prompt_ids"]) < args.max_length]
         keep = {"prompt_ids", "chosen_ids", "rejected_ids", "ref_chosen_logps", "ref_rejected_logps"}
         if hasattr(ds, "remove_columns"):
             ds = ds.remove_columns([c for c in ds.column_names if c not in keep])
