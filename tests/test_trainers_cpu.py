@@ -820,3 +820,56 @@ def test_dpo_drops_fully_truncated_rows_and_prepares_datasets_given_to_evaluate(
     tr.train()
     assert tr.evaluate(eval_dataset=held_out)["eval_loss"] is not None
     assert "eval_x_loss" in tr.evaluate()
+
+
+@pytest.mark.parametrize("kind", ["sft", "reward", "kto"])
+def test_evaluate_accepts_raw_datasets_and_dicts_of_them(tmp_path, tiny_tokenizer, kind):
+    """`evaluate(eval_dataset=...)` takes unprepared rows, a dict / DatasetDict of them, or the name of a dataset given at
+    construction (tests/test_reward_trainer.py:161-187, tests/test_kto_trainer.py:366-404, the same case for SFT)."""
+    from datasets import DatasetDict
+
+    common = dict(output_dir=str(tmp_path), report_to="none", use_cpu=True, bf16=False, per_device_train_batch_size=4,
+                  per_device_eval_batch_size=4, save_strategy="no", max_steps=1)
+    if kind == "sft":
+        cls, cfg, data = SFTTrainer, SFTConfig(**common), "standard_prompt_completion"
+        model = make_tiny_model()
+    elif kind == "reward":
+        cls, cfg, data = RewardTrainer, RewardConfig(**common), "standard_implicit_prompt_preference"
+        model = make_tiny_model(num_labels=1)
+    else:
+        cls, cfg, data = KTOTrainer, KTOConfig(**common), "standard_unpaired_preference"
+        model = make_tiny_model()
+    train, held_out = make_dataset(data, 16), make_dataset(data, 8)
+    kw = dict(train_dataset=train, eval_dataset={"a": held_out}, processing_class=tiny_tokenizer)
+    tr = cls(model, cfg, **kw) if kind != "kto" else cls(model, None, cfg, **kw)
+    assert tr.evaluate(eval_dataset=held_out)["eval_loss"] is not None
+    for given in ({"d1": held_out, "d2": held_out}, DatasetDict({"d1": held_out, "d2": held_out})):
+        m = tr.evaluate(eval_dataset=given)
+        assert m["eval_d1_loss"] == pytest.approx(m["eval_d2_loss"])
+    assert "eval_a_loss" in tr.evaluate() and "eval_a_loss" in tr.evaluate(eval_dataset="a")
+
+
+@pytest.mark.parametrize("loss_type", ["kto", "apo_zero_unpaired"])
+def test_kto_precomputed_reference_log_probs_match_the_live_reference(tmp_path, tiny_tokenizer, loss_type):
+    """With `precompute_ref_log_probs` the datasets carry ref_logps (and ref_KL_logps for the KL estimate), no reference
+    copy is kept, and the first losses equal those of a run with a live reference (tests/test_kto_trainer.py:299-334,
+    :406-426)."""
+    def run(sub, **kw):
+        cfg = KTOConfig(output_dir=str(tmp_path / sub), report_to="none", use_cpu=True, bf16=False, loss_type=loss_type,
+                        per_device_train_batch_size=4, per_device_eval_batch_size=4, save_strategy="no", max_steps=2,
+                        logging_steps=1, learning_rate=1e-4, train_sampling_strategy="sequential", **kw)
+        tr = KTOTrainer(make_tiny_model(seed=0), None, cfg, train_dataset=make_dataset("standard_unpaired_preference", 16),
+                        eval_dataset=make_dataset("standard_unpaired_preference", 8), processing_class=tiny_tokenizer)
+        tr.train()
+        return tr
+
+    live, pre = run("live"), run("pre", precompute_ref_log_probs=True)
+    assert pre.ref_model is None and "ref_logps" in pre.train_dataset.column_names
+    assert ("ref_KL_logps" in pre.train_dataset.column_names) == (loss_type == "kto")
+    assert "ref_logps" in pre.eval_dataset.column_names
+    a = [h["loss"] for h in live.state.log_history if "loss" in h]
+    b = [h["loss"] for h in pre.state.log_history if "loss" in h]
+    assert a == pytest.approx(b, abs=1e-5)
+    with pytest.raises(ValueError, match="Cannot compute reference log-probs"):
+        pre.evaluate(eval_dataset=make_dataset("standard_unpaired_preference", 8))
+    assert pre.evaluate()["eval_loss"] is not None

@@ -787,6 +787,17 @@ class Trainer:
         return loss.detach(), None, None
 
     def evaluate(self, eval_dataset=None, ignore_keys=None, metric_key_prefix: str = "eval"):
+        if isinstance(eval_dataset, str):  # the name of one of the datasets given at construction
+            eval_dataset, metric_key_prefix = self.eval_dataset[eval_dataset], f"{metric_key_prefix}_{eval_dataset}"
+        elif eval_dataset is not None:
+            if isinstance(eval_dataset, dict):  # also DatasetDict / IterableDatasetDict
+                out = {}
+                for name, ds in eval_dataset.items():
+                    out.update(self.evaluate(ds, ignore_keys, f"{metric_key_prefix}_{name}"))
+                return out
+            prepare = getattr(self, "_prepare_given_eval_dataset", None)
+            if prepare is not None:  # raw rows get the preparation of the trainer's constructor (a no-op on prepared rows)
+                eval_dataset = prepare(eval_dataset)
         if eval_dataset is None and isinstance(self.eval_dataset, dict):
             out = {}
             for name, ds in self.eval_dataset.items():

@@ -142,7 +142,10 @@ class KTOTrainer(Trainer):
         with D.main_process_first():
             if train_dataset is not None:
                 train_dataset = self._prepare_dataset(train_dataset, tok, args, args.per_device_train_batch_size, True)
-            if eval_dataset is not None:
+            if isinstance(eval_dataset, dict):
+                eval_dataset = {k: self._prepare_dataset(v, tok, args, args.per_device_eval_batch_size, False)
+                                for k, v in eval_dataset.items()}
+            elif eval_dataset is not None:
                 eval_dataset = self._prepare_dataset(eval_dataset, tok, args, args.per_device_eval_batch_size, False)
         super().__init__(optimizers=optimizers, model=model, args=args, data_collator=data_collator, train_dataset=train_dataset,
                          eval_dataset=eval_dataset, processing_class=tok, callbacks=callbacks,
@@ -153,13 +156,66 @@ class KTOTrainer(Trainer):
             self.ref_model = ref_model.to(self.args.device, dtype=self.model.dtype).eval().requires_grad_(False)
         elif getattr(self.model, "peft_config", None) is not None:
             self.ref_model, self._ref_adapter_off = None, True
+        elif args.precompute_ref_log_probs:
+            self.ref_model = None  # the policy before training is the reference; its log-probs are computed below
         else:
             self.ref_model = copy.deepcopy(self.model).eval().requires_grad_(False)
+        self.precompute_ref_log_probs = args.precompute_ref_log_probs
+        if self.precompute_ref_log_probs:  # the reference is evaluated once over the datasets, before any update
+            if args.sync_ref_model:
+                raise ValueError("sync_ref_model and precompute_ref_log_probs cannot both be enabled")
+            self.train_dataset = self._precompute_ref_logps(self.train_dataset, args.per_device_train_batch_size)
+            if isinstance(self.eval_dataset, dict):
+                self.eval_dataset = {k: self._precompute_ref_logps(v, args.per_device_eval_batch_size)
+                                     for k, v in self.eval_dataset.items()}
+            elif self.eval_dataset is not None:
+                self.eval_dataset = self._precompute_ref_logps(self.eval_dataset, args.per_device_eval_batch_size)
         if args.sync_ref_model and self.ref_model is not None:
             from .callbacks import SyncRefModelCallback
 
             self.add_callback(SyncRefModelCallback(ref_model=self.ref_model))
         self._num_tokens = 0.0
+
+    def _prepare_given_eval_dataset(self, dataset):
+        ds = self._prepare_dataset(dataset, self.processing_class, self.args, self.args.per_device_eval_batch_size, False)
+        if self.precompute_ref_log_probs and "ref_logps" not in next(iter(ds)):
+            if self.ref_model is None and not self._ref_adapter_off and self.state.global_step > 0:
+                raise ValueError("Cannot compute reference log-probs for a dataset passed to `evaluate()` after training "
+                                 "has started: with `precompute_ref_log_probs=True` and no `ref_model` the reference is the "
+                                 "policy before training.")
+            ds = self._precompute_ref_logps(ds, self.args.per_device_eval_batch_size)
+        return ds
+
+    def _precompute_ref_logps(self, dataset, batch_size):
+        """Adds ``ref_logps`` (and ``ref_KL_logps`` for the KL estimate) computed with the reference model in batches of
+        ``batch_size`` rows, the rows in dataset order so the KL rotation stays inside its batch
+        (kto_trainer.py ``precompute_ref_log_probs``)."""
+        if dataset is None or not hasattr(dataset, "__len__"):
+            raise ValueError("precompute_ref_log_probs needs a map-style dataset (its length must be known)")
+        ref = self.ref_model if self.ref_model is not None else self.model
+        was_training = ref.training
+        ref.eval()
+        rows = [dataset[i] for i in range(len(dataset))]
+        lps, kls = [], []
+        with torch.no_grad():
+            for s in range(0, len(rows), batch_size):
+                b = self._prepare_inputs(self.data_collator(rows[s:s + batch_size]))
+                lp, _, _ = self._seq_logps(ref, b["input_ids"], b["attention_mask"], b["completion_mask"],
+                                           adapter_off=self._ref_adapter_off)
+                lps.append(lp.float().cpu())
+                if self.calculate_KL and "KL_input_ids" in b:
+                    kl, _, _ = self._seq_logps(ref, b["KL_input_ids"], b["KL_attention_mask"], b["KL_completion_mask"],
+                                               adapter_off=self._ref_adapter_off)
+                    kls.append(kl.float().cpu())
+        ref.train(was_training)
+        cols = {"ref_logps": torch.cat(lps).tolist()}
+        if kls:
+            cols["ref_KL_logps"] = torch.cat(kls).tolist()
+        if hasattr(dataset, "add_column"):
+            for k, v in cols.items():
+                dataset = dataset.add_column(k, v)
+            return dataset
+        return [{**r, **{k: v[i] for k, v in cols.items()}} for i, r in enumerate(rows)]
 
     def _prepare_dataset(self, dataset, tok, args, batch_size, is_train):
         first = next(iter(dataset))

@@ -112,6 +112,9 @@ class RewardTrainer(Trainer):
         self.model_accepts_loss_kwargs = False
         self._num_tokens = 0.0
 
+    def _prepare_given_eval_dataset(self, dataset):
+        return self._prepare_dataset(dataset, self.processing_class, self.args)
+
     def _prepare_dataset(self, dataset, tok, args):
         first = next(iter(dataset))
         if "chosen_ids" in first:

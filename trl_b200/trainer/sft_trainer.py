@@ -251,6 +251,7 @@ class SFTTrainer(Trainer):
         if args.packing and args.packing_strategy == "wrapped" and args.padding_free:
             warnings.warn("'wrapped' packing has no document boundaries: padding_free has no effect on attention.")
         skip = (args.dataset_kwargs or {}).get("skip_prepare_dataset", False) or self._is_vlm
+        self._skip_prepare, self._formatting_func = skip, formatting_func
         if not skip:
             with D.main_process_first():
                 if train_dataset is not None:
@@ -280,6 +281,14 @@ class SFTTrainer(Trainer):
             self.maybe_activation_offload_context = contextlib.nullcontext()
 
     # ---- dataset ---------------------------------------------------------------------------------
+    def _prepare_given_eval_dataset(self, dataset):
+        if self._skip_prepare:
+            return dataset
+        a = self.args
+        tok = getattr(self.processing_class, "tokenizer", self.processing_class)
+        return self._prepare_dataset(dataset, tok, a, a.packing if a.eval_packing is None else a.eval_packing,
+                                     self._formatting_func, "eval")
+
     def _prepare_dataset(self, dataset, tok, args: SFTConfig, packing: bool, formatting_func, name: str):
         fmt = getattr(dataset, "format", None)
         if isinstance(fmt, dict) and fmt.get("type") == "custom":
